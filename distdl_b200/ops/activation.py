@@ -1,0 +1,121 @@
+"""SwiGLU, GELU and rotary-embedding kernels (new relative to the reference,
+which has no activation or attention code; they are required by the
+GPT-2 / Llama / Mixtral model shapes)."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import _native
+from ._util import stream_ptr, use_native
+
+
+class _SwiGLUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        F = gu.shape[-1] // 2
+        g2 = gu.reshape(-1, 2 * F)
+        if not g2.is_contiguous():
+            g2 = g2.contiguous()
+        out = torch.empty(g2.shape[0], F, dtype=gu.dtype, device=gu.device)
+        _native.call("dd_swiglu_fwd", g2.data_ptr(), out.data_ptr(), g2.shape[0], F, stream_ptr())
+        ctx.save_for_backward(g2)
+        ctx.shape = gu.shape
+        return out.view(*gu.shape[:-1], F)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (g2,) = ctx.saved_tensors
+        F = g2.shape[-1] // 2
+        d2 = dout.reshape(-1, F)
+        if not d2.is_contiguous():
+            d2 = d2.contiguous()
+        dgu = torch.empty_like(g2)
+        _native.call("dd_swiglu_bwd", d2.data_ptr(), g2.data_ptr(), dgu.data_ptr(), g2.shape[0], F, stream_ptr())
+        return dgu.view(ctx.shape)
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up for a tensor whose last dimension is ``[gate | up]``."""
+    F = gate_up.shape[-1] // 2
+    if use_native(gate_up) and gate_up.dtype == torch.bfloat16 and F % 8 == 0:
+        return _SwiGLUFn.apply(gate_up)
+    g, u = gate_up[..., :F], gate_up[..., F:]
+    return torch.nn.functional.silu(g) * u
+
+
+class _GeluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        xc = x.contiguous()
+        y = torch.empty_like(xc)
+        _native.call("dd_gelu_fwd", xc.data_ptr(), y.data_ptr(), xc.numel(), stream_ptr())
+        ctx.save_for_backward(xc)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (xc,) = ctx.saved_tensors
+        dyc = dy.contiguous()
+        dx = torch.empty_like(xc)
+        _native.call("dd_gelu_bwd", dyc.data_ptr(), xc.data_ptr(), dx.data_ptr(), xc.numel(), stream_ptr())
+        return dx
+
+
+def gelu(x: torch.Tensor) -> torch.Tensor:
+    """tanh-approximated GELU (the GPT-2 activation)."""
+    if use_native(x) and x.dtype == torch.bfloat16 and x.numel() % 8 == 0:
+        return _GeluFn.apply(x)
+    return torch.nn.functional.gelu(x, approximate="tanh")
+
+
+_rope_cache = {}
+
+
+def rope_table(seq: int, head_dim: int, theta: float, device) -> torch.Tensor:
+    """[seq, head_dim/2, 2] fp32 table of (cos, sin)."""
+    key = (seq, head_dim, theta, str(device))
+    t = _rope_cache.get(key)
+    if t is None:
+        inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float64) / head_dim))
+        ang = torch.outer(torch.arange(seq, dtype=torch.float64), inv)
+        t = torch.stack([ang.cos(), ang.sin()], dim=-1).float().to(device).contiguous()
+        _rope_cache[key] = t
+    return t
+
+
+class _RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, table, seq, nheads):
+        # qkv: [tokens, heads_total, hd]; rotates heads [0, nheads) in place.
+        ctx.mark_dirty(qkv)
+        tokens, ht, hd = qkv.shape
+        _native.call("dd_rope", qkv.data_ptr(), table.data_ptr(), tokens, seq, ht, nheads, hd, 1.0, stream_ptr())
+        ctx.table, ctx.seq, ctx.nheads = table, seq, nheads
+        return qkv
+
+    @staticmethod
+    def backward(ctx, d):
+        d = d.contiguous()
+        tokens, ht, hd = d.shape
+        _native.call("dd_rope", d.data_ptr(), ctx.table.data_ptr(), tokens, ctx.seq, ht, ctx.nheads, hd, -1.0,
+                     stream_ptr())
+        return d, None, None, None
+
+
+def rope_(qkv: torch.Tensor, seq: int, nheads: int, theta: float = 500000.0) -> torch.Tensor:
+    """Applies rotary position embedding (rotate-half convention) to the first
+    ``nheads`` heads of ``qkv`` [tokens, heads_total, head_dim]; position of a
+    token is its index modulo ``seq``.  In place on CUDA."""
+    tokens, ht, hd = qkv.shape
+    table = rope_table(seq, hd, theta, qkv.device)
+    if use_native(qkv) and qkv.dtype == torch.bfloat16 and hd % 16 == 0 and qkv.is_contiguous():
+        return _RopeFn.apply(qkv, table, seq, nheads)
+    pos = torch.arange(tokens, device=qkv.device) % seq
+    cos = table[pos, :, 0].unsqueeze(1)
+    sin = table[pos, :, 1].unsqueeze(1)
+    x = qkv[:, :nheads].float()
+    a, b = x[..., : hd // 2], x[..., hd // 2:]
+    rot = torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1).to(qkv.dtype)
+    return torch.cat([rot, qkv[:, nheads:]], dim=1)

@@ -1,0 +1,43 @@
+"""Fused AdamW step and sum-of-squares kernels on flat fp32 buffers."""
+from __future__ import annotations
+
+import torch
+
+from .. import _native
+from ._util import ptr, stream_ptr, use_native
+
+
+def adamw_step_(master, m, v, grad, param_bf16, *, lr, beta1, beta2, eps, weight_decay, step,
+                grad_scale_tensor=None, grad_scale=1.0, zero_grad=True):
+    """In-place AdamW on flat fp32 ``master``/``m``/``v`` with fp32 ``grad``;
+    refreshes the bf16 working copy and clears the gradient in the same pass."""
+    n = master.numel()
+    if n == 0:
+        return
+    if use_native(master):
+        _native.call("dd_adamw", master.data_ptr(), m.data_ptr(), v.data_ptr(), grad.data_ptr(), ptr(param_bf16), n,
+                     lr, beta1, beta2, eps, weight_decay, step, ptr(grad_scale_tensor), grad_scale, int(zero_grad),
+                     stream_ptr())
+        return
+    g = grad * grad_scale
+    if grad_scale_tensor is not None:
+        g = g * grad_scale_tensor
+    m.mul_(beta1).add_(g, alpha=1 - beta1)
+    v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
+    bc1 = 1 - beta1 ** step
+    bc2 = 1 - beta2 ** step
+    master.mul_(1 - lr * weight_decay).addcdiv_(m / bc1, (v / bc2).sqrt_().add_(eps), value=-lr)
+    if zero_grad:
+        grad.zero_()
+    if param_bf16 is not None:
+        param_bf16.copy_(master)
+
+
+def sumsq_(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out[0] += sum(x**2) for a flat fp32 tensor."""
+    if x.numel() == 0:
+        return
+    if use_native(x):
+        _native.call("dd_sumsq_f32", x.data_ptr(), x.numel(), out.data_ptr(), stream_ptr())
+    else:
+        out += (x.double() ** 2).sum().float()
