@@ -1,0 +1,56 @@
+"""AllGather along one tensor axis inside a team; adjoint = reduce-scatter.
+Uneven shards follow the balanced rule (first ``n % P`` members hold one more).
+(``src/distdl/backends/nccl_cupy/functional/all_gather.py:86-139``, ``:220-227``.)"""
+from __future__ import annotations
+
+import torch
+
+from ....utilities.slicing import compute_subshape_along_axis
+from ._base import TransportBound, scaled
+
+
+def member_extents(n, P):
+    return [n // P + (1 if i < n % P else 0) for i in range(P)]
+
+
+class AllGatherFunction(TransportBound, torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, input, P_allgather, input_tensor_structure, output_tensor_structure, axes, scale_backward):
+        cls = ctx._forward_cls
+        ctx.P_allgather = P_allgather
+        ctx.axes = axes
+        ctx.scale_backward = scale_backward
+        ctx.input_tensor_structure = input_tensor_structure
+        if not P_allgather.active:
+            return input.clone()
+        axis = int(axes[0])
+        P = P_allgather.size
+        n = int(output_tensor_structure.shape[axis])
+        ext = member_extents(n, P)
+        if int(input.shape[axis]) != ext[P_allgather.rank]:
+            raise ValueError(f"AllGather: local extent {input.shape[axis]} along axis {axis} does not follow the "
+                             f"balanced split of {n} over {P} workers")
+        ctx.extents = ext
+        shapes = None
+        if len(set(ext)) > 1:
+            shapes = []
+            for e in ext:
+                s = list(input.shape)
+                s[axis] = e
+                shapes.append(s)
+        parts = cls.transport().allgather(input.detach(), list(P_allgather.ranks), shapes)
+        out = torch.cat(parts, dim=axis)
+        out.requires_grad_(bool(output_tensor_structure.requires_grad) and out.is_floating_point())
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        cls = ctx._forward_cls
+        P = ctx.P_allgather
+        if not P.active:
+            return grad_output.clone(), None, None, None, None, None
+        axis = int(ctx.axes[0])
+        g = scaled(grad_output, ctx.scale_backward).detach()
+        chunks = list(torch.split(g, ctx.extents, dim=axis))
+        out = cls.transport().reduce_scatter(chunks, list(P.ranks))
+        return out, None, None, None, None, None

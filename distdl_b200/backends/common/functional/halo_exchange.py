@@ -1,0 +1,92 @@
+"""HaloExchange: neighbours on a Cartesian grid swap boundary slabs, one
+dimension after another so that corners propagate.  Adjoint: dimensions in
+reverse; ghost gradients travel back, are added into the bulk and cleared.
+(``src/distdl/backends/mpi_numpy/functional/halo_exchange.py:46-72``, ``:110-138``.)
+
+``slices[d] = (left_bulk, left_ghost, right_bulk, right_ghost)`` (nd-slices of
+the local tensor), ``neighbor_ranks[d] = (left, right)`` as *world* ranks or
+``PROC_NULL``."""
+from __future__ import annotations
+
+import torch
+
+from ..world import PROC_NULL
+from ._base import TransportBound
+
+
+def _volume(sl):
+    v = 1
+    for s in sl:
+        v *= max(0, s.stop - s.start)
+    return v
+
+
+def _shape(sl):
+    return tuple(max(0, s.stop - s.start) for s in sl)
+
+
+class HaloExchangeFunction(TransportBound, torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, input, P_x, slices, buffers, neighbor_ranks):
+        cls = ctx._forward_cls
+        ctx.P_x, ctx.slices, ctx.neighbor_ranks = P_x, slices, neighbor_ranks
+        if not P_x.active or P_x.size == 1:
+            ctx.identity = True
+            return input
+        ctx.identity = False
+        t = cls.transport()
+        out = input.detach().clone()
+        for d in range(P_x.dim):
+            lb, lg, rb, rg = slices[d]
+            left, right = neighbor_ranks[d]
+            sends, recvs, targets = [], [], []
+            if left != PROC_NULL:
+                if _volume(lb):
+                    sends.append((left, out[lb]))
+                if _volume(lg):
+                    recvs.append((left, _shape(lg), out.dtype))
+                    targets.append(lg)
+            if right != PROC_NULL:
+                if _volume(rb):
+                    sends.append((right, out[rb]))
+                if _volume(rg):
+                    recvs.append((right, _shape(rg), out.dtype))
+                    targets.append(rg)
+            got = t.exchange(sends, recvs)
+            for sl, g in zip(targets, got):
+                out[sl] = g.to(out.device)
+        out.requires_grad_(input.requires_grad)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        if ctx.identity:
+            return grad_output, None, None, None, None
+        cls = ctx._forward_cls
+        P_x, slices, neighbor_ranks = ctx.P_x, ctx.slices, ctx.neighbor_ranks
+        t = cls.transport()
+        g = grad_output.detach().clone()
+        for d in reversed(range(P_x.dim)):
+            lb, lg, rb, rg = slices[d]
+            left, right = neighbor_ranks[d]
+            sends, recvs, targets = [], [], []
+            if left != PROC_NULL:
+                if _volume(lg):
+                    sends.append((left, g[lg].clone()))
+                if _volume(lb):
+                    recvs.append((left, _shape(lb), g.dtype))
+                    targets.append(lb)
+            if right != PROC_NULL:
+                if _volume(rg):
+                    sends.append((right, g[rg].clone()))
+                if _volume(rb):
+                    recvs.append((right, _shape(rb), g.dtype))
+                    targets.append(rb)
+            got = t.exchange(sends, recvs)
+            if left != PROC_NULL and _volume(lg):
+                g[lg] = 0
+            if right != PROC_NULL and _volume(rg):
+                g[rg] = 0
+            for sl, r in zip(targets, got):
+                g[sl] += r.to(g.device)
+        return g, None, None, None, None

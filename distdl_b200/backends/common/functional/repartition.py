@@ -1,0 +1,78 @@
+"""Repartition: generalised all-to-all between two Cartesian decompositions of
+the same global tensor.  Adjoint: the reverse repartition.
+(``src/distdl/backends/nccl_cupy/functional/repartition.py:116-205``, ``:282-343``.)
+
+Each overlap entry is ``(slices, shape, partner)`` with ``partner`` a world
+rank, ``"self"`` for the locally copied overlap, or all ``None`` when the two
+sub-tensors do not intersect.  Whether the result needs a gradient is agreed
+once at set-up (the reference broadcasts that flag from the host on every
+call)."""
+from __future__ import annotations
+
+import torch
+
+from ._base import TransportBound, empty_output
+
+
+def _move(transport, src_tensor, out_shape, out_dtype, send_overlaps, recv_overlaps, device):
+    sends = [(partner, src_tensor[sl]) for sl, sh, partner in send_overlaps
+             if sl is not None and partner != "self"]
+    recvs = [(partner, sh, out_dtype) for sl, sh, partner in recv_overlaps
+             if sl is not None and partner != "self"]
+    got = transport.exchange(sends, recvs)
+    out = None
+    if out_shape is not None:
+        out = torch.zeros(tuple(int(s) for s in out_shape), dtype=out_dtype, device=device)
+        k = 0
+        for sl, sh, partner in recv_overlaps:
+            if sl is None:
+                continue
+            if partner == "self":
+                src_sl = next(s for s, _, p in send_overlaps if p == "self")
+                out[sl] = src_tensor[src_sl]
+            else:
+                out[sl] = got[k].to(device)
+                k += 1
+    return out
+
+
+class RepartitionFunction(TransportBound, torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, input, P_union, x_global_structure, x_local_structure, y_local_structure, P_x,
+                P_x_to_y_overlaps, P_x_to_y_buffers, P_y, P_y_to_x_overlaps, P_y_to_x_buffers, preserve_batch):
+        cls = ctx._forward_cls
+        device = input.device
+        ctx.args = (P_union, x_global_structure, x_local_structure, y_local_structure, P_x, P_x_to_y_overlaps,
+                    P_y, P_y_to_x_overlaps, preserve_batch)
+        ctx.device = device
+        if not P_union.active:
+            return empty_output(input, preserve_batch, device)
+        sends = P_x_to_y_overlaps if P_x.active else []
+        recvs = P_y_to_x_overlaps if P_y.active else []
+        out_shape = y_local_structure.shape if P_y.active else None
+        out = _move(cls.transport(), input.detach(), out_shape, x_global_structure.dtype, sends, recvs, device)
+        if out is None:
+            b = input.shape[0] if (preserve_batch and input.dim() > 0) else None
+            from ....utilities.torch import zero_volume_tensor
+            out = zero_volume_tensor(b, dtype=x_global_structure.dtype, device=device)
+        out.requires_grad_(bool(x_global_structure.requires_grad) and out.is_floating_point())
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        cls = ctx._forward_cls
+        (P_union, x_global_structure, x_local_structure, y_local_structure, P_x, P_x_to_y_overlaps, P_y,
+         P_y_to_x_overlaps, preserve_batch) = ctx.args
+        device = ctx.device
+        none = (None,) * 11
+        if not P_union.active:
+            return (empty_output(grad_output, preserve_batch, device),) + none
+        sends = P_y_to_x_overlaps if P_y.active else []
+        recvs = P_x_to_y_overlaps if P_x.active else []
+        out_shape = x_local_structure.shape if P_x.active else None
+        g = _move(cls.transport(), grad_output.detach(), out_shape, x_global_structure.dtype, sends, recvs, device)
+        if g is None:
+            from ....utilities.torch import zero_volume_tensor
+            b = grad_output.shape[0] if (preserve_batch and grad_output.dim() > 0) else None
+            g = zero_volume_tensor(b, dtype=x_global_structure.dtype, device=device)
+        return (g,) + none

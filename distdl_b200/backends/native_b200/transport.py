@@ -1,0 +1,53 @@
+"""Transport of the native backend.
+
+CUDA tensors of a supported dtype move through this library's own kernels
+(:mod:`distdl_b200.parallel.collectives`): one-shot / two-shot all-reduce,
+all-gather, reduce-scatter and all-to-all that read and write the peers'
+symmetric buffers directly over NVLink.  Anything else (CPU tensors, exotic
+dtypes, teams that span more than one node) falls through to the NCCL
+group transport.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..common import world
+from ..common.transport import GroupTransport
+
+
+class NativeTransport(GroupTransport):
+    name = "native"
+
+    def __init__(self):
+        super().__init__()
+        self._coll = None
+
+    def _collectives(self):
+        if self._coll is None:
+            from ...parallel import collectives
+            self._coll = collectives
+        return self._coll
+
+    def prepare(self, ranks):
+        import torch.distributed as dist
+        if dist.is_initialized() and len(ranks) > 1 and torch.cuda.is_available():
+            self._collectives().team(ranks)
+
+    def _native_ok(self, t, ranks):
+        return (t.is_cuda and len(ranks) > 1 and t.dtype in (torch.bfloat16, torch.float32, torch.float16)
+                and self._collectives().available(ranks))
+
+    def allreduce(self, tensor, ranks):
+        if self._native_ok(tensor, ranks):
+            return self._collectives().all_reduce(tensor, ranks)
+        return super().allreduce(tensor, ranks)
+
+    def allgather(self, tensor, ranks, shapes=None):
+        if shapes is None and self._native_ok(tensor, ranks):
+            return list(self._collectives().all_gather(tensor, ranks).unbind(0))
+        return super().allgather(tensor, ranks, shapes)
+
+    def reduce_scatter(self, chunks, ranks):
+        if self._native_ok(chunks[0], ranks) and len({tuple(c.shape) for c in chunks}) == 1:
+            return self._collectives().reduce_scatter(torch.stack([c.contiguous() for c in chunks]), ranks)
+        return super().reduce_scatter(chunks, ranks)

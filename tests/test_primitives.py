@@ -1,0 +1,254 @@
+"""Adjoint and value tests of the seven primitives on CPU ranks (gloo)."""
+import numpy as np
+import pytest
+import torch
+
+from dist_harness import run_ranks
+
+
+def _P(world_ranks, shape):
+    import distdl_b200 as d
+    P_world = d.backends.backend.Partition()
+    P_base = P_world.create_partition_inclusive(world_ranks)
+    return P_base.create_cartesian_topology_partition(shape)
+
+
+# ------------------------------------------------------------------ broadcast
+def body_broadcast(rank, world, P_x_ranks, P_x_shape, P_y_ranks, P_y_shape, tsrc, tdst, x_shape):
+    from adjoint_test import check_adjoint_test_tight
+    from distdl_b200.nn import Broadcast
+    from distdl_b200.utilities.torch import zero_volume_tensor
+    torch.manual_seed(rank)
+    P_x, P_y = _P(P_x_ranks, P_x_shape), _P(P_y_ranks, P_y_shape)
+    layer = Broadcast(P_x, P_y, transpose_src=tsrc, transpose_dest=tdst, preserve_batch=False)
+    x = zero_volume_tensor()
+    if P_x.active:
+        x = torch.randn(*x_shape, dtype=torch.float64)
+    x.requires_grad = True
+    y = layer(x)
+    dy = zero_volume_tensor()
+    if P_y.active:
+        assert tuple(y.shape) == tuple(x_shape)
+        dy = torch.randn(*x_shape, dtype=torch.float64)
+    y.backward(dy)
+    dx = x.grad
+    check_adjoint_test_tight(x.detach(), dx, y.detach(), dy)
+    return True
+
+
+BCAST_CASES = [
+    # P_x ranks, shape, P_y ranks, shape, transpose_src, transpose_dest, x shape
+    ([0], [1], [0, 1, 2, 3], [2, 2], False, False, [3, 5]),
+    ([0, 1], [1, 2], [0, 1, 2, 3], [2, 2], False, False, [3, 5]),
+    ([0, 1], [2, 1], [0, 1, 2, 3], [2, 2], False, False, [4, 2]),
+    ([0, 1], [2], [2, 3, 0, 1], [2, 2], False, False, [4]),      # disjoint-ish ordering
+    ([2, 3], [2], [0, 1, 2, 3], [2, 2], False, False, [4]),      # overlapping, roots not first
+    ([0, 1], [1, 2], [0, 1, 2, 3], [2, 2], True, False, [3]),    # transposed source
+    ([0, 1, 2, 3], [2, 2], [0, 1, 2, 3], [2, 2], False, False, [3]),  # identity
+    ([0], [1], [1, 2], [2], False, False, [6]),                  # disjoint
+]
+
+
+@pytest.mark.parametrize("case", BCAST_CASES)
+def test_broadcast_adjoint(case):
+    run_ranks("test_primitives", "body_broadcast", 4, case)
+
+
+def body_sum_reduce(rank, world, P_x_ranks, P_x_shape, P_y_ranks, P_y_shape, tsrc, tdst, x_shape):
+    from adjoint_test import check_adjoint_test_tight
+    from distdl_b200.nn import SumReduce
+    from distdl_b200.utilities.torch import zero_volume_tensor
+    torch.manual_seed(rank)
+    P_x, P_y = _P(P_x_ranks, P_x_shape), _P(P_y_ranks, P_y_shape)
+    layer = SumReduce(P_x, P_y, transpose_src=tsrc, transpose_dest=tdst, preserve_batch=False)
+    x = zero_volume_tensor()
+    if P_x.active:
+        x = torch.randn(*x_shape, dtype=torch.float64)
+    x.requires_grad = True
+    y = layer(x)
+    dy = zero_volume_tensor()
+    if P_y.active:
+        assert tuple(y.shape) == tuple(x_shape)
+        dy = torch.randn(*x_shape, dtype=torch.float64)
+    y.backward(dy)
+    check_adjoint_test_tight(x.detach(), x.grad, y.detach(), dy)
+    return True
+
+
+@pytest.mark.parametrize("case", [
+    ([0, 1, 2, 3], [2, 2], [0], [1], False, False, [3, 5]),
+    ([0, 1, 2, 3], [2, 2], [0, 1], [1, 2], False, False, [3, 5]),
+    ([0, 1, 2, 3], [2, 2], [2, 3], [2, 1], False, False, [3]),
+    ([0, 1, 2, 3], [2, 2], [0, 1], [1, 2], False, True, [3]),
+    ([1, 2], [2], [0], [1], False, False, [6]),
+])
+def test_sum_reduce_adjoint(case):
+    run_ranks("test_primitives", "body_sum_reduce", 4, case)
+
+
+# ------------------------------------------------- all-reduce / gather / scatter
+def body_team_collectives(rank, world):
+    from adjoint_test import check_adjoint_test_tight
+    from distdl_b200.nn import AllGather, AllSumReduce, ReduceScatter
+    torch.manual_seed(100 + rank)
+    P = _P([0, 1, 2, 3], [2, 2])
+    # AllSumReduce over axis 1: rows {0,1} and {2,3}
+    layer = AllSumReduce(P, axes_reduce=(1,))
+    x = torch.randn(3, 4, dtype=torch.float64, requires_grad=True)
+    y = layer(x)
+    dy = torch.randn(3, 4, dtype=torch.float64)
+    y.backward(dy)
+    check_adjoint_test_tight(x.detach(), x.grad, y.detach(), dy)
+    # value check: ranks in one row agree
+    import torch.distributed as dist
+    rows = [torch.zeros(3, 4, dtype=torch.float64) for _ in range(4)]
+    dist.all_gather(rows, y.detach())
+    assert torch.allclose(rows[0], rows[1]) and torch.allclose(rows[2], rows[3])
+    assert not torch.allclose(rows[0], rows[2])
+
+    # AllGather along tensor axis 1 with an uneven global extent (7 over 2 workers)
+    ext = 4 if P.index[1] == 0 else 3
+    ag = AllGather(P, axes_all_gather=(1,))
+    x = torch.randn(5, ext, dtype=torch.float64, requires_grad=True)
+    y = ag(x)
+    assert tuple(y.shape) == (5, 7)
+    dy = torch.randn(5, 7, dtype=torch.float64)
+    y.backward(dy)
+    check_adjoint_test_tight(x.detach(), x.grad, y.detach(), dy)
+    assert torch.equal(y.detach()[:, :4] if P.index[1] == 0 else y.detach()[:, 4:], x.detach())
+
+    # ReduceScatter along axis 0 (9 rows over 2 workers -> 5 / 4)
+    rs = ReduceScatter(P, axes_reduce_scatter=(0,))
+    x = torch.randn(9, 3, dtype=torch.float64, requires_grad=True)
+    y = rs(x)
+    assert tuple(y.shape) == ((5, 3) if P.index[0] == 0 else (4, 3))
+    dy = torch.randn(*y.shape, dtype=torch.float64)
+    y.backward(dy)
+    check_adjoint_test_tight(x.detach(), x.grad, y.detach(), dy)
+    # scale_backward divides the gradient
+    layer = AllSumReduce(P, axes_reduce=(0, 1), scale_backward=4)
+    x = torch.ones(2, dtype=torch.float64, requires_grad=True)
+    layer(x).sum().backward()
+    assert torch.allclose(x.grad, torch.ones(2, dtype=torch.float64))
+    return True
+
+
+def test_team_collectives():
+    run_ranks("test_primitives", "body_team_collectives", 4)
+
+
+# ---------------------------------------------------------------- repartition
+def body_repartition(rank, world, P_x_ranks, P_x_shape, P_y_ranks, P_y_shape, gshape, balanced):
+    from adjoint_test import check_adjoint_test_tight
+    from distdl_b200.nn import Repartition
+    from distdl_b200.utilities.slicing import compute_start_index, compute_subshape
+    from distdl_b200.utilities.torch import zero_volume_tensor
+    P_x, P_y = _P(P_x_ranks, P_x_shape), _P(P_y_ranks, P_y_shape)
+    layer = Repartition(P_x, P_y, preserve_batch=False)
+    G = torch.arange(int(np.prod(gshape)), dtype=torch.float64).reshape(gshape)
+    x = zero_volume_tensor(dtype=torch.float64)
+    if P_x.active:
+        if balanced:
+            lo = compute_start_index(P_x.shape, P_x.index, gshape)
+            sh = compute_subshape(P_x.shape, P_x.index, gshape)
+        else:  # last worker along dim 0 takes what the others leave (others take 1 row)
+            p0 = int(P_x.shape[0])
+            rows = [1] * (p0 - 1) + [gshape[0] - (p0 - 1)]
+            lo = compute_start_index(P_x.shape, P_x.index, gshape)
+            sh = compute_subshape(P_x.shape, P_x.index, gshape)
+            lo[0] = sum(rows[: int(P_x.index[0])])
+            sh[0] = rows[int(P_x.index[0])]
+        x = G[tuple(slice(int(a), int(a + b)) for a, b in zip(lo, sh))].clone()
+    x.requires_grad = True
+    y = layer(x)
+    dy = zero_volume_tensor(dtype=torch.float64)
+    if P_y.active:
+        lo = compute_start_index(P_y.shape, P_y.index, gshape)
+        sh = compute_subshape(P_y.shape, P_y.index, gshape)
+        want = G[tuple(slice(int(a), int(a + b)) for a, b in zip(lo, sh))]
+        assert torch.equal(y.detach(), want), f"rank {rank}: {y} vs {want}"
+        dy = torch.randn(*want.shape, dtype=torch.float64)
+    y.backward(dy)
+    check_adjoint_test_tight(x.detach(), x.grad, y.detach(), dy)
+    if P_x == P_y:
+        assert all(p in ("self", None) for _, _, p in layer.P_x_to_y_overlaps) or layer.identity
+    return True
+
+
+REPART_CASES = [
+    ([0, 1, 2, 3], [4, 1], [0, 1, 2, 3], [2, 2], [7, 5], True),     # overlapping (the 4x1 -> 2x2 example)
+    ([0, 1], [1, 2], [2, 3], [2, 1], [5, 6], True),                 # disjoint
+    ([0, 1], [2, 1], [3], [1, 1], [5, 4], True),                    # gather with an idle rank
+    ([0], [1, 1], [0, 1, 2, 3], [2, 2], [5, 4], True),              # scatter
+    ([0, 1, 2, 3], [2, 2], [0, 1, 2, 3], [2, 2], [6, 6], True),     # identity
+    ([0, 1, 2], [3, 1], [0, 1, 2, 3], [2, 2], [7, 5], False),       # unbalanced input
+    ([0, 1, 2, 3], [1, 4], [0, 1, 2, 3], [4, 1], [8, 8], True),     # row <-> column transpose
+]
+
+
+@pytest.mark.parametrize("case", REPART_CASES)
+def test_repartition(case):
+    run_ranks("test_primitives", "body_repartition", 4, case)
+
+
+def body_repartition_errors(rank, world):
+    from distdl_b200.nn import Repartition
+    P_x, P_y = _P([0, 1, 2, 3], [2, 2]), _P([0, 1, 2, 3], [4])
+    with pytest.raises(ValueError):
+        Repartition(P_x, P_y)
+    P_y = _P([0, 1, 2, 3], [1, 4])
+    layer = Repartition(P_x, P_y)
+    with pytest.raises(ValueError):
+        layer(torch.zeros(3, 2, 2))       # tensor rank != partition rank
+    P_x1, P_y1 = _P([0], [1, 1]), _P([0, 1], [1, 2])
+    layer = Repartition(P_x1, P_y1)
+    if rank in (0, 1):
+        with pytest.raises(ValueError):
+            layer(torch.zeros(3, 1) if rank == 0 else torch.zeros(0))  # size-1 dim cannot be split
+    return True
+
+
+def test_repartition_errors():
+    run_ranks("test_primitives", "body_repartition_errors", 4)
+
+
+# -------------------------------------------------------------- halo exchange
+def body_halo(rank, world):
+    from adjoint_test import check_adjoint_test_tight
+    from distdl_b200.nn import HaloExchange
+    P = _P([0, 1, 2, 3], [1, 1, 2, 2])
+    halo = np.array([[0, 0], [0, 0], [1, 1], [1, 1]])
+    # ghost regions only exist towards a neighbour
+    idx = P.index
+    halo_local = halo.copy()
+    for d in (2, 3):
+        if idx[d] == 0:
+            halo_local[d][0] = 0
+        if idx[d] == P.shape[d] - 1:
+            halo_local[d][1] = 0
+    layer = HaloExchange(P, halo_local, halo_local, halo_local)
+    bulk = 3
+    shape = [1, 1] + [bulk + halo_local[d][0] + halo_local[d][1] for d in (2, 3)]
+    x = torch.zeros(*shape, dtype=torch.float64)
+    inner = tuple(slice(int(halo_local[d][0]), int(shape[d] - halo_local[d][1])) for d in range(4))
+    x[inner] = float(rank + 1)
+    x.requires_grad = True
+    y = layer(x)
+    yd = y.detach()
+    # every ghost cell now holds the neighbour's value, corners included
+    neigh = {0: {"r": 2, "d": 3, "c": 4}, 1: {"l": 1, "d": 4, "c": 3}, 2: {"r": 4, "u": 1, "c": 2},
+             3: {"l": 3, "u": 2, "c": 1}}[rank]
+    if rank == 0:
+        assert (yd[0, 0, :3, 3] == 2).all() and (yd[0, 0, 3, :3] == 3).all() and yd[0, 0, 3, 3] == 4
+    if rank == 3:
+        assert (yd[0, 0, 1:, 0] == 3).all() and (yd[0, 0, 0, 1:] == 2).all() and yd[0, 0, 0, 0] == 1
+    dy = torch.randn(*shape, dtype=torch.float64)
+    x2 = torch.randn(*shape, dtype=torch.float64, requires_grad=True)
+    y2 = layer(x2)
+    y2.backward(dy)
+    check_adjoint_test_tight(x2.detach(), x2.grad, y2.detach(), dy)
+    return True
+
+
+def test_halo_exchange():
+    run_ranks("test_primitives", "body_halo", 4)
