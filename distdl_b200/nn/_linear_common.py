@@ -1,0 +1,96 @@
+"""Helpers shared by the tensor-parallel linear / expert / embedding layers:
+derived partitions, serial <-> parallel weight re-layouts (fused QKV with or
+without grouped-query heads, GEGLU / SwiGLU halves), prefetch streams.
+
+Layout convention of a fused projection that is split over ``M`` tensor-parallel
+workers along its output features: worker ``p`` stores the blocks
+``[var_0(p) | var_1(p) | ...]`` ("parallel" layout, ``(p v h)``); a serial
+checkpoint stores ``[var_0(all p) | var_1(all p) | ...]`` (``(v p h)``).  The
+reference performs the same conversions with einops patterns
+(``src/distdl/nn/linear_ag.py:275-354``).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..utilities.slicing import compute_subshape, worker_layout
+
+
+def derived_partition(P, index, shape):
+    """Sub-team of Cartesian partition ``P`` selected by the nd ``index`` (tuple
+    of slices into ``worker_layout(P.shape)``), arranged with grid ``shape``."""
+    workers = worker_layout(P.shape)[tuple(index)].reshape(-1).tolist()
+    base = P.create_partition_inclusive(workers)
+    return base.create_cartesian_topology_partition(shape)
+
+
+def root_partition(P):
+    """1-worker Cartesian partition (all dims 1) holding rank 0 of ``P``."""
+    return P.create_partition_inclusive([0]).create_cartesian_topology_partition([1] * P.dim)
+
+
+def split_sizes(n, P):
+    return [int(compute_subshape(P, i, [n])[0]) for i in range(P)]
+
+
+def var_blocks(out_features, num_gpu, num_heads=None, num_heads_kv=None, num_vars=3, geglu=False):
+    """``blocks[p][v]`` = width of variable ``v`` on tensor-parallel worker ``p``."""
+    if num_heads is not None and num_heads_kv is not None:
+        head = out_features // (num_heads + 2 * num_heads_kv)
+        hq, hkv = split_sizes(num_heads, num_gpu), split_sizes(num_heads_kv, num_gpu)
+        return [[hq[p] * head, hkv[p] * head, hkv[p] * head] for p in range(num_gpu)]
+    if num_heads is not None:
+        head = out_features // num_vars // num_heads
+        hq = split_sizes(num_heads, num_gpu)
+        return [[hq[p] * head] * num_vars for p in range(num_gpu)]
+    if geglu:
+        half = split_sizes(out_features // 2, num_gpu)
+        return [[half[p], half[p]] for p in range(num_gpu)]
+    return None
+
+
+def relayout(t, axis, blocks, to_serial):
+    """Re-orders the blocks of ``t`` along ``axis`` between the parallel
+    ``(p v)`` and the serial ``(v p)`` order."""
+    if blocks is None:
+        return t
+    P, V = len(blocks), len(blocks[0])
+    order_par = [(p, v) for p in range(P) for v in range(V)]
+    order_ser = [(p, v) for v in range(V) for p in range(P)]
+    src_order, dst_order = (order_par, order_ser) if to_serial else (order_ser, order_par)
+    sizes = [blocks[p][v] for p, v in src_order]
+    pieces = dict(zip(src_order, torch.split(t, sizes, dim=axis)))
+    return torch.cat([pieces[k] for k in dst_order], dim=axis)
+
+
+def local_out_features(out_features, num_gpu, index, num_heads=None, num_heads_kv=None, num_vars=3, geglu=False):
+    """Output features stored on tensor-parallel worker ``index`` (a whole number
+    of heads / an equal share of each GEGLU half when those are given)."""
+    blocks = var_blocks(out_features, num_gpu, num_heads, num_heads_kv, num_vars, geglu)
+    if blocks is None:
+        return int(compute_subshape(num_gpu, index, [out_features])[0])
+    return int(sum(blocks[index]))
+
+
+class PrefetchStream:
+    """A side stream on which weights are gathered ahead of use.  ``run(fn)``
+    executes ``fn`` on the side stream after everything queued so far on the
+    current stream; ``wait()`` makes the current stream wait for it.  On CPU it
+    degenerates to direct calls."""
+
+    def __init__(self, device):
+        self.stream = None
+        if torch.cuda.is_available() and torch.device(device).type == "cuda":
+            self.stream = torch.cuda.Stream(device=device)
+
+    def run(self, fn):
+        if self.stream is None:
+            return fn()
+        self.stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.stream):
+            return fn()
+
+    def wait(self):
+        if self.stream is not None:
+            torch.cuda.current_stream().wait_stream(self.stream)

@@ -67,6 +67,7 @@ class _Pool:
     def __init__(self, world_size, env):
         ctx = mp.get_context("spawn")
         self.world_size = world_size
+        self.env_key = tuple(sorted(env.items()))
         self.results = ctx.Queue()
         self.jobs = [ctx.Queue() for _ in range(world_size)]
         port = _free_port()
@@ -120,7 +121,6 @@ def run_ranks(module, fn_name, world_size, args=(), timeout=120, env=None):
     pool = _pools.get(key)
     if pool is None:
         pool = _Pool(world_size, env)
-        pool.env_key = key[1]
         _pools[key] = pool
     return pool.run(module, fn_name, args, timeout)
 

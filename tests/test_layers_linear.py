@@ -1,0 +1,248 @@
+"""Linear-family, norm and embedding layers against serial PyTorch on CPU ranks:
+weights are loaded from a serial module through the ``collect_state`` hooks,
+inputs are scattered with Repartition, outputs and input gradients gathered
+back and compared (the reference's vs-serial strategy,
+``tests/layers/test_layernorm.py:143-265``)."""
+import numpy as np
+import pytest
+import torch
+
+from dist_harness import run_ranks
+
+
+def _world():
+    import distdl_b200 as d
+    return d.backends.backend.Partition()
+
+
+def _cart(ranks, shape):
+    P = _world().create_partition_inclusive(ranks)
+    return P.create_cartesian_topology_partition(shape)
+
+
+def _scatter_gather(P_data, gshape_dim):
+    from distdl_b200.nn import Repartition
+    P_root = _cart([0], [1] * gshape_dim)
+    return Repartition(P_root, P_data, preserve_batch=False), Repartition(P_data, P_root, preserve_batch=False), P_root
+
+
+def _run_vs_serial(layer, serial, P_in, P_out, x_global, rank, atol=1e-5, load=True):
+    from distdl_b200.utilities.torch import zero_volume_tensor
+    dim = x_global.dim()
+    scatter, _, P_root = _scatter_gather(P_in, dim)
+    _, gather, _ = _scatter_gather(P_out, dim)
+    gather_dx = _scatter_gather(P_in, dim)[1]
+    if load:
+        sd = serial.state_dict() if P_root.active else {k: zero_volume_tensor() for k in serial.state_dict()}
+        layer.load_state_dict(sd, strict=False)
+    x0 = x_global.clone().requires_grad_() if P_root.active else zero_volume_tensor().requires_grad_()
+    x = scatter(x0)
+    y = layer(x)
+    yg = gather(y)
+    if P_root.active:
+        xs = x_global.clone().requires_grad_()
+        ys = serial(xs)
+        assert yg.shape == ys.shape, (yg.shape, ys.shape)
+        assert torch.allclose(yg, ys, atol=atol, rtol=1e-4), (yg - ys).abs().max()
+        dy = torch.randn_like(ys)
+        ys.backward(dy)
+        yg.backward(dy)
+        assert torch.allclose(x0.grad, xs.grad, atol=atol, rtol=1e-4), (x0.grad - xs.grad).abs().max()
+    else:
+        yg.backward(zero_volume_tensor())
+    # round trip of the state dict in the serial layout
+    out_sd = layer.state_dict()
+    if P_root.active and load:
+        for k, v in serial.state_dict().items():
+            assert torch.allclose(out_sd[k], v), k
+    return True
+
+
+def body_linear_family(rank, world):
+    torch.manual_seed(0)
+    from distdl_b200.nn import (DistributedLinearAllGather, DistributedLinearAllGatherZero,
+                                DistributedLinearReduceScatter, DistributedLinearReduceScatterZero)
+    B, S, Fi, Fo = 4, 6, 16, 24
+    xg = torch.randn(B, S, Fi)
+    serial = torch.nn.Linear(Fi, Fo)
+    P_feat = _cart([0, 1, 2, 3], [2, 1, 2])     # D=2 x M=2, features sharded
+    P_seq = _cart([0, 1, 2, 3], [2, 2, 1])      # sequence sharded (sequence parallel)
+    # column parallel, feature-sharded input and sequence-parallel input
+    for P_x in (P_feat, P_seq):
+        kw = {} if P_x is P_feat else {"P_x": P_x}
+        layer = DistributedLinearAllGather(P_feat, Fi, Fo, collect_state=True, **kw)
+        _run_vs_serial(layer, serial, P_x, P_feat, xg, rank)
+        layer = DistributedLinearAllGatherZero(P_feat, Fi, Fo, collect_state=True, **kw)
+        _run_vs_serial(layer, serial, P_x, P_feat, xg, rank)
+        layer = DistributedLinearAllGatherZero(P_feat, Fi, Fo, collect_state=True, checkpoint=True, **kw)
+        _run_vs_serial(layer, serial, P_x, P_feat, xg, rank)
+    # row parallel, feature- and sequence-sharded output
+    for P_y in (P_feat, P_seq):
+        kw = {} if P_y is P_feat else {"P_y": P_y}
+        layer = DistributedLinearReduceScatter(P_feat, Fi, Fo, collect_state=True, **kw)
+        _run_vs_serial(layer, serial, P_feat, P_y, xg, rank)
+        layer = DistributedLinearReduceScatterZero(P_feat, Fi, Fo, collect_state=True, **kw)
+        _run_vs_serial(layer, serial, P_feat, P_y, xg, rank)
+        layer = DistributedLinearReduceScatterZero(P_feat, Fi, Fo, collect_state=True, checkpoint=True, **kw)
+        _run_vs_serial(layer, serial, P_feat, P_y, xg, rank)
+    # fused QKV with grouped-query heads: serial [q | k | v] <-> per-worker [q_p | k_p | v_p]
+    heads, kv, hd = 4, 2, 2
+    serial = torch.nn.Linear(Fi, (heads + 2 * kv) * hd)
+    layer = DistributedLinearAllGatherZero(P_feat, Fi, (heads + 2 * kv) * hd, collect_state=True, num_heads=heads,
+                                           num_heads_kv=kv)
+    sd = serial.state_dict()
+    from distdl_b200.utilities.torch import zero_volume_tensor
+    layer.load_state_dict(sd if rank == 0 else {k: zero_volume_tensor() for k in sd}, strict=False)
+    out = layer.state_dict()
+    if rank == 0:
+        assert torch.allclose(out["weight"], sd["weight"]) and torch.allclose(out["bias"], sd["bias"])
+    # the local shard holds [q_p | k_p | v_p]: check worker (d=0, m=tp) against the serial rows
+    tp = rank % 2
+    import torch.distributed as dist
+    W = sd["weight"].clone()
+    dist.broadcast(W, src=0)   # ranks drew different random numbers on the way here
+    rows = torch.cat([W[tp * 4:(tp + 1) * 4], W[8 + tp * 2: 8 + (tp + 1) * 2], W[12 + tp * 2: 12 + (tp + 1) * 2]])
+    d = rank // 2
+    local = layer.weight.detach().reshape(Fi // 2, 8)
+    assert torch.allclose(local, rows.t()[d * 8:(d + 1) * 8]), rank
+    return True
+
+
+def test_linear_family_vs_serial():
+    run_ranks("test_layers_linear", "body_linear_family", 4, timeout=300)
+
+
+def body_zero1_mode(rank, world):
+    """auto_clear_buffer=False: gradients accumulate on the gathered weights over
+    two micro-batches and are reduce-scattered once."""
+    torch.manual_seed(0)
+    from distdl_b200.nn import DistributedLinearAllGatherZero
+    Fi, Fo = 8, 12
+    P = _cart([0, 1, 2, 3], [2, 1, 2])
+    a = DistributedLinearAllGatherZero(P, Fi, Fo, auto_clear_buffer=False)
+    b = DistributedLinearAllGatherZero(P, Fi, Fo)
+    b.load_state_dict(a.state_dict())
+    xs = [torch.randn(2, 3, Fi // 2) for _ in range(2)]
+    for x in xs:
+        a(x).sum().backward()
+        b(x).sum().backward()
+    a.clear_weight_buffer()
+    assert torch.allclose(a.weight.grad, b.weight.grad, atol=1e-6)
+    assert torch.allclose(a.bias.grad, b.bias.grad, atol=1e-6)
+    return True
+
+
+def test_zero1_accumulation():
+    run_ranks("test_layers_linear", "body_zero1_mode", 4)
+
+
+def body_config1_mlp(rank, world):
+    """2-layer MLP of DistributedLinear 1024->4096->1024 with GELU and
+    DistributedLayerNorm(1024) on a 2x2 partition, fp32, x ~ N(0,1) [64,1024],
+    MSE loss; forward and backward against the serial model."""
+    torch.manual_seed(0)
+    from distdl_b200.nn import DistributedLayerNorm, DistributedLinear, Repartition
+    from distdl_b200.utilities.torch import zero_volume_tensor
+    P_w = _cart([0, 1, 2, 3], [2, 2])
+    P_x = _cart([0, 1], [1, 2])
+    P_root = _cart([0], [1, 1])
+    l1 = DistributedLinear(P_x, P_x, P_w, 1024, 4096)
+    l2 = DistributedLinear(P_x, P_x, P_w, 4096, 1024)
+    ln = DistributedLayerNorm(P_x, 1024) if rank in (0, 1) else None
+    scatter, gather = Repartition(P_root, P_x, preserve_batch=False), Repartition(P_x, P_root, preserve_batch=False)
+    # serial model with the same weights: gather the blocks onto rank 0
+    gw = Repartition(P_w, P_root, preserve_batch=False)
+
+    def full_weight(layer):
+        return gw(layer.sublinear.weight.detach())
+
+    def full_bias(layer, n):
+        P_col = _cart([0, 2], [2, 1])
+        g = Repartition(P_col, P_root, preserve_batch=False)
+        b = layer.sublinear.bias.detach().reshape(-1, 1) if rank in (0, 2) else zero_volume_tensor()
+        return g(b)
+    W1, W2, b1, b2 = full_weight(l1), full_weight(l2), full_bias(l1, 4096), full_bias(l2, 1024)
+    x_global = torch.randn(64, 1024)
+    target = torch.randn(64, 1024)
+    x0 = x_global.clone().requires_grad_() if rank == 0 else zero_volume_tensor().requires_grad_()
+    x = scatter(x0)
+    h = l1(x)
+    h = torch.nn.functional.gelu(h) if rank in (0, 1) else h
+    h = l2(h)
+    if rank in (0, 1):
+        h = ln(h)
+    y = gather(h)
+    if rank == 0:
+        loss = torch.nn.functional.mse_loss(y, target)
+        loss.backward()
+        xs = x_global.clone().requires_grad_()
+        hs = torch.nn.functional.linear(xs, W1, b1.reshape(-1))
+        hs = torch.nn.functional.linear(torch.nn.functional.gelu(hs), W2, b2.reshape(-1))
+        ys = torch.nn.functional.layer_norm(hs, (1024,))
+        loss_s = torch.nn.functional.mse_loss(ys, target)
+        loss_s.backward()
+        err_y = (y - ys).abs().max().item()
+        err_dx = (x0.grad - xs.grad).abs().max().item()
+        assert err_y < 1e-4 and err_dx < 1e-5, (err_y, err_dx)
+        return (err_y, err_dx)
+    y.backward(torch.zeros_like(y))
+    return None
+
+
+def test_config1_mlp_layernorm_2x2():
+    out = run_ranks("test_layers_linear", "body_config1_mlp", 4, timeout=300)
+    assert out[0] is not None
+
+
+def body_norms_embeddings(rank, world):
+    torch.manual_seed(0)
+    from distdl_b200.nn import (DistributedEmbedding, DistributedEmbeddingZero, DistributedLayerNorm,
+                                DistributedLayerNormZero, DistributedRMSNormZero)
+    from distdl_b200.utilities.torch import zero_volume_tensor
+    B, S, F = 4, 6, 10           # 10 features over 2 workers and over 4 (ZeRO) -> uneven shards
+    xg = torch.randn(B, S, F)
+    P_feat = _cart([0, 1, 2, 3], [2, 1, 2])
+    P_seq = _cart([0, 1, 2, 3], [2, 2, 1])
+    serial = torch.nn.LayerNorm(F)
+    with torch.no_grad():
+        serial.weight.uniform_(0.5, 1.5)
+        serial.bias.uniform_(-0.5, 0.5)
+    for P in (P_feat, P_seq):
+        _run_vs_serial(DistributedLayerNorm(P, F, collect_state=True), serial, P, P, xg, rank)
+    _run_vs_serial(DistributedLayerNormZero(P_seq, F, collect_state=True), serial, P_seq, P_seq, xg, rank)
+
+    class RMS(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.weight = torch.nn.Parameter(torch.rand(F) + 0.5)
+
+        def forward(self, x):
+            return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * self.weight
+    _run_vs_serial(DistributedRMSNormZero(P_seq, F, collect_state=True), RMS(), P_seq, P_seq, xg, rank)
+    with pytest.raises(ValueError):
+        DistributedRMSNormZero(P_feat, F)
+    # embeddings: ids replicated over the tensor-parallel workers, table split
+    V, E = 11, 6
+    import torch.distributed as dist
+    table = torch.randn(V, E)
+    ids = torch.randint(0, V, (B, S))
+    dist.broadcast(table, src=0)   # ranks consumed different amounts of random numbers above
+    dist.broadcast(ids, src=0)
+    P_ids = _cart([0, 1, 2, 3], [2, 2])
+    for cls in (DistributedEmbedding, DistributedEmbeddingZero):
+        layer = cls(P_ids, V, E, collect_state=True)
+        layer.load_state_dict({"weight": table if rank == 0 else zero_volume_tensor()})
+        d, m = rank // 2, rank % 2
+        local_ids = ids[d * 2:(d + 1) * 2]
+        out = layer(local_ids)
+        want = table[local_ids][..., m * 3:(m + 1) * 3]
+        assert torch.allclose(out, want), cls.__name__
+        out.sum().backward()
+        sd = layer.state_dict()
+        if rank == 0:
+            assert torch.allclose(sd["weight"], table)
+    return True
+
+
+def test_norms_and_embeddings():
+    run_ranks("test_layers_linear", "body_norms_embeddings", 4, timeout=300)
