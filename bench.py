@@ -1,0 +1,209 @@
+#!/usr/bin/env python
+"""Headline benchmark: training tokens/s of the Llama-3-8B-shape decoder
+(32 layers, d=4096, 32 heads / 8 KV heads, SwiGLU 14336, RMSNorm, RoPE, vocab
+128256), bf16 parameters with fp32 master weights and AdamW, tensor-parallel
+x ZeRO-3/FSDP on one node.
+
+    python bench.py --gpus N --steps K --warmup W
+    torchrun --nnodes=1 --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
+
+Weak scaling: 8 sequences of 4096 tokens per GPU and step (64 x 4096 at N=8,
+the configuration named by the baseline).  Layout: N=1 -> no parallelism,
+N=2 -> TP=2, N=4 -> TP=2 x FSDP=2, N=8 -> TP=2 x FSDP=4.  Prints one JSON line
+on rank 0.  `value` is device-timed with the token blocks already on the
+device; `e2e` goes through `Trainer.step()` with, every step, the host->device
+copy of the step's tokens from pinned memory and a device->host read of the loss.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "train tokens/sec (8B TP+FSDP, max over ranks)"
+
+
+def reference_arm(args):
+    """The reference (microsoft/distdl) cannot be built or imported offline in
+    this image: report that and exit 0."""
+    why = None
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if os.path.isdir(os.path.join(ref, "distdl")):
+        sys.path.insert(0, ref)
+        try:
+            import distdl  # noqa: F401
+        except Exception as e:  # pragma: no cover
+            why = f"import distdl failed: {type(e).__name__}: {e}"
+        else:
+            why = ("reference imports but has no attention/optimizer/trainer code and needs mpirun to launch; "
+                   "no stock code path produces this metric")
+    else:
+        why = ("offline install failed: its C++ extension does not link here and mpi4py, cupy, pytorch-pfn-extras "
+               "and mpirun are absent, so `import distdl` cannot succeed")
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of this process's GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self._stop = threading.Event()
+        self._t = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
+                if out.returncode == 0 and out.stdout.strip():
+                    self.rows.append([c.strip() for c in out.stdout.strip().splitlines()[0].split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = sorted(float(r[0]) for r in self.rows if r[0].replace(".", "", 1).isdigit())
+        mx = max((float(r[1]) for r in self.rows if r[1].replace(".", "", 1).isdigit()), default=None)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 4 + i and r[4 + i].lower().startswith("active")
+                                                         for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": reasons,
+                "samples": len(self.rows)}
+
+
+def layout_for(n):
+    return {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (4, 2)}[n]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "llama_tiny", "gpt2_xl", "mixtral_8x7b"])
+    ap.add_argument("--seqs-per-gpu", type=int, default=8)
+    ap.add_argument("--micro-batch", type=int, default=0, help="sequences per forward/backward (0 = auto)")
+    ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (invalid as a result)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            # re-launch under torchrun, one rank per GPU
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+                   "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 2000), __file__] + sys.argv[1:]
+            return subprocess.call(cmd)
+        raise SystemExit(f"WORLD_SIZE={world} but --gpus {args.gpus}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+
+    import distdl_b200
+    from distdl_b200 import _native
+    from distdl_b200.backends.common import world as dworld
+    if world > 1:
+        dworld.init_process_group_from_env()
+    rank = dist.get_rank() if world > 1 else 0
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    distdl_b200.config.set_backend("native" if world > 1 else "native", "cupy")
+    from distdl_b200 import models
+    from distdl_b200.parallel import SyntheticTokens, Trainer
+
+    cfg = getattr(models, args.model)()
+    if args.layers:
+        cfg.n_layers = args.layers
+    dp, tp = layout_for(args.gpus)
+    seq = cfg.max_seq
+    global_batch = args.seqs_per_gpu * args.gpus
+    local_batch = global_batch // dp
+    micro = args.micro_batch or (1 if args.gpus == 1 else 2)
+    torch.manual_seed(1234 + rank)
+    layout = models.ParallelLayout(dp, tp)
+    model = models.Decoder(cfg, layout).cuda() if False else models.Decoder(cfg, layout)
+    trainer = Trainer(model, global_tokens_per_step=global_batch * seq, micro_batch=micro, lr=3e-4,
+                      warmup_steps=10, total_steps=1000)
+    data = SyntheticTokens(local_batch, seq, cfg.vocab_size, dp_index=layout.dp_index, seed=0)
+    dev_blocks = [b.cuda() for b in data.blocks]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        l0 = _native.launch_count
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for i in range(steps):
+            fn(i)
+        e.record()
+        barrier()
+        ms = torch.tensor([s.elapsed_time(e)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item(), _native.launch_count - l0
+
+    for i in range(args.warmup):
+        trainer.step_device(dev_blocks[i % len(dev_blocks)])
+    with ClockSampler(local_rank) as clocks:
+        ms_dev, launches = timed(lambda i: trainer.step_device(dev_blocks[i % len(dev_blocks)]), args.steps)
+    losses = []
+    ms_e2e, _ = timed(lambda i: losses.append(trainer.step(data.next()).item()), args.steps)
+    status = _native.read_status()
+
+    tokens_per_step = global_batch * seq
+    value = tokens_per_step * args.steps / (ms_dev / 1e3)
+    e2e = tokens_per_step * args.steps / (ms_e2e / 1e3)
+    if rank == 0:
+        out = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
+            "config": {"model": f"{args.model} ({cfg.num_parameters() / 1e9:.2f}B params)", "global_batch": global_batch,
+                       "seq_len": seq, "parallelism": f"tp{tp} x fsdp{dp}", "micro_batch": micro,
+                       "optimizer": "AdamW fp32 master + moments, grad clip 1.0",
+                       "activation_checkpointing": "per block",
+                       "l2": "per-step working set (>= 16 GB of weights) exceeds the 126 MB L2; no explicit flush"},
+            "clocks": clocks.summary(),
+            "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": data.bytes_per_block, "d2h_bytes_per_step": 4},
+            "gpu_launches": launches, "final_loss": losses[-1] if losses else None, "device_status": status[0],
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,4 @@
+"""Model definitions for the benchmark configurations."""
+from .decoder import Decoder, DecoderConfig, ParallelLayout  # noqa: F401
+from .gpt2 import gpt2_tiny, gpt2_xl  # noqa: F401
+from .llama import llama3_8b, llama_tiny  # noqa: F401

@@ -1,0 +1,235 @@
+"""Decoder-only transformer assembled from the distributed layers.
+
+One class covers the three model families of the benchmark configurations:
+
+* Llama-style: RMSNorm, rotary embedding, grouped-query attention, SwiGLU, no biases;
+* GPT-2-style: LayerNorm, learned positions, multi-head attention, GELU, biases;
+* Mixtral-style: Llama attention with a top-k routed mixture-of-experts FFN.
+
+Parallel layout (``D`` data-parallel x ``M`` tensor-parallel workers):
+activations between blocks are ``[batch / D, seq / M, d]`` (sequence
+parallel); QKV and the first FFN GEMM are column-parallel layers that
+all-gather the sequence, the output projection and second FFN GEMM are
+row-parallel layers that reduce-scatter it back.  With ``zero=True`` every
+weight is additionally sharded over the ``D`` workers (ZeRO-3 / FSDP) and
+gathered on use.  Token embedding, final norm and the LM head work on the
+sequence-sharded tokens as pure data parallelism over all ``D * M`` workers with
+their weights ZeRO-sharded over all of them, so that the loss needs no
+tensor-parallel communication.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.utils.checkpoint
+
+from .. import nn as dnn
+from .. import ops
+from ..utilities.slicing import compute_start_index, compute_subshape
+
+
+@dataclass
+class DecoderConfig:
+    vocab_size: int = 128256
+    d_model: int = 4096
+    n_layers: int = 32
+    n_heads: int = 32
+    n_kv_heads: int = 8
+    ffn_dim: int = 14336
+    max_seq: int = 4096
+    norm: str = "rms"            # "rms" | "layer"
+    activation: str = "swiglu"   # "swiglu" | "gelu"
+    rope: bool = True
+    rope_theta: float = 500000.0
+    bias: bool = False
+    eps: float = 1e-5
+    n_experts: int = 0           # > 0: mixture-of-experts FFN
+    top_k: int = 2
+    capacity_factor: float = 1.25
+    dtype: torch.dtype = torch.bfloat16
+    checkpoint_blocks: bool = True
+    zero: bool = True
+    init_std: float = 0.02
+
+    @property
+    def head_dim(self):
+        return self.d_model // self.n_heads
+
+    def padded_vocab(self, multiple=128):
+        return (self.vocab_size + multiple - 1) // multiple * multiple
+
+    def num_parameters(self):
+        d, f, L = self.d_model, self.ffn_dim, self.n_layers
+        hd = self.head_dim
+        attn = d * (self.n_heads + 2 * self.n_kv_heads) * hd + self.n_heads * hd * d
+        ffn = (3 if self.activation == "swiglu" else 2) * d * f
+        if self.n_experts:
+            ffn = ffn * self.n_experts + d * self.n_experts
+        emb = 2 * self.vocab_size * d + (0 if self.rope else self.max_seq * d)
+        return L * (attn + ffn + 2 * d) + emb + d
+
+
+class ParallelLayout:
+    """The partitions a decoder needs, derived from a ``[D, M]`` worker grid."""
+
+    def __init__(self, dp: int, tp: int, P_world=None):
+        from .. import backends
+        be = backends.backend
+        P_world = P_world if P_world is not None else be.Partition()
+        if dp * tp != P_world.size:
+            raise ValueError(f"dp*tp = {dp * tp} does not match the {P_world.size} workers")
+        base = P_world.create_partition_inclusive(range(P_world.size))
+        self.dp, self.tp = dp, tp
+        self.P_world = P_world
+        self.P_grid = base.create_cartesian_topology_partition([dp, tp])
+        self.P_feat = base.create_cartesian_topology_partition([dp, 1, tp])
+        self.P_seq = base.create_cartesian_topology_partition([dp, tp, 1])
+        self.P_flat = base.create_cartesian_topology_partition([dp * tp, 1, 1])
+        self.P_flat2 = base.create_cartesian_topology_partition([dp * tp, 1])
+        self.dp_index = int(self.P_grid.index[0])
+        self.tp_index = int(self.P_grid.index[1])
+
+
+def _norm(cfg, P, zero):
+    if cfg.norm == "rms":
+        return dnn.DistributedRMSNormZero(P, cfg.d_model, eps=cfg.eps, dtype=cfg.dtype)
+    if zero:
+        return dnn.DistributedLayerNormZero(P, cfg.d_model, eps=cfg.eps, dtype=cfg.dtype)
+    return dnn.DistributedLayerNorm(P, cfg.d_model, eps=cfg.eps, dtype=cfg.dtype)
+
+
+def _col(cfg, layout, fin, fout, **kw):
+    cls = dnn.DistributedLinearAllGatherZero if cfg.zero else dnn.DistributedLinearAllGather
+    return cls(layout.P_feat, fin, fout, bias=cfg.bias, dtype=cfg.dtype, P_x=layout.P_seq, **kw)
+
+
+def _row(cfg, layout, fin, fout):
+    cls = dnn.DistributedLinearReduceScatterZero if cfg.zero else dnn.DistributedLinearReduceScatter
+    return cls(layout.P_feat, fin, fout, bias=cfg.bias, dtype=cfg.dtype, P_y=layout.P_seq)
+
+
+class Attention(torch.nn.Module):
+    def __init__(self, cfg: DecoderConfig, layout: ParallelLayout):
+        super().__init__()
+        self.cfg, self.layout = cfg, layout
+        hd = cfg.head_dim
+        self.hq = int(compute_subshape(layout.tp, layout.tp_index, [cfg.n_heads])[0])
+        self.hkv = int(compute_subshape(layout.tp, layout.tp_index, [cfg.n_kv_heads])[0])
+        self.qkv = _col(cfg, layout, cfg.d_model, (cfg.n_heads + 2 * cfg.n_kv_heads) * hd, num_heads=cfg.n_heads,
+                        num_heads_kv=cfg.n_kv_heads)
+        self.out = _row(cfg, layout, cfg.n_heads * hd, cfg.d_model)
+
+    def forward(self, x):
+        cfg = self.cfg
+        qkv = self.qkv(x)                                     # [b, s, (hq + 2 hkv) * hd]
+        b, s = qkv.shape[0], qkv.shape[1]
+        t = qkv.reshape(b * s, self.hq + 2 * self.hkv, cfg.head_dim)
+        if cfg.rope:
+            t = ops.rope_(t, s, self.hq + self.hkv, cfg.rope_theta)
+        o = ops.attention_packed(t, self.hq, self.hkv, b, s, causal=True)
+        return self.out(o.reshape(b, s, self.hq * cfg.head_dim))
+
+
+class MLP(torch.nn.Module):
+    def __init__(self, cfg: DecoderConfig, layout: ParallelLayout):
+        super().__init__()
+        self.cfg = cfg
+        if cfg.activation == "swiglu":
+            self.up = _col(cfg, layout, cfg.d_model, 2 * cfg.ffn_dim, geglu=True)
+        else:
+            self.up = _col(cfg, layout, cfg.d_model, cfg.ffn_dim)
+        self.down = _row(cfg, layout, cfg.ffn_dim, cfg.d_model)
+
+    def forward(self, x):
+        h = self.up(x)
+        h = ops.swiglu(h) if self.cfg.activation == "swiglu" else ops.gelu(h)
+        return self.down(h)
+
+
+class Block(torch.nn.Module):
+    def __init__(self, cfg: DecoderConfig, layout: ParallelLayout):
+        super().__init__()
+        self.norm1 = _norm(cfg, layout.P_seq, cfg.zero)
+        self.attn = Attention(cfg, layout)
+        self.norm2 = _norm(cfg, layout.P_seq, cfg.zero)
+        if cfg.n_experts:
+            from .moe import MoEFeedForward
+            self.mlp = MoEFeedForward(cfg, layout)
+        else:
+            self.mlp = MLP(cfg, layout)
+
+    def forward(self, x):
+        x = x + self.attn(self.norm1(x))
+        return x + self.mlp(self.norm2(x))
+
+
+class Decoder(torch.nn.Module):
+    """``forward(tokens [b_local, seq]) -> hidden [b_local, seq / M, d]``;
+    ``loss(tokens, targets)`` runs the LM head and the fused cross-entropy."""
+
+    def __init__(self, cfg: DecoderConfig, layout: ParallelLayout):
+        super().__init__()
+        self.cfg, self.layout = cfg, layout
+        V = cfg.padded_vocab()
+        self.padded_vocab = V
+        self.embed = dnn.DistributedEmbeddingZero(layout.P_flat2, V, cfg.d_model, dtype=cfg.dtype)
+        if not cfg.rope:
+            self.pos_embed = dnn.DistributedEmbeddingZero(layout.P_flat2, cfg.max_seq, cfg.d_model, dtype=cfg.dtype)
+        self.blocks = torch.nn.ModuleList(Block(cfg, layout) for _ in range(cfg.n_layers))
+        self.final_norm = _norm(cfg, layout.P_flat, True)
+        self.head = dnn.DistributedLinearAllGatherZero(layout.P_flat, cfg.d_model, V, bias=False, dtype=cfg.dtype)
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        cfg = self.cfg
+        std = cfg.init_std
+        with torch.no_grad():
+            for name, p in self.named_parameters():
+                if p.numel() == 0:
+                    continue
+                if name.endswith("bias"):
+                    p.zero_()
+                elif "norm" in name:
+                    if name.endswith("weight"):
+                        p.fill_(1.0)
+                elif name.endswith("weight"):
+                    s = std / math.sqrt(2 * cfg.n_layers) if (".out." in name or ".down." in name) else std
+                    p.normal_(0.0, s)
+
+    def _local_tokens(self, tokens):
+        """This worker's sequence shard of the (tensor-parallel replicated) token ids."""
+        lay = self.layout
+        s = tokens.shape[1]
+        lo = int(compute_start_index(lay.tp, lay.tp_index, [s])[0])
+        n = int(compute_subshape(lay.tp, lay.tp_index, [s])[0])
+        return tokens[:, lo:lo + n], lo
+
+    def forward(self, tokens):
+        cfg = self.cfg
+        local, lo = self._local_tokens(tokens)
+        x = self.embed(local)
+        if not cfg.rope:
+            pos = torch.arange(lo, lo + local.shape[1], device=tokens.device).unsqueeze(0).expand_as(local)
+            x = x + self.pos_embed(pos)
+        for blk in self.blocks:
+            if cfg.checkpoint_blocks and self.training:
+                x = torch.utils.checkpoint.checkpoint(blk, x, use_reentrant=False)
+            else:
+                x = blk(x)
+        return self.final_norm(x)
+
+    def loss(self, tokens, targets, scale=None):
+        """Sum of this worker's token losses times ``scale`` (default: 1 / local
+        tokens); ``targets`` has the same [b_local, seq] shape as ``tokens``."""
+        h = self.forward(tokens)
+        tl, _ = self._local_tokens(targets)
+        logits = self.head(h)
+        rows = logits.shape[0] * logits.shape[1]
+        logits2 = logits.reshape(rows, logits.shape[-1])
+        return ops.cross_entropy_(logits2, tl.reshape(-1), vocab=cfg_vocab(self.cfg), scale=scale, unit_grad=True)
+
+
+def cfg_vocab(cfg):
+    return cfg.vocab_size

@@ -1,5 +1,5 @@
 """Hand-written sm_100a operators (and their CPU stand-ins for plumbing tests)."""
-from .attention import attention, attention_backward, attention_forward  # noqa: F401
+from .attention import attention, attention_backward, attention_forward, attention_packed  # noqa: F401
 from .activation import gelu, rope_, rope_table, swiglu  # noqa: F401
 from .embedding import embedding  # noqa: F401
 from .gemm import gemm, linear, matmul  # noqa: F401

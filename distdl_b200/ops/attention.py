@@ -106,3 +106,37 @@ def attention(q, k, v, batch: int, seq: int, causal: bool = True, scale: float =
     if native:
         return _AttnFn.apply(q, k, v, batch, seq, causal, scale)
     return _reference(q, k, v, batch, seq, causal, scale)
+
+
+class _PackedAttnFn(torch.autograd.Function):
+    """Attention on a packed ``[tokens, Hq + 2*Hkv, D]`` projection output; the
+    backward kernels write dq / dk / dv straight into one packed gradient."""
+
+    @staticmethod
+    def forward(ctx, qkv, Hq, Hkv, batch, seq, causal, scale):
+        q, k, v = qkv[:, :Hq], qkv[:, Hq:Hq + Hkv], qkv[:, Hq + Hkv:]
+        out, lse = attention_forward(q, k, v, batch, seq, causal, scale)
+        ctx.save_for_backward(qkv, out, lse)
+        ctx.cfg = (Hq, Hkv, batch, seq, causal, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse = ctx.saved_tensors
+        Hq, Hkv, batch, seq, causal, scale = ctx.cfg
+        q, k, v = qkv[:, :Hq], qkv[:, Hq:Hq + Hkv], qkv[:, Hq + Hkv:]
+        dqkv = torch.empty_like(qkv)
+        attention_backward(dout, q, k, v, out, lse, batch, seq, causal, scale, dq=dqkv[:, :Hq],
+                           dk=dqkv[:, Hq:Hq + Hkv], dv=dqkv[:, Hq + Hkv:])
+        return dqkv, None, None, None, None, None, None
+
+
+def attention_packed(qkv, Hq: int, Hkv: int, batch: int, seq: int, causal: bool = True, scale: float = None):
+    """Attention over a packed projection ``[tokens, Hq + 2*Hkv, head_dim]`` (heads
+    ordered q..., k..., v...).  Returns ``[tokens, Hq, head_dim]``."""
+    D = qkv.shape[-1]
+    native = (use_native(qkv) and qkv.dtype == torch.bfloat16 and D in (64, 128) and seq % 128 == 0
+              and qkv.is_contiguous() and os.environ.get("DISTDL_ATTN_IMPL", "native") == "native")
+    if native:
+        return _PackedAttnFn.apply(qkv, Hq, Hkv, batch, seq, causal, scale)
+    return _reference(qkv[:, :Hq], qkv[:, Hq:Hq + Hkv], qkv[:, Hq + Hkv:], batch, seq, causal, scale)

@@ -1,0 +1,4 @@
+"""Symmetric-memory runtime, fused compute+collective kernels, optimizer and
+training drivers."""
+from .optimizer import FlatAdamW, cosine_lr  # noqa: F401
+from .trainer import SyntheticTokens, Trainer  # noqa: F401

@@ -1,0 +1,85 @@
+"""Training step driver: pinned-host input staging, micro-batching with fp32
+gradient accumulation, fused optimizer step, device-side loss."""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .optimizer import FlatAdamW, cosine_lr
+
+
+class Trainer:
+    """``Trainer(model, ...).step(tokens_host)`` runs one optimizer step.
+
+    ``tokens_host`` is this worker's ``[local_batch, seq + 1]`` int64 token block
+    in pinned host memory (tensor-parallel peers of one data-parallel group must
+    be given the same block).  Inputs are ``tokens[:, :-1]``, targets
+    ``tokens[:, 1:]``.  The local batch is cut into ``micro_batch`` sequences
+    per forward/backward.  Returns the mean token loss of the global batch as a
+    device scalar (read it with ``.item()`` when the host needs it).
+    """
+
+    def __init__(self, model, global_tokens_per_step: int, micro_batch: int = 1, lr: float = 3e-4,
+                 weight_decay: float = 0.1, max_grad_norm: float = 1.0, warmup_steps: int = 10,
+                 total_steps: int = 1000, device=None):
+        self.model = model
+        self.micro_batch = micro_batch
+        self.global_tokens = global_tokens_per_step
+        self.opt = FlatAdamW(model, lr=lr, weight_decay=weight_decay, max_grad_norm=max_grad_norm)
+        self.base_lr, self.warmup_steps, self.total_steps = lr, warmup_steps, total_steps
+        self.device = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available()
+                                 else torch.device("cpu"))
+        self._dev_tokens = None
+        self.steps_done = 0
+
+    def stage(self, tokens_host: torch.Tensor) -> torch.Tensor:
+        """Asynchronous host -> device copy into a reused device buffer."""
+        if self._dev_tokens is None or self._dev_tokens.shape != tokens_host.shape:
+            self._dev_tokens = torch.empty(tokens_host.shape, dtype=tokens_host.dtype, device=self.device)
+        self._dev_tokens.copy_(tokens_host, non_blocking=True)
+        return self._dev_tokens
+
+    def step_device(self, tokens: torch.Tensor) -> torch.Tensor:
+        self.model.train()
+        self.opt.set_lr(cosine_lr(self.steps_done, self.base_lr, self.warmup_steps, self.total_steps))
+        total = torch.zeros((), dtype=torch.float32, device=tokens.device)
+        scale = 1.0 / float(self.global_tokens)
+        B = tokens.shape[0]
+        for lo in range(0, B, self.micro_batch):
+            mb = tokens[lo:lo + self.micro_batch]
+            loss = self.model.loss(mb[:, :-1], mb[:, 1:], scale=scale)
+            loss.backward()
+            total += loss.detach().float()
+        self.opt.step()
+        self.steps_done += 1
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(total)
+        return total
+
+    def step(self, tokens_host: torch.Tensor) -> torch.Tensor:
+        return self.step_device(self.stage(tokens_host))
+
+
+class SyntheticTokens:
+    """Uniform random token blocks in pinned host memory, a few of them reused
+    round-robin; the block for a step depends on (seed, step, data-parallel
+    index) only, so tensor-parallel peers see identical data."""
+
+    def __init__(self, local_batch, seq, vocab, dp_index=0, seed=0, n_buffers=4):
+        self.blocks = []
+        for i in range(n_buffers):
+            g = torch.Generator().manual_seed(seed * 100003 + dp_index * 1009 + i)
+            t = torch.randint(0, vocab, (local_batch, seq + 1), generator=g, dtype=torch.int64)
+            if torch.cuda.is_available():
+                t = t.pin_memory()
+            self.blocks.append(t)
+        self.i = 0
+
+    def next(self):
+        t = self.blocks[self.i % len(self.blocks)]
+        self.i += 1
+        return t
+
+    @property
+    def bytes_per_block(self):
+        return self.blocks[0].numel() * self.blocks[0].element_size()
