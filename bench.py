@@ -150,8 +150,11 @@ def main():
     model = models.Decoder(cfg, layout).cuda() if False else models.Decoder(cfg, layout)
     trainer = Trainer(model, global_tokens_per_step=global_batch * seq, micro_batch=micro, lr=3e-4,
                       warmup_steps=10, total_steps=1000)
+    # device-timed arm: one distinct block per step, staged before the clock starts
+    pre = SyntheticTokens(local_batch, seq, cfg.vocab_size, dp_index=layout.dp_index, seed=1,
+                          n_buffers=args.warmup + args.steps)
+    dev_blocks = [b.cuda() for b in pre.blocks]
     data = SyntheticTokens(local_batch, seq, cfg.vocab_size, dp_index=layout.dp_index, seed=0)
-    dev_blocks = [b.cuda() for b in data.blocks]
 
     def barrier():
         if world > 1:
@@ -173,9 +176,9 @@ def main():
         return ms.item(), _native.launch_count - l0
 
     for i in range(args.warmup):
-        trainer.step_device(dev_blocks[i % len(dev_blocks)])
+        trainer.step_device(dev_blocks[i])
     with ClockSampler(local_rank) as clocks:
-        ms_dev, launches = timed(lambda i: trainer.step_device(dev_blocks[i % len(dev_blocks)]), args.steps)
+        ms_dev, launches = timed(lambda i: trainer.step_device(dev_blocks[args.warmup + i]), args.steps)
     losses = []
     ms_e2e, _ = timed(lambda i: losses.append(trainer.step(data.next()).item()), args.steps)
     status = _native.read_status()

@@ -1,0 +1,311 @@
+// Device collectives over peer-mapped ("symmetric") memory: all-reduce
+// (one-shot and two-shot), all-gather, reduce-scatter, all-to-all.  Every GPU
+// of a team runs the same kernel; the kernels read the peers' staging buffers
+// directly over NVLink / NVSwitch with 16-byte loads and synchronise through
+// per-CTA flag words in each GPU's signal pad.
+//
+// Synchronisation protocol.  Signal pad of GPU g: flags[slot][writer] with
+// slot = CTA index, writer = index of the signalling GPU inside the node
+// (at most kMaxPeers).  A flag is a counter: a barrier step adds 1 to "my"
+// flag on every peer (red.release.sys) and waits until every peer's flag on
+// my own pad has reached the value the host computed for this launch
+// (ld.acquire.sys).  Counters only grow, so nothing is ever reset and a late
+// reader can never miss a signal.  Every wait is bounded: after ~2 s the
+// kernel records {where, peer, expected, seen} in the status record and all
+// CTAs fall through to the end.
+//
+// All kernels of this file are launched with exactly kCollectiveCtas CTAs so
+// that every flag slot advances in step on all GPUs.
+#include <cstring>
+
+#include "common.cuh"
+#include "runtime.cuh"
+
+using namespace dd;
+
+namespace {
+
+constexpr int kMaxPeers = 8;
+constexpr int kCollectiveCtas = 32;
+constexpr int kThreads = 512;
+
+struct Team {
+  int n;                        // members
+  int me;                       // my index in the team
+  int my_writer;                // my writer index (node-local rank)
+  void* buf[kMaxPeers];         // staging buffer of member i (peer-mapped)
+  uint32_t* flags[kMaxPeers];   // signal pad of member i (peer-mapped)
+  int writer[kMaxPeers];        // writer index of member i
+  uint32_t expect[kMaxPeers];   // flag value of member i's first signal of this launch
+  StatusRecord* status;
+};
+
+__device__ __forceinline__ void signal_peer(uint32_t* flag) {
+  asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
+}
+__device__ __forceinline__ uint32_t load_flag(const uint32_t* flag) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+  return v;
+}
+
+// Barrier number `step` (0, 1, 2, ...) of this launch between CTA `blockIdx.x`
+// of all team members.  Returns false after a timeout.
+__device__ bool team_barrier(const Team& t, uint32_t step, int* sh_fail) {
+  __syncthreads();
+  if (threadIdx.x < t.n && threadIdx.x != t.me) {
+    const int i = threadIdx.x;
+    __threadfence_system();
+    signal_peer(t.flags[i] + blockIdx.x * kMaxPeers + t.my_writer);
+    const uint32_t want = t.expect[i] + step;
+    const uint32_t* mine = t.flags[t.me] + blockIdx.x * kMaxPeers + t.writer[i];
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t seen = load_flag(mine);
+    uint32_t it = 0;
+    // counters wrap after 2^32 signals: compare as a signed distance
+    while ((int32_t)(seen - want) < 0) {
+      if ((++it & 0xff) == 0 && globaltimer_ns() - t0 > kSpinLimitNs) {
+        report_timeout(t.status, 100 + (int)step, (int)want, (int)seen);
+        *sh_fail = 1;
+        break;
+      }
+      seen = load_flag(mine);
+    }
+  }
+  __syncthreads();
+  return *sh_fail == 0;
+}
+
+__device__ __forceinline__ uint4 ld_peer(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// Sums the 16-byte vector at byte offset `off` over all members.
+template <bool BF16>
+__device__ __forceinline__ uint4 reduce_vec(const Team& t, size_t off) {
+  if (BF16) {
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll 1
+    for (int i = 0; i < t.n; ++i) {
+      const uint4 v = ld_peer(reinterpret_cast<const char*>(t.buf[i]) + off);
+      float2 f;
+      f = unpack_bf16x2(v.x); a[0] += f.x; a[1] += f.y;
+      f = unpack_bf16x2(v.y); a[2] += f.x; a[3] += f.y;
+      f = unpack_bf16x2(v.z); a[4] += f.x; a[5] += f.y;
+      f = unpack_bf16x2(v.w); a[6] += f.x; a[7] += f.y;
+    }
+    return make_uint4(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]), pack_bf16x2(a[4], a[5]),
+                      pack_bf16x2(a[6], a[7]));
+  } else {
+    float a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+#pragma unroll 1
+    for (int i = 0; i < t.n; ++i) {
+      const uint4 v = ld_peer(reinterpret_cast<const char*>(t.buf[i]) + off);
+      a0 += __uint_as_float(v.x); a1 += __uint_as_float(v.y); a2 += __uint_as_float(v.z); a3 += __uint_as_float(v.w);
+    }
+    return make_uint4(__float_as_uint(a0), __float_as_uint(a1), __float_as_uint(a2), __float_as_uint(a3));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// all-reduce.  Input staged at buf[me][0, bytes); result written to `out`
+// (local).  one_shot: every GPU reads everything; else reduce-scatter into the
+// own staging buffer followed by an all-gather.
+// ---------------------------------------------------------------------------
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads)
+allreduce_kernel(const Team t, char* out, size_t bytes, int one_shot) {
+  __shared__ int fail;
+  if (threadIdx.x == 0) fail = 0;
+  const size_t nvec = bytes >> 4;
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  if (!team_barrier(t, 0, &fail)) return;
+  if (one_shot) {
+    for (size_t v = tid; v < nvec; v += stride)
+      *reinterpret_cast<uint4*>(out + (v << 4)) = reduce_vec<BF16>(t, v << 4);
+    team_barrier(t, 1, &fail);
+    return;
+  }
+  // my chunk of the vectors
+  const size_t per = (nvec + t.n - 1) / t.n;
+  const size_t lo = min(nvec, per * t.me), hi = min(nvec, lo + per);
+  char* mine = reinterpret_cast<char*>(t.buf[t.me]);
+  for (size_t v = lo + tid; v < hi; v += stride) {
+    const uint4 r = reduce_vec<BF16>(t, v << 4);
+    *reinterpret_cast<uint4*>(mine + (v << 4)) = r;
+    *reinterpret_cast<uint4*>(out + (v << 4)) = r;
+  }
+  if (!team_barrier(t, 1, &fail)) return;
+  for (int k = 1; k < t.n; ++k) {
+    const int i = (t.me + k) % t.n;   // start with a different peer on every GPU
+    const size_t plo = min(nvec, per * i), phi = min(nvec, plo + per);
+    const char* src = reinterpret_cast<const char*>(t.buf[i]);
+    for (size_t v = plo + tid; v < phi; v += stride)
+      *reinterpret_cast<uint4*>(out + (v << 4)) = ld_peer(src + (v << 4));
+  }
+  team_barrier(t, 2, &fail);
+}
+
+// all-gather: member i's `bytes` staged at buf[i][0, bytes); out[i*bytes ...] = it.
+__global__ void __launch_bounds__(kThreads)
+allgather_kernel(const Team t, char* out, size_t bytes) {
+  __shared__ int fail;
+  if (threadIdx.x == 0) fail = 0;
+  const size_t nvec = bytes >> 4;
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  if (!team_barrier(t, 0, &fail)) return;
+  for (int k = 0; k < t.n; ++k) {
+    const int i = (t.me + k) % t.n;
+    const char* src = reinterpret_cast<const char*>(t.buf[i]);
+    char* dst = out + (size_t)i * bytes;
+    for (size_t v = tid; v < nvec; v += stride)
+      *reinterpret_cast<uint4*>(dst + (v << 4)) = ld_peer(src + (v << 4));
+  }
+  team_barrier(t, 1, &fail);
+}
+
+// reduce-scatter: every member stages n * bytes; out = sum_i buf[i][me*bytes ...].
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads)
+reducescatter_kernel(const Team t, char* out, size_t bytes) {
+  __shared__ int fail;
+  if (threadIdx.x == 0) fail = 0;
+  const size_t nvec = bytes >> 4;
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  if (!team_barrier(t, 0, &fail)) return;
+  const size_t base = (size_t)t.me * bytes;
+  for (size_t v = tid; v < nvec; v += stride)
+    *reinterpret_cast<uint4*>(out + (v << 4)) = reduce_vec<BF16>(t, base + (v << 4));
+  team_barrier(t, 1, &fail);
+}
+
+// all-to-all (equal blocks): out[i*bytes ...] = buf[i][me*bytes ...].
+__global__ void __launch_bounds__(kThreads)
+alltoall_kernel(const Team t, char* out, size_t bytes) {
+  __shared__ int fail;
+  if (threadIdx.x == 0) fail = 0;
+  const size_t nvec = bytes >> 4;
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  if (!team_barrier(t, 0, &fail)) return;
+  for (int k = 0; k < t.n; ++k) {
+    const int i = (t.me + k) % t.n;
+    const char* src = reinterpret_cast<const char*>(t.buf[i]) + (size_t)t.me * bytes;
+    char* dst = out + (size_t)i * bytes;
+    for (size_t v = tid; v < nvec; v += stride)
+      *reinterpret_cast<uint4*>(dst + (v << 4)) = ld_peer(src + (v << 4));
+  }
+  team_barrier(t, 1, &fail);
+}
+
+// Only the barrier: used to order host-driven phases and by tests of the
+// time-out path (a peer that never signals).
+__global__ void __launch_bounds__(kThreads) barrier_only_kernel(const Team t) {
+  __shared__ int fail;
+  if (threadIdx.x == 0) fail = 0;
+  team_barrier(t, 0, &fail);
+}
+
+int fill_team(Team& t, int n, int me, int my_writer, void* const* bufs, void* const* flags, const int* writers,
+              const unsigned* expect) {
+  if (n < 1 || n > kMaxPeers || me < 0 || me >= n) return DD_ERR_BAD_ARG;
+  t.n = n; t.me = me; t.my_writer = my_writer;
+  for (int i = 0; i < n; ++i) {
+    t.buf[i] = bufs[i];
+    t.flags[i] = reinterpret_cast<uint32_t*>(flags[i]);
+    t.writer[i] = writers[i];
+    t.expect[i] = expect[i];
+    if (writers[i] < 0 || writers[i] >= kMaxPeers) return DD_ERR_BAD_ARG;
+  }
+  int err = 0;
+  t.status = device_status(&err);
+  return err;
+}
+
+}  // namespace
+
+// ------------------------------ symmetric heap ------------------------------
+DD_API int dd_symm_alloc(size_t bytes, void** out) {
+  cudaError_t e = cudaMalloc(out, bytes);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaMemset(*out, 0, bytes);
+}
+DD_API int dd_symm_free(void* p) { return (int)cudaFree(p); }
+DD_API int dd_ipc_get_handle(void* p, void* handle64) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) return (int)e;
+  memcpy(handle64, &h, sizeof(h));
+  return 0;
+}
+DD_API int dd_ipc_open_handle(const void* handle64, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  return (int)cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess);
+}
+DD_API int dd_ipc_close_handle(void* p) { return (int)cudaIpcCloseMemHandle(p); }
+DD_API int dd_collective_ctas() { return kCollectiveCtas; }
+DD_API int dd_collective_max_peers() { return kMaxPeers; }
+
+// dtype: 0 = bf16, 1 = fp32.  `bytes` must be a multiple of 16.  Number of
+// barrier steps consumed (to advance the host-side counters) is returned in
+// *steps.
+DD_API int dd_allreduce(int n, int me, int my_writer, void* const* bufs, void* const* flags, const int* writers,
+                        const unsigned* expect, void* out, size_t bytes, int dtype, int one_shot, int* steps,
+                        void* stream) {
+  if (bytes % 16) return DD_ERR_ALIGN;
+  Team t;
+  int r = fill_team(t, n, me, my_writer, bufs, flags, writers, expect);
+  if (r) return r;
+  *steps = one_shot ? 2 : 3;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == 0) allreduce_kernel<true><<<kCollectiveCtas, kThreads, 0, s>>>(t, (char*)out, bytes, one_shot);
+  else allreduce_kernel<false><<<kCollectiveCtas, kThreads, 0, s>>>(t, (char*)out, bytes, one_shot);
+  return (int)cudaGetLastError();
+}
+DD_API int dd_allgather(int n, int me, int my_writer, void* const* bufs, void* const* flags, const int* writers,
+                        const unsigned* expect, void* out, size_t bytes, int* steps, void* stream) {
+  if (bytes % 16) return DD_ERR_ALIGN;
+  Team t;
+  int r = fill_team(t, n, me, my_writer, bufs, flags, writers, expect);
+  if (r) return r;
+  *steps = 2;
+  allgather_kernel<<<kCollectiveCtas, kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(t, (char*)out, bytes);
+  return (int)cudaGetLastError();
+}
+DD_API int dd_reducescatter(int n, int me, int my_writer, void* const* bufs, void* const* flags, const int* writers,
+                            const unsigned* expect, void* out, size_t bytes, int dtype, int* steps, void* stream) {
+  if (bytes % 16) return DD_ERR_ALIGN;
+  Team t;
+  int r = fill_team(t, n, me, my_writer, bufs, flags, writers, expect);
+  if (r) return r;
+  *steps = 2;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == 0) reducescatter_kernel<true><<<kCollectiveCtas, kThreads, 0, s>>>(t, (char*)out, bytes);
+  else reducescatter_kernel<false><<<kCollectiveCtas, kThreads, 0, s>>>(t, (char*)out, bytes);
+  return (int)cudaGetLastError();
+}
+DD_API int dd_alltoall(int n, int me, int my_writer, void* const* bufs, void* const* flags, const int* writers,
+                       const unsigned* expect, void* out, size_t bytes, int* steps, void* stream) {
+  if (bytes % 16) return DD_ERR_ALIGN;
+  Team t;
+  int r = fill_team(t, n, me, my_writer, bufs, flags, writers, expect);
+  if (r) return r;
+  *steps = 2;
+  alltoall_kernel<<<kCollectiveCtas, kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(t, (char*)out, bytes);
+  return (int)cudaGetLastError();
+}
+DD_API int dd_team_barrier(int n, int me, int my_writer, void* const* bufs, void* const* flags, const int* writers,
+                           const unsigned* expect, int* steps, void* stream) {
+  Team t;
+  int r = fill_team(t, n, me, my_writer, bufs, flags, writers, expect);
+  if (r) return r;
+  *steps = 1;
+  barrier_only_kernel<<<kCollectiveCtas, kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(t);
+  return (int)cudaGetLastError();
+}

@@ -2,6 +2,7 @@
 // tensor-map cache, version / capability queries.
 #include "runtime.cuh"
 
+#include <cstdio>
 #include <mutex>
 #include <unordered_map>
 #include <vector>
@@ -92,6 +93,15 @@ int get_tensor_map_bf16_3d(CUtensorMap* out, const void* base, uint64_t inner, u
   }
   auto enc = tensor_map_encoder();
   if (!enc) return DD_ERR_DRIVER;
+  // Driver calls need the primary context current on the calling thread; a
+  // thread that has only ever used the runtime lazily (e.g. an autograd worker)
+  // may not have it bound yet.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaSetDevice(dev);
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   cuuint64_t dims[3] = {inner, outer, batch};
   cuuint64_t strides[2] = {outer_stride_bytes, batch_stride_bytes};
   cuuint32_t box[3] = {box_inner, box_outer, 1};
@@ -99,7 +109,14 @@ int get_tensor_map_bf16_3d(CUtensorMap* out, const void* base, uint64_t inner, u
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return DD_ERR_DRIVER;
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr,
+            "distdl_b200: cuTensorMapEncodeTiled failed (%d): base=%p dims={%llu,%llu,%llu} strides={%llu,%llu} "
+            "box={%u,%u,1}\n",
+            (int)r, base, (unsigned long long)inner, (unsigned long long)outer, (unsigned long long)batch,
+            (unsigned long long)outer_stride_bytes, (unsigned long long)batch_stride_bytes, box_inner, box_outer);
+    return DD_ERR_DRIVER;
+  }
   {
     std::lock_guard<std::mutex> lk(g_mu);
     if (g_maps.size() > 65536) g_maps.clear();

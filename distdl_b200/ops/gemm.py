@@ -89,13 +89,16 @@ class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, b):
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, w, bias=b)
+        # the result is allocated in its final shape (never a view), so that
+        # in-place ops such as the rotary embedding may follow
+        y = torch.empty(*x.shape[:-1], w.shape[0], dtype=x.dtype, device=x.device)
+        gemm(x2, w, out=y.view(-1, w.shape[0]), bias=b)
         ctx.save_for_backward(x2, w)
         ctx.has_bias = b is not None
         ctx.wref = w
         ctx.bref = b
         ctx.xshape = x.shape
-        return y.view(*x.shape[:-1], w.shape[0])
+        return y
 
     @staticmethod
     def backward(ctx, dy):

@@ -1,0 +1,167 @@
+"""Host wrappers of the native device collectives (all-reduce, all-gather,
+reduce-scatter, all-to-all) over the symmetric heap.
+
+Each call copies the operand into the local staging buffer (a local
+HBM-to-HBM copy), then launches ONE kernel on every GPU of the team that pulls
+what it needs from the peers' staging buffers over NVLink and synchronises
+through flag counters.  Message sizes above the staging capacity are processed
+in slices.  Replaces the NCCL calls of the reference's ``nccl_cupy`` backend
+(``src/distdl/backends/nccl_cupy/functional/all_sum_reduce.py:73-76``,
+``all_gather.py:101-109``, ``reduce_scatter.py:117-125``).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from .. import _native
+from ..ops._util import stream_ptr
+from . import symm
+
+ONE_SHOT_BYTES = 256 * 1024
+_DT = {torch.bfloat16: 0, torch.float32: 1}
+
+
+def available(ranks) -> bool:
+    if not (dist.is_available() and dist.is_initialized() and torch.cuda.is_available()):
+        return False
+    if not _native.available() or len(ranks) > 8:
+        return False
+    return True
+
+
+def team(ranks):
+    """Makes sure the heap exists (collective over all processes on first call)."""
+    return symm.heap()
+
+
+def _launch(name, h, ranks, *args):
+    if h.poisoned:
+        raise RuntimeError("symmetric heap is poisoned by an earlier time-out; restart the job")
+    steps = ctypes.c_int(0)
+    targs = h.team_args(ranks)
+    _native.launch_count += 1
+    _native.check(getattr(_native.lib(), name)(*targs, *args, ctypes.byref(steps), stream_ptr()), name)
+    h.advance(ranks, steps.value)
+
+
+def all_reduce(x: torch.Tensor, ranks) -> torch.Tensor:
+    """Team-wide sum of ``x`` (bf16 or fp32; fp32 accumulation); returns a new tensor."""
+    h = symm.heap()
+    ranks = list(ranks)
+    flat = x.contiguous().view(-1)
+    if flat.dtype not in _DT:
+        flat = flat.float()
+    out = torch.empty_like(flat)
+    es = flat.element_size()
+    per = 16 // es
+    cap = h.staging_bytes // 16 * 16
+    n = flat.numel()
+    done = 0
+    while done < n:
+        cnt = min(n - done, cap // es)
+        nbytes = (cnt * es + 15) // 16 * 16
+        stage = h.staging_tensor(nbytes, flat.dtype)
+        if cnt % per:
+            stage[cnt:].zero_()
+        stage[:cnt].copy_(flat[done:done + cnt])
+        if cnt * es == nbytes:
+            dst = out[done:done + cnt]
+            _launch("dd_allreduce", h, ranks, dst.data_ptr(), nbytes, _DT[flat.dtype], int(nbytes <= ONE_SHOT_BYTES))
+        else:
+            tmp = torch.empty(nbytes // es, dtype=flat.dtype, device=flat.device)
+            _launch("dd_allreduce", h, ranks, tmp.data_ptr(), nbytes, _DT[flat.dtype], int(nbytes <= ONE_SHOT_BYTES))
+            out[done:done + cnt].copy_(tmp[:cnt])
+        done += cnt
+    return out.view(x.shape).to(x.dtype)
+
+
+def all_gather(x: torch.Tensor, ranks) -> torch.Tensor:
+    """Stacks every member's ``x`` (equal shapes) along a new leading axis."""
+    h = symm.heap()
+    ranks = list(ranks)
+    P = len(ranks)
+    flat = x.contiguous().view(-1).view(torch.uint8)
+    nbytes_total = flat.numel()
+    out = torch.empty(P, nbytes_total, dtype=torch.uint8, device=x.device)
+    cap = h.staging_bytes // 16 * 16
+    done = 0
+    while done < nbytes_total:
+        cnt = min(nbytes_total - done, cap)
+        padded = (cnt + 15) // 16 * 16
+        stage = h.staging_tensor(padded, torch.uint8)
+        stage[:cnt].copy_(flat[done:done + cnt])
+        if padded == cnt and P * cnt == out.numel():
+            _launch("dd_allgather", h, ranks, out.data_ptr(), padded)
+        else:
+            tmp = torch.empty(P, padded, dtype=torch.uint8, device=x.device)
+            _launch("dd_allgather", h, ranks, tmp.data_ptr(), padded)
+            out[:, done:done + cnt].copy_(tmp[:, :cnt])
+        done += cnt
+    return out.view(x.dtype).view((P,) + tuple(x.shape))
+
+
+def reduce_scatter(x: torch.Tensor, ranks) -> torch.Tensor:
+    """``x`` is ``[P, ...]``: member ``i`` receives the team-wide sum of ``x[i]``."""
+    h = symm.heap()
+    ranks = list(ranks)
+    P = len(ranks)
+    assert x.shape[0] == P
+    xs = x.contiguous()
+    if xs.dtype not in _DT:
+        xs = xs.float()
+    es = xs.element_size()
+    chunk = xs[0].numel()
+    out = torch.empty(chunk, dtype=xs.dtype, device=x.device)
+    flat = xs.view(P, chunk)
+    cap_elems = (h.staging_bytes // P) // 16 * 16 // es
+    done = 0
+    while done < chunk:
+        cnt = min(chunk - done, cap_elems)
+        padded = (cnt * es + 15) // 16 * 16
+        pe = padded // es
+        stage = h.staging_tensor(P * padded, xs.dtype).view(P, pe)
+        if pe != cnt:
+            stage[:, cnt:].zero_()
+        stage[:, :cnt].copy_(flat[:, done:done + cnt])
+        if pe == cnt:
+            _launch("dd_reducescatter", h, ranks, out[done:done + cnt].data_ptr(), padded, _DT[xs.dtype])
+        else:
+            tmp = torch.empty(pe, dtype=xs.dtype, device=x.device)
+            _launch("dd_reducescatter", h, ranks, tmp.data_ptr(), padded, _DT[xs.dtype])
+            out[done:done + cnt].copy_(tmp[:cnt])
+        done += cnt
+    return out.view(x.shape[1:]).to(x.dtype)
+
+
+def all_to_all(x: torch.Tensor, ranks) -> torch.Tensor:
+    """``x`` is ``[P, ...]`` with equal blocks: block ``i`` goes to member ``i``;
+    returns ``[P, ...]`` whose block ``i`` came from member ``i``."""
+    h = symm.heap()
+    ranks = list(ranks)
+    P = len(ranks)
+    xs = x.contiguous().view(P, -1).view(torch.uint8)
+    chunk = xs.shape[1]
+    out = torch.empty(P, chunk, dtype=torch.uint8, device=x.device)
+    cap = (h.staging_bytes // P) // 16 * 16
+    done = 0
+    while done < chunk:
+        cnt = min(chunk - done, cap)
+        padded = (cnt + 15) // 16 * 16
+        stage = h.staging_tensor(P * padded, torch.uint8).view(P, padded)
+        stage[:, :cnt].copy_(xs[:, done:done + cnt])
+        if padded == cnt and cnt == chunk:
+            _launch("dd_alltoall", h, ranks, out.data_ptr(), padded)
+        else:
+            tmp = torch.empty(P, padded, dtype=torch.uint8, device=x.device)
+            _launch("dd_alltoall", h, ranks, tmp.data_ptr(), padded)
+            out[:, done:done + cnt].copy_(tmp[:, :cnt])
+        done += cnt
+    return out.view(x.dtype).view(x.shape)
+
+
+def barrier(ranks):
+    h = symm.heap()
+    _launch("dd_team_barrier", h, list(ranks))

@@ -1,0 +1,141 @@
+"""Symmetric (peer-mapped) memory of the native backend.
+
+Every process allocates one staging buffer and one signal pad on its GPU,
+exports them as CUDA IPC handles, and maps the buffers of every other process
+of the node; after that a kernel on any GPU can load from / store to any
+peer's buffer over NVLink / NVSwitch.  Handles are exchanged once through
+``torch.distributed`` (plumbing only).  The reference bootstraps one NCCL
+communicator per rank set instead (``src/distdl/backends/nccl_cupy/nccl_comm.py:132-144``).
+
+Flag protocol bookkeeping lives here as well: flags are counters that only
+grow, and the host keeps, per peer, how many barrier steps have been consumed,
+so each launch knows the value its first barrier has to wait for.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from .. import _native
+from ..backends.common import world
+
+c_void_p, c_int, c_size_t = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+_PP = ctypes.POINTER(c_void_p)
+_IP = ctypes.POINTER(c_int)
+_UP = ctypes.POINTER(ctypes.c_uint)
+
+_native.declare("dd_symm_alloc", [c_size_t, _PP])
+_native.declare("dd_symm_free", [c_void_p])
+_native.declare("dd_ipc_get_handle", [c_void_p, ctypes.c_char_p])
+_native.declare("dd_ipc_open_handle", [ctypes.c_char_p, _PP])
+_native.declare("dd_ipc_close_handle", [c_void_p])
+_native.declare("dd_collective_ctas", [])
+_native.declare("dd_collective_max_peers", [])
+_TEAM = [c_int, c_int, c_int, _PP, _PP, _IP, _UP]
+_native.declare("dd_allreduce", _TEAM + [c_void_p, c_size_t, c_int, c_int, _IP, c_void_p])
+_native.declare("dd_allgather", _TEAM + [c_void_p, c_size_t, _IP, c_void_p])
+_native.declare("dd_reducescatter", _TEAM + [c_void_p, c_size_t, c_int, _IP, c_void_p])
+_native.declare("dd_alltoall", _TEAM + [c_void_p, c_size_t, _IP, c_void_p])
+_native.declare("dd_team_barrier", _TEAM + [_IP, c_void_p])
+
+SIGNAL_PAD_BYTES = 64 * 1024
+
+
+class SymmetricHeap:
+    """One staging buffer + signal pad per process, mapped into every process."""
+
+    def __init__(self, staging_bytes: int):
+        if not (dist.is_available() and dist.is_initialized()):
+            raise RuntimeError("torch.distributed must be initialised before the symmetric heap")
+        lib = _native.lib()
+        self.world = dist.get_world_size()
+        self.rank = dist.get_rank()
+        self.max_peers = lib.dd_collective_max_peers()
+        if self.world > self.max_peers:
+            raise RuntimeError(f"the native transport handles up to {self.max_peers} GPUs of one node")
+        self.staging_bytes = int(staging_bytes)
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self._local_buf, self._local_pad = c_void_p(), c_void_p()
+        _native.check(lib.dd_symm_alloc(self.staging_bytes, ctypes.byref(self._local_buf)), "dd_symm_alloc")
+        _native.check(lib.dd_symm_alloc(SIGNAL_PAD_BYTES, ctypes.byref(self._local_pad)), "dd_symm_alloc")
+        hb, hp = ctypes.create_string_buffer(64), ctypes.create_string_buffer(64)
+        _native.check(lib.dd_ipc_get_handle(self._local_buf, hb), "dd_ipc_get_handle")
+        _native.check(lib.dd_ipc_get_handle(self._local_pad, hp), "dd_ipc_get_handle")
+        mine = (bytes(hb.raw), bytes(hp.raw), os.getpid())
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, mine)
+        self.buf_ptrs, self.pad_ptrs = [], []
+        for r, (b, p, _pid) in enumerate(gathered):
+            if r == self.rank:
+                self.buf_ptrs.append(self._local_buf.value)
+                self.pad_ptrs.append(self._local_pad.value)
+                continue
+            pb, pp = c_void_p(), c_void_p()
+            _native.check(lib.dd_ipc_open_handle(b, ctypes.byref(pb)), "dd_ipc_open_handle")
+            _native.check(lib.dd_ipc_open_handle(p, ctypes.byref(pp)), "dd_ipc_open_handle")
+            self.buf_ptrs.append(pb.value)
+            self.pad_ptrs.append(pp.value)
+        # barrier steps consumed so far with every peer (flags are counters)
+        self.steps_done = [0] * self.world
+        self.poisoned = False
+        dist.barrier()
+
+    def staging_tensor(self, nbytes: int, dtype=torch.uint8) -> torch.Tensor:
+        """A tensor view of the head of the local staging buffer (no copy, no ownership)."""
+        if nbytes > self.staging_bytes:
+            raise ValueError(f"{nbytes} bytes exceed the staging buffer ({self.staging_bytes})")
+        n = nbytes // torch.empty((), dtype=dtype).element_size()
+        return _wrap_device_pointer(self._local_buf.value, n, dtype, self.device)
+
+    def team_args(self, ranks):
+        """ctypes arguments describing a team (ordered world ranks containing this rank)."""
+        n = len(ranks)
+        me = list(ranks).index(self.rank)
+        bufs = (c_void_p * n)(*[self.buf_ptrs[r] for r in ranks])
+        pads = (c_void_p * n)(*[self.pad_ptrs[r] for r in ranks])
+        writers = (c_int * n)(*[int(r) for r in ranks])
+        expect = (ctypes.c_uint * n)(*[(self.steps_done[r] + 1) & 0xFFFFFFFF for r in ranks])
+        return n, me, self.rank, bufs, pads, writers, expect
+
+    def advance(self, ranks, steps: int):
+        for r in ranks:
+            if r != self.rank:
+                self.steps_done[r] += steps
+
+
+class _DevicePointer:
+    """Minimal object exposing ``__cuda_array_interface__`` for a raw pointer."""
+
+    def __init__(self, ptr, n, typestr):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
+_TYPESTR = {torch.uint8: "|u1", torch.float32: "<f4", torch.int32: "<i4", torch.int16: "<i2", torch.int64: "<i8"}
+
+
+def _wrap_device_pointer(ptr, n, dtype, device):
+    if dtype in _TYPESTR:
+        return torch.as_tensor(_DevicePointer(ptr, n, _TYPESTR[dtype]), device=device)
+    # bf16 / fp16 have no typestr torch accepts here: wrap as int16 and reinterpret
+    t = torch.as_tensor(_DevicePointer(ptr, n, "<i2"), device=device)
+    return t.view(dtype)
+
+
+_heap = None
+
+
+def heap(staging_bytes: int = None) -> SymmetricHeap:
+    """The process-wide heap (created on first use; every process must call)."""
+    global _heap
+    if _heap is None:
+        size = staging_bytes or int(os.environ.get("DISTDL_SYMM_BYTES", str(1 << 30)))
+        _heap = SymmetricHeap(size)
+    return _heap
+
+
+def heap_ready() -> bool:
+    return _heap is not None

@@ -61,22 +61,28 @@ class Trainer:
 
 
 class SyntheticTokens:
-    """Uniform random token blocks in pinned host memory, a few of them reused
-    round-robin; the block for a step depends on (seed, step, data-parallel
+    """Uniform random token blocks in pinned host memory.  Every call of
+    :meth:`next` draws fresh tokens into the next of a few pinned buffers
+    (round-robin, so a buffer is not rewritten while its asynchronous copy may
+    still be in flight); the stream of blocks depends on (seed, data-parallel
     index) only, so tensor-parallel peers see identical data."""
 
     def __init__(self, local_batch, seq, vocab, dp_index=0, seed=0, n_buffers=4):
+        self.vocab = vocab
+        self.gen = torch.Generator().manual_seed(seed * 100003 + dp_index * 1009 + 17)
         self.blocks = []
-        for i in range(n_buffers):
-            g = torch.Generator().manual_seed(seed * 100003 + dp_index * 1009 + i)
-            t = torch.randint(0, vocab, (local_batch, seq + 1), generator=g, dtype=torch.int64)
+        for _ in range(n_buffers):
+            t = torch.empty((local_batch, seq + 1), dtype=torch.int64)
             if torch.cuda.is_available():
                 t = t.pin_memory()
+            torch.randint(0, vocab, t.shape, generator=self.gen, out=t)
             self.blocks.append(t)
         self.i = 0
 
     def next(self):
         t = self.blocks[self.i % len(self.blocks)]
+        if self.i >= len(self.blocks):
+            torch.randint(0, self.vocab, t.shape, generator=self.gen, out=t)
         self.i += 1
         return t
 

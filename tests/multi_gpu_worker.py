@@ -1,0 +1,98 @@
+"""Worker body of the multi-GPU tests: run under torchrun, one rank per GPU.
+Compares the native device collectives and the fused kernels against NCCL
+(`torch.distributed`) on the same inputs."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def check_collectives():
+    from distdl_b200.parallel import collectives as C
+    world, rank = dist.get_world_size(), dist.get_rank()
+    ranks = list(range(world))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    for dtype in (torch.bfloat16, torch.float32):
+        for n in (8, 1000, 4096, 65536 + 24, 3 * 1024 * 1024 + 8):
+            torch.manual_seed(n + rank)
+            x = (torch.rand(n, device=dev) * 2 - 1).to(dtype)
+            ref = x.clone().float()
+            dist.all_reduce(ref)
+            got = C.all_reduce(x, ranks)
+            tol = 3e-2 if dtype == torch.bfloat16 else 1e-5
+            assert (got.float() - ref).abs().max().item() < tol * world, ("all_reduce", dtype, n)
+            g = C.all_gather(x, ranks)
+            refg = torch.empty(world, n, dtype=dtype, device=dev)
+            dist.all_gather_into_tensor(refg, x)
+            assert torch.equal(g, refg), ("all_gather", dtype, n)
+            xs = (torch.rand(world, n, device=dev) * 2 - 1).to(dtype)
+            rs = C.reduce_scatter(xs, ranks)
+            refrs = torch.empty(n, dtype=torch.float32, device=dev)
+            dist.reduce_scatter_tensor(refrs, xs.float().contiguous())
+            assert (rs.float() - refrs).abs().max().item() < tol * world, ("reduce_scatter", dtype, n)
+            a2a = C.all_to_all(xs, ranks)
+            refa = torch.empty_like(xs)
+            dist.all_to_all_single(refa, xs.contiguous())
+            assert torch.equal(a2a, refa), ("all_to_all", dtype, n)
+    # a sub-team (first two ranks) while the others idle
+    if world >= 4:
+        sub = [0, 1]
+        if rank in sub:
+            x = torch.full((1024,), float(rank + 1), device=dev)
+            got = C.all_reduce(x, sub)
+            assert torch.allclose(got, torch.full_like(got, 3.0))
+    torch.cuda.synchronize()
+    from distdl_b200 import _native
+    assert _native.read_status()[0] == 0
+
+
+def check_primitives_native():
+    """The primitive modules on the native backend against their definition."""
+    import distdl_b200
+    from distdl_b200.nn import AllGather, AllSumReduce, ReduceScatter, Repartition
+    world, rank = dist.get_world_size(), dist.get_rank()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    P_world = distdl_b200.backends.backend.Partition()
+    P = P_world.create_cartesian_topology_partition([1, world])
+    x = torch.full((4, 6), float(rank + 1), device=dev, dtype=torch.float32, requires_grad=True)
+    y = AllSumReduce(P, axes_reduce=(1,))(x)
+    assert torch.allclose(y, torch.full_like(y, world * (world + 1) / 2))
+    y.sum().backward()
+    assert torch.allclose(x.grad, torch.full_like(x.grad, float(world)))
+    g = AllGather(P, axes_all_gather=(1,))(x.detach())
+    assert g.shape == (4, 6 * world) and torch.allclose(g[:, 6 * rank:6 * rank + 6], x.detach())
+    r = ReduceScatter(P, axes_reduce_scatter=(1,))(torch.ones(4, 2 * world, device=dev))
+    assert r.shape == (4, 2) and torch.allclose(r, torch.full_like(r, float(world)))
+    # row partition -> column partition transpose of an [N, N] tensor
+    N = 8 * world
+    P_rows = P_world.create_cartesian_topology_partition([world, 1])
+    G = torch.arange(N * N, device=dev, dtype=torch.float32).reshape(N, N)
+    rows = G[rank * 8:(rank + 1) * 8].clone()
+    cols = Repartition(P_rows, P)(rows)
+    assert torch.equal(cols, G[:, rank * 8:(rank + 1) * 8])
+
+
+def main():
+    import distdl_b200
+    from distdl_b200.backends.common import world as dworld
+    dworld.init_process_group_from_env()
+    distdl_b200.config.set_backend("native", "cupy")
+    what = sys.argv[1] if len(sys.argv) > 1 else "collectives"
+    if what in ("collectives", "all"):
+        check_collectives()
+    if what in ("primitives", "all"):
+        check_primitives_native()
+    if what in ("fused", "all"):
+        from multi_gpu_fused import check_fused
+        check_fused()
+    dist.barrier()
+    if dist.get_rank() == 0:
+        print(f"multi-gpu {what}: OK on {dist.get_world_size()} GPUs")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

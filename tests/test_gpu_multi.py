@@ -1,0 +1,35 @@
+"""Multi-GPU tests (skipped with fewer than 2 devices): child processes, one
+rank per GPU, NVLS off in NCCL, plain peer loads in this library's kernels."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(what, nproc):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29400 + os.getpid() % 500),
+           os.path.join(HERE, "multi_gpu_worker.py"), what]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "OK" in res.stdout
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_native_collectives_match_nccl():
+    _run("collectives", min(_ngpu(), 8))
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_primitives_on_native_backend():
+    _run("primitives", min(_ngpu(), 8))
