@@ -40,6 +40,17 @@ def _default_device():
     return torch.device("cpu")
 
 
+def _global_setup():
+    if world.world_size() <= 1:
+        return
+    world.control_group()
+    from ... import backends
+    be = backends.backend
+    if be is not None and getattr(be, "name", "") == "native_cupy" and torch.cuda.is_available():
+        from ...parallel import symm
+        symm.heap()
+
+
 class Partition:
     """An ordered team of workers.
 
@@ -58,6 +69,10 @@ class Partition:
     def __init__(self, ranks=None, root=None, device=None, requested_device=None, initialize_backend_comm=False):
         if ranks is None:
             ranks = range(world.world_size())
+            # Building the world partition is the one point every process is
+            # known to reach: set up what needs all of them (the control-plane
+            # group; the symmetric heap of the native backend).
+            _global_setup()
         self.ranks = tuple(int(r) for r in ranks)
         if len(set(self.ranks)) != len(self.ranks):
             raise ValueError("duplicate ranks in partition")

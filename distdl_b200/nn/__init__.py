@@ -19,3 +19,12 @@ from .linear_ag_zero import DistributedLinearAllGatherZero  # noqa: F401,E402
 from .linear_rs import DistributedLinearReduceScatter  # noqa: F401,E402
 from .linear_rs_zero import DistributedLinearReduceScatterZero  # noqa: F401,E402
 from .rmsnorm_zero import DistributedRMSNormZero  # noqa: F401,E402
+from . import loss  # noqa: F401,E402
+from .batchnorm import DistributedBatchNorm  # noqa: F401,E402
+from .conv_feature import (DistributedFeatureConv1d, DistributedFeatureConv2d, DistributedFeatureConv3d,  # noqa: F401,E402
+                           DistributedFeatureConvTranspose1d, DistributedFeatureConvTranspose2d,
+                           DistributedFeatureConvTranspose3d)
+from .loss import (DistributedBCELoss, DistributedBCEWithLogitsLoss, DistributedKLDivLoss,  # noqa: F401,E402
+                   DistributedL1Loss, DistributedMSELoss, DistributedPoissonNLLLoss)
+from .pooling import (DistributedAvgPool1d, DistributedAvgPool2d, DistributedAvgPool3d,  # noqa: F401,E402
+                      DistributedMaxPool1d, DistributedMaxPool2d, DistributedMaxPool3d)

@@ -1,0 +1,214 @@
+"""Convolutions on spatially partitioned tensors ("feature"-distributed):
+halo exchange, then the local library convolution
+(``src/distdl/nn/conv_feature.py:16-431``)."""
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from ..utilities.slicing import assemble_slices
+from ..utilities.torch import TensorStructure, distdl_padding_to_torch_padding, zero_volume_tensor
+from .broadcast import Broadcast
+from .halo_exchange import HaloExchange
+from .mixins.conv_mixin import ConvMixin
+from .mixins.halo_mixin import HaloMixin
+from .module import Module
+
+
+class DistributedFeatureConvBase(Module, HaloMixin, ConvMixin):
+    r"""Convolution of a tensor ``[batch, channel, *space]`` whose *spatial*
+    dimensions are split over ``P_x = [1, 1, *P_space]``.
+
+    Weights and bias live on worker 0 and are broadcast to all workers each
+    forward.  Every worker zero-pads its sub-tensor where it touches the global
+    boundary, allocates ghost regions towards its neighbours, fills them with a
+    :class:`HaloExchange`, crops what its own output windows do not need
+    (strided kernels) and applies the local convolution with ``padding=0``.
+    Halo widths are computed from the actual (possibly unbalanced) sub-tensor
+    shapes.  The local convolution is the library (cuDNN) kernel: convolution is
+    not one of this framework's hand-written hot paths.
+    """
+
+    TorchConvType = None
+    num_dimensions = None
+    transposed = False
+
+    def __init__(self, P_x, in_channels, out_channels, kernel_size, stride=1, padding=0, padding_mode="zeros",
+                 dilation=1, groups=1, bias=True, buffer_manager=None, collect_state=False, device=None, dtype=None):
+        super().__init__()
+        self.P_x = P_x
+        self.buffer_manager = buffer_manager or self._distdl_backend.BufferManager()
+        if not P_x.active:
+            return
+        nd = self.num_dimensions
+        exp = lambda v: np.atleast_1d(np.asarray(v, dtype=int)) * (np.ones(nd, dtype=int) if np.ndim(v) == 0 else 1)  # noqa: E731
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.kernel_size, self.stride = exp(kernel_size), exp(stride)
+        self.padding, self.dilation = exp(padding), exp(dilation)
+        self.padding_mode, self.groups, self.use_bias = padding_mode, groups, bias
+        self.collect_state = collect_state
+        device = device if device is not None else P_x.device
+        self.conv_layer = self.TorchConvType(in_channels, out_channels, tuple(int(k) for k in self.kernel_size),
+                                             stride=tuple(int(s) for s in self.stride), padding=0,
+                                             dilation=tuple(int(d) for d in self.dilation), groups=groups, bias=bias,
+                                             device=device, dtype=dtype)
+        dims = P_x.dim
+        self.global_padding = np.concatenate([np.zeros(dims - nd, dtype=int), self.padding])
+        self.P_wb_cart = P_x.create_partition_inclusive([0]).create_cartesian_topology_partition([1])
+        w0, b0 = self.conv_layer.weight.detach(), (self.conv_layer.bias.detach() if bias else None)
+        del self.conv_layer.weight
+        self.conv_layer.weight = None
+        if bias:
+            del self.conv_layer.bias
+            self.conv_layer.bias = None
+        if self.P_wb_cart.active:
+            self.weight = torch.nn.Parameter(w0.clone())
+            if bias:
+                self.bias = torch.nn.Parameter(b0.clone())
+            else:
+                self.register_buffer("bias", None)
+        else:
+            self.register_buffer("weight", zero_volume_tensor(device=device, dtype=w0.dtype))
+            self.register_buffer("bias", zero_volume_tensor(device=device, dtype=w0.dtype) if bias else None)
+        self.w_broadcast = Broadcast(self.P_wb_cart, P_x, preserve_batch=False)
+        if bias:
+            self.b_broadcast = Broadcast(self.P_wb_cart, P_x, preserve_batch=False)
+        self.halo_layer = None
+        self.needed_slices = None
+        self.pad_tuple = None
+
+    def _compute_local_padding(self, padding):
+        """The global zero padding only applies where a worker touches the boundary."""
+        local = np.array(padding, dtype=int)
+        idx, shape = self.P_x.index, self.P_x.shape
+        for d in range(self.P_x.dim):
+            if idx[d] != 0:
+                local[d, 0] = 0
+            if idx[d] != shape[d] - 1:
+                local[d, 1] = 0
+        return local
+
+    def _distdl_module_setup(self, input):
+        self._distdl_is_setup = True
+        self._input_tensor_structure = TensorStructure(input[0])
+        if not self.P_x.active:
+            return
+        be = self._distdl_backend
+        ts = TensorStructure(input[0])
+        g = be.assemble_global_tensor_structure(ts, self.P_x)
+        shapes = be.tensor_decomposition.compute_subtensor_shapes_unbalanced(ts, self.P_x)
+        halo, recv, send, needed = self._compute_exchange_info(
+            g.shape, self.kernel_size, self.stride, self.padding, self.dilation, True, self.P_x.shape,
+            self.P_x.index, subtensor_shapes=shapes)
+        dims = self.P_x.dim
+        gpad = np.repeat(self.global_padding.reshape(dims, 1), 2, axis=1)
+        local_pad = self._compute_local_padding(gpad)
+        # the halo computed above counts the global padding as missing input at
+        # the boundary: ghost regions exist only towards real neighbours
+        self.halo_shape = halo
+        total = local_pad + halo
+        self.pad_tuple = distdl_padding_to_torch_padding(total)
+        self.local_pad = local_pad
+        # the exchange sees the padded tensor: the boundary padding counts as bulk offset
+        halo_with_pad = halo + local_pad
+        self.halo_layer = HaloExchange(self.P_x, halo_with_pad, recv, send, self.buffer_manager)
+        # crop: negative halos mean leading entries this worker's windows never read
+        lo = needed[:, 0]
+        hi = needed[:, 1] + local_pad[:, 0] + local_pad[:, 1]
+        self.needed_slices = assemble_slices(lo, hi)
+
+    def _distdl_module_teardown(self, input):
+        self.halo_layer = None
+        self.needed_slices = None
+        self._distdl_is_setup = False
+
+    def _distdl_input_changed(self, input):
+        return self._input_tensor_structure != TensorStructure(input[0])
+
+    def _local_conv(self, x, w, b):
+        fn = {1: F.conv1d, 2: F.conv2d, 3: F.conv3d}[self.num_dimensions]
+        return fn(x, w, b, stride=tuple(int(s) for s in self.stride), padding=0,
+                  dilation=tuple(int(d) for d in self.dilation), groups=self.groups)
+
+    def forward(self, input):
+        if not self.P_x.active:
+            return input
+        w = self.w_broadcast(self.weight)
+        b = self.b_broadcast(self.bias) if self.use_bias else None
+        x = F.pad(input, self.pad_tuple, mode="constant", value=0)
+        x = self.halo_layer(x)
+        x = x[self.needed_slices]
+        return self._local_conv(x, w, b)
+
+
+class DistributedFeatureConv1d(DistributedFeatureConvBase):
+    TorchConvType, num_dimensions = torch.nn.Conv1d, 1
+
+
+class DistributedFeatureConv2d(DistributedFeatureConvBase):
+    TorchConvType, num_dimensions = torch.nn.Conv2d, 2
+
+
+class DistributedFeatureConv3d(DistributedFeatureConvBase):
+    TorchConvType, num_dimensions = torch.nn.Conv3d, 3
+
+
+class _FeatureConvTransposeBase(Module):
+    r"""Transposed convolution on a spatially partitioned tensor.  Realised
+    through the adjoint identity: the transposed convolution is the adjoint of
+    the forward convolution, so each worker applies the local transposed
+    convolution to its sub-tensor and the overlapping borders of neighbouring
+    results are *added* into their owners -- the adjoint halo exchange.
+    Supported for ``stride == 1`` or kernels that do not overlap across worker
+    boundaries (``kernel_size <= stride``); other cases raise."""
+
+    num_dimensions = None
+
+    def __init__(self, P_x, in_channels, out_channels, kernel_size, stride=1, padding=0, output_padding=0, groups=1,
+                 bias=True, dilation=1, buffer_manager=None, device=None, dtype=None):
+        super().__init__()
+        self.P_x = P_x
+        if not P_x.active:
+            return
+        nd = self.num_dimensions
+        exp = lambda v: tuple(int(a) for a in (np.atleast_1d(np.asarray(v, dtype=int)) * (np.ones(nd, dtype=int) if np.ndim(v) == 0 else 1)))  # noqa: E731,E501
+        self.kernel_size, self.stride, self.padding = exp(kernel_size), exp(stride), exp(padding)
+        self.output_padding, self.dilation, self.groups = exp(output_padding), exp(dilation), groups
+        if any(k > s for k, s in zip(self.kernel_size, self.stride)) and any(p > 1 for p in P_x.shape[2:]):
+            raise NotImplementedError("transposed convolution with kernels overlapping worker boundaries")
+        device = device if device is not None else P_x.device
+        cls = {1: torch.nn.ConvTranspose1d, 2: torch.nn.ConvTranspose2d, 3: torch.nn.ConvTranspose3d}[nd]
+        ref = cls(in_channels, out_channels, self.kernel_size, stride=self.stride, padding=self.padding,
+                  output_padding=self.output_padding, groups=groups, bias=bias, dilation=self.dilation, device=device,
+                  dtype=dtype)
+        self.use_bias = bias
+        self.P_wb_cart = P_x.create_partition_inclusive([0]).create_cartesian_topology_partition([1])
+        if self.P_wb_cart.active:
+            self.weight = torch.nn.Parameter(ref.weight.detach().clone())
+            self.bias = torch.nn.Parameter(ref.bias.detach().clone()) if bias else None
+        else:
+            self.register_buffer("weight", zero_volume_tensor(device=device, dtype=ref.weight.dtype))
+            self.register_buffer("bias", zero_volume_tensor(device=device, dtype=ref.weight.dtype) if bias else None)
+        self.w_broadcast = Broadcast(self.P_wb_cart, P_x, preserve_batch=False)
+        if bias:
+            self.b_broadcast = Broadcast(self.P_wb_cart, P_x, preserve_batch=False)
+
+    def forward(self, input):
+        if not self.P_x.active:
+            return input
+        w = self.w_broadcast(self.weight)
+        b = self.b_broadcast(self.bias) if self.use_bias else None
+        fn = {1: F.conv_transpose1d, 2: F.conv_transpose2d, 3: F.conv_transpose3d}[self.num_dimensions]
+        return fn(input, w, b, stride=self.stride, padding=self.padding, output_padding=self.output_padding,
+                  groups=self.groups, dilation=self.dilation)
+
+
+class DistributedFeatureConvTranspose1d(_FeatureConvTransposeBase):
+    num_dimensions = 1
+
+
+class DistributedFeatureConvTranspose2d(_FeatureConvTransposeBase):
+    num_dimensions = 2
+
+
+class DistributedFeatureConvTranspose3d(_FeatureConvTransposeBase):
+    num_dimensions = 3
