@@ -3,7 +3,10 @@
 // scatter-add, fused softmax-cross-entropy, fused AdamW on fp32 master weights,
 // sum of squares, residual add, cast.  All of them move 16 bytes per thread per
 // access and accumulate in fp32.
+#include <cstdio>
+
 #include "common.cuh"
+#include "no_alloc.h"
 
 using namespace dd;
 
@@ -644,5 +647,66 @@ DD_API int dd_cast_f32_bf16(const float* src, void* dst, long long n, float scal
 DD_API int dd_cast_bf16_f32(const void* src, float* dst, long long n, float scale, int accumulate, void* stream) {
   if (n <= 0) return DD_OK;
   cast_bf16_f32_kernel<<<grid_for(n, 256), 256, 0, STREAM(stream)>>>(CBF(src), dst, n, scale, accumulate);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// Norm backward without any allocation (declared in no_alloc.h).
+//
+// Same kernels as dd_norm_bwd, but the per-CTA partial sums of dw / db go to a
+// fixed array that is part of the loaded library instead of a buffer the caller
+// allocates.  For callers that are not able to allocate device memory at the
+// time of the call: a plug-in or custom-call hook inside a host program that
+// reserved the whole device up front (a later cudaMalloc there simply fails),
+// or a latency-critical section in which the implicit device synchronisation of
+// cudaMalloc / cudaFree is not acceptable.
+// ---------------------------------------------------------------------------
+namespace {
+constexpr int kNoAllocMaxD = kNormThreads * kMaxVec * 8;   // 8192 columns
+constexpr int kNoAllocParts = 148;                          // one partial row pair per SM
+// 148 * 2 * 8192 floats = 9.25 MiB, resident on every GPU that loads the library.
+static __device__ __align__(256) float g_norm_bwd_scratch[(size_t)kNoAllocParts * 2 * kNoAllocMaxD];
+float* g_norm_bwd_scratch_addr[64] = {nullptr};
+}  // namespace
+
+DD_API int dd_norm_bwd_noalloc_max_d() { return kNoAllocMaxD; }
+DD_API long long dd_norm_bwd_noalloc_scratch_bytes() { return (long long)sizeof(float) * kNoAllocParts * 2 * kNoAllocMaxD; }
+
+DD_API int dd_norm_bwd_noalloc(int rms, const void* dy, const void* x, const void* w, const void* stats, void* dx,
+                               float* dw, float* db, int accumulate, int rows, int d, void* stream) {
+  if (rows <= 0 || d <= 0 || d % 8 != 0) {
+    fprintf(stderr, "dd_norm_bwd_noalloc: rows must be positive and d a positive multiple of 8 (rows=%d, d=%d)\n",
+            rows, d);
+    return DD_ERR_BAD_ARG;
+  }
+  if (d > kNoAllocMaxD) {
+    fprintf(stderr, "dd_norm_bwd_noalloc: d=%d exceeds the built-in scratch (at most %d columns)\n", d, kNoAllocMaxD);
+    return DD_ERR_TOO_LARGE;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return DD_ERR_BAD_ARG;
+  // One-time set-up per device, with that device current: in host code the
+  // array's name is only a handle, the device address has to be looked up.
+  if (g_norm_bwd_scratch_addr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_norm_bwd_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_norm_bwd_scratch_addr[dev] = p;
+  }
+  float* partial = g_norm_bwd_scratch_addr[dev];
+  const int grid = rows < kNoAllocParts ? rows : kNoAllocParts;
+  // Every CTA overwrites its whole [2][d] slice of the scratch, so nothing left
+  // by an earlier call is ever read: no clearing is needed.
+  if (rms)
+    norm_bwd_kernel<true><<<grid, kNormThreads, 0, STREAM(stream)>>>(CBF(dy), CBF(x), CBF(w), (const float2*)stats,
+                                                                     nullptr, BF(dx), partial, rows, d);
+  else
+    norm_bwd_kernel<false><<<grid, kNormThreads, 0, STREAM(stream)>>>(CBF(dy), CBF(x), CBF(w),
+                                                                      (const float2*)stats, nullptr, BF(dx), partial,
+                                                                      rows, d);
+  if (dw != nullptr || db != nullptr)
+    norm_bwd_reduce_kernel<<<(d + 255) / 256, 256, 0, STREAM(stream)>>>(partial, grid, d, dw, db, accumulate);
   return (int)cudaGetLastError();
 }
