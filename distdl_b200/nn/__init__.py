@@ -28,3 +28,5 @@ from .loss import (DistributedBCELoss, DistributedBCEWithLogitsLoss, Distributed
                    DistributedL1Loss, DistributedMSELoss, DistributedPoissonNLLLoss)
 from .pooling import (DistributedAvgPool1d, DistributedAvgPool2d, DistributedAvgPool3d,  # noqa: F401,E402
                       DistributedMaxPool1d, DistributedMaxPool2d, DistributedMaxPool3d)
+from .linear_ag_expert import DistributedExpertAllGather  # noqa: F401,E402
+from .linear_rs_expert import DistributedExpertReduceScatter  # noqa: F401,E402

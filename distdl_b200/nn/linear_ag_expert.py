@@ -1,0 +1,126 @@
+"""Expert-parallel column-parallel linear layer
+(``src/distdl/nn/linear_ag_expert.py:22-422``)."""
+import math
+
+import torch
+
+from ..utilities.slicing import compute_subshape
+from ..utilities.torch import zero_volume_tensor
+from ._linear_common import PrefetchStream, derived_partition
+from .all_gather import AllGather
+from .broadcast import Broadcast
+from .module import Module
+from .reduce_scatter import ReduceScatter
+
+
+def _expert_matmul(x, w):
+    """x [e, rows, in], w [e, out, in] -> [e, rows, out] (grouped GEMM on the native kernel on CUDA)."""
+    from ..models.moe import batched_linear
+    return batched_linear(x, w)
+
+
+class DistributedExpertAllGather(Module):
+    r"""One linear map per expert, ``y[e] = x[e] W[e]^T + b[e]``, on routed tokens
+    ``[expert, capacity, seq, feat]``.
+
+    ``P_expert_emb = [E, N, 1, M]``: experts split over ``E`` (expert
+    parallelism), capacity over ``N`` (data parallelism inside an expert
+    group), features over ``M`` (tensor parallelism); ``P_expert_seq =
+    [E, N, S, 1]`` selects sequence-sharded input instead.  Weight shard
+    ``[experts/E, in/N, out/M]`` on ``P_weight = [E, N, M]``: ZeRO-sharded over
+    ``N`` along the input features, gathered on use; bias ``[experts/E, 1,
+    out/M]`` on the first ``N`` row.  Forward: gather weight, broadcast bias,
+    all-gather the tokens over ``M`` (features, or sequence), grouped GEMM.
+    ``auto_clear_buffer=False`` keeps the gathered weights across micro-batches."""
+
+    def __init__(self, P_expert_emb, num_experts, in_features, out_features, bias=True, device=None, dtype=None,
+                 P_weight=None, P_bias=None, collect_state=False, scale_backward=None, P_expert_seq=None,
+                 auto_clear_buffer=True, geglu=False):
+        super().__init__()
+        self.P_expert_emb, self.P_expert_seq = P_expert_emb, P_expert_seq
+        if not P_expert_emb.active:
+            return
+        assert P_expert_emb.dim == 4
+        device = device if device is not None else P_expert_emb.device
+        kw = {"device": device, "dtype": dtype}
+        self.num_experts, self.in_features, self.out_features = num_experts, in_features, out_features
+        self.use_bias, self.geglu, self.collect_state = bias, geglu, collect_state
+        self.scale_backward, self.auto_clear_buffer, self.dtype = scale_backward, auto_clear_buffer, dtype
+        E, N, M = (int(P_expert_emb.shape[i]) for i in (0, 1, 3))
+        if P_weight is None:
+            P_weight = P_expert_emb.create_partition_inclusive(range(P_expert_emb.size)) \
+                .create_cartesian_topology_partition([E, N, M])
+        self.P_weight = P_weight
+        if bias and P_bias is None:
+            P_bias = derived_partition(P_weight, [slice(0, E), slice(0, 1), slice(0, M)], [E, 1, M])
+        self.P_bias = P_bias if bias else None
+        self.e_local = int(compute_subshape(E, P_weight.index[0], [num_experts])[0])
+        in_local = int(compute_subshape(N, P_weight.index[1], [in_features])[0])
+        self.out_local = int(compute_subshape(M, P_weight.index[2], [out_features])[0])
+        self.weight = torch.nn.Parameter(torch.empty(self.e_local, in_local, self.out_local, **kw))
+        if bias and self.P_bias.active:
+            self.bias = torch.nn.Parameter(torch.empty(self.e_local, 1, self.out_local, **kw))
+        elif bias:
+            self.register_buffer("bias", zero_volume_tensor(device=device, dtype=dtype, requires_grad=True))
+        else:
+            self.register_parameter("bias", None)
+        self.reset_parameters()
+        if P_expert_seq is not None:
+            self.all_gather_hidden = AllGather(P_expert_seq, axes_all_gather=(2,))
+        else:
+            self.all_gather_hidden = AllGather(P_expert_emb, axes_all_gather=(3,))
+        self.all_gather_weight = AllGather(P_weight, axes_all_gather=(1,), scale_backward=scale_backward)
+        self.reduce_scatter_weight = ReduceScatter(P_weight, axes_reduce_scatter=(1,))
+        if bias:
+            self.broadcast_bias = Broadcast(self.P_bias, P_weight, scale_backward=scale_backward,
+                                            preserve_batch=False)
+        self.prefetch = PrefetchStream(device)
+        self.weight_buffer = None
+        self.bias_buffer = None
+
+    def reset_parameters(self):
+        bound = 1 / math.sqrt(self.in_features) if self.in_features > 0 else 0
+        with torch.no_grad():
+            self.weight.uniform_(-bound, bound)
+            if self.use_bias and self.P_bias.active:
+                self.bias.uniform_(-bound, bound)
+
+    def _collect_weights(self):
+        w = self.all_gather_weight(self.weight)                 # [e, in, out/M]
+        self.weight_buffer = w if self.auto_clear_buffer else w.detach().requires_grad_(True)
+        if self.use_bias:
+            self.bias_buffer = self.broadcast_bias(self.bias)
+
+    def collect_weights(self):
+        if self.weight_buffer is None:
+            self.prefetch.run(self._collect_weights)
+
+    prefetch_weights = collect_weights
+
+    def wait_for_streams(self):
+        self.prefetch.wait()
+
+    def clear_weight_buffer(self):
+        if not self.auto_clear_buffer and self.weight_buffer is not None and self.weight_buffer.grad is not None:
+            g = self.weight_buffer.grad
+            if self.scale_backward is not None:
+                g = g / self.scale_backward
+            gl = self.reduce_scatter_weight(g)
+            self.weight.grad = gl if self.weight.grad is None else self.weight.grad + gl
+        self.weight_buffer = None
+        self.bias_buffer = None
+
+    def forward(self, input):
+        if not self.P_expert_emb.active:
+            return input
+        self.collect_weights()
+        self.wait_for_streams()
+        w, b = self.weight_buffer, self.bias_buffer
+        x = self.all_gather_hidden(input)                       # [e, c, s, in]
+        e, c, s, m = x.shape
+        y = _expert_matmul(x.reshape(e, c * s, m), w.transpose(1, 2))
+        if b is not None:
+            y = y + b.reshape(e, 1, -1)
+        if self.auto_clear_buffer:
+            self.clear_weight_buffer()
+        return y.reshape(e, c, s, -1)

@@ -245,8 +245,13 @@ class DistributedLinearAllGatherZero(Module):
         self.collect_weights()
         self.wait_for_streams()
         w, b = self.weight_buffer, self.bias_buffer
-        x = self.all_gather(input)
-        y = ops.linear(x, w.t(), b)
+        y = None
+        if input.is_cuda and getattr(self._distdl_backend, "name", "") == "native_cupy":
+            from ..parallel import fused
+            y = fused.maybe_ag_linear(self, input, w.t(), b)
+        if y is None:
+            x = self.all_gather(input)
+            y = ops.linear(x, w.t(), b)
         if self.auto_clear_buffer:
             self.clear_weight_buffer()
         return y

@@ -174,6 +174,11 @@ class DistributedLinearReduceScatterZero(Module):
         self.bias_buffer = None
 
     def _apply(self, input, w, b):
+        if input.is_cuda and getattr(self._distdl_backend, "name", "") == "native_cupy":
+            from ..parallel import fused
+            y = fused.maybe_linear_rs(self, input, w, b)
+            if y is not None:
+                return y
         y = ops.linear(input, w, b)
         return self.reduce_scatter(y)
 

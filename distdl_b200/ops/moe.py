@@ -1,0 +1,120 @@
+"""Mixture-of-experts token routing ops (slot assignment, permuted scatter,
+weighted gather) with autograd; CUDA kernels in ``csrc/moe.cu``.  New relative to
+the reference (its expert layers expect already-routed ``[expert, capacity,
+...]`` tensors, ``src/distdl/nn/linear_ag_expert.py:393-422``)."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _native
+from ._util import ptr, stream_ptr, use_native
+
+_v, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_native.declare("dd_moe_assign", [_v, _i, _i, _i, _v, _v, _v])
+_native.declare("dd_moe_scatter_rows", [_v, _v, _v, _v, _v, _i, _i, _i, _i, _v])
+_native.declare("dd_moe_gather_rows", [_v, _v, _v, _v, _v, _i, _i, _i, _i, _v])
+_native.declare("dd_moe_pair_dot", [_v, _v, _v, _v, _v, _i, _i, _i, _i, _v])
+
+
+def assign_slots(ids: torch.Tensor, num_experts: int, capacity: int):
+    """ids [pairs] int32 -> (slot [pairs] int32 with -1 for dropped pairs, counts [E] int32)."""
+    flat = ids.reshape(-1).to(torch.int32).contiguous()
+    if use_native(flat):
+        counts = torch.zeros(num_experts, dtype=torch.int32, device=flat.device)
+        slot = torch.empty_like(flat)
+        _native.call("dd_moe_assign", flat.data_ptr(), flat.numel(), num_experts, capacity, counts.data_ptr(),
+                     slot.data_ptr(), stream_ptr())
+        return slot, counts
+    onehot = torch.nn.functional.one_hot(flat.long(), num_experts)
+    pos = (onehot.cumsum(0) - 1)[torch.arange(flat.numel()), flat.long()]
+    slot = torch.where(pos < capacity, pos, torch.full_like(pos, -1)).to(torch.int32)
+    return slot, onehot.sum(0).to(torch.int32)
+
+
+def _scatter(src, ids, slot, w, E, C, k):
+    d = src.shape[-1]
+    dst = torch.zeros(E, C, d, dtype=src.dtype, device=src.device)
+    if use_native(src) and src.dtype == torch.bfloat16 and d % 8 == 0:
+        _native.call("dd_moe_scatter_rows", src.data_ptr(), ids.data_ptr(), slot.data_ptr(), ptr(w), dst.data_ptr(),
+                     ids.numel(), k, C, d, stream_ptr())
+        return dst
+    keep = slot >= 0
+    rows = src[torch.arange(ids.numel(), device=src.device) // k]
+    if w is not None:
+        rows = rows * w.reshape(-1, 1).to(rows.dtype)
+    dst[ids[keep].long(), slot[keep].long()] = rows[keep]
+    return dst
+
+
+def _gather(src, ids, slot, w, tokens, k):
+    E, C, d = src.shape
+    if use_native(src) and src.dtype == torch.bfloat16 and d % 8 == 0:
+        dst = torch.empty(tokens, d, dtype=src.dtype, device=src.device)
+        _native.call("dd_moe_gather_rows", src.data_ptr(), ids.data_ptr(), slot.data_ptr(), ptr(w), dst.data_ptr(),
+                     tokens, k, C, d, stream_ptr())
+        return dst
+    keep = (slot >= 0).reshape(tokens, k, 1)
+    rows = src[ids.long().clamp(min=0), slot.long().clamp(min=0)].reshape(tokens, k, d).float()
+    if w is not None:
+        rows = rows * w.reshape(tokens, k, 1)
+    return (rows * keep).sum(1).to(src.dtype)
+
+
+def _pair_dot(a, b, ids, slot, k):
+    E, C, d = b.shape
+    n = ids.numel()
+    if use_native(a) and a.dtype == torch.bfloat16 and d % 8 == 0:
+        out = torch.empty(n, dtype=torch.float32, device=a.device)
+        _native.call("dd_moe_pair_dot", a.data_ptr(), b.data_ptr(), ids.data_ptr(), slot.data_ptr(), out.data_ptr(),
+                     n, k, C, d, stream_ptr())
+        return out
+    rows = b[ids.long().clamp(min=0), slot.long().clamp(min=0)].float()
+    av = a[torch.arange(n, device=a.device) // k].float()
+    return (rows * av).sum(-1) * (slot >= 0)
+
+
+class DispatchFn(torch.autograd.Function):
+    """x [T, d] -> per-expert capacity buffers [E, C, d] (unused slots zero)."""
+
+    @staticmethod
+    def forward(ctx, x, ids, slot, E, C, k):
+        ctx.save_for_backward(ids, slot)
+        ctx.cfg = (x.shape[0], k)
+        return _scatter(x.contiguous(), ids, slot, None, E, C, k)
+
+    @staticmethod
+    def backward(ctx, g):
+        ids, slot = ctx.saved_tensors
+        T, k = ctx.cfg
+        return _gather(g.contiguous(), ids, slot, None, T, k), None, None, None, None, None
+
+
+class CombineFn(torch.autograd.Function):
+    """y[t] = sum_c w[t, c] * buf[ids[t, c], slot[t, c]]."""
+
+    @staticmethod
+    def forward(ctx, buf, w, ids, slot, T, k):
+        bufc, wc = buf.contiguous(), w.reshape(-1).float().contiguous()
+        ctx.save_for_backward(bufc, wc, ids, slot)
+        ctx.cfg = (T, k, w.shape, w.dtype)
+        return _gather(bufc, ids, slot, wc, T, k)
+
+    @staticmethod
+    def backward(ctx, dy):
+        buf, w, ids, slot = ctx.saved_tensors
+        T, k, wshape, wdtype = ctx.cfg
+        E, C, d = buf.shape
+        dyc = dy.contiguous()
+        dbuf = _scatter(dyc, ids, slot, w, E, C, k)
+        dw = _pair_dot(dyc, buf, ids, slot, k).reshape(wshape).to(wdtype)
+        return dbuf, dw, None, None, None, None
+
+
+def dispatch(x, ids, slot, num_experts, capacity, k):
+    return DispatchFn.apply(x, ids, slot, num_experts, capacity, k)
+
+
+def combine(buf, weights, ids, slot, tokens, k):
+    return CombineFn.apply(buf, weights, ids, slot, tokens, k)

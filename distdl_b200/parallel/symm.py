@@ -42,6 +42,9 @@ _native.declare("dd_alltoall", _TEAM + [c_void_p, c_size_t, _IP, c_void_p])
 _native.declare("dd_team_barrier", _TEAM + [_IP, c_void_p])
 
 SIGNAL_PAD_BYTES = 64 * 1024
+MB = 1 << 20
+# Regions of the staging buffer (same layout on every process).
+REGION_SIZES = (("coll", None), ("ag_shard", 128 * MB), ("rs0", 224 * MB), ("rs1", 224 * MB), ("misc", 4 * MB))
 
 
 class SymmetricHeap:
@@ -57,9 +60,16 @@ class SymmetricHeap:
         if self.world > self.max_peers:
             raise RuntimeError(f"the native transport handles up to {self.max_peers} GPUs of one node")
         self.staging_bytes = int(staging_bytes)
+        self.regions = {}
+        off = 0
+        for name, size in REGION_SIZES:
+            size = self.staging_bytes if size is None else size
+            self.regions[name] = (off, size)
+            off += size
+        self.total_bytes = off
         self.device = torch.device("cuda", torch.cuda.current_device())
         self._local_buf, self._local_pad = c_void_p(), c_void_p()
-        _native.check(lib.dd_symm_alloc(self.staging_bytes, ctypes.byref(self._local_buf)), "dd_symm_alloc")
+        _native.check(lib.dd_symm_alloc(self.total_bytes, ctypes.byref(self._local_buf)), "dd_symm_alloc")
         _native.check(lib.dd_symm_alloc(SIGNAL_PAD_BYTES, ctypes.byref(self._local_pad)), "dd_symm_alloc")
         hb, hp = ctypes.create_string_buffer(64), ctypes.create_string_buffer(64)
         _native.check(lib.dd_ipc_get_handle(self._local_buf, hb), "dd_ipc_get_handle")
@@ -89,6 +99,19 @@ class SymmetricHeap:
             raise ValueError(f"{nbytes} bytes exceed the staging buffer ({self.staging_bytes})")
         n = nbytes // torch.empty((), dtype=dtype).element_size()
         return _wrap_device_pointer(self._local_buf.value, n, dtype, self.device)
+
+    def region_ptr(self, name, rank=None, offset=0):
+        """Address of a region in the staging buffer of ``rank`` (default: mine), as mapped here."""
+        base = self.buf_ptrs[self.rank if rank is None else rank]
+        return base + self.regions[name][0] + offset
+
+    def region_tensor(self, name, nbytes, dtype=torch.uint8, offset=0):
+        """Tensor view of (the head of) one of my regions."""
+        off, size = self.regions[name]
+        if offset + nbytes > size:
+            raise ValueError(f"{nbytes} bytes do not fit region {name!r} ({size} bytes)")
+        n = nbytes // torch.empty((), dtype=dtype).element_size()
+        return _wrap_device_pointer(self._local_buf.value + off + offset, n, dtype, self.device)
 
     def team_args(self, ranks):
         """ctypes arguments describing a team (ordered world ranks containing this rank)."""
@@ -132,7 +155,7 @@ def heap(staging_bytes: int = None) -> SymmetricHeap:
     """The process-wide heap (created on first use; every process must call)."""
     global _heap
     if _heap is None:
-        size = staging_bytes or int(os.environ.get("DISTDL_SYMM_BYTES", str(1 << 30)))
+        size = staging_bytes or int(os.environ.get("DISTDL_SYMM_BYTES", str(512 * MB)))
         _heap = SymmetricHeap(size)
     return _heap
 

@@ -1,0 +1,61 @@
+"""Fused all-gather->GEMM and GEMM->reduce-scatter against the unfused NCCL +
+fp32 reference, forward and backward."""
+import torch
+import torch.distributed as dist
+
+
+def check_fused():
+    from distdl_b200 import _native
+    from distdl_b200.parallel import fused
+    world, rank = dist.get_world_size(), dist.get_rank()
+    ranks = tuple(range(world))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    for (b, s_local, K, N) in [(1, 128, 256, 512), (2, 256, 1024, 768), (2, 1024, 4096, 3072)]:
+        for trial in range(2):
+            torch.manual_seed(1000 + trial)            # same weights everywhere
+            w = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16).requires_grad_()
+            bias = (torch.randn(N, device=dev) * 0.1).to(torch.bfloat16).requires_grad_()
+            torch.manual_seed(rank * 7 + trial)
+            x = torch.randn(b, s_local, K, device=dev).to(torch.bfloat16).requires_grad_()
+            # ---- all-gather -> GEMM
+            y = fused.AgLinearFn.apply(x, w, bias, ranks)
+            xs = [torch.empty_like(x) for _ in range(world)]
+            dist.all_gather(xs, x.detach())
+            xg = torch.cat(xs, dim=1).float()
+            ref = xg @ w.detach().float().t() + bias.detach().float()
+            err = (y.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+            assert err < 2e-2, ("ag_gemm fwd", b, s_local, K, N, err)
+            dy = torch.randn_like(y)
+            y.backward(dy)
+            dxg = dy.float() @ w.detach().float()                      # [b, P*s_local, K] partial of this member
+            dist.all_reduce(dxg)
+            dx_ref = dxg[:, rank * s_local:(rank + 1) * s_local]
+            err = (x.grad.float() - dx_ref).abs().max().item() / (dx_ref.abs().max().item() + 1e-6)
+            assert err < 3e-2, ("ag_gemm dx", b, s_local, K, N, err)
+            dw_ref = dy.reshape(-1, N).float().t() @ xg.reshape(-1, K)
+            err = (w.grad.float() - dw_ref).abs().max().item() / (dw_ref.abs().max().item() + 1e-6)
+            assert err < 3e-2, ("ag_gemm dw", err)
+            # ---- GEMM -> reduce-scatter (row parallel: K is this member's feature slice)
+            w2 = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16).requires_grad_()
+            xin = torch.randn(b, world * s_local, K, device=dev).to(torch.bfloat16).requires_grad_()
+            out = fused.LinearRsFn.apply(xin, w2, bias.detach() if rank == 0 else None, ranks)
+            full = xin.detach().float() @ w2.detach().float().t()
+            if rank == 0:
+                full = full + bias.detach().float()
+            dist.all_reduce(full)
+            ref = full[:, rank * s_local:(rank + 1) * s_local]
+            err = (out.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+            assert err < 3e-2, ("gemm_rs fwd", b, s_local, K, N, err)
+            dyl = torch.randn_like(out)
+            out.backward(dyl)
+            dys = [torch.empty_like(dyl) for _ in range(world)]
+            dist.all_gather(dys, dyl)
+            dyg = torch.cat(dys, dim=1).float()
+            dx_ref = dyg @ w2.detach().float()
+            err = (xin.grad.float() - dx_ref).abs().max().item() / (dx_ref.abs().max().item() + 1e-6)
+            assert err < 3e-2, ("gemm_rs dx", err)
+            dw_ref = dyg.reshape(-1, N).t() @ xin.detach().reshape(-1, K).float()
+            err = (w2.grad.float() - dw_ref).abs().max().item() / (dw_ref.abs().max().item() + 1e-6)
+            assert err < 3e-2, ("gemm_rs dw", err)
+    torch.cuda.synchronize()
+    assert _native.read_status()[0] == 0, _native.read_status()

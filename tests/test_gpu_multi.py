@@ -33,3 +33,8 @@ def test_native_collectives_match_nccl():
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_primitives_on_native_backend():
     _run("primitives", min(_ngpu(), 8))
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_fused_ag_gemm_and_gemm_rs():
+    _run("fused", min(_ngpu(), 8))
