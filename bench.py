@@ -144,7 +144,7 @@ def main():
     seq = cfg.max_seq
     global_batch = args.seqs_per_gpu * args.gpus
     local_batch = global_batch // dp
-    micro = args.micro_batch or (1 if args.gpus == 1 else 2)
+    micro = args.micro_batch or {1: 1, 2: 2}.get(args.gpus, 4)
     torch.manual_seed(1234 + rank)
     layout = models.ParallelLayout(dp, tp)
     model = models.Decoder(cfg, layout).cuda() if False else models.Decoder(cfg, layout)

@@ -38,8 +38,13 @@ class AllGatherFunction(TransportBound, torch.autograd.Function):
                 s = list(input.shape)
                 s[axis] = e
                 shapes.append(s)
-        parts = cls.transport().allgather(input.detach(), list(P_allgather.ranks), shapes)
-        out = torch.cat(parts, dim=axis)
+        if axis == 0 and shapes is None:
+            # equal shards along the leading axis: the stacked result *is* the concatenation
+            stacked = cls.transport().allgather_stacked(input.detach(), list(P_allgather.ranks))
+            out = stacked.reshape((-1,) + tuple(input.shape[1:]))
+        else:
+            parts = cls.transport().allgather(input.detach(), list(P_allgather.ranks), shapes)
+            out = torch.cat(parts, dim=axis)
         out.requires_grad_(bool(output_tensor_structure.requires_grad) and out.is_floating_point())
         return out
 
@@ -51,6 +56,10 @@ class AllGatherFunction(TransportBound, torch.autograd.Function):
             return grad_output.clone(), None, None, None, None, None
         axis = int(ctx.axes[0])
         g = scaled(grad_output, ctx.scale_backward).detach()
-        chunks = list(torch.split(g, ctx.extents, dim=axis))
-        out = cls.transport().reduce_scatter(chunks, list(P.ranks))
+        if axis == 0 and len(set(ctx.extents)) == 1:
+            stacked = g.contiguous().reshape((P.size, ctx.extents[0]) + tuple(g.shape[1:]))
+            out = cls.transport().reduce_scatter_stacked(stacked, list(P.ranks))
+        else:
+            chunks = list(torch.split(g, ctx.extents, dim=axis))
+            out = cls.transport().reduce_scatter(chunks, list(P.ranks))
         return out, None, None, None, None, None

@@ -165,6 +165,14 @@ class P2PTransport:
             total = c.clone() if total is None else total.add_(c)
         return total.to(dt).to(device)
 
+    def allgather_stacked(self, tensor, ranks):
+        """Equal shapes: ``[P, *shape]`` with every member's tensor."""
+        return torch.stack(self.allgather(tensor, ranks))
+
+    def reduce_scatter_stacked(self, stacked, ranks):
+        """``stacked[i]`` is my contribution to member ``i`` (equal shapes)."""
+        return self.reduce_scatter(list(stacked.unbind(0)), ranks)
+
     def exchange(self, sends, recvs):
         """Generic neighbour exchange.  ``sends`` = [(world_rank, tensor)],
         ``recvs`` = [(world_rank, shape, dtype)] -> list of received tensors (CPU

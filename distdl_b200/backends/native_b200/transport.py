@@ -51,3 +51,13 @@ class NativeTransport(GroupTransport):
         if self._native_ok(chunks[0], ranks) and len({tuple(c.shape) for c in chunks}) == 1:
             return self._collectives().reduce_scatter(torch.stack([c.contiguous() for c in chunks]), ranks)
         return super().reduce_scatter(chunks, ranks)
+
+    def allgather_stacked(self, tensor, ranks):
+        if self._native_ok(tensor, ranks):
+            return self._collectives().all_gather(tensor, ranks)
+        return super().allgather_stacked(tensor, ranks)
+
+    def reduce_scatter_stacked(self, stacked, ranks):
+        if self._native_ok(stacked, ranks):
+            return self._collectives().reduce_scatter(stacked, ranks)
+        return super().reduce_scatter_stacked(stacked, ranks)

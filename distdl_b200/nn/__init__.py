@@ -30,3 +30,6 @@ from .pooling import (DistributedAvgPool1d, DistributedAvgPool2d, DistributedAvg
                       DistributedMaxPool1d, DistributedMaxPool2d, DistributedMaxPool3d)
 from .linear_ag_expert import DistributedExpertAllGather  # noqa: F401,E402
 from .linear_rs_expert import DistributedExpertReduceScatter  # noqa: F401,E402
+from .conv import DistributedConv1d, DistributedConv2d, DistributedConv3d  # noqa: F401,E402
+from .conv_channel import DistributedChannelConv1d, DistributedChannelConv2d, DistributedChannelConv3d  # noqa: F401,E402
+from .conv_general import DistributedGeneralConv1d, DistributedGeneralConv2d, DistributedGeneralConv3d  # noqa: F401,E402
