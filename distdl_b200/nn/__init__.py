@@ -33,3 +33,10 @@ from .linear_rs_expert import DistributedExpertReduceScatter  # noqa: F401,E402
 from .conv import DistributedConv1d, DistributedConv2d, DistributedConv3d  # noqa: F401,E402
 from .conv_channel import DistributedChannelConv1d, DistributedChannelConv2d, DistributedChannelConv3d  # noqa: F401,E402
 from .conv_general import DistributedGeneralConv1d, DistributedGeneralConv2d, DistributedGeneralConv3d  # noqa: F401,E402
+from .conv_channel_ag import (DistributedChannelAllGatherConv1d, DistributedChannelAllGatherConv2d,  # noqa: F401,E402
+                              DistributedChannelAllGatherConv3d, DistributedChannelAllGatherConvTranspose1d,
+                              DistributedChannelAllGatherConvTranspose2d, DistributedChannelAllGatherConvTranspose3d)
+from .conv_channel_rs import (DistributedChannelReduceScatterConv1d, DistributedChannelReduceScatterConv2d,  # noqa: F401,E402
+                              DistributedChannelReduceScatterConv3d, DistributedChannelReduceScatterConvTranspose1d,
+                              DistributedChannelReduceScatterConvTranspose2d,
+                              DistributedChannelReduceScatterConvTranspose3d)

@@ -67,8 +67,10 @@ class DistributedFeatureConvBase(Module, HaloMixin, ConvMixin):
             else:
                 self.register_buffer("bias", None)
         else:
-            self.register_buffer("weight", zero_volume_tensor(device=device, dtype=w0.dtype))
-            self.register_buffer("bias", zero_volume_tensor(device=device, dtype=w0.dtype) if bias else None)
+            # zero-volume stand-ins must require grad, or autograd would skip the adjoint of the broadcast here
+            self.register_buffer("weight", zero_volume_tensor(device=device, dtype=w0.dtype, requires_grad=True))
+            self.register_buffer("bias", zero_volume_tensor(device=device, dtype=w0.dtype, requires_grad=True)
+                                 if bias else None)
         self.w_broadcast = Broadcast(self.P_wb_cart, P_x, preserve_batch=False)
         if bias:
             self.b_broadcast = Broadcast(self.P_wb_cart, P_x, preserve_batch=False)
@@ -186,8 +188,9 @@ class _FeatureConvTransposeBase(Module):
             self.weight = torch.nn.Parameter(ref.weight.detach().clone())
             self.bias = torch.nn.Parameter(ref.bias.detach().clone()) if bias else None
         else:
-            self.register_buffer("weight", zero_volume_tensor(device=device, dtype=ref.weight.dtype))
-            self.register_buffer("bias", zero_volume_tensor(device=device, dtype=ref.weight.dtype) if bias else None)
+            self.register_buffer("weight", zero_volume_tensor(device=device, dtype=ref.weight.dtype, requires_grad=True))
+            self.register_buffer("bias", zero_volume_tensor(device=device, dtype=ref.weight.dtype, requires_grad=True)
+                                 if bias else None)
         self.w_broadcast = Broadcast(self.P_wb_cart, P_x, preserve_batch=False)
         if bias:
             self.b_broadcast = Broadcast(self.P_wb_cart, P_x, preserve_batch=False)

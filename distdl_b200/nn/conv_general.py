@@ -41,18 +41,38 @@ class DistributedGeneralConvBase(Module, HaloMixin, ConvMixin):
         if padding_mode != "zeros":
             raise NotImplementedError("only zero padding is supported")
         device = device if device is not None else (P_w.device if P_w.active else P_x.device)
+        # Weights live once per (out-channel, in-channel) block, on the workers of
+        # P_w with spatial index 0 (P_wr), and are broadcast to the spatial replicas.
+        self.has_bias_here = False
         if P_w.active:
+            from ._linear_common import derived_partition
+            dim = P_w.dim
+            idx = [slice(0, int(P_w.shape[0])), slice(0, int(P_w.shape[1]))] + [slice(0, 1)] * (dim - 2)
+            shape = [int(P_w.shape[0]), int(P_w.shape[1])] + [1] * (dim - 2)
+            self.P_wr = derived_partition(P_w, idx, shape)
+            self.w_broadcast = Broadcast(self.P_wr, P_w, preserve_batch=False)
+            self.b_broadcast = Broadcast(self.P_wr, P_w, preserve_batch=False) if bias else None
             co = int(compute_subshape(P_w.shape[0], P_w.index[0], [out_channels])[0])
             ci = int(compute_subshape(P_w.shape[1], P_w.index[1], [in_channels])[0])
             fan_in = in_channels // groups * int(np.prod(self.kernel_size))
             bound = 1.0 / np.sqrt(fan_in)
-            self.weight = torch.nn.Parameter(
-                torch.empty(co, ci // groups, *[int(k) for k in self.kernel_size], device=device,
-                            dtype=dtype).uniform_(-bound, bound))
-            if bias and int(P_w.index[1]) == 0:
-                self.bias = torch.nn.Parameter(torch.empty(co, device=device, dtype=dtype).uniform_(-bound, bound))
+            self.has_bias_here = bias and int(P_w.index[1]) == 0
+            if self.P_wr.active:
+                self.weight = torch.nn.Parameter(
+                    torch.empty(co, ci // groups, *[int(k) for k in self.kernel_size], device=device,
+                                dtype=dtype).uniform_(-bound, bound))
+                if self.has_bias_here:
+                    self.bias = torch.nn.Parameter(torch.empty(co, device=device, dtype=dtype).uniform_(-bound, bound))
+                elif bias:
+                    self.register_buffer("bias", zero_volume_tensor(device=device, dtype=dtype, requires_grad=True))
+                else:
+                    self.register_parameter("bias", None)
             else:
-                self.register_parameter("bias", None)
+                self.register_buffer("weight", zero_volume_tensor(device=device, dtype=dtype, requires_grad=True))
+                if bias:
+                    self.register_buffer("bias", zero_volume_tensor(device=device, dtype=dtype, requires_grad=True))
+                else:
+                    self.register_parameter("bias", None)
         else:
             self.register_buffer("weight", zero_volume_tensor(device=device, dtype=dtype))
             self.register_parameter("bias", None)
@@ -104,7 +124,11 @@ class DistributedGeneralConvBase(Module, HaloMixin, ConvMixin):
             x = x[self.needed_slices]
         x = self.x_broadcast(x)
         if self.P_w.active:
-            x = _CONV[self.num_dimensions](x, self.weight, self.bias, stride=tuple(int(s) for s in self.stride),
+            w = self.w_broadcast(self.weight)
+            b = self.b_broadcast(self.bias) if self.use_bias else None
+            if not self.has_bias_here:
+                b = None
+            x = _CONV[self.num_dimensions](x, w, b, stride=tuple(int(s) for s in self.stride),
                                            padding=0, dilation=tuple(int(d) for d in self.dilation),
                                            groups=self.groups)
         return self.y_sum_reduce(x)

@@ -1,0 +1,206 @@
+"""Convolution, pooling, batch-norm and loss layers against serial PyTorch on
+CPU ranks, plus the halo arithmetic golden values."""
+import numpy as np
+import pytest
+import torch
+
+from dist_harness import run_ranks
+
+
+def test_halo_mixin_golden_values():
+    """Expected arrays for a [1,1,10] tensor, kernel 2 / stride 2 pooling, on a
+    [1,1,4] partition (values as in the reference's utility test)."""
+    from distdl_b200.nn.mixins import HaloMixin, PoolingMixin
+
+    class Mock(HaloMixin, PoolingMixin):
+        pass
+    want = {0: ([[0, 0], [0, 0], [0, 1]], [[0, 0], [0, 0], [0, 1]], [[0, 0], [0, 0], [0, 0]], [[0, 1], [0, 1], [0, 4]]),
+            1: ([[0, 0], [0, 0], [0, 0]], [[0, 0], [0, 0], [0, 0]], [[0, 0], [0, 0], [1, 0]], [[0, 1], [0, 1], [1, 3]]),
+            2: ([[0, 0], [0, 0], [0, 0]], [[0, 0], [0, 0], [0, 0]], [[0, 0], [0, 0], [0, 0]], [[0, 1], [0, 1], [0, 2]]),
+            3: ([[0, 0], [0, 0], [0, 0]], [[0, 0], [0, 0], [0, 0]], [[0, 0], [0, 0], [0, 0]], [[0, 1], [0, 1], [0, 2]])}
+    for r in range(4):
+        got = Mock()._compute_exchange_info(np.array([1, 1, 10]), np.array([2]), np.array([2]), np.array([0]),
+                                            np.array([1]), True, [1, 1, 4], [0, 0, r])
+        for g, w in zip(got, want[r]):
+            assert np.array_equal(g, np.array(w)), (r, g, w)
+    assert Mock()._compute_exchange_info(np.array([1, 1, 10]), [2], [2], [0], [1], False, [1, 1, 4], [0, 0, 0]) == \
+        (None, None, None, None)
+
+
+def _cart(ranks, shape):
+    import distdl_b200 as d
+    return d.backends.backend.Partition().create_partition_inclusive(ranks).create_cartesian_topology_partition(shape)
+
+
+def _scatter(P, x_global, rank, dim):
+    from distdl_b200.nn import Repartition
+    from distdl_b200.utilities.torch import zero_volume_tensor
+    P_root = _cart([0], [1] * dim)
+    x0 = x_global.clone().requires_grad_() if rank == 0 else zero_volume_tensor().requires_grad_()
+    return x0, Repartition(P_root, P, preserve_batch=False)(x0)
+
+
+def _gather(P, y, dim):
+    from distdl_b200.nn import Repartition
+    return Repartition(P, _cart([0], [1] * dim), preserve_batch=False)(y)
+
+
+def _sync(t):
+    import torch.distributed as dist
+    dist.broadcast(t, src=0)
+    return t
+
+
+def body_feature_conv_pool(rank, world):
+    from distdl_b200.nn import DistributedAvgPool2d, DistributedFeatureConv2d, DistributedMaxPool1d
+    torch.manual_seed(0)
+    P = _cart([0, 1, 2, 3], [1, 1, 2, 2])
+    xg = _sync(torch.randn(2, 3, 11, 9))
+    for (k, s, p, d) in [(3, 1, 1, 1), (3, 2, 1, 1), (2, 2, 0, 1), (3, 1, 2, 2)]:
+        layer = DistributedFeatureConv2d(P, 3, 4, k, stride=s, padding=p, dilation=d)
+        w = _sync(layer.weight.detach().clone() if rank == 0 else torch.empty(4, 3, k, k))
+        b = _sync(layer.bias.detach().clone() if rank == 0 else torch.empty(4))
+        x0, x = _scatter(P, xg, rank, 4)
+        y = _gather(P, layer(x), 4)
+        if rank == 0:
+            xs = xg.clone().requires_grad_()
+            ys = torch.nn.functional.conv2d(xs, w, b, stride=s, padding=p, dilation=d)
+            assert y.shape == ys.shape, (y.shape, ys.shape, k, s, p, d)
+            assert torch.allclose(y, ys, atol=1e-5), (k, s, p, d)
+            g = torch.randn_like(ys)
+            ys.backward(g)
+            y.backward(g)
+            assert torch.allclose(x0.grad, xs.grad, atol=1e-5)
+            assert torch.allclose(layer.weight.grad, torch.autograd.grad(
+                torch.nn.functional.conv2d(xg, w.requires_grad_(), b, stride=s, padding=p, dilation=d), w, g)[0],
+                atol=1e-4)
+        else:
+            y.backward(torch.zeros_like(y))
+    pool = DistributedAvgPool2d(P, 2, stride=2)
+    x0, x = _scatter(P, xg, rank, 4)
+    y = _gather(P, pool(x), 4)
+    if rank == 0:
+        assert torch.allclose(y, torch.nn.functional.avg_pool2d(xg, 2, 2), atol=1e-6)
+    P1 = _cart([0, 1, 2, 3], [1, 1, 4])
+    x1 = _sync(torch.randn(2, 3, 10))
+    mp = DistributedMaxPool1d(P1, 3, stride=2, padding=1)
+    _, x = _scatter(P1, x1, rank, 3)
+    y = _gather(P1, mp(x), 3)
+    if rank == 0:
+        assert torch.allclose(y, torch.nn.functional.max_pool1d(x1, 3, 2, 1))
+    return True
+
+
+def test_feature_conv_and_pooling_vs_serial():
+    run_ranks("test_layers_conv", "body_feature_conv_pool", 4, timeout=300)
+
+
+def body_channel_convs(rank, world):
+    from distdl_b200.nn import (DistributedChannelAllGatherConv1d, DistributedChannelConv2d, DistributedConv2d,
+                                DistributedChannelReduceScatterConv1d, DistributedGeneralConv1d)
+    import torch.distributed as dist
+    torch.manual_seed(0)
+    # --- 2-D channel conv: P_x [1,2,1,1], P_y [1,2,1,1], P_w [2,2,1,1]
+    P_x, P_y, P_w = _cart([0, 1], [1, 2, 1, 1]), _cart([0, 1], [1, 2, 1, 1]), _cart([0, 1, 2, 3], [2, 2, 1, 1])
+    layer = DistributedConv2d(P_x, P_y, P_w, in_channels=4, out_channels=6, kernel_size=3, padding=1)
+    assert isinstance(layer, DistributedChannelConv2d)
+    xg = _sync(torch.randn(2, 4, 5, 5))
+    # assemble the serial weight from the blocks
+    Wfull = torch.zeros(6, 4, 3, 3)
+    bfull = torch.zeros(6)
+    co, ci = rank // 2, rank % 2
+    Wfull[co * 3:(co + 1) * 3, ci * 2:(ci + 1) * 2] = layer.conv_layer.weight.detach()
+    if ci == 0:
+        bfull[co * 3:(co + 1) * 3] = layer.conv_layer.bias.detach()
+    dist.all_reduce(Wfull)
+    dist.all_reduce(bfull)
+    _, x = _scatter(P_x, xg, rank, 4)
+    y = _gather(P_y, layer(x), 4)
+    if rank == 0:
+        assert torch.allclose(y, torch.nn.functional.conv2d(xg, Wfull, bfull, padding=1), atol=1e-5)
+    # --- channel all-gather / reduce-scatter 1-D convs on [D=2, M=2, 1]
+    P = _cart([0, 1, 2, 3], [2, 2, 1])
+    x1 = _sync(torch.randn(4, 6, 9))
+    d, m = rank // 2, rank % 2
+    ag = DistributedChannelAllGatherConv1d(P, 6, 8, 3, padding=1)
+    W = torch.zeros(8, 6, 3)
+    b = torch.zeros(8)
+    if d == 0:
+        W[m * 4:(m + 1) * 4] = ag.weight.detach()
+        b[m * 4:(m + 1) * 4] = ag.bias.detach()
+    dist.all_reduce(W)
+    dist.all_reduce(b)
+    xl = x1[d * 2:(d + 1) * 2, m * 3:(m + 1) * 3].clone()
+    y = ag(xl)
+    want = torch.nn.functional.conv1d(x1, W, b, padding=1)[d * 2:(d + 1) * 2, m * 4:(m + 1) * 4]
+    assert torch.allclose(y, want, atol=1e-5)
+    rs = DistributedChannelReduceScatterConv1d(P, 6, 8, 3, padding=1)
+    W = torch.zeros(8, 6, 3)
+    b = torch.zeros(8)
+    if d == 0:
+        W[:, m * 3:(m + 1) * 3] = rs.weight.detach()
+    if rank == 0:
+        b = rs.bias.detach().clone()
+    dist.all_reduce(W)
+    dist.all_reduce(b)
+    y = rs(xl)
+    want = torch.nn.functional.conv1d(x1, W, b, padding=1)[d * 2:(d + 1) * 2, m * 4:(m + 1) * 4]
+    assert torch.allclose(y, want, atol=1e-5)
+    y.sum().backward()
+    # --- general conv: channels and space split
+    P_x, P_y, P_w = _cart([0, 1], [1, 1, 2]), _cart([0, 1], [1, 1, 2]), _cart([0, 1], [1, 1, 2])
+    gen = DistributedGeneralConv1d(P_x, P_y, P_w, 3, 5, 3, padding=1)
+    x2 = _sync(torch.randn(2, 3, 12))
+    if rank in (0, 1):
+        Wg = _sync_pair(gen.weight.detach().clone() if rank == 0 else torch.empty(5, 3, 3), rank)
+        bg = _sync_pair(gen.bias.detach().clone() if rank == 0 else torch.empty(5), rank)
+        xl = x2[:, :, rank * 6:(rank + 1) * 6].clone()
+        y = gen(xl)
+        want = torch.nn.functional.conv1d(x2, Wg, bg, padding=1)[:, :, rank * 6:(rank + 1) * 6]
+        assert torch.allclose(y, want, atol=1e-5)
+    return True
+
+
+def _sync_pair(t, rank):
+    """rank 0 -> rank 1 copy inside the pair {0, 1}."""
+    import torch.distributed as dist
+    if rank == 0:
+        dist.send(t, dst=1)
+    else:
+        dist.recv(t, src=0)
+    return t
+
+
+def test_channel_and_general_convs_vs_serial():
+    run_ranks("test_layers_conv", "body_channel_convs", 4, timeout=300)
+
+
+def body_batchnorm_loss(rank, world):
+    from distdl_b200.nn import DistributedBatchNorm, DistributedMSELoss
+    torch.manual_seed(0)
+    P = _cart([0, 1, 2, 3], [2, 2, 1])
+    xg = _sync(torch.randn(6, 4, 5))
+    d, m = rank // 2, rank % 2
+    xl = xg[d * 3:(d + 1) * 3, m * 2:(m + 1) * 2].clone().requires_grad_()
+    bn = DistributedBatchNorm(P, 4)
+    y = bn(xl)
+    ref = torch.nn.BatchNorm1d(4)
+    xs = xg.clone().requires_grad_()
+    ys = ref(xs)
+    assert torch.allclose(y, ys[d * 3:(d + 1) * 3, m * 2:(m + 1) * 2], atol=1e-5)
+    if d == 0:
+        assert torch.allclose(bn.running_var.reshape(-1), ref.running_var[m * 2:(m + 1) * 2], atol=1e-5)
+    tg = _sync(torch.randn(6, 4, 5))
+    crit = DistributedMSELoss(P)
+    loss = crit(y, tg[d * 3:(d + 1) * 3, m * 2:(m + 1) * 2])
+    loss.backward()
+    ls = torch.nn.functional.mse_loss(ys, tg)
+    ls.backward()
+    if rank == 0:
+        assert abs(loss.item() - ls.item()) < 1e-6
+    assert torch.allclose(xl.grad, xs.grad[d * 3:(d + 1) * 3, m * 2:(m + 1) * 2], atol=1e-6)
+    return True
+
+
+def test_batchnorm_and_loss_vs_serial():
+    run_ranks("test_layers_conv", "body_batchnorm_loss", 4, timeout=300)
