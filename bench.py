@@ -103,7 +103,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl_cublas"],
+                    help="nccl_cublas: the same model on library kernels only (cuBLAS GEMMs, library attention, "
+                         "ATen elementwise, NCCL collectives, no fusion): the restated reference op sequence")
     ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "llama_tiny", "gpt2_xl", "mixtral_8x7b"])
     ap.add_argument("--seqs-per-gpu", type=int, default=8)
     ap.add_argument("--micro-batch", type=int, default=0, help="sequences per forward/backward (0 = auto)")
@@ -111,6 +113,9 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.impl == "nccl_cublas":
+        os.environ["DISTDL_FORCE_TORCH"] = "1"
+        os.environ["DISTDL_FUSED"] = "0"
 
     import torch
     import torch.distributed as dist
@@ -133,7 +138,7 @@ def main():
     rank = dist.get_rank() if world > 1 else 0
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
-    distdl_b200.config.set_backend("native" if world > 1 else "native", "cupy")
+    distdl_b200.config.set_backend("nccl" if args.impl == "nccl_cublas" else "native", "cupy")
     from distdl_b200 import models
     from distdl_b200.parallel import SyntheticTokens, Trainer
 
@@ -188,7 +193,7 @@ def main():
     e2e = tokens_per_step * args.steps / (ms_e2e / 1e3)
     if rank == 0:
         out = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+            "metric": METRIC, "impl": args.impl, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
             "config": {"model": f"{args.model} ({cfg.num_parameters() / 1e9:.2f}B params)", "global_batch": global_batch,

@@ -1,2 +1,3 @@
 """Functional layer: zero-volume corrector and the native interpolation op."""
+from . import interpolate  # noqa: F401
 from .zero_volume_corrector import ZeroVolumeCorrectorFunction  # noqa: F401

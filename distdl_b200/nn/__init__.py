@@ -40,3 +40,27 @@ from .conv_channel_rs import (DistributedChannelReduceScatterConv1d, Distributed
                               DistributedChannelReduceScatterConv3d, DistributedChannelReduceScatterConvTranspose1d,
                               DistributedChannelReduceScatterConvTranspose2d,
                               DistributedChannelReduceScatterConvTranspose3d)
+from . import mixins  # noqa: F401,E402
+from .interpolate import Interpolate  # noqa: F401,E402
+from .upsampling import DistributedUpsample  # noqa: F401,E402
+
+__all__ = [
+    "AllGather", "AllSumReduce", "Broadcast", "DistributedBatchNorm", "DistributedConv1d", "DistributedConv2d",
+    "DistributedConv3d", "DistributedChannelConv1d", "DistributedChannelConv2d", "DistributedChannelConv3d",
+    "DistributedFeatureConv1d", "DistributedFeatureConv2d", "DistributedFeatureConv3d",
+    "DistributedFeatureConvTranspose1d", "DistributedFeatureConvTranspose2d", "DistributedFeatureConvTranspose3d",
+    "DistributedChannelReduceScatterConv1d", "DistributedChannelReduceScatterConv2d",
+    "DistributedChannelReduceScatterConv3d", "DistributedChannelReduceScatterConvTranspose1d",
+    "DistributedChannelReduceScatterConvTranspose2d", "DistributedChannelReduceScatterConvTranspose3d",
+    "DistributedChannelAllGatherConv1d", "DistributedChannelAllGatherConv2d", "DistributedChannelAllGatherConv3d",
+    "DistributedChannelAllGatherConvTranspose1d", "DistributedChannelAllGatherConvTranspose2d",
+    "DistributedChannelAllGatherConvTranspose3d", "DistributedGeneralConv1d", "DistributedGeneralConv2d",
+    "DistributedGeneralConv3d", "HaloExchange", "DistributedEmbeddingZero", "DistributedEmbedding",
+    "DistributedLayerNormZero", "DistributedLayerNorm", "DistributedRMSNormZero", "DistributedLinear",
+    "DistributedLinearAllGather", "DistributedLinearAllGatherZero", "DistributedLinearReduceScatter",
+    "DistributedLinearReduceScatterZero", "DistributedExpertAllGather", "DistributedExpertReduceScatter",
+    "DistributedL1Loss", "DistributedMSELoss", "DistributedPoissonNLLLoss", "DistributedBCELoss",
+    "DistributedBCEWithLogitsLoss", "DistributedKLDivLoss", "Module", "DistributedAvgPool1d", "DistributedAvgPool2d",
+    "DistributedAvgPool3d", "DistributedMaxPool1d", "DistributedMaxPool2d", "DistributedMaxPool3d", "Repartition",
+    "ReduceScatter", "SumReduce", "DistributedTranspose", "Interpolate", "DistributedUpsample", "loss",
+]

@@ -1,6 +1,8 @@
 """Small helpers shared by the op wrappers."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import _native
@@ -22,6 +24,8 @@ def use_native(*tensors) -> bool:
     plumbing and adjoint tests only.  On a CUDA device a missing native
     library is an error, never a silent fallback.
     """
+    if os.environ.get("DISTDL_FORCE_TORCH", "0") == "1":
+        return False            # baseline arm: library kernels (cuBLAS / cuDNN / ATen) everywhere
     for t in tensors:
         if t is not None and t.is_cuda:
             if not _native.available():

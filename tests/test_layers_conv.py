@@ -204,3 +204,33 @@ def body_batchnorm_loss(rank, world):
 
 def test_batchnorm_and_loss_vs_serial():
     run_ranks("test_layers_conv", "body_batchnorm_loss", 4, timeout=300)
+
+
+def body_upsample(rank, world):
+    from distdl_b200.nn import DistributedUpsample
+    torch.manual_seed(0)
+    P = _cart([0, 1, 2, 3], [1, 1, 2, 2])
+    xg = _sync(torch.randn(2, 2, 9, 7))
+    for kw, tkw in [(dict(scale_factor=2, mode="linear"), dict(scale_factor=2, mode="bilinear")),
+                    (dict(size=(20, 11), mode="linear", align_corners=True),
+                     dict(size=(20, 11), mode="bilinear", align_corners=True)),
+                    (dict(scale_factor=3, mode="nearest"), dict(scale_factor=3, mode="nearest"))]:
+        layer = DistributedUpsample(P, **kw)
+        x0, x = _scatter(P, xg, rank, 4)
+        y = _gather(P, layer(x), 4)
+        if rank == 0:
+            xs = xg.clone().requires_grad_()
+            ys = torch.nn.functional.interpolate(xs, **tkw)
+            assert y.shape == ys.shape, (y.shape, ys.shape)
+            assert torch.allclose(y, ys, atol=1e-5), kw
+            g = torch.randn_like(ys)
+            ys.backward(g)
+            y.backward(g)
+            assert torch.allclose(x0.grad, xs.grad, atol=1e-5), kw
+        else:
+            y.backward(torch.zeros_like(y))
+    return True
+
+
+def test_upsample_vs_serial():
+    run_ranks("test_layers_conv", "body_upsample", 4, timeout=300)
