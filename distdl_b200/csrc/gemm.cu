@@ -1,4 +1,7 @@
 // C entry point of the tcgen05 GEMM.
+#include <cstdlib>
+
+#include "gemm2_tcgen05.cuh"
 #include "gemm_tcgen05.cuh"
 #include "runtime.cuh"
 
@@ -18,6 +21,20 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int gr
     configured[dev & 63] = true;
   }
   kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  return (int)cudaGetLastError();
+}
+template <bool A_MN, bool B_MN>
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int grid, cudaStream_t stream) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  auto kern = dd::gemm2::gemm2_bf16_kernel<A_MN, B_MN>;
+  if (!configured[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dd::gemm2::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    configured[dev & 63] = true;
+  }
+  kern<<<grid, dd::gemm2::NUM_THREADS, dd::gemm2::SMEM_BYTES, stream>>>(ta, tb, p);
   return (int)cudaGetLastError();
 }
 }  // namespace
@@ -40,6 +57,35 @@ DD_API int dd_gemm_bf16(const void* A, int a_mn, long long lda, long long stride
     strideA = (a_mn ? (long long)K : (long long)M) * lda;
     strideB = (b_mn ? (long long)K : (long long)N) * ldb;
     strideD = (long long)M * ldd;
+  }
+  // CTA pairs (cta_group::2) unless disabled or the problem is a single tile row
+  static const bool pair_ok = []() { const char* e = getenv("DISTDL_GEMM_PAIR"); return !(e && e[0] == '0'); }();
+  if (pair_ok && M > BM) {
+    CUtensorMap pa, pb;
+    int rr;
+    namespace g2 = dd::gemm2;
+    if (a_mn) rr = get_tensor_map_bf16_3d(&pa, A, M, K, batch, lda * 2, strideA * 2, 64, g2::BK);
+    else      rr = get_tensor_map_bf16_3d(&pa, A, K, M, batch, lda * 2, strideA * 2, g2::BK, g2::BM);
+    if (rr) return rr;
+    if (b_mn) rr = get_tensor_map_bf16_3d(&pb, B, N, K, batch, ldb * 2, strideB * 2, 64, g2::BK);
+    else      rr = get_tensor_map_bf16_3d(&pb, B, K, N, batch, ldb * 2, strideB * 2, g2::BK, g2::BNH);
+    if (rr) return rr;
+    int err2 = 0;
+    Params q;
+    q.M = M; q.N = N; q.K = K; q.batch = batch;
+    q.D = D; q.ldd = ldd; q.strideD = strideD; q.bias = bias; q.flags = flags; q.group_m = 4;
+    q.status = device_status(&err2);
+    if (err2) return err2;
+    const int ptiles = ((M + 2 * g2::BM - 1) / (2 * g2::BM)) * ((N + g2::BN - 1) / g2::BN) * batch;
+    int ctas = current_sm_count() & ~1;
+    if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas & ~1;
+    if (ctas < 2) ctas = 2;
+    const int pgrid = 2 * ptiles < ctas ? 2 * ptiles : ctas;
+    cudaStream_t ps = reinterpret_cast<cudaStream_t>(stream);
+    if (a_mn && b_mn) return launch_pair<true, true>(pa, pb, q, pgrid, ps);
+    if (a_mn) return launch_pair<true, false>(pa, pb, q, pgrid, ps);
+    if (b_mn) return launch_pair<false, true>(pa, pb, q, pgrid, ps);
+    return launch_pair<false, false>(pa, pb, q, pgrid, ps);
   }
   CUtensorMap ta, tb;
   int r;

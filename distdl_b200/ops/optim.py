@@ -19,18 +19,24 @@ def adamw_step_(master, m, v, grad, param_bf16, *, lr, beta1, beta2, eps, weight
                      lr, beta1, beta2, eps, weight_decay, step, ptr(grad_scale_tensor), grad_scale, int(zero_grad),
                      stream_ptr())
         return
-    g = grad * grad_scale
-    if grad_scale_tensor is not None:
-        g = g * grad_scale_tensor
-    m.mul_(beta1).add_(g, alpha=1 - beta1)
-    v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
+    # library-kernel path (CPU plumbing and the baseline arm): processed in slices so
+    # that the temporaries stay small next to the optimizer state
     bc1 = 1 - beta1 ** step
     bc2 = 1 - beta2 ** step
-    master.mul_(1 - lr * weight_decay).addcdiv_(m / bc1, (v / bc2).sqrt_().add_(eps), value=-lr)
-    if zero_grad:
-        grad.zero_()
-    if param_bf16 is not None:
-        param_bf16.copy_(master)
+    chunk = 1 << 26
+    for lo in range(0, n, chunk):
+        sl = slice(lo, min(n, lo + chunk))
+        g = grad[sl] * grad_scale
+        if grad_scale_tensor is not None:
+            g = g * grad_scale_tensor
+        m[sl].mul_(beta1).add_(g, alpha=1 - beta1)
+        v[sl].mul_(beta2).addcmul_(g, g, value=1 - beta2)
+        denom = (v[sl] / bc2).sqrt_().add_(eps)
+        master[sl].mul_(1 - lr * weight_decay).addcdiv_(m[sl], denom, value=-lr / bc1)
+        if zero_grad:
+            grad[sl].zero_()
+        if param_bf16 is not None:
+            param_bf16[sl].copy_(master[sl])
 
 
 def sumsq_(x: torch.Tensor, out: torch.Tensor) -> None:
@@ -40,4 +46,6 @@ def sumsq_(x: torch.Tensor, out: torch.Tensor) -> None:
     if use_native(x):
         _native.call("dd_sumsq_f32", x.data_ptr(), x.numel(), out.data_ptr(), stream_ptr())
     else:
-        out += (x.double() ** 2).sum().float()
+        for lo in range(0, x.numel(), 1 << 26):
+            c = x[lo:lo + (1 << 26)]
+            out += (c.float() * c.float()).sum()

@@ -1,0 +1,110 @@
+"""Primitive sweep (run under torchrun, one rank per GPU):
+
+    torchrun --nnodes=1 --nproc-per-node N -m distdl_b200.utils.primitive_bench [--max-bytes B]
+
+AllSumReduce, AllGather, ReduceScatter and Repartition (an [n, n] tensor from a
+row partition to a column partition) in bf16 for message sizes 4 KB ... 1 GB in
+powers of 4, values ~ U(-1, 1), seed 1; plus HaloExchange of an fp32
+[8, 64, 512, 512] tensor with width-1 halos on a 2 x (N/2) spatial partition.
+Each op is timed on the device (CUDA events, warm-up, max over ranks) for the
+native backend (this library's kernels over peer memory) and for the NCCL
+backend (library collectives); bus bandwidth uses the usual factors
+(all-reduce 2(P-1)/P, others (P-1)/P of the full message).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+import torch
+import torch.distributed as dist
+
+
+def _time(fn, iters=5, warmup=2):
+    for _ in range(warmup):
+        fn()
+    dist.barrier()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--max-bytes", type=int, default=1 << 30)
+    ap.add_argument("--json", default=None)
+    args = ap.parse_args()
+    import distdl_b200
+    from distdl_b200.backends.common import world as dworld
+    dworld.init_process_group_from_env()
+    rank, P = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    rows = []
+    sizes = []
+    b = 4096
+    while b <= args.max_bytes:
+        sizes.append(b)
+        b *= 4
+    for backend in ("native", "nccl"):
+        distdl_b200.config.set_backend(backend, "cupy")
+        from distdl_b200.nn import AllGather, AllSumReduce, HaloExchange, ReduceScatter, Repartition
+        P_world = distdl_b200.backends.backend.Partition()
+        P_flat = P_world.create_cartesian_topology_partition([P])
+        P_rows = P_world.create_cartesian_topology_partition([P, 1])
+        P_cols = P_world.create_cartesian_topology_partition([1, P])
+        for nbytes in sizes:
+            n = nbytes // 2
+            torch.manual_seed(1)
+            x = (torch.rand(n, device=dev) * 2 - 1).to(torch.bfloat16)
+            ar, ag, rs = AllSumReduce(P_flat, axes_reduce=(0,)), AllGather(P_flat, axes_all_gather=(0,)), \
+                ReduceScatter(P_flat, axes_reduce_scatter=(0,))
+            shard = x[: max(8, n // P // 8 * 8)]
+            full = x[: shard.numel() * P]
+            for name, fn, factor, msg in (
+                    ("all_sum_reduce", lambda: ar(x), 2 * (P - 1) / P, nbytes),
+                    ("all_gather", lambda: ag(shard), (P - 1) / P, shard.numel() * 2 * P),
+                    ("reduce_scatter", lambda: rs(full), (P - 1) / P, full.numel() * 2)):
+                ms = _time(fn)
+                rows.append({"op": name, "backend": backend, "bytes": msg, "ms": ms,
+                             "busbw_GBs": msg * factor / ms / 1e6})
+            side = int(math.sqrt(n)) // (8 * P) * (8 * P)
+            if side >= 8 * P:
+                m = torch.rand(side // P, side, device=dev).to(torch.bfloat16)
+                rp = Repartition(P_rows, P_cols)
+                ms = _time(lambda: rp(m))
+                msg = side * side * 2
+                rows.append({"op": "repartition_row_to_col", "backend": backend, "bytes": msg, "ms": ms,
+                             "busbw_GBs": msg / P * (P - 1) / P / ms / 1e6})
+        if P >= 2:
+            py = 2 if P % 2 == 0 and P > 2 else 1
+            px = P // py
+            P_sp = P_world.create_cartesian_topology_partition([1, 1, py, px])
+            halo = [[0, 0], [0, 0], [int(P_sp.index[2] > 0), int(P_sp.index[2] < py - 1)],
+                    [int(P_sp.index[3] > 0), int(P_sp.index[3] < px - 1)]]
+            H, Wd = 512 // py, 512 // px
+            xt = torch.rand(8, 64, H + halo[2][0] + halo[2][1], Wd + halo[3][0] + halo[3][1], device=dev)
+            he = HaloExchange(P_sp, halo, halo, halo)
+            ms = _time(lambda: he(xt))
+            rows.append({"op": f"halo_exchange_8x64x512x512_on_{py}x{px}", "backend": backend,
+                         "bytes": xt.numel() * 4, "ms": ms, "busbw_GBs": None})
+    if rank == 0:
+        for r in rows:
+            bw = "" if r["busbw_GBs"] is None else f"{r['busbw_GBs']:.1f} GB/s"
+            print(f"{r['op']:<40} {r['backend']:<7} {r['bytes']:>12} B  {r['ms']:.4f} ms  {bw}")
+        if args.json:
+            with open(args.json, "w") as fh:
+                json.dump(rows, fh)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
