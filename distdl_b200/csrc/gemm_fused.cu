@@ -29,98 +29,16 @@
 //
 // All flags are counters that only grow; every wait is bounded (2 s) and
 // reports through the status record.
-#include "gemm_tcgen05.cuh"
+#include <cstdlib>
+
+#include "gemm_fused_common.cuh"
 #include "runtime.cuh"
 
 using namespace dd;
 using namespace dd::gemm;
+using namespace dd::fused;
 
 namespace {
-
-constexpr int kMaxPeers = 8;
-constexpr int FUSED_THREADS = NUM_THREADS + 128;   // + 4 comm warps (ag_gemm)
-constexpr int kReduceCtas = 64;
-
-// word offsets inside a signal pad (uint32 units); the first 1024 words belong
-// to the standalone collectives
-constexpr int PAD_AG = 1024;          // [writer]: ag_gemm start / end signals
-constexpr int PAD_RS_DELIVERED = 1040;  // [parity * 8 + writer]
-constexpr int PAD_RS_CONSUMED = 1072;   // [parity * 8 + writer]
-
-struct Geometry {
-  int P, me;            // team size, my index
-  int batch;            // batch entries
-  int s_local;          // rows per (batch entry, member); multiple of 128
-  __device__ __forceinline__ int blocks_per_seg() const { return s_local / BM; }
-  __device__ __forceinline__ int row_blocks() const { return batch * P * blocks_per_seg(); }
-  // order index -> row-block; `first` is the member whose blocks come first
-  __device__ __forceinline__ int block_of(int o, int first, int& owner, int& local_block) const {
-    const int q = blocks_per_seg();
-    const int per_member = batch * q;
-    const int rr = o / per_member, rem = o - rr * per_member;
-    const int bi = rem / q, j = rem - bi * q;
-    owner = (rr + first) % P;
-    local_block = bi * q + j;                    // block index inside the owner's shard
-    return bi * (P * q) + owner * q + j;         // block index in the gathered matrix
-  }
-};
-
-__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void red_release_sys(uint32_t* p) {
-  asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p) : "memory");
-}
-__device__ __forceinline__ void proxy_fence_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
-__device__ __forceinline__ uint4 ld_peer16(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
-// Bounded spin until *p (as a counter) has reached `want`.
-template <bool SYS>
-__device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t want, volatile int* abort_flag,
-                                             StatusRecord* st, int where) {
-  const uint64_t t0 = globaltimer_ns();
-  uint32_t it = 0;
-  while (true) {
-    const uint32_t seen = SYS ? ld_acquire_sys(p) : ld_acquire_gpu(p);
-    if ((int32_t)(seen - want) >= 0) return true;
-    if ((++it & 0x3f) == 0) {
-      if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kSpinLimitNs) {
-        *abort_flag = 1;
-        report_timeout(st, where, (int)want, (int)seen);
-        return false;
-      }
-    }
-  }
-}
-
-// ------------------------------- ag_gemm -----------------------------------
-struct AgParams {
-  Params g;                          // GEMM part (M = batch * P * s_local)
-  Geometry geo;
-  const void* shard[kMaxPeers];      // member i's shard [batch*s_local, K] (peer-mapped; [me] = local)
-  __nv_bfloat16* G;                  // gathered activation [M, K], local
-  uint32_t* ready;                   // [row_blocks] words, local; value == epoch when the block is in G
-  uint32_t epoch;
-  uint32_t* pad[kMaxPeers];          // signal pads (peer-mapped)
-  int writer[kMaxPeers];             // writer index of member i
-  uint32_t expect[kMaxPeers];        // value of member i's "shard is staged" signal for this call
-  uint32_t* done_counter;            // local: CTAs that finished pulling (monotone)
-  uint32_t done_target;              // value of done_counter when all CTAs of this call are through
-};
 
 template <bool B_MN>
 __global__ void __launch_bounds__(FUSED_THREADS, 1)
@@ -317,18 +235,6 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 }
 
 // ------------------------------- gemm_rs -----------------------------------
-struct RsParams {
-  Params g;                          // GEMM part; g.D unused
-  Geometry geo;
-  __nv_bfloat16* slot[kMaxPeers];    // member i's staging, slot [source = me]: [batch*s_local, N] (peer-mapped)
-  uint32_t* pad[kMaxPeers];
-  int writer[kMaxPeers];
-  int parity;
-  uint32_t consumed_expect[kMaxPeers];  // peer i must have consumed the previous use of this parity
-  uint32_t* done_counter;            // local, monotone
-  uint32_t done_target;
-};
-
 template <bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -548,6 +454,13 @@ int set_smem(K kern, int bytes) {
 
 DD_API int dd_fused_reduce_ctas() { return kReduceCtas; }
 
+static bool fused_pair_enabled() {
+  static const bool on = []() { const char* e = getenv("DISTDL_FUSED_PAIR"); return !(e && e[0] == '0'); }();
+  return on;
+}
+// Grid size of the fused GEMM kernels (the completion counters count CTAs).
+DD_API int dd_fused_gemm_ctas() { return fused_pair_enabled() ? (current_sm_count() & ~1) : current_sm_count(); }
+
 // All pointer arrays have P entries in team order.  `w` is the [N, K] weight
 // (w_mn = 0) or its [K, N] storage read as MN-major (w_mn = 1, ldw = N-stride).
 DD_API int dd_ag_gemm(int P, int me, void* const* shards, void* G, const void* w, int w_mn, long long ldw, void* D,
@@ -559,8 +472,9 @@ DD_API int dd_ag_gemm(int P, int me, void* const* shards, void* G, const void* w
   CUtensorMap ta, tb;
   int r = get_tensor_map_bf16_3d(&ta, G, K, M, 1, (uint64_t)K * 2, (uint64_t)M * K * 2, BK, BM);
   if (r) return r;
+  const bool pair = fused_pair_enabled();
   if (w_mn) r = get_tensor_map_bf16_3d(&tb, w, N, K, 1, ldw * 2, (uint64_t)K * ldw * 2, 64, BK);
-  else      r = get_tensor_map_bf16_3d(&tb, w, K, N, 1, ldw * 2, (uint64_t)N * ldw * 2, BK, BN);
+  else      r = get_tensor_map_bf16_3d(&tb, w, K, N, 1, ldw * 2, (uint64_t)N * ldw * 2, BK, pair ? 128 : BN);
   if (r) return r;
   int err = 0;
   AgParams ap;
@@ -582,8 +496,11 @@ DD_API int dd_ag_gemm(int P, int me, void* const* shards, void* G, const void* w
   ap.epoch = epoch;
   ap.done_counter = reinterpret_cast<uint32_t*>(done_counter);
   ap.done_target = done_target;
-  int ctas = current_sm_count();
-  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  int ctas = dd_fused_gemm_ctas();
+  if (pair) {
+    ap.g.group_m = 4;
+    return dd_launch_ag_pair(ta, tb, ap, w_mn, ctas, reinterpret_cast<cudaStream_t>(stream));
+  }
   static bool configured = false;
   if (!configured) {
     if ((r = set_smem(ag_gemm_kernel<false>, SMEM_BYTES))) return r;
@@ -610,8 +527,9 @@ DD_API int dd_gemm_rs(int P, int me, const void* x, long long ldx, const void* w
   CUtensorMap ta, tb;
   int r = get_tensor_map_bf16_3d(&ta, x, K, M, 1, (uint64_t)ldx * 2, (uint64_t)M * ldx * 2, BK, BM);
   if (r) return r;
+  const bool pair = fused_pair_enabled();
   if (w_mn) r = get_tensor_map_bf16_3d(&tb, w, N, K, 1, ldw * 2, (uint64_t)K * ldw * 2, 64, BK);
-  else      r = get_tensor_map_bf16_3d(&tb, w, K, N, 1, ldw * 2, (uint64_t)N * ldw * 2, BK, BN);
+  else      r = get_tensor_map_bf16_3d(&tb, w, K, N, 1, ldw * 2, (uint64_t)N * ldw * 2, BK, pair ? 128 : BN);
   if (r) return r;
   int err = 0;
   RsParams rp;
@@ -630,18 +548,22 @@ DD_API int dd_gemm_rs(int P, int me, const void* x, long long ldx, const void* w
   }
   rp.done_counter = reinterpret_cast<uint32_t*>(done_counter_gemm);
   rp.done_target = done_target_gemm;
-  int ctas = current_sm_count();
-  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
-  static bool configured = false;
-  if (!configured) {
-    if ((r = set_smem(gemm_rs_kernel<false>, SMEM_BYTES))) return r;
-    if ((r = set_smem(gemm_rs_kernel<true>, SMEM_BYTES))) return r;
-    configured = true;
-  }
+  int ctas = dd_fused_gemm_ctas();
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (w_mn) gemm_rs_kernel<true><<<ctas, NUM_THREADS, SMEM_BYTES, s>>>(ta, tb, rp);
-  else      gemm_rs_kernel<false><<<ctas, NUM_THREADS, SMEM_BYTES, s>>>(ta, tb, rp);
-  r = (int)cudaGetLastError();
+  if (pair) {
+    rp.g.group_m = 4;
+    r = dd_launch_rs_pair(ta, tb, rp, w_mn, ctas, s);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      if ((r = set_smem(gemm_rs_kernel<false>, SMEM_BYTES))) return r;
+      if ((r = set_smem(gemm_rs_kernel<true>, SMEM_BYTES))) return r;
+      configured = true;
+    }
+    if (w_mn) gemm_rs_kernel<true><<<ctas, NUM_THREADS, SMEM_BYTES, s>>>(ta, tb, rp);
+    else      gemm_rs_kernel<false><<<ctas, NUM_THREADS, SMEM_BYTES, s>>>(ta, tb, rp);
+    r = (int)cudaGetLastError();
+  }
   if (r) return r;
   ReduceParams q;
   q.P = P; q.me = me; q.parity = parity;

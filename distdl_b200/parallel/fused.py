@@ -32,6 +32,7 @@ _native.declare("dd_gemm_rs", [c_int, c_int, c_void_p, c_ll, c_void_p, c_int, c_
                                c_int, c_int, c_int, c_int, c_int, _PP, _IP, _UP, _UP, c_void_p, c_uint, c_void_p,
                                c_uint, c_int, c_void_p])
 _native.declare("dd_fused_reduce_ctas", [])
+_native.declare("dd_fused_gemm_ctas", [])
 
 ENABLED = os.environ.get("DISTDL_FUSED", "1") != "0"
 
@@ -48,7 +49,7 @@ class _State:
         self.rs_calls = 0
         self.epoch = 0
         lib = _native.lib()
-        self.sm = lib.dd_sm_count()
+        self.sm = lib.dd_fused_gemm_ctas()      # grid of the fused GEMM kernels (completion counters count CTAs)
         self.reduce_ctas = lib.dd_fused_reduce_ctas()
         # misc region: [0, 64) counters, then the row-block ready words
         self.misc = self.h.region_tensor("misc", self.h.regions["misc"][1], torch.int32)
