@@ -109,6 +109,9 @@ def main():
     ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "llama_tiny", "gpt2_xl", "mixtral_8x7b"])
     ap.add_argument("--seqs-per-gpu", type=int, default=8)
     ap.add_argument("--micro-batch", type=int, default=0, help="sequences per forward/backward (0 = auto)")
+    ap.add_argument("--profile", action="store_true",
+                    help="diagnosis only: after the timed runs, trace ONE step with torch.profiler on rank 0 and "
+                         "print the kernels by total device time (numbers under a profiler are never bench values)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (invalid as a result)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -187,6 +190,18 @@ def main():
     losses = []
     ms_e2e, _ = timed(lambda i: losses.append(trainer.step(data.next()).item()), args.steps)
     status = _native.read_status()
+    if args.profile:
+        from torch.profiler import ProfilerActivity, profile
+        barrier()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            trainer.step_device(dev_blocks[0])
+            torch.cuda.synchronize()
+        if rank == 0:
+            rows = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)[:28]
+            total = sum(e.device_time_total for e in prof.key_averages())
+            sys.stderr.write(f"[profile] total device time of one step: {total / 1e3:.1f} ms\n")
+            for e in rows:
+                sys.stderr.write(f"[profile] {e.device_time_total / 1e3:9.2f} ms  x{e.count:<6d} {e.key[:110]}\n")
 
     tokens_per_step = global_batch * seq
     value = tokens_per_step * args.steps / (ms_dev / 1e3)

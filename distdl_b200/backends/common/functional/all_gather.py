@@ -31,6 +31,9 @@ class AllGatherFunction(TransportBound, torch.autograd.Function):
             raise ValueError(f"AllGather: local extent {input.shape[axis]} along axis {axis} does not follow the "
                              f"balanced split of {n} over {P} workers")
         ctx.extents = ext
+        # a parameter with an fp32 gradient accumulator (set by the optimizer) gets its
+        # reduce-scattered gradient added there directly in backward
+        ctx.grad_acc = getattr(input, "main_grad_view", None)
         shapes = None
         if len(set(ext)) > 1:
             shapes = []
@@ -57,8 +60,14 @@ class AllGatherFunction(TransportBound, torch.autograd.Function):
         axis = int(ctx.axes[0])
         g = scaled(grad_output, ctx.scale_backward).detach()
         if axis == 0 and len(set(ctx.extents)) == 1:
+            t = cls.transport()
+            if ctx.grad_acc is not None and hasattr(t, "reduce_scatter_accumulate") and grad_output.is_cuda:
+                gs = grad_output.contiguous().reshape(P.size, -1)
+                scale = 1.0 if ctx.scale_backward is None else 1.0 / float(ctx.scale_backward)
+                if t.reduce_scatter_accumulate(gs, ctx.grad_acc, list(P.ranks), scale):
+                    return None, None, None, None, None, None
             stacked = g.contiguous().reshape((P.size, ctx.extents[0]) + tuple(g.shape[1:]))
-            out = cls.transport().reduce_scatter_stacked(stacked, list(P.ranks))
+            out = t.reduce_scatter_stacked(stacked, list(P.ranks))
         else:
             chunks = list(torch.split(g, ctx.extents, dim=axis))
             out = cls.transport().reduce_scatter(chunks, list(P.ranks))

@@ -61,3 +61,9 @@ class NativeTransport(GroupTransport):
         if self._native_ok(stacked, ranks):
             return self._collectives().reduce_scatter(stacked, ranks)
         return super().reduce_scatter_stacked(stacked, ranks)
+
+    def reduce_scatter_accumulate(self, stacked, acc, ranks, scale=1.0):
+        """acc(fp32) += scale * reduce_scatter(stacked bf16); False when not applicable."""
+        if not self._native_ok(stacked, ranks):
+            return False
+        return self._collectives().reduce_scatter_accumulate_(stacked, acc, ranks, scale)

@@ -184,6 +184,38 @@ reducescatter_kernel(const Team t, char* out, size_t bytes) {
   team_barrier(t, 1, &fail);
 }
 
+// reduce-scatter of bf16 gradients fused with scale + accumulation into an fp32
+// buffer: acc[v] += scale * sum_i buf[i][me*bytes ...]  (the ZeRO gradient path:
+// no bf16 intermediate, no separate cast / add pass).
+__global__ void __launch_bounds__(kThreads)
+reducescatter_acc_kernel(const Team t, float* acc, size_t bytes, float scale) {
+  __shared__ int fail;
+  if (threadIdx.x == 0) fail = 0;
+  const size_t nvec = bytes >> 4;
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  if (!team_barrier(t, 0, &fail)) return;
+  const size_t base = (size_t)t.me * bytes;
+  for (size_t v = tid; v < nvec; v += stride) {
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll 1
+    for (int i = 0; i < t.n; ++i) {
+      const uint4 u = ld_peer(reinterpret_cast<const char*>(t.buf[i]) + base + (v << 4));
+      float2 f;
+      f = unpack_bf16x2(u.x); a[0] += f.x; a[1] += f.y;
+      f = unpack_bf16x2(u.y); a[2] += f.x; a[3] += f.y;
+      f = unpack_bf16x2(u.z); a[4] += f.x; a[5] += f.y;
+      f = unpack_bf16x2(u.w); a[6] += f.x; a[7] += f.y;
+    }
+    float4* o = reinterpret_cast<float4*>(acc + v * 8);
+    float4 lo = o[0], hi = o[1];
+    lo.x += scale * a[0]; lo.y += scale * a[1]; lo.z += scale * a[2]; lo.w += scale * a[3];
+    hi.x += scale * a[4]; hi.y += scale * a[5]; hi.z += scale * a[6]; hi.w += scale * a[7];
+    o[0] = lo; o[1] = hi;
+  }
+  team_barrier(t, 1, &fail);
+}
+
 // all-to-all (equal blocks): out[i*bytes ...] = buf[i][me*bytes ...].
 __global__ void __launch_bounds__(kThreads)
 alltoall_kernel(const Team t, char* out, size_t bytes) {
@@ -288,6 +320,18 @@ DD_API int dd_reducescatter(int n, int me, int my_writer, void* const* bufs, voi
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == 0) reducescatter_kernel<true><<<kCollectiveCtas, kThreads, 0, s>>>(t, (char*)out, bytes);
   else reducescatter_kernel<false><<<kCollectiveCtas, kThreads, 0, s>>>(t, (char*)out, bytes);
+  return (int)cudaGetLastError();
+}
+DD_API int dd_reducescatter_acc(int n, int me, int my_writer, void* const* bufs, void* const* flags,
+                                const int* writers, const unsigned* expect, float* acc, size_t bytes, float scale,
+                                int* steps, void* stream) {
+  if (bytes % 16 || (reinterpret_cast<uintptr_t>(acc) & 15)) return DD_ERR_ALIGN;
+  Team t;
+  int r = fill_team(t, n, me, my_writer, bufs, flags, writers, expect);
+  if (r) return r;
+  *steps = 2;
+  reducescatter_acc_kernel<<<kCollectiveCtas, kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(t, acc, bytes,
+                                                                                                  scale);
   return (int)cudaGetLastError();
 }
 DD_API int dd_alltoall(int n, int me, int my_writer, void* const* bufs, void* const* flags, const int* writers,

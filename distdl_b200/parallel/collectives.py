@@ -136,6 +136,30 @@ def reduce_scatter(x: torch.Tensor, ranks) -> torch.Tensor:
     return out.view(x.shape[1:]).to(x.dtype)
 
 
+def reduce_scatter_accumulate_(x: torch.Tensor, acc: torch.Tensor, ranks, scale: float = 1.0) -> bool:
+    """``acc += scale * reduce_scatter(x)`` in one kernel: ``x`` is bf16 ``[P, n]``,
+    ``acc`` a flat fp32 buffer of ``n`` elements (16-byte aligned, ``n % 8 == 0``).
+    Returns False (doing nothing) when the operands do not qualify."""
+    h = symm.heap()
+    ranks = list(ranks)
+    P = len(ranks)
+    if (x.dtype != torch.bfloat16 or acc.dtype != torch.float32 or x.shape[0] != P or not acc.is_contiguous()
+            or acc.data_ptr() % 16):
+        return False
+    n = x[0].numel()
+    if n % 8 or acc.numel() != n or P * n * 2 > h.staging_bytes // 16 * 16:
+        return False
+    stage = h.staging_tensor(P * n * 2, torch.bfloat16)
+    stage.copy_(x.reshape(-1))
+    steps = ctypes.c_int(0)
+    targs = h.team_args(ranks)
+    _native.launch_count += 1
+    _native.check(_native.lib().dd_reducescatter_acc(*targs, acc.data_ptr(), n * 2, float(scale), ctypes.byref(steps),
+                                                     stream_ptr()), "dd_reducescatter_acc")
+    h.advance(ranks, steps.value)
+    return True
+
+
 def all_to_all(x: torch.Tensor, ranks) -> torch.Tensor:
     """``x`` is ``[P, ...]`` with equal blocks: block ``i`` goes to member ``i``;
     returns ``[P, ...]`` whose block ``i`` came from member ``i``."""

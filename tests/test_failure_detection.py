@@ -1,0 +1,88 @@
+"""Failure detection without faulting a GPU.
+
+Host side (CPU ranks): a rank that raises, and a rank that never joins a
+collective, are reported to the caller within the time limit instead of hanging
+the job.  Device side: a bounded wait that runs out (a flag that nothing ever
+sets) ends the kernel normally, records a status the host can read, and leaves
+the CUDA context usable.
+"""
+import time
+
+import pytest
+import torch
+
+from dist_harness import run_ranks
+
+
+def body_rank_raises(rank, world):
+    if rank == 1:
+        raise RuntimeError("injected failure on rank 1")
+    return True
+
+
+def test_rank_that_raises_is_reported():
+    with pytest.raises(AssertionError, match="injected failure on rank 1"):
+        run_ranks("test_failure_detection", "body_rank_raises", 2, timeout=60)
+
+
+def body_rank_never_joins(rank, world):
+    """Rank 1 skips the collective: rank 0's bounded receive must raise, not hang."""
+    import distdl_b200
+    from distdl_b200.nn import AllSumReduce
+    if rank == 1:
+        time.sleep(3)
+        return "skipped"
+    P = distdl_b200.backends.backend.Partition().create_cartesian_topology_partition([world])
+    try:
+        AllSumReduce(P, axes_reduce=(0,))(torch.ones(4))
+    except RuntimeError as e:
+        return f"detected: {type(e).__name__}"
+    return "no error"
+
+
+def test_rank_that_never_joins_times_out():
+    # the gloo process group of the harness has a 60 s limit; the pool is rebuilt afterwards
+    try:
+        out = run_ranks("test_failure_detection", "body_rank_never_joins", 2, timeout=150)
+    except AssertionError as e:
+        # the harness's own closing barrier can be what notices the broken world first
+        assert any(k in str(e) for k in ("Timed out", "timeout", "detected", "Connection closed")), str(e)[-400:]
+        return
+    assert out[0].startswith("detected"), out
+
+
+@pytest.mark.gpu
+def test_device_wait_that_runs_out_reports_status_and_context_survives():
+    import ctypes
+
+    from distdl_b200 import _native
+    lib = _native.lib()
+    vp, ci = ctypes.c_void_p, ctypes.c_int
+    lib.dd_symm_alloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(vp)]
+    lib.dd_team_barrier.argtypes = [ci, ci, ci, ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(ci),
+                                    ctypes.POINTER(ctypes.c_uint), ctypes.POINTER(ci), vp]
+    pad, buf = vp(), vp()
+    assert lib.dd_symm_alloc(64 * 1024, ctypes.byref(pad)) == 0
+    assert lib.dd_symm_alloc(4096, ctypes.byref(buf)) == 0
+    _native.read_status()                               # clear
+    # a "team" of two whose second member does not exist: its flag is never raised
+    bufs = (vp * 2)(buf.value, buf.value)
+    pads = (vp * 2)(pad.value, pad.value)
+    writers = (ci * 2)(0, 1)
+    expect = (ctypes.c_uint * 2)(1, 1)
+    steps = ci(0)
+    t0 = time.time()
+    assert lib.dd_team_barrier(2, 0, 0, bufs, pads, writers, expect, ctypes.byref(steps),
+                               torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    dt = time.time() - t0
+    code, where, expected, seen = _native.read_status()
+    assert code == 1005 and where == 100 and expected == 1 and seen == 0, (code, where, expected, seen)
+    assert 1.0 < dt < 20.0, dt
+    # the context is alive: an ordinary kernel still runs and the status is clear again
+    x = torch.ones(1024, device="cuda")
+    assert float((x * 2).sum()) == 2048.0
+    assert _native.read_status()[0] == 0
+    lib.dd_symm_free.argtypes = [vp]
+    lib.dd_symm_free(pad)
+    lib.dd_symm_free(buf)
