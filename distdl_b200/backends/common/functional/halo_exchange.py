@@ -52,7 +52,7 @@ class HaloExchangeFunction(TransportBound, torch.autograd.Function):
                 if _volume(rg):
                     recvs.append((right, _shape(rg), out.dtype))
                     targets.append(rg)
-            got = t.exchange(sends, recvs)
+            got = t.exchange(sends, recvs, list(P_x.ranks))
             for sl, g in zip(targets, got):
                 out[sl] = g.to(out.device)
         out.requires_grad_(input.requires_grad)
@@ -82,7 +82,7 @@ class HaloExchangeFunction(TransportBound, torch.autograd.Function):
                 if _volume(rb):
                     recvs.append((right, _shape(rb), g.dtype))
                     targets.append(rb)
-            got = t.exchange(sends, recvs)
+            got = t.exchange(sends, recvs, list(P_x.ranks))
             if left != PROC_NULL and _volume(lg):
                 g[lg] = 0
             if right != PROC_NULL and _volume(rg):

@@ -14,12 +14,12 @@ import torch
 from ._base import TransportBound, empty_output
 
 
-def _move(transport, src_tensor, out_shape, out_dtype, send_overlaps, recv_overlaps, device):
+def _move(transport, src_tensor, out_shape, out_dtype, send_overlaps, recv_overlaps, device, team=None):
     sends = [(partner, src_tensor[sl]) for sl, sh, partner in send_overlaps
              if sl is not None and partner != "self"]
     recvs = [(partner, sh, out_dtype) for sl, sh, partner in recv_overlaps
              if sl is not None and partner != "self"]
-    got = transport.exchange(sends, recvs)
+    got = transport.exchange(sends, recvs, team)
     out = None
     if out_shape is not None:
         out = torch.zeros(tuple(int(s) for s in out_shape), dtype=out_dtype, device=device)
@@ -50,7 +50,8 @@ class RepartitionFunction(TransportBound, torch.autograd.Function):
         sends = P_x_to_y_overlaps if P_x.active else []
         recvs = P_y_to_x_overlaps if P_y.active else []
         out_shape = y_local_structure.shape if P_y.active else None
-        out = _move(cls.transport(), input.detach(), out_shape, x_global_structure.dtype, sends, recvs, device)
+        out = _move(cls.transport(), input.detach(), out_shape, x_global_structure.dtype, sends, recvs, device,
+                    list(P_union.ranks))
         if out is None:
             b = input.shape[0] if (preserve_batch and input.dim() > 0) else None
             from ....utilities.torch import zero_volume_tensor
@@ -70,7 +71,8 @@ class RepartitionFunction(TransportBound, torch.autograd.Function):
         sends = P_y_to_x_overlaps if P_y.active else []
         recvs = P_x_to_y_overlaps if P_x.active else []
         out_shape = x_local_structure.shape if P_x.active else None
-        g = _move(cls.transport(), grad_output.detach(), out_shape, x_global_structure.dtype, sends, recvs, device)
+        g = _move(cls.transport(), grad_output.detach(), out_shape, x_global_structure.dtype, sends, recvs, device,
+                  list(P_union.ranks))
         if g is None:
             from ....utilities.torch import zero_volume_tensor
             b = grad_output.shape[0] if (preserve_batch and grad_output.dim() > 0) else None

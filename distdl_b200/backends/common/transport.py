@@ -173,8 +173,8 @@ class P2PTransport:
         """``stacked[i]`` is my contribution to member ``i`` (equal shapes)."""
         return self.reduce_scatter(list(stacked.unbind(0)), ranks)
 
-    def exchange(self, sends, recvs):
-        """Generic neighbour exchange.  ``sends`` = [(world_rank, tensor)],
+    def exchange(self, sends, recvs, team=None):
+        """Generic neighbour exchange (``team``: all workers that make this call together).  ``sends`` = [(world_rank, tensor)],
         ``recvs`` = [(world_rank, shape, dtype)] -> list of received tensors (CPU
         or the transport's native device) in the order of ``recvs``."""
         outs, reqs = [], []
@@ -347,10 +347,10 @@ class GroupTransport(P2PTransport):
         dist.reduce_scatter_tensor(out, inp, group=self.subgroup(ranks))
         return out
 
-    def exchange(self, sends, recvs):
+    def exchange(self, sends, recvs, team=None):
         cuda = any(t.is_cuda for _, t in sends) or (torch.cuda.is_available() and dist.get_backend() == "nccl")
         if not cuda:
-            return super().exchange(sends, recvs)
+            return super().exchange(sends, recvs, team)
         dev = torch.device("cuda", torch.cuda.current_device())
         outs, ops, keep = [], [], []
         for src, shape, dtype in recvs:

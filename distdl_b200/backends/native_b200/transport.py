@@ -67,3 +67,11 @@ class NativeTransport(GroupTransport):
         if not self._native_ok(stacked, ranks):
             return False
         return self._collectives().reduce_scatter_accumulate_(stacked, acc, ranks, scale)
+
+    def exchange(self, sends, recvs, team=None):
+        dev_ok = all(t.is_cuda for _, t in sends) and torch.cuda.is_available()
+        if team is not None and dev_ok and 1 < len(team) <= 8 and self._collectives().available(team):
+            got = self._collectives().exchange(team, sends, recvs)
+            if got is not None:
+                return got
+        return super().exchange(sends, recvs, team)

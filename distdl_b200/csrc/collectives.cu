@@ -235,6 +235,31 @@ alltoall_kernel(const Team t, char* out, size_t bytes) {
   team_barrier(t, 1, &fail);
 }
 
+// Point-to-point exchange inside a team (Repartition, HaloExchange): every member
+// stages the message for member j in slot j of its staging buffer; after the
+// barrier each member pulls slot [me] of every peer it expects data from.
+struct ExchangeDesc {
+  char* dst[kMaxPeers];
+  unsigned long long bytes[kMaxPeers];   // multiple of 16; 0 = nothing from that member
+  unsigned long long slot_bytes;
+};
+__global__ void __launch_bounds__(kThreads) exchange_kernel(const Team t, const ExchangeDesc d) {
+  __shared__ int fail;
+  if (threadIdx.x == 0) fail = 0;
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  if (!team_barrier(t, 0, &fail)) return;
+  for (int k = 1; k < t.n; ++k) {
+    const int i = (t.me + k) % t.n;
+    const size_t nvec = d.bytes[i] >> 4;
+    if (nvec == 0) continue;
+    const char* src = reinterpret_cast<const char*>(t.buf[i]) + (size_t)t.me * d.slot_bytes;
+    char* dst = d.dst[i];
+    for (size_t v = tid; v < nvec; v += stride) *reinterpret_cast<uint4*>(dst + (v << 4)) = ld_peer(src + (v << 4));
+  }
+  team_barrier(t, 1, &fail);
+}
+
 // Only the barrier: used to order host-driven phases and by tests of the
 // time-out path (a peer that never signals).
 __global__ void __launch_bounds__(kThreads) barrier_only_kernel(const Team t) {
@@ -342,6 +367,24 @@ DD_API int dd_alltoall(int n, int me, int my_writer, void* const* bufs, void* co
   if (r) return r;
   *steps = 2;
   alltoall_kernel<<<kCollectiveCtas, kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(t, (char*)out, bytes);
+  return (int)cudaGetLastError();
+}
+DD_API int dd_exchange(int n, int me, int my_writer, void* const* bufs, void* const* flags, const int* writers,
+                       const unsigned* expect, void* const* dst, const unsigned long long* bytes,
+                       unsigned long long slot_bytes, int* steps, void* stream) {
+  Team t;
+  int r = fill_team(t, n, me, my_writer, bufs, flags, writers, expect);
+  if (r) return r;
+  ExchangeDesc d;
+  for (int i = 0; i < kMaxPeers; ++i) { d.dst[i] = nullptr; d.bytes[i] = 0; }
+  for (int i = 0; i < n; ++i) {
+    if (bytes[i] % 16 || bytes[i] > slot_bytes) return DD_ERR_ALIGN;
+    d.dst[i] = reinterpret_cast<char*>(dst[i]);
+    d.bytes[i] = bytes[i];
+  }
+  d.slot_bytes = slot_bytes;
+  *steps = 2;
+  exchange_kernel<<<kCollectiveCtas, kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(t, d);
   return (int)cudaGetLastError();
 }
 DD_API int dd_team_barrier(int n, int me, int my_writer, void* const* bufs, void* const* flags, const int* writers,

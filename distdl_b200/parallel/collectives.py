@@ -186,6 +186,53 @@ def all_to_all(x: torch.Tensor, ranks) -> torch.Tensor:
     return out.view(x.dtype).view(x.shape)
 
 
+def exchange(team, sends, recvs):
+    """Point-to-point messages inside ``team`` in one kernel.  ``sends`` =
+    [(world_rank, tensor)], ``recvs`` = [(world_rank, shape, dtype)]; at most one
+    message per ordered pair.  Returns the received tensors in the order of
+    ``recvs``, or ``None`` when a message does not fit its staging slot (the
+    caller then uses the library path)."""
+    h = symm.heap()
+    team = list(team)
+    P = len(team)
+    slot = (h.staging_bytes // P) // 256 * 256
+    sizes = {}
+    for dst, t in sends:
+        nb = t.numel() * t.element_size()
+        if nb > slot or dst in sizes:
+            return None
+        sizes[dst] = nb
+    outs, dsts, nbytes = [], [0] * P, [0] * P
+    seen = set()
+    for src, shape, dtype in recvs:
+        n = 1
+        for s_ in shape:
+            n *= int(s_)
+        nb = n * torch.empty((), dtype=dtype).element_size()
+        if nb > slot or src in seen:
+            return None
+        seen.add(src)
+        padded = (nb + 15) // 16 * 16
+        raw = torch.empty(padded, dtype=torch.uint8, device=h.device)
+        outs.append(raw[:nb].view(dtype).view(tuple(int(s_) for s_ in shape)))
+        i = team.index(src)
+        dsts[i], nbytes[i] = raw.data_ptr(), (padded if nb else 0)
+    for dst, t in sends:
+        nb = t.numel() * t.element_size()
+        if nb == 0:
+            continue
+        j = team.index(dst)
+        stage = h.staging_tensor(slot * P, torch.uint8)[j * slot: j * slot + nb]
+        stage.view(t.dtype).view(t.shape).copy_(t)            # the "pack": strided source -> contiguous slot
+    steps = ctypes.c_int(0)
+    targs = h.team_args(team)
+    _native.launch_count += 1
+    _native.check(_native.lib().dd_exchange(*targs, (ctypes.c_void_p * P)(*dsts), (ctypes.c_ulonglong * P)(*nbytes),
+                                            slot, ctypes.byref(steps), stream_ptr()), "dd_exchange")
+    h.advance(team, steps.value)
+    return outs
+
+
 def barrier(ranks):
     h = symm.heap()
     _launch("dd_team_barrier", h, list(ranks))

@@ -73,6 +73,28 @@ def check_primitives_native():
     rows = G[rank * 8:(rank + 1) * 8].clone()
     cols = Repartition(P_rows, P)(rows)
     assert torch.equal(cols, G[:, rank * 8:(rank + 1) * 8])
+    # halo exchange along a 1-D chain of all GPUs: ghosts receive the neighbours' values
+    from distdl_b200.nn import HaloExchange
+    P_chain = P_world.create_cartesian_topology_partition([1, 1, world])
+    hl, hr = int(rank > 0), int(rank < world - 1)
+    halo = [[0, 0], [0, 0], [hl, hr]]
+    t = torch.zeros(2, 3, 5 + hl + hr, device=dev)
+    t[:, :, hl:hl + 5] = float(rank + 1)
+    t.requires_grad_()
+    out = HaloExchange(P_chain, halo, halo, halo)(t)
+    if hl:
+        assert torch.all(out[:, :, 0] == float(rank))
+    if hr:
+        assert torch.all(out[:, :, -1] == float(rank + 2))
+    out.sum().backward()
+    want = torch.ones_like(t)
+    if hl:
+        want[:, :, 0] = 0
+        want[:, :, hl] = 2
+    if hr:
+        want[:, :, -1] = 0
+        want[:, :, -1 - hr] = 2
+    assert torch.equal(t.grad, want)
 
 
 def check_zero_grad_accumulate():
