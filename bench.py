@@ -109,6 +109,7 @@ def main():
     ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "llama_tiny", "gpt2_xl", "mixtral_8x7b"])
     ap.add_argument("--seqs-per-gpu", type=int, default=8)
     ap.add_argument("--micro-batch", type=int, default=0, help="sequences per forward/backward (0 = auto)")
+    ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size (0 = the layout named by the baseline)")
     ap.add_argument("--profile", action="store_true",
                     help="diagnosis only: after the timed runs, trace ONE step with torch.profiler on rank 0 and "
                          "print the kernels by total device time (numbers under a profiler are never bench values)")
@@ -149,6 +150,10 @@ def main():
     if args.layers:
         cfg.n_layers = args.layers
     dp, tp = layout_for(args.gpus)
+    if args.tp:
+        tp, dp = args.tp, args.gpus // args.tp
+    if cfg.n_experts:
+        dp, tp = args.gpus, 1                      # expert parallel over all GPUs
     seq = cfg.max_seq
     global_batch = args.seqs_per_gpu * args.gpus
     local_batch = global_batch // dp

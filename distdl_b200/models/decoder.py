@@ -105,9 +105,9 @@ def _col(cfg, layout, fin, fout, **kw):
     return cls(layout.P_feat, fin, fout, bias=cfg.bias, dtype=cfg.dtype, P_x=layout.P_seq, **kw)
 
 
-def _row(cfg, layout, fin, fout):
+def _row(cfg, layout, fin, fout, **kw):
     cls = dnn.DistributedLinearReduceScatterZero if cfg.zero else dnn.DistributedLinearReduceScatter
-    return cls(layout.P_feat, fin, fout, bias=cfg.bias, dtype=cfg.dtype, P_y=layout.P_seq)
+    return cls(layout.P_feat, fin, fout, bias=cfg.bias, dtype=cfg.dtype, P_y=layout.P_seq, **kw)
 
 
 class Attention(torch.nn.Module):
@@ -119,7 +119,7 @@ class Attention(torch.nn.Module):
         self.hkv = int(compute_subshape(layout.tp, layout.tp_index, [cfg.n_kv_heads])[0])
         self.qkv = _col(cfg, layout, cfg.d_model, (cfg.n_heads + 2 * cfg.n_kv_heads) * hd, num_heads=cfg.n_heads,
                         num_heads_kv=cfg.n_kv_heads)
-        self.out = _row(cfg, layout, cfg.n_heads * hd, cfg.d_model)
+        self.out = _row(cfg, layout, cfg.n_heads * hd, cfg.d_model, num_heads=cfg.n_heads)
 
     def forward(self, x):
         cfg = self.cfg

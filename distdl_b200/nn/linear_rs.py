@@ -16,6 +16,15 @@ from .reduce_scatter import ReduceScatter
 from .repartition import Repartition
 
 
+def _local_in(in_features, M, index, num_heads):
+    """Input features held by tensor-parallel worker ``index``: the balanced split, or --
+    with ``num_heads`` -- a whole number of attention heads (so that it lines up with the
+    per-worker output of a head-split QKV projection when heads do not divide evenly)."""
+    if num_heads is None:
+        return int(compute_subshape(M, index, [in_features])[0])
+    return int(compute_subshape(M, index, [num_heads])[0]) * (in_features // num_heads)
+
+
 class DistributedLinearReduceScatter(Module):
     r"""``y = x W^T + b`` with ``W`` split over its *input* features.
 
@@ -30,7 +39,8 @@ class DistributedLinearReduceScatter(Module):
     """
 
     def __init__(self, P_x, in_features, out_features, bias=True, device=None, dtype=None, P_y=None,
-                 P_weight=None, P_store_bias=None, P_apply_bias=None, collect_state=False, scale_backward=None):
+                 P_weight=None, P_store_bias=None, P_apply_bias=None, collect_state=False, scale_backward=None,
+                 num_heads=None):
         super().__init__()
         self.P_x = P_x
         if not P_x.active:
@@ -68,7 +78,7 @@ class DistributedLinearReduceScatter(Module):
             self.broadcast_bias = Broadcast(P_store_bias, P_apply_bias, scale_backward=scale_backward)
         if P_weight.active:
             wshape = [1] * dim
-            wshape[-1] = int(compute_subshape(M, P_weight.index[-1], [in_features])[0])
+            wshape[-1] = _local_in(in_features, M, int(P_weight.index[-1]), num_heads)
             wshape[-2] = out_features
             self.weight = torch.nn.Parameter(torch.empty(tuple(wshape), **kw))
         else:

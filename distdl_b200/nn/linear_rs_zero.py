@@ -15,6 +15,15 @@ from .reduce_scatter import ReduceScatter
 from .repartition import Repartition
 
 
+def _local_in(in_features, M, index, num_heads):
+    """Input features held by tensor-parallel worker ``index``: the balanced split, or --
+    with ``num_heads`` -- a whole number of attention heads (so that it lines up with the
+    per-worker output of a head-split QKV projection when heads do not divide evenly)."""
+    if num_heads is None:
+        return int(compute_subshape(M, index, [in_features])[0])
+    return int(compute_subshape(M, index, [num_heads])[0]) * (in_features // num_heads)
+
+
 class DistributedLinearReduceScatterZero(Module):
     r"""``y = x W^T + b`` with ``W`` split over its input features across the
     ``M`` tensor-parallel workers and over its output features across the ``D``
@@ -30,7 +39,8 @@ class DistributedLinearReduceScatterZero(Module):
     """
 
     def __init__(self, P_x, in_features, out_features, bias=True, device=None, dtype=None, P_y=None,
-                 P_bias=None, collect_state=False, checkpoint=False, scale_backward=None, auto_clear_buffer=True):
+                 P_bias=None, collect_state=False, checkpoint=False, scale_backward=None, auto_clear_buffer=True,
+                 num_heads=None):
         super().__init__()
         self.P_x = P_x
         if not P_x.active:
@@ -58,7 +68,7 @@ class DistributedLinearReduceScatterZero(Module):
         self.reduce_scatter_weight = ReduceScatter(P_x, axes_reduce_scatter=(0,))
         wshape = [1] * dim
         wshape[0] = int(compute_subshape(D, P_x.index[0], [out_features])[0])
-        wshape[-1] = int(compute_subshape(M, P_x.index[-1], [in_features])[0])
+        wshape[-1] = _local_in(in_features, M, int(P_x.index[-1]), num_heads)
         self.in_features_local = wshape[-1]
         self.weight = torch.nn.Parameter(torch.empty(tuple(wshape), **kw))
         if bias and self.P_bias.active:
