@@ -110,6 +110,9 @@ def main():
     ap.add_argument("--seqs-per-gpu", type=int, default=8)
     ap.add_argument("--micro-batch", type=int, default=0, help="sequences per forward/backward (0 = auto)")
     ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size (0 = the layout named by the baseline)")
+    ap.add_argument("--keep-gathered", action="store_true",
+                    help="gather the ZeRO shards once per optimizer step and reduce-scatter the gradients once "
+                         "(ZeRO-1 behaviour within a step; not the named ZeRO-3 configuration)")
     ap.add_argument("--profile", action="store_true",
                     help="diagnosis only: after the timed runs, trace ONE step with torch.profiler on rank 0 and "
                          "print the kernels by total device time (numbers under a profiler are never bench values)")
@@ -149,6 +152,7 @@ def main():
     cfg = getattr(models, args.model)()
     if args.layers:
         cfg.n_layers = args.layers
+    cfg.keep_gathered = bool(args.keep_gathered)
     dp, tp = layout_for(args.gpus)
     if args.tp:
         tp, dp = args.tp, args.gpus // args.tp
@@ -157,7 +161,7 @@ def main():
     seq = cfg.max_seq
     global_batch = args.seqs_per_gpu * args.gpus
     local_batch = global_batch // dp
-    micro = args.micro_batch or {1: 1, 2: 2}.get(args.gpus, 4)
+    micro = args.micro_batch or {1: 2, 2: 2}.get(args.gpus, 4)
     torch.manual_seed(1234 + rank)
     layout = models.ParallelLayout(dp, tp)
     model = models.Decoder(cfg, layout).cuda() if False else models.Decoder(cfg, layout)
@@ -218,6 +222,7 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
             "config": {"model": f"{args.model} ({cfg.num_parameters() / 1e9:.2f}B params)", "global_batch": global_batch,
                        "seq_len": seq, "parallelism": f"tp{tp} x fsdp{dp}", "micro_batch": micro,
+                       "zero": "gathered once per step (--keep-gathered)" if args.keep_gathered else "ZeRO-3: re-gathered at every use",
                        "optimizer": "AdamW fp32 master + moments, grad clip 1.0",
                        "activation_checkpointing": "per block",
                        "l2": "per-step working set (>= 16 GB of weights) exceeds the 126 MB L2; no explicit flush"},

@@ -215,17 +215,31 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
 }
 
 // dw[c] (+)= sum_p partial[p][0][c];  db[c] (+)= sum_p partial[p][1][c]
-__global__ void norm_bwd_reduce_kernel(const float* __restrict__ partial, int nparts, int d,
-                                       float* __restrict__ dw, float* __restrict__ db, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= d) return;
+// Block = 32 columns x 16 part-lanes: the parts are split over the lanes and
+// folded through shared memory, so the serial chain per thread is nparts / 16.
+constexpr int kRedCols = 32, kRedLanes = 16;
+__global__ void __launch_bounds__(kRedCols * kRedLanes)
+norm_bwd_reduce_kernel(const float* __restrict__ partial, int nparts, int d,
+                       float* __restrict__ dw, float* __restrict__ db, int accumulate) {
+  __shared__ float s_w[kRedLanes][kRedCols + 1], s_b[kRedLanes][kRedCols + 1];
+  const int col = threadIdx.x, lane = threadIdx.y;
+  const int c = blockIdx.x * kRedCols + col;
   float sw = 0.f, sb = 0.f;
-  for (int p = 0; p < nparts; ++p) {
-    sw += partial[(size_t)p * 2 * d + c];
-    sb += partial[(size_t)p * 2 * d + d + c];
+  if (c < d) {
+    for (int p = lane; p < nparts; p += kRedLanes) {
+      sw += partial[(size_t)p * 2 * d + c];
+      sb += partial[(size_t)p * 2 * d + d + c];
+    }
   }
-  if (dw != nullptr) dw[c] = accumulate ? dw[c] + sw : sw;
-  if (db != nullptr) db[c] = accumulate ? db[c] + sb : sb;
+  s_w[lane][col] = sw;
+  s_b[lane][col] = sb;
+  __syncthreads();
+  if (lane == 0 && c < d) {
+#pragma unroll
+    for (int l = 1; l < kRedLanes; ++l) { sw += s_w[l][col]; sb += s_b[l][col]; }
+    if (dw != nullptr) dw[c] = accumulate ? dw[c] + sw : sw;
+    if (db != nullptr) db[c] = accumulate ? db[c] + sb : sb;
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -563,7 +577,7 @@ DD_API int dd_norm_bwd(int rms, const void* dy, const void* x, const void* w, co
                                                                       (const float2*)stats, CBF(dres), BF(dx),
                                                                       partial, rows, d);
   if (partial != nullptr && (dw != nullptr || db != nullptr))
-    norm_bwd_reduce_kernel<<<(d + 255) / 256, 256, 0, STREAM(stream)>>>(partial, grid, d, dw, db, accumulate);
+    norm_bwd_reduce_kernel<<<(d + kRedCols - 1) / kRedCols, dim3(kRedCols, kRedLanes), 0, STREAM(stream)>>>(partial, grid, d, dw, db, accumulate);
   return (int)cudaGetLastError();
 }
 
@@ -707,6 +721,6 @@ DD_API int dd_norm_bwd_noalloc(int rms, const void* dy, const void* x, const voi
                                                                       (const float2*)stats, nullptr, BF(dx), partial,
                                                                       rows, d);
   if (dw != nullptr || db != nullptr)
-    norm_bwd_reduce_kernel<<<(d + 255) / 256, 256, 0, STREAM(stream)>>>(partial, grid, d, dw, db, accumulate);
+    norm_bwd_reduce_kernel<<<(d + kRedCols - 1) / kRedCols, dim3(kRedCols, kRedLanes), 0, STREAM(stream)>>>(partial, grid, d, dw, db, accumulate);
   return (int)cudaGetLastError();
 }

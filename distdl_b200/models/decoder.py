@@ -51,6 +51,7 @@ class DecoderConfig:
     dtype: torch.dtype = torch.bfloat16
     checkpoint_blocks: bool = True
     zero: bool = True
+    keep_gathered: bool = False  # gather ZeRO shards once per optimizer step, reduce-scatter gradients once
     init_std: float = 0.02
 
     @property
@@ -94,19 +95,25 @@ class ParallelLayout:
 
 def _norm(cfg, P, zero):
     if cfg.norm == "rms":
-        return dnn.DistributedRMSNormZero(P, cfg.d_model, eps=cfg.eps, dtype=cfg.dtype)
+        return dnn.DistributedRMSNormZero(P, cfg.d_model, eps=cfg.eps, dtype=cfg.dtype,
+                                          auto_clear_buffer=not cfg.keep_gathered)
     if zero:
-        return dnn.DistributedLayerNormZero(P, cfg.d_model, eps=cfg.eps, dtype=cfg.dtype)
+        return dnn.DistributedLayerNormZero(P, cfg.d_model, eps=cfg.eps, dtype=cfg.dtype,
+                                            auto_clear_buffer=not cfg.keep_gathered)
     return dnn.DistributedLayerNorm(P, cfg.d_model, eps=cfg.eps, dtype=cfg.dtype)
 
 
 def _col(cfg, layout, fin, fout, **kw):
     cls = dnn.DistributedLinearAllGatherZero if cfg.zero else dnn.DistributedLinearAllGather
+    if cfg.zero:
+        kw["auto_clear_buffer"] = not cfg.keep_gathered
     return cls(layout.P_feat, fin, fout, bias=cfg.bias, dtype=cfg.dtype, P_x=layout.P_seq, **kw)
 
 
 def _row(cfg, layout, fin, fout, **kw):
     cls = dnn.DistributedLinearReduceScatterZero if cfg.zero else dnn.DistributedLinearReduceScatter
+    if cfg.zero:
+        kw["auto_clear_buffer"] = not cfg.keep_gathered
     return cls(layout.P_feat, fin, fout, bias=cfg.bias, dtype=cfg.dtype, P_y=layout.P_seq, **kw)
 
 
@@ -174,12 +181,15 @@ class Decoder(torch.nn.Module):
         self.cfg, self.layout = cfg, layout
         V = cfg.padded_vocab()
         self.padded_vocab = V
-        self.embed = dnn.DistributedEmbeddingZero(layout.P_flat2, V, cfg.d_model, dtype=cfg.dtype)
+        self.embed = dnn.DistributedEmbeddingZero(layout.P_flat2, V, cfg.d_model, dtype=cfg.dtype,
+                                                  auto_clear_buffer=not cfg.keep_gathered)
         if not cfg.rope:
-            self.pos_embed = dnn.DistributedEmbeddingZero(layout.P_flat2, cfg.max_seq, cfg.d_model, dtype=cfg.dtype)
+            self.pos_embed = dnn.DistributedEmbeddingZero(layout.P_flat2, cfg.max_seq, cfg.d_model, dtype=cfg.dtype,
+                                                          auto_clear_buffer=not cfg.keep_gathered)
         self.blocks = torch.nn.ModuleList(Block(cfg, layout) for _ in range(cfg.n_layers))
         self.final_norm = _norm(cfg, layout.P_flat, True)
-        self.head = dnn.DistributedLinearAllGatherZero(layout.P_flat, cfg.d_model, V, bias=False, dtype=cfg.dtype)
+        self.head = dnn.DistributedLinearAllGatherZero(layout.P_flat, cfg.d_model, V, bias=False, dtype=cfg.dtype,
+                                                       auto_clear_buffer=not cfg.keep_gathered)
         self.reset_parameters()
 
     def reset_parameters(self):
@@ -197,6 +207,15 @@ class Decoder(torch.nn.Module):
                 elif name.endswith("weight"):
                     s = std / math.sqrt(2 * cfg.n_layers) if (".out." in name or ".down." in name) else std
                     p.normal_(0.0, s)
+
+    def release_gathered(self):
+        """With ``keep_gathered``: reduce-scatters the gradients accumulated on the
+        gathered parameters into the shards and drops the gathered copies.  Call
+        once per optimizer step, after the last micro-batch's backward."""
+        for m in self.modules():
+            clear = getattr(m, "clear_weight_buffer", None)
+            if clear is not None:
+                clear()
 
     def _local_tokens(self, tokens):
         """This worker's sequence shard of the (tensor-parallel replicated) token ids."""

@@ -94,7 +94,8 @@ class MoEFeedForward(torch.nn.Module):
             raise ValueError("experts must divide evenly over the expert-parallel workers")
         self.e_local = E // self.ep
         self.ep_ranks = tuple(layout.P_grid.ranks)
-        self.router = dnn.DistributedLinearAllGatherZero(layout.P_flat, d, max(E, 8), bias=False, dtype=cfg.dtype)
+        self.router = dnn.DistributedLinearAllGatherZero(layout.P_flat, d, max(E, 8), bias=False, dtype=cfg.dtype,
+                                                         auto_clear_buffer=not cfg.keep_gathered)
         dev = layout.P_flat.device
         self.w_up = torch.nn.Parameter(torch.empty(self.e_local, 2 * F, d, dtype=cfg.dtype, device=dev))
         self.w_down = torch.nn.Parameter(torch.empty(self.e_local, d, F, dtype=cfg.dtype, device=dev))

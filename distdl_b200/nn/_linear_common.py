@@ -11,6 +11,8 @@ reference performs the same conversions with einops patterns
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import torch
 
@@ -71,6 +73,45 @@ def local_out_features(out_features, num_gpu, index, num_heads=None, num_heads_k
     if blocks is None:
         return int(compute_subshape(num_gpu, index, [out_features])[0])
     return int(sum(blocks[index]))
+
+
+def deliver_grad(param, g):
+    """Adds the gradient shard ``g`` to ``param``: into the optimizer's fp32
+    accumulator when the parameter has one (``main_grad_view``), else into
+    ``param.grad``.  Used where a layer produces a parameter gradient outside of
+    autograd (the deferred reduce-scatter of ZeRO-1 mode)."""
+    acc = getattr(param, "main_grad_view", None)
+    if acc is not None:
+        from ..ops.optim import accumulate_f32_
+        accumulate_f32_(acc, g)
+    else:
+        param.grad = g if param.grad is None else param.grad + g
+
+
+def direct_main_grad(param, gather, shape):
+    """fp32 gradient accumulator of ``param`` viewed with ``shape``, when the
+    all-gather ``gather`` of that parameter is the identity (one worker along the
+    gathered partition dimension) and the optimizer attached an accumulator.  The
+    weight-gradient GEMM then accumulates into it directly; otherwise None."""
+    acc = getattr(param, "main_grad_view", None)
+    if acc is None or not param.is_cuda or os.environ.get("DISTDL_DIRECT_MAIN_GRAD", "1") == "0":
+        return None
+    axis = gather.axes_all_gather[0]
+    if int(gather.P_x.shape[axis]) != 1 or gather.scale_backward is not None:
+        return None
+    return acc.view(shape)
+
+
+def reduce_scatter_grad(rs, full_grad, param, scale_backward=None):
+    """Reduce-scatters the gradient accumulated on a gathered parameter and
+    delivers the slice to ``param`` (fused into the fp32 accumulator when the
+    transport can)."""
+    acc = getattr(param, "main_grad_view", None)
+    scale = 1.0 if scale_backward is None else 1.0 / float(scale_backward)
+    if acc is not None and rs.accumulate_into(full_grad, acc, scale):
+        return
+    g = full_grad if scale_backward is None else full_grad / scale_backward
+    deliver_grad(param, rs(g))
 
 
 class PrefetchStream:

@@ -6,7 +6,7 @@ import torch
 
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
-from ._linear_common import PrefetchStream, root_partition
+from ._linear_common import PrefetchStream, deliver_grad, root_partition
 from .all_gather import AllGather
 from .module import Module
 from .reduce_scatter import ReduceScatter
@@ -108,7 +108,7 @@ class _ZeroNormBase(Module):
                 g = full.grad if self.scale_backward is None else full.grad / self.scale_backward
                 gl = self.reduce_scatter(g.reshape([self.num_features] + [1] * (self.P_x.dim - 1)))
                 p = getattr(self, n)
-                p.grad = gl if p.grad is None else p.grad + gl
+                deliver_grad(p, gl)
         self.buffers_gathered = None
 
     def _gathered(self):

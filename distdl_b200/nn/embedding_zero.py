@@ -6,7 +6,7 @@ import torch
 from .. import ops
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
-from ._linear_common import PrefetchStream
+from ._linear_common import PrefetchStream, reduce_scatter_grad
 from .all_gather import AllGather
 from .module import Module
 from .reduce_scatter import ReduceScatter
@@ -98,11 +98,7 @@ class DistributedEmbeddingZero(Module):
 
     def clear_weight_buffer(self):
         if not self.auto_clear_buffer and self.weight_buffer is not None and self.weight_buffer.grad is not None:
-            g = self.weight_buffer.grad
-            if self.scale_backward is not None:
-                g = g / self.scale_backward
-            gl = self.reduce_scatter(g)
-            self.weight.grad = gl if self.weight.grad is None else self.weight.grad + gl
+            reduce_scatter_grad(self.reduce_scatter, self.weight_buffer.grad, self.weight, self.scale_backward)
         self.weight_buffer = None
 
     def forward(self, input):

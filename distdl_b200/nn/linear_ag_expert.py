@@ -6,7 +6,7 @@ import torch
 
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
-from ._linear_common import PrefetchStream, derived_partition
+from ._linear_common import PrefetchStream, deliver_grad, derived_partition
 from .all_gather import AllGather
 from .broadcast import Broadcast
 from .module import Module
@@ -106,7 +106,7 @@ class DistributedExpertAllGather(Module):
             if self.scale_backward is not None:
                 g = g / self.scale_backward
             gl = self.reduce_scatter_weight(g)
-            self.weight.grad = gl if self.weight.grad is None else self.weight.grad + gl
+            deliver_grad(self.weight, gl)
         self.weight_buffer = None
         self.bias_buffer = None
 

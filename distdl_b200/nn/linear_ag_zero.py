@@ -9,7 +9,7 @@ from .. import ops
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
 from . import init
-from ._linear_common import PrefetchStream, local_out_features, relayout, root_partition, var_blocks
+from ._linear_common import PrefetchStream, deliver_grad, direct_main_grad, reduce_scatter_grad, local_out_features, relayout, root_partition, var_blocks
 from .all_gather import AllGather
 from .module import Module
 from .reduce_scatter import ReduceScatter
@@ -220,10 +220,8 @@ class DistributedLinearAllGatherZero(Module):
         gradients accumulated on them into ``weight.grad`` / ``bias.grad``."""
         if not self.auto_clear_buffer and self.weight_buffer is not None and self.weight_buffer.grad is not None:
             g = self.weight_buffer.grad
-            if self.scale_backward is not None:
-                g = g / self.scale_backward
-            gw = self.reduce_scatter_weight(g.reshape([self.in_features] + list(self.weight.shape[1:])))
-            self.weight.grad = gw if self.weight.grad is None else self.weight.grad + gw
+            reduce_scatter_grad(self.reduce_scatter_weight, g.reshape([self.in_features] + list(self.weight.shape[1:])),
+                                self.weight, self.scale_backward)
             if self.bias is not None and self.bias_buffer.grad is not None:
                 gb = self.bias_buffer.grad
                 if self.scale_backward is not None:
@@ -233,7 +231,7 @@ class DistributedLinearAllGatherZero(Module):
                 if not hasattr(self, "_bias_rs"):
                     object.__setattr__(self, "_bias_rs", ReduceScatter(self.P_weight, axes_reduce_scatter=(0,)))
                 gbl = self._bias_rs(gb.reshape(shape)).transpose(0, -2)
-                self.bias.grad = gbl if self.bias.grad is None else self.bias.grad + gbl
+                deliver_grad(self.bias, gbl)
         self.weight_buffer = None
         self.bias_buffer = None
 
@@ -245,13 +243,17 @@ class DistributedLinearAllGatherZero(Module):
         self.collect_weights()
         self.wait_for_streams()
         w, b = self.weight_buffer, self.bias_buffer
+        wt = w.t()
+        mg = direct_main_grad(self.weight, self.allgather_weight, w.shape)
+        if mg is not None:
+            wt.main_grad = mg.t()
         y = None
         if input.is_cuda and getattr(self._distdl_backend, "name", "") == "native_cupy":
             from ..parallel import fused
-            y = fused.maybe_ag_linear(self, input, w.t(), b)
+            y = fused.maybe_ag_linear(self, input, wt, b)
         if y is None:
             x = self.all_gather(input)
-            y = ops.linear(x, w.t(), b)
+            y = ops.linear(x, wt, b)
         if self.auto_clear_buffer:
             self.clear_weight_buffer()
         return y

@@ -8,7 +8,7 @@ import torch
 from .. import ops
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
-from ._linear_common import PrefetchStream, derived_partition, root_partition
+from ._linear_common import PrefetchStream, deliver_grad, direct_main_grad, reduce_scatter_grad, derived_partition, root_partition
 from .all_gather import AllGather
 from .module import Module
 from .reduce_scatter import ReduceScatter
@@ -170,16 +170,14 @@ class DistributedLinearReduceScatterZero(Module):
     def clear_weight_buffer(self):
         if not self.auto_clear_buffer and self.weight_buffer is not None and self.weight_buffer.grad is not None:
             g = self.weight_buffer.grad
-            if self.scale_backward is not None:
-                g = g / self.scale_backward
-            gw = self.reduce_scatter_weight(g.reshape([self.out_features] + list(self.weight.shape[1:])))
-            self.weight.grad = gw if self.weight.grad is None else self.weight.grad + gw
+            reduce_scatter_grad(self.reduce_scatter_weight, g.reshape([self.out_features] + list(self.weight.shape[1:])),
+                                self.weight, self.scale_backward)
             if self.bias_buffer is not None and self.bias_buffer.grad is not None:
                 gb = self.bias_buffer.grad
                 if self.scale_backward is not None:
                     gb = gb / self.scale_backward
                 gbl = self.reduce_scatter_bias(gb.reshape([self.out_features] + [1] * (self.P_x.dim - 1)))
-                self.bias.grad = gbl if self.bias.grad is None else self.bias.grad + gbl
+                deliver_grad(self.bias, gbl)
         self.weight_buffer = None
         self.bias_buffer = None
 
@@ -200,7 +198,12 @@ class DistributedLinearReduceScatterZero(Module):
             return _CheckpointedRSZero.apply(self, input, self.weight, bias)
         self.collect_weights()
         self.wait_for_streams()
-        y = self._apply(input, self.weight_buffer, self.bias_buffer)
+        w = self.weight_buffer
+        mg = direct_main_grad(self.weight, self.allgather_weight, w.shape)
+        if mg is not None:
+            w = w.view(w.shape)              # a fresh tensor object to carry the attribute
+            w.main_grad = mg
+        y = self._apply(input, w, self.bias_buffer)
         if self.auto_clear_buffer:
             self.clear_weight_buffer()
         return y

@@ -51,5 +51,21 @@ class ReduceScatter(Module):
         return Function.apply(input, self.P_reducescatter, self.input_tensor_structure,
                               self.output_tensor_structure, self.axes_reduce_scatter)
 
+    def accumulate_into(self, input, acc, scale=1.0):
+        """Fused form for gradients: ``acc += scale * reduce_scatter(input)`` with a
+        flat fp32 accumulator of the size of this worker's slice.  Returns False
+        (and does nothing) when the transport has no such kernel or the layout is
+        not the equal split along dimension 0 that it serves."""
+        if self.identity or not self.P_x.active or not input.is_cuda or self.axes_reduce_scatter[0] != 0:
+            return False
+        self._distdl_forward_pre_hook(self, (input,))
+        P = self.P_reducescatter
+        if P.size == 1 or input.shape[0] % P.size or acc.numel() * P.size != input.numel():
+            return False
+        t = self._distdl_backend.functional.ReduceScatterFunction.transport()
+        if not hasattr(t, "reduce_scatter_accumulate"):
+            return False
+        return bool(t.reduce_scatter_accumulate(input.contiguous().reshape(P.size, -1), acc, list(P.ranks), scale))
+
     def extra_repr(self):
         return f"P_x={self.P_x.shape.tolist()}, axes_reduce_scatter={self.axes_reduce_scatter}"

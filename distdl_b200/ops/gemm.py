@@ -78,6 +78,29 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None, *, bias: to
     return out
 
 
+def weight_grad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor):
+    """Gradient of ``y = x @ w.T`` with respect to ``w`` ([out, in]) from
+    ``dy2 [tokens, out]`` and ``x2 [tokens, in]``.
+
+    * ``w.main_grad`` (an fp32 tensor in the layout of ``w``, possibly a
+      transposed view): the GEMM epilogue accumulates into it and ``None`` is
+      returned, so no bf16 gradient is ever written.
+    * ``w`` a transposed view of a contiguous ``[in, out]`` tensor: the gradient
+      is produced in that storage order (``x^T dy``) and returned as the matching
+      view, so autograd's transpose back is free instead of a strided copy.
+    """
+    mg = getattr(w, "main_grad", None)
+    if mg is not None:
+        if mg.is_contiguous():
+            gemm(dy2.t(), x2.t(), out=mg, accumulate=True)
+        else:
+            gemm(x2.t(), dy2.t(), out=mg.t(), accumulate=True)
+        return None
+    if not w.is_contiguous() and w.t().is_contiguous():
+        return gemm(x2.t(), dy2.t()).t()
+    return gemm(dy2.t(), x2.t())
+
+
 class _LinearFn(torch.autograd.Function):
     """y = x @ w.T + b with all three GEMMs on the native kernel.
 
@@ -110,11 +133,7 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w.t()).view(ctx.xshape)
         if ctx.needs_input_grad[1]:
-            mg = getattr(ctx.wref, "main_grad", None)
-            if mg is not None:
-                gemm(dy2.t(), x2.t(), out=mg.view(w.shape), accumulate=True)
-            else:
-                dw = gemm(dy2.t(), x2.t())
+            dw = weight_grad(dy2, x2, ctx.wref)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             mg = getattr(ctx.bref, "main_grad", None)
             s = dy2.sum(0, dtype=torch.float32)

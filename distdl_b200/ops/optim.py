@@ -49,3 +49,12 @@ def sumsq_(x: torch.Tensor, out: torch.Tensor) -> None:
         for lo in range(0, x.numel(), 1 << 26):
             c = x[lo:lo + (1 << 26)]
             out += (c.float() * c.float()).sum()
+
+
+def accumulate_f32_(acc: torch.Tensor, g: torch.Tensor, scale: float = 1.0) -> None:
+    """``acc += scale * g`` with a flat fp32 accumulator and a gradient of any
+    float dtype (one fused cast-and-add kernel for contiguous bf16 on a GPU)."""
+    if use_native(g) and g.dtype == torch.bfloat16 and g.is_contiguous() and acc.is_contiguous():
+        _native.call("dd_cast_bf16_f32", g.data_ptr(), acc.data_ptr(), g.numel(), float(scale), 1, stream_ptr())
+    else:
+        acc.add_(g.reshape(-1).to(acc.dtype), alpha=scale)

@@ -69,11 +69,7 @@ class FlatAdamW:
             g = param.grad
             if g is None:
                 return
-            dst = param.main_grad_view
-            if use_native(g) and g.dtype == torch.bfloat16 and g.is_contiguous():
-                _native.call("dd_cast_bf16_f32", g.data_ptr(), dst.data_ptr(), g.numel(), 1.0, 1, stream_ptr())
-            else:
-                dst.add_(g.reshape(-1).float())
+            ops.optim.accumulate_f32_(param.main_grad_view, g)
             param.grad = None
         return hook
 

@@ -7,7 +7,7 @@ import torch
 from dist_harness import run_ranks
 
 
-def body_train(rank, world, family, dp, tp):
+def body_train(rank, world, family, dp, tp, keep_gathered=False):
     from distdl_b200 import models
     from distdl_b200.parallel import SyntheticTokens, Trainer
     torch.manual_seed(0)
@@ -17,6 +17,7 @@ def body_train(rank, world, family, dp, tp):
         cfg.n_heads = cfg.n_kv_heads = 3          # 3 heads over 2 workers: 2 + 1
     else:
         cfg.n_heads, cfg.n_kv_heads = 4, 2
+    cfg.keep_gathered = keep_gathered
     layout = models.ParallelLayout(dp, tp)
     model = models.Decoder(cfg, layout)
     trainer = Trainer(model, global_tokens_per_step=2 * dp * 32, micro_batch=1, lr=5e-3, warmup_steps=0,
@@ -36,3 +37,12 @@ def test_llama_tp2_zero2_trains():
 
 def test_gpt2_uneven_heads_tp2_trains():
     run_ranks("test_models", "body_train", 2, args=("gpt2", 1, 2), timeout=300)
+
+
+def test_keep_gathered_matches_zero3():
+    """Gathering once per step and reduce-scattering the gradients once gives the
+    same training trajectory as re-gathering at every use."""
+    a = run_ranks("test_models", "body_train", 4, args=("llama", 2, 2, False), timeout=300)[0]
+    b = run_ranks("test_models", "body_train", 4, args=("llama", 2, 2, True), timeout=300)[0]
+    for x, y in zip(a, b):
+        assert abs(x - y) < 2e-4 * max(1.0, abs(x)), (a, b)
