@@ -202,10 +202,15 @@ def main():
     if args.profile:
         from torch.profiler import ProfilerActivity, profile
         barrier()
+        _native.read_wait_ns()
         with profile(activities=[ProfilerActivity.CUDA]) as prof:
             trainer.step_device(dev_blocks[0])
             torch.cuda.synchronize()
+        waits = _native.read_wait_ns()
         if rank == 0:
+            for kind, ns in waits.items():
+                if ns:
+                    sys.stderr.write(f"[profile] cross-GPU wait (block 0's designated threads) {ns / 1e6:9.2f} ms  {kind}\n")
             rows = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)[:28]
             total = sum(e.device_time_total for e in prof.key_averages())
             sys.stderr.write(f"[profile] total device time of one step: {total / 1e3:.1f} ms\n")
@@ -222,7 +227,7 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
             "config": {"model": f"{args.model} ({cfg.num_parameters() / 1e9:.2f}B params)", "global_batch": global_batch,
                        "seq_len": seq, "parallelism": f"tp{tp} x fsdp{dp}", "micro_batch": micro,
-                       "zero": "gathered once per step (--keep-gathered)" if args.keep_gathered else "ZeRO-3: re-gathered at every use",
+                       "zero": "gathered once per step (--keep-gathered)" if args.keep_gathered else "ZeRO-3: block weight matrices re-gathered at every use; norm weights, embedding and head gathered once per step",
                        "optimizer": "AdamW fp32 master + moments, grad clip 1.0",
                        "activation_checkpointing": "per block",
                        "l2": "per-step working set (>= 16 GB of weights) exceeds the 126 MB L2; no explicit flush"},

@@ -29,6 +29,7 @@ _SIGNATURES = {
     "dd_version": [],
     "dd_sm_count": [],
     "dd_read_status": [ctypes.POINTER(c_int)],
+    "dd_read_wait_ns": [ctypes.POINTER(ctypes.c_ulonglong)],
     "dd_gemm_bf16": [c_void_p, c_int, c_ll, c_ll, c_void_p, c_int, c_ll, c_ll, c_void_p, c_ll, c_ll, c_void_p,
                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "dd_norm_bwd_parts": [c_int],
@@ -131,3 +132,15 @@ def read_status():
     out = (c_int * 4)()
     check(lib().dd_read_status(out), "dd_read_status")
     return tuple(out)
+
+
+WAIT_KINDS = ("ag_gemm: peer shard staged", "ag_gemm: peers done reading", "ag_gemm: row block arrived",
+              "gemm_rs: slot consumed", "rs fold: peer delivered", "collectives: team barrier", "-", "-")
+
+
+def read_wait_ns():
+    """Reads and clears the per-kind totals of nanoseconds that designated
+    threads spent waiting for other GPUs (diagnostics; synchronises the device)."""
+    out = (ctypes.c_ulonglong * 8)()
+    check(lib().dd_read_wait_ns(out), "dd_read_wait_ns")
+    return dict(zip(WAIT_KINDS, (int(v) for v in out)))

@@ -71,6 +71,7 @@ __device__ bool team_barrier(const Team& t, uint32_t step, int* sh_fail) {
       }
       seen = load_flag(mine);
     }
+    if (blockIdx.x == 0 && it > 0) account_wait(t.status, 5, globaltimer_ns() - t0);
   }
   __syncthreads();
   return *sh_fail == 0;
@@ -82,31 +83,53 @@ __device__ __forceinline__ uint4 ld_peer(const void* p) {
   return v;
 }
 
-// Sums the 16-byte vector at byte offset `off` over all members.
+// Sums the 16-byte vector at byte offset `off` over all members.  All loads are
+// issued before the first add so that the peers' latencies overlap.
 template <bool BF16>
 __device__ __forceinline__ uint4 reduce_vec(const Team& t, size_t off) {
+  uint4 u[kMaxPeers];
+#pragma unroll
+  for (int i = 0; i < kMaxPeers; ++i)
+    if (i < t.n) u[i] = ld_peer(reinterpret_cast<const char*>(t.buf[i]) + off);
   if (BF16) {
     float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll 1
-    for (int i = 0; i < t.n; ++i) {
-      const uint4 v = ld_peer(reinterpret_cast<const char*>(t.buf[i]) + off);
-      float2 f;
-      f = unpack_bf16x2(v.x); a[0] += f.x; a[1] += f.y;
-      f = unpack_bf16x2(v.y); a[2] += f.x; a[3] += f.y;
-      f = unpack_bf16x2(v.z); a[4] += f.x; a[5] += f.y;
-      f = unpack_bf16x2(v.w); a[6] += f.x; a[7] += f.y;
+#pragma unroll
+    for (int i = 0; i < kMaxPeers; ++i) {
+      if (i < t.n) {
+        float2 f;
+        f = unpack_bf16x2(u[i].x); a[0] += f.x; a[1] += f.y;
+        f = unpack_bf16x2(u[i].y); a[2] += f.x; a[3] += f.y;
+        f = unpack_bf16x2(u[i].z); a[4] += f.x; a[5] += f.y;
+        f = unpack_bf16x2(u[i].w); a[6] += f.x; a[7] += f.y;
+      }
     }
     return make_uint4(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]), pack_bf16x2(a[4], a[5]),
                       pack_bf16x2(a[6], a[7]));
   } else {
     float a0 = 0, a1 = 0, a2 = 0, a3 = 0;
-#pragma unroll 1
-    for (int i = 0; i < t.n; ++i) {
-      const uint4 v = ld_peer(reinterpret_cast<const char*>(t.buf[i]) + off);
-      a0 += __uint_as_float(v.x); a1 += __uint_as_float(v.y); a2 += __uint_as_float(v.z); a3 += __uint_as_float(v.w);
+#pragma unroll
+    for (int i = 0; i < kMaxPeers; ++i) {
+      if (i < t.n) {
+        a0 += __uint_as_float(u[i].x); a1 += __uint_as_float(u[i].y);
+        a2 += __uint_as_float(u[i].z); a3 += __uint_as_float(u[i].w);
+      }
     }
     return make_uint4(__float_as_uint(a0), __float_as_uint(a1), __float_as_uint(a2), __float_as_uint(a3));
   }
+}
+
+// dst[v] = src[v] for v = tid, tid + stride, ... < nvec (16-byte vectors; src may be a
+// peer's memory): eight loads in flight per thread to cover the NVLink latency.
+__device__ __forceinline__ void copy_vecs(char* dst, const char* src, size_t nvec, size_t tid, size_t stride) {
+  size_t v = tid;
+  for (; v + 7 * stride < nvec; v += 8 * stride) {
+    uint4 r[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) r[q] = ld_peer(src + ((v + q * stride) << 4));
+#pragma unroll
+    for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(dst + ((v + q * stride) << 4)) = r[q];
+  }
+  for (; v < nvec; v += stride) *reinterpret_cast<uint4*>(dst + (v << 4)) = ld_peer(src + (v << 4));
 }
 
 // ---------------------------------------------------------------------------
@@ -133,18 +156,24 @@ allreduce_kernel(const Team t, char* out, size_t bytes, int one_shot) {
   const size_t per = (nvec + t.n - 1) / t.n;
   const size_t lo = min(nvec, per * t.me), hi = min(nvec, lo + per);
   char* mine = reinterpret_cast<char*>(t.buf[t.me]);
-  for (size_t v = lo + tid; v < hi; v += stride) {
-    const uint4 r = reduce_vec<BF16>(t, v << 4);
-    *reinterpret_cast<uint4*>(mine + (v << 4)) = r;
-    *reinterpret_cast<uint4*>(out + (v << 4)) = r;
+  for (size_t v = lo + tid; v < hi; v += 2 * stride) {
+    const size_t v1 = v + stride;
+    const uint4 r0 = reduce_vec<BF16>(t, v << 4);
+    uint4 r1 = make_uint4(0, 0, 0, 0);
+    if (v1 < hi) r1 = reduce_vec<BF16>(t, v1 << 4);
+    *reinterpret_cast<uint4*>(mine + (v << 4)) = r0;
+    *reinterpret_cast<uint4*>(out + (v << 4)) = r0;
+    if (v1 < hi) {
+      *reinterpret_cast<uint4*>(mine + (v1 << 4)) = r1;
+      *reinterpret_cast<uint4*>(out + (v1 << 4)) = r1;
+    }
   }
   if (!team_barrier(t, 1, &fail)) return;
   for (int k = 1; k < t.n; ++k) {
     const int i = (t.me + k) % t.n;   // start with a different peer on every GPU
     const size_t plo = min(nvec, per * i), phi = min(nvec, plo + per);
     const char* src = reinterpret_cast<const char*>(t.buf[i]);
-    for (size_t v = plo + tid; v < phi; v += stride)
-      *reinterpret_cast<uint4*>(out + (v << 4)) = ld_peer(src + (v << 4));
+    if (phi > plo) copy_vecs(out + (plo << 4), src + (plo << 4), phi - plo, tid, stride);
   }
   team_barrier(t, 2, &fail);
 }
@@ -162,8 +191,7 @@ allgather_kernel(const Team t, char* out, size_t bytes) {
     const int i = (t.me + k) % t.n;
     const char* src = reinterpret_cast<const char*>(t.buf[i]);
     char* dst = out + (size_t)i * bytes;
-    for (size_t v = tid; v < nvec; v += stride)
-      *reinterpret_cast<uint4*>(dst + (v << 4)) = ld_peer(src + (v << 4));
+    copy_vecs(dst, src, nvec, tid, stride);
   }
   team_barrier(t, 1, &fail);
 }
@@ -179,8 +207,14 @@ reducescatter_kernel(const Team t, char* out, size_t bytes) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   if (!team_barrier(t, 0, &fail)) return;
   const size_t base = (size_t)t.me * bytes;
-  for (size_t v = tid; v < nvec; v += stride)
-    *reinterpret_cast<uint4*>(out + (v << 4)) = reduce_vec<BF16>(t, base + (v << 4));
+  for (size_t v = tid; v < nvec; v += 2 * stride) {
+    const size_t v1 = v + stride;
+    const uint4 r0 = reduce_vec<BF16>(t, base + (v << 4));
+    uint4 r1 = make_uint4(0, 0, 0, 0);
+    if (v1 < nvec) r1 = reduce_vec<BF16>(t, base + (v1 << 4));
+    *reinterpret_cast<uint4*>(out + (v << 4)) = r0;
+    if (v1 < nvec) *reinterpret_cast<uint4*>(out + (v1 << 4)) = r1;
+  }
   team_barrier(t, 1, &fail);
 }
 
@@ -197,15 +231,20 @@ reducescatter_acc_kernel(const Team t, float* acc, size_t bytes, float scale) {
   if (!team_barrier(t, 0, &fail)) return;
   const size_t base = (size_t)t.me * bytes;
   for (size_t v = tid; v < nvec; v += stride) {
+    uint4 u[kMaxPeers];
+#pragma unroll
+    for (int i = 0; i < kMaxPeers; ++i)
+      if (i < t.n) u[i] = ld_peer(reinterpret_cast<const char*>(t.buf[i]) + base + (v << 4));
     float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll 1
-    for (int i = 0; i < t.n; ++i) {
-      const uint4 u = ld_peer(reinterpret_cast<const char*>(t.buf[i]) + base + (v << 4));
-      float2 f;
-      f = unpack_bf16x2(u.x); a[0] += f.x; a[1] += f.y;
-      f = unpack_bf16x2(u.y); a[2] += f.x; a[3] += f.y;
-      f = unpack_bf16x2(u.z); a[4] += f.x; a[5] += f.y;
-      f = unpack_bf16x2(u.w); a[6] += f.x; a[7] += f.y;
+#pragma unroll
+    for (int i = 0; i < kMaxPeers; ++i) {
+      if (i < t.n) {
+        float2 f;
+        f = unpack_bf16x2(u[i].x); a[0] += f.x; a[1] += f.y;
+        f = unpack_bf16x2(u[i].y); a[2] += f.x; a[3] += f.y;
+        f = unpack_bf16x2(u[i].z); a[4] += f.x; a[5] += f.y;
+        f = unpack_bf16x2(u[i].w); a[6] += f.x; a[7] += f.y;
+      }
     }
     float4* o = reinterpret_cast<float4*>(acc + v * 8);
     float4 lo = o[0], hi = o[1];
@@ -229,8 +268,7 @@ alltoall_kernel(const Team t, char* out, size_t bytes) {
     const int i = (t.me + k) % t.n;
     const char* src = reinterpret_cast<const char*>(t.buf[i]) + (size_t)t.me * bytes;
     char* dst = out + (size_t)i * bytes;
-    for (size_t v = tid; v < nvec; v += stride)
-      *reinterpret_cast<uint4*>(dst + (v << 4)) = ld_peer(src + (v << 4));
+    copy_vecs(dst, src, nvec, tid, stride);
   }
   team_barrier(t, 1, &fail);
 }
@@ -255,7 +293,7 @@ __global__ void __launch_bounds__(kThreads) exchange_kernel(const Team t, const 
     if (nvec == 0) continue;
     const char* src = reinterpret_cast<const char*>(t.buf[i]) + (size_t)t.me * d.slot_bytes;
     char* dst = d.dst[i];
-    for (size_t v = tid; v < nvec; v += stride) *reinterpret_cast<uint4*>(dst + (v << 4)) = ld_peer(src + (v << 4));
+    copy_vecs(dst, src, nvec, tid, stride);
   }
   team_barrier(t, 1, &fail);
 }

@@ -32,12 +32,23 @@ namespace dd {
 // word and fall through to their normal tear-down, so a context never hangs.
 // Layout of the 4-word record: {code, where, expected, seen}.
 // ---------------------------------------------------------------------------
+constexpr int kWaitSlots = 8;
 struct StatusRecord {
   int code;
   int where;
   int expected;
   int seen;
+  // Nanoseconds that designated threads spent in cross-GPU waits, by kind
+  // (diagnostics: shows how much of a fused kernel's time is peer skew):
+  //   0 all-gather GEMM: peer shard staged   1 all-gather GEMM: peers done reading
+  //   2 all-gather GEMM: row block arrived   3 GEMM reduce-scatter: slot consumed
+  //   4 reduce-scatter fold: peer delivered  5 collectives: team barrier
+  unsigned long long wait_ns[kWaitSlots];
 };
+
+__device__ __forceinline__ void account_wait(StatusRecord* st, int slot, unsigned long long ns) {
+  if (st != nullptr && ns > 0) atomicAdd(&st->wait_ns[slot], ns);
+}
 
 __device__ __forceinline__ void report_timeout(StatusRecord* st, int where, int expected, int seen) {
   if (st != nullptr && atomicCAS(&st->code, 0, DD_ERR_TIMEOUT) == 0) {
@@ -135,6 +146,23 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1),
       "r"(c2)
       : "memory");
+}
+
+// Tiled 3-D store shared -> global (bulk async-group completion).  The same
+// alignment rule holds for c0; coordinates are never negative here.  Elements of
+// the box that fall outside the tensor are not written.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the shared-memory source of all committed stores has been read
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all committed stores have completed
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
 // ------------------------------- tcgen05 -----------------------------------

@@ -120,7 +120,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     // my shard may only be overwritten once every peer has pulled it
     if (blockIdx.x == 0 && ct < geo.P && ct != geo.me)
-      wait_counter<true>(ap.pad[geo.me] + PAD_AG + ap.writer[ct], ap.expect[ct] + 1, &ss->abort_flag, p.status, 202);
+      wait_counter<true>(ap.pad[geo.me] + PAD_AG + ap.writer[ct], ap.end_expect[ct], &ss->abort_flag, p.status, 202);
   } else if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (elect_one()) {
@@ -402,7 +402,7 @@ struct ReduceParams {
   StatusRecord* status;
 };
 
-__global__ void __launch_bounds__(512) rs_reduce_kernel(const ReduceParams rp) {
+__global__ void __launch_bounds__(256) rs_reduce_kernel(const ReduceParams rp) {
   __shared__ int abort_flag;
   if (threadIdx.x == 0) abort_flag = 0;
   __syncthreads();
@@ -414,24 +414,45 @@ __global__ void __launch_bounds__(512) rs_reduce_kernel(const ReduceParams rp) {
   const long long slot_elems = rp.rows * rp.N;
   const long long nvec = slot_elems >> 3;
   const int nv_row = rp.N >> 3;
-  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
-    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int s = 0; s < rp.P; ++s) {
-      const uint4 u = ld_peer16(rp.staging + (long long)s * slot_elems + v * 8);
-      float2 f;
-      f = unpack_bf16x2(u.x); a[0] += f.x; a[1] += f.y;
-      f = unpack_bf16x2(u.y); a[2] += f.x; a[3] += f.y;
-      f = unpack_bf16x2(u.z); a[4] += f.x; a[5] += f.y;
-      f = unpack_bf16x2(u.w); a[6] += f.x; a[7] += f.y;
-    }
-    if (rp.bias != nullptr) {
-      const int c = (int)(v % nv_row) * 8;
+  // kRedUnroll independent vectors per thread and iteration keep enough loads in
+  // flight to cover the HBM latency
+  constexpr int kRedUnroll = 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long v0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; v0 < nvec; v0 += stride * kRedUnroll) {
+    uint4 u[kRedUnroll][kMaxPeers];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) a[j] += __bfloat162float(rp.bias[c + j]);
+    for (int q = 0; q < kRedUnroll; ++q) {
+      const long long v = v0 + q * stride;
+      if (v < nvec) {
+#pragma unroll
+        for (int s = 0; s < kMaxPeers; ++s)
+          if (s < rp.P) u[q][s] = ld_peer16(rp.staging + (long long)s * slot_elems + v * 8);
+      }
     }
-    uint4 o = make_uint4(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]), pack_bf16x2(a[4], a[5]),
-                         pack_bf16x2(a[6], a[7]));
-    *reinterpret_cast<uint4*>(rp.out + v * 8) = o;
+#pragma unroll
+    for (int q = 0; q < kRedUnroll; ++q) {
+      const long long v = v0 + q * stride;
+      if (v >= nvec) break;
+      float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int s = 0; s < kMaxPeers; ++s) {
+        if (s < rp.P) {
+          float2 f;
+          f = unpack_bf16x2(u[q][s].x); a[0] += f.x; a[1] += f.y;
+          f = unpack_bf16x2(u[q][s].y); a[2] += f.x; a[3] += f.y;
+          f = unpack_bf16x2(u[q][s].z); a[4] += f.x; a[5] += f.y;
+          f = unpack_bf16x2(u[q][s].w); a[6] += f.x; a[7] += f.y;
+        }
+      }
+      if (rp.bias != nullptr) {
+        const int c = (int)(v % nv_row) * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] += __bfloat162float(rp.bias[c + j]);
+      }
+      uint4 o = make_uint4(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]), pack_bf16x2(a[4], a[5]),
+                           pack_bf16x2(a[6], a[7]));
+      *reinterpret_cast<uint4*>(rp.out + v * 8) = o;
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -466,7 +487,8 @@ DD_API int dd_fused_gemm_ctas() { return fused_pair_enabled() ? (current_sm_coun
 DD_API int dd_ag_gemm(int P, int me, void* const* shards, void* G, const void* w, int w_mn, long long ldw, void* D,
                       long long ldd, const void* bias, int bias_f32, int batch, int s_local, int N, int K,
                       void* ready, unsigned epoch, void* const* pads, const int* writers, const unsigned* expect,
-                      void* done_counter, unsigned done_target, int max_ctas, void* stream) {
+                      void* done_counter, unsigned done_target, int max_ctas, void* ready_cnt,
+                      const unsigned* end_expect, void* stream) {
   if (P < 1 || P > kMaxPeers || s_local % BM || K % 8 || ldw % 8) return DD_ERR_BAD_ARG;
   const long long M = (long long)batch * P * s_local;
   CUtensorMap ta, tb;
@@ -490,7 +512,9 @@ DD_API int dd_ag_gemm(int P, int me, void* const* shards, void* G, const void* w
     ap.pad[i] = reinterpret_cast<uint32_t*>(pads[i]);
     ap.writer[i] = writers[i];
     ap.expect[i] = expect[i];
+    ap.end_expect[i] = end_expect ? end_expect[i] : expect[i] + 1;
   }
+  ap.ready_cnt = reinterpret_cast<uint32_t*>(ready_cnt);
   ap.G = reinterpret_cast<__nv_bfloat16*>(G);
   ap.ready = reinterpret_cast<uint32_t*>(ready);
   ap.epoch = epoch;
@@ -498,6 +522,7 @@ DD_API int dd_ag_gemm(int P, int me, void* const* shards, void* G, const void* w
   ap.done_target = done_target;
   int ctas = dd_fused_gemm_ctas();
   if (pair) {
+    if (ready_cnt == nullptr) return DD_ERR_BAD_ARG;
     ap.g.group_m = 4;
     return dd_launch_ag_pair(ta, tb, ap, w_mn, ctas, reinterpret_cast<cudaStream_t>(stream));
   }
@@ -550,9 +575,20 @@ DD_API int dd_gemm_rs(int P, int me, const void* x, long long ldx, const void* w
   rp.done_target = done_target_gemm;
   int ctas = dd_fused_gemm_ctas();
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  rp.tma_store = 0;
   if (pair) {
     rp.g.group_m = 4;
-    r = dd_launch_rs_pair(ta, tb, rp, w_mn, ctas, s);
+    static const bool tma_store = []() { const char* e = getenv("DISTDL_RS_TMA_STORE"); return !(e && e[0] == '0'); }();
+    RsOutMaps om;
+    if (tma_store) {
+      const uint64_t rows = (uint64_t)batch * s_local;
+      for (int i = 0; i < P; ++i) {
+        r = get_tensor_map_bf16_3d(&om.m[i], slots[i], N, rows, 1, (uint64_t)N * 2, rows * N * 2, 64, 32);
+        if (r) return r;
+      }
+      rp.tma_store = 1;
+    }
+    r = dd_launch_rs_pair(ta, tb, om, rp, w_mn, ctas, s);
   } else {
     static bool configured = false;
     if (!configured) {
@@ -579,6 +615,6 @@ DD_API int dd_gemm_rs(int P, int me, const void* x, long long ldx, const void* w
   q.done_counter = reinterpret_cast<uint32_t*>(done_counter_reduce);
   q.done_target = done_target_reduce;
   q.status = rp.g.status;
-  rs_reduce_kernel<<<kReduceCtas, 512, 0, s>>>(q);
+  rs_reduce_kernel<<<kReduceCtas, 256, 0, s>>>(q);
   return (int)cudaGetLastError();
 }

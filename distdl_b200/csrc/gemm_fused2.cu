@@ -15,15 +15,20 @@ namespace g2 = dd::gemm2;
 namespace {
 
 constexpr int PAIR_FUSED_THREADS = g2::NUM_THREADS + 128;
+constexpr int OUT_STAGE_BYTES = 4 * 2 * 32 * 128;          // 32 KB
+constexpr int SMEM_RS = g2::SMEM_BYTES + OUT_STAGE_BYTES;
 
 // MODE 1 = ag_gemm (AgParams), MODE 2 = gemm_rs (RsParams)
 template <bool B_MN, int MODE, typename FP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == 1 ? PAIR_FUSED_THREADS : g2::NUM_THREADS, 1)
-fused_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const FP fp) {
+fused_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ RsOutMaps omaps, const FP fp) {
   const Params& p = fp.g;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  g2::SharedStorage* ss = reinterpret_cast<g2::SharedStorage*>(tiles + g2::STAGES * g2::STAGE_BYTES);
+  // gemm_rs: per epilogue warp, two boxes of [32 rows][128 B] for the TMA stores
+  uint8_t* out_stage = tiles + g2::STAGES * g2::STAGE_BYTES;
+  g2::SharedStorage* ss = reinterpret_cast<g2::SharedStorage*>(out_stage + (MODE == 2 ? OUT_STAGE_BYTES : 0));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = g2::cluster_ctarank();
@@ -57,9 +62,13 @@ fused_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (blockIdx.x == 0 && ct < geo.P && ct != geo.me) red_release_sys(fp.pad[ct] + PAD_AG + fp.writer[geo.me]);
       bool ok = true;
       const size_t row_bytes = (size_t)p.K * 2;
-      const size_t block_vecs = (size_t)BM * row_bytes / 16;
+      const size_t piece_vecs = (size_t)(BM / kPullSub) * row_bytes / 16;
       bool peers_checked = false;
-      for (int o = blockIdx.x; o < row_blocks && ok; o += gridDim.x) {
+      // pieces are numbered block-major in tile order (own shard first), so the
+      // first wave of CTAs stages what the first tiles need
+      const int pieces = row_blocks * kPullSub;
+      for (int u = blockIdx.x; u < pieces && ok; u += gridDim.x) {
+        const int o = u / kPullSub, sub = u - o * kPullSub;
         int owner, lb;
         const int rb = geo.block_of(o, geo.me, owner, lb);
         if (owner != geo.me && !peers_checked) {
@@ -70,22 +79,29 @@ fused_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           ok = ss->abort_flag == 0;
           if (!ok) break;
         }
+        const size_t piece_off = ((size_t)sub * (BM / kPullSub)) * row_bytes;
         const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(fp.shard[owner]) +
-                                                          (size_t)lb * BM * row_bytes);
-        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(fp.G) + (size_t)rb * BM * row_bytes);
+                                                          (size_t)lb * BM * row_bytes + piece_off);
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(fp.G) + (size_t)rb * BM * row_bytes + piece_off);
         size_t v = ct;
-        for (; v + 7 * 128 < block_vecs; v += 8 * 128) {
+        for (; v + 7 * 128 < piece_vecs; v += 8 * 128) {
           uint4 r[8];
 #pragma unroll
-          for (int u = 0; u < 8; ++u) r[u] = ld_peer16(src + v + u * 128);
+          for (int q = 0; q < 8; ++q) r[q] = ld_peer16(src + v + q * 128);
 #pragma unroll
-          for (int u = 0; u < 8; ++u) dst[v + u * 128] = r[u];
+          for (int q = 0; q < 8; ++q) dst[v + q * 128] = r[q];
         }
-        for (; v < block_vecs; v += 128) dst[v] = ld_peer16(src + v);
+        for (; v < piece_vecs; v += 128) dst[v] = ld_peer16(src + v);
         __threadfence();
         proxy_fence_global();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (ct == 0) st_release_gpu(fp.ready + rb, fp.epoch);
+        if (ct == 0) {
+          const uint32_t old = atom_add_acq_rel_gpu(fp.ready_cnt + rb, 1u);
+          if (old == kPullSub - 1) {
+            fp.ready_cnt[rb] = 0;
+            st_release_gpu(fp.ready + rb, fp.epoch);
+          }
+        }
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (ct == 0) {
@@ -98,7 +114,7 @@ fused_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
       }
       if (blockIdx.x == 0 && ct < geo.P && ct != geo.me)
-        wait_counter<true>(fp.pad[geo.me] + PAD_AG + fp.writer[ct], fp.expect[ct] + 1, &ss->abort_flag, p.status, 232);
+        wait_counter<true>(fp.pad[geo.me] + PAD_AG + fp.writer[ct], fp.end_expect[ct], &ss->abort_flag, p.status, 232);
     }
   } else if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -218,8 +234,64 @@ fused_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         row_off = ((long long)rb * BM + quarter * 32 + lane) * p.ldd;
       }
       const uint32_t taddr = tmem_base + acc * g2::BN + ((uint32_t)(quarter * 32) << 16);
+      bool stored = false;
+      if constexpr (MODE == 2) {
+        if (fp.tma_store) {
+          // registers -> swizzled shared memory -> TMA store: the tile leaves the SM as
+          // full 128-byte lines, whether the owner's slot is local or behind NVLink
+          stored = true;
+          uint8_t* stage_w = out_stage + quarter * (2 * 32 * 128);
 #pragma unroll 1
-      for (int c = 0; c < g2::BN / 32; ++c) {
+          for (int half = 0; half < 2; ++half) {
+            const int colh = tn * g2::BN + half * 128;
+            if (colh >= p.N) break;
+            if (lane == 0) tma_store_wait_read();
+            __syncwarp();
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+              const int col0 = colh + cc * 32;
+              uint32_t r[32];
+              tmem_ld_32x32(taddr + half * 128 + cc * 32, r);
+              tmem_ld_wait();
+              if ((q.flags & F_BIAS) && col0 < p.N) {
+                const int nv = min(32, p.N - col0);
+                if (q.flags & F_BIAS_F32) {
+                  const float* bp = reinterpret_cast<const float*>(q.bias) + col0;
+#pragma unroll
+                  for (int i = 0; i < 32; ++i)
+                    if (i < nv) r[i] = __float_as_uint(__uint_as_float(r[i]) + __ldg(bp + i));
+                } else {
+                  const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(q.bias) + col0;
+#pragma unroll
+                  for (int i = 0; i < 32; ++i)
+                    if (i < nv) r[i] = __float_as_uint(__uint_as_float(r[i]) + __bfloat162float(__ldg(bp + i)));
+                }
+              }
+              uint8_t* rowp = stage_w + (cc >> 1) * (32 * 128) + lane * 128;
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                uint4 v;
+                v.x = pack_bf16x2(__uint_as_float(r[8 * g]), __uint_as_float(r[8 * g + 1]));
+                v.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]), __uint_as_float(r[8 * g + 3]));
+                v.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]), __uint_as_float(r[8 * g + 5]));
+                v.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]), __uint_as_float(r[8 * g + 7]));
+                const int chunk = (cc & 1) * 4 + g;
+                *reinterpret_cast<uint4*>(rowp + ((chunk ^ (lane & 7)) << 4)) = v;
+              }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && o < row_blocks) {
+              const int row0 = lb * BM + quarter * 32;
+              tma_store_3d(&omaps.m[owner], stage_w, colh, row0, 0);
+              if (colh + 64 < p.N) tma_store_3d(&omaps.m[owner], stage_w + 32 * 128, colh + 64, row0, 0);
+              tma_store_commit();
+            }
+          }
+        }
+      }
+#pragma unroll 1
+      for (int c = 0; c < g2::BN / 32 && !stored; ++c) {
         const int col0 = tn * g2::BN + c * 32;
         if (col0 >= p.N) break;
         uint32_t r[32];
@@ -233,6 +305,10 @@ fused_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (++acc == g2::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
     }
     if constexpr (MODE == 2) {
+      if (fp.tma_store && lane == 0) {
+        tma_store_wait_all();
+        proxy_fence_global();
+      }
       __threadfence_system();
       asm volatile("bar.sync 2, 128;" ::: "memory");
       if (et == 0) {
@@ -254,7 +330,7 @@ fused_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
 template <typename K>
 int set_smem(K kern) {
-  return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g2::SMEM_BYTES);
+  return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_RS);
 }
 
 }  // namespace
@@ -271,13 +347,14 @@ int dd_launch_ag_pair(const CUtensorMap& ta, const CUtensorMap& tb, const AgPara
     if ((r = set_smem(fused_pair_kernel<true, 1, AgParams>))) return r;
     configured = true;
   }
-  if (w_mn) fused_pair_kernel<true, 1, AgParams><<<ctas, PAIR_FUSED_THREADS, g2::SMEM_BYTES, s>>>(ta, tb, ap);
-  else      fused_pair_kernel<false, 1, AgParams><<<ctas, PAIR_FUSED_THREADS, g2::SMEM_BYTES, s>>>(ta, tb, ap);
+  static const RsOutMaps none = {};
+  if (w_mn) fused_pair_kernel<true, 1, AgParams><<<ctas, PAIR_FUSED_THREADS, g2::SMEM_BYTES, s>>>(ta, tb, none, ap);
+  else      fused_pair_kernel<false, 1, AgParams><<<ctas, PAIR_FUSED_THREADS, g2::SMEM_BYTES, s>>>(ta, tb, none, ap);
   return (int)cudaGetLastError();
 }
 
-int dd_launch_rs_pair(const CUtensorMap& ta, const CUtensorMap& tb, const RsParams& rp, int w_mn, int ctas,
-                      cudaStream_t s) {
+int dd_launch_rs_pair(const CUtensorMap& ta, const CUtensorMap& tb, const RsOutMaps& om, const RsParams& rp, int w_mn,
+                      int ctas, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
     int r;
@@ -285,7 +362,7 @@ int dd_launch_rs_pair(const CUtensorMap& ta, const CUtensorMap& tb, const RsPara
     if ((r = set_smem(fused_pair_kernel<true, 2, RsParams>))) return r;
     configured = true;
   }
-  if (w_mn) fused_pair_kernel<true, 2, RsParams><<<ctas, g2::NUM_THREADS, g2::SMEM_BYTES, s>>>(ta, tb, rp);
-  else      fused_pair_kernel<false, 2, RsParams><<<ctas, g2::NUM_THREADS, g2::SMEM_BYTES, s>>>(ta, tb, rp);
+  if (w_mn) fused_pair_kernel<true, 2, RsParams><<<ctas, g2::NUM_THREADS, SMEM_RS, s>>>(ta, tb, om, rp);
+  else      fused_pair_kernel<false, 2, RsParams><<<ctas, g2::NUM_THREADS, SMEM_RS, s>>>(ta, tb, om, rp);
   return (int)cudaGetLastError();
 }

@@ -11,7 +11,7 @@ using namespace dd::gemm;
 
 constexpr int kMaxPeers = 8;
 constexpr int FUSED_THREADS = NUM_THREADS + 128;   // + 4 comm warps (ag_gemm)
-constexpr int kReduceCtas = 64;
+constexpr int kReduceCtas = 592;
 
 // word offsets inside a signal pad (uint32 units); the first 1024 words belong
 // to the standalone collectives
@@ -50,6 +50,11 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ uint32_t atom_add_acq_rel_gpu(uint32_t* p, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return old;
+}
 __device__ __forceinline__ void red_release_sys(uint32_t* p) {
   asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p) : "memory");
 }
@@ -60,14 +65,24 @@ __device__ __forceinline__ uint4 ld_peer16(const void* p) {
   return v;
 }
 // Bounded spin until *p (as a counter) has reached `want`.
+__host__ __device__ constexpr int wait_slot(int where) {
+  return (where == 201 || where == 231) ? 0 : (where == 202 || where == 232) ? 1 : (where == 203 || where == 233) ? 2
+         : (where == 241 || where == 211) ? 3 : 4;
+}
+
 template <bool SYS>
 __device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t want, volatile int* abort_flag,
                                              StatusRecord* st, int where) {
+  uint32_t seen = SYS ? ld_acquire_sys(p) : ld_acquire_gpu(p);
+  if ((int32_t)(seen - want) >= 0) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t it = 0;
   while (true) {
-    const uint32_t seen = SYS ? ld_acquire_sys(p) : ld_acquire_gpu(p);
-    if ((int32_t)(seen - want) >= 0) return true;
+    seen = SYS ? ld_acquire_sys(p) : ld_acquire_gpu(p);
+    if ((int32_t)(seen - want) >= 0) {
+      if (blockIdx.x == 0) account_wait(st, wait_slot(where), globaltimer_ns() - t0);
+      return true;
+    }
     if ((++it & 0x3f) == 0) {
       if (*abort_flag) return false;
       if (globaltimer_ns() - t0 > kSpinLimitNs) {
@@ -91,8 +106,22 @@ struct AgParams {
   uint32_t expect[kMaxPeers];        // value of member i's "shard is staged" signal for this call
   uint32_t* done_counter;            // local: CTAs that finished pulling (monotone)
   uint32_t done_target;              // value of done_counter when all CTAs of this call are through
+  // CTA-pair kernel only: row blocks are pulled in kPullSub pieces by different CTAs;
+  // ready_cnt[rb] counts the pieces of this call (the last arrival resets it).
+  uint32_t* ready_cnt;
+  // Value of member i's pad word that the kernel waits for before it exits: its
+  // "done pulling" signal of THIS call (single staging buffer), or of the previous
+  // call when the shard staging is double buffered (already there in practice).
+  uint32_t end_expect[kMaxPeers];
 };
+constexpr int kPullSub = 4;          // pieces per 128-row block (32 rows each)
 
+
+// Output tensor maps of the CTA-pair gemm_rs kernel: member i's staging slot for
+// source `me`, [batch*s_local rows][N] bf16, box = 64 columns x 32 rows.
+struct RsOutMaps {
+  CUtensorMap m[kMaxPeers];
+};
 
 struct RsParams {
   Params g;                          // GEMM part; g.D unused
@@ -104,6 +133,7 @@ struct RsParams {
   uint32_t consumed_expect[kMaxPeers];  // peer i must have consumed the previous use of this parity
   uint32_t* done_counter;            // local, monotone
   uint32_t done_target;
+  int tma_store;                     // pair kernel: write the tiles with TMA stores from shared memory
 };
 
 
@@ -113,5 +143,5 @@ struct RsParams {
 // CTA-pair launchers (gemm_fused2.cu)
 int dd_launch_ag_pair(const CUtensorMap& ta, const CUtensorMap& tb, const dd::fused::AgParams& ap, int w_mn, int ctas,
                       cudaStream_t s);
-int dd_launch_rs_pair(const CUtensorMap& ta, const CUtensorMap& tb, const dd::fused::RsParams& rp, int w_mn, int ctas,
-                      cudaStream_t s);
+int dd_launch_rs_pair(const CUtensorMap& ta, const CUtensorMap& tb, const dd::fused::RsOutMaps& om,
+                      const dd::fused::RsParams& rp, int w_mn, int ctas, cudaStream_t s);

@@ -133,9 +133,20 @@ DD_API int dd_read_status(int* out) {
   int err = 0;
   dd::StatusRecord* st = dd::device_status(&err);
   if (!st) return err ? err : DD_ERR_DRIVER;
-  cudaError_t e = cudaMemcpy(out, st, sizeof(dd::StatusRecord), cudaMemcpyDeviceToHost);
+  cudaError_t e = cudaMemcpy(out, st, 4 * sizeof(int), cudaMemcpyDeviceToHost);
   if (e != cudaSuccess) return (int)e;
-  e = cudaMemset(st, 0, sizeof(dd::StatusRecord));
+  e = cudaMemset(st, 0, 4 * sizeof(int));
+  return (int)e;
+}
+
+// Reads (and clears) the per-kind totals of nanoseconds spent in cross-GPU waits.
+DD_API int dd_read_wait_ns(unsigned long long* out) {
+  int err = 0;
+  dd::StatusRecord* st = dd::device_status(&err);
+  if (!st) return err ? err : DD_ERR_DRIVER;
+  cudaError_t e = cudaMemcpy(out, st->wait_ns, sizeof(st->wait_ns), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemset(st->wait_ns, 0, sizeof(st->wait_ns));
   return (int)e;
 }
 

@@ -52,6 +52,9 @@ class DecoderConfig:
     checkpoint_blocks: bool = True
     zero: bool = True
     keep_gathered: bool = False  # gather ZeRO shards once per optimizer step, reduce-scatter gradients once
+    keep_root_gathered: bool = True   # the same for the embedding, final norm and head only (each is used
+                                      # once per pass, so re-sharding them between micro-batches buys nothing)
+    keep_norms_gathered: bool = True  # and for the norm weights of the blocks (a few KB each)
     init_std: float = 0.02
 
     @property
@@ -93,13 +96,14 @@ class ParallelLayout:
         self.tp_index = int(self.P_grid.index[1])
 
 
-def _norm(cfg, P, zero):
+def _norm(cfg, P, zero, keep=None):
+    keep = (cfg.keep_gathered or cfg.keep_norms_gathered) if keep is None else keep
     if cfg.norm == "rms":
         return dnn.DistributedRMSNormZero(P, cfg.d_model, eps=cfg.eps, dtype=cfg.dtype,
-                                          auto_clear_buffer=not cfg.keep_gathered)
+                                          auto_clear_buffer=not keep)
     if zero:
         return dnn.DistributedLayerNormZero(P, cfg.d_model, eps=cfg.eps, dtype=cfg.dtype,
-                                            auto_clear_buffer=not cfg.keep_gathered)
+                                            auto_clear_buffer=not keep)
     return dnn.DistributedLayerNorm(P, cfg.d_model, eps=cfg.eps, dtype=cfg.dtype)
 
 
@@ -181,15 +185,16 @@ class Decoder(torch.nn.Module):
         self.cfg, self.layout = cfg, layout
         V = cfg.padded_vocab()
         self.padded_vocab = V
+        keep_root = cfg.keep_gathered or cfg.keep_root_gathered
         self.embed = dnn.DistributedEmbeddingZero(layout.P_flat2, V, cfg.d_model, dtype=cfg.dtype,
-                                                  auto_clear_buffer=not cfg.keep_gathered)
+                                                  auto_clear_buffer=not keep_root)
         if not cfg.rope:
             self.pos_embed = dnn.DistributedEmbeddingZero(layout.P_flat2, cfg.max_seq, cfg.d_model, dtype=cfg.dtype,
-                                                          auto_clear_buffer=not cfg.keep_gathered)
+                                                          auto_clear_buffer=not keep_root)
         self.blocks = torch.nn.ModuleList(Block(cfg, layout) for _ in range(cfg.n_layers))
-        self.final_norm = _norm(cfg, layout.P_flat, True)
+        self.final_norm = _norm(cfg, layout.P_flat, True, keep=keep_root)
         self.head = dnn.DistributedLinearAllGatherZero(layout.P_flat, cfg.d_model, V, bias=False, dtype=cfg.dtype,
-                                                       auto_clear_buffer=not cfg.keep_gathered)
+                                                       auto_clear_buffer=not keep_root)
         self.reset_parameters()
 
     def reset_parameters(self):

@@ -87,6 +87,9 @@ class _ZeroNormBase(Module):
             full = self.allgather(getattr(self, n)).reshape(self.num_features)
             if not self.auto_clear_buffer:
                 full = full.detach().requires_grad_(True)
+                if full.is_cuda and full.dtype == torch.bfloat16:
+                    # the fused norm backward accumulates dw / db of every micro-batch here in fp32
+                    full.main_grad = torch.zeros(self.num_features, dtype=torch.float32, device=full.device)
             out[n] = full
         self.buffers_gathered = out
 
@@ -103,9 +106,12 @@ class _ZeroNormBase(Module):
     def clear_weight_buffer(self):
         if self.buffers_gathered is not None and not self.auto_clear_buffer:
             for n, full in self.buffers_gathered.items():
-                if full.grad is None:
+                g = full.grad
+                if g is None:
+                    g = getattr(full, "main_grad", None)
+                if g is None:
                     continue
-                g = full.grad if self.scale_backward is None else full.grad / self.scale_backward
+                g = g if self.scale_backward is None else g / self.scale_backward
                 gl = self.reduce_scatter(g.reshape([self.num_features] + [1] * (self.P_x.dim - 1)))
                 p = getattr(self, n)
                 deliver_grad(p, gl)

@@ -27,7 +27,7 @@ c_void_p, c_int, c_ll, c_uint = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
 _PP, _IP, _UP = ctypes.POINTER(c_void_p), ctypes.POINTER(c_int), ctypes.POINTER(c_uint)
 _native.declare("dd_ag_gemm", [c_int, c_int, _PP, c_void_p, c_void_p, c_int, c_ll, c_void_p, c_ll, c_void_p, c_int,
                                c_int, c_int, c_int, c_int, c_void_p, c_uint, _PP, _IP, _UP, c_void_p, c_uint, c_int,
-                               c_void_p])
+                               c_void_p, _UP, c_void_p])
 _native.declare("dd_gemm_rs", [c_int, c_int, c_void_p, c_ll, c_void_p, c_int, c_ll, _PP, c_void_p, c_void_p, c_void_p,
                                c_int, c_int, c_int, c_int, c_int, _PP, _IP, _UP, _UP, c_void_p, c_uint, c_void_p,
                                c_uint, c_int, c_void_p])
@@ -55,13 +55,23 @@ class _State:
         self.misc = self.h.region_tensor("misc", self.h.regions["misc"][1], torch.int32)
         self.misc.zero_()
         self.done = [0, 0, 0]                           # ag pull, rs gemm, rs reduce (totals so far)
-        self.ready_words = self.misc.numel() - 64
+        # after the counters: ready words, then the per-block piece counters of the pull
+        self.ready_words = (self.misc.numel() - 64) // 2
+        # the shard staging is double buffered: a call only has to know that the readers
+        # of the call before the previous one are through, which the previous call's
+        # kernel has already checked
+        self.ag_calls = {}
+        self.ag_last_team = None
+        self.ag_unconfirmed = None
 
     def counter_ptr(self, i):
         return self.h.region_ptr("misc", offset=4 * i)
 
     def ready_ptr(self):
         return self.h.region_ptr("misc", offset=4 * 64)
+
+    def ready_cnt_ptr(self):
+        return self.h.region_ptr("misc", offset=4 * (64 + self.ready_words))
 
 
 _state = None
@@ -72,6 +82,25 @@ def state() -> _State:
     if _state is None:
         _state = _State()
     return _state
+
+
+PAD_AG_WORD = 1024      # word offset of the ag_gemm signals inside a signal pad
+
+
+def _confirm_readers(st, limit_s: float = 2.0):
+    """Host-side bounded wait until the peers of the last double-buffered ``ag_gemm``
+    have signalled that they are done reading this process's shard."""
+    import time
+    _team, expected = st.ag_unconfirmed
+    pad = symm._wrap_device_pointer(st.h._local_pad.value, symm.SIGNAL_PAD_BYTES // 4, torch.int32, st.h.device)
+    torch.cuda.current_stream().synchronize()
+    t0 = time.time()
+    for r, want in expected.items():
+        while ((int(pad[PAD_AG_WORD + r].item()) & 0xFFFFFFFF) - (want & 0xFFFFFFFF)) & 0x80000000:
+            if time.time() - t0 > limit_s:
+                raise RuntimeError(f"peer {r} did not finish reading the all-gather shard within {limit_s} s")
+            time.sleep(0.0005)
+    st.ag_unconfirmed = None
 
 
 def _team_arrays(h, ranks):
@@ -94,16 +123,33 @@ def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, bias, ranks):
     b, s_local, K = x_local.shape
     N = w.shape[0]
     nbytes = x_local.numel() * 2
-    stage = h.region_tensor("ag_shard", nbytes, torch.bfloat16)
+    half = h.regions["ag_shard"][1] // 2 // 256 * 256
+    # The shard staging is double buffered: this call's kernel then only checks, before
+    # it exits, that the readers of the PREVIOUS call are through (they are, in
+    # practice), instead of waiting for its own readers.  That is sound while
+    # consecutive calls use the same team; on a change of team the host first confirms
+    # the readers of the last double-buffered call.
+    team = tuple(ranks)
+    if st.ag_unconfirmed is not None and (st.ag_unconfirmed[0] != team or nbytes > half):
+        _confirm_readers(st)
+    double = nbytes <= half and st.ag_last_team == team
+    parity = st.ag_calls.get(team, 0) & 1 if nbytes <= half else 0
+    if nbytes <= half:
+        st.ag_calls[team] = st.ag_calls.get(team, 0) + 1
+    st.ag_last_team = team if nbytes <= half else None
+    off = parity * half
+    stage = h.region_tensor("ag_shard", nbytes, torch.bfloat16, offset=off)
     stage.copy_(x_local.reshape(-1))
     M = b * P * s_local
     if M // 128 > st.ready_words:
         raise ValueError("too many row blocks for the ready-word region")
     G = torch.empty(b, P * s_local, K, dtype=torch.bfloat16, device=x_local.device)
     y = torch.empty(b, P * s_local, N, dtype=torch.bfloat16, device=x_local.device)
-    shards = (c_void_p * P)(*[h.region_ptr("ag_shard", r) for r in ranks])
+    shards = (c_void_p * P)(*[h.region_ptr("ag_shard", r, off) for r in ranks])
     pads, writers = _team_arrays(h, ranks)
     expect = (c_uint * P)(*[(st.ag_signals[r] + 1) & 0xFFFFFFFF for r in ranks])
+    # "done pulling" of this call, or (double buffered) of the previous call
+    end_expect = (c_uint * P)(*[(st.ag_signals[r] + (0 if double else 2)) & 0xFFFFFFFF for r in ranks])
     st.epoch += 1
     st.done[0] += st.sm
     w_mn, ldw, _ = _major(w)
@@ -111,10 +157,13 @@ def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, bias, ranks):
     _native.check(_native.lib().dd_ag_gemm(
         P, me, shards, G.data_ptr(), w.data_ptr(), w_mn, ldw, y.data_ptr(), N, ptr(bias),
         int(bias is not None and bias.dtype == torch.float32), b, s_local, N, K, st.ready_ptr(), st.epoch, pads,
-        writers, expect, st.counter_ptr(0), st.done[0] & 0xFFFFFFFF, 0, stream_ptr()), "dd_ag_gemm")
+        writers, expect, st.counter_ptr(0), st.done[0] & 0xFFFFFFFF, 0, st.ready_cnt_ptr(), end_expect,
+        stream_ptr()), "dd_ag_gemm")
     for r in ranks:
         if r != h.rank:
             st.ag_signals[r] += 2
+    # readers of this call are confirmed by the next call's kernel, if there is one
+    st.ag_unconfirmed = (team, {r: st.ag_signals[r] for r in ranks if r != h.rank}) if nbytes <= half else None
     return y, G
 
 

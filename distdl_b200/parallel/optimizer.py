@@ -27,6 +27,7 @@ class FlatAdamW:
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.max_grad_norm = max_grad_norm
         self.step_count = 0
+        self._release = getattr(model, "release_gathered", None)
         params = [(n, p) for n, p in model.named_parameters() if p.requires_grad and p.numel() > 0]
         decay = [(n, p) for n, p in params if not any(k in n for k in no_decay)]
         plain = [(n, p) for n, p in params if any(k in n for k in no_decay)]
@@ -79,7 +80,11 @@ class FlatAdamW:
     def step(self, grad_scale: float = 1.0):
         """Applies one AdamW update from the accumulated fp32 gradients (which are
         cleared).  With ``max_grad_norm`` the global gradient norm is computed
-        over all workers and the clipping coefficient stays on the device."""
+        over all workers and the clipping coefficient stays on the device.
+        A model that keeps gathered ZeRO parameters across micro-batches
+        (``release_gathered``) is asked to flush their gradients first."""
+        if self._release is not None:
+            self._release()
         if self.total == 0:
             if self.max_grad_norm and dist.is_initialized() and dist.get_world_size() > 1:
                 dist.all_reduce(torch.zeros(1, device="cuda" if torch.cuda.is_available() else "cpu"))

@@ -50,9 +50,6 @@ class Trainer:
             loss = self.model.loss(mb[:, :-1], mb[:, 1:], scale=scale)
             loss.backward()
             total += loss.detach().float()
-        release = getattr(self.model, "release_gathered", None)
-        if release is not None:
-            release()
         self.opt.step()
         self.steps_done += 1
         if dist.is_initialized() and dist.get_world_size() > 1:

@@ -57,5 +57,25 @@ def check_fused():
             dw_ref = dyg.reshape(-1, N).t() @ xin.detach().reshape(-1, K).float()
             err = (w2.grad.float() - dw_ref).abs().max().item() / (dw_ref.abs().max().item() + 1e-6)
             assert err < 3e-2, ("gemm_rs dw", err)
+    # back-to-back calls without synchronisation in between: the shard staging is double
+    # buffered, so a call must never overwrite a shard that a slower peer still reads
+    b, s_local, K, N = 2, 512, 2048, 1024
+    torch.manual_seed(5)
+    w = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16)
+    torch.manual_seed(100 + rank)
+    xs_local = [torch.randn(b, s_local, K, device=dev).to(torch.bfloat16) for _ in range(7)]
+    outs = []
+    for i, x in enumerate(xs_local):
+        if i % 3 == rank % 3:
+            torch.cuda._sleep(2_000_000)               # skew the members against each other
+        outs.append(fused.ag_gemm(x, w, None, ranks))
+    for x, (y, G) in zip(xs_local, outs):
+        xs = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(xs, x)
+        xg = torch.cat(xs, dim=1)
+        assert torch.equal(G, xg), "gathered activation differs"
+        ref = xg.float() @ w.float().t()
+        err = (y.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+        assert err < 2e-2, ("ag_gemm back-to-back", err)
     torch.cuda.synchronize()
     assert _native.read_status()[0] == 0, _native.read_status()

@@ -33,6 +33,7 @@ def _grads(env):
         tok = _tokens(cfg)
         for _ in range(2):                              # two micro-batches accumulate
             model.loss(tok[:, :-1], tok[:, 1:], scale=1.0 / tok[:, 1:].numel()).backward()
+        model.release_gathered()
         torch.cuda.synchronize()
         return opt.grad.clone(), opt.names
     finally:
