@@ -300,6 +300,170 @@ __global__ void __launch_bounds__(kThreads) exchange_kernel(const Team t, const 
 
 // Only the barrier: used to order host-driven phases and by tests of the
 // time-out path (a peer that never signals).
+
+// ---------------------------------------------------------------------------
+// LayerNorm / RMSNorm over a feature dimension that is split across the team
+// (tensor parallelism over the features): the statistics exchange is part of the
+// norm kernel.  Every member holds x [rows, d_local]; CTA b of every member handles
+// the same rows (warp-per-row, rows b*16+w, +512, ...), so the per-CTA team barrier
+// is the only synchronisation:
+//   phase 1  per-row partial sums of the local features -> own staging [rows] float4
+//   barrier  (same-index CTAs of all members)
+//   phase 2  read the partials of every member (peer loads), finish the statistics,
+//            normalise the local features.
+// Forward partials: {sum x, sum x^2, local feature count}; unequal shards are exact
+// because the counts travel with the sums.  Backward partials: {sum g, sum g*xhat}
+// with g = dy * w; dw / db are local to the shard and reduced with atomics.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void ld8f(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ void st8f(__nv_bfloat16* p, const float (&f)[8]) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]),
+                                            pack_bf16x2(f[6], f[7]));
+}
+__device__ __forceinline__ float4 team_sum4(const Team& t, size_t row) {
+  float4 u[kMaxPeers];
+#pragma unroll
+  for (int i = 0; i < kMaxPeers; ++i)
+    if (i < t.n) {
+      const uint4 v = ld_peer(reinterpret_cast<const char*>(t.buf[i]) + row * 16);
+      u[i] = make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
+    }
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < kMaxPeers; ++i)
+    if (i < t.n) { a.x += u[i].x; a.y += u[i].y; a.z += u[i].z; a.w += u[i].w; }
+  return a;
+}
+
+template <bool RMS>
+__global__ void __launch_bounds__(kThreads)
+split_norm_fwd_kernel(const Team t, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                      const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y, float2* __restrict__ stats,
+                      int rows, int d, float eps) {
+  __shared__ int fail;
+  if (threadIdx.x == 0) fail = 0;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wpb = kThreads / 32;
+  const int nvec = d >> 3;
+  float4* mine = reinterpret_cast<float4*>(t.buf[t.me]);
+  for (int row = blockIdx.x * wpb + warp; row < rows; row += gridDim.x * wpb) {
+    const __nv_bfloat16* xr = x + (size_t)row * d;
+    float s = 0.f, ss = 0.f;
+    for (int vi = lane; vi < nvec; vi += 32) {
+      float v[8];
+      ld8f(xr + vi * 8, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { s += v[j]; ss += v[j] * v[j]; }
+    }
+    s = warp_sum(s);
+    ss = warp_sum(ss);
+    if (lane == 0) mine[row] = make_float4(s, ss, (float)d, 0.f);
+  }
+  __threadfence_system();
+  if (!team_barrier(t, 0, &fail)) return;
+  for (int row = blockIdx.x * wpb + warp; row < rows; row += gridDim.x * wpb) {
+    const float4 a = team_sum4(t, (size_t)row);
+    const float n = a.z;
+    const float mean = RMS ? 0.f : a.x / n;
+    const float var = RMS ? a.y / n : fmaxf(a.y / n - mean * mean, 0.f);
+    const float rstd = rsqrtf(var + eps);
+    if (lane == 0 && stats != nullptr) stats[row] = make_float2(mean, rstd);
+    const __nv_bfloat16* xr = x + (size_t)row * d;
+    __nv_bfloat16* yr = y + (size_t)row * d;
+    for (int vi = lane; vi < nvec; vi += 32) {
+      float v[8], wv[8], o[8];
+      ld8f(xr + vi * 8, v);
+      if (w != nullptr) ld8f(w + vi * 8, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (v[j] - mean) * rstd * (w != nullptr ? wv[j] : 1.f);
+      if (b != nullptr) {
+        float bv[8];
+        ld8f(b + vi * 8, bv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += bv[j];
+      }
+      st8f(yr + vi * 8, o);
+    }
+  }
+  team_barrier(t, 1, &fail);
+}
+
+template <bool RMS>
+__global__ void __launch_bounds__(kThreads)
+split_norm_bwd_kernel(const Team t, const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                      const __nv_bfloat16* __restrict__ w, const float2* __restrict__ stats,
+                      __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, float* __restrict__ db, int rows, int d,
+                      float n_global) {
+  __shared__ int fail;
+  if (threadIdx.x == 0) fail = 0;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wpb = kThreads / 32;
+  const int nvec = d >> 3;
+  float4* mine = reinterpret_cast<float4*>(t.buf[t.me]);
+  for (int row = blockIdx.x * wpb + warp; row < rows; row += gridDim.x * wpb) {
+    const float2 st = stats[row];
+    float sg = 0.f, sgx = 0.f;
+    for (int vi = lane; vi < nvec; vi += 32) {
+      float g[8], v[8], wv[8];
+      ld8f(dy + (size_t)row * d + vi * 8, g);
+      ld8f(x + (size_t)row * d + vi * 8, v);
+      if (w != nullptr) ld8f(w + vi * 8, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float gj = g[j] * (w != nullptr ? wv[j] : 1.f);
+        sg += gj;
+        sgx += gj * (v[j] - st.x) * st.y;
+      }
+    }
+    sg = warp_sum(sg);
+    sgx = warp_sum(sgx);
+    if (lane == 0) mine[row] = make_float4(sg, sgx, 0.f, 0.f);
+  }
+  __threadfence_system();
+  if (!team_barrier(t, 0, &fail)) return;
+  const float inv_n = 1.f / n_global;
+  for (int row = blockIdx.x * wpb + warp; row < rows; row += gridDim.x * wpb) {
+    const float4 a = team_sum4(t, (size_t)row);
+    const float2 st = stats[row];
+    const float c1 = RMS ? 0.f : a.x * inv_n, c2 = a.y * inv_n;
+    for (int vi = lane; vi < nvec; vi += 32) {
+      float g[8], v[8], wv[8], o[8];
+      ld8f(dy + (size_t)row * d + vi * 8, g);
+      ld8f(x + (size_t)row * d + vi * 8, v);
+      if (w != nullptr) ld8f(w + vi * 8, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = (v[j] - st.x) * st.y;
+        const float gj = g[j] * (w != nullptr ? wv[j] : 1.f);
+        o[j] = st.y * (gj - c1 - xh * c2);
+      }
+      st8f(dx + (size_t)row * d + vi * 8, o);
+    }
+  }
+  // dw / db of the local features: column sums over this CTA's rows, then atomics
+  if (dw != nullptr || db != nullptr) {
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+      float aw = 0.f, ab = 0.f;
+      for (int k = 0; k < wpb; ++k)
+        for (int row = blockIdx.x * wpb + k; row < rows; row += gridDim.x * wpb) {
+          const float2 st = stats[row];
+          const float g = __bfloat162float(dy[(size_t)row * d + c]);
+          aw += g * (__bfloat162float(x[(size_t)row * d + c]) - st.x) * st.y;
+          ab += g;
+        }
+      if (dw != nullptr) atomicAdd(dw + c, aw);
+      if (db != nullptr) atomicAdd(db + c, ab);
+    }
+  }
+  team_barrier(t, 1, &fail);
+}
+
 __global__ void __launch_bounds__(kThreads) barrier_only_kernel(const Team t) {
   __shared__ int fail;
   if (threadIdx.x == 0) fail = 0;
@@ -423,6 +587,45 @@ DD_API int dd_exchange(int n, int me, int my_writer, void* const* bufs, void* co
   d.slot_bytes = slot_bytes;
   *steps = 2;
   exchange_kernel<<<kCollectiveCtas, kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(t, d);
+  return (int)cudaGetLastError();
+}
+// Norm over a feature dimension split across the team, statistics exchange fused
+// (see split_norm_fwd_kernel).  x, y: [rows, d] bf16 local shards; stats: [rows]
+// float2 {mean, rstd} of the FULL rows; the staging buffer must hold rows * 16 bytes.
+DD_API int dd_split_norm_fwd(int n, int me, int my_writer, void* const* bufs, void* const* flags, const int* writers,
+                             const unsigned* expect, int rms, const void* x, const void* w, const void* b, void* y,
+                             void* stats, int rows, int d, float eps, int* steps, void* stream) {
+  if (d % 8 || rows <= 0) return DD_ERR_BAD_ARG;
+  Team t;
+  int r = fill_team(t, n, me, my_writer, bufs, flags, writers, expect);
+  if (r) return r;
+  *steps = 2;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  auto X = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto W = reinterpret_cast<const __nv_bfloat16*>(w);
+  auto B = reinterpret_cast<const __nv_bfloat16*>(b);
+  auto Y = reinterpret_cast<__nv_bfloat16*>(y);
+  if (rms) split_norm_fwd_kernel<true><<<kCollectiveCtas, kThreads, 0, s>>>(t, X, W, B, Y, (float2*)stats, rows, d, eps);
+  else split_norm_fwd_kernel<false><<<kCollectiveCtas, kThreads, 0, s>>>(t, X, W, B, Y, (float2*)stats, rows, d, eps);
+  return (int)cudaGetLastError();
+}
+// dw / db: fp32 [d], ADDED to (the caller zeroes or accumulates); n_global = full feature count.
+DD_API int dd_split_norm_bwd(int n, int me, int my_writer, void* const* bufs, void* const* flags, const int* writers,
+                             const unsigned* expect, int rms, const void* dy, const void* x, const void* w,
+                             const void* stats, void* dx, float* dw, float* db, int rows, int d, float n_global,
+                             int* steps, void* stream) {
+  if (d % 8 || rows <= 0 || n_global <= 0.f) return DD_ERR_BAD_ARG;
+  Team t;
+  int r = fill_team(t, n, me, my_writer, bufs, flags, writers, expect);
+  if (r) return r;
+  *steps = 2;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  auto DY = reinterpret_cast<const __nv_bfloat16*>(dy);
+  auto X = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto W = reinterpret_cast<const __nv_bfloat16*>(w);
+  auto DX = reinterpret_cast<__nv_bfloat16*>(dx);
+  if (rms) split_norm_bwd_kernel<true><<<kCollectiveCtas, kThreads, 0, s>>>(t, DY, X, W, (const float2*)stats, DX, dw, db, rows, d, n_global);
+  else split_norm_bwd_kernel<false><<<kCollectiveCtas, kThreads, 0, s>>>(t, DY, X, W, (const float2*)stats, DX, dw, db, rows, d, n_global);
   return (int)cudaGetLastError();
 }
 DD_API int dd_team_barrier(int n, int me, int my_writer, void* const* bufs, void* const* flags, const int* writers,

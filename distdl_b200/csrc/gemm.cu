@@ -2,6 +2,8 @@
 #include <cstdlib>
 
 #include "gemm2_tcgen05.cuh"
+#include <cstring>
+
 #include "gemm_tcgen05.cuh"
 #include "runtime.cuh"
 
@@ -24,7 +26,8 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int gr
   return (int)cudaGetLastError();
 }
 template <bool A_MN, bool B_MN>
-int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int grid, cudaStream_t stream) {
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const Params& p, int grid,
+                cudaStream_t stream) {
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -34,7 +37,7 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, i
     if (e != cudaSuccess) return (int)e;
     configured[dev & 63] = true;
   }
-  kern<<<grid, dd::gemm2::NUM_THREADS, dd::gemm2::SMEM_BYTES, stream>>>(ta, tb, p);
+  kern<<<grid, dd::gemm2::NUM_THREADS, dd::gemm2::SMEM_BYTES, stream>>>(ta, tb, td, p);
   return (int)cudaGetLastError();
 }
 }  // namespace
@@ -82,10 +85,23 @@ DD_API int dd_gemm_bf16(const void* A, int a_mn, long long lda, long long stride
     if (ctas < 2) ctas = 2;
     const int pgrid = 2 * ptiles < ctas ? 2 * ptiles : ctas;
     cudaStream_t ps = reinterpret_cast<cudaStream_t>(stream);
-    if (a_mn && b_mn) return launch_pair<true, true>(pa, pb, q, pgrid, ps);
-    if (a_mn) return launch_pair<true, false>(pa, pb, q, pgrid, ps);
-    if (b_mn) return launch_pair<false, true>(pa, pb, q, pgrid, ps);
-    return launch_pair<false, false>(pa, pb, q, pgrid, ps);
+    // TMA epilogue where the output qualifies: bf16 store, fp32 store or fp32 add
+    static const bool tma_epi = []() { const char* e = getenv("DISTDL_GEMM_TMA_EPI"); return !(e && e[0] == '0'); }();
+    CUtensorMap pd;
+    memset(&pd, 0, sizeof(pd));
+    const bool f32 = (flags & F_OUT_F32) != 0;
+    const long long es = f32 ? 4 : 2;
+    if (tma_epi && (f32 || !(flags & F_ACCUMULATE)) && (reinterpret_cast<uintptr_t>(D) & 15) == 0 &&
+        (ldd * es) % 16 == 0 && (strideD * es) % 16 == 0) {
+      rr = f32 ? get_tensor_map_f32_3d(&pd, D, N, M, batch, ldd * 4, strideD * 4, 32, 32)
+               : get_tensor_map_bf16_3d(&pd, D, N, M, batch, ldd * 2, strideD * 2, 64, 32);
+      if (rr) return rr;
+      q.flags |= F_TMA_EPI;
+    }
+    if (a_mn && b_mn) return launch_pair<true, true>(pa, pb, pd, q, pgrid, ps);
+    if (a_mn) return launch_pair<true, false>(pa, pb, pd, q, pgrid, ps);
+    if (b_mn) return launch_pair<false, true>(pa, pb, pd, q, pgrid, ps);
+    return launch_pair<false, false>(pa, pb, pd, q, pgrid, ps);
   }
   CUtensorMap ta, tb;
   int r;

@@ -36,7 +36,10 @@ constexpr int B_STAGE_BYTES = BNH * BK * 2;   // 16 KB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int TMEM_COLS = ACC_STAGES * BN;
 constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
+// epilogue staging: per epilogue warp two boxes of [32 rows][128 B]
+constexpr int OUT_WARP_BYTES = 2 * 32 * 128;
+constexpr int OUT_STAGE_BYTES = 4 * OUT_WARP_BYTES;          // 32 KB
+constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + OUT_STAGE_BYTES + 256;
 
 struct SharedStorage {
   uint64_t full[STAGES];
@@ -107,6 +110,80 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 }
 
 
+// TMA epilogue of one warp: its 32 rows x BN columns of the accumulator at `taddr`
+// go registers -> 128B-swizzled shared memory -> TMA, so that the tile leaves the SM
+// as full 128-byte lines (local memory or a peer's, behind NVLink).  bf16 output:
+// rounds of 128 columns (two boxes of 64); fp32: rounds of 64 columns (two boxes of
+// 32), stored or, with F_ACCUMULATE, added at L2 by a TMA reduction, which spares
+// the read of D.  `map` has box {64 | 32 columns, 32 rows}; rows and columns past
+// the tensor are clipped by the hardware.  `write` = false skips the stores.
+__device__ __forceinline__ void epilogue_tma(const Params& q, const CUtensorMap* map, uint32_t taddr, uint8_t* stage_w,
+                                             int lane, int col_tile0, int row0, int tb, bool write) {
+  const bool f32 = (q.flags & gemm::F_OUT_F32) != 0;
+  const bool add = (q.flags & gemm::F_ACCUMULATE) != 0;
+  const int round_cols = f32 ? 64 : 128;
+  const int box_cols = round_cols / 2;
+#pragma unroll 1
+  for (int rd = 0; rd < BN / round_cols; ++rd) {
+    const int colr = col_tile0 + rd * round_cols;
+    if (colr >= q.N) break;
+    if (lane == 0) tma_store_wait_read();
+    __syncwarp();
+#pragma unroll 1
+    for (int cc = 0; cc < round_cols / 32; ++cc) {
+      const int col0 = colr + cc * 32;
+      uint32_t r[32];
+      tmem_ld_32x32(taddr + rd * round_cols + cc * 32, r);
+      tmem_ld_wait();
+      if ((q.flags & gemm::F_BIAS) && col0 < q.N) {
+        const int nv = min(32, q.N - col0);
+        if (q.flags & gemm::F_BIAS_F32) {
+          const float* bp = reinterpret_cast<const float*>(q.bias) + col0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (i < nv) r[i] = __float_as_uint(__uint_as_float(r[i]) + __ldg(bp + i));
+        } else {
+          const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(q.bias) + col0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (i < nv) r[i] = __float_as_uint(__uint_as_float(r[i]) + __bfloat162float(__ldg(bp + i)));
+        }
+      }
+      if (f32) {
+        uint8_t* rowp = stage_w + cc * (32 * 128) + lane * 128;      // box cc: 32 fp32 = 128 B per row
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+          *reinterpret_cast<uint4*>(rowp + ((g ^ (lane & 7)) << 4)) = make_uint4(r[4 * g], r[4 * g + 1], r[4 * g + 2],
+                                                                               r[4 * g + 3]);
+      } else {
+        uint8_t* rowp = stage_w + (cc >> 1) * (32 * 128) + lane * 128;  // box cc / 2: 64 bf16 = 128 B per row
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 v;
+          v.x = pack_bf16x2(__uint_as_float(r[8 * g]), __uint_as_float(r[8 * g + 1]));
+          v.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]), __uint_as_float(r[8 * g + 3]));
+          v.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]), __uint_as_float(r[8 * g + 5]));
+          v.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]), __uint_as_float(r[8 * g + 7]));
+          const int chunk = (cc & 1) * 4 + g;
+          *reinterpret_cast<uint4*>(rowp + ((chunk ^ (lane & 7)) << 4)) = v;
+        }
+      }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && write) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int c0 = colr + j * box_cols;
+        if (c0 >= q.N) break;
+        if (add) tma_reduce_add_3d(map, stage_w + j * (32 * 128), c0, row0, tb);
+        else     tma_store_3d(map, stage_w + j * (32 * 128), c0, row0, tb);
+      }
+      tma_store_commit();
+    }
+  }
+}
+
 __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn,
                                                  int& tb) {
   gemm::tile_coords(tile, tiles_m, tiles_n, group_m, tm, tn, tb);
@@ -115,10 +192,11 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                  const Params p) {
+                  const __grid_constant__ CUtensorMap tmap_d, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  SharedStorage* ss = reinterpret_cast<SharedStorage*>(tiles + STAGES * STAGE_BYTES);
+  uint8_t* out_stage = tiles + STAGES * STAGE_BYTES;
+  SharedStorage* ss = reinterpret_cast<SharedStorage*>(out_stage + OUT_STAGE_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();          // 0 = leader
@@ -236,20 +314,26 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const int row = tm * 2 * BM + (int)rank * BM + quarter * 32 + lane;
       const long long row_off = (long long)tb * p.strideD + (long long)row * p.ldd;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+      if (p.flags & gemm::F_TMA_EPI) {
+        epilogue_tma(p, &tmap_d, taddr, out_stage + quarter * OUT_WARP_BYTES, lane, tn * BN,
+                     tm * 2 * BM + (int)rank * BM + quarter * 32, tb, true);
+      } else {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = tn * BN + c * 32;
-        if (col0 >= p.N) break;
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        if (row < p.M) store_chunk(p, r, row_off, col0, min(32, p.N - col0), vec_ok);
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = tn * BN + c * 32;
+          if (col0 >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (row < p.M) store_chunk(p, r, row_off, col0, min(32, p.N - col0), vec_ok);
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&ss->tmem_empty[acc]), 0));
       if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
     }
+    if ((p.flags & gemm::F_TMA_EPI) && lane == 0) tma_store_wait_all();
   }
 
   tc_fence_before();

@@ -30,6 +30,7 @@
 // All flags are counters that only grow; every wait is bounded (2 s) and
 // reports through the status record.
 #include <cstdlib>
+#include <cstring>
 
 #include "gemm_fused_common.cuh"
 #include "runtime.cuh"
@@ -524,7 +525,15 @@ DD_API int dd_ag_gemm(int P, int me, void* const* shards, void* G, const void* w
   if (pair) {
     if (ready_cnt == nullptr) return DD_ERR_BAD_ARG;
     ap.g.group_m = 4;
-    return dd_launch_ag_pair(ta, tb, ap, w_mn, ctas, reinterpret_cast<cudaStream_t>(stream));
+    static const bool tma_epi = []() { const char* e = getenv("DISTDL_GEMM_TMA_EPI"); return !(e && e[0] == '0'); }();
+    RsOutMaps om;
+    memset(&om, 0, sizeof(om));
+    if (tma_epi && (reinterpret_cast<uintptr_t>(D) & 15) == 0 && ldd % 8 == 0) {
+      r = get_tensor_map_bf16_3d(&om.m[0], D, N, M, 1, (uint64_t)ldd * 2, (uint64_t)M * ldd * 2, 64, 32);
+      if (r) return r;
+      ap.g.flags |= F_TMA_EPI;
+    }
+    return dd_launch_ag_pair(ta, tb, om, ap, w_mn, ctas, reinterpret_cast<cudaStream_t>(stream));
   }
   static bool configured = false;
   if (!configured) {
@@ -580,6 +589,7 @@ DD_API int dd_gemm_rs(int P, int me, const void* x, long long ldx, const void* w
     rp.g.group_m = 4;
     static const bool tma_store = []() { const char* e = getenv("DISTDL_RS_TMA_STORE"); return !(e && e[0] == '0'); }();
     RsOutMaps om;
+    memset(&om, 0, sizeof(om));
     if (tma_store) {
       const uint64_t rows = (uint64_t)batch * s_local;
       for (int i = 0; i < P; ++i) {

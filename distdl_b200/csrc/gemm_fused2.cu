@@ -15,8 +15,6 @@ namespace g2 = dd::gemm2;
 namespace {
 
 constexpr int PAIR_FUSED_THREADS = g2::NUM_THREADS + 128;
-constexpr int OUT_STAGE_BYTES = 4 * 2 * 32 * 128;          // 32 KB
-constexpr int SMEM_RS = g2::SMEM_BYTES + OUT_STAGE_BYTES;
 
 // MODE 1 = ag_gemm (AgParams), MODE 2 = gemm_rs (RsParams)
 template <bool B_MN, int MODE, typename FP>
@@ -26,9 +24,8 @@ fused_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const Params& p = fp.g;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  // gemm_rs: per epilogue warp, two boxes of [32 rows][128 B] for the TMA stores
   uint8_t* out_stage = tiles + g2::STAGES * g2::STAGE_BYTES;
-  g2::SharedStorage* ss = reinterpret_cast<g2::SharedStorage*>(out_stage + (MODE == 2 ? OUT_STAGE_BYTES : 0));
+  g2::SharedStorage* ss = reinterpret_cast<g2::SharedStorage*>(out_stage + g2::OUT_STAGE_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = g2::cluster_ctarank();
@@ -234,60 +231,17 @@ fused_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         row_off = ((long long)rb * BM + quarter * 32 + lane) * p.ldd;
       }
       const uint32_t taddr = tmem_base + acc * g2::BN + ((uint32_t)(quarter * 32) << 16);
-      bool stored = false;
-      if constexpr (MODE == 2) {
-        if (fp.tma_store) {
-          // registers -> swizzled shared memory -> TMA store: the tile leaves the SM as
-          // full 128-byte lines, whether the owner's slot is local or behind NVLink
-          stored = true;
-          uint8_t* stage_w = out_stage + quarter * (2 * 32 * 128);
-#pragma unroll 1
-          for (int half = 0; half < 2; ++half) {
-            const int colh = tn * g2::BN + half * 128;
-            if (colh >= p.N) break;
-            if (lane == 0) tma_store_wait_read();
-            __syncwarp();
-#pragma unroll 1
-            for (int cc = 0; cc < 4; ++cc) {
-              const int col0 = colh + cc * 32;
-              uint32_t r[32];
-              tmem_ld_32x32(taddr + half * 128 + cc * 32, r);
-              tmem_ld_wait();
-              if ((q.flags & F_BIAS) && col0 < p.N) {
-                const int nv = min(32, p.N - col0);
-                if (q.flags & F_BIAS_F32) {
-                  const float* bp = reinterpret_cast<const float*>(q.bias) + col0;
-#pragma unroll
-                  for (int i = 0; i < 32; ++i)
-                    if (i < nv) r[i] = __float_as_uint(__uint_as_float(r[i]) + __ldg(bp + i));
-                } else {
-                  const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(q.bias) + col0;
-#pragma unroll
-                  for (int i = 0; i < 32; ++i)
-                    if (i < nv) r[i] = __float_as_uint(__uint_as_float(r[i]) + __bfloat162float(__ldg(bp + i)));
-                }
-              }
-              uint8_t* rowp = stage_w + (cc >> 1) * (32 * 128) + lane * 128;
-#pragma unroll
-              for (int g = 0; g < 4; ++g) {
-                uint4 v;
-                v.x = pack_bf16x2(__uint_as_float(r[8 * g]), __uint_as_float(r[8 * g + 1]));
-                v.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]), __uint_as_float(r[8 * g + 3]));
-                v.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]), __uint_as_float(r[8 * g + 5]));
-                v.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]), __uint_as_float(r[8 * g + 7]));
-                const int chunk = (cc & 1) * 4 + g;
-                *reinterpret_cast<uint4*>(rowp + ((chunk ^ (lane & 7)) << 4)) = v;
-              }
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0 && o < row_blocks) {
-              const int row0 = lb * BM + quarter * 32;
-              tma_store_3d(&omaps.m[owner], stage_w, colh, row0, 0);
-              if (colh + 64 < p.N) tma_store_3d(&omaps.m[owner], stage_w + 32 * 128, colh + 64, row0, 0);
-              tma_store_commit();
-            }
-          }
+      // TMA epilogue: omaps.m[owner] is the owner's slot (gemm_rs) / omaps.m[0] is D (ag_gemm)
+      bool stored;
+      if constexpr (MODE == 2) stored = fp.tma_store != 0;
+      else stored = (p.flags & F_TMA_EPI) != 0;
+      if (stored) {
+        if constexpr (MODE == 2) {
+          g2::epilogue_tma(q, &omaps.m[owner], taddr, out_stage + quarter * g2::OUT_WARP_BYTES, lane, tn * g2::BN,
+                           lb * BM + quarter * 32, 0, o < row_blocks);
+        } else {
+          g2::epilogue_tma(q, &omaps.m[0], taddr, out_stage + quarter * g2::OUT_WARP_BYTES, lane, tn * g2::BN,
+                           rb * BM + quarter * 32, 0, o < row_blocks);
         }
       }
 #pragma unroll 1
@@ -303,6 +257,9 @@ fused_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       __syncwarp();
       if (lane == 0) g2::mbar_arrive_cluster(g2::mapa(smem_u32(&ss->tmem_empty[acc]), 0));
       if (++acc == g2::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+    }
+    if constexpr (MODE == 1) {
+      if ((p.flags & F_TMA_EPI) && lane == 0) tma_store_wait_all();
     }
     if constexpr (MODE == 2) {
       if (fp.tma_store && lane == 0) {
@@ -330,7 +287,7 @@ fused_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
 template <typename K>
 int set_smem(K kern) {
-  return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_RS);
+  return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g2::SMEM_BYTES);
 }
 
 }  // namespace
@@ -338,8 +295,8 @@ int set_smem(K kern) {
 // Launchers used by gemm_fused.cu when CTA pairs are enabled.  The tensor maps
 // must have been encoded with the pair tile boxes (A: {64, 128}; B: {64, 128}
 // K-major or {64, 64} MN-major).
-int dd_launch_ag_pair(const CUtensorMap& ta, const CUtensorMap& tb, const AgParams& ap, int w_mn, int ctas,
-                      cudaStream_t s) {
+int dd_launch_ag_pair(const CUtensorMap& ta, const CUtensorMap& tb, const RsOutMaps& om, const AgParams& ap, int w_mn,
+                      int ctas, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
     int r;
@@ -347,9 +304,8 @@ int dd_launch_ag_pair(const CUtensorMap& ta, const CUtensorMap& tb, const AgPara
     if ((r = set_smem(fused_pair_kernel<true, 1, AgParams>))) return r;
     configured = true;
   }
-  static const RsOutMaps none = {};
-  if (w_mn) fused_pair_kernel<true, 1, AgParams><<<ctas, PAIR_FUSED_THREADS, g2::SMEM_BYTES, s>>>(ta, tb, none, ap);
-  else      fused_pair_kernel<false, 1, AgParams><<<ctas, PAIR_FUSED_THREADS, g2::SMEM_BYTES, s>>>(ta, tb, none, ap);
+  if (w_mn) fused_pair_kernel<true, 1, AgParams><<<ctas, PAIR_FUSED_THREADS, g2::SMEM_BYTES, s>>>(ta, tb, om, ap);
+  else      fused_pair_kernel<false, 1, AgParams><<<ctas, PAIR_FUSED_THREADS, g2::SMEM_BYTES, s>>>(ta, tb, om, ap);
   return (int)cudaGetLastError();
 }
 
@@ -362,7 +318,7 @@ int dd_launch_rs_pair(const CUtensorMap& ta, const CUtensorMap& tb, const RsOutM
     if ((r = set_smem(fused_pair_kernel<true, 2, RsParams>))) return r;
     configured = true;
   }
-  if (w_mn) fused_pair_kernel<true, 2, RsParams><<<ctas, g2::NUM_THREADS, SMEM_RS, s>>>(ta, tb, om, rp);
-  else      fused_pair_kernel<false, 2, RsParams><<<ctas, g2::NUM_THREADS, SMEM_RS, s>>>(ta, tb, om, rp);
+  if (w_mn) fused_pair_kernel<true, 2, RsParams><<<ctas, g2::NUM_THREADS, g2::SMEM_BYTES, s>>>(ta, tb, om, rp);
+  else      fused_pair_kernel<false, 2, RsParams><<<ctas, g2::NUM_THREADS, g2::SMEM_BYTES, s>>>(ta, tb, om, rp);
   return (int)cudaGetLastError();
 }

@@ -117,8 +117,9 @@ struct AgParams {
 constexpr int kPullSub = 4;          // pieces per 128-row block (32 rows each)
 
 
-// Output tensor maps of the CTA-pair gemm_rs kernel: member i's staging slot for
-// source `me`, [batch*s_local rows][N] bf16, box = 64 columns x 32 rows.
+// Output tensor maps of the CTA-pair kernels, box = 64 columns x 32 rows of bf16.
+// gemm_rs: m[i] = member i's staging slot for source `me`, [batch*s_local rows][N];
+// ag_gemm: m[0] = the output D.
 struct RsOutMaps {
   CUtensorMap m[kMaxPeers];
 };
@@ -141,7 +142,7 @@ struct RsParams {
 }  // namespace dd
 
 // CTA-pair launchers (gemm_fused2.cu)
-int dd_launch_ag_pair(const CUtensorMap& ta, const CUtensorMap& tb, const dd::fused::AgParams& ap, int w_mn, int ctas,
-                      cudaStream_t s);
+int dd_launch_ag_pair(const CUtensorMap& ta, const CUtensorMap& tb, const dd::fused::RsOutMaps& om,
+                      const dd::fused::AgParams& ap, int w_mn, int ctas, cudaStream_t s);
 int dd_launch_rs_pair(const CUtensorMap& ta, const CUtensorMap& tb, const dd::fused::RsOutMaps& om,
                       const dd::fused::RsParams& rp, int w_mn, int ctas, cudaStream_t s);

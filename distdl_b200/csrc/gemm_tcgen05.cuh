@@ -45,6 +45,7 @@ enum Flags : int {
   F_ACCUMULATE = 2,   // D += result (else D = result)
   F_BIAS = 4,         // add bias[n] (bf16)
   F_BIAS_F32 = 8,     // bias is fp32
+  F_TMA_EPI = 16,     // CTA-pair kernels: the tile leaves through shared memory + TMA (set by the host)
 };
 
 struct Params {

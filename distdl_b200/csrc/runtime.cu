@@ -20,8 +20,9 @@ struct MapKey {
   uint64_t inner, outer, batch, s1, s2;
   uint32_t b0, b1;
   int dev;
+  int f32;
   bool operator==(const MapKey& o) const {
-    return base == o.base && inner == o.inner && outer == o.outer && batch == o.batch && s1 == o.s1 &&
+    return f32 == o.f32 && base == o.base && inner == o.inner && outer == o.outer && batch == o.batch && s1 == o.s1 &&
            s2 == o.s2 && b0 == o.b0 && b1 == o.b1 && dev == o.dev;
   }
 };
@@ -29,7 +30,7 @@ struct MapKeyHash {
   size_t operator()(const MapKey& k) const {
     uint64_t h = reinterpret_cast<uint64_t>(k.base) * 0x9E3779B97F4A7C15ull;
     auto mix = [&h](uint64_t v) { h ^= v + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2); };
-    mix(k.inner); mix(k.outer); mix(k.batch); mix(k.s1); mix(k.s2); mix(k.b0); mix(k.b1); mix(k.dev);
+    mix(k.inner); mix(k.outer); mix(k.batch); mix(k.s1); mix(k.s2); mix(k.b0); mix(k.b1); mix(k.dev); mix(k.f32);
     return (size_t)h;
   }
 };
@@ -78,14 +79,32 @@ PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
   return fn;
 }
 
+namespace {
+int get_tensor_map_3d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t batch,
+                      uint64_t outer_stride_bytes, uint64_t batch_stride_bytes, uint32_t box_inner,
+                      uint32_t box_outer, int f32);
+}
 int get_tensor_map_bf16_3d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
                            uint64_t batch, uint64_t outer_stride_bytes, uint64_t batch_stride_bytes,
                            uint32_t box_inner, uint32_t box_outer) {
+  return get_tensor_map_3d(out, base, inner, outer, batch, outer_stride_bytes, batch_stride_bytes, box_inner,
+                           box_outer, 0);
+}
+int get_tensor_map_f32_3d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                          uint64_t batch, uint64_t outer_stride_bytes, uint64_t batch_stride_bytes,
+                          uint32_t box_inner, uint32_t box_outer) {
+  return get_tensor_map_3d(out, base, inner, outer, batch, outer_stride_bytes, batch_stride_bytes, box_inner,
+                           box_outer, 1);
+}
+namespace {
+int get_tensor_map_3d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t batch,
+                      uint64_t outer_stride_bytes, uint64_t batch_stride_bytes, uint32_t box_inner,
+                      uint32_t box_outer, int f32) {
   if ((reinterpret_cast<uintptr_t>(base) & 15) || (outer_stride_bytes & 15) || (batch_stride_bytes & 15))
     return DD_ERR_ALIGN;
   int dev = 0;
   cudaGetDevice(&dev);
-  MapKey key{base, inner, outer, batch, outer_stride_bytes, batch_stride_bytes, box_inner, box_outer, dev};
+  MapKey key{base, inner, outer, batch, outer_stride_bytes, batch_stride_bytes, box_inner, box_outer, dev, f32};
   {
     std::lock_guard<std::mutex> lk(g_mu);
     auto it = g_maps.find(key);
@@ -106,7 +125,7 @@ int get_tensor_map_bf16_3d(CUtensorMap* out, const void* base, uint64_t inner, u
   cuuint64_t strides[2] = {outer_stride_bytes, batch_stride_bytes};
   cuuint32_t box[3] = {box_inner, box_outer, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = enc(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -124,6 +143,7 @@ int get_tensor_map_bf16_3d(CUtensorMap* out, const void* base, uint64_t inner, u
   }
   return 0;
 }
+}  // namespace
 
 }  // namespace dd
 

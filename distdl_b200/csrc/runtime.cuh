@@ -22,6 +22,11 @@ int get_tensor_map_bf16_3d(CUtensorMap* out, const void* base, uint64_t inner, u
                            uint64_t batch, uint64_t outer_stride_bytes, uint64_t batch_stride_bytes,
                            uint32_t box_inner, uint32_t box_outer);
 
+// The same for fp32 elements (outputs written or reduced by TMA).
+int get_tensor_map_f32_3d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                          uint64_t batch, uint64_t outer_stride_bytes, uint64_t batch_stride_bytes,
+                          uint32_t box_inner, uint32_t box_outer);
+
 int current_sm_count();
 
 }  // namespace dd

@@ -110,6 +110,15 @@ class DistributedLayerNorm(Module):
             shape = tuple(input.shape[-nn:])
             return torch.nn.functional.layer_norm(input, shape, None if w is None else w.reshape(shape),
                                                   None if b is None else b.reshape(shape), self.eps)
+        if nn == 1 and input.is_cuda and getattr(self._distdl_backend, "name", "") == "native_cupy":
+            # feature-split rows on the native backend: statistics exchange fused into the norm kernel
+            from ..parallel import split_norm
+            team = getattr(self, "_stat_team", None)
+            if team is None:
+                team = tuple(self.P_x.create_allreduction_partition(self.dim_reduce).ranks)
+                object.__setattr__(self, "_stat_team", team)
+            if split_norm.usable(input, w, b, team):
+                return split_norm.split_norm(input, w, b, self.eps, team, self.normalized_shape[0])
         dims = tuple(range(input.dim() - nn, input.dim()))
         xf = input.float()
         local_n = float(np.prod([input.shape[d] for d in dims]))

@@ -123,6 +123,46 @@ def check_zero_grad_accumulate():
     assert err < 2e-2, err
 
 
+def check_split_norm():
+    """Feature-split LayerNorm / RMSNorm with the fused statistics exchange against
+    the serial fp32 norm of the concatenated features (unequal shards)."""
+    from distdl_b200.parallel import split_norm
+    world, rank = dist.get_world_size(), dist.get_rank()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    ranks = tuple(range(world))
+    rows = 777
+    d_r = 64 + 8 * (rank % 2)
+    for rms in (False, True):
+        torch.manual_seed(10 + rank)
+        x = torch.randn(rows, d_r, device=dev).to(torch.bfloat16).requires_grad_()
+        w = (1 + 0.1 * torch.randn(d_r, device=dev)).to(torch.bfloat16).requires_grad_()
+        b = None if rms else (0.1 * torch.randn(d_r, device=dev)).to(torch.bfloat16).requires_grad_()
+        dy = torch.randn(rows, d_r, device=dev).to(torch.bfloat16)
+        parts = [None] * world
+        dist.all_gather_object(parts, (x.detach().float().cpu(), w.detach().float().cpu(),
+                                       None if b is None else b.detach().float().cpu(), dy.float().cpu()))
+        n_global = sum(p[0].shape[1] for p in parts)
+        assert split_norm.usable(x, w, b, ranks)
+        y = split_norm.split_norm(x, w, b, 1e-5, ranks, n_global, rms=rms)
+        y.backward(dy)
+        xf = torch.cat([p[0] for p in parts], 1).requires_grad_()
+        wf = torch.cat([p[1] for p in parts]).requires_grad_()
+        bf = None if rms else torch.cat([p[2] for p in parts]).requires_grad_()
+        dyf = torch.cat([p[3] for p in parts], 1)
+        if rms:
+            ref = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf
+        else:
+            ref = torch.nn.functional.layer_norm(xf, (n_global,), wf, bf, 1e-5)
+        ref.backward(dyf)
+        lo = sum(p[0].shape[1] for p in parts[:rank])
+        sl = slice(lo, lo + d_r)
+        for got, want, what in ((y, ref[:, sl], "y"), (x.grad, xf.grad[:, sl], "dx"), (w.grad, wf.grad[sl], "dw")) + \
+                (() if rms else ((b.grad, bf.grad[sl], "db"),)):
+            want = want.detach().to(dev)
+            err = (got.float() - want).abs().max().item() / (want.abs().max().item() + 1e-6)
+            assert err < 2e-2, ("split_norm", rms, what, err)
+
+
 def main():
     import distdl_b200
     from distdl_b200.backends.common import world as dworld
@@ -134,6 +174,7 @@ def main():
     if what in ("primitives", "all"):
         check_primitives_native()
         check_zero_grad_accumulate()
+        check_split_norm()
     if what in ("fused", "all"):
         from multi_gpu_fused import check_fused
         check_fused()
