@@ -25,7 +25,7 @@ using namespace dd;
 namespace {
 
 constexpr int BT = 128;  // tile edge for queries and keys
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;      // TMA warp, MMA warp, two softmax warpgroups (column halves)
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct BwdParams {
@@ -42,10 +42,13 @@ struct BwdParams {
 // One softmax-thread step shared by both kernels: reads row `row` of S and dP
 // from TMEM, forms P and dS (bf16) and stores them into the swizzled tiles.
 // sP may be null (dQ kernel needs only dS).
+// `half` selects the 64 key columns this thread handles: P and dS need no row-wide
+// reduction in the backward pass (lse and delta are given), so the two softmax
+// warpgroups split every row between them.
 __device__ __forceinline__ void form_p_ds(uint32_t tS, uint32_t tdP, uint8_t* sP, uint8_t* sdS, int row,
-                                          float lse_l2, float delta, float c, float scale, bool diag) {
+                                          float lse_l2, float delta, float c, float scale, bool diag, int half) {
 #pragma unroll 1
-  for (int ch = 0; ch < 4; ++ch) {
+  for (int ch = 2 * half; ch < 2 * half + 2; ++ch) {
     uint32_t s[32], dp[32];
     tmem_ld_32x32(tS + ch * 32, s);
     tmem_ld_32x32(tdP + ch * 32, dp);
@@ -177,8 +180,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     mbar_init(&bar->kv_full, 1);
     mbar_init(&bar->q_full, 1); mbar_init(&bar->q_empty, 1);
     mbar_init(&bar->do_full, 1); mbar_init(&bar->do_empty, 1);
-    mbar_init(&bar->sdp_full, 1); mbar_init(&bar->sdp_empty, 4);
-    mbar_init(&bar->pds_full, 4); mbar_init(&bar->pds_empty, 1);
+    mbar_init(&bar->sdp_full, 1); mbar_init(&bar->sdp_empty, 8);
+    mbar_init(&bar->pds_full, 8); mbar_init(&bar->pds_empty, 1);
     mbar_init(&bar->acc_done, 1);
     bar->abort_flag = 0;
     mbar_fence_init();
@@ -275,6 +278,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     }
   } else {
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;               // softmax warpgroup = column half
     const int row = quarter * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const float c = p.scale * kLog2e;
@@ -291,7 +295,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       ok = mbar_wait(&bar->pds_empty, ph ^ 1, &bar->abort_flag, p.status, 39);
       if (!ok) break;
       tc_fence_after();
-      form_p_ds(tS + lane_off, tdP + lane_off, sP, sdS, row, lse_l2, delta, c, p.scale, p.causal && i == j);
+      form_p_ds(tS + lane_off, tdP + lane_off, sP, sdS, row, lse_l2, delta, c, p.scale, p.causal && i == j, half);
       tc_fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
@@ -301,8 +305,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     if (ok) {
       tc_fence_after();
       const long long t = kv_row0 + row;
-      store_acc_row<D>(tdV + lane_off, p.dv + t * p.dv_row + (long long)hkv * p.dv_head, true);
-      store_acc_row<D>(tdK + lane_off, p.dk + t * p.dk_row + (long long)hkv * p.dk_head, true);
+      if (half == 0) store_acc_row<D>(tdV + lane_off, p.dv + t * p.dv_row + (long long)hkv * p.dv_head, true);
+      else           store_acc_row<D>(tdK + lane_off, p.dk + t * p.dk_row + (long long)hkv * p.dk_head, true);
     }
   }
   tc_fence_before();
@@ -362,8 +366,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       mbar_init(&bar->k_full[s], 1); mbar_init(&bar->k_empty[s], 1);
       mbar_init(&bar->v_full[s], 1); mbar_init(&bar->v_empty[s], 1);
     }
-    mbar_init(&bar->sdp_full, 1); mbar_init(&bar->sdp_empty, 4);
-    mbar_init(&bar->ds_full, 4); mbar_init(&bar->ds_empty, 1);
+    mbar_init(&bar->sdp_full, 1); mbar_init(&bar->sdp_empty, 8);
+    mbar_init(&bar->ds_full, 8); mbar_init(&bar->ds_empty, 1);
     mbar_init(&bar->acc_done, 1);
     bar->abort_flag = 0;
     mbar_fence_init();
@@ -455,6 +459,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     }
   } else {
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;               // softmax warpgroup = column half
     const int row = quarter * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const float c = p.scale * kLog2e;
@@ -468,7 +473,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       ok = mbar_wait(&bar->ds_empty, (jj & 1) ^ 1, &bar->abort_flag, p.status, 59);
       if (!ok) break;
       tc_fence_after();
-      form_p_ds(tS + lane_off, tdP + lane_off, nullptr, sdS, row, lse_l2, delta, c, p.scale, p.causal && jj == i);
+      form_p_ds(tS + lane_off, tdP + lane_off, nullptr, sdS, row, lse_l2, delta, c, p.scale, p.causal && jj == i, half);
       tc_fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
@@ -478,7 +483,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     if (ok) {
       tc_fence_after();
       const long long t = q_row0 + row;
-      store_acc_row<D>(tdQ + lane_off, p.dq + t * p.dq_row + (long long)h * p.dq_head, true);
+      store_acc_row<D / 2>(tdQ + lane_off + half * (D / 2), p.dq + t * p.dq_row + (long long)h * p.dq_head + half * (D / 2),
+                           true);
     }
   }
   tc_fence_before();
