@@ -85,16 +85,16 @@ __device__ __forceinline__ uint4 ld_peer(const void* p) {
 
 // Sums the 16-byte vector at byte offset `off` over all members.  All loads are
 // issued before the first add so that the peers' latencies overlap.
-template <bool BF16>
+template <bool BF16, int NMAX = kMaxPeers>
 __device__ __forceinline__ uint4 reduce_vec(const Team& t, size_t off) {
-  uint4 u[kMaxPeers];
+  uint4 u[NMAX];
 #pragma unroll
-  for (int i = 0; i < kMaxPeers; ++i)
+  for (int i = 0; i < NMAX; ++i)
     if (i < t.n) u[i] = ld_peer(reinterpret_cast<const char*>(t.buf[i]) + off);
   if (BF16) {
     float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
-    for (int i = 0; i < kMaxPeers; ++i) {
+    for (int i = 0; i < NMAX; ++i) {
       if (i < t.n) {
         float2 f;
         f = unpack_bf16x2(u[i].x); a[0] += f.x; a[1] += f.y;
@@ -108,7 +108,7 @@ __device__ __forceinline__ uint4 reduce_vec(const Team& t, size_t off) {
   } else {
     float a0 = 0, a1 = 0, a2 = 0, a3 = 0;
 #pragma unroll
-    for (int i = 0; i < kMaxPeers; ++i) {
+    for (int i = 0; i < NMAX; ++i) {
       if (i < t.n) {
         a0 += __uint_as_float(u[i].x); a1 += __uint_as_float(u[i].y);
         a2 += __uint_as_float(u[i].z); a3 += __uint_as_float(u[i].w);
@@ -132,6 +132,34 @@ __device__ __forceinline__ void copy_vecs(char* dst, const char* src, size_t nve
   for (; v < nvec; v += stride) *reinterpret_cast<uint4*>(dst + (v << 4)) = ld_peer(src + (v << 4));
 }
 
+// store(v, sum) for the vectors v = lo + tid, + stride, ... < hi, where sum is the team-wide
+// sum of the 16-byte vector at byte offset byte_base + 16 v.  U vectors per thread are in
+// flight at once; U shrinks as the team grows so that the loads fit the register file.
+template <bool BF16, int U, int NMAX, typename Store>
+__device__ __forceinline__ void reduce_loop_u(const Team& t, size_t byte_base, size_t lo, size_t hi, size_t tid,
+                                              size_t stride, Store store) {
+  for (size_t v = lo + tid; v < hi; v += U * stride) {
+    uint4 r[U];
+#pragma unroll
+    for (int q = 0; q < U; ++q) {
+      const size_t vq = v + q * stride;
+      if (vq < hi) r[q] = reduce_vec<BF16, NMAX>(t, byte_base + (vq << 4));
+    }
+#pragma unroll
+    for (int q = 0; q < U; ++q) {
+      const size_t vq = v + q * stride;
+      if (vq < hi) store(vq, r[q]);
+    }
+  }
+}
+template <bool BF16, typename Store>
+__device__ __forceinline__ void reduce_loop(const Team& t, size_t byte_base, size_t lo, size_t hi, size_t tid,
+                                            size_t stride, Store store) {
+  if (t.n <= 2) reduce_loop_u<BF16, 8, 2>(t, byte_base, lo, hi, tid, stride, store);
+  else if (t.n <= 4) reduce_loop_u<BF16, 4, 4>(t, byte_base, lo, hi, tid, stride, store);
+  else reduce_loop_u<BF16, 2, 8>(t, byte_base, lo, hi, tid, stride, store);
+}
+
 // ---------------------------------------------------------------------------
 // all-reduce.  Input staged at buf[me][0, bytes); result written to `out`
 // (local).  one_shot: every GPU reads everything; else reduce-scatter into the
@@ -147,8 +175,8 @@ allreduce_kernel(const Team t, char* out, size_t bytes, int one_shot) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   if (!team_barrier(t, 0, &fail)) return;
   if (one_shot) {
-    for (size_t v = tid; v < nvec; v += stride)
-      *reinterpret_cast<uint4*>(out + (v << 4)) = reduce_vec<BF16>(t, v << 4);
+    reduce_loop<BF16>(t, 0, 0, nvec, tid, stride,
+                      [&](size_t v, const uint4& r) { *reinterpret_cast<uint4*>(out + (v << 4)) = r; });
     team_barrier(t, 1, &fail);
     return;
   }
@@ -156,18 +184,10 @@ allreduce_kernel(const Team t, char* out, size_t bytes, int one_shot) {
   const size_t per = (nvec + t.n - 1) / t.n;
   const size_t lo = min(nvec, per * t.me), hi = min(nvec, lo + per);
   char* mine = reinterpret_cast<char*>(t.buf[t.me]);
-  for (size_t v = lo + tid; v < hi; v += 2 * stride) {
-    const size_t v1 = v + stride;
-    const uint4 r0 = reduce_vec<BF16>(t, v << 4);
-    uint4 r1 = make_uint4(0, 0, 0, 0);
-    if (v1 < hi) r1 = reduce_vec<BF16>(t, v1 << 4);
-    *reinterpret_cast<uint4*>(mine + (v << 4)) = r0;
-    *reinterpret_cast<uint4*>(out + (v << 4)) = r0;
-    if (v1 < hi) {
-      *reinterpret_cast<uint4*>(mine + (v1 << 4)) = r1;
-      *reinterpret_cast<uint4*>(out + (v1 << 4)) = r1;
-    }
-  }
+  reduce_loop<BF16>(t, 0, lo, hi, tid, stride, [&](size_t v, const uint4& r) {
+    *reinterpret_cast<uint4*>(mine + (v << 4)) = r;
+    *reinterpret_cast<uint4*>(out + (v << 4)) = r;
+  });
   if (!team_barrier(t, 1, &fail)) return;
   for (int k = 1; k < t.n; ++k) {
     const int i = (t.me + k) % t.n;   // start with a different peer on every GPU
@@ -207,15 +227,47 @@ reducescatter_kernel(const Team t, char* out, size_t bytes) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   if (!team_barrier(t, 0, &fail)) return;
   const size_t base = (size_t)t.me * bytes;
-  for (size_t v = tid; v < nvec; v += 2 * stride) {
-    const size_t v1 = v + stride;
-    const uint4 r0 = reduce_vec<BF16>(t, base + (v << 4));
-    uint4 r1 = make_uint4(0, 0, 0, 0);
-    if (v1 < nvec) r1 = reduce_vec<BF16>(t, base + (v1 << 4));
-    *reinterpret_cast<uint4*>(out + (v << 4)) = r0;
-    if (v1 < nvec) *reinterpret_cast<uint4*>(out + (v1 << 4)) = r1;
-  }
+  reduce_loop<BF16>(t, base, 0, nvec, tid, stride,
+                    [&](size_t v, const uint4& r) { *reinterpret_cast<uint4*>(out + (v << 4)) = r; });
   team_barrier(t, 1, &fail);
+}
+
+template <int U, int NMAX>
+__device__ __forceinline__ void rs_acc_loop(const Team& t, float* acc, size_t base, size_t nvec, size_t tid,
+                                            size_t stride, float scale) {
+  for (size_t v = tid; v < nvec; v += U * stride) {
+    uint4 u[U][NMAX];
+#pragma unroll
+    for (int q = 0; q < U; ++q) {
+      const size_t vq = v + q * stride;
+      if (vq < nvec) {
+#pragma unroll
+        for (int i = 0; i < NMAX; ++i)
+          if (i < t.n) u[q][i] = ld_peer(reinterpret_cast<const char*>(t.buf[i]) + base + (vq << 4));
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < U; ++q) {
+      const size_t vq = v + q * stride;
+      if (vq >= nvec) break;
+      float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int i = 0; i < NMAX; ++i) {
+        if (i < t.n) {
+          float2 f;
+          f = unpack_bf16x2(u[q][i].x); a[0] += f.x; a[1] += f.y;
+          f = unpack_bf16x2(u[q][i].y); a[2] += f.x; a[3] += f.y;
+          f = unpack_bf16x2(u[q][i].z); a[4] += f.x; a[5] += f.y;
+          f = unpack_bf16x2(u[q][i].w); a[6] += f.x; a[7] += f.y;
+        }
+      }
+      float4* o = reinterpret_cast<float4*>(acc + vq * 8);
+      float4 lo = o[0], hi = o[1];
+      lo.x += scale * a[0]; lo.y += scale * a[1]; lo.z += scale * a[2]; lo.w += scale * a[3];
+      hi.x += scale * a[4]; hi.y += scale * a[5]; hi.z += scale * a[6]; hi.w += scale * a[7];
+      o[0] = lo; o[1] = hi;
+    }
+  }
 }
 
 // reduce-scatter of bf16 gradients fused with scale + accumulation into an fp32
@@ -230,28 +282,9 @@ reducescatter_acc_kernel(const Team t, float* acc, size_t bytes, float scale) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   if (!team_barrier(t, 0, &fail)) return;
   const size_t base = (size_t)t.me * bytes;
-  for (size_t v = tid; v < nvec; v += stride) {
-    uint4 u[kMaxPeers];
-#pragma unroll
-    for (int i = 0; i < kMaxPeers; ++i)
-      if (i < t.n) u[i] = ld_peer(reinterpret_cast<const char*>(t.buf[i]) + base + (v << 4));
-    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-    for (int i = 0; i < kMaxPeers; ++i) {
-      if (i < t.n) {
-        float2 f;
-        f = unpack_bf16x2(u[i].x); a[0] += f.x; a[1] += f.y;
-        f = unpack_bf16x2(u[i].y); a[2] += f.x; a[3] += f.y;
-        f = unpack_bf16x2(u[i].z); a[4] += f.x; a[5] += f.y;
-        f = unpack_bf16x2(u[i].w); a[6] += f.x; a[7] += f.y;
-      }
-    }
-    float4* o = reinterpret_cast<float4*>(acc + v * 8);
-    float4 lo = o[0], hi = o[1];
-    lo.x += scale * a[0]; lo.y += scale * a[1]; lo.z += scale * a[2]; lo.w += scale * a[3];
-    hi.x += scale * a[4]; hi.y += scale * a[5]; hi.z += scale * a[6]; hi.w += scale * a[7];
-    o[0] = lo; o[1] = hi;
-  }
+  if (t.n <= 2) rs_acc_loop<8, 2>(t, acc, base, nvec, tid, stride, scale);
+  else if (t.n <= 4) rs_acc_loop<4, 4>(t, acc, base, nvec, tid, stride, scale);
+  else rs_acc_loop<2, 8>(t, acc, base, nvec, tid, stride, scale);
   team_barrier(t, 1, &fail);
 }
 

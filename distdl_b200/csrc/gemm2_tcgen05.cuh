@@ -117,8 +117,12 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 // 32), stored or, with F_ACCUMULATE, added at L2 by a TMA reduction, which spares
 // the read of D.  `map` has box {64 | 32 columns, 32 rows}; rows and columns past
 // the tensor are clipped by the hardware.  `write` = false skips the stores.
+// `add_src[0 .. n_add)`: optional bf16 matrices [rows][add_ld] (local memory) whose rows
+// row0 .. row0 + 31 are added to the tile before it is written (partials of other GPUs).
 __device__ __forceinline__ void epilogue_tma(const Params& q, const CUtensorMap* map, uint32_t taddr, uint8_t* stage_w,
-                                             int lane, int col_tile0, int row0, int tb, bool write) {
+                                             int lane, int col_tile0, int row0, int tb, bool write,
+                                             const __nv_bfloat16* const* add_src = nullptr, int n_add = 0,
+                                             long long add_ld = 0) {
   const bool f32 = (q.flags & gemm::F_OUT_F32) != 0;
   const bool add = (q.flags & gemm::F_ACCUMULATE) != 0;
   const int round_cols = f32 ? 64 : 128;
@@ -147,6 +151,26 @@ __device__ __forceinline__ void epilogue_tma(const Params& q, const CUtensorMap*
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             if (i < nv) r[i] = __float_as_uint(__uint_as_float(r[i]) + __bfloat162float(__ldg(bp + i)));
+        }
+      }
+      if (n_add > 0 && write) {
+        for (int a = 0; a < n_add; ++a) {
+          const __nv_bfloat16* src = add_src[a] + (long long)(row0 + lane) * add_ld + col0;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (col0 + 8 * g < q.N) {
+              const uint4 u = *reinterpret_cast<const uint4*>(src + 8 * g);
+              float2 f;
+              f = unpack_bf16x2(u.x); r[8 * g] = __float_as_uint(__uint_as_float(r[8 * g]) + f.x);
+              r[8 * g + 1] = __float_as_uint(__uint_as_float(r[8 * g + 1]) + f.y);
+              f = unpack_bf16x2(u.y); r[8 * g + 2] = __float_as_uint(__uint_as_float(r[8 * g + 2]) + f.x);
+              r[8 * g + 3] = __float_as_uint(__uint_as_float(r[8 * g + 3]) + f.y);
+              f = unpack_bf16x2(u.z); r[8 * g + 4] = __float_as_uint(__uint_as_float(r[8 * g + 4]) + f.x);
+              r[8 * g + 5] = __float_as_uint(__uint_as_float(r[8 * g + 5]) + f.y);
+              f = unpack_bf16x2(u.w); r[8 * g + 6] = __float_as_uint(__uint_as_float(r[8 * g + 6]) + f.x);
+              r[8 * g + 7] = __float_as_uint(__uint_as_float(r[8 * g + 7]) + f.y);
+            }
+          }
         }
       }
       if (f32) {

@@ -548,6 +548,21 @@ DD_API int dd_ag_gemm(int P, int me, void* const* shards, void* G, const void* w
   return (int)cudaGetLastError();
 }
 
+// 1 when dd_gemm_rs folds the partials inside the GEMM kernel for this geometry (CTA pairs,
+// TMA stores, and a member's row blocks a multiple of the 8-block tile group, so that every
+// CTA meets all tiles of the other members before its own); the completion counter of the
+// reduction then counts the GEMM's CTAs.
+DD_API int dd_gemm_rs_folds(int batch, int s_local) {
+  static const bool on = []() {
+    const char* e = getenv("DISTDL_RS_FOLD");
+    const char* t = getenv("DISTDL_RS_TMA_STORE");
+    return !(e && e[0] == '0') && !(t && t[0] == '0');
+  }();
+  if (!on || !fused_pair_enabled() || s_local % BM) return 0;
+  const long long blocks = (long long)batch * (s_local / BM);
+  return blocks % 8 == 0 ? 1 : 0;
+}
+
 // Launches the GEMM with scatter epilogue, then the reduction.  `slots[i]` =
 // member i's staging slot for source `me`; `staging` = my own staging
 // ([P][batch*s_local][N]); x is the local [batch*P*s_local, K] operand.
@@ -585,6 +600,10 @@ DD_API int dd_gemm_rs(int P, int me, const void* x, long long ldx, const void* w
   int ctas = dd_fused_gemm_ctas();
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   rp.tma_store = 0;
+  rp.fold = 0;
+  rp.done_counter2 = reinterpret_cast<uint32_t*>(done_counter_reduce);
+  rp.done_target2 = done_target_reduce;
+  bool fold = false;
   if (pair) {
     rp.g.group_m = 4;
     static const bool tma_store = []() { const char* e = getenv("DISTDL_RS_TMA_STORE"); return !(e && e[0] == '0'); }();
@@ -592,11 +611,21 @@ DD_API int dd_gemm_rs(int P, int me, const void* x, long long ldx, const void* w
     memset(&om, 0, sizeof(om));
     if (tma_store) {
       const uint64_t rows = (uint64_t)batch * s_local;
+      fold = dd_gemm_rs_folds(batch, s_local) != 0;
       for (int i = 0; i < P; ++i) {
-        r = get_tensor_map_bf16_3d(&om.m[i], slots[i], N, rows, 1, (uint64_t)N * 2, rows * N * 2, 64, 32);
+        // with the fold inside the GEMM the tiles of my own rows go straight to the output
+        void* base = (fold && i == me) ? out : slots[i];
+        r = get_tensor_map_bf16_3d(&om.m[i], base, N, rows, 1, (uint64_t)N * 2, rows * N * 2, 64, 32);
         if (r) return r;
       }
       rp.tma_store = 1;
+      if (fold) {
+        rp.fold = 1;
+        for (int i = 0; i < P; ++i) {
+          rp.my_slot[i] = reinterpret_cast<const __nv_bfloat16*>(staging) + (size_t)i * rows * N;
+          rp.delivered_expect[i] = delivered_expect[i];
+        }
+      }
     }
     r = dd_launch_rs_pair(ta, tb, om, rp, w_mn, ctas, s);
   } else {
@@ -611,6 +640,7 @@ DD_API int dd_gemm_rs(int P, int me, const void* x, long long ldx, const void* w
     r = (int)cudaGetLastError();
   }
   if (r) return r;
+  if (fold) return 0;
   ReduceParams q;
   q.P = P; q.me = me; q.parity = parity;
   q.staging = reinterpret_cast<const __nv_bfloat16*>(staging);

@@ -214,12 +214,55 @@ fused_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       vec_ok = ((p.flags & F_OUT_F32) ? (p.ldd % 4 == 0) : (p.ldd % 8 == 0)) &&
                ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0);
     }
+    // gemm_rs with the fold inside: once this CTA's tiles for the other members are stored
+    // (they come first), it reports "delivered" and, before its first own tile, waits for
+    // the partials of the peers
+    bool delivered_sent = false;
+    const __nv_bfloat16* addends[kMaxPeers];
+    int n_add = 0;
+    auto signal_delivered = [&]() {
+      if constexpr (MODE == 2) {
+        if (fp.tma_store && lane == 0) {
+          tma_store_wait_all();
+          proxy_fence_global();
+        }
+        __threadfence_system();
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (et == 0) {
+          const uint32_t old = atomicAdd(fp.done_counter, 1u);
+          if (old + 1 == fp.done_target) {
+            __threadfence_system();
+            for (int i = 0; i < geo.P; ++i)
+              if (i != geo.me) red_release_sys(fp.pad[i] + PAD_RS_DELIVERED + fp.parity * 8 + fp.writer[geo.me]);
+          }
+        }
+        delivered_sent = true;
+      }
+    };
+    if constexpr (MODE == 2) {
+      if (fp.fold)
+        for (int i = 0; i < geo.P; ++i)
+          if (i != geo.me) addends[n_add++] = fp.my_slot[i];
+    }
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
       int tm, tn, tb;
       gemm::tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn, tb);
       const int o = 2 * tm + (int)rank;
       int owner = 0, lb = 0;
       const int rb = o < row_blocks ? geo.block_of(o, first, owner, lb) : row_blocks;
+      bool own = false;
+      if constexpr (MODE == 2) {
+        own = fp.fold && owner == geo.me && o < row_blocks;
+        if (own && !delivered_sent) {
+          signal_delivered();
+          if (et < geo.P && et != geo.me)
+            wait_counter<true>(fp.pad[geo.me] + PAD_RS_DELIVERED + fp.parity * 8 + fp.writer[et],
+                               fp.delivered_expect[et], &ss->abort_flag, p.status, 221);
+          asm volatile("bar.sync 2, 128;" ::: "memory");
+          ok = ss->abort_flag == 0;
+          if (!ok) break;
+        }
+      }
       ok = mbar_wait(&ss->tmem_full[acc], acc_phase, &ss->abort_flag, p.status, 304);
       if (!ok) break;
       tc_fence_after();
@@ -238,7 +281,7 @@ fused_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (stored) {
         if constexpr (MODE == 2) {
           g2::epilogue_tma(q, &omaps.m[owner], taddr, out_stage + quarter * g2::OUT_WARP_BYTES, lane, tn * g2::BN,
-                           lb * BM + quarter * 32, 0, o < row_blocks);
+                           lb * BM + quarter * 32, 0, o < row_blocks, addends, own ? n_add : 0, (long long)p.N);
         } else {
           g2::epilogue_tma(q, &omaps.m[0], taddr, out_stage + quarter * g2::OUT_WARP_BYTES, lane, tn * g2::BN,
                            rb * BM + quarter * 32, 0, o < row_blocks);
@@ -262,18 +305,21 @@ fused_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if ((p.flags & F_TMA_EPI) && lane == 0) tma_store_wait_all();
     }
     if constexpr (MODE == 2) {
-      if (fp.tma_store && lane == 0) {
-        tma_store_wait_all();
-        proxy_fence_global();
-      }
-      __threadfence_system();
-      asm volatile("bar.sync 2, 128;" ::: "memory");
-      if (et == 0) {
-        const uint32_t old = atomicAdd(fp.done_counter, 1u);
-        if (old + 1 == fp.done_target) {
-          __threadfence_system();
-          for (int i = 0; i < geo.P; ++i)
-            if (i != geo.me) red_release_sys(fp.pad[i] + PAD_RS_DELIVERED + fp.parity * 8 + fp.writer[geo.me]);
+      if (!fp.fold) {
+        signal_delivered();
+      } else {
+        if (!delivered_sent) signal_delivered();      // a CTA without own tiles
+        // all own tiles written: the peers may reuse my staging slots of this parity
+        if (fp.tma_store && lane == 0) tma_store_wait_all();
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (et == 0) {
+          __threadfence();
+          const uint32_t old = atomicAdd(fp.done_counter2, 1u);
+          if (old + 1 == fp.done_target2) {
+            __threadfence_system();
+            for (int i = 0; i < geo.P; ++i)
+              if (i != geo.me) red_release_sys(fp.pad[i] + PAD_RS_CONSUMED + fp.parity * 8 + fp.writer[geo.me]);
+          }
         }
       }
     }

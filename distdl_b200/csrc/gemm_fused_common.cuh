@@ -135,6 +135,14 @@ struct RsParams {
   uint32_t* done_counter;            // local, monotone
   uint32_t done_target;
   int tma_store;                     // pair kernel: write the tiles with TMA stores from shared memory
+  // pair kernel with the fold inside the GEMM: the tiles of this member's own rows add the
+  // partials that the peers delivered (my_slot[i] = local staging slot of source i) and go
+  // straight to the output (omaps.m[me]); no separate reduction kernel.
+  int fold;
+  const __nv_bfloat16* my_slot[kMaxPeers];
+  uint32_t delivered_expect[kMaxPeers];
+  uint32_t* done_counter2;           // local, monotone: CTAs through with their own tiles
+  uint32_t done_target2;
 };
 
 

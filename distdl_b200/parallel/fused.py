@@ -32,6 +32,7 @@ _native.declare("dd_gemm_rs", [c_int, c_int, c_void_p, c_ll, c_void_p, c_int, c_
                                c_int, c_int, c_int, c_int, c_int, _PP, _IP, _UP, _UP, c_void_p, c_uint, c_void_p,
                                c_uint, c_int, c_void_p])
 _native.declare("dd_fused_reduce_ctas", [])
+_native.declare("dd_gemm_rs_folds", [c_int, c_int])
 _native.declare("dd_fused_gemm_ctas", [])
 
 ENABLED = os.environ.get("DISTDL_FUSED", "1") != "0"
@@ -190,9 +191,11 @@ def gemm_rs(x: torch.Tensor, w: torch.Tensor, bias, ranks, batch: int, s_local: 
     delivered = (c_uint * P)(*[(st.rs_delivered[parity][r] + 1) & 0xFFFFFFFF for r in ranks])
     out = torch.empty(batch, s_local, N, dtype=torch.bfloat16, device=x.device)
     st.done[1] += st.sm
-    st.done[2] += st.reduce_ctas
+    # the reduction's completion counter counts the GEMM's CTAs when the fold runs inside the GEMM
+    folds = bool(_native.lib().dd_gemm_rs_folds(batch, s_local))
+    st.done[2] += st.sm if folds else st.reduce_ctas
     w_mn, ldw, _ = _major(w)
-    _native.launch_count += 2
+    _native.launch_count += 1 if folds else 2
     _native.check(_native.lib().dd_gemm_rs(
         P, me, x.data_ptr(), x.stride(0), w.data_ptr(), w_mn, ldw, slots, h.region_ptr(region), out.data_ptr(),
         ptr(bias), batch, s_local, N, K, parity, pads, writers, consumed, delivered, st.counter_ptr(1),
