@@ -194,6 +194,13 @@ def main():
 
     for i in range(args.warmup):
         trainer.step_device(dev_blocks[i])
+        # a bounded device-side wait that ran out leaves every later kernel waiting too:
+        # stop at once instead of running into the caller's time limit
+        st = _native.read_status()
+        if st[0]:
+            sys.stderr.write(f"[bench] rank {rank}: device status {st} after warm-up step {i}; aborting\n")
+            sys.stderr.flush()
+            os._exit(3)
     with ClockSampler(local_rank) as clocks:
         ms_dev, launches = timed(lambda i: trainer.step_device(dev_blocks[args.warmup + i]), args.steps)
     losses = []

@@ -54,6 +54,10 @@ class NativeTransport(GroupTransport):
 
     def allgather_stacked(self, tensor, ranks):
         if self._native_ok(tensor, ranks):
+            # parameter shards in the optimizer's peer-mapped buffer are read in place
+            out = self._collectives().gather_in_place(tensor, ranks)
+            if out is not None:
+                return out
             return self._collectives().all_gather(tensor, ranks)
         return super().allgather_stacked(tensor, ranks)
 

@@ -497,6 +497,23 @@ split_norm_bwd_kernel(const Team t, const __nv_bfloat16* __restrict__ dy, const 
   team_barrier(t, 1, &fail);
 }
 
+// One-sided gather of data that does not change while it is read (ZeRO parameter shards
+// between two optimizer steps): out[i * bytes ...] = src[i][0 .. bytes), sources in peer
+// memory.  No flags and no waits, so the kernel may run on any stream next to other work.
+struct PullDesc {
+  const char* src[kMaxPeers];
+  int n, first;
+};
+__global__ void __launch_bounds__(kThreads) gather_pull_kernel(const PullDesc d, char* out, size_t bytes) {
+  const size_t nvec = bytes >> 4;
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (int k = 0; k < d.n; ++k) {
+    const int i = (d.first + k) % d.n;           // every GPU starts with a different peer
+    copy_vecs(out + (size_t)i * bytes, d.src[i], nvec, tid, stride);
+  }
+}
+
 __global__ void __launch_bounds__(kThreads) barrier_only_kernel(const Team t) {
   __shared__ int fail;
   if (threadIdx.x == 0) fail = 0;
@@ -660,6 +677,33 @@ DD_API int dd_split_norm_bwd(int n, int me, int my_writer, void* const* bufs, vo
   if (rms) split_norm_bwd_kernel<true><<<kCollectiveCtas, kThreads, 0, s>>>(t, DY, X, W, (const float2*)stats, DX, dw, db, rows, d, n_global);
   else split_norm_bwd_kernel<false><<<kCollectiveCtas, kThreads, 0, s>>>(t, DY, X, W, (const float2*)stats, DX, dw, db, rows, d, n_global);
   return (int)cudaGetLastError();
+}
+// srcs[i]: address (as mapped in this process) of member i's block of `bytes` bytes.
+DD_API int dd_gather_pull(int n, int first, void* const* srcs, void* out, size_t bytes, int ctas, void* stream) {
+  if (n < 1 || n > kMaxPeers || bytes % 16 || (reinterpret_cast<uintptr_t>(out) & 15)) return DD_ERR_ALIGN;
+  PullDesc d;
+  d.n = n; d.first = ((first % n) + n) % n;
+  for (int i = 0; i < n; ++i) {
+    if (reinterpret_cast<uintptr_t>(srcs[i]) & 15) return DD_ERR_ALIGN;
+    d.src[i] = reinterpret_cast<const char*>(srcs[i]);
+  }
+  if (ctas <= 0) ctas = 64;
+  const size_t want = (bytes / 16 + kThreads * 8 - 1) / (kThreads * 8);
+  if ((size_t)ctas > want) ctas = (int)(want > 0 ? want : 1);
+  gather_pull_kernel<<<ctas, kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(d, (char*)out, bytes);
+  return (int)cudaGetLastError();
+}
+// The same gather with the copy engines: one asynchronous device-to-device copy per member,
+// no SM is used, so it overlaps compute kernels without taking resources from them.
+DD_API int dd_gather_pull_ce(int n, void* const* srcs, void* out, size_t bytes, void* stream) {
+  if (n < 1 || n > kMaxPeers) return DD_ERR_BAD_ARG;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  for (int i = 0; i < n; ++i) {
+    cudaError_t e = cudaMemcpyAsync(reinterpret_cast<char*>(out) + (size_t)i * bytes, srcs[i], bytes,
+                                    cudaMemcpyDeviceToDevice, s);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
 }
 DD_API int dd_team_barrier(int n, int me, int my_writer, void* const* bufs, void* const* flags, const int* writers,
                            const unsigned* expect, int* steps, void* stream) {

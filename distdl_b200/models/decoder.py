@@ -55,6 +55,7 @@ class DecoderConfig:
     keep_root_gathered: bool = True   # the same for the embedding, final norm and head only (each is used
                                       # once per pass, so re-sharding them between micro-batches buys nothing)
     keep_norms_gathered: bool = True  # and for the norm weights of the blocks (a few KB each)
+    prefetch: bool = True             # gather the next block's ZeRO weights while the current block computes
     init_std: float = 0.02
 
     @property
@@ -175,6 +176,14 @@ class Block(torch.nn.Module):
         x = x + self.attn(self.norm1(x))
         return x + self.mlp(self.norm2(x))
 
+    def prefetch(self):
+        """Starts gathering the ZeRO weight shards of this block's linear layers (a no-op for
+        layers whose weights are already gathered or that are not ZeRO layers)."""
+        for m in (self.attn.qkv, self.attn.out, getattr(self.mlp, "up", None), getattr(self.mlp, "down", None)):
+            fn = getattr(m, "prefetch_weights", None)
+            if fn is not None:
+                fn()
+
 
 class Decoder(torch.nn.Module):
     """``forward(tokens [b_local, seq]) -> hidden [b_local, seq / M, d]``;
@@ -237,11 +246,27 @@ class Decoder(torch.nn.Module):
         if not cfg.rope:
             pos = torch.arange(lo, lo + local.shape[1], device=tokens.device).unsqueeze(0).expand_as(local)
             x = x + self.pos_embed(pos)
-        for blk in self.blocks:
-            if cfg.checkpoint_blocks and self.training:
-                x = torch.utils.checkpoint.checkpoint(blk, x, use_reentrant=False)
+        ckpt = cfg.checkpoint_blocks and self.training
+        pre = cfg.prefetch and cfg.zero and not cfg.keep_gathered
+        n = len(self.blocks)
+        self._backward_phase = False
+
+        def run(x, i):
+            # inside the recomputation of the backward pass the blocks come in reverse order
+            if pre and self._backward_phase and i > 0:
+                self.blocks[i - 1].prefetch()
+            return self.blocks[i](x)
+
+        for i in range(n):
+            if pre and i + 1 < n:
+                self.blocks[i + 1].prefetch()
+            if ckpt:
+                x = torch.utils.checkpoint.checkpoint(run, x, i, use_reentrant=False)
             else:
-                x = blk(x)
+                x = self.blocks[i](x)
+        if pre and ckpt and torch.is_grad_enabled():
+            self.blocks[n - 1].prefetch()          # the first block that the backward pass recomputes
+        self._backward_phase = True
         return self.final_norm(x)
 
     def loss(self, tokens, targets, scale=None):

@@ -115,23 +115,23 @@ def reduce_scatter_grad(rs, full_grad, param, scale_backward=None):
 
 
 class PrefetchStream:
-    """A side stream on which weights are gathered ahead of use.  ``run(fn)``
-    executes ``fn`` on the side stream after everything queued so far on the
-    current stream; ``wait()`` makes the current stream wait for it.  On CPU it
-    degenerates to direct calls."""
+    """Weight prefetch of a layer.  ``run(fn)`` executes ``fn`` (the gathers) on the current
+    stream; gathers that need no handshake with other GPUs (parameter shards read in place
+    from the optimizer's peer-mapped buffer) are moved to the device's side stream inside
+    ``fn`` and are not waited for until ``wait()``, so a prefetch issued early overlaps the
+    compute that follows it.  Everything else stays ordered on the current stream."""
 
     def __init__(self, device):
-        self.stream = None
-        if torch.cuda.is_available() and torch.device(device).type == "cuda":
-            self.stream = torch.cuda.Stream(device=device)
+        self.cuda = torch.cuda.is_available() and torch.device(device).type == "cuda"
 
     def run(self, fn):
-        if self.stream is None:
+        if not self.cuda:
             return fn()
-        self.stream.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(self.stream):
+        from ..utilities import streams
+        with streams.deferred():
             return fn()
 
     def wait(self):
-        if self.stream is not None:
-            torch.cuda.current_stream().wait_stream(self.stream)
+        if self.cuda:
+            from ..utilities import streams
+            streams.join()

@@ -12,12 +12,14 @@ in slices.  Replaces the NCCL calls of the reference's ``nccl_cupy`` backend
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
 
 from .. import _native
 from ..ops._util import stream_ptr
+from ..utilities import streams
 from . import symm
 
 ONE_SHOT_BYTES = 256 * 1024
@@ -101,6 +103,58 @@ def all_gather(x: torch.Tensor, ranks) -> torch.Tensor:
             out[:, done:done + cnt].copy_(tmp[:, :cnt])
         done += cnt
     return out.view(x.dtype).view((P,) + tuple(x.shape))
+
+
+_native.declare("dd_gather_pull", [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p,
+                                   ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p])
+
+
+_native.declare("dd_gather_pull_ce", [ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.c_size_t,
+                                      ctypes.c_void_p])
+# messages of at least this many bytes per member go through the copy engines
+GATHER_CE_BYTES = int(os.environ.get("DISTDL_GATHER_CE_BYTES", str(1 << 20)))
+
+
+def _pull(P, first, srcs, out, nbytes, stream):
+    if nbytes >= GATHER_CE_BYTES:
+        _native.check(_native.lib().dd_gather_pull_ce(P, srcs, out.data_ptr(), nbytes, stream), "dd_gather_pull_ce")
+    else:
+        _native.check(_native.lib().dd_gather_pull(P, first, srcs, out.data_ptr(), nbytes, 0, stream), "dd_gather_pull")
+
+
+def gather_in_place(x: torch.Tensor, ranks):
+    """All-gather of a tensor that lives at the same offset of a registered parameter
+    region on every member (ZeRO shards in the optimizer's flat buffer): the peers'
+    copies are read where they are, without staging copy, flags or waits.  Returns the
+    stacked ``[P, ...]`` result, or ``None`` when ``x`` is not such a tensor.  The
+    caller guarantees that no member writes its shard meanwhile (the optimizer brackets
+    its update with barriers)."""
+    nbytes = x.numel() * x.element_size()
+    if not x.is_contiguous() or nbytes == 0 or nbytes % 16 or x.data_ptr() % 16:
+        return None
+    reg = symm.find_param_region(x.data_ptr(), nbytes)
+    if reg is None:
+        return None
+    ranks = list(ranks)
+    P = len(ranks)
+    off = x.data_ptr() - reg.local_ptr
+    srcs = (ctypes.c_void_p * P)(*[reg.ptrs[r] + off for r in ranks])
+    out = torch.empty((P,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+    first = ranks.index(reg.heap.rank)
+    _native.launch_count += 1
+    side = streams.side_stream(x.device)
+    main = torch.cuda.current_stream(x.device)
+    if side is None or side.cuda_stream == main.cuda_stream:
+        _pull(P, first, srcs, out, nbytes, main.cuda_stream)
+        return out
+    # wait-free copy: runs on the side stream, after what is queued so far (the memory of
+    # `out` may have been in use by earlier kernels of this stream)
+    side.wait_stream(main)
+    _pull(P, first, srcs, out, nbytes, side.cuda_stream)
+    out.record_stream(side)
+    if not streams.is_deferred():
+        main.wait_stream(side)
+    return out
 
 
 def reduce_scatter(x: torch.Tensor, ranks) -> torch.Tensor:

@@ -13,6 +13,7 @@ post-accumulate hooks, so micro-batches are summed in fp32.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -28,22 +29,41 @@ class FlatAdamW:
         self.max_grad_norm = max_grad_norm
         self.step_count = 0
         self._release = getattr(model, "release_gathered", None)
-        params = [(n, p) for n, p in model.named_parameters() if p.requires_grad and p.numel() > 0]
-        decay = [(n, p) for n, p in params if not any(k in n for k in no_decay)]
-        plain = [(n, p) for n, p in params if any(k in n for k in no_decay)]
+        named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        decay = [(n, p) for n, p in named if not any(k in n for k in no_decay)]
+        plain = [(n, p) for n, p in named if any(k in n for k in no_decay)]
         self.groups = []
         ordered = decay + plain
-        if not ordered:
+        multi = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+        # Slot sizes: with identical parameter lists on every process the slots take the
+        # largest local size, so that a parameter sits at the SAME offset everywhere (the
+        # native transport then gathers ZeRO shards by reading the peers' buffers in place).
+        sizes = [p.numel() for _, p in ordered]
+        self.uniform_layout = False
+        if multi and ordered:
+            table = [None] * dist.get_world_size()
+            dist.all_gather_object(table, [(n, p.numel()) for n, p in ordered])
+            if all([n for n, _ in t] == [n for n, _ in table[0]] for t in table):
+                sizes = [max(t[i][1] for t in table) for i in range(len(ordered))]
+                self.uniform_layout = True
+        if not self.uniform_layout:
+            keep = [i for i, (_, p) in enumerate(ordered) if p.numel() > 0]
+            n_dec = sum(1 for i in keep if i < len(decay))
+            ordered = [ordered[i] for i in keep]
+            sizes = [sizes[i] for i in keep]
+            decay = ordered[:n_dec]
+        if not ordered or sum(sizes) == 0:
             self.total = 0
             return
-        device, dtype = ordered[0][1].device, ordered[0][1].dtype
+        ref = next(p for _, p in ordered if p.numel() > 0) if any(p.numel() for _, p in ordered) else ordered[0][1]
+        device, dtype = ref.device, ref.dtype
         offsets, off = [], 0
-        for _, p in ordered:
+        for sz in sizes:
             offsets.append(off)
-            off += (p.numel() + 7) // 8 * 8          # 16-byte alignment of every bf16 view
+            off += (sz + 7) // 8 * 8          # 16-byte alignment of every bf16 view
         self.total = off
         n_decay = offsets[len(decay)] if len(decay) < len(ordered) else off
-        self.param_flat = torch.zeros(off, dtype=dtype, device=device)
+        self.param_flat = self._alloc_params(off, dtype, device, multi)
         self.master = torch.zeros(off, dtype=torch.float32, device=device)
         self.exp_avg = torch.zeros(off, dtype=torch.float32, device=device)
         self.exp_avg_sq = torch.zeros(off, dtype=torch.float32, device=device)
@@ -52,6 +72,8 @@ class FlatAdamW:
         self.names = []
         for (name, p), o in zip(ordered, offsets):
             n = p.numel()
+            if n == 0:
+                continue
             view = self.param_flat[o:o + n].view(p.shape)
             view.copy_(p.data)
             p.data = view
@@ -63,6 +85,34 @@ class FlatAdamW:
         self._norm_sq = torch.zeros(1, dtype=torch.float32, device=device)
         self._clip = torch.ones(1, dtype=torch.float32, device=device)
         self.last_grad_norm = None
+        self._publish()
+
+    def _alloc_params(self, numel, dtype, device, multi):
+        """The flat bf16 parameter buffer; in peer-mapped memory on the native backend."""
+        self._symmetric = False
+        if (multi and self.uniform_layout and device.type == "cuda" and dtype == torch.bfloat16
+                and dist.get_world_size() <= 8 and os.environ.get("DISTDL_SYMM_PARAMS", "1") != "0"):
+            from . import symm
+            if symm.heap_ready():
+                region = symm.SymmetricRegion(symm.heap(), numel * 2)
+                symm.register_param_region(region)
+                self._region = region
+                self._symmetric = True
+                return region.tensor(numel, dtype)
+        return torch.zeros(numel, dtype=dtype, device=device)
+
+    def _publish(self):
+        """After the parameters changed: no process may read a peer's shard in place
+        before every process has finished writing its own."""
+        if self._symmetric:
+            from . import collectives
+            collectives.barrier(list(range(dist.get_world_size())))
+
+    def _quiesce(self):
+        """Before the parameters change: every process has finished reading."""
+        if self._symmetric:
+            from . import collectives
+            collectives.barrier(list(range(dist.get_world_size())))
 
     @staticmethod
     def _make_hook(p):
@@ -101,6 +151,8 @@ class FlatAdamW:
             torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0, out=self._clip)
             clip_ptr = self._clip
         b1, b2 = self.betas
+        if not self.max_grad_norm:
+            self._quiesce()           # (the all-reduce of the gradient norm already orders the processes)
         for start, length, wd in self.groups:
             if length == 0:
                 continue
@@ -108,6 +160,7 @@ class FlatAdamW:
             ops.adamw_step_(self.master[sl], self.exp_avg[sl], self.exp_avg_sq[sl], self.grad[sl],
                             self.param_flat[sl], lr=self.lr, beta1=b1, beta2=b2, eps=self.eps, weight_decay=wd,
                             step=self.step_count, grad_scale_tensor=clip_ptr, grad_scale=grad_scale, zero_grad=True)
+        self._publish()
 
     def zero_grad(self):
         if self.total:
@@ -125,7 +178,9 @@ class FlatAdamW:
             self.master.copy_(sd["master"])
             self.exp_avg.copy_(sd["exp_avg"])
             self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+            self._quiesce()
             self.param_flat.copy_(self.master)
+            self._publish()
 
 
 def cosine_lr(step, base_lr, warmup, total, min_ratio=0.1):

@@ -131,6 +131,57 @@ class SymmetricHeap:
                 self.steps_done[r] += steps
 
 
+class SymmetricRegion:
+    """A separately allocated buffer of the same size on every process, mapped into all
+    of them (``ptrs[rank]`` = address of that rank's copy as seen from here)."""
+
+    def __init__(self, heap: "SymmetricHeap", nbytes: int):
+        lib = _native.lib()
+        sizes = [None] * heap.world
+        dist.all_gather_object(sizes, int(nbytes))
+        self.nbytes = (max(sizes) + 255) // 256 * 256
+        self.heap = heap
+        self._local = c_void_p()
+        _native.check(lib.dd_symm_alloc(self.nbytes, ctypes.byref(self._local)), "dd_symm_alloc")
+        hb = ctypes.create_string_buffer(64)
+        _native.check(lib.dd_ipc_get_handle(self._local, hb), "dd_ipc_get_handle")
+        handles = [None] * heap.world
+        dist.all_gather_object(handles, bytes(hb.raw))
+        self.ptrs = []
+        for r, hnd in enumerate(handles):
+            if r == heap.rank:
+                self.ptrs.append(self._local.value)
+                continue
+            p = c_void_p()
+            _native.check(lib.dd_ipc_open_handle(hnd, ctypes.byref(p)), "dd_ipc_open_handle")
+            self.ptrs.append(p.value)
+        self.local_ptr = self._local.value
+        dist.barrier()
+
+    def tensor(self, numel: int, dtype) -> torch.Tensor:
+        """Tensor view of the head of the local copy."""
+        return _wrap_device_pointer(self.local_ptr, numel, dtype, self.heap.device)
+
+    def contains(self, ptr: int, nbytes: int) -> bool:
+        return self.local_ptr <= ptr and ptr + nbytes <= self.local_ptr + self.nbytes
+
+
+_param_regions = []
+
+
+def register_param_region(region: SymmetricRegion):
+    """Declares ``region`` to hold parameters at the same offsets on every process: the
+    native transport then gathers such a parameter by reading the peers' copies in place."""
+    _param_regions.append(region)
+
+
+def find_param_region(ptr: int, nbytes: int):
+    for reg in _param_regions:
+        if reg.contains(ptr, nbytes):
+            return reg
+    return None
+
+
 class _DevicePointer:
     """Minimal object exposing ``__cuda_array_interface__`` for a raw pointer."""
 

@@ -163,6 +163,31 @@ def check_split_norm():
             assert err < 2e-2, ("split_norm", rms, what, err)
 
 
+def check_symmetric_params():
+    """ZeRO shards gathered in place from the optimizer's peer-mapped buffer give the same
+    training trajectory as the staged all-gather."""
+    import os
+    from distdl_b200 import models
+    from distdl_b200.parallel import SyntheticTokens, Trainer
+    world = dist.get_world_size()
+    losses = {}
+    for mode in ("0", "1"):
+        os.environ["DISTDL_SYMM_PARAMS"] = mode
+        torch.manual_seed(0)
+        cfg = models.llama_tiny(d_model=256, n_heads=4, n_kv_heads=2, ffn_dim=512, max_seq=128, vocab_size=1024)
+        layout = models.ParallelLayout(world, 1)
+        model = models.Decoder(cfg, layout)
+        trainer = Trainer(model, global_tokens_per_step=2 * world * 128, micro_batch=1, lr=2e-3, warmup_steps=0)
+        assert trainer.opt._symmetric == (mode == "1"), "unexpected parameter placement"
+        data = SyntheticTokens(2, 128, cfg.vocab_size, dp_index=layout.dp_index, seed=3)
+        block = data.next()
+        losses[mode] = [trainer.step(block).item() for _ in range(4)]
+    os.environ.pop("DISTDL_SYMM_PARAMS", None)
+    for a, b in zip(losses["0"], losses["1"]):
+        assert abs(a - b) < 1e-3 * max(1.0, abs(a)), losses
+    assert losses["1"][-1] < losses["1"][0], losses
+
+
 def main():
     import distdl_b200
     from distdl_b200.backends.common import world as dworld
@@ -175,6 +200,7 @@ def main():
         check_primitives_native()
         check_zero_grad_accumulate()
         check_split_norm()
+        check_symmetric_params()
     if what in ("fused", "all"):
         from multi_gpu_fused import check_fused
         check_fused()

@@ -51,6 +51,7 @@ def body_expert_parallel(rank, world):
     tok = torch.randint(0, 200, (2, 33), generator=g)
     loss = m.loss(tok[:, :-1], tok[:, 1:])
     loss.backward()
+    m.release_gathered()          # parameters kept gathered for the step deliver their gradients now
     assert math.isfinite(loss.item())
     for n, p in m.named_parameters():
         if p.numel():
