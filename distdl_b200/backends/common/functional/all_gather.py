@@ -21,6 +21,13 @@ class AllGatherFunction(TransportBound, torch.autograd.Function):
         ctx.axes = axes
         ctx.scale_backward = scale_backward
         ctx.input_tensor_structure = input_tensor_structure
+        # A parameter whose gradient is accumulated elsewhere (unsharded accumulator of the
+        # optimizer) produces no gradient for the gathered tensor: its adjoint is then skipped
+        # instead of reduce-scattering zeros.  Every member of the team sets the accumulator
+        # up or none does, so the decision is the same everywhere.
+        ctx.skip_without_grad = getattr(input, "full_grad_view", None) is not None
+        ctx.set_materialize_grads(False)
+        ctx.out_meta = None
         if not P_allgather.active:
             return input.clone()
         axis = int(axes[0])
@@ -49,12 +56,18 @@ class AllGatherFunction(TransportBound, torch.autograd.Function):
             parts = cls.transport().allgather(input.detach(), list(P_allgather.ranks), shapes)
             out = torch.cat(parts, dim=axis)
         out.requires_grad_(bool(output_tensor_structure.requires_grad) and out.is_floating_point())
+        ctx.out_meta = (tuple(out.shape), out.dtype, out.device)
         return out
 
     @staticmethod
     def backward(ctx, grad_output):
         cls = ctx._forward_cls
         P = ctx.P_allgather
+        if grad_output is None:
+            if ctx.skip_without_grad or not P.active or ctx.out_meta is None:
+                return None, None, None, None, None, None
+            shape, dtype, device = ctx.out_meta
+            grad_output = torch.zeros(shape, dtype=dtype, device=device)
         if not P.active:
             return grad_output.clone(), None, None, None, None, None
         axis = int(ctx.axes[0])

@@ -514,6 +514,43 @@ __global__ void __launch_bounds__(kThreads) gather_pull_kernel(const PullDesc d,
   }
 }
 
+// acc[i] += scale * sum_k src[k][i] over fp32 vectors that do not change while they are
+// read (the unsharded gradient accumulators of a step, between two barriers): the peers'
+// slices are read in place, no staging, no flags.
+struct PullDescF32 {
+  const float4* src[kMaxPeers];
+  int n;
+};
+__global__ void __launch_bounds__(256) rs_pull_f32_kernel(const PullDescF32 d, float4* acc, size_t nvec, float scale) {
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t v = tid; v < nvec; v += 2 * stride) {
+    const size_t v1 = v + stride;
+    uint4 u[2][kMaxPeers];
+#pragma unroll
+    for (int k = 0; k < kMaxPeers; ++k)
+      if (k < d.n) {
+        u[0][k] = ld_peer(d.src[k] + v);
+        if (v1 < nvec) u[1][k] = ld_peer(d.src[k] + v1);
+      }
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const size_t vq = q == 0 ? v : v1;
+      if (vq >= nvec) break;
+      float4 a = acc[vq];
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+      for (int k = 0; k < kMaxPeers; ++k)
+        if (k < d.n) {
+          s0 += __uint_as_float(u[q][k].x); s1 += __uint_as_float(u[q][k].y);
+          s2 += __uint_as_float(u[q][k].z); s3 += __uint_as_float(u[q][k].w);
+        }
+      a.x += scale * s0; a.y += scale * s1; a.z += scale * s2; a.w += scale * s3;
+      acc[vq] = a;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads) barrier_only_kernel(const Team t) {
   __shared__ int fail;
   if (threadIdx.x == 0) fail = 0;
@@ -704,6 +741,22 @@ DD_API int dd_gather_pull_ce(int n, void* const* srcs, void* out, size_t bytes, 
     if (e != cudaSuccess) return (int)e;
   }
   return 0;
+}
+DD_API int dd_rs_pull_f32(int n, void* const* srcs, float* acc, size_t count, float scale, void* stream) {
+  if (n < 1 || n > kMaxPeers || count % 4 || (reinterpret_cast<uintptr_t>(acc) & 15)) return DD_ERR_ALIGN;
+  PullDescF32 d;
+  d.n = n;
+  for (int i = 0; i < n; ++i) {
+    if (reinterpret_cast<uintptr_t>(srcs[i]) & 15) return DD_ERR_ALIGN;
+    d.src[i] = reinterpret_cast<const float4*>(srcs[i]);
+  }
+  const size_t nvec = count / 4;
+  if (nvec == 0) return 0;
+  size_t ctas = (nvec + 256 * 2 - 1) / (256 * 2);
+  if (ctas > 148 * 4) ctas = 148 * 4;
+  rs_pull_f32_kernel<<<(int)ctas, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(d, reinterpret_cast<float4*>(acc),
+                                                                                  nvec, scale);
+  return (int)cudaGetLastError();
 }
 DD_API int dd_team_barrier(int n, int me, int my_writer, void* const* bufs, void* const* flags, const int* writers,
                            const unsigned* expect, int* steps, void* stream) {

@@ -89,17 +89,28 @@ def deliver_grad(param, g):
 
 
 def direct_main_grad(param, gather, shape):
-    """fp32 gradient accumulator of ``param`` viewed with ``shape``, when the
-    all-gather ``gather`` of that parameter is the identity (one worker along the
-    gathered partition dimension) and the optimizer attached an accumulator.  The
-    weight-gradient GEMM then accumulates into it directly; otherwise None."""
+    """An fp32 gradient buffer, viewed with the gathered ``shape``, into which the
+    weight-gradient GEMM of a ZeRO layer may accumulate directly, or None.
+
+    * the all-gather ``gather`` of ``param`` is the identity (one worker along the
+      gathered dimension): the optimizer's accumulator of the shard itself;
+    * otherwise, when the optimizer set one up (``param.full_grad_view``): the
+      UNSHARDED accumulator of this step, which the optimizer reduce-scatters once,
+      at the step, instead of after every micro-batch.
+    Autograd then sees no gradient for the gathered weight, so the per-micro-batch
+    reduce-scatter adjoint of the all-gather does not run."""
     acc = getattr(param, "main_grad_view", None)
     if acc is None or not param.is_cuda or os.environ.get("DISTDL_DIRECT_MAIN_GRAD", "1") == "0":
         return None
-    axis = gather.axes_all_gather[0]
-    if int(gather.P_x.shape[axis]) != 1 or gather.scale_backward is not None:
+    if gather.scale_backward is not None:
         return None
-    return acc.view(shape)
+    axis = gather.axes_all_gather[0]
+    if int(gather.P_x.shape[axis]) == 1:
+        return acc.view(shape)
+    full = getattr(param, "full_grad_view", None)
+    if full is not None and full.numel() == int(np.prod(shape)):
+        return full.view(shape)
+    return None
 
 
 def reduce_scatter_grad(rs, full_grad, param, scale_backward=None):

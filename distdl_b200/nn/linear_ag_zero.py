@@ -72,6 +72,8 @@ class DistributedLinearAllGatherZero(Module):
         wshape[0] = int(compute_subshape(D, P_weight.index[0], [in_features])[0])
         wshape[-2] = self.out_features_local
         self.weight = torch.nn.Parameter(torch.empty(tuple(wshape), **kw))
+        # lets an optimizer find the all-gather of this ZeRO shard (team, gathered layout)
+        self.weight.zero_gather = self.allgather_weight
         if bias:
             bshape = [1] * dim
             bshape[-2] = int(compute_subshape(D, P_weight.index[0], [self.out_features_local])[0])

@@ -71,6 +71,8 @@ class DistributedLinearReduceScatterZero(Module):
         wshape[-1] = _local_in(in_features, M, int(P_x.index[-1]), num_heads)
         self.in_features_local = wshape[-1]
         self.weight = torch.nn.Parameter(torch.empty(tuple(wshape), **kw))
+        # lets an optimizer find the all-gather of this ZeRO shard (team, gathered layout)
+        self.weight.zero_gather = self.allgather_weight
         if bias and self.P_bias.active:
             self.allgather_bias = AllGather(self.P_bias, axes_all_gather=(0,), scale_backward=scale_backward)
             self.reduce_scatter_bias = ReduceScatter(self.P_bias, axes_reduce_scatter=(0,))

@@ -85,6 +85,7 @@ class FlatAdamW:
         self._norm_sq = torch.zeros(1, dtype=torch.float32, device=device)
         self._clip = torch.ones(1, dtype=torch.float32, device=device)
         self.last_grad_norm = None
+        self._setup_full_grads(ordered)
         self._publish()
 
     def _alloc_params(self, numel, dtype, device, multi):
@@ -100,6 +101,73 @@ class FlatAdamW:
                 self._symmetric = True
                 return region.tensor(numel, dtype)
         return torch.zeros(numel, dtype=dtype, device=device)
+
+    def _setup_full_grads(self, ordered):
+        """Unsharded fp32 gradient accumulators for the ZeRO weight matrices (peer-mapped):
+        the weight-gradient GEMMs of all micro-batches add into them and ``step()``
+        reduce-scatters them once, each worker reading its slice of every peer's
+        accumulator in place, instead of one reduce-scatter per layer and micro-batch."""
+        self._full = []
+        self._full_region = None
+        if not self._symmetric or os.environ.get("DISTDL_FULL_GRADS", "1") == "0":
+            return
+        plan, off = [], 0
+        for _, p in ordered:
+            gather = getattr(p, "zero_gather", None)
+            if gather is None or p.numel() == 0 or p.numel() % 8 or not hasattr(p, "main_grad_view"):
+                continue
+            axis = gather.axes_all_gather[0]
+            if int(gather.P_x.shape[axis]) <= 1 or gather.scale_backward is not None or not gather.P_x.active:
+                continue
+            team = tuple(int(r) for r in gather.P_x.create_allreduction_partition(gather.axes_all_gather).ranks)
+            if len(team) <= 1 or len(team) > 8:
+                continue
+            plan.append((p, off, p.numel(), team, team.index(dist.get_rank())))
+            off += len(team) * p.numel()
+        # the allocation is collective: every process takes part as soon as one needs it, and the
+        # slot layout must agree within every team (same model structure everywhere)
+        needs = [None] * dist.get_world_size()
+        dist.all_gather_object(needs, [(n, len(t)) for _, _, n, t, _ in plan])
+        if not any(needs):
+            return
+        if any(x != needs[0] for x in needs):
+            return                      # differing layouts: keep the per-micro-batch reduce-scatter
+        from . import symm
+        region = symm.SymmetricRegion(symm.heap(), max(off, 4) * 4)
+        self._full_region = region
+        self._full_flat = region.tensor(off, torch.float32)
+        self._full_flat.zero_()
+        for p, o, n, team, me in plan:
+            p.full_grad_view = self._full_flat[o:o + len(team) * n]
+            self._full.append((p, o, n, team, me))
+
+    def _reduce_full_grads(self):
+        if not self._full:
+            return
+        import ctypes
+        from . import collectives
+        from .. import _native
+        everyone = list(range(dist.get_world_size()))
+        collectives.barrier(everyone)                  # all accumulators of this step are complete
+        lib = _native.lib()
+        reg = self._full_region
+        stream = stream_ptr()
+        for p, o, n, team, me in self._full:
+            srcs = (ctypes.c_void_p * len(team))(*[reg.ptrs[r] + 4 * (o + me * n) for r in team])
+            _native.launch_count += 1
+            _native.check(lib.dd_rs_pull_f32(len(team), srcs, p.main_grad_view.data_ptr(), n, 1.0, stream),
+                          "dd_rs_pull_f32")
+        collectives.barrier(everyone)                  # nobody reads my accumulators any more
+        self._full_flat.zero_()
+
+    def reduce_gradients(self):
+        """Brings every gradient of this step into the sharded fp32 accumulator: flushes the
+        parameters that the model keeps gathered and reduce-scatters the unsharded
+        accumulators.  ``step()`` calls it; collective over all processes."""
+        if self._release is not None:
+            self._release()
+        if self.total:
+            self._reduce_full_grads()
 
     def _publish(self):
         """After the parameters changed: no process may read a peer's shard in place
@@ -133,8 +201,7 @@ class FlatAdamW:
         over all workers and the clipping coefficient stays on the device.
         A model that keeps gathered ZeRO parameters across micro-batches
         (``release_gathered``) is asked to flush their gradients first."""
-        if self._release is not None:
-            self._release()
+        self.reduce_gradients()
         if self.total == 0:
             if self.max_grad_norm and dist.is_initialized() and dist.get_world_size() > 1:
                 dist.all_reduce(torch.zeros(1, device="cuda" if torch.cuda.is_available() else "cpu"))
@@ -165,6 +232,8 @@ class FlatAdamW:
     def zero_grad(self):
         if self.total:
             self.grad.zero_()
+            if getattr(self, "_full", None):
+                self._full_flat.zero_()
 
     # ------------------------------------------------------------ checkpoints
     def state_dict(self):

@@ -98,29 +98,37 @@ def check_primitives_native():
 
 
 def check_zero_grad_accumulate():
-    """ZeRO weight gradients: reduce-scatter fused with scale + fp32 accumulation into the
-    optimizer's buffer must equal the unfused path (bf16 reduce-scatter, then cast + add)."""
+    """ZeRO weight gradients on the fast paths must equal the plain path (bf16 reduce-scatter
+    by autograd): (1) unsharded fp32 accumulators filled by the weight-gradient GEMMs and
+    reduce-scattered once, in place; (2) the reduce-scatter fused with scale + fp32
+    accumulation after every micro-batch."""
+    import os
     import distdl_b200
     from distdl_b200.nn import DistributedLinearAllGatherZero
     from distdl_b200.parallel import FlatAdamW
     world, rank = dist.get_world_size(), dist.get_rank()
     dev = torch.device("cuda", torch.cuda.current_device())
     P = distdl_b200.backends.backend.Partition().create_cartesian_topology_partition([world, 1, 1])
-    torch.manual_seed(5)
-    a = DistributedLinearAllGatherZero(P, 256, 512, bias=False, dtype=torch.bfloat16)
-    b = DistributedLinearAllGatherZero(P, 256, 512, bias=False, dtype=torch.bfloat16)
-    b.load_state_dict(a.state_dict())
-    opt = FlatAdamW(a, max_grad_norm=None)
-    torch.manual_seed(100 + rank)
-    for _ in range(2):                                   # two micro-batches accumulate
-        x = torch.randn(4, 64, 256, device=dev, dtype=torch.bfloat16)
-        a(x).float().pow(2).sum().backward()
-        b(x).float().pow(2).sum().backward()
-    assert a.weight.grad is None                          # went straight into the fp32 accumulator
-    ref = b.weight.grad.float().reshape(-1)
-    got = a.weight.main_grad_view
-    err = (got - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
-    assert err < 2e-2, err
+    for full in ("1", "0"):
+        os.environ["DISTDL_FULL_GRADS"] = full
+        torch.manual_seed(5)
+        a = DistributedLinearAllGatherZero(P, 256, 512, bias=False, dtype=torch.bfloat16)
+        b = DistributedLinearAllGatherZero(P, 256, 512, bias=False, dtype=torch.bfloat16)
+        b.load_state_dict(a.state_dict())
+        opt = FlatAdamW(a, max_grad_norm=None)
+        assert bool(opt._full) == (full == "1")
+        torch.manual_seed(100 + rank)
+        for _ in range(2):                                   # two micro-batches accumulate
+            x = torch.randn(4, 64, 256, device=dev, dtype=torch.bfloat16)
+            a(x).float().pow(2).sum().backward()
+            b(x).float().pow(2).sum().backward()
+        opt.reduce_gradients()
+        assert a.weight.grad is None                          # never materialised as a bf16 gradient
+        ref = b.weight.grad.float().reshape(-1)
+        got = a.weight.main_grad_view
+        err = (got - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+        assert err < 2e-2, (full, err)
+    os.environ.pop("DISTDL_FULL_GRADS", None)
 
 
 def check_split_norm():
