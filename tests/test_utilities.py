@@ -1,0 +1,122 @@
+"""Utilities that need no process group: balanced splits, intersections, index helpers, dtype
+tables, growable buffers and the halo arithmetic of sliding-window layers (golden values of a
+4-worker pooling case)."""
+import numpy as np
+import pytest
+import torch
+
+from distdl_b200.backends.common.buffer import BufferManager, ExpandableBuffer
+from distdl_b200.nn.mixins.halo_mixin import HaloMixin
+from distdl_b200.nn.mixins.pooling_mixin import PoolingMixin
+from distdl_b200.utilities import slicing
+from distdl_b200.utilities.tensor_decomposition import (compute_subtensor_intersection_slice,
+                                                        compute_subtensor_shapes_balanced,
+                                                        compute_subtensor_start_indices,
+                                                        compute_subtensor_stop_indices)
+from distdl_b200.utilities.torch import TensorStructure, zero_volume_tensor
+
+
+def test_balanced_split_rule():
+    # n over P workers: n // P each, the first n % P get one more
+    shapes = [int(slicing.compute_subshape([4], [i], [10])[0]) for i in range(4)]
+    assert shapes == [3, 3, 2, 2]
+    starts = [int(slicing.compute_start_index([4], [i], [10])[0]) for i in range(4)]
+    stops = [int(slicing.compute_stop_index([4], [i], [10])[0]) for i in range(4)]
+    assert starts == [0, 3, 6, 8] and stops == [3, 6, 8, 10]
+    assert list(slicing.compute_subshape([2, 3], [1, 2], [7, 8])) == [3, 2]
+    assert list(slicing.compute_subshape_along_axis([4], [1], [10, 5], 0)) == [3, 5]
+
+
+def test_partition_intersection_and_slices():
+    # rows split over 2 workers vs columns split over 2 workers of a [4, 6] tensor
+    sl = slicing.compute_partition_intersection([2, 1], [0, 0], [1, 2], [0, 1], [4, 6])
+    assert sl is not None
+    assert list(slicing.compute_nd_slice_shape(sl)) == [2, 3]
+    assert slicing.compute_nd_slice_volume(sl) == 6
+    lo, hi, extent = slicing.compute_intersection(np.array([0]), np.array([2]), np.array([2]), np.array([4]))
+    assert extent.tolist() == [0]                            # the ranges only touch
+    lo, hi, extent = slicing.compute_intersection(np.array([0, 1]), np.array([4, 5]), np.array([2, 0]), np.array([6, 3]))
+    assert lo.tolist() == [2, 1] and hi.tolist() == [4, 3] and extent.tolist() == [2, 2]
+    assert slicing.assemble_slices([1, 2], [3, 5]) == (slice(1, 3, None), slice(2, 5, None))
+
+
+def test_worker_layout_and_range_index():
+    lay = slicing.worker_layout([2, 3])
+    assert lay.shape == (2, 3) and lay.reshape(-1).tolist() == list(range(6))
+    idx = list(slicing.range_index([2, 2]))
+    assert [tuple(i) for i in idx] == [(0, 0), (0, 1), (1, 0), (1, 1)]
+
+
+def test_tensor_decomposition_tables():
+    ts = TensorStructure()
+    ts.shape = torch.Size([7, 5])
+    shapes = compute_subtensor_shapes_balanced(ts, [3, 2])
+    assert shapes.shape[:2] == (3, 2)
+    assert shapes[0, 0].tolist() == [3, 3] and shapes[2, 1].tolist() == [2, 2]
+    starts = compute_subtensor_start_indices(shapes)
+    stops = compute_subtensor_stop_indices(shapes)
+    assert starts[1, 1].tolist() == [3, 3] and stops[2, 1].tolist() == [7, 5]
+    sl = compute_subtensor_intersection_slice(starts[0, 0], stops[0, 0], np.array([2, 1]), np.array([5, 4]))
+    assert sl == (slice(2, 3, None), slice(1, 3, None))
+
+
+def test_zero_volume_and_structure():
+    z = zero_volume_tensor()
+    assert z.numel() == 0
+    zb = zero_volume_tensor(5)
+    assert zb.shape[0] == 5 and zb.numel() == 0
+    a = TensorStructure(torch.zeros(2, 3, requires_grad=True))
+    b = TensorStructure(torch.zeros(2, 3, requires_grad=True))
+    assert a == b and a.shape == torch.Size([2, 3]) and a.requires_grad
+    assert a != TensorStructure(torch.zeros(2, 4))
+
+
+def test_expandable_buffer_keeps_contents_and_views():
+    buf = ExpandableBuffer(torch.float32, 4)
+    v = buf.get_view((2, 2))
+    v.copy_(torch.arange(4.).view(2, 2))
+    big = buf.get_view((3, 4))                     # larger than the capacity: reallocates
+    assert buf.capacity >= 12 and big.shape == (3, 4)
+    assert buf.get_view((2, 2)).reshape(-1).tolist() == [0., 1., 2., 3.]   # contents and view survive
+    assert buf.get_view((2, 2)).data_ptr() == buf.raw_buffer.data_ptr()
+
+
+def test_buffer_manager_shares_buffers_between_requests():
+    bm = BufferManager()
+    a = bm.request_buffers(2, torch.float32)
+    b = bm.request_buffers(3, torch.float32)
+    assert a[0] is b[0] and a[1] is b[1] and len(b) == 3
+    c = bm.request_buffers(1, torch.float64)
+    assert c[0] is not a[0] and c[0].dtype == torch.float64
+
+
+class _Pool(HaloMixin, PoolingMixin):
+    pass
+
+
+@pytest.mark.parametrize("index,halo,send,needed", [
+    (0, [[0, 0], [0, 0], [0, 1]], [[0, 0], [0, 0], [0, 0]], [[0, 1], [0, 1], [0, 4]]),
+    (1, [[0, 0], [0, 0], [0, 0]], [[0, 0], [0, 0], [1, 0]], [[0, 1], [0, 1], [1, 3]]),
+    (2, [[0, 0], [0, 0], [0, 0]], [[0, 0], [0, 0], [0, 0]], [[0, 1], [0, 1], [0, 2]]),
+    (3, [[0, 0], [0, 0], [0, 0]], [[0, 0], [0, 0], [0, 0]], [[0, 1], [0, 1], [0, 2]])])
+def test_halo_arithmetic_of_strided_pooling(index, halo, send, needed):
+    # a length-10 signal over 4 workers (3, 3, 2, 2), window 2, stride 2: worker 0's last
+    # window needs one entry of worker 1, whose own first entry is then not needed locally
+    layer = _Pool()
+    h, r, s, n = layer._compute_exchange_info(np.array([1, 1, 10]), np.array([2]), np.array([2]), np.array([0]),
+                                              np.array([1]), True, [1, 1, 4], [0, 0, index])
+    assert np.array_equal(h, np.array(halo))
+    assert np.array_equal(r, np.array(halo))
+    assert np.array_equal(s, np.array(send))
+    assert np.array_equal(n, np.array(needed))
+    assert layer._compute_exchange_info(np.array([1, 1, 10]), np.array([2]), np.array([2]), np.array([0]),
+                                        np.array([1]), False, [1, 1, 4], [0, 0, index]) == (None, None, None, None)
+
+
+def test_dtype_tables():
+    from distdl_b200.utilities import dtype as dt
+    assert dt.torch_to_numpy_dtype_dict[torch.float32] == np.float32
+    assert dt.numpy_to_torch_dtype_dict[np.dtype(np.float64)] == torch.float64
+    assert torch.bfloat16 in dt.torch_to_intID_dtype_dict
+    back = dt.intID_to_torch_dtype_dict[dt.torch_to_intID_dtype_dict[torch.bfloat16]]
+    assert back == torch.bfloat16
