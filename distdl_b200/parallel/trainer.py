@@ -2,6 +2,9 @@
 gradient accumulation, fused optimizer step, device-side loss."""
 from __future__ import annotations
 
+import json
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -21,8 +24,9 @@ class Trainer:
 
     def __init__(self, model, global_tokens_per_step: int, micro_batch: int = 1, lr: float = 3e-4,
                  weight_decay: float = 0.1, max_grad_norm: float = 1.0, warmup_steps: int = 10,
-                 total_steps: int = 1000, device=None):
+                 total_steps: int = 1000, device=None, metrics=None):
         self.model = model
+        self.metrics = metrics          # a parallel.metrics.MetricsSink, or None
         self.micro_batch = micro_batch
         self.global_tokens = global_tokens_per_step
         self.opt = FlatAdamW(model, lr=lr, weight_decay=weight_decay, max_grad_norm=max_grad_norm)
@@ -54,10 +58,60 @@ class Trainer:
         self.steps_done += 1
         if dist.is_initialized() and dist.get_world_size() > 1:
             dist.all_reduce(total)
+        if self.metrics is not None:
+            self.metrics.step(self.steps_done, total, self.global_tokens, lr=self.opt.lr,
+                              grad_norm=self.opt.last_grad_norm, device=tokens.device)
         return total
 
     def step(self, tokens_host: torch.Tensor) -> torch.Tensor:
         return self.step_device(self.stage(tokens_host))
+
+    # ------------------------------------------------------------ checkpoints
+    def save_checkpoint(self, directory: str, extra: dict = None):
+        """Writes ``rank<r>.pt`` (this worker's shards: model ``state_dict``, fp32 master
+        weights and moments, step counters, RNG states) and, on rank 0, ``manifest.json``
+        (world size, step, parallel layout and model configuration when the model has
+        them).  Collective: every worker calls it; returns after all files are written."""
+        os.makedirs(directory, exist_ok=True)
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        state = {"model": self.model.state_dict(), "optimizer": self.opt.state_dict(), "steps_done": self.steps_done,
+                 "rng_cpu": torch.get_rng_state(),
+                 "rng_cuda": torch.cuda.get_rng_state() if torch.cuda.is_available() else None}
+        torch.save(state, os.path.join(directory, f"rank{rank}.pt"))
+        if rank == 0:
+            layout = getattr(self.model, "layout", None)
+            cfg = getattr(self.model, "cfg", None)
+            manifest = {"world_size": world, "steps_done": self.steps_done,
+                        "layout": None if layout is None else {"dp": layout.dp, "tp": layout.tp},
+                        "model": None if cfg is None else {k: (str(v) if isinstance(v, torch.dtype) else v)
+                                                           for k, v in vars(cfg).items()},
+                        "files": [f"rank{r}.pt" for r in range(world)], "extra": extra or {}}
+            with open(os.path.join(directory, "manifest.json"), "w") as fh:
+                json.dump(manifest, fh, indent=1)
+        if dist.is_initialized() and world > 1:
+            dist.barrier()
+
+    def load_checkpoint(self, directory: str) -> dict:
+        """Restores what :meth:`save_checkpoint` wrote on the same worker grid; returns the
+        manifest.  (To move between grids, save the model with ``collect_state=True``
+        layers and load that serial ``state_dict``.)"""
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        with open(os.path.join(directory, "manifest.json")) as fh:
+            manifest = json.load(fh)
+        if manifest["world_size"] != world:
+            raise ValueError(f"checkpoint was written by {manifest['world_size']} workers, this job has {world}")
+        state = torch.load(os.path.join(directory, f"rank{rank}.pt"), map_location=self.device, weights_only=False)
+        self.model.load_state_dict(state["model"])
+        self.opt.load_state_dict(state["optimizer"])
+        self.steps_done = int(state["steps_done"])
+        torch.set_rng_state(state["rng_cpu"].cpu())
+        if state.get("rng_cuda") is not None and torch.cuda.is_available():
+            torch.cuda.set_rng_state(state["rng_cuda"].cpu())
+        if dist.is_initialized() and world > 1:
+            dist.barrier()
+        return manifest
 
 
 class SyntheticTokens:

@@ -46,3 +46,44 @@ def test_keep_gathered_matches_zero3():
     b = run_ranks("test_models", "body_train", 4, args=("llama", 2, 2, True), timeout=300)[0]
     for x, y in zip(a, b):
         assert abs(x - y) < 2e-4 * max(1.0, abs(x)), (a, b)
+
+
+def body_trainer_checkpoint(rank, world, tmp):
+    """save at step 3, keep training to step 6; a fresh trainer that loads the checkpoint
+    reproduces steps 4-6 exactly; the metrics sink writes one JSON line per step on rank 0."""
+    import json
+    import os
+    from distdl_b200 import models
+    from distdl_b200.parallel import MetricsSink, SyntheticTokens, Trainer
+
+    def make(metrics=None):
+        torch.manual_seed(0)
+        cfg = models.llama_tiny(dtype=torch.float32, max_seq=32, vocab_size=200, d_model=48, ffn_dim=96)
+        cfg.n_heads, cfg.n_kv_heads = 4, 2
+        layout = models.ParallelLayout(2, 1)
+        model = models.Decoder(cfg, layout)
+        return Trainer(model, global_tokens_per_step=2 * 2 * 32, micro_batch=1, lr=5e-3, warmup_steps=0,
+                       metrics=metrics), layout, cfg
+
+    sink = MetricsSink(os.path.join(tmp, "metrics.jsonl"))
+    a, layout, cfg = make(sink)
+    data = SyntheticTokens(2, 32, cfg.vocab_size, dp_index=layout.dp_index, seed=5, n_buffers=8)
+    blocks = [data.next().clone() for _ in range(6)]
+    for i in range(3):
+        a.step(blocks[i])
+    a.save_checkpoint(os.path.join(tmp, "ckpt"))
+    ref = [a.step(blocks[i]).item() for i in range(3, 6)]
+    sink.close()
+    b, _, _ = make()
+    manifest = b.load_checkpoint(os.path.join(tmp, "ckpt"))
+    assert manifest["world_size"] == world and manifest["steps_done"] == 3 and manifest["layout"] == {"dp": 2, "tp": 1}
+    got = [b.step(blocks[i]).item() for i in range(3, 6)]
+    assert all(abs(x - y) < 1e-6 * max(1.0, abs(x)) for x, y in zip(ref, got)), (ref, got)
+    if rank == 0:
+        lines = [json.loads(line) for line in open(os.path.join(tmp, "metrics.jsonl"))]
+        assert [ln["step"] for ln in lines] == [1, 2, 3, 4, 5, 6] and all("loss" in ln for ln in lines)
+    return True
+
+
+def test_trainer_checkpoint_and_metrics(tmp_path):
+    run_ranks("test_models", "body_trainer_checkpoint", 2, args=(str(tmp_path),), timeout=300)
