@@ -497,6 +497,121 @@ split_norm_bwd_kernel(const Team t, const __nv_bfloat16* __restrict__ dy, const 
   team_barrier(t, 1, &fail);
 }
 
+
+// ---------------------------------------------------------------------------
+// Expert-parallel token routing over peer memory.  Experts e = r * El + el live on member
+// r; the staging buffer of every member holds capacity buffers [El][P (source member)][C][d]
+// (bf16), i.e. already in the [expert, rows, d] layout the grouped expert GEMM reads.
+//   scatter: row of pair p = (token, choice) goes straight into the destination member's
+//            buffer (peer stores, optionally scaled by the router weight): the top-k
+//            permutation and the all-to-all of the dispatch are one kernel.
+//   gather : y[t] = sum_c w * row(expert, slot) read straight from the owning member's
+//            buffer (peer loads): all-to-all + weighted un-permutation of the combine.
+//   dot    : <a[t], row(expert, slot)> per pair, rows read from the owners (router-weight
+//            gradients).
+// The receiver zeroes its buffer before the scatter kernel; barrier 0 orders that (and any
+// earlier use of the staging) before the first peer access, barrier 1 publishes the result.
+// ---------------------------------------------------------------------------
+struct MoeGeom {
+  int P, me, El, C, d, k;
+};
+__device__ __forceinline__ size_t moe_row_offset(const MoeGeom& g, int e, int src, int slot) {
+  return (((size_t)(e % g.El) * g.P + src) * g.C + slot) * (size_t)g.d;   // in elements, inside member e / El
+}
+
+__global__ void __launch_bounds__(kThreads)
+moe_scatter_peer_kernel(const Team t, const MoeGeom g, const __nv_bfloat16* __restrict__ src,
+                        const int* __restrict__ ids, const int* __restrict__ slot, const float* __restrict__ w,
+                        int npairs) {
+  __shared__ int fail;
+  if (threadIdx.x == 0) fail = 0;
+  if (!team_barrier(t, 0, &fail)) return;
+  const int dv = g.d >> 3;
+  const long long total = (long long)npairs * dv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int p = (int)(i / dv);
+    const int c = (int)(i - (long long)p * dv) * 8;
+    const int s = slot[p];
+    if (s < 0) continue;
+    const int e = ids[p];
+    const uint4 u = *reinterpret_cast<const uint4*>(src + (size_t)(p / g.k) * g.d + c);
+    uint4 o = u;
+    if (w != nullptr) {
+      const float sc = w[p];
+      float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), cc = unpack_bf16x2(u.z), ee = unpack_bf16x2(u.w);
+      o.x = pack_bf16x2(a.x * sc, a.y * sc); o.y = pack_bf16x2(b.x * sc, b.y * sc);
+      o.z = pack_bf16x2(cc.x * sc, cc.y * sc); o.w = pack_bf16x2(ee.x * sc, ee.y * sc);
+    }
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(t.buf[e / g.El]) + moe_row_offset(g, e, g.me, s) + c;
+    *reinterpret_cast<uint4*>(dst) = o;
+  }
+  __threadfence_system();
+  team_barrier(t, 1, &fail);
+}
+
+__global__ void __launch_bounds__(kThreads)
+moe_gather_peer_kernel(const Team t, const MoeGeom g, const int* __restrict__ ids, const int* __restrict__ slot,
+                       const float* __restrict__ w, __nv_bfloat16* __restrict__ dst, int tokens) {
+  __shared__ int fail;
+  if (threadIdx.x == 0) fail = 0;
+  if (!team_barrier(t, 0, &fail)) return;
+  const int dv = g.d >> 3;
+  const long long total = (long long)tokens * dv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int tok = (int)(i / dv);
+    const int c = (int)(i - (long long)tok * dv) * 8;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = 0; j < g.k; ++j) {
+      const int p = tok * g.k + j;
+      const int s = slot[p];
+      if (s < 0) continue;
+      const int e = ids[p];
+      const float sc = w ? w[p] : 1.f;
+      const uint4 u = ld_peer(reinterpret_cast<const __nv_bfloat16*>(t.buf[e / g.El]) + moe_row_offset(g, e, g.me, s) + c);
+      float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), cc = unpack_bf16x2(u.z), ee = unpack_bf16x2(u.w);
+      acc[0] += sc * a.x; acc[1] += sc * a.y; acc[2] += sc * b.x; acc[3] += sc * b.y;
+      acc[4] += sc * cc.x; acc[5] += sc * cc.y; acc[6] += sc * ee.x; acc[7] += sc * ee.y;
+    }
+    *reinterpret_cast<uint4*>(dst + (size_t)tok * g.d + c) =
+        make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                   pack_bf16x2(acc[6], acc[7]));
+  }
+  team_barrier(t, 1, &fail);
+}
+
+__global__ void __launch_bounds__(kThreads)
+moe_dot_peer_kernel(const Team t, const MoeGeom g, const __nv_bfloat16* __restrict__ a, const int* __restrict__ ids,
+                    const int* __restrict__ slot, float* __restrict__ out, int npairs) {
+  __shared__ int fail;
+  if (threadIdx.x == 0) fail = 0;
+  if (!team_barrier(t, 0, &fail)) return;
+  const int lane = threadIdx.x & 31;
+  const int wpb = kThreads / 32;
+  for (int p = blockIdx.x * wpb + (threadIdx.x >> 5); p < npairs; p += gridDim.x * wpb) {
+    const int s = slot[p];
+    float acc = 0.f;
+    if (s >= 0) {
+      const int e = ids[p];
+      const __nv_bfloat16* ar = a + (size_t)(p / g.k) * g.d;
+      const __nv_bfloat16* br = reinterpret_cast<const __nv_bfloat16*>(t.buf[e / g.El]) + moe_row_offset(g, e, g.me, s);
+      for (int c = lane * 8; c < g.d; c += 256) {
+        const uint4 u = *reinterpret_cast<const uint4*>(ar + c);
+        const uint4 v = ld_peer(br + c);
+        float2 x, y;
+        x = unpack_bf16x2(u.x); y = unpack_bf16x2(v.x); acc += x.x * y.x + x.y * y.y;
+        x = unpack_bf16x2(u.y); y = unpack_bf16x2(v.y); acc += x.x * y.x + x.y * y.y;
+        x = unpack_bf16x2(u.z); y = unpack_bf16x2(v.z); acc += x.x * y.x + x.y * y.y;
+        x = unpack_bf16x2(u.w); y = unpack_bf16x2(v.w); acc += x.x * y.x + x.y * y.y;
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) out[p] = acc;
+  }
+  team_barrier(t, 1, &fail);
+}
+
 // One-sided gather of data that does not change while it is read (ZeRO parameter shards
 // between two optimizer steps): out[i * bytes ...] = src[i][0 .. bytes), sources in peer
 // memory.  No flags and no waits, so the kernel may run on any stream next to other work.
@@ -756,6 +871,33 @@ DD_API int dd_rs_pull_f32(int n, void* const* srcs, float* acc, size_t count, fl
   if (ctas > 148 * 4) ctas = 148 * 4;
   rs_pull_f32_kernel<<<(int)ctas, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(d, reinterpret_cast<float4*>(acc),
                                                                                   nvec, scale);
+  return (int)cudaGetLastError();
+}
+// Expert-parallel routing over peer memory (see moe_scatter_peer_kernel).  mode 0: scatter
+// rows of `x` [tokens, d] into the owners' buffers (w optional); mode 1: gather-sum into
+// `x` [tokens, d] from the owners' buffers (w optional); mode 2: per-pair dot of `x` rows
+// with the owners' rows into `out` [pairs] fp32.  The staging buffer of every member must
+// hold El * P * C * d bf16 elements.
+DD_API int dd_moe_peer(int n, int me, int my_writer, void* const* bufs, void* const* flags, const int* writers,
+                       const unsigned* expect, int mode, void* x, const int* ids, const int* slot, const float* w,
+                       float* out, int tokens, int k, int El, int C, int d, int* steps, void* stream) {
+  if (d % 8 || tokens <= 0 || k <= 0 || El <= 0 || C <= 0) return DD_ERR_BAD_ARG;
+  Team t;
+  int r = fill_team(t, n, me, my_writer, bufs, flags, writers, expect);
+  if (r) return r;
+  *steps = 2;
+  MoeGeom g;
+  g.P = n; g.me = me; g.El = El; g.C = C; g.d = d; g.k = k;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (mode == 0)
+    moe_scatter_peer_kernel<<<kCollectiveCtas, kThreads, 0, s>>>(t, g, reinterpret_cast<const __nv_bfloat16*>(x), ids,
+                                                                 slot, w, tokens * k);
+  else if (mode == 1)
+    moe_gather_peer_kernel<<<kCollectiveCtas, kThreads, 0, s>>>(t, g, ids, slot, w,
+                                                                reinterpret_cast<__nv_bfloat16*>(x), tokens);
+  else
+    moe_dot_peer_kernel<<<kCollectiveCtas, kThreads, 0, s>>>(t, g, reinterpret_cast<const __nv_bfloat16*>(x), ids, slot,
+                                                             out, tokens * k);
   return (int)cudaGetLastError();
 }
 DD_API int dd_team_barrier(int n, int me, int my_writer, void* const* bufs, void* const* flags, const int* writers,

@@ -12,6 +12,7 @@ dispatch and combine are new.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -122,8 +123,21 @@ class MoEFeedForward(torch.nn.Module):
         frac = counts.float() / float(T * k)
         self.aux_loss = E * (frac.detach() * probs.mean(0)).sum()
         self.last_dropped = (slot < 0).sum()
-        send = moe_ops.dispatch(xt, ids, slot, E, C, k)                       # [E, C, d]
         P, El = self.ep, self.e_local
+        peer = None
+        if xt.is_cuda and P > 1 and os.environ.get("DISTDL_MOE_PEER", "1") != "0":
+            from ..parallel import moe_peer
+            if moe_peer.usable(xt, self.ep_ranks, El, C):
+                peer = moe_peer
+        if peer is not None:
+            # dispatch and combine over peer memory: permutation + all-to-all in one kernel each
+            h = peer.dispatch(xt, ids, slot, self.ep_ranks, El, C, k)             # [El, P*C, d]
+            h = batched_linear(h, self.w_up)
+            h = ops.swiglu(h)
+            h = batched_linear(h, self.w_down)
+            y = peer.combine(h, topw, ids, slot, self.ep_ranks, T, k, C)
+            return y.reshape(b, s, d).to(x.dtype)
+        send = moe_ops.dispatch(xt, ids, slot, E, C, k)                       # [E, C, d]
         recv = _AllToAllFn.apply(send.reshape(P, El * C, d), self.ep_ranks)   # [P(src), El*C, d]
         h = recv.reshape(P, El, C, d).transpose(0, 1).reshape(El, P * C, d)
         h = batched_linear(h, self.w_up)

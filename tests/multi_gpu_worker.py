@@ -196,6 +196,33 @@ def check_symmetric_params():
     assert losses["1"][-1] < losses["1"][0], losses
 
 
+def check_moe_peer():
+    """Expert-parallel block: dispatch / combine over peer memory against the unfused path
+    (permutation kernels + all-to-all), outputs and all gradients."""
+    import os
+    from distdl_b200 import models
+    world, rank = dist.get_world_size(), dist.get_rank()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    results = {}
+    for mode in ("0", "1"):
+        os.environ["DISTDL_MOE_PEER"] = mode
+        torch.manual_seed(0)
+        cfg = models.mixtral_tiny(n_experts=2 * world, d_model=256, ffn_dim=512, n_heads=4, n_kv_heads=2,
+                                  vocab_size=512, max_seq=128, checkpoint_blocks=False, n_layers=1)
+        lay = models.ParallelLayout(world, 1)
+        m = models.Decoder(cfg, lay)
+        moe = m.blocks[0].mlp
+        torch.manual_seed(50 + rank)
+        x = (torch.randn(2, 128, 256, device=dev) * 0.5).to(torch.bfloat16).requires_grad_()
+        y = moe(x)
+        (y.float() * torch.linspace(-1, 1, 256, device=dev)).sum().backward()
+        results[mode] = (y.detach().float(), x.grad.float(), moe.w_up.grad.float(), moe.w_down.grad.float())
+    os.environ.pop("DISTDL_MOE_PEER", None)
+    for a, b, what in zip(results["0"], results["1"], ("y", "dx", "dw_up", "dw_down")):
+        err = (a - b).abs().max().item() / (a.abs().max().item() + 1e-6)
+        assert err < 2e-2, ("moe peer", what, err)
+
+
 def main():
     import distdl_b200
     from distdl_b200.backends.common import world as dworld
@@ -209,6 +236,7 @@ def main():
         check_zero_grad_accumulate()
         check_split_norm()
         check_symmetric_params()
+        check_moe_peer()
     if what in ("fused", "all"):
         from multi_gpu_fused import check_fused
         check_fused()
