@@ -233,11 +233,19 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
             "config": {"model": f"{args.model} ({cfg.num_parameters() / 1e9:.2f}B params)", "global_batch": global_batch,
-                       "seq_len": seq, "parallelism": f"tp{tp} x fsdp{dp}", "micro_batch": micro,
-                       "zero": "gathered once per step (--keep-gathered)" if args.keep_gathered else "ZeRO-3: block weight matrices re-gathered at every use; norm weights, embedding and head gathered once per step",
+                       "seq_len": seq,
+                       "parallelism": (f"ep{dp} (experts) + fsdp{dp} (attention, router, embedding)" if cfg.n_experts
+                                       else f"tp{tp} x fsdp{dp}"),
+                       "micro_batch": micro,
+                       "zero": ("not used (parameters live on their tensor-parallel owners)" if not cfg.zero else
+                                "gathered once per step (--keep-gathered)" if args.keep_gathered else
+                                "ZeRO-3 parameters and optimizer state: block weight matrices re-gathered at every "
+                                "use; their gradients accumulate unsharded in fp32 and are reduce-scattered once per "
+                                "step; norm weights, embedding and head gathered once per step"),
                        "optimizer": "AdamW fp32 master + moments, grad clip 1.0",
                        "activation_checkpointing": "per block",
-                       "l2": "per-step working set (>= 16 GB of weights) exceeds the 126 MB L2; no explicit flush"},
+                       "l2": "inputs larger than L2: every step streams the model's weights, gradients and optimizer state "
+                             f"({cfg.num_parameters() * 16 / max(1, args.gpus) / 1e9:.0f} GB per GPU) through the 126 MB L2; no explicit flush"},
             "clocks": clocks.summary(),
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": data.bytes_per_block, "d2h_bytes_per_step": 4},
