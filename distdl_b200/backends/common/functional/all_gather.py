@@ -5,7 +5,6 @@ from __future__ import annotations
 
 import torch
 
-from ....utilities.slicing import compute_subshape_along_axis
 from ._base import TransportBound, scaled
 
 

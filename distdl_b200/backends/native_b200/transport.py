@@ -11,7 +11,6 @@ from __future__ import annotations
 
 import torch
 
-from ..common import world
 from ..common.transport import GroupTransport
 
 

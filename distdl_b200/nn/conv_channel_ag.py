@@ -13,7 +13,6 @@ from .all_gather import AllGather
 from .broadcast import Broadcast
 from .conv_channel import _CONV, _CONVT, _expand
 from .module import Module
-from .repartition import Repartition
 
 
 class _ChannelConvNd(Module):

@@ -5,7 +5,7 @@ import torch
 from .. import ops
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
-from ._linear_common import derived_partition, root_partition
+from ._linear_common import derived_partition
 from .broadcast import Broadcast
 from .module import Module
 from .repartition import Repartition

@@ -8,7 +8,6 @@ import torch
 from .. import ops
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
-from . import init
 from ._linear_common import PrefetchStream, deliver_grad, direct_main_grad, reduce_scatter_grad, local_out_features, relayout, root_partition, var_blocks
 from .all_gather import AllGather
 from .module import Module

@@ -3,7 +3,6 @@ which has no activation or attention code; they are required by the
 GPT-2 / Llama / Mixtral model shapes)."""
 from __future__ import annotations
 
-import math
 
 import torch
 

@@ -20,7 +20,7 @@ import torch
 
 from .. import _native
 from ..ops._util import ptr, stream_ptr
-from ..ops.gemm import _major, gemm, weight_grad
+from ..ops.gemm import _major, weight_grad
 from . import symm
 
 c_void_p, c_int, c_ll, c_uint = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_uint

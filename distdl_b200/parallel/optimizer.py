@@ -19,7 +19,7 @@ import torch
 import torch.distributed as dist
 
 from .. import _native, ops
-from ..ops._util import stream_ptr, use_native
+from ..ops._util import stream_ptr
 
 
 class FlatAdamW:

@@ -20,7 +20,6 @@ import torch
 import torch.distributed as dist
 
 from .. import _native
-from ..backends.common import world
 
 c_void_p, c_int, c_size_t = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
 _PP = ctypes.POINTER(c_void_p)

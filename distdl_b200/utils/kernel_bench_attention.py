@@ -1,5 +1,4 @@
 """Attention part of :mod:`distdl_b200.utils.kernel_bench`."""
-import math
 
 import torch
 

@@ -1,7 +1,6 @@
 """Convolution, pooling, batch-norm and loss layers against serial PyTorch on
 CPU ranks, plus the halo arithmetic golden values."""
 import numpy as np
-import pytest
 import torch
 
 from dist_harness import run_ranks

@@ -3,7 +3,6 @@ weights are loaded from a serial module through the ``collect_state`` hooks,
 inputs are scattered with Repartition, outputs and input gradients gathered
 back and compared (the reference's vs-serial strategy,
 ``tests/layers/test_layernorm.py:143-265``)."""
-import numpy as np
 import pytest
 import torch
 
