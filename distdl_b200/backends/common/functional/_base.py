@@ -10,7 +10,6 @@ from __future__ import annotations
 
 import types
 
-
 from ....utilities.torch import zero_volume_tensor
 
 

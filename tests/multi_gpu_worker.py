@@ -171,6 +171,34 @@ def check_split_norm():
             assert err < 2e-2, ("split_norm", rms, what, err)
 
 
+def check_layernorm_module():
+    """DistributedLayerNorm over a feature dimension split across all GPUs takes the fused
+    kernel on the native backend and matches the serial LayerNorm (forward and input gradient)."""
+    import distdl_b200
+    from distdl_b200 import _native
+    from distdl_b200.nn import DistributedLayerNorm
+    world, rank = dist.get_world_size(), dist.get_rank()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    D = 64 * world
+    P = distdl_b200.backends.backend.Partition().create_cartesian_topology_partition([1, world])
+    ln = DistributedLayerNorm(P, D, dtype=torch.bfloat16)
+    torch.manual_seed(7)
+    full = torch.randn(200, D, device=dev)
+    dyf = torch.randn(200, D, device=dev)
+    x = full[:, rank * 64:(rank + 1) * 64].to(torch.bfloat16).contiguous().requires_grad_()
+    before = _native.launch_count
+    y = ln(x)
+    assert _native.launch_count > before, "the fused split-norm kernel did not run"
+    y.backward(dyf[:, rank * 64:(rank + 1) * 64].to(torch.bfloat16))
+    xf = full.to(torch.bfloat16).float().requires_grad_()
+    ref = torch.nn.functional.layer_norm(xf, (D,), None, None, ln.eps)
+    ref.backward(dyf.to(torch.bfloat16).float())
+    sl = slice(rank * 64, (rank + 1) * 64)
+    for got, want, what in ((y, ref[:, sl], "y"), (x.grad, xf.grad[:, sl], "dx")):
+        err = (got.float() - want.detach()).abs().max().item() / (want.abs().max().item() + 1e-6)
+        assert err < 2e-2, ("layernorm module", what, err)
+
+
 def check_symmetric_params():
     """ZeRO shards gathered in place from the optimizer's peer-mapped buffer give the same
     training trajectory as the staged all-gather."""
@@ -235,6 +263,7 @@ def main():
         check_primitives_native()
         check_zero_grad_accumulate()
         check_split_norm()
+        check_layernorm_module()
         check_symmetric_params()
         check_moe_peer()
     if what in ("fused", "all"):
