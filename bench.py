@@ -172,7 +172,7 @@ def main():
     elif cfg.num_parameters() < 3e9:
         micro = min(local_batch, 16)
     else:
-        micro = {1: 2, 2: 2}.get(args.gpus, 4)
+        micro = {2: 2}.get(args.gpus, 4)      # 1 GPU: 15.8k / 16.5k / 14.6k tokens/s at 2 / 4 / 8 sequences
     torch.manual_seed(1234 + rank)
     layout = models.ParallelLayout(dp, tp)
     model = models.Decoder(cfg, layout)
