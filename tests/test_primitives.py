@@ -252,3 +252,30 @@ def body_halo(rank, world):
 
 def test_halo_exchange():
     run_ranks("test_primitives", "body_halo", 4)
+
+
+def body_allgather_skips_adjoint_when_gradient_goes_elsewhere(rank, world):
+    """A parameter whose gradient is accumulated outside of autograd (``full_grad_view``)
+    yields no gradient for its gathered copy; the adjoint reduce-scatter is then skipped on
+    every member alike (nothing hangs) and the parameter receives no ``.grad``; a gathered
+    tensor that simply is not used still gets an exact zero gradient."""
+    import distdl_b200
+    from distdl_b200.nn import AllGather
+    P_world = distdl_b200.backends.backend.Partition()
+    P = P_world.create_partition_inclusive(range(world)).create_cartesian_topology_partition([world, 1])
+    gather = AllGather(P, axes_all_gather=(0,))
+    w = torch.nn.Parameter(torch.randn(3, 4))
+    w.full_grad_view = torch.zeros(world * 12)           # marks "accumulated elsewhere"
+    other = torch.nn.Parameter(torch.randn(3, 4))
+    full = gather(w)
+    full_other = gather(other)
+    unused = gather(torch.nn.Parameter(torch.ones(3, 4)))
+    assert full.shape == (3 * world, 4) and unused.shape == (3 * world, 4)
+    (full_other.sum() * 2.0 + full.detach().sum()).backward()
+    assert w.grad is None
+    assert torch.allclose(other.grad, torch.full((3, 4), 2.0 * world))
+    return True
+
+
+def test_allgather_adjoint_skipped_without_gradient():
+    run_ranks("test_primitives", "body_allgather_skips_adjoint_when_gradient_goes_elsewhere", 2, timeout=120)
