@@ -130,19 +130,27 @@ class PrefetchStream:
     stream; gathers that need no handshake with other GPUs (parameter shards read in place
     from the optimizer's peer-mapped buffer) are moved to the device's side stream inside
     ``fn`` and are not waited for until ``wait()``, so a prefetch issued early overlaps the
-    compute that follows it.  Everything else stays ordered on the current stream."""
+    compute that follows it.  ``wait()`` waits for THIS layer's gathers only (an event
+    recorded right after them), not for prefetches of other layers queued later on the same
+    side stream.  Everything else stays ordered on the current stream."""
 
     def __init__(self, device):
         self.cuda = torch.cuda.is_available() and torch.device(device).type == "cuda"
+        self._event = None
 
     def run(self, fn):
         if not self.cuda:
             return fn()
         from ..utilities import streams
         with streams.deferred():
-            return fn()
+            out = fn()
+        side = streams.side_stream()
+        if side is not None:
+            self._event = torch.cuda.Event()
+            self._event.record(side)
+        return out
 
     def wait(self):
-        if self.cuda:
-            from ..utilities import streams
-            streams.join()
+        if self.cuda and self._event is not None:
+            torch.cuda.current_stream().wait_event(self._event)
+            self._event = None
