@@ -116,10 +116,36 @@ def check(status: int, what: str = "") -> None:
         raise NativeError(f"{what}: {msg} (status {status})")
 
 
+_nvtx = None
+
+
+def _nvtx_module():
+    """``torch.cuda.nvtx`` when ``DISTDL_NVTX=1`` (every native launch then sits in an NVTX
+    range named after its entry point), else ``False``."""
+    global _nvtx
+    if _nvtx is None:
+        _nvtx = False
+        if os.environ.get("DISTDL_NVTX", "0") == "1":
+            try:
+                import torch
+                _nvtx = torch.cuda.nvtx
+            except Exception:       # noqa: BLE001
+                _nvtx = False
+    return _nvtx
+
+
 def call(name: str, *args) -> None:
     """Calls an entry point and raises :class:`NativeError` on failure."""
     global launch_count
     launch_count += 1
+    nvtx = _nvtx_module()
+    if nvtx:
+        nvtx.range_push(name)
+        try:
+            check(getattr(lib(), name)(*args), name)
+        finally:
+            nvtx.range_pop()
+        return
     check(getattr(lib(), name)(*args), name)
 
 

@@ -214,3 +214,22 @@ def heap(staging_bytes: int = None) -> SymmetricHeap:
 
 def heap_ready() -> bool:
     return _heap is not None
+
+
+class DeviceTimeout(RuntimeError):
+    """A kernel gave up a bounded wait for another GPU."""
+
+
+def check_health():
+    """Reads the device status record (synchronises the device).  If a kernel gave up a
+    bounded wait since the last check, the symmetric heap is marked poisoned (its flag
+    counters are out of step with the peers, so every later collective would time out as
+    well) and :class:`DeviceTimeout` is raised with the recorded place and counter values.
+    Recovery: restart the job from the last checkpoint."""
+    code, where, expected, seen = _native.read_status()
+    if code == 0:
+        return
+    if _heap is not None:
+        _heap.poisoned = True
+    raise DeviceTimeout(f"device status {code}: a bounded wait ran out at site {where} "
+                        f"(waited for {expected & 0xFFFFFFFF}, saw {seen & 0xFFFFFFFF})")

@@ -24,8 +24,9 @@ class Trainer:
 
     def __init__(self, model, global_tokens_per_step: int, micro_batch: int = 1, lr: float = 3e-4,
                  weight_decay: float = 0.1, max_grad_norm: float = 1.0, warmup_steps: int = 10,
-                 total_steps: int = 1000, device=None, metrics=None):
+                 total_steps: int = 1000, device=None, metrics=None, health_check_every: int = 50):
         self.model = model
+        self.health_check_every = health_check_every   # steps between reads of the device status record
         self.metrics = metrics          # a parallel.metrics.MetricsSink, or None
         self.micro_batch = micro_batch
         self.global_tokens = global_tokens_per_step
@@ -58,6 +59,9 @@ class Trainer:
         self.steps_done += 1
         if dist.is_initialized() and dist.get_world_size() > 1:
             dist.all_reduce(total)
+        if (self.health_check_every and tokens.is_cuda and self.steps_done % self.health_check_every == 0):
+            from . import symm
+            symm.check_health()       # raises DeviceTimeout if a kernel gave up waiting for a peer
         if self.metrics is not None:
             self.metrics.step(self.steps_done, total, self.global_tokens, lr=self.opt.lr,
                               grad_norm=self.opt.last_grad_norm, device=tokens.device)

@@ -83,6 +83,15 @@ def test_device_wait_that_runs_out_reports_status_and_context_survives():
     x = torch.ones(1024, device="cuda")
     assert float((x * 2).sum()) == 2048.0
     assert _native.read_status()[0] == 0
+    # the host-side health check turns the same event into an exception (and a clean record)
+    from distdl_b200.parallel import symm
+    symm.check_health()                                  # nothing pending: returns
+    expect2 = (ctypes.c_uint * 2)(2, 2)
+    assert lib.dd_team_barrier(2, 0, 0, bufs, pads, writers, expect2, ctypes.byref(steps),
+                               torch.cuda.current_stream().cuda_stream) == 0
+    with pytest.raises(symm.DeviceTimeout):
+        symm.check_health()
+    symm.check_health()
     lib.dd_symm_free.argtypes = [vp]
     lib.dd_symm_free(pad)
     lib.dd_symm_free(buf)
