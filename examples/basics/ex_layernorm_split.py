@@ -24,4 +24,4 @@ lo = sum(sizes[:rank])
 x = full[:, lo:lo + sizes[rank]].clone().requires_grad_()
 y = ln(x)
 ref = torch.nn.functional.layer_norm(full, (D,))
-say(P_world, "local features", tuple(x.shape), "max |y - serial|", float((y - ref[:, lo:lo + sizes[rank]]).abs().max()))
+say(P_world, "local features", tuple(x.shape), "max |y - serial|", float((y.detach() - ref[:, lo:lo + sizes[rank]]).abs().max()))
