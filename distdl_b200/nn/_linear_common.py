@@ -125,6 +125,35 @@ def reduce_scatter_grad(rs, full_grad, param, scale_backward=None):
     deliver_grad(param, rs(g))
 
 
+class KeptBufferGuard:
+    """Detects a kept (``auto_clear_buffer=False``) gathered buffer that has gone stale: the
+    shard parameters were updated in place (an optimizer step) without
+    ``clear_weight_buffer()`` in between.  The stale copy is dropped and re-gathered, with a
+    one-time warning, because the gradients accumulated on it were never delivered."""
+
+    _warned = False
+
+    def __init__(self):
+        self.versions = None
+
+    def remember(self, *params):
+        self.versions = tuple(p._version for p in params if p is not None)
+
+    def stale(self, *params):
+        if self.versions is None:
+            return False
+        now = tuple(p._version for p in params if p is not None)
+        if now == self.versions:
+            return False
+        if not KeptBufferGuard._warned:
+            KeptBufferGuard._warned = True
+            import warnings
+            warnings.warn("a ZeRO layer with auto_clear_buffer=False saw its parameters change while a gathered "
+                          "copy was kept: call clear_weight_buffer() (or model.release_gathered()) before the "
+                          "optimizer step; the stale copy is re-gathered and its pending gradients are dropped")
+        return True
+
+
 class PrefetchStream:
     """Weight prefetch of a layer.  ``run(fn)`` executes ``fn`` (the gathers) on the current
     stream; gathers that need no handshake with other GPUs (parameter shards read in place

@@ -6,7 +6,7 @@ import torch
 
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
-from ._linear_common import PrefetchStream, deliver_grad, root_partition
+from ._linear_common import KeptBufferGuard, PrefetchStream, deliver_grad, root_partition
 from .all_gather import AllGather
 from .module import Module
 from .reduce_scatter import ReduceScatter
@@ -49,6 +49,7 @@ class _ZeroNormBase(Module):
             else:
                 self.register_parameter(n, None)
         self.prefetch = PrefetchStream(device)
+        self._kept = KeptBufferGuard()
         self.buffers_gathered = None
         self._register_state_dict_hook(self.gather_state_dict)
         self._register_load_state_dict_pre_hook(self.scatter_state_dict)
@@ -94,8 +95,14 @@ class _ZeroNormBase(Module):
         self.buffers_gathered = out
 
     def collect_weights(self):
-        if self.buffers_gathered is None and self.elementwise_affine:
+        if not self.elementwise_affine:
+            return
+        params = [getattr(self, n) for n in self.param_names]
+        if self.buffers_gathered is not None and not self.auto_clear_buffer and self._kept.stale(*params):
+            self.buffers_gathered = None
+        if self.buffers_gathered is None:
             self.prefetch.run(self._collect)
+            self._kept.remember(*params)
 
     prefetch_weights = collect_weights
 

@@ -6,7 +6,7 @@ import torch
 from .. import ops
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
-from ._linear_common import PrefetchStream, reduce_scatter_grad
+from ._linear_common import KeptBufferGuard, PrefetchStream, reduce_scatter_grad
 from .all_gather import AllGather
 from .module import Module
 from .reduce_scatter import ReduceScatter
@@ -49,6 +49,7 @@ class DistributedEmbeddingZero(Module):
         self.scatter_weight = Repartition(self.P_root, self.P_weight, preserve_batch=False)
         self.gather_weight = Repartition(self.P_weight, self.P_root, preserve_batch=False)
         self.prefetch = PrefetchStream(device)
+        self._kept = KeptBufferGuard()
         self.weight_buffer = None
         self.reset_parameters(_weight)
         self._register_state_dict_hook(self.gather_state_dict)
@@ -88,8 +89,11 @@ class DistributedEmbeddingZero(Module):
         self.weight_buffer = w if self.auto_clear_buffer else w.detach().requires_grad_(True)
 
     def collect_weights(self):
+        if self.weight_buffer is not None and not self.auto_clear_buffer and self._kept.stale(self.weight):
+            self.weight_buffer = None
         if self.weight_buffer is None:
             self.prefetch.run(self._collect)
+            self._kept.remember(self.weight)
 
     prefetch_weights = collect_weights
 

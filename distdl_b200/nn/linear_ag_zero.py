@@ -8,7 +8,7 @@ import torch
 from .. import ops
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
-from ._linear_common import PrefetchStream, deliver_grad, direct_main_grad, reduce_scatter_grad, local_out_features, relayout, root_partition, var_blocks
+from ._linear_common import KeptBufferGuard, PrefetchStream, deliver_grad, direct_main_grad, reduce_scatter_grad, local_out_features, relayout, root_partition, var_blocks
 from .all_gather import AllGather
 from .module import Module
 from .reduce_scatter import ReduceScatter
@@ -73,6 +73,7 @@ class DistributedLinearAllGatherZero(Module):
         self.weight = torch.nn.Parameter(torch.empty(tuple(wshape), **kw))
         # lets an optimizer find the all-gather of this ZeRO shard (team, gathered layout)
         self.weight.zero_gather = self.allgather_weight
+        self._kept = KeptBufferGuard()
         if bias:
             bshape = [1] * dim
             bshape[-2] = int(compute_subshape(D, P_weight.index[0], [self.out_features_local])[0])
@@ -208,8 +209,11 @@ class DistributedLinearAllGatherZero(Module):
 
     def collect_weights(self):
         """Gathers the weight (and bias) shards, on the side stream when there is one."""
+        if self.weight_buffer is not None and not self.auto_clear_buffer and self._kept.stale(self.weight, self.bias):
+            self.weight_buffer = self.bias_buffer = None
         if self.weight_buffer is None:
             self.prefetch.run(self._collect_weights)
+            self._kept.remember(self.weight, self.bias)
 
     prefetch_weights = collect_weights
 

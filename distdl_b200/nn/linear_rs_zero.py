@@ -8,7 +8,7 @@ import torch
 from .. import ops
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
-from ._linear_common import PrefetchStream, deliver_grad, direct_main_grad, reduce_scatter_grad, derived_partition, root_partition
+from ._linear_common import KeptBufferGuard, PrefetchStream, deliver_grad, direct_main_grad, reduce_scatter_grad, derived_partition, root_partition
 from .all_gather import AllGather
 from .module import Module
 from .reduce_scatter import ReduceScatter
@@ -73,6 +73,7 @@ class DistributedLinearReduceScatterZero(Module):
         self.weight = torch.nn.Parameter(torch.empty(tuple(wshape), **kw))
         # lets an optimizer find the all-gather of this ZeRO shard (team, gathered layout)
         self.weight.zero_gather = self.allgather_weight
+        self._kept = KeptBufferGuard()
         if bias and self.P_bias.active:
             self.allgather_bias = AllGather(self.P_bias, axes_all_gather=(0,), scale_backward=scale_backward)
             self.reduce_scatter_bias = ReduceScatter(self.P_bias, axes_reduce_scatter=(0,))
@@ -161,8 +162,12 @@ class DistributedLinearReduceScatterZero(Module):
                 self.bias_buffer = self.bias_buffer.detach().requires_grad_(True)
 
     def collect_weights(self):
+        bias = self.bias if (self.use_bias and self.P_bias.active) else None
+        if self.weight_buffer is not None and not self.auto_clear_buffer and self._kept.stale(self.weight, bias):
+            self.weight_buffer = self.bias_buffer = None
         if self.weight_buffer is None:
             self.prefetch.run(self._collect_weights)
+            self._kept.remember(self.weight, bias)
 
     prefetch_weights = collect_weights
 

