@@ -1,0 +1,22 @@
+"""A few of the examples run end to end on CPU ranks (one per family), so that they keep
+working with the library."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("script,nproc", [("examples/primitives/ex_repartition.py", 4),
+                                          ("examples/basics/ex_linear_tp_sp.py", 4),
+                                          ("examples/basics/ex_pipeline.py", 3),
+                                          ("examples/basics/ex_layernorm_split.py", 3)])
+def test_example_runs(script, nproc):
+    port = 29600 + (os.getpid() + hash(script)) % 300
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, script)]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1")
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240, cwd=ROOT)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
