@@ -1,7 +1,7 @@
 """Runs a few launches of ONE hand-written kernel on a small case, for use
 under a profiler:
 
-    python -m distdl_b200.utils.profile_case gemm|gemm_wgrad|attn_fwd|attn_bwd|rmsnorm|adamw|xent [launches]
+    python -m distdl_b200.utils.profile_case gemm|gemm_wgrad|ag_gemm|gemm_rs|attn_fwd|attn_bwd|rmsnorm|adamw|xent [launches]
 
 Inputs are larger than the 126 MB L2 where that matters for the DRAM figures
 but stay well under a few GB.
@@ -26,6 +26,29 @@ def main():
         x = torch.randn(8192, 4096, device=dev, dtype=torch.bfloat16)
         out = torch.zeros(14336, 4096, device=dev, dtype=torch.float32)
         fn = lambda: ops.gemm(dy.t(), x.t(), out=out, accumulate=True)  # noqa: E731
+    elif what in ("ag_gemm", "gemm_rs"):
+        # The fused tensor-parallel kernels on a team of ONE process: the same kernels (comm
+        # warps, ready words, owner-ordered tiles, TMA-store epilogue) with every "peer" being
+        # this GPU, so that a profiler can be attached (it must never wrap a multi-rank job).
+        import os
+
+        import torch.distributed as dist
+
+        import distdl_b200
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29655")
+        dist.init_process_group("nccl", rank=0, world_size=1)
+        distdl_b200.config.set_backend("native", "cupy")
+        distdl_b200.backends.backend.Partition()                 # creates the symmetric heap
+        from distdl_b200.parallel import fused
+        if what == "ag_gemm":
+            x = torch.randn(2, 4096, 4096, device=dev, dtype=torch.bfloat16)
+            w = torch.randn(14336, 4096, device=dev, dtype=torch.bfloat16)
+            fn = lambda: fused.ag_gemm(x, w, None, (0,))  # noqa: E731
+        else:
+            x = torch.randn(8192, 7168, device=dev, dtype=torch.bfloat16)
+            w = torch.randn(4096, 7168, device=dev, dtype=torch.bfloat16)
+            fn = lambda: fused.gemm_rs(x, w, None, (0,), 2, 4096)  # noqa: E731
     elif what in ("attn_fwd", "attn_bwd"):
         batch, seq, Hq, Hkv, D = 2, 4096, 32, 8, 128
         qkv = torch.randn(batch * seq, Hq + 2 * Hkv, D, device=dev, dtype=torch.bfloat16)
