@@ -64,10 +64,17 @@ __device__ bool team_barrier(const Team& t, uint32_t step, int* sh_fail) {
     uint32_t it = 0;
     // counters wrap after 2^32 signals: compare as a signed distance
     while ((int32_t)(seen - want) < 0) {
-      if ((++it & 0xff) == 0 && globaltimer_ns() - t0 > kSpinLimitNs) {
-        report_timeout(t.status, 100 + (int)step, (int)want, (int)seen);
-        *sh_fail = 1;
-        break;
+      if ((++it & 0xff) == 0) {
+        // once a wait has run out, the counters are out of step: later waits fail at once
+        if (t.status != nullptr && *reinterpret_cast<volatile int*>(&t.status->code) != 0) {
+          *sh_fail = 1;
+          break;
+        }
+        if (globaltimer_ns() - t0 > kSpinLimitNs) {
+          report_timeout(t.status, 100 + (int)step, (int)want, (int)seen);
+          *sh_fail = 1;
+          break;
+        }
       }
       seen = load_flag(mine);
     }

@@ -85,6 +85,12 @@ __device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t want, v
     }
     if ((++it & 0x3f) == 0) {
       if (*abort_flag) return false;
+      // a wait that ran out earlier (in this or a previous kernel) leaves the counters out of
+      // step: fail at once instead of spending the full limit again in every later kernel
+      if (st != nullptr && *reinterpret_cast<volatile int*>(&st->code) != 0) {
+        *abort_flag = 1;
+        return false;
+      }
       if (globaltimer_ns() - t0 > kSpinLimitNs) {
         *abort_flag = 1;
         report_timeout(st, where, (int)want, (int)seen);

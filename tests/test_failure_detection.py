@@ -89,6 +89,14 @@ def test_device_wait_that_runs_out_reports_status_and_context_survives():
     expect2 = (ctypes.c_uint * 2)(2, 2)
     assert lib.dd_team_barrier(2, 0, 0, bufs, pads, writers, expect2, ctypes.byref(steps),
                                torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()                             # that wait has run out: the record is set
+    # while the record is set, later waits give up at once instead of spending the limit again
+    t1 = time.time()
+    expect3 = (ctypes.c_uint * 2)(3, 3)
+    assert lib.dd_team_barrier(2, 0, 0, bufs, pads, writers, expect3, ctypes.byref(steps),
+                               torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert time.time() - t1 < 1.0
     with pytest.raises(symm.DeviceTimeout):
         symm.check_health()
     symm.check_health()
