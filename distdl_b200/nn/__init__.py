@@ -64,3 +64,7 @@ __all__ = [
     "DistributedAvgPool3d", "DistributedMaxPool1d", "DistributedMaxPool2d", "DistributedMaxPool3d", "Repartition",
     "ReduceScatter", "SumReduce", "DistributedTranspose", "Interpolate", "DistributedUpsample", "loss",
 ]
+
+# beyond the reference's 64 names: attention over a sequence-split tensor (kept out of
+# ``__all__`` so that the list above stays the reference's)
+from .attention import DistributedSelfAttention  # noqa: E402,F401

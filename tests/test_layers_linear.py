@@ -273,3 +273,35 @@ def body_kept_buffer_goes_stale(rank, world):
 
 def test_kept_buffer_is_regathered_after_parameter_update():
     run_ranks("test_layers_linear", "body_kept_buffer_goes_stale", 2, timeout=120)
+
+
+def body_context_parallel_attention(rank, world, causal):
+    """Sequence split over all workers: head <-> sequence repartitions around the local attention
+    reproduce serial attention (GQA), forward and input gradients."""
+    import distdl_b200
+    from distdl_b200.nn import DistributedSelfAttention
+    P = distdl_b200.backends.backend.Partition().create_cartesian_topology_partition([1, world, 1, 1])
+    att = DistributedSelfAttention(P, causal=causal)
+    b, s, hq, hkv, d = 2, 8 * world, 2 * world, world, 16
+    torch.manual_seed(4)
+    Q, K, V = torch.randn(b, s, hq, d), torch.randn(b, s, hkv, d), torch.randn(b, s, hkv, d)
+    dO = torch.randn(b, s, hq, d)
+    sl = slice(rank * (s // world), (rank + 1) * (s // world))
+    q, k, v = (t[:, sl].clone().requires_grad_() for t in (Q, K, V))
+    out = att(q, k, v)
+    out.backward(dO[:, sl])
+    Qr, Kr, Vr = (t.clone().requires_grad_() for t in (Q, K, V))
+    rep = hq // hkv
+    ref = torch.nn.functional.scaled_dot_product_attention(
+        Qr.transpose(1, 2), Kr.transpose(1, 2).repeat_interleave(rep, 1), Vr.transpose(1, 2).repeat_interleave(rep, 1),
+        is_causal=causal).transpose(1, 2)
+    ref.backward(dO)
+    assert torch.allclose(out, ref[:, sl], atol=1e-5), (out - ref[:, sl]).abs().max()
+    for got, want in ((q.grad, Qr.grad), (k.grad, Kr.grad), (v.grad, Vr.grad)):
+        assert torch.allclose(got, want[:, sl], atol=1e-5), (got - want[:, sl]).abs().max()
+    return True
+
+
+def test_context_parallel_attention_matches_serial():
+    run_ranks("test_layers_linear", "body_context_parallel_attention", 2, args=(True,), timeout=120)
+    run_ranks("test_layers_linear", "body_context_parallel_attention", 4, args=(False,), timeout=120)
