@@ -68,3 +68,4 @@ __all__ = [
 # beyond the reference's 64 names: attention over a sequence-split tensor (kept out of
 # ``__all__`` so that the list above stays the reference's)
 from .attention import DistributedSelfAttention  # noqa: E402,F401
+from .ring_attention import DistributedRingAttention  # noqa: E402,F401

@@ -228,6 +228,35 @@ def check_context_parallel_attention():
         assert err < 3e-2, ("context-parallel attention", what, err)
 
 
+def check_ring_attention():
+    """DistributedRingAttention on GPUs: the flash-attention kernels per (query block, key block)
+    pair with the global log-sum-exp, ring hops over peer memory, against serial fp32 attention."""
+    import distdl_b200
+    from distdl_b200.nn import DistributedRingAttention
+    world, rank = dist.get_world_size(), dist.get_rank()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    P = distdl_b200.backends.backend.Partition().create_cartesian_topology_partition([1, world, 1, 1])
+    att = DistributedRingAttention(P, causal=True)
+    b, s, hq, hkv, d = 2, 256 * world, 4, 2, 128
+    torch.manual_seed(11)
+    Q, K, V = (torch.randn(b, s, h, d, device=dev) for h in (hq, hkv, hkv))
+    dO = torch.randn(b, s, hq, d, device=dev)
+    sl = slice(rank * (s // world), (rank + 1) * (s // world))
+    q, k, v = (t[:, sl].to(torch.bfloat16).contiguous().requires_grad_() for t in (Q, K, V))
+    out = att(q, k, v)
+    out.backward(dO[:, sl].to(torch.bfloat16).contiguous())
+    Qr, Kr, Vr = (t.to(torch.bfloat16).float().requires_grad_() for t in (Q, K, V))
+    rep = hq // hkv
+    ref = torch.nn.functional.scaled_dot_product_attention(
+        Qr.transpose(1, 2), Kr.transpose(1, 2).repeat_interleave(rep, 1), Vr.transpose(1, 2).repeat_interleave(rep, 1),
+        is_causal=True).transpose(1, 2)
+    ref.backward(dO.to(torch.bfloat16).float())
+    for got, want, what in ((out, ref[:, sl], "out"), (q.grad, Qr.grad[:, sl], "dq"), (k.grad, Kr.grad[:, sl], "dk"),
+                            (v.grad, Vr.grad[:, sl], "dv")):
+        err = (got.float() - want.detach()).abs().max().item() / (want.abs().max().item() + 1e-6)
+        assert err < 3e-2, ("ring attention", what, err)
+
+
 def check_symmetric_params():
     """ZeRO shards gathered in place from the optimizer's peer-mapped buffer give the same
     training trajectory as the staged all-gather."""
@@ -294,6 +323,7 @@ def main():
         check_split_norm()
         check_layernorm_module()
         check_context_parallel_attention()
+        check_ring_attention()
         check_symmetric_params()
         check_moe_peer()
     if what in ("fused", "all"):

@@ -305,3 +305,35 @@ def body_context_parallel_attention(rank, world, causal):
 def test_context_parallel_attention_matches_serial():
     run_ranks("test_layers_linear", "body_context_parallel_attention", 2, args=(True,), timeout=120)
     run_ranks("test_layers_linear", "body_context_parallel_attention", 4, args=(False,), timeout=120)
+
+
+def body_ring_attention(rank, world, causal, hq, hkv):
+    """K / V blocks travel around the ring; result and all three gradients equal serial attention
+    (head counts need not divide by the ring size)."""
+    import distdl_b200
+    from distdl_b200.nn import DistributedRingAttention
+    P = distdl_b200.backends.backend.Partition().create_cartesian_topology_partition([1, world, 1, 1])
+    att = DistributedRingAttention(P, causal=causal)
+    b, s, d = 2, 6 * world, 16
+    torch.manual_seed(9)
+    Q, K, V = torch.randn(b, s, hq, d), torch.randn(b, s, hkv, d), torch.randn(b, s, hkv, d)
+    dO = torch.randn(b, s, hq, d)
+    sl = slice(rank * (s // world), (rank + 1) * (s // world))
+    q, k, v = (t[:, sl].clone().requires_grad_() for t in (Q, K, V))
+    out = att(q, k, v)
+    out.backward(dO[:, sl])
+    Qr, Kr, Vr = (t.clone().requires_grad_() for t in (Q, K, V))
+    rep = hq // hkv
+    ref = torch.nn.functional.scaled_dot_product_attention(
+        Qr.transpose(1, 2), Kr.transpose(1, 2).repeat_interleave(rep, 1), Vr.transpose(1, 2).repeat_interleave(rep, 1),
+        is_causal=causal).transpose(1, 2)
+    ref.backward(dO)
+    assert torch.allclose(out, ref[:, sl], atol=2e-5), (out - ref[:, sl]).abs().max()
+    for got, want, what in ((q.grad, Qr.grad, "dq"), (k.grad, Kr.grad, "dk"), (v.grad, Vr.grad, "dv")):
+        assert torch.allclose(got, want[:, sl], atol=2e-5), (what, (got - want[:, sl]).abs().max())
+    return True
+
+
+def test_ring_attention_matches_serial():
+    run_ranks("test_layers_linear", "body_ring_attention", 3, args=(True, 4, 2), timeout=180)
+    run_ranks("test_layers_linear", "body_ring_attention", 4, args=(False, 3, 3), timeout=180)
