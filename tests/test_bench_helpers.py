@@ -1,0 +1,42 @@
+"""bench.py helpers that need no GPU: the layouts named by the benchmark configuration, the
+summary of sampled clocks, and the reference arm's answer."""
+import importlib.util
+import json
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _bench():
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(ROOT, "bench.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_layouts_named_by_the_configuration():
+    b = _bench()
+    assert b.layout_for(1) == (1, 1) and b.layout_for(2) == (1, 2)
+    assert b.layout_for(4) == (2, 2) and b.layout_for(8) == (4, 2)          # TP=2 x FSDP=4 on 8 GPUs
+
+
+def test_clock_summary_median_and_reasons():
+    b = _bench()
+    s = b.ClockSampler(0)
+    assert s.summary()["reasons"] == ["unsampled"]
+    s.rows = [["1300", "1965", "990.1", "0x4", "Not Active", "Not Active", "Not Active", "Active"],
+              ["1400", "1965", "1001.0", "0x4", "Not Active", "Not Active", "Not Active", "Active"],
+              ["1900", "1965", "400.0", "0x0", "Not Active", "Not Active", "Not Active", "Not Active"]]
+    out = s.summary()
+    assert out["sm_mhz"] == 1400.0 and out["sm_max_mhz"] == 1965.0 and out["reasons"] == ["sw_power_cap"]
+    assert out["samples"] == 3
+
+
+def test_reference_arm_reports_unavailable_and_exits_zero():
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "1",
+                          "--steps", "2", "--warmup", "3"], capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0
+    line = json.loads(res.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line
