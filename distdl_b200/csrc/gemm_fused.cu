@@ -27,8 +27,20 @@
 //   "consumed" on the peers, which the next gemm_rs using the same staging
 //   parity waits for before it overwrites the slot.
 //
+//
+// This file holds the host entry points, the single-CTA-tile kernels (fallback,
+// `DISTDL_FUSED_PAIR=0`) and the separate fold kernel.  The default kernels are the
+// CTA-pair versions in gemm_fused2.cu; they differ in three ways: row blocks are
+// pulled in 32-row pieces spread over all CTAs (the shard staging is double buffered,
+// so a kernel waits for the readers of the PREVIOUS call only), tiles leave through
+// shared memory and TMA stores (also into a peer's slot), and gemm_rs folds the
+// partials inside the GEMM: a CTA reports "delivered" once its tiles for the other
+// members are stored, and its tiles of this member's own rows, which come last, add
+// the partials the peers delivered and go straight to the output.
+//
 // All flags are counters that only grow; every wait is bounded (2 s) and
-// reports through the status record.
+// reports through the status record; once a wait has run out, later waits fail at
+// once.
 #include <cstdlib>
 #include <cstring>
 
