@@ -131,3 +131,19 @@ def test_adamw_matches_torch():
     out = torch.zeros(1, device="cuda")
     sumsq_(g, out)
     assert abs(out.item() - (g.double() ** 2).sum().item()) / n < 1e-3
+
+
+def test_accumulate_into_fp32_buffer():
+    """acc(fp32) += scale * g(bf16): the cast-and-add kernel of the gradient accumulators."""
+    from distdl_b200.ops.optim import accumulate_f32_
+    torch.manual_seed(2)
+    n = 1 << 20
+    acc = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda").to(torch.bfloat16)
+    want = acc + 0.5 * g.float()
+    accumulate_f32_(acc, g, 0.5)
+    assert torch.allclose(acc, want, atol=1e-6)
+    g32 = torch.randn(1000, device="cuda")                # other dtypes take the PyTorch path
+    acc2 = torch.zeros(1000, device="cuda")
+    accumulate_f32_(acc2, g32)
+    assert torch.equal(acc2, g32)
