@@ -262,11 +262,10 @@ def body_kept_buffer_goes_stale(rank, world):
     y0 = lin(x)
     with torch.no_grad():
         lin.weight.mul_(2.0)                              # an in-place update, as an optimizer makes
-    with warnings.catch_warnings(record=True) as caught:
-        warnings.simplefilter("always")
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")                  # the one-time warning about the stale copy
         y1 = lin(x)
     assert torch.allclose(y1, 2.0 * y0, atol=1e-5)
-    assert any("auto_clear_buffer" in str(w.message) for w in caught) or True    # warned once per process
     lin.clear_weight_buffer()
     return True
 
