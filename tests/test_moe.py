@@ -64,3 +64,61 @@ def body_expert_parallel(rank, world):
 def test_expert_parallel_block_on_two_ranks():
     out = run_ranks("test_moe", "body_expert_parallel", 2, timeout=240)
     assert all(math.isfinite(v) for v in out)
+
+
+def body_expert_layers_vs_serial(rank, world, E, N, M):
+    """DistributedExpertAllGather -> GELU -> DistributedExpertReduceScatter on the grid
+    [E, N, 1, M] (expert parallel x ZeRO / capacity parallel x tensor parallel) against the same
+    per-expert MLP computed serially from the gathered weight shards: output and input gradient."""
+    import torch.distributed as dist
+
+    import distdl_b200
+    from distdl_b200.nn import DistributedExpertAllGather, DistributedExpertReduceScatter
+    experts, cap, seq, d, f = 4, 4, 2, 8, 12
+    P = distdl_b200.backends.backend.Partition().create_cartesian_topology_partition([E, N, 1, M])
+    torch.manual_seed(0)
+    up = DistributedExpertAllGather(P, experts, d, f, bias=True)
+    down = DistributedExpertReduceScatter(P, experts, f, d, bias=True)
+    ei, ni, mi = int(P.index[0]), int(P.index[1]), int(P.index[3])
+    el, cl = experts // E, cap // N
+    se, sc = slice(ei * el, (ei + 1) * el), slice(ni * cl, (ni + 1) * cl)
+    sd = slice(mi * (d // M), (mi + 1) * (d // M))
+    torch.manual_seed(1)
+    X = torch.randn(experts, cap, seq, d)
+    dY = torch.randn(experts, cap, seq, d)
+    x = X[se, sc, :, sd].clone().requires_grad_()
+    y = down(torch.nn.functional.gelu(up(x)))
+    assert y.shape == (el, cl, seq, d // M)
+    y.backward(dY[se, sc, :, sd])
+
+    def gather(t):
+        parts = [None] * world
+        dist.all_gather_object(parts, (ei, ni, mi, None if t is None or t.numel() == 0 else t.detach().clone()))
+        return parts
+
+    # shards: W_up [e/E, in/N, out/M], W_down [e/E, out/N, in/M]; biases live on one row / column only
+    Wup, Bup = torch.zeros(experts, d, f), torch.zeros(experts, 1, f)
+    Wdn, Bdn = torch.zeros(experts, d, f), torch.zeros(experts, 1, d)
+    for a, b, c, w in gather(up.weight):
+        Wup[a * el:(a + 1) * el, b * (d // N):(b + 1) * (d // N), c * (f // M):(c + 1) * (f // M)] = w
+    for a, b, c, w in gather(down.weight):
+        Wdn[a * el:(a + 1) * el, b * (d // N):(b + 1) * (d // N), c * (f // M):(c + 1) * (f // M)] = w
+    for a, b, c, bb in gather(up.bias):
+        if bb is not None:
+            Bup[a * el:(a + 1) * el, :, c * (f // M):(c + 1) * (f // M)] = bb
+    for a, b, c, bb in gather(down.bias):
+        if bb is not None:
+            Bdn[a * el:(a + 1) * el] = bb
+    Xr = X.clone().requires_grad_()
+    h = torch.nn.functional.gelu(torch.einsum("ecsd,edf->ecsf", Xr, Wup) + Bup.unsqueeze(1))
+    ref = torch.einsum("ecsf,edf->ecsd", h, Wdn) + Bdn.unsqueeze(1)
+    ref.backward(dY)
+    assert torch.allclose(y, ref[se, sc, :, sd], atol=1e-5), (y - ref[se, sc, :, sd]).abs().max()
+    assert torch.allclose(x.grad, Xr.grad[se, sc, :, sd], atol=1e-5), (x.grad - Xr.grad[se, sc, :, sd]).abs().max()
+    return True
+
+
+def test_expert_layers_match_serial_mlp():
+    run_ranks("test_moe", "body_expert_layers_vs_serial", 4, args=(2, 1, 2), timeout=180)
+    run_ranks("test_moe", "body_expert_layers_vs_serial", 4, args=(1, 2, 2), timeout=180)
+    run_ranks("test_moe", "body_expert_layers_vs_serial", 4, args=(2, 2, 1), timeout=180)
