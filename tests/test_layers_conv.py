@@ -233,3 +233,152 @@ def body_upsample(rank, world):
 
 def test_upsample_vs_serial():
     run_ranks("test_layers_conv", "body_upsample", 4, timeout=300)
+
+
+def body_losses(rank, world):
+    """All six distributed losses against their torch counterparts on the full tensors (value on
+    worker 0, gradients on every worker), mean and sum reductions."""
+    import distdl_b200.nn as dnn
+    P = _cart([0, 1, 2, 3], [2, 2])
+    torch.manual_seed(0)
+    cases = [
+        (dnn.DistributedL1Loss, torch.nn.L1Loss, lambda t: t, lambda t: t),
+        (dnn.DistributedMSELoss, torch.nn.MSELoss, lambda t: t, lambda t: t),
+        (dnn.DistributedPoissonNLLLoss, torch.nn.PoissonNLLLoss, lambda t: t, lambda t: t.abs()),
+        (dnn.DistributedBCELoss, torch.nn.BCELoss, torch.sigmoid, torch.sigmoid),
+        (dnn.DistributedBCEWithLogitsLoss, torch.nn.BCEWithLogitsLoss, lambda t: t, torch.sigmoid),
+        (dnn.DistributedKLDivLoss, torch.nn.KLDivLoss, lambda t: torch.log_softmax(t, -1),
+         lambda t: torch.softmax(t, -1)),
+    ]
+    d, m = rank // 2, rank % 2
+    sl = (slice(d * 3, (d + 1) * 3), slice(m * 4, (m + 1) * 4))
+    for Dist, Ref, fx, ft in cases:
+        for reduction in ("mean", "sum"):
+            raw_x = _sync(torch.randn(6, 8))
+            raw_t = _sync(torch.randn(6, 8))
+            xs = raw_x.clone().requires_grad_()
+            ref = Ref(reduction=reduction)(fx(xs), ft(raw_t))
+            ref.backward()
+            xl = raw_x[sl].clone().requires_grad_()
+            # softmax-type transforms act on full rows: apply them on the full tensor, then cut
+            if Dist is dnn.DistributedKLDivLoss:
+                xin = fx(raw_x)[sl].clone().requires_grad_()
+            else:
+                xin = fx(xl)
+            loss = Dist(P, reduction=reduction)(xin, ft(raw_t)[sl])
+            loss.backward()
+            if rank == 0:
+                assert abs(loss.item() - ref.item()) < 1e-5 * max(1.0, abs(ref.item())), (Dist.__name__, reduction)
+            if Dist is not dnn.DistributedKLDivLoss:
+                assert torch.allclose(xl.grad, xs.grad[sl], atol=1e-6), (Dist.__name__, reduction)
+    return True
+
+
+def test_all_losses_vs_serial():
+    run_ranks("test_layers_conv", "body_losses", 4, timeout=300)
+
+
+def body_conv_pool_other_dims(rank, world):
+    """1-D and 3-D variants, transposed feature convolutions, the selector classes, the
+    DistributedTranspose alias and the sub-tensor Interpolate against serial torch."""
+    import distdl_b200.nn as dnn
+    torch.manual_seed(0)
+    # ---- 1-D feature conv + avg pool, 3-D feature conv + max pool, through the selector
+    P1 = _cart([0, 1, 2, 3], [1, 1, 4])
+    x1 = _sync(torch.randn(2, 3, 21))
+    conv1 = dnn.DistributedConv1d(P1, in_channels=3, out_channels=5, kernel_size=3, padding=1)
+    assert isinstance(conv1, dnn.DistributedFeatureConv1d)
+    w = _sync(conv1.weight.detach().clone() if rank == 0 else torch.empty(5, 3, 3))
+    b = _sync(conv1.bias.detach().clone() if rank == 0 else torch.empty(5))
+    _, x = _scatter(P1, x1, rank, 3)
+    y = _gather(P1, conv1(x), 3)
+    if rank == 0:
+        assert torch.allclose(y, torch.nn.functional.conv1d(x1, w, b, padding=1), atol=1e-5)
+    _, x = _scatter(P1, x1, rank, 3)
+    y = _gather(P1, dnn.DistributedAvgPool1d(P1, 3, stride=3)(x), 3)
+    if rank == 0:
+        assert torch.allclose(y, torch.nn.functional.avg_pool1d(x1, 3, 3), atol=1e-6)
+    P3 = _cart([0, 1, 2, 3], [1, 1, 2, 2, 1])
+    x3 = _sync(torch.randn(1, 2, 8, 6, 5))
+    conv3 = dnn.DistributedConv3d(P3, in_channels=2, out_channels=3, kernel_size=3, padding=1)
+    assert isinstance(conv3, dnn.DistributedFeatureConv3d)
+    w = _sync(conv3.weight.detach().clone() if rank == 0 else torch.empty(3, 2, 3, 3, 3))
+    b = _sync(conv3.bias.detach().clone() if rank == 0 else torch.empty(3))
+    _, x = _scatter(P3, x3, rank, 5)
+    y = _gather(P3, conv3(x), 5)
+    if rank == 0:
+        assert torch.allclose(y, torch.nn.functional.conv3d(x3, w, b, padding=1), atol=1e-5)
+    for Pool, fn in ((dnn.DistributedMaxPool3d, torch.nn.functional.max_pool3d),
+                     (dnn.DistributedAvgPool3d, torch.nn.functional.avg_pool3d)):
+        _, x = _scatter(P3, x3, rank, 5)
+        y = _gather(P3, Pool(P3, 2, stride=2)(x), 5)
+        if rank == 0:
+            assert torch.allclose(y, fn(x3, 2, 2), atol=1e-6), Pool.__name__
+    P2 = _cart([0, 1, 2, 3], [1, 1, 2, 2])
+    x2 = _sync(torch.randn(2, 3, 10, 8))
+    _, x = _scatter(P2, x2, rank, 4)
+    y = _gather(P2, dnn.DistributedMaxPool2d(P2, 2, stride=2)(x), 4)
+    if rank == 0:
+        assert torch.allclose(y, torch.nn.functional.max_pool2d(x2, 2, 2))
+    # ---- the alias and the selector's other branches
+    assert issubclass(dnn.DistributedTranspose, dnn.Repartition)
+    Pc_x, Pc_y, Pc_w = _cart([0, 1], [1, 2, 1]), _cart([0, 1], [1, 2, 1]), _cart([0, 1, 2, 3], [2, 2, 1])
+    assert isinstance(dnn.DistributedConv1d(Pc_x, Pc_y, Pc_w, in_channels=4, out_channels=4, kernel_size=1),
+                      dnn.DistributedChannelConv1d)
+    return True
+
+
+def test_other_dimensions_selector_and_alias():
+    run_ranks("test_layers_conv", "body_conv_pool_other_dims", 4, timeout=300)
+
+
+def body_transposed_general_interpolate(rank, world):
+    """Transposed feature convolutions (1-3 D, kernels that do not cross worker boundaries), the
+    2-D and 3-D general convolutions through the selector, channel convolutions in 1-D / 3-D form
+    and the sub-tensor Interpolate module against serial torch."""
+    import distdl_b200.nn as dnn
+    torch.manual_seed(0)
+    for nd, Pshape, xshape, Cls, fn in (
+            (1, [1, 1, 4], (2, 3, 8), dnn.DistributedFeatureConvTranspose1d, torch.nn.functional.conv_transpose1d),
+            (2, [1, 1, 2, 2], (2, 3, 6, 4), dnn.DistributedFeatureConvTranspose2d, torch.nn.functional.conv_transpose2d),
+            (3, [1, 1, 2, 2, 1], (1, 2, 4, 4, 3), dnn.DistributedFeatureConvTranspose3d,
+             torch.nn.functional.conv_transpose3d)):
+        P = _cart([0, 1, 2, 3], Pshape)
+        xg = _sync(torch.randn(*xshape))
+        layer = Cls(P, xshape[1], 4, 2, stride=2)
+        w = _sync(layer.weight.detach().clone() if rank == 0 else torch.empty(xshape[1], 4, *([2] * nd)))
+        b = _sync(layer.bias.detach().clone() if rank == 0 else torch.empty(4))
+        _, x = _scatter(P, xg, rank, nd + 2)
+        y = _gather(P, layer(x), nd + 2)
+        if rank == 0:
+            assert torch.allclose(y, fn(xg, w, b, stride=2), atol=1e-5), nd
+    # ---- general convolution, 2-D (space split over two workers of the pair {0, 1}) via the selector
+    P_x, P_y, P_w = _cart([0, 1], [1, 1, 2, 1]), _cart([0, 1], [1, 1, 2, 1]), _cart([0, 1], [1, 1, 2, 1])
+    gen = dnn.DistributedConv2d(P_x, P_y, P_w, in_channels=3, out_channels=5, kernel_size=3, padding=1)
+    assert isinstance(gen, dnn.DistributedGeneralConv2d)
+    x2 = _sync(torch.randn(2, 3, 12, 5))
+    if rank in (0, 1):
+        Wg = _sync_pair(gen.weight.detach().clone() if rank == 0 else torch.empty(5, 3, 3, 3), rank)
+        bg = _sync_pair(gen.bias.detach().clone() if rank == 0 else torch.empty(5), rank)
+        xl = x2[:, :, rank * 6:(rank + 1) * 6].clone()
+        y = gen(xl)
+        want = torch.nn.functional.conv2d(x2, Wg, bg, padding=1)[:, :, rank * 6:(rank + 1) * 6]
+        assert torch.allclose(y, want, atol=1e-5)
+    # ---- Interpolate on a sub-tensor: each worker produces its slab of the global result
+    xg = _sync(torch.randn(1, 2, 16))
+    lo, hi = rank * 4, (rank + 1) * 4
+    for mode, ac in (("nearest", False), ("linear", False), ("linear", True)):
+        full = torch.nn.functional.interpolate(xg, size=32, mode=mode, **({} if mode == "nearest" else
+                                                                          {"align_corners": ac}))
+        ylo, yhi = rank * 8, (rank + 1) * 8
+        # the slab of the input that this output slab needs (one extra point on either side)
+        xlo, xhi = max(0, lo - 1), min(16, hi + 1)
+        mod = dnn.Interpolate([0, 0, xlo], [1, 2, xhi], [1, 2, 16], [0, 0, ylo], [1, 2, yhi], [1, 2, 32],
+                              mode=mode, align_corners=ac)
+        y = mod(xg[:, :, xlo:xhi].contiguous())
+        assert torch.allclose(y, full[:, :, ylo:yhi], atol=1e-5), (mode, ac)
+    return True
+
+
+def test_transposed_general_and_interpolate():
+    run_ranks("test_layers_conv", "body_transposed_general_interpolate", 4, timeout=300)
