@@ -336,3 +336,34 @@ def body_ring_attention(rank, world, causal, hq, hkv):
 def test_ring_attention_matches_serial():
     run_ranks("test_layers_linear", "body_ring_attention", 3, args=(True, 4, 2), timeout=180)
     run_ranks("test_layers_linear", "body_ring_attention", 4, args=(False, 3, 3), timeout=180)
+
+
+def body_init(rank, world):
+    """Xavier / Kaiming initialisers take their fans from the GLOBAL tensor: a [64, 32] weight
+    split over 4 workers gets the bound of the unsplit weight, on every worker."""
+    import math
+
+    import distdl_b200
+    from distdl_b200.nn import init
+    P = distdl_b200.backends.backend.Partition().create_cartesian_topology_partition([2, 2])
+    torch.manual_seed(rank)
+    w = torch.empty(32, 16)                                 # local shard of the [64, 32] weight
+    init.xavier_uniform_(P, w)
+    bound = math.sqrt(3.0) * math.sqrt(2.0 / (32 + 64))
+    assert w.abs().max() <= bound + 1e-6 and w.abs().max() > 0.8 * bound
+    init.kaiming_uniform_(P, w, a=math.sqrt(5))
+    kb = math.sqrt(3.0) * math.sqrt(2.0 / (1 + 5)) / math.sqrt(32)      # fan_in of the global weight = 32
+    assert w.abs().max() <= kb + 1e-6 and w.abs().max() > 0.8 * kb
+    init.xavier_normal_(P, w)
+    assert abs(w.std().item() - math.sqrt(2.0 / 96)) < 0.02
+    init.kaiming_normal_(P, w, mode="fan_out", nonlinearity="relu")
+    assert abs(w.std().item() - math.sqrt(2.0 / 64)) < 0.03
+    z = torch.empty(0)
+    assert init.xavier_uniform_(P, torch.empty(32, 16)[:0]).numel() == 0 and z.numel() == 0
+    init.zeros_(w)
+    assert float(w.abs().sum()) == 0.0
+    return True
+
+
+def test_initialisers_use_global_fans():
+    run_ranks("test_layers_linear", "body_init", 4, timeout=120)
