@@ -120,3 +120,18 @@ def test_dtype_tables():
     assert torch.bfloat16 in dt.torch_to_intID_dtype_dict
     back = dt.intID_to_torch_dtype_dict[dt.torch_to_intID_dtype_dict[torch.bfloat16]]
     assert back == torch.bfloat16
+
+
+def test_zero_volume_corrector():
+    """A worker without a loss value gets a scalar it can call backward on; the adjoint hands a
+    zero-volume gradient upstream.  A real tensor passes through unchanged."""
+    from distdl_b200.functional import ZeroVolumeCorrectorFunction
+    empty = zero_volume_tensor(3).requires_grad_()
+    s = ZeroVolumeCorrectorFunction.apply(empty)
+    assert s.shape == () and float(s) == 0.0
+    s.backward()
+    assert empty.grad is not None and empty.grad.numel() == 0 and empty.grad.shape[0] == 3
+    x = torch.randn(2, 2, requires_grad=True)
+    y = ZeroVolumeCorrectorFunction.apply(x)
+    y.sum().backward()
+    assert torch.equal(y, x) and torch.equal(x.grad, torch.ones(2, 2))
