@@ -6,11 +6,12 @@ import torch
 
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
-from ._linear_common import PrefetchStream, deliver_grad, derived_partition
+from ._linear_common import PrefetchStream, deliver_grad, derived_partition, relayout, root_partition, var_blocks
 from .all_gather import AllGather
 from .broadcast import Broadcast
 from .module import Module
 from .reduce_scatter import ReduceScatter
+from .repartition import Repartition
 
 
 def _expert_matmul(x, w):
@@ -31,7 +32,13 @@ class DistributedExpertAllGather(Module):
     ``N`` along the input features, gathered on use; bias ``[experts/E, 1,
     out/M]`` on the first ``N`` row.  Forward: gather weight, broadcast bias,
     all-gather the tokens over ``M`` (features, or sequence), grouped GEMM.
-    ``auto_clear_buffer=False`` keeps the gathered weights across micro-batches."""
+    ``auto_clear_buffer=False`` keeps the gathered weights across micro-batches.
+
+    ``collect_state=True``: ``state_dict()`` holds, on the first worker only, the whole weight
+    ``[experts, in, out]`` and bias ``[experts, 1, out]`` (with ``geglu=True`` the two halves of
+    the output features in the order a single worker would store them); ``load_state_dict``
+    takes that layout on the first worker and scatters it
+    (``src/distdl/nn/linear_ag_expert.py:247-323``)."""
 
     def __init__(self, P_expert_emb, num_experts, in_features, out_features, bias=True, device=None, dtype=None,
                  P_weight=None, P_bias=None, collect_state=False, scale_backward=None, P_expert_seq=None,
@@ -77,6 +84,67 @@ class DistributedExpertAllGather(Module):
         self.prefetch = PrefetchStream(device)
         self.weight_buffer = None
         self.bias_buffer = None
+        self._register_state_dict_hook(self.gather_state_dict)
+        self._register_load_state_dict_pre_hook(self.scatter_state_dict)
+        if collect_state:
+            self.P_root = root_partition(P_weight)
+            self.gather_weight = Repartition(P_weight, self.P_root, preserve_batch=False)
+            self.scatter_weight = Repartition(self.P_root, P_weight, preserve_batch=False)
+            if bias:
+                self.gather_bias = Repartition(self.P_bias, self.P_root, preserve_batch=False)
+                self.scatter_bias = Repartition(self.P_root, self.P_bias, preserve_batch=False)
+
+    def _geglu_blocks(self):
+        return var_blocks(self.out_features, int(self.P_weight.shape[-1]), geglu=True) if self.geglu else None
+
+    def geglu_weight_to_serial(self, weight):
+        """Output features from the per-worker order ``(worker, half)`` to the serial ``(half, worker)``."""
+        return relayout(weight, -1, self._geglu_blocks(), to_serial=True)
+
+    def geglu_weight_to_parallel(self, weight):
+        return relayout(weight, -1, self._geglu_blocks(), to_serial=False)
+
+    def gather_state_dict(self, module, destination, prefix, *args):
+        if not (getattr(self, "collect_state", False) and self.P_expert_emb.active):
+            return destination
+        weight_key, bias_key = prefix + "weight", prefix + "bias"
+        if self.use_bias:
+            bias = destination.pop(bias_key).detach()
+            if self.P_bias.active or self.P_root.active:
+                bias = self.gather_bias(bias)
+        weight = self.gather_weight(destination.pop(weight_key).detach())
+        if self.P_root.active:
+            destination[weight_key] = self.geglu_weight_to_serial(weight)
+            if self.use_bias:
+                destination[bias_key] = self.geglu_weight_to_serial(bias)
+        return destination
+
+    def scatter_state_dict(self, destination, prefix, *args):
+        if not (getattr(self, "collect_state", False) and self.P_expert_emb.active):
+            return destination
+        weight_key, bias_key = prefix + "weight", prefix + "bias"
+        dev = self.P_weight.device
+        weight = destination.pop(weight_key, None)
+        if self.P_root.active:
+            weight = self.geglu_weight_to_parallel(weight.to(dev))
+        else:
+            weight = zero_volume_tensor(device=dev, dtype=self.weight.dtype)
+        destination[weight_key] = self.scatter_weight(weight)
+        if self.use_bias:
+            bias = destination.pop(bias_key, None)
+            if self.P_root.active:
+                bias = self.geglu_weight_to_parallel(bias.to(dev))
+            else:
+                bias = zero_volume_tensor(device=dev, dtype=self.weight.dtype)
+            if self.P_bias.active or self.P_root.active:
+                bias = self.scatter_bias(bias)
+            destination[bias_key] = bias if self.P_bias.active else zero_volume_tensor(device=dev,
+                                                                                     dtype=self.weight.dtype)
+        return destination
+
+    def extra_repr(self):
+        return (f"in_features={self.in_features}, out_features={self.out_features}, "
+                f"num_experts={self.num_experts}, bias={self.use_bias}")
 
     def reset_parameters(self):
         bound = 1 / math.sqrt(self.in_features) if self.in_features > 0 else 0

@@ -6,12 +6,13 @@ import torch
 
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
-from ._linear_common import PrefetchStream, deliver_grad, derived_partition
+from ._linear_common import PrefetchStream, deliver_grad, derived_partition, root_partition
 from .all_gather import AllGather
 from .broadcast import Broadcast
 from .linear_ag_expert import _expert_matmul
 from .module import Module
 from .reduce_scatter import ReduceScatter
+from .repartition import Repartition
 
 
 class DistributedExpertReduceScatter(Module):
@@ -22,7 +23,11 @@ class DistributedExpertReduceScatter(Module):
     grouped GEMM on the local feature slice, reduce-scatter of the partial
     outputs over ``M`` (features, or sequence with ``P_expert_seq = [E, N, S, 1]``).
     The bias ``[experts/E, 1, 1 -> out]`` is stored once per expert group and
-    added on the first tensor-parallel column only."""
+    added on the first tensor-parallel column only.
+
+    ``collect_state=True``: ``state_dict()`` holds, on the first worker only, the whole weight
+    ``[experts, out, in]`` and bias ``[experts, 1, out]``; ``load_state_dict`` scatters that
+    layout from the first worker (``src/distdl/nn/linear_rs_expert.py:253-298``)."""
 
     def __init__(self, P_expert_emb, num_experts, in_features, out_features, bias=True, device=None, dtype=None,
                  P_store_bias=None, P_apply_bias=None, P_weight=None, collect_state=False, scale_backward=None,
@@ -70,6 +75,54 @@ class DistributedExpertReduceScatter(Module):
         self.prefetch = PrefetchStream(device)
         self.weight_buffer = None
         self.bias_buffer = None
+        self._register_state_dict_hook(self.gather_state_dict)
+        self._register_load_state_dict_pre_hook(self.scatter_state_dict)
+        if collect_state:
+            self.P_root = root_partition(P_weight)
+            self.gather_weight = Repartition(P_weight, self.P_root, preserve_batch=False)
+            self.scatter_weight = Repartition(self.P_root, P_weight, preserve_batch=False)
+            if bias:
+                self.gather_bias = Repartition(self.P_store_bias, self.P_root, preserve_batch=False)
+                self.scatter_bias = Repartition(self.P_root, self.P_store_bias, preserve_batch=False)
+
+    def gather_state_dict(self, module, destination, prefix, *args):
+        if not (getattr(self, "collect_state", False) and self.P_expert_emb.active):
+            return destination
+        weight_key, bias_key = prefix + "weight", prefix + "bias"
+        has_bias_entry = self.use_bias and bias_key in destination
+        if has_bias_entry:
+            bias = destination.pop(bias_key).detach()
+        if self.use_bias and (self.P_store_bias.active or self.P_root.active):
+            bias = self.gather_bias(bias)
+        weight = self.gather_weight(destination.pop(weight_key).detach())
+        if self.P_root.active:
+            destination[weight_key] = weight
+            if self.use_bias:
+                destination[bias_key] = bias
+        return destination
+
+    def scatter_state_dict(self, destination, prefix, *args):
+        if not (getattr(self, "collect_state", False) and self.P_expert_emb.active):
+            return destination
+        weight_key, bias_key = prefix + "weight", prefix + "bias"
+        dev = self.P_weight.device
+        weight = destination.pop(weight_key, None)
+        weight = weight.to(dev) if self.P_root.active else zero_volume_tensor(device=dev, dtype=self.weight.dtype)
+        destination[weight_key] = self.scatter_weight(weight)
+        if self.use_bias:
+            bias = destination.pop(bias_key, None)
+            bias = bias.to(dev) if self.P_root.active else zero_volume_tensor(device=dev, dtype=self.weight.dtype)
+            if self.P_store_bias.active or self.P_root.active:
+                bias = self.scatter_bias(bias)
+            if self.P_store_bias.active:
+                destination[bias_key] = bias
+            elif self.P_apply_bias.active:
+                destination[bias_key] = zero_volume_tensor(device=dev, dtype=self.weight.dtype)
+        return destination
+
+    def extra_repr(self):
+        return (f"in_features={self.in_features}, out_features={self.out_features}, "
+                f"num_experts={self.num_experts}, bias={self.use_bias}")
 
     def reset_parameters(self):
         bound = 1 / math.sqrt(self.in_features) if self.in_features > 0 else 0

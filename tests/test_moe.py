@@ -122,3 +122,56 @@ def test_expert_layers_match_serial_mlp():
     run_ranks("test_moe", "body_expert_layers_vs_serial", 4, args=(2, 1, 2), timeout=180)
     run_ranks("test_moe", "body_expert_layers_vs_serial", 4, args=(1, 2, 2), timeout=180)
     run_ranks("test_moe", "body_expert_layers_vs_serial", 4, args=(2, 2, 1), timeout=180)
+
+
+def body_expert_collect_state(rank, world, E, N, M, geglu):
+    """collect_state=True: the first worker loads whole-layer tensors ([experts, in, out] /
+    [experts, out, in], biases [experts, 1, out]); the layers then reproduce the serial per-expert
+    MLP (with geglu: value * gelu(gate) on the serial halves), and state_dict() returns the same
+    tensors on the first worker and nothing on the others."""
+    import distdl_b200
+    from distdl_b200.nn import DistributedExpertAllGather, DistributedExpertReduceScatter
+    experts, cap, seq, d, f = 4, 4, 2, 8, 16
+    fo = f // 2 if geglu else f
+    P = distdl_b200.backends.backend.Partition().create_cartesian_topology_partition([E, N, 1, M])
+    up = DistributedExpertAllGather(P, experts, d, f, bias=True, collect_state=True, geglu=geglu)
+    down = DistributedExpertReduceScatter(P, experts, fo, d, bias=True, collect_state=True)
+    torch.manual_seed(3)
+    Wup, Bup = torch.randn(experts, d, f), torch.randn(experts, 1, f)
+    Wdn, Bdn = torch.randn(experts, d, fo), torch.randn(experts, 1, d)
+    first = rank == 0
+    up.load_state_dict({"weight": Wup.clone(), "bias": Bup.clone()} if first else {})
+    down.load_state_dict({"weight": Wdn.clone(), "bias": Bdn.clone()} if first else {})
+    ei, ni, mi = int(P.index[0]), int(P.index[1]), int(P.index[3])
+    el, cl = experts // E, cap // N
+    se, sc = slice(ei * el, (ei + 1) * el), slice(ni * cl, (ni + 1) * cl)
+    sd = slice(mi * (d // M), (mi + 1) * (d // M))
+    X = torch.randn(experts, cap, seq, d)
+    h = up(X[se, sc, :, sd].clone())
+    if geglu:                                   # local layout [value | gate] of this worker's share
+        a, g = h.chunk(2, dim=-1)
+        h = a * torch.nn.functional.gelu(g)
+    else:
+        h = torch.nn.functional.gelu(h)
+    y = down(h)
+    hr = torch.einsum("ecsd,edf->ecsf", X, Wup) + Bup.unsqueeze(1)
+    if geglu:
+        a, g = hr.chunk(2, dim=-1)
+        hr = a * torch.nn.functional.gelu(g)
+    else:
+        hr = torch.nn.functional.gelu(hr)
+    ref = torch.einsum("ecsf,edf->ecsd", hr, Wdn) + Bdn.unsqueeze(1)
+    assert torch.allclose(y, ref[se, sc, :, sd], atol=1e-4), (y - ref[se, sc, :, sd]).abs().max()
+    su, sdn = up.state_dict(), down.state_dict()
+    if first:
+        assert torch.equal(su["weight"], Wup) and torch.equal(su["bias"], Bup)
+        assert torch.equal(sdn["weight"], Wdn) and torch.equal(sdn["bias"], Bdn)
+    else:
+        assert len(su) == 0 and len(sdn) == 0
+    return True
+
+
+def test_expert_layers_collect_state_round_trip():
+    run_ranks("test_moe", "body_expert_collect_state", 4, args=(2, 1, 2, False), timeout=180)
+    run_ranks("test_moe", "body_expert_collect_state", 4, args=(1, 2, 2, True), timeout=180)
+    run_ranks("test_moe", "body_expert_collect_state", 4, args=(2, 2, 1, True), timeout=180)
