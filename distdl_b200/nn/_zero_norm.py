@@ -58,6 +58,16 @@ class _ZeroNormBase(Module):
             self.gather = Repartition(self.P_w, self.P_root, preserve_batch=False)
             self.scatter = Repartition(self.P_root, self.P_w, preserve_batch=False)
 
+    def reset_parameters(self):
+        """Weight to one, bias to zero (``src/distdl/nn/layernorm_zero.py:162-165``)."""
+        with torch.no_grad():
+            for n in self.param_names:
+                getattr(self, n).fill_(1.0 if n == "weight" else 0.0)
+        self.buffers_gathered = None
+
+    def extra_repr(self):
+        return f"normalized_shape={self.normalized_shape}"
+
     def gather_state_dict(self, module, destination, prefix, *args):
         if not (self.collect_state and self.P_x.active):
             return destination

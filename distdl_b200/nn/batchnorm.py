@@ -4,9 +4,10 @@ import torch
 
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
-from ._linear_common import derived_partition
+from ._linear_common import derived_partition, root_partition
 from .broadcast import Broadcast
 from .module import Module
+from .repartition import Repartition
 from .sum_reduce import SumReduce
 
 
@@ -15,7 +16,12 @@ class DistributedBatchNorm(Module):
     partition ``P_x`` (the feature dimension may be split too).  Per-feature
     sums are reduced onto ``P_sum = [1, F, 1, ...]`` (one worker per feature
     shard), turned into mean / variance there, and broadcast back; running
-    statistics and the affine ``gamma`` / ``beta`` live on ``P_sum``."""
+    statistics and the affine ``gamma`` / ``beta`` live on ``P_sum``.
+
+    ``collect_state=True``: ``state_dict()`` holds ``gamma``, ``beta`` and the running statistics of
+    ALL features, shape ``[1, F, 1, ...]``, on the first worker only, and ``load_state_dict`` takes
+    them there (``src/distdl/nn/batchnorm.py:136-190``).  ``prefetch_weights()`` broadcasts
+    ``gamma`` / ``beta`` ahead of the next forward (``:290-304``)."""
 
     def __init__(self, P_x, num_features, eps=1e-05, momentum=0.1, affine=True, track_running_stats=True,
                  device=None, dtype=None, collect_state=False, scale_backward=None):
@@ -61,6 +67,49 @@ class DistributedBatchNorm(Module):
                 self.register_buffer("running_mean", zero_volume_tensor(device=device, dtype=dtype))
                 self.register_buffer("running_var", zero_volume_tensor(device=device, dtype=dtype))
         self.global_count = None
+        self.gamma_buffer = self.beta_buffer = None
+        self._register_state_dict_hook(self.gather_state_dict)
+        self._register_load_state_dict_pre_hook(self.scatter_state_dict)
+        if collect_state:
+            self.P_root = root_partition(P_x)
+            self.gather_affine = Repartition(self.P_sum, self.P_root, preserve_batch=False)
+            self.scatter_affine = Repartition(self.P_root, self.P_sum, preserve_batch=False)
+
+    def extra_repr(self):
+        return f"num_features={self.num_features}"
+
+    def _state_names(self):
+        names = ["gamma", "beta"] if self.affine else []
+        return names + (["running_mean", "running_var"] if self.track_running_stats else [])
+
+    def gather_state_dict(self, module, destination, prefix, *args):
+        if not (getattr(self, "collect_state", False) and self.P_x.active):
+            return destination
+        for name in self._state_names():
+            t = destination.pop(prefix + name).detach()
+            if self.P_sum.active:                     # the first worker is a member of P_sum
+                t = self.gather_affine(t)
+            if self.P_root.active:
+                destination[prefix + name] = t
+        return destination
+
+    def scatter_state_dict(self, destination, prefix, *args):
+        if not (getattr(self, "collect_state", False) and self.P_x.active):
+            return destination
+        dev = self.P_x.device
+        for name in self._state_names():
+            t = destination.pop(prefix + name, None)
+            dtype = getattr(self, name).dtype
+            t = t.to(dev) if self.P_root.active else zero_volume_tensor(device=dev, dtype=dtype)
+            if self.P_sum.active:
+                t = self.scatter_affine(t)
+            destination[prefix + name] = t
+        return destination
+
+    def prefetch_weights(self):
+        if self.affine and self.P_x.active:
+            self.gamma_buffer = self.bc_g(self.gamma)
+            self.beta_buffer = self.bc_b(self.beta)
 
     def _distdl_module_setup(self, input):
         self._distdl_is_setup = True
@@ -95,5 +144,8 @@ class DistributedBatchNorm(Module):
             var = self.bc_rv(self.running_var)
         y = (input - mean) / torch.sqrt(var + self.eps)
         if self.affine:
-            y = self.bc_g(self.gamma) * y + self.bc_b(self.beta)
+            if self.gamma_buffer is None:
+                self.prefetch_weights()
+            y = self.gamma_buffer * y + self.beta_buffer
+            self.gamma_buffer = self.beta_buffer = None
         return y

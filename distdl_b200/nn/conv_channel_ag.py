@@ -13,6 +13,7 @@ from .all_gather import AllGather
 from .broadcast import Broadcast
 from .conv_channel import _CONV, _CONVT, _expand
 from .module import Module
+from .repartition import Repartition
 
 
 class _ChannelConvNd(Module):
@@ -68,6 +69,70 @@ class _ChannelConvNd(Module):
         else:
             self.register_parameter("bias", None)
         self.reset_parameters()
+        # the weight dimension that is split over the workers: out channels are dim 0 of a
+        # convolution kernel and dim 1 of a transposed one, in channels the other way round
+        self.split_dim = 0 if (self.shard == "out") != self.transposed else 1
+        self._register_state_dict_hook(self.gather_state_dict)
+        self._register_load_state_dict_pre_hook(self.scatter_state_dict)
+        if collect_state:
+            self.P_root = root_partition(P_x)
+            self.gather_weight = Repartition(self.P_weight, self.P_root, preserve_batch=False)
+            self.scatter_weight = Repartition(self.P_root, self.P_weight, preserve_batch=False)
+            if bias and self.shard == "out":
+                self.gather_bias = Repartition(self.P_weight, self.P_root, preserve_batch=False)
+                self.scatter_bias = Repartition(self.P_root, self.P_weight, preserve_batch=False)
+
+    def _to_grid(self, w):
+        """Puts the split dimension of a kernel where ``P_weight = [1, M, 1, ...]`` splits."""
+        return w.transpose(0, 1).contiguous() if self.split_dim == 0 and w.dim() > 1 else w
+
+    def gather_state_dict(self, module, destination, prefix, *args):
+        """``collect_state=True``: the whole kernel (PyTorch layout) and bias on the first worker
+        only (``src/distdl/nn/conv_channel_ag.py:264-300``)."""
+        if not (getattr(self, "collect_state", False) and self.P_x.active):
+            return destination
+        weight_key, bias_key = prefix + "weight", prefix + "bias"
+        bias = destination.pop(bias_key, None)
+        if self.use_bias and self.shard == "out" and self.P_weight.active:
+            shape = [1] * self.P_x.dim
+            shape[1] = -1
+            bias = self.gather_bias(bias.detach().reshape(shape))
+        weight = destination.pop(weight_key).detach()
+        if self.P_weight.active:
+            weight = self.gather_weight(self._to_grid(weight))
+        if self.P_root.active:
+            destination[weight_key] = self._to_grid(weight).contiguous()
+            if self.use_bias:
+                destination[bias_key] = bias.detach().reshape(-1)
+        return destination
+
+    def scatter_state_dict(self, destination, prefix, *args):
+        if not (getattr(self, "collect_state", False) and self.P_x.active):
+            return destination
+        weight_key, bias_key = prefix + "weight", prefix + "bias"
+        dev, dt = self._device, self.weight.dtype
+        weight, bias = destination.pop(weight_key, None), destination.pop(bias_key, None)
+        weight = self._to_grid(weight.to(dev)) if self.P_root.active else zero_volume_tensor(device=dev, dtype=dt)
+        if self.P_weight.active:
+            weight = self._to_grid(self.scatter_weight(weight)).contiguous()
+        destination[weight_key] = weight
+        if self.use_bias:
+            if self.shard == "out":
+                shape = [1] * self.P_x.dim
+                shape[1] = -1
+                bias = bias.to(dev).reshape(shape) if self.P_root.active else zero_volume_tensor(device=dev, dtype=dt)
+                if self.P_weight.active:
+                    bias = self.scatter_bias(bias).reshape(-1)
+            elif not self.P_root.active:
+                bias = zero_volume_tensor(device=dev, dtype=dt)
+            else:
+                bias = bias.to(dev)
+            destination[bias_key] = bias
+        return destination
+
+    def extra_repr(self):
+        return (f"{self.in_channels}, {self.out_channels}, kernel_size={self.kernel_size}, stride={self.stride}, "
+                f"padding={self.padding}, dilation={self.dilation}, groups={self.groups}, bias={self.use_bias}")
 
     def reset_parameters(self):
         fan_in = (self.out_channels if self.transposed else self.in_channels) // self.groups * \
@@ -102,8 +167,6 @@ class _ChannelAllGatherConv(_ChannelConvNd):
             return
         self.all_gather = AllGather(self.P_x, axes_all_gather=(1,))
         self.broadcast_bias = Broadcast(self.P_weight, self.P_x, preserve_batch=False) if self.use_bias else None
-        if self.collect_state:
-            self.P_root = root_partition(self.P_x)
 
     def forward(self, input):
         if not self.P_x.active:

@@ -77,6 +77,27 @@ class DistributedFeatureConvBase(Module, HaloMixin, ConvMixin):
         self.halo_layer = None
         self.needed_slices = None
         self.pad_tuple = None
+        self._register_state_dict_hook(self.gather_state_dict)
+        self._register_load_state_dict_pre_hook(self.scatter_state_dict)
+
+    def gather_state_dict(self, module, destination, prefix, *args):
+        """``collect_state=True``: only the worker that stores the kernel keeps ``weight`` / ``bias``
+        in its state dict (``src/distdl/nn/conv_feature.py:215-226``)."""
+        if getattr(self, "collect_state", False) and self.P_x.active and not self.P_wb_cart.active:
+            destination.pop(prefix + "weight", None)
+            destination.pop(prefix + "bias", None)
+        return destination
+
+    def scatter_state_dict(self, destination, prefix, *args):
+        """``collect_state=True``: the other workers load their zero-volume stand-ins, whatever
+        (if anything) the given state dict holds for this layer (``:228-243``)."""
+        if getattr(self, "collect_state", False) and self.P_x.active and not self.P_wb_cart.active:
+            destination[prefix + "weight"] = self.weight.detach().clone()
+            if self.use_bias:
+                destination[prefix + "bias"] = self.bias.detach().clone()
+            else:
+                destination.pop(prefix + "bias", None)
+        return destination
 
     def _compute_local_padding(self, padding):
         """The global zero padding only applies where a worker touches the boundary."""

@@ -49,6 +49,7 @@ class DistributedEmbedding(Module):
                                              requires_grad=not _freeze)
         else:
             self.register_buffer("weight", zero_volume_tensor(device=device, requires_grad=True, dtype=dtype))
+        self.weight_buffer = None
         self.reset_parameters(_weight)
         self._register_state_dict_hook(self.gather_state_dict)
         self._register_load_state_dict_pre_hook(self.scatter_state_dict)
@@ -94,14 +95,25 @@ class DistributedEmbedding(Module):
         destination[key] = zero_volume_tensor(device=self._device, dtype=self.dtype)
         return destination
 
-    def forward(self, input):
+    def extra_repr(self):
+        return f"num_embeddings={self.num_embeddings}, embedding_dim={self.embedding_dim}"
+
+    def prefetch_weights(self):
+        """Broadcasts the table over the data-parallel workers ahead of the next forward
+        (``src/distdl/nn/embedding.py:213-220``)."""
         if not self.P_x.active:
-            return input
+            return
         w = self.weight
         if self.P_weight_bcast.active:
             w = w.reshape([1] * (self.P_x.dim - 2) + list(self.weight.shape))
-        w = self.broadcast_weight(w)
-        w = w.reshape(self.num_embeddings, -1)
+        self.weight_buffer = self.broadcast_weight(w).reshape(self.num_embeddings, -1)
+
+    def forward(self, input):
+        if not self.P_x.active:
+            return input
+        if self.weight_buffer is None:
+            self.prefetch_weights()
+        w, self.weight_buffer = self.weight_buffer, None
         if self.max_norm is None and not self.scale_grad_by_freq and not self.sparse:
             return ops.embedding(input, w, self.padding_idx)
         return torch.nn.functional.embedding(input, w, self.padding_idx, self.max_norm, self.norm_type,

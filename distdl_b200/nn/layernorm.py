@@ -70,6 +70,23 @@ class DistributedLayerNorm(Module):
         else:
             self.register_parameter("weight", None)
             self.register_parameter("bias", None)
+        self.weight_buffer = self.bias_buffer = None
+
+    def reset_parameters(self):
+        if self.elementwise_affine and self.P_w.active:
+            with torch.no_grad():
+                self.weight.fill_(1.0)
+                self.bias.zero_()
+
+    def extra_repr(self):
+        return f"normalized_shape={self.normalized_shape}"
+
+    def prefetch_weights(self):
+        """Broadcasts the affine parameters ahead of the next forward
+        (``src/distdl/nn/layernorm.py:249-263``)."""
+        if self.P_x.active and self.elementwise_affine:
+            self.weight_buffer = self.broadcast_weight(self.weight)
+            self.bias_buffer = self.broadcast_bias(self.bias)
 
     def gather_state_dict(self, module, destination, prefix, *args):
         if not (self.collect_state and self.P_x.active and self.elementwise_affine):
@@ -100,8 +117,10 @@ class DistributedLayerNorm(Module):
             return input
         w = b = None
         if self.elementwise_affine:
-            w = self.broadcast_weight(self.weight)
-            b = self.broadcast_bias(self.bias)
+            if self.weight_buffer is None:
+                self.prefetch_weights()
+            w, b = self.weight_buffer, self.bias_buffer
+            self.weight_buffer = self.bias_buffer = None
         nn = len(self.normalized_shape)
         if self.num_reduce == 1:
             if nn == 1:

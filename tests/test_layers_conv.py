@@ -382,3 +382,95 @@ def body_transposed_general_interpolate(rank, world):
 
 def test_transposed_general_and_interpolate():
     run_ranks("test_layers_conv", "body_transposed_general_interpolate", 4, timeout=300)
+
+
+def body_collect_state_bn_conv(rank, world):
+    """collect_state=True on DistributedBatchNorm (features split over 2 workers, the rest over 2)
+    and DistributedFeatureConv2d: the first worker loads a serial module's tensors, the layers
+    reproduce the serial module, and state_dict() returns whole tensors on the first worker only."""
+    from distdl_b200.nn import DistributedBatchNorm, DistributedFeatureConv2d
+    torch.manual_seed(0)
+    first = rank == 0
+    # batch norm, evaluation mode: uses the loaded running statistics and affine parameters
+    P = _cart([0, 1, 2, 3], [2, 2, 1])
+    ref = torch.nn.BatchNorm1d(6)
+    with torch.no_grad():
+        for t in (ref.weight, ref.bias, ref.running_mean):
+            t.copy_(_sync(torch.randn(6)))
+        ref.running_var.copy_(_sync(torch.rand(6) + 0.5))
+    bn = DistributedBatchNorm(P, 6, collect_state=True)
+    serial = {"gamma": ref.weight.detach().reshape(1, 6, 1), "beta": ref.bias.detach().reshape(1, 6, 1),
+              "running_mean": ref.running_mean.reshape(1, 6, 1), "running_var": ref.running_var.reshape(1, 6, 1)}
+    bn.load_state_dict({k: v.clone() for k, v in serial.items()} if first else {})
+    bn.eval()
+    ref.eval()
+    xg = _sync(torch.randn(4, 6, 5))
+    _, x = _scatter(P, xg, rank, 3)
+    y = _gather(P, bn(x), 3)
+    if first:
+        assert torch.allclose(y, ref(xg), atol=1e-5), (y - ref(xg)).abs().max()
+    sd = bn.state_dict()
+    if first:
+        assert list(sd) == list(serial)
+        for k, v in serial.items():
+            assert torch.equal(sd[k], v), k
+    else:
+        assert len(sd) == 0, list(sd)
+    # feature convolution: the kernel lives on the first worker only
+    P4 = _cart([0, 1, 2, 3], [1, 1, 2, 2])
+    conv = DistributedFeatureConv2d(P4, 3, 4, 3, padding=1, collect_state=True)
+    cref = torch.nn.Conv2d(3, 4, 3, padding=1)
+    with torch.no_grad():
+        cref.weight.copy_(_sync(cref.weight.detach().clone()))
+        cref.bias.copy_(_sync(cref.bias.detach().clone()))
+    conv.load_state_dict(cref.state_dict() if first else {})
+    xg = _sync(torch.randn(2, 3, 8, 6))
+    _, x = _scatter(P4, xg, rank, 4)
+    y = _gather(P4, conv(x), 4)
+    sd = conv.state_dict()
+    if first:
+        assert torch.allclose(y, cref(xg), atol=1e-5)
+        assert torch.equal(sd["weight"], cref.weight) and torch.equal(sd["bias"], cref.bias)
+    else:
+        assert len(sd) == 0, list(sd)
+    return True
+
+
+def test_collect_state_batchnorm_and_feature_conv():
+    run_ranks("test_layers_conv", "body_collect_state_bn_conv", 4, timeout=300)
+
+
+def body_collect_state_channel_convs(rank, world):
+    """collect_state=True on the channel all-gather / reduce-scatter convolutions, plain (1-D) and
+    transposed (2-D), on [D=2, M=2, 1, ...]: a serial PyTorch module's state dict is loaded on the
+    first worker, the layer reproduces the module, and state_dict() gives the tensors back there."""
+    from distdl_b200 import nn
+    torch.manual_seed(0)
+    first = rank == 0
+    d, m = rank // 2, rank % 2
+    cases = [(nn.DistributedChannelAllGatherConv1d, torch.nn.Conv1d, 1, dict(padding=1)),
+             (nn.DistributedChannelReduceScatterConv1d, torch.nn.Conv1d, 1, dict(padding=1)),
+             (nn.DistributedChannelAllGatherConvTranspose2d, torch.nn.ConvTranspose2d, 2, dict(stride=2)),
+             (nn.DistributedChannelReduceScatterConvTranspose2d, torch.nn.ConvTranspose2d, 2, dict(stride=2))]
+    for cls, serial_cls, nd, kw in cases:
+        P = _cart([0, 1, 2, 3], [2, 2] + [1] * nd)
+        serial = serial_cls(6, 8, 3, **kw)
+        with torch.no_grad():
+            for t in serial.parameters():
+                t.copy_(_sync(t.detach().clone()))
+        layer = cls(P, 6, 8, 3, collect_state=True, **kw)
+        layer.load_state_dict(serial.state_dict() if first else {})
+        xg = _sync(torch.randn(4, 6, *([7] * nd)))
+        y = layer(xg[d * 2:(d + 1) * 2, m * 3:(m + 1) * 3].clone())
+        want = serial(xg)[d * 2:(d + 1) * 2, m * 4:(m + 1) * 4]
+        assert torch.allclose(y, want, atol=1e-5), (cls.__name__, (y - want).abs().max())
+        sd = layer.state_dict()
+        if first:
+            assert torch.equal(sd["weight"], serial.weight) and torch.equal(sd["bias"], serial.bias), cls.__name__
+        else:
+            assert len(sd) == 0, (cls.__name__, list(sd))
+    return True
+
+
+def test_collect_state_channel_convs():
+    run_ranks("test_layers_conv", "body_collect_state_channel_convs", 4, timeout=300)
