@@ -178,7 +178,8 @@ class _ChannelAllGatherConv(_ChannelConvNd):
 
 
 def _make(base, nd, transposed, name, doc):
-    return type(name, (base,), {"num_dimensions": nd, "transposed": transposed, "__doc__": doc})
+    return type(name, (base,), {"num_dimensions": nd, "transposed": transposed, "__doc__": doc,
+                                "__module__": base.__module__})
 
 
 _DOC = "Channel all-gather {}convolution, {}-D (see the base class)."
