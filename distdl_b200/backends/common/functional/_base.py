@@ -40,7 +40,8 @@ def scaled(grad, scale_backward):
 
 
 def bind_functional(transport, overrides=None):
-    """Namespace with the seven Function classes bound to ``transport``.
+    """Namespace with the Function classes of the seven primitives (and the accumulate form of the
+    halo exchange) bound to ``transport``.
     ``overrides`` maps a class name to a replacement class (the native backend
     swaps in its fused-kernel versions)."""
     from . import all_gather, all_sum_reduce, broadcast, halo_exchange, reduce_scatter, repartition, sum_reduce
@@ -48,7 +49,7 @@ def bind_functional(transport, overrides=None):
     for mod, name in ((broadcast, "BroadcastFunction"), (sum_reduce, "SumReduceFunction"),
                       (all_sum_reduce, "AllSumReduceFunction"), (all_gather, "AllGatherFunction"),
                       (reduce_scatter, "ReduceScatterFunction"), (repartition, "RepartitionFunction"),
-                      (halo_exchange, "HaloExchangeFunction")):
+                      (halo_exchange, "HaloExchangeFunction"), (halo_exchange, "HaloAccumulateFunction")):
         base = (overrides or {}).get(name) or getattr(mod, name)
         bound = type(name, (base,), {"_transport": transport})
         setattr(ns, name, bound)

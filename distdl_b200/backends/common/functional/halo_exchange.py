@@ -25,6 +25,61 @@ def _shape(sl):
     return tuple(max(0, s.stop - s.start) for s in sl)
 
 
+def fill_ghosts(t, x, P_x, slices, neighbor_ranks):
+    """The exchange itself: a copy of ``x`` whose ghost regions hold the neighbours' bulk regions."""
+    out = x.detach().clone()
+    for d in range(P_x.dim):
+        lb, lg, rb, rg = slices[d]
+        left, right = neighbor_ranks[d]
+        sends, recvs, targets = [], [], []
+        if left != PROC_NULL:
+            if _volume(lb):
+                sends.append((left, out[lb]))
+            if _volume(lg):
+                recvs.append((left, _shape(lg), out.dtype))
+                targets.append(lg)
+        if right != PROC_NULL:
+            if _volume(rb):
+                sends.append((right, out[rb]))
+            if _volume(rg):
+                recvs.append((right, _shape(rg), out.dtype))
+                targets.append(rg)
+        got = t.exchange(sends, recvs, list(P_x.ranks))
+        for sl, g in zip(targets, got):
+            out[sl] = g.to(out.device)
+    return out
+
+
+def fold_ghosts(t, x, P_x, slices, neighbor_ranks):
+    """The adjoint of :func:`fill_ghosts`: ghost regions travel to the neighbours they came from,
+    are ADDED to the bulk regions there, and are cleared here."""
+    g = x.detach().clone()
+    for d in reversed(range(P_x.dim)):
+        lb, lg, rb, rg = slices[d]
+        left, right = neighbor_ranks[d]
+        sends, recvs, targets = [], [], []
+        if left != PROC_NULL:
+            if _volume(lg):
+                sends.append((left, g[lg].clone()))
+            if _volume(lb):
+                recvs.append((left, _shape(lb), g.dtype))
+                targets.append(lb)
+        if right != PROC_NULL:
+            if _volume(rg):
+                sends.append((right, g[rg].clone()))
+            if _volume(rb):
+                recvs.append((right, _shape(rb), g.dtype))
+                targets.append(rb)
+        got = t.exchange(sends, recvs, list(P_x.ranks))
+        if left != PROC_NULL and _volume(lg):
+            g[lg] = 0
+        if right != PROC_NULL and _volume(rg):
+            g[rg] = 0
+        for sl, r in zip(targets, got):
+            g[sl] += r.to(g.device)
+    return g
+
+
 class HaloExchangeFunction(TransportBound, torch.autograd.Function):
     @staticmethod
     def forward(ctx, input, P_x, slices, buffers, neighbor_ranks):
@@ -34,27 +89,7 @@ class HaloExchangeFunction(TransportBound, torch.autograd.Function):
             ctx.identity = True
             return input
         ctx.identity = False
-        t = cls.transport()
-        out = input.detach().clone()
-        for d in range(P_x.dim):
-            lb, lg, rb, rg = slices[d]
-            left, right = neighbor_ranks[d]
-            sends, recvs, targets = [], [], []
-            if left != PROC_NULL:
-                if _volume(lb):
-                    sends.append((left, out[lb]))
-                if _volume(lg):
-                    recvs.append((left, _shape(lg), out.dtype))
-                    targets.append(lg)
-            if right != PROC_NULL:
-                if _volume(rb):
-                    sends.append((right, out[rb]))
-                if _volume(rg):
-                    recvs.append((right, _shape(rg), out.dtype))
-                    targets.append(rg)
-            got = t.exchange(sends, recvs, list(P_x.ranks))
-            for sl, g in zip(targets, got):
-                out[sl] = g.to(out.device)
+        out = fill_ghosts(cls.transport(), input, P_x, slices, neighbor_ranks)
         out.requires_grad_(input.requires_grad)
         return out
 
@@ -63,30 +98,30 @@ class HaloExchangeFunction(TransportBound, torch.autograd.Function):
         if ctx.identity:
             return grad_output, None, None, None, None
         cls = ctx._forward_cls
-        P_x, slices, neighbor_ranks = ctx.P_x, ctx.slices, ctx.neighbor_ranks
-        t = cls.transport()
-        g = grad_output.detach().clone()
-        for d in reversed(range(P_x.dim)):
-            lb, lg, rb, rg = slices[d]
-            left, right = neighbor_ranks[d]
-            sends, recvs, targets = [], [], []
-            if left != PROC_NULL:
-                if _volume(lg):
-                    sends.append((left, g[lg].clone()))
-                if _volume(lb):
-                    recvs.append((left, _shape(lb), g.dtype))
-                    targets.append(lb)
-            if right != PROC_NULL:
-                if _volume(rg):
-                    sends.append((right, g[rg].clone()))
-                if _volume(rb):
-                    recvs.append((right, _shape(rb), g.dtype))
-                    targets.append(rb)
-            got = t.exchange(sends, recvs, list(P_x.ranks))
-            if left != PROC_NULL and _volume(lg):
-                g[lg] = 0
-            if right != PROC_NULL and _volume(rg):
-                g[rg] = 0
-            for sl, r in zip(targets, got):
-                g[sl] += r.to(g.device)
-        return g, None, None, None, None
+        return fold_ghosts(cls.transport(), grad_output, ctx.P_x, ctx.slices, ctx.neighbor_ranks), None, None, None, None
+
+
+class HaloAccumulateFunction(TransportBound, torch.autograd.Function):
+    """The halo exchange run backwards as a forward operation: every worker's ghost regions are
+    added into the owning neighbours' bulk regions (and cleared).  Used where workers produce
+    contributions to entries their neighbours own (transposed convolution).  Its adjoint is the
+    plain exchange.  Same arguments as :class:`HaloExchangeFunction`."""
+
+    @staticmethod
+    def forward(ctx, input, P_x, slices, buffers, neighbor_ranks):
+        cls = ctx._forward_cls
+        ctx.P_x, ctx.slices, ctx.neighbor_ranks = P_x, slices, neighbor_ranks
+        if not P_x.active or P_x.size == 1:
+            ctx.identity = True
+            return input
+        ctx.identity = False
+        out = fold_ghosts(cls.transport(), input, P_x, slices, neighbor_ranks)
+        out.requires_grad_(input.requires_grad)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        if ctx.identity:
+            return grad_output, None, None, None, None
+        cls = ctx._forward_cls
+        return fill_ghosts(cls.transport(), grad_output, ctx.P_x, ctx.slices, ctx.neighbor_ranks), None, None, None, None

@@ -176,28 +176,42 @@ class DistributedFeatureConv3d(DistributedFeatureConvBase):
 
 
 class _FeatureConvTransposeBase(Module):
-    r"""Transposed convolution on a spatially partitioned tensor.  Realised
-    through the adjoint identity: the transposed convolution is the adjoint of
-    the forward convolution, so each worker applies the local transposed
-    convolution to its sub-tensor and the overlapping borders of neighbouring
-    results are *added* into their owners -- the adjoint halo exchange.
-    Supported for ``stride == 1`` or kernels that do not overlap across worker
-    boundaries (``kernel_size <= stride``); other cases raise."""
+    r"""Transposed convolution of a tensor ``[batch, channel, *space]`` whose spatial dimensions
+    are split over ``P_x = [1, 1, *P_space]``; any kernel size, stride, padding, output padding,
+    dilation and groups.
+
+    Input entry ``i`` contributes to the output entries ``i * stride - padding + dilation * j``,
+    ``j < kernel``.  A worker that holds the input block ``[a, b)`` owns the output entries
+    ``[a * stride - padding, b * stride - padding)`` (the last worker: up to the end; everything
+    clipped to the global output).  It applies the local, unpadded transposed convolution to its
+    block; where the kernel is longer than the stride, the last ``dilation * (kernel - 1) + 1 -
+    stride`` entries of the result belong to the right-hand neighbour and are ADDED to its block
+    by a halo exchange in accumulate mode (the adjoint of the exchange that the forward
+    convolution does); the global padding is then cropped on the boundary workers and the bias
+    added.  The outputs are therefore not balanced: the first worker is ``padding`` entries
+    short, the last one carries the tail.
+
+    (The reference routes the transposed classes through the halo arithmetic of the forward
+    convolution, ``src/distdl/nn/conv_feature.py:442-465``, which is only meaningful when kernel
+    and stride coincide, as in its example.)"""
 
     num_dimensions = None
 
     def __init__(self, P_x, in_channels, out_channels, kernel_size, stride=1, padding=0, output_padding=0, groups=1,
-                 bias=True, dilation=1, buffer_manager=None, device=None, dtype=None):
+                 bias=True, dilation=1, buffer_manager=None, collect_state=False, device=None, dtype=None):
         super().__init__()
         self.P_x = P_x
+        self.buffer_manager = buffer_manager or self._distdl_backend.BufferManager()
         if not P_x.active:
             return
         nd = self.num_dimensions
         exp = lambda v: tuple(int(a) for a in (np.atleast_1d(np.asarray(v, dtype=int)) * (np.ones(nd, dtype=int) if np.ndim(v) == 0 else 1)))  # noqa: E731,E501
+        self.in_channels, self.out_channels = in_channels, out_channels
         self.kernel_size, self.stride, self.padding = exp(kernel_size), exp(stride), exp(padding)
         self.output_padding, self.dilation, self.groups = exp(output_padding), exp(dilation), groups
-        if any(k > s for k, s in zip(self.kernel_size, self.stride)) and any(p > 1 for p in P_x.shape[2:]):
-            raise NotImplementedError("transposed convolution with kernels overlapping worker boundaries")
+        self.collect_state = collect_state
+        if any(int(p) != 1 for p in P_x.shape[:P_x.dim - nd]):
+            raise ValueError("only the spatial dimensions may be partitioned")
         device = device if device is not None else P_x.device
         cls = {1: torch.nn.ConvTranspose1d, 2: torch.nn.ConvTranspose2d, 3: torch.nn.ConvTranspose3d}[nd]
         ref = cls(in_channels, out_channels, self.kernel_size, stride=self.stride, padding=self.padding,
@@ -215,15 +229,88 @@ class _FeatureConvTransposeBase(Module):
         self.w_broadcast = Broadcast(self.P_wb_cart, P_x, preserve_batch=False)
         if bias:
             self.b_broadcast = Broadcast(self.P_wb_cart, P_x, preserve_batch=False)
+        # spill of a local result into the right-hand neighbour's entries, per spatial dimension
+        self.spill = tuple(max(0, d * (k - 1) + 1 - s) for k, s, d in zip(self.kernel_size, self.stride, self.dilation))
+        self.halo_layer = None
+        self._register_state_dict_hook(DistributedFeatureConvBase.gather_state_dict.__get__(self))
+        self._register_load_state_dict_pre_hook(DistributedFeatureConvBase.scatter_state_dict.__get__(self))
+
+    def _distdl_module_setup(self, input):
+        self._distdl_is_setup = True
+        self._input_tensor_structure = TensorStructure(input[0])
+        if not self.P_x.active:
+            return
+        be = self._distdl_backend
+        nd, dim = self.num_dimensions, self.P_x.dim
+        ts = TensorStructure(input[0])
+        shapes = np.asarray(be.tensor_decomposition.compute_subtensor_shapes_unbalanced(ts, self.P_x), dtype=int)
+        from ..utilities.tensor_decomposition import compute_subtensor_start_indices
+        starts = compute_subtensor_start_indices(shapes)
+        idx = tuple(int(i) for i in self.P_x.index)
+        halo = np.zeros((dim, 2), dtype=int)
+        recv = np.zeros((dim, 2), dtype=int)
+        send = np.zeros((dim, 2), dtype=int)
+        self.extend, self.crop = [], []
+        exchange = False
+        for i in range(nd):
+            d = dim - nd + i
+            column = shapes[idx[:d] + (slice(None),) + idx[d + 1:]][:, d]      # extents of all workers along d
+            n, a, l_in = int(shapes[idx][d]), int(starts[idx][d]), int(column.sum())
+            P, me = int(self.P_x.shape[d]), idx[d]
+            k, s, p, op, dil, r = (self.kernel_size[i], self.stride[i], self.padding[i], self.output_padding[i],
+                                   self.dilation[i], self.spill[i])
+            last = me == P - 1
+            l_out = (l_in - 1) * s - 2 * p + dil * (k - 1) + op + 1
+            if r and P > 1:
+                exchange = True
+                if not last:
+                    # the last r entries are the ghost region that travels to the right-hand neighbour
+                    if int(column[me + 1]) * s < r:
+                        raise ValueError("a worker's block is too small for the kernel of this transposed convolution")
+                    halo[d, 1], recv[d, 1] = r, r
+                if me > 0:
+                    send[d, 0] = r                 # ... and arrives on the first r entries there
+            # local result -> [own entries (n * s) | spill (r)], plus the output padding at the very end
+            z_len = (n - 1) * s + dil * (k - 1) + 1
+            length = max(z_len, n * s + r) + (op if last else 0)
+            self.extend.append(length - z_len)
+            # entry j sits at global output position a * s - p + j; keep what is inside [0, l_out) and owned
+            own_end = length if last else n * s
+            lo = min(max(0, p - a * s), own_end)
+            hi = max(lo, min(own_end, l_out - (a * s - p)))
+            self.crop.append((lo, hi))
+        self.halo_layer = None
+        if exchange:
+            self.halo_layer = HaloExchange(self.P_x, halo, recv, send, self.buffer_manager, accumulate=True)
+
+    def _distdl_module_teardown(self, input):
+        self.halo_layer = None
+        self._distdl_is_setup = False
+
+    def _distdl_input_changed(self, input):
+        return self._input_tensor_structure != TensorStructure(input[0])
 
     def forward(self, input):
         if not self.P_x.active:
             return input
         w = self.w_broadcast(self.weight)
         b = self.b_broadcast(self.bias) if self.use_bias else None
-        fn = {1: F.conv_transpose1d, 2: F.conv_transpose2d, 3: F.conv_transpose3d}[self.num_dimensions]
-        return fn(input, w, b, stride=self.stride, padding=self.padding, output_padding=self.output_padding,
-                  groups=self.groups, dilation=self.dilation)
+        nd = self.num_dimensions
+        fn = {1: F.conv_transpose1d, 2: F.conv_transpose2d, 3: F.conv_transpose3d}[nd]
+        z = fn(input, w, None, stride=self.stride, padding=0, output_padding=0, groups=self.groups,
+               dilation=self.dilation)
+        if any(self.extend):
+            pad = []
+            for e in reversed(self.extend):
+                pad += [0, e]
+            z = F.pad(z, pad)
+        if self.halo_layer is not None:
+            z = self.halo_layer(z)
+        sl = [slice(None)] * (z.dim() - nd) + [slice(lo, hi) for lo, hi in self.crop]
+        y = z[tuple(sl)]
+        if b is not None:
+            y = y + b.reshape([1, -1] + [1] * nd)
+        return y
 
 
 class DistributedFeatureConvTranspose1d(_FeatureConvTransposeBase):

@@ -13,11 +13,18 @@ class HaloExchange(Module):
     ``halo_shape[d] = (left, right)`` widths of the ghost regions already present
     in the input tensor; ``recv_buffer_shape`` / ``send_buffer_shape`` give the
     widths actually received / sent per side (they differ for strided
-    kernels).  Dimensions are exchanged in order so that corners propagate."""
+    kernels).  Dimensions are exchanged in order so that corners propagate.
 
-    def __init__(self, P_x, halo_shape, recv_buffer_shape, send_buffer_shape, buffer_manager=None):
+    ``accumulate=True`` runs the exchange backwards instead: the ghost regions are sent to the
+    neighbours they would have come from, ADDED to the bulk regions there and cleared here (for
+    layers whose workers produce contributions to entries of their neighbours, such as a
+    transposed convolution); the widths keep their meaning, so ``recv_buffer_shape`` is what
+    leaves the ghost regions and ``send_buffer_shape`` what arrives on the bulk."""
+
+    def __init__(self, P_x, halo_shape, recv_buffer_shape, send_buffer_shape, buffer_manager=None, accumulate=False):
         super().__init__()
         self.P_x = P_x
+        self.accumulate = accumulate
         self.halo_shape = np.asarray(halo_shape, dtype=int)
         self.recv_buffer_shape = np.asarray(recv_buffer_shape, dtype=int)
         self.send_buffer_shape = np.asarray(send_buffer_shape, dtype=int)
@@ -81,5 +88,6 @@ class HaloExchange(Module):
     def forward(self, input):
         if not self.P_x.active:
             return input
-        Function = self._distdl_backend.functional.HaloExchangeFunction
+        functional = self._distdl_backend.functional
+        Function = functional.HaloAccumulateFunction if self.accumulate else functional.HaloExchangeFunction
         return Function.apply(input, self.P_x, self.slices, self.buffers, self.neighbor_ranks)

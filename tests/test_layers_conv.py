@@ -474,3 +474,51 @@ def body_collect_state_channel_convs(rank, world):
 
 def test_collect_state_channel_convs():
     run_ranks("test_layers_conv", "body_collect_state_channel_convs", 4, timeout=300)
+
+
+def body_transposed_feature_conv_general(rank, world):
+    """Spatially partitioned transposed convolutions whose kernels cross worker boundaries (kernel
+    larger than the stride), with padding, output padding, dilation and groups: output, input
+    gradient and kernel gradient against serial PyTorch."""
+    import distdl_b200.nn as dnn
+    torch.manual_seed(0)
+    fns = {1: torch.nn.functional.conv_transpose1d, 2: torch.nn.functional.conv_transpose2d,
+           3: torch.nn.functional.conv_transpose3d}
+    classes = {1: dnn.DistributedFeatureConvTranspose1d, 2: dnn.DistributedFeatureConvTranspose2d,
+               3: dnn.DistributedFeatureConvTranspose3d}
+    cases = [(1, [1, 1, 4], (2, 4, 11), dict(kernel_size=4, stride=2, padding=1)),
+             (1, [1, 1, 4], (2, 4, 9), dict(kernel_size=3, stride=1, padding=1)),
+             (1, [1, 1, 4], (1, 4, 13), dict(kernel_size=5, stride=2, padding=2, output_padding=1, groups=2)),
+             (1, [1, 1, 4], (1, 4, 12), dict(kernel_size=3, stride=2, dilation=2)),
+             (1, [1, 1, 4], (1, 4, 8), dict(kernel_size=2, stride=3, output_padding=2)),
+             (2, [1, 1, 2, 2], (2, 4, 6, 5), dict(kernel_size=3, stride=2, padding=1, output_padding=1)),
+             (2, [1, 1, 4, 1], (1, 4, 9, 4), dict(kernel_size=(4, 3), stride=(2, 1), padding=(1, 0))),
+             (3, [1, 1, 2, 1, 2], (1, 4, 4, 3, 5), dict(kernel_size=3, stride=1, padding=1))]
+    for nd, Pshape, xshape, kw in cases:
+        P = _cart([0, 1, 2, 3], Pshape)
+        layer = classes[nd](P, xshape[1], 6, **kw)
+        serial = {1: torch.nn.ConvTranspose1d, 2: torch.nn.ConvTranspose2d, 3: torch.nn.ConvTranspose3d}[nd](
+            xshape[1], 6, **kw)
+        w = _sync(layer.weight.detach().clone() if rank == 0 else torch.empty_like(serial.weight))
+        b = _sync(layer.bias.detach().clone() if rank == 0 else torch.empty(6))
+        xg = _sync(torch.randn(*xshape))
+        x0, x = _scatter(P, xg, rank, nd + 2)
+        y = _gather(P, layer(x), nd + 2)
+        fkw = {k: v for k, v in kw.items() if k != "kernel_size"}
+        if rank == 0:
+            xs, ws = xg.clone().requires_grad_(), w.clone().requires_grad_()
+            ys = fns[nd](xs, ws, b, **fkw)
+            assert y.shape == ys.shape, (kw, y.shape, ys.shape)
+            assert torch.allclose(y, ys, atol=1e-5), (kw, (y - ys).abs().max())
+            g = torch.randn_like(ys)
+            ys.backward(g)
+            y.backward(g)
+            assert torch.allclose(x0.grad, xs.grad, atol=1e-5), kw
+            assert torch.allclose(layer.weight.grad, ws.grad, atol=1e-4), kw
+        else:
+            y.backward(torch.zeros_like(y))
+    return True
+
+
+def test_transposed_feature_conv_crossing_worker_boundaries():
+    run_ranks("test_layers_conv", "body_transposed_feature_conv_general", 4, timeout=300)

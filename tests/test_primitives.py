@@ -247,6 +247,17 @@ def body_halo(rank, world):
     y2 = layer(x2)
     y2.backward(dy)
     check_adjoint_test_tight(x2.detach(), x2.grad, y2.detach(), dy)
+    # accumulate mode: the same exchange run backwards (ghosts are added to the neighbours' bulk and
+    # cleared); its adjoint is the plain exchange, and it is the transpose of the operator above
+    acc = HaloExchange(P, halo_local, halo_local, halo_local, accumulate=True)
+    x3 = torch.randn(*shape, dtype=torch.float64, requires_grad=True)
+    y3 = acc(x3)
+    y3.backward(dy)
+    check_adjoint_test_tight(x3.detach(), x3.grad, y3.detach(), dy)
+    assert torch.equal(x3.grad, layer(dy.clone()).detach())
+    ghost = torch.ones(*shape, dtype=torch.bool)
+    ghost[inner] = False
+    assert (y3.detach()[ghost] == 0).all()
     return True
 
 
