@@ -12,7 +12,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 @pytest.mark.parametrize("script,nproc", [("examples/primitives/ex_repartition.py", 4),
                                           ("examples/basics/ex_linear_tp_sp.py", 4),
                                           ("examples/basics/ex_pipeline.py", 3),
-                                          ("examples/basics/ex_layernorm_split.py", 3)])
+                                          ("examples/basics/ex_layernorm_split.py", 3),
+                                          ("examples/basics/ex_conv_transpose.py", 4),
+                                          ("examples/basics/ex_expert.py", 4),
+                                          ("examples/basics/ex_linear_zero.py", 4)])
 def test_example_runs(script, nproc):
     port = 29600 + (os.getpid() + hash(script)) % 300
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
