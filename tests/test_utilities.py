@@ -135,3 +135,52 @@ def test_zero_volume_corrector():
     y = ZeroVolumeCorrectorFunction.apply(x)
     y.sum().backward()
     assert torch.equal(y, x) and torch.equal(x.grad, torch.ones(2, 2))
+
+
+def body_buffer_sharing_network(rank, world):
+    """A network of repartitions, a spatially partitioned convolution and a pooling layer that
+    share ONE buffer manager (as in the reference's buffer-management network tests,
+    ``tests/utilities/test_buffer.py:128-440``): the manager ends with no more buffers than its
+    hungriest layer needs, and the result equals that of the same network with a manager per layer."""
+    import distdl_b200
+    from distdl_b200.nn import DistributedFeatureConv2d, DistributedMaxPool2d, Repartition
+    be = distdl_b200.backends.backend
+    base = be.Partition().create_partition_inclusive(range(4))
+    P_a, P_b = base.create_cartesian_topology_partition([1, 1, 4, 1]), base.create_cartesian_topology_partition(
+        [1, 1, 2, 2])
+
+    def network(shared):
+        mk = (lambda: shared) if shared is not None else be.BufferManager
+        torch.manual_seed(0)
+        return [Repartition(P_a, P_b, buffer_manager=mk()),
+                DistributedFeatureConv2d(P_b, 2, 3, 3, padding=1, buffer_manager=mk()),
+                DistributedMaxPool2d(P_b, 2, buffer_manager=mk()),
+                Repartition(P_b, P_a, buffer_manager=mk())]
+
+    def run(layers, x):
+        for layer in layers:
+            x = layer(x)
+        return x
+    bm = be.BufferManager()
+    shared, separate = network(bm), network(None)
+    if rank == 0:                                   # same kernel in both networks
+        with torch.no_grad():
+            separate[1].weight.copy_(shared[1].weight)
+            separate[1].bias.copy_(shared[1].bias)
+    torch.manual_seed(1 + rank)
+    x = torch.randn(2, 2, 4, 12)
+    for _ in range(2):                              # the second pass reuses every view
+        y_shared, y_sep = run(shared, x), run(separate, x)
+        assert torch.equal(y_shared, y_sep)
+    counts = {dt: len(pool) for dt, pool in bm.buffers_map.items()}
+    most = max(sum(len(pool) for pool in layer.buffer_manager.buffers_map.values()) if hasattr(layer, "buffer_manager")
+               else 0 for layer in separate)
+    assert sum(counts.values()) <= max(most, 4), (counts, most)
+    assert sum(counts.values()) < sum(sum(len(p) for p in layer.buffer_manager.buffers_map.values())
+                                      for layer in separate if hasattr(layer, "buffer_manager"))
+    return True
+
+
+def test_buffer_manager_shared_by_a_network_of_layers():
+    from dist_harness import run_ranks
+    run_ranks("test_utilities", "body_buffer_sharing_network", 4, timeout=240)
