@@ -212,6 +212,123 @@ def test_repartition_errors():
     run_ranks("test_primitives", "body_repartition_errors", 4)
 
 
+# ------------------------------------------------- topology matrix on six workers
+def body_gather_scatter_matrix(rank, world):
+    """AllGather / ReduceScatter / AllSumReduce on 2 x 3 and 1 x 2 x 3 grids, along every
+    dimension, with ``axes_keep`` as well as the explicit axes, even and uneven extents: shapes,
+    values against the assembled global tensor, and the adjoint identity."""
+    from adjoint_test import check_adjoint_test_tight
+    from distdl_b200.nn import AllGather, AllSumReduce, ReduceScatter
+    from distdl_b200.utilities.slicing import compute_start_index, compute_subshape
+    for pshape, gshape in (([2, 3], [4, 9]), ([2, 3], [5, 7]), ([1, 2, 3], [2, 6, 7])):
+        P = _P(list(range(6)), pshape)
+        dim = len(pshape)
+        torch.manual_seed(7)                       # the same global tensor on every worker
+        G = torch.randn(*gshape, dtype=torch.float64)
+        lo, sh = compute_start_index(P.shape, P.index, gshape), compute_subshape(P.shape, P.index, gshape)
+        local = G[tuple(slice(int(a), int(a + b)) for a, b in zip(lo, sh))].clone()
+        for axis in range(dim):
+            keep = tuple(a for a in range(dim) if a != axis)
+            for kw in (dict(axes_all_gather=(axis,)), dict(axes_keep=keep)):
+                x = local.clone().requires_grad_()
+                y = AllGather(P, **kw)(x)
+                sl = [slice(int(a), int(a + b)) for a, b in zip(lo, sh)]
+                sl[axis] = slice(None)
+                assert torch.equal(y.detach(), G[tuple(sl)]), (pshape, gshape, axis)
+                dy = torch.randn_like(y)
+                y.backward(dy)
+                check_adjoint_test_tight(x.detach(), x.grad, y.detach(), dy)
+            # reduce-scatter of the gathered slab: every worker of the team adds the same slab, so
+            # the result is team size times the own block
+            for kw in (dict(axes_reduce_scatter=(axis,)), dict(axes_keep=keep)):
+                sl = [slice(int(a), int(a + b)) for a, b in zip(lo, sh)]
+                sl[axis] = slice(None)
+                x = G[tuple(sl)].clone().requires_grad_()
+                y = ReduceScatter(P, **kw)(x)
+                assert torch.allclose(y.detach(), local * pshape[axis]), (pshape, gshape, axis)
+                dy = torch.randn_like(y)
+                y.backward(dy)
+                check_adjoint_test_tight(x.detach(), x.grad, y.detach(), dy)
+            for kw in (dict(axes_reduce=(axis,)), dict(axes_keep=keep)):
+                x = torch.full((3, 2), float(rank + 1), dtype=torch.float64, requires_grad=True)
+                y = AllSumReduce(P, **kw)(x)
+                team = [r for r in range(6) if all(
+                    a == axis or P.cartesian_index(r)[a] == P.index[a] for a in range(dim))]
+                assert torch.allclose(y.detach(), torch.full((3, 2), float(sum(r + 1 for r in team)),
+                                                             dtype=torch.float64)), (pshape, axis, team)
+                dy = torch.randn_like(y)
+                y.backward(dy)
+                check_adjoint_test_tight(x.detach(), x.grad, y.detach(), dy)
+    return True
+
+
+def test_gather_scatter_allreduce_topology_matrix():
+    run_ranks("test_primitives", "body_gather_scatter_matrix", 6, timeout=300)
+
+
+# ------------------------------------------- partitions that once deadlocked; dtypes
+def body_send_recv_pairs(rank, world, P_x_ranks, P_x_shape, P_w_ranks, P_w_shape):
+    """Source partition in the middle of the rank range, destination over all ranks: the order in
+    which the send / receive teams are created must not deadlock
+    (``tests/primitives/test_broadcast.py:212-285`` of the reference), and the broadcast works."""
+    from distdl_b200.nn import Broadcast
+    from distdl_b200.utilities.torch import zero_volume_tensor
+    P_x, P_w = _P(P_x_ranks, P_x_shape), _P(P_w_ranks, P_w_shape)
+    layer = Broadcast(P_x, P_w, preserve_batch=False)
+    x = torch.full((2, 3), float(P_x.rank + 1)) if P_x.active else zero_volume_tensor()
+    y = layer(x)
+    assert tuple(y.shape) == (2, 3)
+    # the source of a destination worker is the source worker with the same index in the matching dims
+    src_index = [i if int(p) > 1 else 0 for i, p in zip(P_w.index, [1] * (P_w.dim - P_x.dim) + list(P_x.shape))]
+    want = int(np.ravel_multi_index(src_index[P_w.dim - P_x.dim:], [int(p) for p in P_x.shape])) + 1
+    assert (y == want).all(), (rank, y, want)
+    return True
+
+
+def test_potentially_deadlocked_send_recv_pairs():
+    run_ranks("test_primitives", "body_send_recv_pairs", 4, ([1, 2], [1, 2], [0, 1, 2, 3], [2, 2]))
+    run_ranks("test_primitives", "body_send_recv_pairs", 8, ([2, 3, 4, 5], [1, 2, 2], list(range(8)), [2, 2, 2]),
+              timeout=240)
+
+
+def body_dtypes(rank, world):
+    """Broadcast, SumReduce, Repartition, AllGather and HaloExchange keep the dtype of their input
+    (float32, float64, bfloat16 with gradients; int32 and int64 forward only)."""
+    from distdl_b200.nn import AllGather, Broadcast, HaloExchange, Repartition, SumReduce
+    from distdl_b200.utilities.torch import zero_volume_tensor
+    P_one, P_all, P_col = _P([0], [1, 1]), _P([0, 1, 2, 3], [2, 2]), _P([0, 1, 2, 3], [1, 4])
+    for dtype, backward in ((torch.float32, True), (torch.float64, True), (torch.bfloat16, True),
+                            (torch.int32, False), (torch.int64, False)):
+        def data(shape, active=True):
+            if not active:
+                return zero_volume_tensor(dtype=dtype)
+            return (10 * torch.randn(*shape)).to(dtype)
+        for make, P_in, P_out, shape in ((lambda: Broadcast(P_one, P_all, preserve_batch=False), P_one, P_all, (3, 4)),
+                                         (lambda: SumReduce(P_all, P_one, preserve_batch=False), P_all, P_one, (3, 4)),
+                                         (lambda: Repartition(P_all, P_col, preserve_batch=False), P_all, P_col, (2, 6)),
+                                         (lambda: AllGather(P_all, axes_all_gather=(1,)), P_all, P_all, (2, 3))):
+            x = data(shape, P_in.active)
+            x.requires_grad = backward
+            y = make()(x)
+            if P_out.active:
+                assert y.dtype == dtype, (dtype, y.dtype)
+            if backward:
+                y.backward(torch.ones_like(y))
+                if P_in.active:
+                    assert x.grad.dtype == dtype and x.grad.shape == x.shape
+        P_h = _P([0, 1, 2, 3], [1, 4])
+        left, right = int(P_h.index[1] > 0), int(P_h.index[1] < 3)
+        halo = np.array([[0, 0], [left, right]])
+        x = data((2, 3 + left + right))
+        y = HaloExchange(P_h, halo, halo, halo)(x)
+        assert y.dtype == dtype and y.shape == x.shape
+    return True
+
+
+def test_primitives_keep_dtypes():
+    run_ranks("test_primitives", "body_dtypes", 4, timeout=240)
+
+
 # -------------------------------------------------------------- halo exchange
 def body_halo(rank, world):
     from adjoint_test import check_adjoint_test_tight
