@@ -109,6 +109,8 @@ def main():
     ap.add_argument("--seqs-per-gpu", type=int, default=8)
     ap.add_argument("--micro-batch", type=int, default=0, help="sequences per forward/backward (0 = auto)")
     ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size (0 = the layout named by the baseline)")
+    ap.add_argument("--cp", type=int, default=1,
+                    help="context-parallel size: every sequence is split into this many blocks (ring attention)")
     ap.add_argument("--keep-gathered", action="store_true",
                     help="gather the ZeRO shards once per optimizer step and reduce-scatter the gradients once "
                          "(ZeRO-1 behaviour within a step; not the named ZeRO-3 configuration)")
@@ -161,6 +163,10 @@ def main():
         tp, dp = args.tp, args.gpus // args.tp
     if cfg.n_experts:
         dp, tp = args.gpus, 1                      # expert parallel over all GPUs
+    cp = max(1, args.cp)
+    if dp % cp:
+        raise SystemExit(f"--cp {cp} does not divide the {dp} data-parallel workers")
+    dp //= cp
     seq = cfg.max_seq
     global_batch = args.seqs_per_gpu * args.gpus
     local_batch = global_batch // dp
@@ -174,7 +180,7 @@ def main():
     else:
         micro = {2: 2}.get(args.gpus, 4)      # 1 GPU: 15.8k / 16.5k / 14.6k tokens/s at 2 / 4 / 8 sequences
     torch.manual_seed(1234 + rank)
-    layout = models.ParallelLayout(dp, tp)
+    layout = models.ParallelLayout(dp, tp, cp=cp)
     model = models.Decoder(cfg, layout)
     trainer = Trainer(model, global_tokens_per_step=global_batch * seq, micro_batch=micro, lr=3e-4,
                       warmup_steps=10, total_steps=1000)
@@ -246,7 +252,8 @@ def main():
             "config": {"model": f"{args.model} ({cfg.num_parameters() / 1e9:.2f}B params)", "global_batch": global_batch,
                        "seq_len": seq,
                        "parallelism": (f"ep{dp} (experts) + fsdp{dp} (attention, router, embedding)" if cfg.n_experts
-                                       else f"tp{tp} x fsdp{dp}"),
+                                       else f"tp{tp} x fsdp{dp}" if cp == 1 else
+                                       f"tp{tp} x cp{cp} x dp{dp} (ZeRO over {dp * cp} workers, ring attention)"),
                        "micro_batch": micro,
                        "zero": ("not used (parameters live on their tensor-parallel owners)" if not cfg.zero else
                                 "gathered once per step (--keep-gathered)" if args.keep_gathered else

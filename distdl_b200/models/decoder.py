@@ -77,24 +77,34 @@ class DecoderConfig:
 
 
 class ParallelLayout:
-    """The partitions a decoder needs, derived from a ``[D, M]`` worker grid."""
+    """The partitions a decoder needs, derived from a ``[D, C, M]`` worker grid: ``D`` data-parallel
+    replicas, ``C`` context-parallel workers that each hold one block of every sequence, ``M``
+    tensor-parallel workers.  To every layer but attention a context-parallel worker is one more
+    data-parallel worker (its "batch" is a block of the sequence), so parameters, gradients and
+    optimizer state are ZeRO-sharded over ``D * C`` workers and only attention (ring over ``C``)
+    and the token positions know about ``C``."""
 
-    def __init__(self, dp: int, tp: int, P_world=None):
+    def __init__(self, dp: int, tp: int, P_world=None, cp: int = 1):
         from .. import backends
         be = backends.backend
         P_world = P_world if P_world is not None else be.Partition()
-        if dp * tp != P_world.size:
-            raise ValueError(f"dp*tp = {dp * tp} does not match the {P_world.size} workers")
+        if dp * cp * tp != P_world.size:
+            raise ValueError(f"dp*cp*tp = {dp * cp * tp} does not match the {P_world.size} workers")
         base = P_world.create_partition_inclusive(range(P_world.size))
-        self.dp, self.tp = dp, tp
+        self.dp, self.tp, self.cp = dp, tp, cp
+        rows = dp * cp                                 # workers that differ in the data they see
+        self.shard = rows
         self.P_world = P_world
-        self.P_grid = base.create_cartesian_topology_partition([dp, tp])
-        self.P_feat = base.create_cartesian_topology_partition([dp, 1, tp])
-        self.P_seq = base.create_cartesian_topology_partition([dp, tp, 1])
-        self.P_flat = base.create_cartesian_topology_partition([dp * tp, 1, 1])
-        self.P_flat2 = base.create_cartesian_topology_partition([dp * tp, 1])
-        self.dp_index = int(self.P_grid.index[0])
+        self.P_grid = base.create_cartesian_topology_partition([rows, tp])
+        self.P_feat = base.create_cartesian_topology_partition([rows, 1, tp])
+        self.P_seq = base.create_cartesian_topology_partition([rows, tp, 1])
+        self.P_flat = base.create_cartesian_topology_partition([rows * tp, 1, 1])
+        self.P_flat2 = base.create_cartesian_topology_partition([rows * tp, 1])
+        row = int(self.P_grid.index[0])
+        self.dp_index, self.cp_index = row // cp, row % cp
         self.tp_index = int(self.P_grid.index[1])
+        # [data, sequence block, heads, 1]: the ring of a worker = same data and head shard
+        self.P_ring = base.create_cartesian_topology_partition([dp, cp, tp, 1]) if cp > 1 else None
 
 
 def _norm(cfg, P, zero, keep=None):
@@ -132,15 +142,24 @@ class Attention(torch.nn.Module):
         self.qkv = _col(cfg, layout, cfg.d_model, (cfg.n_heads + 2 * cfg.n_kv_heads) * hd, num_heads=cfg.n_heads,
                         num_heads_kv=cfg.n_kv_heads)
         self.out = _row(cfg, layout, cfg.n_heads * hd, cfg.d_model, num_heads=cfg.n_heads)
+        self.ring = dnn.DistributedRingAttention(layout.P_ring, causal=True) if layout.cp > 1 else None
 
     def forward(self, x):
         cfg = self.cfg
         qkv = self.qkv(x)                                     # [b, s, (hq + 2 hkv) * hd]
         b, s = qkv.shape[0], qkv.shape[1]
         t = qkv.reshape(b * s, self.hq + 2 * self.hkv, cfg.head_dim)
-        if cfg.rope:
-            t = ops.rope_(t, s, self.hq + self.hkv, cfg.rope_theta)
-        o = ops.attention_packed(t, self.hq, self.hkv, b, s, causal=True)
+        if self.ring is None:
+            if cfg.rope:
+                t = ops.rope_(t, s, self.hq + self.hkv, cfg.rope_theta)
+            o = ops.attention_packed(t, self.hq, self.hkv, b, s, causal=True)
+        else:
+            # context parallel: s is this worker's block of the sequence; positions are global
+            if cfg.rope:
+                t = ops.rope_(t, s, self.hq + self.hkv, cfg.rope_theta, offset=self.layout.cp_index * s)
+            t = t.reshape(b, s, self.hq + 2 * self.hkv, cfg.head_dim)
+            q, k, v = t.split([self.hq, self.hkv, self.hkv], dim=2)
+            o = self.ring(q.contiguous(), k.contiguous(), v.contiguous())
         return self.out(o.reshape(b, s, self.hq * cfg.head_dim))
 
 
@@ -232,10 +251,18 @@ class Decoder(torch.nn.Module):
                 clear()
 
     def _local_tokens(self, tokens):
-        """This worker's sequence shard of the (tensor-parallel replicated) token ids."""
+        """This worker's part of the token ids ``[b_local, seq]`` (the same on all context- and
+        tensor-parallel workers of a data-parallel replica): its context-parallel block of the
+        sequence, and of that its sequence-parallel shard.  Returns (ids, global start position)."""
         lay = self.layout
         s = tokens.shape[1]
-        lo = int(compute_start_index(lay.tp, lay.tp_index, [s])[0])
+        base = 0
+        if lay.cp > 1:
+            if s % lay.cp:
+                raise ValueError(f"sequence length {s} must divide by the context-parallel size {lay.cp}")
+            s //= lay.cp
+            base = lay.cp_index * s
+        lo = base + int(compute_start_index(lay.tp, lay.tp_index, [s])[0])
         n = int(compute_subshape(lay.tp, lay.tp_index, [s])[0])
         return tokens[:, lo:lo + n], lo
 

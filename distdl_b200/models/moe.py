@@ -90,7 +90,7 @@ class MoEFeedForward(torch.nn.Module):
         E, d, F = cfg.n_experts, cfg.d_model, cfg.ffn_dim
         if layout.tp != 1:
             raise ValueError("the expert-parallel block expects tensor-parallel size 1")
-        self.ep = layout.dp
+        self.ep = layout.shard          # data- and context-parallel workers alike hold tokens to route
         if E % self.ep:
             raise ValueError("experts must divide evenly over the expert-parallel workers")
         self.e_local = E // self.ep

@@ -138,8 +138,10 @@ class _RingAttnFn(torch.autograd.Function):
 
 class DistributedRingAttention(Module):
     r"""``forward(q, k, v) -> out`` with ``q [b, s_local, Hq, D]``, ``k, v [b, s_local, Hkv, D]`` on
-    ``P_seq = [B, S, 1, 1]`` (equal sequence blocks, block ``i`` on the worker with sequence index
-    ``i``).  Exact attention over the whole sequence, causal by global position if ``causal``."""
+    ``P_seq = [B, S, H, 1]`` (equal sequence blocks, block ``i`` on the worker with sequence index
+    ``i``; ``H`` > 1 when the heads are additionally split over tensor-parallel workers, each of
+    which then runs its own ring).  Exact attention over the whole sequence, causal by global
+    position if ``causal``."""
 
     def __init__(self, P_seq, causal=True, scale=None):
         super().__init__()
@@ -147,8 +149,8 @@ class DistributedRingAttention(Module):
         self.causal, self.scale = causal, scale
         if not P_seq.active:
             return
-        if P_seq.dim != 4 or int(P_seq.shape[2]) != 1 or int(P_seq.shape[3]) != 1:
-            raise ValueError("DistributedRingAttention expects a partition of shape [B, S, 1, 1]")
+        if P_seq.dim != 4 or int(P_seq.shape[3]) != 1:
+            raise ValueError("DistributedRingAttention expects a partition of shape [B, S, H, 1]")
         ring = P_seq.create_allreduction_partition((1,))
         self.ranks = tuple(int(r) for r in ring.ranks)          # ordered by sequence index
         from ..backends.common import world

@@ -103,12 +103,13 @@ class _RopeFn(torch.autograd.Function):
         return d, None, None, None
 
 
-def rope_(qkv: torch.Tensor, seq: int, nheads: int, theta: float = 500000.0) -> torch.Tensor:
+def rope_(qkv: torch.Tensor, seq: int, nheads: int, theta: float = 500000.0, offset: int = 0) -> torch.Tensor:
     """Applies rotary position embedding (rotate-half convention) to the first
     ``nheads`` heads of ``qkv`` [tokens, heads_total, head_dim]; position of a
-    token is its index modulo ``seq``.  In place on CUDA."""
+    token is ``offset`` plus its index modulo ``seq`` (``offset`` > 0 for a worker that holds a
+    later block of a sequence split across workers).  In place on CUDA."""
     tokens, ht, hd = qkv.shape
-    table = rope_table(seq, hd, theta, qkv.device)
+    table = rope_table(offset + seq, hd, theta, qkv.device)[offset:]      # rows [offset, offset + seq)
     if use_native(qkv) and qkv.dtype == torch.bfloat16 and hd % 16 == 0 and qkv.is_contiguous():
         return _RopeFn.apply(qkv, table, seq, nheads)
     pos = torch.arange(tokens, device=qkv.device) % seq

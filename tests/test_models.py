@@ -76,7 +76,7 @@ def body_trainer_checkpoint(rank, world, tmp):
     sink.close()
     b, _, _ = make()
     manifest = b.load_checkpoint(os.path.join(tmp, "ckpt"))
-    assert manifest["world_size"] == world and manifest["steps_done"] == 3 and manifest["layout"] == {"dp": 2, "tp": 1}
+    assert manifest["world_size"] == world and manifest["steps_done"] == 3 and manifest["layout"] == {"dp": 2, "tp": 1, "cp": 1}
     got = [b.step(blocks[i]).item() for i in range(3, 6)]
     assert all(abs(x - y) < 1e-6 * max(1.0, abs(x)) for x, y in zip(ref, got)), (ref, got)
     if rank == 0:
@@ -87,3 +87,50 @@ def body_trainer_checkpoint(rank, world, tmp):
 
 def test_trainer_checkpoint_and_metrics(tmp_path):
     run_ranks("test_models", "body_trainer_checkpoint", 2, args=(str(tmp_path),), timeout=300)
+
+
+def body_context_parallel(rank, world, family, tp):
+    """Context parallelism (ring attention over two blocks of every sequence) against the same
+    weights run WITHOUT it.  On the same worker grid, ``ParallelLayout(dp=1, cp=2, tp)`` and
+    ``ParallelLayout(dp=2, cp=1, tp)`` shard every parameter identically, so the same seed gives the
+    same model.  The data-parallel model is fed the whole sequences on both replicas: its summed
+    loss and gradients are then exactly twice those of the context-parallel model, in which every
+    worker sees one block and attention, rotary / learned positions and the token slicing have to
+    reproduce the global sequence."""
+    import torch.distributed as dist
+
+    from distdl_b200 import models
+    cfg = {"llama": models.llama_tiny, "gpt2": models.gpt2_tiny}[family](dtype=torch.float32, max_seq=32,
+                                                                       vocab_size=200, d_model=48, ffn_dim=96)
+    cfg.n_heads, cfg.n_kv_heads = (4, 2) if family == "llama" else (3, 3)
+    cfg.n_layers = 2
+    torch.manual_seed(0)
+    cp_model = models.Decoder(cfg, models.ParallelLayout(1, tp, cp=2))
+    torch.manual_seed(0)
+    dp_model = models.Decoder(cfg, models.ParallelLayout(2, tp))
+    for a, b in zip(cp_model.parameters(), dp_model.parameters()):
+        assert a.shape == b.shape and torch.equal(a, b)
+    gen = torch.Generator().manual_seed(5)
+    tokens = torch.randint(0, cfg.vocab_size, (2, 33), generator=gen)        # the same on every worker
+    out = {}
+    for name, model in (("cp", cp_model), ("dp", dp_model)):
+        model.train()
+        loss = model.loss(tokens[:, :-1], tokens[:, 1:], scale=1.0 / 64)
+        loss.backward()
+        model.release_gathered()
+        total = loss.detach().clone()
+        dist.all_reduce(total)
+        out[name] = (total, [None if p.grad is None else p.grad.clone() for p in model.parameters()])
+    assert torch.allclose(out["cp"][0] * 2, out["dp"][0], rtol=1e-5), (out["cp"][0], out["dp"][0])
+    names = [n for n, _ in cp_model.named_parameters()]
+    for n, ga, gb in zip(names, out["cp"][1], out["dp"][1]):
+        assert (ga is None) == (gb is None), n
+        if ga is not None and ga.numel():
+            assert torch.allclose(ga * 2, gb, rtol=2e-4, atol=2e-6), (n, (ga * 2 - gb).abs().max())
+    return float(out["cp"][0])
+
+
+def test_context_parallel_decoder_matches_full_sequence_attention():
+    run_ranks("test_models", "body_context_parallel", 2, args=("llama", 1), timeout=300)
+    run_ranks("test_models", "body_context_parallel", 4, args=("llama", 2), timeout=300)
+    run_ranks("test_models", "body_context_parallel", 4, args=("gpt2", 2), timeout=300)
