@@ -24,8 +24,10 @@ class Trainer:
 
     def __init__(self, model, global_tokens_per_step: int, micro_batch: int = 1, lr: float = 3e-4,
                  weight_decay: float = 0.1, max_grad_norm: float = 1.0, warmup_steps: int = 10,
-                 total_steps: int = 1000, device=None, metrics=None, health_check_every: int = 50):
+                 total_steps: int = 1000, device=None, metrics=None, health_check_every: int = 50, heartbeat=None):
         self.model = model
+        self.heartbeat = heartbeat      # a parallel.health.Heartbeat: checked before every step, so that a
+                                        # missing rank raises RankFailure here instead of hanging a collective
         self.health_check_every = health_check_every   # steps between reads of the device status record
         self.metrics = metrics          # a parallel.metrics.MetricsSink, or None
         self.micro_batch = micro_batch
@@ -45,6 +47,8 @@ class Trainer:
         return self._dev_tokens
 
     def step_device(self, tokens: torch.Tensor) -> torch.Tensor:
+        if self.heartbeat is not None:
+            self.heartbeat.check()
         self.model.train()
         self.opt.set_lr(cosine_lr(self.steps_done, self.base_lr, self.warmup_steps, self.total_steps))
         total = torch.zeros((), dtype=torch.float32, device=tokens.device)

@@ -103,3 +103,105 @@ def test_device_wait_that_runs_out_reports_status_and_context_survives():
     lib.dd_symm_free.argtypes = [vp]
     lib.dd_symm_free(pad)
     lib.dd_symm_free(buf)
+
+
+def body_heartbeat(rank, world):
+    """Three ranks beat into the rendezvous store.  Rank 2 falls silent (a stalled process), then
+    rank 1 leaves in an orderly way; the remaining ranks learn of both on the host, by name, within
+    the limit, and no collective is involved."""
+    from distdl_b200.parallel import Heartbeat, RankFailure
+    hb = Heartbeat(interval=0.1, limit=1.0, prefix="test/hb").start()
+    hb.wait_for_all(timeout=30)
+    time.sleep(0.5)
+    hb.check()                                   # everybody alive
+    seen = {}
+
+    def poll(expect_ranks, seconds):
+        end = time.monotonic() + seconds
+        while time.monotonic() < end:
+            try:
+                hb.check()
+            except RankFailure as e:
+                if set(expect_ranks) <= set(e.ranks):
+                    return e
+            time.sleep(0.1)
+        return None
+    if rank == 2:
+        hb.stop()                                # no goodbye: looks like a hang
+        time.sleep(4.0)
+        return "silent"
+    t0 = time.monotonic()
+    e = poll([2], 6.0)
+    assert e is not None and 2 in e.ranks and 2 not in e.left, e
+    seen["silent_after"] = time.monotonic() - t0
+    assert "no heartbeat from rank(s) [2]" in str(e)
+    if rank == 1:
+        hb.leave()
+        return seen
+    e = poll([1, 2], 6.0)
+    assert e is not None and e.left == (1,) and set(e.ranks) == {1, 2}, e
+    assert "left the job" in str(e)
+    hb.stop()
+    return seen
+
+
+def test_heartbeat_names_silent_and_departed_ranks():
+    out = run_ranks("test_failure_detection", "body_heartbeat", 3, timeout=120)
+    assert out[2] == "silent" and 0.5 < out[0]["silent_after"] < 6.0, out
+
+
+def test_watchdog_fires_only_when_the_block_overruns():
+    from distdl_b200.parallel import Watchdog
+    fired = []
+    with Watchdog(5.0, "quick block", on_expire=lambda w, s: fired.append(w), exit_code=None) as w:
+        time.sleep(0.05)
+    assert not w.expired and not fired
+    with Watchdog(0.1, "slow block", on_expire=lambda w, s: fired.append(w), exit_code=None, dump_stacks=False) as w:
+        time.sleep(0.5)
+    assert w.expired and fired == ["slow block"]
+
+
+def test_watchdog_ends_a_stuck_process_with_its_exit_code():
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = ("import time\nfrom distdl_b200.parallel.health import Watchdog\n"
+            "with Watchdog(0.3, 'stuck rendezvous'):\n    time.sleep(60)\n")
+    t0 = time.monotonic()
+    res = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True, timeout=120,
+                         env=dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=root))
+    assert res.returncode == 87, (res.returncode, res.stderr[-500:])
+    assert "stuck rendezvous" in res.stderr and time.monotonic() - t0 < 60
+
+
+def body_trainer_heartbeat(rank, world):
+    """The trainer checks the heartbeat before every step: after rank 1 has gone silent, rank 0's next
+    step raises RankFailure on the host instead of entering a collective that nobody answers."""
+    from distdl_b200 import models
+    from distdl_b200.parallel import Heartbeat, RankFailure, SyntheticTokens, Trainer
+    torch.manual_seed(0)
+    cfg = models.llama_tiny(dtype=torch.float32, max_seq=16, vocab_size=64, d_model=32, ffn_dim=64)
+    cfg.n_layers, cfg.n_heads, cfg.n_kv_heads = 1, 2, 2
+    layout = models.ParallelLayout(2, 1)
+    hb = Heartbeat(interval=0.1, limit=1.0, prefix="test/hb_trainer").start()
+    hb.wait_for_all(timeout=30)
+    trainer = Trainer(models.Decoder(cfg, layout), global_tokens_per_step=2 * 16, micro_batch=1, warmup_steps=0,
+                      heartbeat=hb)
+    block = SyntheticTokens(1, 16, cfg.vocab_size, dp_index=layout.dp_index).next()
+    trainer.step(block)                          # both ranks alive: a normal step
+    if rank == 1:
+        hb.stop()
+        time.sleep(3.0)
+        return "silent"
+    time.sleep(2.0)
+    try:
+        trainer.step(block)
+    except RankFailure as e:
+        return f"detected {e.ranks}"
+    return "not detected"
+
+
+def test_trainer_step_raises_when_a_peer_stopped_beating():
+    out = run_ranks("test_failure_detection", "body_trainer_heartbeat", 2, timeout=180)
+    assert out == ["detected (1,)", "silent"], out
