@@ -86,8 +86,8 @@ class HaloExchange(Module):
         return self._input_tensor_structure != TensorStructure(input[0])
 
     def forward(self, input):
-        if not self.P_x.active:
-            return input
+        if not self.P_x.active or self.P_x.size == 1:
+            return input                               # no neighbours: nothing to exchange
         functional = self._distdl_backend.functional
         Function = functional.HaloAccumulateFunction if self.accumulate else functional.HaloExchangeFunction
         return Function.apply(input, self.P_x, self.slices, self.buffers, self.neighbor_ranks)
