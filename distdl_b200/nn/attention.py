@@ -11,7 +11,6 @@ sees whole sequences of its own heads, and one more Repartition brings the outpu
 Backward is the adjoint chain (Repartition is its own adjoint pair), so nothing but the
 partitions has to be specified.
 """
-import torch
 
 from .. import ops
 from .module import Module

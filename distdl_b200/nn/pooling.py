@@ -1,6 +1,5 @@
 """Pooling on spatially partitioned tensors (``src/distdl/nn/pooling.py:13-338``)."""
 import numpy as np
-import torch
 import torch.nn.functional as F
 
 from ..utilities.slicing import assemble_slices

@@ -1,6 +1,5 @@
 """Upsampling of spatially partitioned tensors (``src/distdl/nn/upsampling.py:16-258``)."""
 import numpy as np
-import torch
 import torch.nn.functional as F
 
 from ..utilities.slicing import compute_start_index, compute_stop_index
