@@ -204,25 +204,43 @@ class Block(torch.nn.Module):
                 fn()
 
 
+def stage_layers(n_layers: int, stage: int, n_stages: int):
+    """Half-open range of the blocks that pipeline stage ``stage`` of ``n_stages`` owns (balanced:
+    the first stages get the extra blocks)."""
+    lo = int(compute_start_index(n_stages, stage, [n_layers])[0])
+    return lo, lo + int(compute_subshape(n_stages, stage, [n_layers])[0])
+
+
 class Decoder(torch.nn.Module):
     """``forward(tokens [b_local, seq]) -> hidden [b_local, seq / M, d]``;
-    ``loss(tokens, targets)`` runs the LM head and the fused cross-entropy."""
+    ``loss(tokens, targets)`` runs the LM head and the fused cross-entropy.
 
-    def __init__(self, cfg: DecoderConfig, layout: ParallelLayout):
+    ``stage=(i, n)`` builds pipeline stage ``i`` of ``n`` only: its share of the blocks, the
+    embedding on the first stage, the final norm and the head on the last.  ``forward`` of a
+    later stage takes the hidden state of the stage before it instead of token ids; ``layout`` then
+    describes the workers of THIS stage (``ParallelLayout(..., P_world=<the stage's partition>)``)."""
+
+    def __init__(self, cfg: DecoderConfig, layout: ParallelLayout, stage=(0, 1)):
         super().__init__()
         self.cfg, self.layout = cfg, layout
+        self.stage_index, self.n_stages = int(stage[0]), int(stage[1])
+        self.first_stage, self.last_stage = self.stage_index == 0, self.stage_index == self.n_stages - 1
         V = cfg.padded_vocab()
         self.padded_vocab = V
         keep_root = cfg.keep_gathered or cfg.keep_root_gathered
-        self.embed = dnn.DistributedEmbeddingZero(layout.P_flat2, V, cfg.d_model, dtype=cfg.dtype,
-                                                  auto_clear_buffer=not keep_root)
-        if not cfg.rope:
-            self.pos_embed = dnn.DistributedEmbeddingZero(layout.P_flat2, cfg.max_seq, cfg.d_model, dtype=cfg.dtype,
-                                                          auto_clear_buffer=not keep_root)
-        self.blocks = torch.nn.ModuleList(Block(cfg, layout) for _ in range(cfg.n_layers))
-        self.final_norm = _norm(cfg, layout.P_flat, True, keep=keep_root)
-        self.head = dnn.DistributedLinearAllGatherZero(layout.P_flat, cfg.d_model, V, bias=False, dtype=cfg.dtype,
-                                                       auto_clear_buffer=not keep_root)
+        if self.first_stage:
+            self.embed = dnn.DistributedEmbeddingZero(layout.P_flat2, V, cfg.d_model, dtype=cfg.dtype,
+                                                      auto_clear_buffer=not keep_root)
+            if not cfg.rope:
+                self.pos_embed = dnn.DistributedEmbeddingZero(layout.P_flat2, cfg.max_seq, cfg.d_model,
+                                                              dtype=cfg.dtype, auto_clear_buffer=not keep_root)
+        lo, hi = stage_layers(cfg.n_layers, self.stage_index, self.n_stages)
+        self.layer_range = (lo, hi)
+        self.blocks = torch.nn.ModuleList(Block(cfg, layout) for _ in range(hi - lo))
+        if self.last_stage:
+            self.final_norm = _norm(cfg, layout.P_flat, True, keep=keep_root)
+            self.head = dnn.DistributedLinearAllGatherZero(layout.P_flat, cfg.d_model, V, bias=False, dtype=cfg.dtype,
+                                                           auto_clear_buffer=not keep_root)
         self.reset_parameters()
 
     def reset_parameters(self):
@@ -268,11 +286,14 @@ class Decoder(torch.nn.Module):
 
     def forward(self, tokens):
         cfg = self.cfg
-        local, lo = self._local_tokens(tokens)
-        x = self.embed(local)
-        if not cfg.rope:
-            pos = torch.arange(lo, lo + local.shape[1], device=tokens.device).unsqueeze(0).expand_as(local)
-            x = x + self.pos_embed(pos)
+        if self.first_stage:
+            local, lo = self._local_tokens(tokens)
+            x = self.embed(local)
+            if not cfg.rope:
+                pos = torch.arange(lo, lo + local.shape[1], device=tokens.device).unsqueeze(0).expand_as(local)
+                x = x + self.pos_embed(pos)
+        else:
+            x = tokens                                 # the hidden state handed over by the stage before
         ckpt = cfg.checkpoint_blocks and self.training
         pre = cfg.prefetch and cfg.zero and not cfg.keep_gathered
         n = len(self.blocks)
@@ -291,15 +312,18 @@ class Decoder(torch.nn.Module):
                 x = torch.utils.checkpoint.checkpoint(run, x, i, use_reentrant=False)
             else:
                 x = self.blocks[i](x)
-        if pre and ckpt and torch.is_grad_enabled():
+        if pre and ckpt and n and torch.is_grad_enabled():
             self.blocks[n - 1].prefetch()          # the first block that the backward pass recomputes
         self._backward_phase = True
-        return self.final_norm(x)
+        return self.final_norm(x) if self.last_stage else x
 
     def loss(self, tokens, targets, scale=None):
         """Sum of this worker's token losses times ``scale`` (default: 1 / local
         tokens); ``targets`` has the same [b_local, seq] shape as ``tokens``."""
-        h = self.forward(tokens)
+        return self.loss_from_hidden(self.forward(tokens), targets, scale)
+
+    def loss_from_hidden(self, h, targets, scale=None):
+        """The head and the cross-entropy on the output ``h`` of :meth:`forward` (last stage)."""
         tl, _ = self._local_tokens(targets)
         logits = self.head(h)
         rows = logits.shape[0] * logits.shape[1]

@@ -134,3 +134,75 @@ def test_context_parallel_decoder_matches_full_sequence_attention():
     run_ranks("test_models", "body_context_parallel", 2, args=("llama", 1), timeout=300)
     run_ranks("test_models", "body_context_parallel", 4, args=("llama", 2), timeout=300)
     run_ranks("test_models", "body_context_parallel", 4, args=("gpt2", 2), timeout=300)
+
+
+def body_pipelined_decoder(rank, world):
+    """Two pipeline stages of one worker each against the whole model on one worker, with the same
+    weights (copied from the whole model's state dict): loss and every gradient agree after a
+    1F1B pass over three micro-batches."""
+    import distdl_b200
+    from distdl_b200 import models
+    cfg = models.llama_tiny(dtype=torch.float32, max_seq=16, vocab_size=96, d_model=32, ffn_dim=64)
+    cfg.n_layers, cfg.n_heads, cfg.n_kv_heads = 3, 4, 2
+    torch.manual_seed(0)
+    P_me = distdl_b200.backends.backend.Partition().create_partition_inclusive([rank])
+    whole = models.Decoder(cfg, models.ParallelLayout(1, 1, P_world=P_me))
+    piped = models.PipelinedDecoder(cfg, pp=2, dp=1, tp=1)
+    lo, hi = piped.model.layer_range
+    assert (lo, hi) == ((0, 2) if rank == 0 else (2, 3))
+    src = whole.state_dict()
+    mapped = {}
+    for k in piped.model.state_dict():
+        parts = k.split(".")
+        if parts[0] == "blocks":
+            parts[1] = str(int(parts[1]) + lo)
+        mapped[k] = src[".".join(parts)]
+    piped.model.load_state_dict(mapped)
+    gen = torch.Generator().manual_seed(3)
+    tokens = torch.randint(0, cfg.vocab_size, (3, 17), generator=gen)
+    scale = 1.0 / (3 * 16)
+    total = piped.global_loss(piped.forward_backward(tokens, micro_batch=1, scale=scale))
+    piped.model.release_gathered()
+    whole.train()
+    ref = whole.loss(tokens[:, :-1], tokens[:, 1:], scale=scale)
+    ref.backward()
+    whole.release_gathered()
+    assert torch.allclose(total, ref.detach(), rtol=1e-5), (total, ref)
+    ref_grads = dict(whole.named_parameters())
+    for k, p in piped.model.named_parameters():
+        parts = k.split(".")
+        if parts[0] == "blocks":
+            parts[1] = str(int(parts[1]) + lo)
+        g = ref_grads[".".join(parts)].grad
+        assert p.grad is not None and torch.allclose(p.grad, g, rtol=1e-4, atol=1e-6), (k, (p.grad - g).abs().max())
+    return float(total)
+
+
+def test_pipelined_decoder_matches_whole_model():
+    out = run_ranks("test_models", "body_pipelined_decoder", 2, timeout=300)
+    assert out[0] == out[1]
+
+
+def body_pipelined_tp_trains(rank, world):
+    """Two stages of two tensor-parallel workers each: the loss falls on a repeated batch."""
+    from distdl_b200 import models
+    from distdl_b200.parallel import FlatAdamW
+    torch.manual_seed(0)
+    cfg = models.llama_tiny(dtype=torch.float32, max_seq=16, vocab_size=96, d_model=32, ffn_dim=64)
+    cfg.n_layers, cfg.n_heads, cfg.n_kv_heads = 2, 4, 2
+    piped = models.PipelinedDecoder(cfg, pp=2, dp=1, tp=2)
+    opt = FlatAdamW(piped.model, lr=1e-2, weight_decay=0.0, max_grad_norm=1.0)
+    gen = torch.Generator().manual_seed(3)
+    tokens = torch.randint(0, cfg.vocab_size, (4, 17), generator=gen)
+    losses = []
+    for _ in range(6):
+        total = piped.global_loss(piped.forward_backward(tokens, micro_batch=2, scale=1.0 / 64))
+        opt.step()
+        losses.append(float(total))
+    assert losses[-1] < losses[0] - 0.2, losses
+    return losses
+
+
+def test_pipelined_tensor_parallel_decoder_trains():
+    out = run_ranks("test_models", "body_pipelined_tp_trains", 4, timeout=300)
+    assert out[0] == out[3]
