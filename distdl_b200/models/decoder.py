@@ -57,6 +57,8 @@ class DecoderConfig:
     keep_norms_gathered: bool = True  # and for the norm weights of the blocks (a few KB each)
     prefetch: bool = True             # gather the next block's ZeRO weights while the current block computes
     init_std: float = 0.02
+    collect_state: bool = False       # state_dict() / load_state_dict() in the serial layout on the first worker:
+                                      # a checkpoint that loads on any worker grid (dense models only)
 
     @property
     def head_dim(self):
@@ -111,25 +113,27 @@ def _norm(cfg, P, zero, keep=None):
     keep = (cfg.keep_gathered or cfg.keep_norms_gathered) if keep is None else keep
     if cfg.norm == "rms":
         return dnn.DistributedRMSNormZero(P, cfg.d_model, eps=cfg.eps, dtype=cfg.dtype,
-                                          auto_clear_buffer=not keep)
+                                          auto_clear_buffer=not keep, collect_state=cfg.collect_state)
     if zero:
         return dnn.DistributedLayerNormZero(P, cfg.d_model, eps=cfg.eps, dtype=cfg.dtype,
-                                            auto_clear_buffer=not keep)
-    return dnn.DistributedLayerNorm(P, cfg.d_model, eps=cfg.eps, dtype=cfg.dtype)
+                                            auto_clear_buffer=not keep, collect_state=cfg.collect_state)
+    return dnn.DistributedLayerNorm(P, cfg.d_model, eps=cfg.eps, dtype=cfg.dtype, collect_state=cfg.collect_state)
 
 
 def _col(cfg, layout, fin, fout, **kw):
     cls = dnn.DistributedLinearAllGatherZero if cfg.zero else dnn.DistributedLinearAllGather
     if cfg.zero:
         kw["auto_clear_buffer"] = not cfg.keep_gathered
-    return cls(layout.P_feat, fin, fout, bias=cfg.bias, dtype=cfg.dtype, P_x=layout.P_seq, **kw)
+    return cls(layout.P_feat, fin, fout, bias=cfg.bias, dtype=cfg.dtype, P_x=layout.P_seq,
+               collect_state=cfg.collect_state, **kw)
 
 
 def _row(cfg, layout, fin, fout, **kw):
     cls = dnn.DistributedLinearReduceScatterZero if cfg.zero else dnn.DistributedLinearReduceScatter
     if cfg.zero:
         kw["auto_clear_buffer"] = not cfg.keep_gathered
-    return cls(layout.P_feat, fin, fout, bias=cfg.bias, dtype=cfg.dtype, P_y=layout.P_seq, **kw)
+    return cls(layout.P_feat, fin, fout, bias=cfg.bias, dtype=cfg.dtype, P_y=layout.P_seq,
+               collect_state=cfg.collect_state, **kw)
 
 
 class Attention(torch.nn.Module):
@@ -230,17 +234,22 @@ class Decoder(torch.nn.Module):
         keep_root = cfg.keep_gathered or cfg.keep_root_gathered
         if self.first_stage:
             self.embed = dnn.DistributedEmbeddingZero(layout.P_flat2, V, cfg.d_model, dtype=cfg.dtype,
-                                                      auto_clear_buffer=not keep_root)
+                                                      auto_clear_buffer=not keep_root,
+                                                      collect_state=cfg.collect_state)
             if not cfg.rope:
                 self.pos_embed = dnn.DistributedEmbeddingZero(layout.P_flat2, cfg.max_seq, cfg.d_model,
-                                                              dtype=cfg.dtype, auto_clear_buffer=not keep_root)
+                                                              dtype=cfg.dtype, auto_clear_buffer=not keep_root,
+                                                              collect_state=cfg.collect_state)
         lo, hi = stage_layers(cfg.n_layers, self.stage_index, self.n_stages)
         self.layer_range = (lo, hi)
         self.blocks = torch.nn.ModuleList(Block(cfg, layout) for _ in range(hi - lo))
         if self.last_stage:
             self.final_norm = _norm(cfg, layout.P_flat, True, keep=keep_root)
             self.head = dnn.DistributedLinearAllGatherZero(layout.P_flat, cfg.d_model, V, bias=False, dtype=cfg.dtype,
-                                                           auto_clear_buffer=not keep_root)
+                                                           auto_clear_buffer=not keep_root,
+                                                           collect_state=cfg.collect_state)
+        if cfg.collect_state and cfg.n_experts:
+            raise ValueError("collect_state is implemented for dense decoders only")
         self.reset_parameters()
 
     def reset_parameters(self):

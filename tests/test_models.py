@@ -206,3 +206,46 @@ def body_pipelined_tp_trains(rank, world):
 def test_pipelined_tensor_parallel_decoder_trains():
     out = run_ranks("test_models", "body_pipelined_tp_trains", 4, timeout=300)
     assert out[0] == out[3]
+
+
+def body_collected_decoder(rank, world, family, dp, tp, cp, serial, tokens):
+    """With ``collect_state`` the decoder's state dict is the serial one on the first worker: saved on
+    one worker grid, it loads on another and gives the same loss on the same batch."""
+    import torch.distributed as dist
+
+    from distdl_b200 import models
+    cfg = {"llama": models.llama_tiny, "gpt2": models.gpt2_tiny}[family](dtype=torch.float32, max_seq=16,
+                                                                       vocab_size=100, d_model=48, ffn_dim=96)
+    cfg.n_layers, cfg.collect_state = 2, True
+    cfg.n_heads, cfg.n_kv_heads = (4, 2) if family == "llama" else (4, 4)
+    torch.manual_seed(rank)
+    model = models.Decoder(cfg, models.ParallelLayout(dp, tp, cp=cp))
+    if serial is not None:
+        model.load_state_dict(serial if rank == 0 else {})
+    model.eval()
+    with torch.no_grad():
+        loss = model.loss(tokens[:, :-1], tokens[:, 1:], scale=1.0 / (dp * tokens.shape[0] * 16))
+        model.release_gathered()
+    dist.all_reduce(loss)
+    sd = model.state_dict()
+    if rank != 0:
+        assert len(sd) == 0, list(sd)[:4]
+    return float(loss), ({k: v.clone() for k, v in sd.items()} if rank == 0 else None)
+
+
+def test_collected_decoder_checkpoint_moves_between_worker_grids():
+    gen = torch.Generator().manual_seed(9)
+    tokens = torch.randint(0, 100, (2, 17), generator=gen)        # every data-parallel replica: the same batch
+    for family in ("llama", "gpt2"):
+        loss4, serial = run_ranks("test_models", "body_collected_decoder", 4,
+                                  args=(family, 2, 2, 1, None, tokens), timeout=300)[0]
+        assert all(v.dim() <= 2 for v in serial.values())
+        loss2 = run_ranks("test_models", "body_collected_decoder", 2, args=(family, 1, 2, 1, serial, tokens),
+                          timeout=300)[0][0]
+        loss1, again = run_ranks("test_models", "body_collected_decoder", 1, args=(family, 1, 1, 1, serial, tokens),
+                                 timeout=300)[0]
+        losscp = run_ranks("test_models", "body_collected_decoder", 4, args=(family, 1, 2, 2, serial, tokens),
+                           timeout=300)[0][0]
+        assert abs(loss4 - loss1) < 1e-4 * abs(loss1) and abs(loss2 - loss1) < 1e-4 * abs(loss1), (loss4, loss2, loss1)
+        assert abs(losscp - loss1) < 1e-4 * abs(loss1), (losscp, loss1)
+        assert set(again) == set(serial) and all(torch.equal(again[k], serial[k]) for k in serial)
