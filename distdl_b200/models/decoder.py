@@ -57,6 +57,8 @@ class DecoderConfig:
     keep_norms_gathered: bool = True  # and for the norm weights of the blocks (a few KB each)
     prefetch: bool = True             # gather the next block's ZeRO weights while the current block computes
     init_std: float = 0.02
+    cp_mode: str = "ring"             # context-parallel attention: "ring" (K / V blocks travel) or "a2a"
+                                      # (head <-> sequence all-to-all; local head counts must divide by cp)
     collect_state: bool = False       # state_dict() / load_state_dict() in the serial layout on the first worker:
                                       # a checkpoint that loads on any worker grid (dense models only)
 
@@ -146,7 +148,10 @@ class Attention(torch.nn.Module):
         self.qkv = _col(cfg, layout, cfg.d_model, (cfg.n_heads + 2 * cfg.n_kv_heads) * hd, num_heads=cfg.n_heads,
                         num_heads_kv=cfg.n_kv_heads)
         self.out = _row(cfg, layout, cfg.n_heads * hd, cfg.d_model, num_heads=cfg.n_heads)
-        self.ring = dnn.DistributedRingAttention(layout.P_ring, causal=True) if layout.cp > 1 else None
+        self.ring = None
+        if layout.cp > 1:
+            cls = {"ring": dnn.DistributedRingAttention, "a2a": dnn.DistributedSelfAttention}[cfg.cp_mode]
+            self.ring = cls(layout.P_ring, causal=True)
 
     def forward(self, x):
         cfg = self.cfg

@@ -19,9 +19,10 @@ from .repartition import Repartition
 
 class DistributedSelfAttention(Module):
     r"""``forward(q, k, v) -> out`` with ``q [b, s_local, Hq, D]``, ``k, v [b, s_local, Hkv, D]``
-    on ``P_seq = [B, S, 1, 1]`` (batch x sequence split); heads must divide by ``S``
-    (``Hkv`` too).  ``causal`` masks with GLOBAL positions, which the head-split layout
-    gives for free because every worker then holds complete sequences."""
+    on ``P_seq = [B, S, H, 1]`` (batch x sequence split; ``H`` > 1 when the heads are already
+    split over tensor-parallel workers); the local head counts must divide by ``S`` (``Hkv``
+    too).  ``causal`` masks with GLOBAL positions, which the head-split layout gives for free
+    because every worker then holds complete sequences."""
 
     def __init__(self, P_seq, causal=True, scale=None):
         super().__init__()
@@ -29,12 +30,13 @@ class DistributedSelfAttention(Module):
         self.causal, self.scale = causal, scale
         if not P_seq.active:
             return
-        if P_seq.dim != 4 or int(P_seq.shape[2]) != 1 or int(P_seq.shape[3]) != 1:
-            raise ValueError("DistributedSelfAttention expects a partition of shape [B, S, 1, 1]")
-        B, S = int(P_seq.shape[0]), int(P_seq.shape[1])
+        if P_seq.dim != 4 or int(P_seq.shape[3]) != 1:
+            raise ValueError("DistributedSelfAttention expects a partition of shape [B, S, H, 1]")
+        B, S, H = int(P_seq.shape[0]), int(P_seq.shape[1]), int(P_seq.shape[2])
         self.S = S
         base = P_seq.create_partition_inclusive(range(P_seq.size))
-        self.P_head = base.create_cartesian_topology_partition([B, 1, S, 1])
+        # worker (b, c, t) of the input grid becomes head shard c * H + t of batch shard b
+        self.P_head = base.create_cartesian_topology_partition([B, 1, S * H, 1])
         self.to_heads_q = Repartition(P_seq, self.P_head)
         self.to_heads_k = Repartition(P_seq, self.P_head)
         self.to_heads_v = Repartition(P_seq, self.P_head)

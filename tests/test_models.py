@@ -89,7 +89,7 @@ def test_trainer_checkpoint_and_metrics(tmp_path):
     run_ranks("test_models", "body_trainer_checkpoint", 2, args=(str(tmp_path),), timeout=300)
 
 
-def body_context_parallel(rank, world, family, tp):
+def body_context_parallel(rank, world, family, tp, cp_mode="ring"):
     """Context parallelism (ring attention over two blocks of every sequence) against the same
     weights run WITHOUT it.  On the same worker grid, ``ParallelLayout(dp=1, cp=2, tp)`` and
     ``ParallelLayout(dp=2, cp=1, tp)`` shard every parameter identically, so the same seed gives the
@@ -103,7 +103,9 @@ def body_context_parallel(rank, world, family, tp):
     cfg = {"llama": models.llama_tiny, "gpt2": models.gpt2_tiny}[family](dtype=torch.float32, max_seq=32,
                                                                        vocab_size=200, d_model=48, ffn_dim=96)
     cfg.n_heads, cfg.n_kv_heads = (4, 2) if family == "llama" else (3, 3)
-    cfg.n_layers = 2
+    if cp_mode == "a2a":
+        cfg.n_heads, cfg.n_kv_heads = 8, 4           # local head counts must divide by the context-parallel size
+    cfg.n_layers, cfg.cp_mode = 2, cp_mode
     torch.manual_seed(0)
     cp_model = models.Decoder(cfg, models.ParallelLayout(1, tp, cp=2))
     torch.manual_seed(0)
@@ -134,6 +136,7 @@ def test_context_parallel_decoder_matches_full_sequence_attention():
     run_ranks("test_models", "body_context_parallel", 2, args=("llama", 1), timeout=300)
     run_ranks("test_models", "body_context_parallel", 4, args=("llama", 2), timeout=300)
     run_ranks("test_models", "body_context_parallel", 4, args=("gpt2", 2), timeout=300)
+    run_ranks("test_models", "body_context_parallel", 4, args=("llama", 2, "a2a"), timeout=300)
 
 
 def body_pipelined_decoder(rank, world):
