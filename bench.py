@@ -97,6 +97,23 @@ def layout_for(n):
     return {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (4, 2)}[n]
 
 
+def model_flops_report(cfg, seq, tokens_per_s, gpus):
+    """Model FLOPs per token (forward + backward, recomputation not counted) turned into TFLOP/s per
+    GPU, and its fraction of the measured sustained cuBLAS bf16 rate when that file is present."""
+    per_token = cfg.train_flops_per_token(seq)
+    tflops = tokens_per_s * per_token / max(1, gpus) / 1e12
+    out = {"gflop_per_token": per_token / 1e9, "tflops_per_gpu": tflops}
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as fh:
+                peak = float(json.load(fh)["bf16_tflops_sustained"])
+            out["fraction_of_measured_sustained_bf16"] = tflops / peak
+        except (OSError, ValueError, KeyError):
+            pass
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -268,6 +285,7 @@ def main():
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": data.bytes_per_block, "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "final_loss": losses[-1] if losses else None, "device_status": status[0],
+            "model_flops": model_flops_report(cfg, seq, value, args.gpus),
         }
         print(json.dumps(out))
     if world > 1:

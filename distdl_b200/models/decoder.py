@@ -79,6 +79,21 @@ class DecoderConfig:
         emb = 2 * self.vocab_size * d + (0 if self.rope else self.max_seq * d)
         return L * (attn + ffn + 2 * d) + emb + d
 
+    def train_flops_per_token(self, seq: int = None):
+        """Model FLOPs of one training token (forward + backward, no recomputation): 6 per weight
+        that takes part in a matrix product (of the experts only the ``top_k`` that a token
+        visits; the embedding lookup is not a product, the head is) plus causal attention."""
+        seq = self.max_seq if seq is None else seq
+        d, f, L, hd = self.d_model, self.ffn_dim, self.n_layers, self.head_dim
+        attn = d * (self.n_heads + 2 * self.n_kv_heads) * hd + self.n_heads * hd * d
+        ffn = (3 if self.activation == "swiglu" else 2) * d * f
+        if self.n_experts:
+            ffn = ffn * self.top_k + d * self.n_experts
+        weights = L * (attn + ffn) + self.vocab_size * d
+        # scores and context: 2 products of seq x head_dim per head and token, half of them masked
+        attention = L * 2 * 2 * seq * self.n_heads * hd * 0.5
+        return 6.0 * weights + 3.0 * attention
+
 
 class ParallelLayout:
     """The partitions a decoder needs, derived from a ``[D, C, M]`` worker grid: ``D`` data-parallel

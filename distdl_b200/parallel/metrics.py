@@ -1,6 +1,9 @@
 """Rank-0 JSONL metrics sink: one line per training step (step, loss, step time as the
-maximum over ranks, tokens/s of the whole job, learning rate, gradient norm) plus
-free-form records.  The reference has logging only (``src/distdl/logger.py``)."""
+maximum over ranks, tokens/s of the whole job, learning rate, gradient norm; with
+``flops_per_token`` also the model TFLOP/s per GPU and, with ``peak_tflops``, the fraction of
+that peak; with ``device_waits`` the milliseconds this rank's fused kernels spent waiting for
+other GPUs since the last logged step, by kind) plus free-form records.  The reference has
+logging only (``src/distdl/logger.py``)."""
 from __future__ import annotations
 
 import json
@@ -11,8 +14,11 @@ import torch.distributed as dist
 
 
 class MetricsSink:
-    def __init__(self, path: str, every: int = 1):
+    def __init__(self, path: str, every: int = 1, flops_per_token: float = None, peak_tflops: float = None,
+                 device_waits: bool = False):
         self.path, self.every = path, max(1, int(every))
+        self.flops_per_token, self.peak_tflops, self.device_waits = flops_per_token, peak_tflops, device_waits
+        self.world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
         self.rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
         self._fh = open(path, "a", buffering=1) if self.rank == 0 else None
         self._t_last = None
@@ -36,9 +42,18 @@ class MetricsSink:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         self._t_last = (now, step)
-        self.record(step=int(step), loss=float(loss), ms_per_step=ms,
-                    tokens_per_s=(tokens / (ms / 1e3)) if ms else None, lr=lr,
-                    grad_norm=None if grad_norm is None else float(grad_norm))
+        tps = (tokens / (ms / 1e3)) if ms else None
+        extra = {}
+        if self.flops_per_token and tps:
+            extra["model_tflops_per_gpu"] = tps * self.flops_per_token / self.world / 1e12
+            if self.peak_tflops:
+                extra["fraction_of_peak"] = extra["model_tflops_per_gpu"] / self.peak_tflops
+        if self.device_waits and torch.cuda.is_available():
+            from .. import _native
+            waits = _native.read_wait_ns()          # reads and clears; synchronises the device
+            extra["wait_ms"] = {k: v / 1e6 for k, v in waits.items() if v}
+        self.record(step=int(step), loss=float(loss), ms_per_step=ms, tokens_per_s=tps, lr=lr,
+                    grad_norm=None if grad_norm is None else float(grad_norm), **extra)
 
     def close(self):
         if self._fh is not None:

@@ -40,3 +40,14 @@ def test_reference_arm_reports_unavailable_and_exits_zero():
     assert res.returncode == 0
     line = json.loads(res.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and "unavailable" in line
+
+
+def test_model_flops_report():
+    from distdl_b200 import models
+    b = _bench()
+    cfg = models.llama3_8b()
+    r = b.model_flops_report(cfg, 4096, 8 * 16000.0, 8)
+    assert abs(r["tflops_per_gpu"] - 16000.0 * r["gflop_per_token"] / 1e3) < 1e-6
+    assert 700 < r["tflops_per_gpu"] < 850
+    if "fraction_of_measured_sustained_bf16" in r:
+        assert 0.3 < r["fraction_of_measured_sustained_bf16"] < 1.0

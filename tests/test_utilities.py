@@ -184,3 +184,28 @@ def body_buffer_sharing_network(rank, world):
 def test_buffer_manager_shared_by_a_network_of_layers():
     from dist_harness import run_ranks
     run_ranks("test_utilities", "body_buffer_sharing_network", 4, timeout=240)
+
+
+def test_metrics_sink_reports_model_flops(tmp_path):
+    import json
+    import time
+
+    from distdl_b200 import models
+    from distdl_b200.parallel import MetricsSink
+    cfg = models.llama3_8b()
+    # 6 FLOPs per matrix weight and token plus causal attention: about 48 GFLOP per token at 4096
+    assert 47e9 < cfg.train_flops_per_token() < 50e9
+    assert cfg.train_flops_per_token(8192) > cfg.train_flops_per_token(4096)
+    moe = models.mixtral_8x7b()
+    assert moe.train_flops_per_token() < 6.0 * moe.num_parameters() / 2      # two of eight experts per token
+    path = tmp_path / "m.jsonl"
+    sink = MetricsSink(str(path), flops_per_token=1e9, peak_tflops=1.0)
+    sink.step(1, 2.0, tokens=1000)
+    time.sleep(0.05)
+    sink.step(2, 1.5, tokens=1000, lr=1e-3, grad_norm=0.7)
+    sink.close()
+    rows = [json.loads(line) for line in path.read_text().splitlines()]
+    assert rows[0]["ms_per_step"] is None and "model_tflops_per_gpu" not in rows[0]
+    r = rows[1]
+    assert abs(r["model_tflops_per_gpu"] - r["tokens_per_s"] * 1e9 / 1e12) < 1e-9
+    assert abs(r["fraction_of_peak"] - r["model_tflops_per_gpu"]) < 1e-12 and r["grad_norm"] == 0.7
