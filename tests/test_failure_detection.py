@@ -205,3 +205,54 @@ def body_trainer_heartbeat(rank, world):
 def test_trainer_step_raises_when_a_peer_stopped_beating():
     out = run_ranks("test_failure_detection", "body_trainer_heartbeat", 2, timeout=180)
     assert out == ["detected (1,)", "silent"], out
+
+
+# ------------------------------------------------ the flag protocol, modelled on the host
+def test_flag_protocol_overlapping_teams_and_counter_wrap():
+    """Counters are per pair of ranks and only grow: launches on overlapping teams stay in step
+    without any reset, also across the wrap of the 32-bit counters."""
+    from distdl_b200.parallel import protocol_model as pm
+    assert pm.signed_distance(3, 0xFFFFFFFE) == 5 and pm.signed_distance(0xFFFFFFFE, 3) == -5
+    teams = [[0, 1, 2, 3], [0, 1], [2, 3], [0, 2], [1, 3], [1, 2], [3, 0, 1]]
+    for start in (0, (1 << 32) - 7):
+        world = pm.World(4, ctas=2, start=start, spin_limit_s=20.0)
+
+        def rank_program(me):
+            seen = []
+            for it in range(12):
+                for team in teams:
+                    if me in team:
+                        got = world.all_gather(me, team, (me, it, tuple(team)))
+                        assert got == [(peer, it, tuple(team)) for peer in team], (me, it, team, got)
+                        seen.append(len(got))
+            return sum(seen)
+        out = pm.run_ranks(world, rank_program)
+        assert all(world.status[r].code == 0 for r in range(4)) and out[0] > 0
+        # 12 rounds x 2 steps per launch, counted per pair: ranks 0 and 1 share three of the teams
+        assert world.steps_done[0][1] - start == 12 * 2 * 3
+        assert world.pad[0][0][1] == (start + 12 * 2 * 3) & 0xFFFFFFFF
+
+
+def test_flag_protocol_withheld_signal_times_out_and_fails_fast():
+    """A peer whose signals never arrive: the bounded wait records (1005, 100 + step, expected, seen),
+    the launch returns without a result, and every later wait of that rank gives up at once."""
+    from distdl_b200.parallel import protocol_model as pm
+    world = pm.World(2, ctas=1, spin_limit_s=0.3)
+    world.withheld.add((1, 0))                     # rank 1's signals to rank 0 are lost
+
+    def rank_program(me):
+        t0 = time.monotonic()
+        first = world.all_gather(me, [0, 1], me)
+        t1 = time.monotonic()
+        second = world.all_gather(me, [0, 1], me)
+        return first, second, t1 - t0, time.monotonic() - t1
+    (a1, a2, ta1, ta2), (b1, b2, _, _) = pm.run_ranks(world, rank_program)
+    assert a1 is None and a2 is None
+    code, where, expected, seen = world.status[0].read()
+    assert (code, where, expected, seen) == (pm.TIMEOUT_CODE, 100, 1, 0)
+    assert ta1 >= 0.3 and ta2 < 0.2                # the second launch does not wait again
+    # rank 1 got rank 0's first signal and read a result; after that its counters are out of step with
+    # rank 0's (whose second launch signals again while giving up at once), so one of its later waits runs
+    # out as well: a failure on one rank surfaces on its peers, which is why the heap is then poisoned
+    assert b1 == [0, 1] and b2 is None
+    assert world.status[1].code == pm.TIMEOUT_CODE and world.status[1].where in (100, 101)
