@@ -309,6 +309,41 @@ def check_moe_peer():
         assert err < 2e-2, ("moe peer", what, err)
 
 
+def check_context_parallel_decoder():
+    """The decoder with a context-parallel size of 2 against the data-parallel decoder with the
+    same shards fed whole sequences on both replicas (its loss and gradients are exactly twice
+    those of the context-parallel model).  bf16, head dim 128, block length 256: the ring runs
+    the tcgen05 attention kernels per block and the rotary kernel with a position offset.
+    Run by name only (``multi_gpu_worker.py context_decoder`` on an even number of GPUs)."""
+    from distdl_b200 import models
+    world = dist.get_world_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    cfg = models.llama_tiny(d_model=512, n_heads=4, n_kv_heads=2, ffn_dim=1024, max_seq=512, vocab_size=1024)
+    cfg.n_layers = 2
+    tp = world // 2
+    torch.manual_seed(0)
+    cp_model = models.Decoder(cfg, models.ParallelLayout(1, tp, cp=2))
+    torch.manual_seed(0)
+    dp_model = models.Decoder(cfg, models.ParallelLayout(2, tp))
+    gen = torch.Generator().manual_seed(5)
+    tokens = torch.randint(0, cfg.vocab_size, (2, 513), generator=gen).to(dev)
+    out = {}
+    for name, model in (("cp", cp_model), ("dp", dp_model)):
+        model.train()
+        loss = model.loss(tokens[:, :-1], tokens[:, 1:], scale=1.0 / 1024)
+        loss.backward()
+        model.release_gathered()
+        total = loss.detach().float().clone()
+        dist.all_reduce(total)
+        out[name] = (total, [None if p.grad is None else p.grad.float().clone() for p in model.parameters()])
+    assert abs(float(out["cp"][0]) * 2 - float(out["dp"][0])) < 2e-2 * abs(float(out["dp"][0])), \
+        (float(out["cp"][0]), float(out["dp"][0]))
+    for ga, gb in zip(out["cp"][1], out["dp"][1]):
+        if ga is not None and ga.numel():
+            err = (ga * 2 - gb).abs().max() / gb.abs().max().clamp_min(1e-6)
+            assert err < 5e-2, float(err)
+
+
 def main():
     import distdl_b200
     from distdl_b200.backends.common import world as dworld
@@ -326,6 +361,8 @@ def main():
         check_ring_attention()
         check_symmetric_params()
         check_moe_peer()
+    if what == "context_decoder":
+        check_context_parallel_decoder()
     if what in ("fused", "all"):
         from multi_gpu_fused import check_fused
         check_fused()
