@@ -522,3 +522,72 @@ def body_transposed_feature_conv_general(rank, world):
 
 def test_transposed_feature_conv_crossing_worker_boundaries():
     run_ranks("test_layers_conv", "body_transposed_feature_conv_general", 4, timeout=300)
+
+
+def body_conv3d_channel_and_general(rank, world):
+    """3-D channel convolution (kernel blocks on a 2 x 2 grid) and 3-D general convolution (channels
+    AND space split, 4 workers) through the selector, against serial conv3d: output and input gradient."""
+    import torch.distributed as dist
+
+    import distdl_b200.nn as dnn
+    torch.manual_seed(0)
+    # channel: P_x [1, 2, 1, 1, 1] (in), P_y [1, 2, 1, 1, 1] (out), P_w [2, 2, 1, 1, 1]
+    P_x, P_y = _cart([0, 1], [1, 2, 1, 1, 1]), _cart([0, 1], [1, 2, 1, 1, 1])
+    P_w = _cart([0, 1, 2, 3], [2, 2, 1, 1, 1])
+    layer = dnn.DistributedConv3d(P_x, P_y, P_w, in_channels=4, out_channels=6, kernel_size=3, padding=1)
+    assert isinstance(layer, dnn.DistributedChannelConv3d)
+    W, b = torch.zeros(6, 4, 3, 3, 3), torch.zeros(6)
+    co, ci = rank // 2, rank % 2
+    W[co * 3:(co + 1) * 3, ci * 2:(ci + 1) * 2] = layer.conv_layer.weight.detach()
+    if ci == 0:
+        b[co * 3:(co + 1) * 3] = layer.conv_layer.bias.detach()
+    dist.all_reduce(W)
+    dist.all_reduce(b)
+    xg = _sync(torch.randn(2, 4, 4, 5, 3))
+    x0, x = _scatter(P_x, xg, rank, 5)
+    y = _gather(P_y, layer(x), 5)
+    if rank == 0:
+        xs = xg.clone().requires_grad_()
+        ys = torch.nn.functional.conv3d(xs, W, b, padding=1)
+        assert torch.allclose(y, ys, atol=1e-5)
+        g = torch.randn_like(ys)
+        ys.backward(g)
+        y.backward(g)
+        assert torch.allclose(x0.grad, xs.grad, atol=1e-5)
+    else:
+        y.backward(torch.zeros_like(y))
+    # general: input channels over 2 workers and depth over 2 workers
+    P_x = _cart([0, 1, 2, 3], [1, 2, 2, 1, 1])
+    P_y = _cart([0, 1], [1, 1, 2, 1, 1])            # one block of output channels: the workers with ci = 0
+    P_w = _cart([0, 1, 2, 3], [1, 2, 2, 1, 1])
+    gen = dnn.DistributedConv3d(P_x, P_y, P_w, in_channels=4, out_channels=4, kernel_size=3, padding=1)
+    assert isinstance(gen, dnn.DistributedGeneralConv3d)
+    xg = _sync(torch.randn(1, 4, 6, 4, 3))
+    x0, x = _scatter(P_x, xg, rank, 5)
+    # kernel blocks [co, ci / 2, 3, 3, 3] live on the workers with depth index 0 (ranks 0 and 2), the bias on rank 0
+    Wg, bg = torch.zeros(4, 4, 3, 3, 3), torch.zeros(4)
+    if rank in (0, 2):
+        Wg[:, rank:rank + 2] = gen.weight.detach()
+    if rank == 0:
+        bg += gen.bias.detach()
+    dist.all_reduce(Wg)
+    dist.all_reduce(bg)
+    yl = gen(x)
+    if P_y.active:
+        assert tuple(yl.shape) == (1, 4, 3, 4, 3)
+    y = _gather(P_y, yl, 5)
+    if rank == 0:
+        xs = xg.clone().requires_grad_()
+        ys = torch.nn.functional.conv3d(xs, Wg, bg, padding=1)
+        assert torch.allclose(y, ys, atol=1e-5), (y - ys).abs().max()
+        g = torch.randn_like(ys)
+        ys.backward(g)
+        y.backward(g)
+        assert torch.allclose(x0.grad, xs.grad, atol=1e-5)
+    else:
+        y.backward(torch.zeros_like(y))
+    return True
+
+
+def test_conv3d_channel_and_general_via_selector():
+    run_ranks("test_layers_conv", "body_conv3d_channel_and_general", 4, timeout=300)
