@@ -183,9 +183,8 @@ def _make(base, nd, transposed, name, doc):
 
 
 _DOC = "Channel all-gather {}convolution, {}-D (see the base class)."
-DistributedChannelAllGatherConv1d = _make(_ChannelAllGatherConv, 1, False, "DistributedChannelAllGatherConv1d", _DOC.format("", 1))
-DistributedChannelAllGatherConv2d = _make(_ChannelAllGatherConv, 2, False, "DistributedChannelAllGatherConv2d", _DOC.format("", 2))
-DistributedChannelAllGatherConv3d = _make(_ChannelAllGatherConv, 3, False, "DistributedChannelAllGatherConv3d", _DOC.format("", 3))
-DistributedChannelAllGatherConvTranspose1d = _make(_ChannelAllGatherConv, 1, True, "DistributedChannelAllGatherConvTranspose1d", _DOC.format("transposed ", 1))
-DistributedChannelAllGatherConvTranspose2d = _make(_ChannelAllGatherConv, 2, True, "DistributedChannelAllGatherConvTranspose2d", _DOC.format("transposed ", 2))
-DistributedChannelAllGatherConvTranspose3d = _make(_ChannelAllGatherConv, 3, True, "DistributedChannelAllGatherConvTranspose3d", _DOC.format("transposed ", 3))
+for _nd in (1, 2, 3):
+    for _transposed in (False, True):
+        _name = f"DistributedChannelAllGatherConv{'Transpose' if _transposed else ''}{_nd}d"
+        globals()[_name] = _make(_ChannelAllGatherConv, _nd, _transposed, _name, _DOC.format("transposed " if _transposed else "", _nd))
+del _nd, _transposed, _name

@@ -44,9 +44,8 @@ class _ChannelReduceScatterConv(_ChannelConvNd):
 
 
 _DOC = "Channel reduce-scatter {}convolution, {}-D (see the base class)."
-DistributedChannelReduceScatterConv1d = _make(_ChannelReduceScatterConv, 1, False, "DistributedChannelReduceScatterConv1d", _DOC.format("", 1))
-DistributedChannelReduceScatterConv2d = _make(_ChannelReduceScatterConv, 2, False, "DistributedChannelReduceScatterConv2d", _DOC.format("", 2))
-DistributedChannelReduceScatterConv3d = _make(_ChannelReduceScatterConv, 3, False, "DistributedChannelReduceScatterConv3d", _DOC.format("", 3))
-DistributedChannelReduceScatterConvTranspose1d = _make(_ChannelReduceScatterConv, 1, True, "DistributedChannelReduceScatterConvTranspose1d", _DOC.format("transposed ", 1))
-DistributedChannelReduceScatterConvTranspose2d = _make(_ChannelReduceScatterConv, 2, True, "DistributedChannelReduceScatterConvTranspose2d", _DOC.format("transposed ", 2))
-DistributedChannelReduceScatterConvTranspose3d = _make(_ChannelReduceScatterConv, 3, True, "DistributedChannelReduceScatterConvTranspose3d", _DOC.format("transposed ", 3))
+for _nd in (1, 2, 3):
+    for _transposed in (False, True):
+        _name = f"DistributedChannelReduceScatterConv{'Transpose' if _transposed else ''}{_nd}d"
+        globals()[_name] = _make(_ChannelReduceScatterConv, _nd, _transposed, _name, _DOC.format("transposed " if _transposed else "", _nd))
+del _nd, _transposed, _name

@@ -14,6 +14,12 @@ from .mixins.halo_mixin import HaloMixin
 from .module import Module
 
 
+def _per_dim(v, nd):
+    """A scalar or per-dimension setting as an integer array with one entry per spatial dimension."""
+    a = np.atleast_1d(np.asarray(v, dtype=int))
+    return a * np.ones(nd, dtype=int) if np.ndim(v) == 0 else a
+
+
 class DistributedFeatureConvBase(Module, HaloMixin, ConvMixin):
     r"""Convolution of a tensor ``[batch, channel, *space]`` whose *spatial*
     dimensions are split over ``P_x = [1, 1, *P_space]``.
@@ -40,7 +46,7 @@ class DistributedFeatureConvBase(Module, HaloMixin, ConvMixin):
         if not P_x.active:
             return
         nd = self.num_dimensions
-        exp = lambda v: np.atleast_1d(np.asarray(v, dtype=int)) * (np.ones(nd, dtype=int) if np.ndim(v) == 0 else 1)  # noqa: E731
+        exp = lambda v: _per_dim(v, nd)  # noqa: E731
         self.in_channels, self.out_channels = in_channels, out_channels
         self.kernel_size, self.stride = exp(kernel_size), exp(stride)
         self.padding, self.dilation = exp(padding), exp(dilation)
@@ -205,7 +211,7 @@ class _FeatureConvTransposeBase(Module):
         if not P_x.active:
             return
         nd = self.num_dimensions
-        exp = lambda v: tuple(int(a) for a in (np.atleast_1d(np.asarray(v, dtype=int)) * (np.ones(nd, dtype=int) if np.ndim(v) == 0 else 1)))  # noqa: E731,E501
+        exp = lambda v: tuple(int(a) for a in _per_dim(v, nd))  # noqa: E731
         self.in_channels, self.out_channels = in_channels, out_channels
         self.kernel_size, self.stride, self.padding = exp(kernel_size), exp(stride), exp(padding)
         self.output_padding, self.dilation, self.groups = exp(output_padding), exp(dilation), groups
