@@ -225,9 +225,11 @@ class Partition:
             raise Exception("Cannot create union: partitions do not share a root.")
         me = world.world_rank()
         in_src, in_dest = me in self.ranks, me in P_dest.ranks
+        # pure arithmetic on rank lists: workers outside both partitions check the rules as well, so
+        # that a violation raises on every worker and not only on the members
+        groups, src_colour, dest_colour = self._broadcast_groups(P_dest, transpose_src, transpose_dest)
         if not (in_src or in_dest):
             return null, null
-        groups, src_colour, dest_colour = self._broadcast_groups(P_dest, transpose_src, transpose_dest)
         P_send, P_recv = null, null
         if in_src:
             root, dests = groups[src_colour[me]]
