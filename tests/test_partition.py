@@ -172,3 +172,69 @@ def test_print_sequential(tmp_path):
     out = run_ranks("test_partition", "body_print_sequential", 3, args=(str(tmp_path),), timeout=120)
     for r, text in enumerate(out):
         assert f"hello from {r}" in text and all(f"hello from {o}" not in text for o in range(3) if o != r)
+
+
+def body_tensor_structures(rank, world):
+    """Structure exchange: broadcast along send / receive teams, global shape of an UNBALANCED
+    decomposition (also delivered to a second partition), the shape table, and the per-axis form."""
+    import torch
+
+    import distdl_b200
+    from distdl_b200.utilities.torch import TensorStructure
+    be = distdl_b200.backends.backend
+    P_world = be.Partition()
+    P = P_world.create_partition_inclusive([0, 1, 2, 3]).create_cartesian_topology_partition([2, 2])
+    P_out = P_world.create_partition_inclusive([4, 5]).create_cartesian_topology_partition([1, 2])
+    # unbalanced: row 0 has 3 rows, row 1 has 1; column 0 has 2 columns, column 1 has 5
+    rows, cols = [3, 1], [2, 5]
+    ts = TensorStructure()
+    if P.active:
+        t = torch.zeros(rows[int(P.index[0])], cols[int(P.index[1])], dtype=torch.float64, requires_grad=True)
+        ts = TensorStructure(t)
+    g = be.assemble_global_tensor_structure(ts, P, P_out)
+    assert tuple(g.shape) == (4, 7) and g.dtype == torch.float64 and g.requires_grad
+    table = be.tensor_decomposition.compute_subtensor_shapes_unbalanced(ts, P, P_out)
+    assert table.shape == (2, 2, 2) and table[1, 0].tolist() == [1, 2] and table[0, 1].tolist() == [3, 5]
+    if P.active:
+        g1 = be.assemble_global_tensor_structure_along_axis(ts, P.create_allreduction_partition((1,)), 1)
+        assert tuple(g1.shape) == (rows[int(P.index[0])], 7)
+    # broadcast of the root's structure down its team
+    P_src = P_world.create_partition_inclusive([4]).create_cartesian_topology_partition([1, 1])
+    P_send, P_recv = P_src.create_broadcast_partition_to(P)
+    mine = TensorStructure(torch.zeros(5, 2, dtype=torch.bfloat16)) if rank == 4 else TensorStructure()
+    if P_send.active or P_recv.active:
+        got = be.broadcast_tensor_structure(mine, P_send, P_recv)
+        assert tuple(got.shape) == (5, 2) and got.dtype == torch.bfloat16 and not got.requires_grad
+    return True
+
+
+def test_tensor_structure_exchange():
+    run_ranks("test_partition", "body_tensor_structures", 6, timeout=180)
+
+
+def test_small_local_utilities():
+    import torch
+
+    from distdl_b200.utilities.index_tricks import cartesian_index_c, cartesian_index_f
+    from distdl_b200.utilities.misc import Bunch, DummyContext, stream_barrier
+    from distdl_b200.utilities.slicing import (assemble_index_filter, filtered_range_index, get_rearrange_ordering,
+                                               range_index)
+    from distdl_b200.utilities.torch import distdl_padding_to_torch_padding
+    assert cartesian_index_c([2, 3], [1, 2]) == 5 and cartesian_index_f([2, 3], [1, 2]) == 5
+    assert cartesian_index_c([2, 3], [1, 0]) == 3 and cartesian_index_f([2, 3], [1, 0]) == 1
+    assert list(range_index([2, 2])) == [(0, 0), (0, 1), (1, 0), (1, 1)]
+    # all indices of a 2 x 3 grid whose first entry is 1
+    filt = assemble_index_filter((1, 0), [0])
+    assert list(filtered_range_index([2, 3], filt)) == [(1, 0), (1, 1), (1, 2)]
+    assert get_rearrange_ordering(3, 1) == ("p a b c", "a (p b) c")
+    # per-dimension (left, right) pads -> torch.nn.functional.pad order (last dimension first)
+    assert tuple(distdl_padding_to_torch_padding(np.array([[0, 0], [1, 2], [3, 4]]))) == (3, 4, 1, 2, 0, 0)
+    b = Bunch(a=1)
+    b.c = 2
+    assert b.a == 1 and b["c"] == 2
+    with pytest.raises(AttributeError):
+        b.missing
+    ctx = DummyContext()
+    ctx.save_for_backward(torch.ones(1))
+    assert len(ctx.saved_tensors) == 1
+    stream_barrier(None)                                   # a no-op without a stream
