@@ -209,3 +209,32 @@ def test_metrics_sink_reports_model_flops(tmp_path):
     r = rows[1]
     assert abs(r["model_tflops_per_gpu"] - r["tokens_per_s"] * 1e9 / 1e12) < 1e-9
     assert abs(r["fraction_of_peak"] - r["model_tflops_per_gpu"]) < 1e-12 and r["grad_norm"] == 0.7
+
+
+def test_buffer_allocators_assign_views_per_message():
+    """Repartition: one buffer per message that leaves or enters (none for "self" / empty overlaps),
+    sends first; halo exchange: four buffers re-viewed per dimension."""
+    from distdl_b200.backends.common.buffer_allocator import (allocate_halo_exchange_buffers,
+                                                              allocate_repartition_buffers)
+    bm = BufferManager()
+    sl = (slice(0, 2), slice(0, 3))
+    x_to_y = [(sl, (2, 3), 1), (sl, (2, 3), "self"), (None, None, None), (sl, (4, 1), 3)]
+    y_to_x = [(sl, (5,), 2), (sl, (2, 3), "self")]
+    send, recv = allocate_repartition_buffers(bm, x_to_y, y_to_x, torch.float32)
+    assert [None if v is None else tuple(v.shape) for v in send] == [(2, 3), None, None, (4, 1)]
+    assert [None if v is None else tuple(v.shape) for v in recv] == [(5,), None]
+    assert len(bm.buffers_map[torch.float32]) == 3                 # two sends + one receive
+    assert send[0].data_ptr() != send[3].data_ptr() != recv[0].data_ptr()
+    # a second layer with smaller messages reuses the same three buffers
+    send2, _ = allocate_repartition_buffers(bm, [(sl, (1, 2), 1)], [], torch.float32)
+    assert len(bm.buffers_map[torch.float32]) == 3 and send2[0].data_ptr() == send[0].data_ptr()
+    # halo exchange on a [6, 8] tensor with width-1 halos in both dimensions
+    def s(a, b):
+        return slice(a, b)
+    slices = [((s(1, 2), s(1, 7)), (s(0, 1), s(1, 7)), (s(4, 5), s(1, 7)), (s(5, 6), s(1, 7))),
+              ((s(0, 6), s(1, 2)), (s(0, 6), s(0, 1)), (s(0, 6), s(6, 7)), (s(0, 6), s(7, 8)))]
+    widths = np.array([[1, 1], [1, 0]])                            # nothing moves to / from the right in dim 1
+    views = allocate_halo_exchange_buffers(bm, slices, widths, widths, torch.float32)
+    assert [tuple(v.shape) for v in views[0]] == [(1, 6)] * 4
+    assert tuple(views[1][0].shape) == (6, 1) and views[1][2] is None and views[1][3] is None
+    assert len(bm.buffers_map[torch.float32]) == 4                 # the manager grew to the halo layer's four
