@@ -238,3 +238,30 @@ def test_buffer_allocators_assign_views_per_message():
     assert [tuple(v.shape) for v in views[0]] == [(1, 6)] * 4
     assert tuple(views[1][0].shape) == (6, 1) and views[1][2] is None and views[1][3] is None
     assert len(bm.buffers_map[torch.float32]) == 4                 # the manager grew to the halo layer's four
+
+
+@pytest.mark.parametrize("nd", [1, 2, 3])
+@pytest.mark.parametrize("mode,ac", [("nearest", False), ("linear", False), ("linear", True)])
+def test_interpolate_function_cpu_adjoint_and_values(nd, mode, ac):
+    """The native interpolation on CPU tensors, fp64: equals torch's interpolation on whole tensors,
+    a sub-slab in global coordinates equals the matching slice of the whole result, and the backward
+    pass is the exact adjoint (dot-product test)."""
+    from distdl_b200.functional.interpolate import InterpolateFunction
+    torch.manual_seed(nd)
+    n_in, n_out = [5, 6, 4][:nd], [11, 9, 10][:nd]
+    x = torch.randn(2, 3, *n_in, dtype=torch.float64, requires_grad=True)
+    zeros = [0] * nd
+    y = InterpolateFunction.apply(x, zeros, n_in, n_in, zeros, n_out, n_out, None, mode, ac)
+    tmode = {1: "linear", 2: "bilinear", 3: "trilinear"}[nd] if mode == "linear" else "nearest"
+    want = torch.nn.functional.interpolate(x.detach(), size=n_out, mode=tmode,
+                                           **({} if mode == "nearest" else {"align_corners": ac}))
+    assert torch.allclose(y, want, atol=1e-12), (y - want).abs().max()
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    lhs, rhs = (y.detach() * dy).sum(), (x.detach() * x.grad).sum()
+    assert abs(lhs - rhs) < 1e-10 * max(1.0, abs(lhs)), (lhs, rhs)
+    # output slab [3, 8) of the first spatial dimension, computed from the whole input
+    lo, hi = 3, 8
+    y_lo, y_hi = [lo] + zeros[1:], [hi] + n_out[1:]
+    part = InterpolateFunction.apply(x.detach(), zeros, n_in, n_in, y_lo, y_hi, n_out, None, mode, ac)
+    assert torch.allclose(part, want[:, :, lo:hi], atol=1e-12)
