@@ -128,7 +128,7 @@ def test_zero_volume_corrector():
     from distdl_b200.functional import ZeroVolumeCorrectorFunction
     empty = zero_volume_tensor(3).requires_grad_()
     s = ZeroVolumeCorrectorFunction.apply(empty)
-    assert s.shape == () and float(s) == 0.0
+    assert s.shape == () and float(s.detach()) == 0.0
     s.backward()
     assert empty.grad is not None and empty.grad.numel() == 0 and empty.grad.shape[0] == 3
     x = torch.randn(2, 2, requires_grad=True)
