@@ -252,6 +252,21 @@ class FlatAdamW:
             self._publish()
 
 
+    def sync_master_from_params(self, reset_moments: bool = True):
+        """After the model's parameters were overwritten in place (``model.load_state_dict`` of a
+        checkpoint written on another worker grid): takes the fp32 master weights from the parameters
+        and, by default, clears the moments and the step count (they belong to the old sharding)."""
+        if self.total:
+            self._quiesce()
+            self.master.copy_(self.param_flat)
+            if reset_moments:
+                self.exp_avg.zero_()
+                self.exp_avg_sq.zero_()
+            self._publish()
+        if reset_moments:
+            self.step_count = 0
+
+
 def cosine_lr(step, base_lr, warmup, total, min_ratio=0.1):
     if step < warmup:
         return base_lr * (step + 1) / max(1, warmup)

@@ -122,6 +122,40 @@ class Trainer:
         return manifest
 
 
+    # ------------------------------------------- checkpoints that move between worker grids
+    def save_model_collected(self, path: str):
+        """Writes the SERIAL model state (one file, written by the first worker) of a model whose layers
+        were built with ``collect_state=True`` (``DecoderConfig.collect_state``), together with the step
+        count.  Collective.  The file loads on any worker grid with :meth:`load_model_collected`."""
+        state = self.model.state_dict()                     # collective: the hooks gather onto worker 0
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        if rank == 0:
+            if not state:
+                raise ValueError("the model has no collected state: build its layers with collect_state=True")
+            torch.save({"model": {k: v.detach().cpu() for k, v in state.items()}, "steps_done": self.steps_done},
+                       path)
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.barrier()
+
+    def load_model_collected(self, path: str, keep_step_count: bool = True):
+        """Loads a file written by :meth:`save_model_collected`, on this job's worker grid whatever grid
+        wrote it: the first worker reads it, the layers' hooks scatter it.  The optimizer restarts from
+        these weights with cleared moments (they were sharded for the old grid)."""
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        meta = [None]
+        if rank == 0:
+            blob = torch.load(path, map_location="cpu", weights_only=False)
+            self.model.load_state_dict(blob["model"])
+            meta[0] = int(blob["steps_done"])
+        else:
+            self.model.load_state_dict({})
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.broadcast_object_list(meta, src=0)
+        self.opt.sync_master_from_params(reset_moments=True)
+        if keep_step_count:
+            self.steps_done = meta[0]                       # the learning-rate schedule continues
+
+
 class SyntheticTokens:
     """Uniform random token blocks in pinned host memory.  Every call of
     :meth:`next` draws fresh tokens into the next of a few pinned buffers

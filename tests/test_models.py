@@ -252,3 +252,40 @@ def test_collected_decoder_checkpoint_moves_between_worker_grids():
         assert abs(loss4 - loss1) < 1e-4 * abs(loss1) and abs(loss2 - loss1) < 1e-4 * abs(loss1), (loss4, loss2, loss1)
         assert abs(losscp - loss1) < 1e-4 * abs(loss1), (losscp, loss1)
         assert set(again) == set(serial) and all(torch.equal(again[k], serial[k]) for k in serial)
+
+
+def body_elastic(rank, world, dp, tp, path, mode):
+    """Train on one worker grid, save the collected model, continue on another grid."""
+    from distdl_b200 import models
+    from distdl_b200.parallel import Trainer
+    cfg = models.llama_tiny(dtype=torch.float32, max_seq=16, vocab_size=100, d_model=48, ffn_dim=96)
+    cfg.n_layers, cfg.n_heads, cfg.n_kv_heads, cfg.collect_state = 2, 4, 2, True
+    torch.manual_seed(rank)
+    layout = models.ParallelLayout(dp, tp)
+    trainer = Trainer(models.Decoder(cfg, layout), global_tokens_per_step=4 * 16, micro_batch=1, lr=5e-3,
+                      warmup_steps=0, max_grad_norm=1.0)
+    gen = torch.Generator().manual_seed(21)
+    tokens = torch.randint(0, 100, (4, 17), generator=gen)
+    per = 4 // dp
+    block = tokens[layout.dp_index * per:(layout.dp_index + 1) * per]      # the same global batch on every grid
+    if mode == "train_and_save":
+        losses = [trainer.step(block).item() for _ in range(4)]
+        trainer.save_model_collected(path)
+        return losses
+    trainer.load_model_collected(path)
+    assert trainer.steps_done == 4 and trainer.opt.step_count == 0
+    return [trainer.step(block).item() for _ in range(3)]
+
+
+def test_training_moves_to_another_worker_grid(tmp_path):
+    path = str(tmp_path / "model.pt")
+    first = run_ranks("test_models", "body_elastic", 4, args=(2, 2, path, "train_and_save"), timeout=300)[0]
+    for world, dp, tp in ((2, 1, 2), (2, 2, 1), (1, 1, 1)):
+        cont = run_ranks("test_models", "body_elastic", world, args=(dp, tp, path, "continue"), timeout=300)[0]
+        # the first loss after the move is that of the saved weights: below where training started and
+        # close to the last loss before the save (one optimizer step apart); every grid agrees on it
+        assert cont[0] < first[0] - 0.2 and abs(cont[0] - first[-1]) < 0.5, (first, cont)
+        if world == 2 and tp == 2:
+            ref = cont
+        assert abs(cont[0] - ref[0]) < 1e-4 * abs(ref[0]), (cont, ref)
+        assert min(cont[1:]) < cont[0] and all(math.isfinite(v) for v in cont), cont   # and training goes on
