@@ -265,3 +265,32 @@ def test_interpolate_function_cpu_adjoint_and_values(nd, mode, ac):
     y_lo, y_hi = [lo] + zeros[1:], [hi] + n_out[1:]
     part = InterpolateFunction.apply(x.detach(), zeros, n_in, n_in, y_lo, y_hi, n_out, None, mode, ac)
     assert torch.allclose(part, want[:, :, lo:hi], atol=1e-12)
+
+
+def test_conv_mixin_input_ranges():
+    from distdl_b200.nn.mixins.conv_mixin import ConvMixin
+    m = ConvMixin()
+    # kernel 3, stride 2, padding 1, dilation 2: output 4 reads inputs 7 .. 11
+    assert m._compute_min_input_range(4, 3, 2, 1, 2) == 7 and m._compute_max_input_range(4, 3, 2, 1, 2) == 11
+    assert m._compute_min_input_range(0, 3, 1, 1, 1) == -1 and m._compute_max_input_range(0, 3, 1, 1, 1) == 1
+
+
+@pytest.mark.parametrize("mode,ac", [("nearest", False), ("linear", False), ("linear", True)])
+@pytest.mark.parametrize("n_in,n_out", [(16, 32), (10, 25), (12, 7)])
+def test_interpolate_mixin_needed_range_covers_what_torch_reads(mode, ac, n_in, n_out):
+    """For every output slab, the input range that the mixin asks for is exactly wide enough: interpolating
+    the slab from that range alone (in global coordinates) reproduces torch's result on the whole tensor."""
+    from distdl_b200.functional.interpolate import InterpolateFunction
+    from distdl_b200.nn.mixins.interpolate_mixin import InterpolateMixin
+    m = InterpolateMixin()
+    torch.manual_seed(0)
+    x = torch.randn(1, 2, n_in, dtype=torch.float64)
+    want = torch.nn.functional.interpolate(x, size=n_out, mode=mode, **({} if mode == "nearest" else
+                                                                        {"align_corners": ac}))
+    for y_lo, y_hi in ((0, n_out // 3), (n_out // 3, 2 * n_out // 3), (2 * n_out // 3, n_out)):
+        lo, hi = m._compute_needed_range([y_lo], [y_hi], [n_in], [n_out], [None], mode, ac)
+        lo, hi = int(lo[0]), int(hi[0])
+        assert 0 <= lo < hi <= n_in
+        part = InterpolateFunction.apply(x[:, :, lo:hi].contiguous(), [lo], [hi], [n_in], [y_lo], [y_hi], [n_out],
+                                         None, mode, ac)
+        assert torch.allclose(part, want[:, :, y_lo:y_hi], atol=1e-12), (mode, ac, y_lo, y_hi, lo, hi)
