@@ -46,6 +46,8 @@ class FlatAdamW:
             if all([n for n, _ in t] == [n for n, _ in table[0]] for t in table):
                 sizes = [max(t[i][1] for t in table) for i in range(len(ordered))]
                 self.uniform_layout = True
+            else:
+                sizes = self._grouped_sizes(ordered, table, sizes)
         if not self.uniform_layout:
             keep = [i for i, (_, p) in enumerate(ordered) if p.numel() > 0]
             n_dec = sum(1 for i in keep if i < len(decay))
@@ -87,6 +89,31 @@ class FlatAdamW:
         self.last_grad_norm = None
         self._setup_full_grads(ordered)
         self._publish()
+
+    def _grouped_sizes(self, ordered, table, sizes):
+        """Parameter lists that differ between processes (pipeline stages): processes with the same
+        list form a group, and the slots take the largest size within the group.  That keeps every
+        parameter at one offset throughout its group, which is enough for the in-place gathers as long
+        as no ZeRO gather team reaches outside its group; every process checks its own teams and the
+        layout is used only if all of them agree (the decision must be the same everywhere, because
+        allocating the peer-mapped buffer is collective)."""
+        rank = dist.get_rank()
+        names = [[n for n, _ in t] for t in table]
+        group = [r for r in range(len(table)) if names[r] == names[rank]]
+        ok = True
+        for _, p in ordered:
+            gather = getattr(p, "zero_gather", None)
+            if gather is None or not gather.P_x.active:
+                continue
+            team = gather.P_x.create_allreduction_partition(gather.axes_all_gather).ranks
+            ok = ok and all(int(r) in group for r in team)
+        verdicts = [None] * len(table)
+        dist.all_gather_object(verdicts, bool(ok))
+        if not all(verdicts):
+            return sizes
+        self.uniform_layout = True
+        self.layout_group = group
+        return [max(table[r][i][1] for r in group) for i in range(len(ordered))]
 
     def _alloc_params(self, numel, dtype, device, multi):
         """The flat bf16 parameter buffer; in peer-mapped memory on the native backend."""

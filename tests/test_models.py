@@ -289,3 +289,40 @@ def test_training_moves_to_another_worker_grid(tmp_path):
             ref = cont
         assert abs(cont[0] - ref[0]) < 1e-4 * abs(ref[0]), (cont, ref)
         assert min(cont[1:]) < cont[0] and all(math.isfinite(v) for v in cont), cont   # and training goes on
+
+
+def body_pipelined_optimizer_layout(rank, world):
+    """Pipeline stages have different parameter lists.  The flat optimizer then lays its slots out per
+    group of processes with the same list (here: per stage), with equal offsets inside a group even
+    when the shards are uneven (3 heads over 2 tensor-parallel workers), and training works."""
+    import torch.distributed as dist
+
+    from distdl_b200 import models
+    from distdl_b200.parallel import FlatAdamW
+    torch.manual_seed(0)
+    cfg = models.llama_tiny(dtype=torch.float32, max_seq=16, vocab_size=96, d_model=48, ffn_dim=96)
+    cfg.n_layers, cfg.n_heads, cfg.n_kv_heads = 2, 3, 3
+    piped = models.PipelinedDecoder(cfg, pp=2, dp=1, tp=2)
+    opt = FlatAdamW(piped.model, lr=1e-2, weight_decay=0.0)
+    assert opt.uniform_layout and opt.layout_group == ([0, 1] if rank < 2 else [2, 3])
+    layouts = [None] * world
+    dist.all_gather_object(layouts, [(n, o) for n, o, _ in opt.names])
+    mate = rank ^ 1
+    mine, theirs = dict(layouts[rank]), dict(layouts[mate])
+    shared = set(mine) & set(theirs)
+    assert shared and all(mine[n] == theirs[n] for n in shared)
+    assert set(dict(layouts[0])) != set(dict(layouts[2]))            # the stages really differ
+    gen = torch.Generator().manual_seed(3)
+    tokens = torch.randint(0, cfg.vocab_size, (4, 17), generator=gen)
+    losses = []
+    for _ in range(5):
+        total = piped.global_loss(piped.forward_backward(tokens, micro_batch=2, scale=1.0 / 64))
+        opt.step()
+        losses.append(float(total))
+    assert losses[-1] < losses[0] - 0.1, losses
+    return losses
+
+
+def test_flat_optimizer_lays_out_pipeline_stages_per_group():
+    out = run_ranks("test_models", "body_pipelined_optimizer_layout", 4, timeout=300)
+    assert out[0] == out[3]
