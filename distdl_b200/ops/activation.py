@@ -109,7 +109,9 @@ def rope_(qkv: torch.Tensor, seq: int, nheads: int, theta: float = 500000.0, off
     token is ``offset`` plus its index modulo ``seq`` (``offset`` > 0 for a worker that holds a
     later block of a sequence split across workers).  In place on CUDA."""
     tokens, ht, hd = qkv.shape
-    table = rope_table(offset + seq, hd, theta, qkv.device)[offset:]      # rows [offset, offset + seq)
+    table = rope_table(offset + seq, hd, theta, qkv.device)
+    if offset:
+        table = table[offset:]                                # rows [offset, offset + seq)
     if use_native(qkv) and qkv.dtype == torch.bfloat16 and hd % 16 == 0 and qkv.is_contiguous():
         return _RopeFn.apply(qkv, table, seq, nheads)
     pos = torch.arange(tokens, device=qkv.device) % seq
