@@ -60,7 +60,7 @@ class DecoderConfig:
     cp_mode: str = "ring"             # context-parallel attention: "ring" (K / V blocks travel) or "a2a"
                                       # (head <-> sequence all-to-all; local head counts must divide by cp)
     collect_state: bool = False       # state_dict() / load_state_dict() in the serial layout on the first worker:
-                                      # a checkpoint that loads on any worker grid (dense models only)
+                                      # a checkpoint that loads on any worker grid
 
     @property
     def head_dim(self):
@@ -268,8 +268,6 @@ class Decoder(torch.nn.Module):
             self.head = dnn.DistributedLinearAllGatherZero(layout.P_flat, cfg.d_model, V, bias=False, dtype=cfg.dtype,
                                                            auto_clear_buffer=not keep_root,
                                                            collect_state=cfg.collect_state)
-        if cfg.collect_state and cfg.n_experts:
-            raise ValueError("collect_state is implemented for dense decoders only")
         self.reset_parameters()
 
     def reset_parameters(self):

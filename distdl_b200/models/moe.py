@@ -95,8 +95,10 @@ class MoEFeedForward(torch.nn.Module):
             raise ValueError("experts must divide evenly over the expert-parallel workers")
         self.e_local = E // self.ep
         self.ep_ranks = tuple(layout.P_grid.ranks)
+        collect = bool(getattr(cfg, "collect_state", False))
         self.router = dnn.DistributedLinearAllGatherZero(layout.P_flat, d, max(E, 8), bias=False, dtype=cfg.dtype,
-                                                         auto_clear_buffer=not cfg.keep_gathered)
+                                                         auto_clear_buffer=not cfg.keep_gathered,
+                                                         collect_state=collect)
         dev = layout.P_flat.device
         self.w_up = torch.nn.Parameter(torch.empty(self.e_local, 2 * F, d, dtype=cfg.dtype, device=dev))
         self.w_down = torch.nn.Parameter(torch.empty(self.e_local, d, F, dtype=cfg.dtype, device=dev))
@@ -105,6 +107,36 @@ class MoEFeedForward(torch.nn.Module):
             self.w_down.normal_(0.0, cfg.init_std / math.sqrt(2 * cfg.n_layers))
         self.aux_loss = None
         self.last_dropped = None
+        self.collect_state = collect
+        if collect:
+            # serial layout: all experts along dimension 0, on the first worker only
+            from ..nn._linear_common import root_partition
+            self.P_ep = layout.P_flat                                  # [ep, 1, 1]: experts over the workers
+            self.P_root = root_partition(self.P_ep)
+            # one pair per tensor: a module re-runs its (collective) set-up when its input structure
+            # changes, and the workers that feed zero-volume tensors would not notice the change
+            self.gather_experts = torch.nn.ModuleDict(
+                {n: dnn.Repartition(self.P_ep, self.P_root, preserve_batch=False) for n in ("w_up", "w_down")})
+            self.scatter_experts = torch.nn.ModuleDict(
+                {n: dnn.Repartition(self.P_root, self.P_ep, preserve_batch=False) for n in ("w_up", "w_down")})
+            self._register_state_dict_hook(self._gather_state_dict)
+            self._register_load_state_dict_pre_hook(self._scatter_state_dict)
+
+    def _gather_state_dict(self, module, destination, prefix, *args):
+        for name in ("w_up", "w_down"):
+            full = self.gather_experts[name](destination.pop(prefix + name).detach())
+            if self.P_root.active:
+                destination[prefix + name] = full
+        return destination
+
+    def _scatter_state_dict(self, destination, prefix, *args):
+        from ..utilities.torch import zero_volume_tensor
+        for name in ("w_up", "w_down"):
+            p = getattr(self, name)
+            full = destination.pop(prefix + name, None)
+            full = full.to(p.device) if self.P_root.active else zero_volume_tensor(device=p.device, dtype=p.dtype)
+            destination[prefix + name] = self.scatter_experts[name](full)
+        return destination
 
     def forward(self, x):
         cfg = self.cfg

@@ -217,10 +217,11 @@ def body_collected_decoder(rank, world, family, dp, tp, cp, serial, tokens):
     import torch.distributed as dist
 
     from distdl_b200 import models
-    cfg = {"llama": models.llama_tiny, "gpt2": models.gpt2_tiny}[family](dtype=torch.float32, max_seq=16,
-                                                                       vocab_size=100, d_model=48, ffn_dim=96)
+    make = {"llama": models.llama_tiny, "gpt2": models.gpt2_tiny, "mixtral": models.mixtral_tiny}[family]
+    cfg = make(dtype=torch.float32, max_seq=16, vocab_size=100, d_model=48, ffn_dim=96)
     cfg.n_layers, cfg.collect_state = 2, True
-    cfg.n_heads, cfg.n_kv_heads = (4, 2) if family == "llama" else (4, 4)
+    cfg.n_heads, cfg.n_kv_heads = (4, 4) if family == "gpt2" else (4, 2)
+    cfg.capacity_factor = 8.0                      # experts: no token is dropped, whatever the grid
     torch.manual_seed(rank)
     model = models.Decoder(cfg, models.ParallelLayout(dp, tp, cp=cp))
     if serial is not None:
@@ -252,6 +253,14 @@ def test_collected_decoder_checkpoint_moves_between_worker_grids():
         assert abs(loss4 - loss1) < 1e-4 * abs(loss1) and abs(loss2 - loss1) < 1e-4 * abs(loss1), (loss4, loss2, loss1)
         assert abs(losscp - loss1) < 1e-4 * abs(loss1), (losscp, loss1)
         assert set(again) == set(serial) and all(torch.equal(again[k], serial[k]) for k in serial)
+    # mixture of experts: the experts move between expert-parallel sizes 4, 2 and 1
+    loss4, serial = run_ranks("test_models", "body_collected_decoder", 4, args=("mixtral", 4, 1, 1, None, tokens),
+                              timeout=300)[0]
+    assert serial["blocks.0.mlp.w_up"].shape[0] == 4
+    for world in (2, 1):
+        loss = run_ranks("test_models", "body_collected_decoder", world,
+                         args=("mixtral", world, 1, 1, serial, tokens), timeout=300)[0][0]
+        assert abs(loss - loss4) < 2e-4 * abs(loss4), (world, loss, loss4)
 
 
 def body_elastic(rank, world, dp, tp, path, mode):
