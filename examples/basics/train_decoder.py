@@ -5,6 +5,7 @@ a fresh trainer.  Works on CPU ranks with gloo and on GPUs with the native backe
     torchrun --nproc-per-node 4 --master-addr 127.0.0.1 examples/basics/train_decoder.py [--gpu] [--cp 2]
 """
 import os
+import shutil
 import sys
 import tempfile
 
@@ -53,3 +54,6 @@ loss = resumed.step(block).item()
 if rank == 0:
     print(f"resumed at step {resumed.steps_done - 1}: loss {loss:.4f} (matches step 5 above)")
 heartbeat.leave()
+dist.barrier()
+if rank == 0:
+    shutil.rmtree(folder[0], ignore_errors=True)
