@@ -98,7 +98,8 @@ class HaloExchangeFunction(TransportBound, torch.autograd.Function):
         if ctx.identity:
             return grad_output, None, None, None, None
         cls = ctx._forward_cls
-        return fold_ghosts(cls.transport(), grad_output, ctx.P_x, ctx.slices, ctx.neighbor_ranks), None, None, None, None
+        g = fold_ghosts(cls.transport(), grad_output, ctx.P_x, ctx.slices, ctx.neighbor_ranks)
+        return g, None, None, None, None
 
 
 class HaloAccumulateFunction(TransportBound, torch.autograd.Function):
@@ -124,4 +125,5 @@ class HaloAccumulateFunction(TransportBound, torch.autograd.Function):
         if ctx.identity:
             return grad_output, None, None, None, None
         cls = ctx._forward_cls
-        return fill_ghosts(cls.transport(), grad_output, ctx.P_x, ctx.slices, ctx.neighbor_ranks), None, None, None, None
+        g = fill_ghosts(cls.transport(), grad_output, ctx.P_x, ctx.slices, ctx.neighbor_ranks)
+        return g, None, None, None, None

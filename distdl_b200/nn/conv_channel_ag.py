@@ -186,5 +186,6 @@ _DOC = "Channel all-gather {}convolution, {}-D (see the base class)."
 for _nd in (1, 2, 3):
     for _transposed in (False, True):
         _name = f"DistributedChannelAllGatherConv{'Transpose' if _transposed else ''}{_nd}d"
-        globals()[_name] = _make(_ChannelAllGatherConv, _nd, _transposed, _name, _DOC.format("transposed " if _transposed else "", _nd))
+        globals()[_name] = _make(_ChannelAllGatherConv, _nd, _transposed, _name,
+                                 _DOC.format("transposed " if _transposed else "", _nd))
 del _nd, _transposed, _name

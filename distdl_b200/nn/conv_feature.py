@@ -229,7 +229,8 @@ class _FeatureConvTransposeBase(Module):
             self.weight = torch.nn.Parameter(ref.weight.detach().clone())
             self.bias = torch.nn.Parameter(ref.bias.detach().clone()) if bias else None
         else:
-            self.register_buffer("weight", zero_volume_tensor(device=device, dtype=ref.weight.dtype, requires_grad=True))
+            self.register_buffer("weight",
+                                 zero_volume_tensor(device=device, dtype=ref.weight.dtype, requires_grad=True))
             self.register_buffer("bias", zero_volume_tensor(device=device, dtype=ref.weight.dtype, requires_grad=True)
                                  if bias else None)
         self.w_broadcast = Broadcast(self.P_wb_cart, P_x, preserve_batch=False)

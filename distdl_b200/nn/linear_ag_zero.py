@@ -8,7 +8,8 @@ import torch
 from .. import ops
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
-from ._linear_common import KeptBufferGuard, PrefetchStream, deliver_grad, direct_main_grad, reduce_scatter_grad, local_out_features, relayout, root_partition, var_blocks
+from ._linear_common import (KeptBufferGuard, PrefetchStream, deliver_grad, direct_main_grad, local_out_features,
+                             reduce_scatter_grad, relayout, root_partition, var_blocks)
 from .all_gather import AllGather
 from .module import Module
 from .reduce_scatter import ReduceScatter

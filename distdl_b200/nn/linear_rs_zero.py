@@ -8,7 +8,8 @@ import torch
 from .. import ops
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
-from ._linear_common import KeptBufferGuard, PrefetchStream, deliver_grad, direct_main_grad, reduce_scatter_grad, derived_partition, root_partition
+from ._linear_common import (KeptBufferGuard, PrefetchStream, deliver_grad, derived_partition, direct_main_grad,
+                             reduce_scatter_grad, root_partition)
 from .all_gather import AllGather
 from .module import Module
 from .reduce_scatter import ReduceScatter

@@ -4,6 +4,7 @@ import torch.nn.functional as F
 
 from ..utilities.slicing import assemble_slices
 from ..utilities.torch import TensorStructure, distdl_padding_to_torch_padding
+from .conv_feature import _per_dim
 from .halo_exchange import HaloExchange
 from .mixins.halo_mixin import HaloMixin
 from .mixins.pooling_mixin import PoolingMixin
@@ -25,7 +26,7 @@ class DistributedPoolBase(Module, HaloMixin, PoolingMixin):
         if not P_x.active:
             return
         nd = self.num_dimensions
-        exp = lambda v: np.atleast_1d(np.asarray(v, dtype=int)) * (np.ones(nd, dtype=int) if np.ndim(v) == 0 else 1)  # noqa: E731
+        exp = lambda v: _per_dim(v, nd)  # noqa: E731
         self.kernel_size, self.stride = exp(kernel_size), exp(stride)
         self.padding, self.dilation = exp(padding), exp(dilation)
         if self.pool_kind == "avg" and np.any(self.dilation != 1):

@@ -91,7 +91,8 @@ class Trainer:
             layout = getattr(self.model, "layout", None)
             cfg = getattr(self.model, "cfg", None)
             manifest = {"world_size": world, "steps_done": self.steps_done,
-                        "layout": None if layout is None else {"dp": layout.dp, "tp": layout.tp, "cp": getattr(layout, "cp", 1)},
+                        "layout": None if layout is None else {"dp": layout.dp, "tp": layout.tp,
+                                                               "cp": getattr(layout, "cp", 1)},
                         "model": None if cfg is None else {k: (str(v) if isinstance(v, torch.dtype) else v)
                                                            for k, v in vars(cfg).items()},
                         "files": [f"rank{r}.pt" for r in range(world)], "extra": extra or {}}
