@@ -141,12 +141,18 @@ class DistributedRingAttention(Module):
     ``P_seq = [B, S, H, 1]`` (equal sequence blocks, block ``i`` on the worker with sequence index
     ``i``; ``H`` > 1 when the heads are additionally split over tensor-parallel workers, each of
     which then runs its own ring).  Exact attention over the whole sequence, causal by global
-    position if ``causal``."""
+    position if ``causal``.
 
-    def __init__(self, P_seq, causal=True, scale=None):
+    ``zigzag=True`` selects the load-balanced layout for causal attention: the sequence is cut into
+    ``2S`` chunks and the worker with sequence index ``r`` holds chunks ``r`` and ``2S - 1 - r``
+    (concatenated, so ``s_local`` is two chunks).  With contiguous blocks the last worker attends to
+    ``S`` blocks and the first to one; with this layout every worker does the same work in every
+    step of the ring."""
+
+    def __init__(self, P_seq, causal=True, scale=None, zigzag=False):
         super().__init__()
         self.P_seq = P_seq
-        self.causal, self.scale = causal, scale
+        self.causal, self.scale, self.zigzag = causal, scale, zigzag
         if not P_seq.active:
             return
         if P_seq.dim != 4 or int(P_seq.shape[3]) != 1:
@@ -165,6 +171,97 @@ class DistributedRingAttention(Module):
         hkv = k.shape[2]
         scale = self.scale if self.scale is not None else 1.0 / math.sqrt(d)
         transport = self._distdl_backend.transport()
+        if self.zigzag and self.causal and len(self.ranks) > 1:
+            if s % 2:
+                raise ValueError("the zigzag layout holds two chunks per worker: the local length must be even")
+            o = _ZigzagRingAttnFn.apply(q.reshape(b * s, hq, d), k.reshape(b * s, hkv, d), v.reshape(b * s, hkv, d),
+                                        b, s, scale, self.ranks, self.me, transport)
+            return o.reshape(b, s, hq, d)
+        # without a causal mask attention does not depend on the order of the keys: the plain ring serves
+        # both layouts
         o = _RingAttnFn.apply(q.reshape(b * s, hq, d), k.reshape(b * s, hkv, d), v.reshape(b * s, hkv, d), b, s,
                               self.causal, scale, self.ranks, self.me, transport)
         return o.reshape(b, s, hq, d)
+
+
+def _halves(t, batch, c):
+    """[batch * 2c, H, D] (tokens batch-major, two chunks of c per sequence) -> the two chunks."""
+    H, D = t.shape[1], t.shape[2]
+    t4 = t.reshape(batch, 2, c, H, D)
+    return t4[:, 0].reshape(batch * c, H, D).contiguous(), t4[:, 1].reshape(batch * c, H, D).contiguous()
+
+
+def _join(lo, hi, batch, c):
+    H, D = lo.shape[1], lo.shape[2]
+    return torch.stack([lo.reshape(batch, c, H, D), hi.reshape(batch, c, H, D)], dim=1).reshape(batch * 2 * c, H, D)
+
+
+def _zigzag_pairs(j, me):
+    """(query half, key half, triangular mask?) combinations that a worker computes while the K / V
+    of worker ``j`` are with it.  Worker ``r`` holds chunks ``r`` (half 0) and ``2S - 1 - r`` (half 1)
+    of the 2S chunks of the sequence, so every visit costs two or three chunk pairs: the causal
+    work is the same on every worker."""
+    if j == me:
+        return [(0, 0, True), (1, 0, False), (1, 1, True)]
+    if j < me:
+        return [(0, 0, False), (1, 0, False)]        # both of my chunks come after j's early chunk only
+    return [(1, 0, False), (1, 1, False)]            # only my late chunk comes after j's chunks
+
+
+class _ZigzagRingAttnFn(torch.autograd.Function):
+    """Causal ring attention on the load-balanced ("zigzag") layout."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, batch, seq, scale, ranks, me, transport):
+        S, c = len(ranks), seq // 2
+        nxt, prv = ranks[(me + 1) % S], ranks[(me - 1) % S]
+        Hq, D = q.shape[1], q.shape[2]
+        qh = _halves(q, batch, c)
+        out = [torch.zeros(batch * c, Hq, D, dtype=torch.float32, device=q.device) for _ in range(2)]
+        lse = [torch.full((batch, Hq, c), float("-inf"), dtype=torch.float32, device=q.device) for _ in range(2)]
+        kb, vb = k.contiguous(), v.contiguous()
+        for t in range(S):
+            j = (me - t) % S
+            kh, vh = _halves(kb, batch, c), _halves(vb, batch, c)
+            for a, b, tri in _zigzag_pairs(j, me):
+                o_t, lse_t = _pair_forward(qh[a], kh[b], vh[b], batch, c, tri, scale)
+                new = torch.logaddexp(lse[a], lse_t)
+                out[a] = out[a] * torch.exp(_lse_rows(lse[a] - new, batch * c, Hq)) + \
+                    o_t.float() * torch.exp(_lse_rows(lse_t - new, batch * c, Hq))
+                lse[a] = new
+            if t + 1 < S:
+                kv = transport.exchange([(nxt, torch.stack([kb, vb]))], [(prv, (2,) + tuple(kb.shape), kb.dtype)],
+                                        team=list(ranks))[0].to(q.device)
+                kb, vb = kv[0], kv[1]
+        res = _join(out[0], out[1], batch, c).to(q.dtype)
+        ctx.save_for_backward(q, k, v, res, lse[0], lse[1])
+        ctx.cfg = (batch, seq, scale, tuple(ranks), me, transport)
+        return res
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse0, lse1 = ctx.saved_tensors
+        batch, seq, scale, ranks, me, transport = ctx.cfg
+        S, c = len(ranks), seq // 2
+        nxt, prv = ranks[(me + 1) % S], ranks[(me - 1) % S]
+        qh, oh, dh, lse = _halves(q, batch, c), _halves(out, batch, c), _halves(dout.contiguous(), batch, c), (lse0, lse1)
+        dq = [torch.zeros_like(qh[0], dtype=torch.float32) for _ in range(2)]
+        kb, vb = k.contiguous(), v.contiguous()
+        dkb = torch.zeros_like(kb, dtype=torch.float32)
+        dvb = torch.zeros_like(vb, dtype=torch.float32)
+        for t in range(S):
+            j = (me - t) % S
+            kh, vh = _halves(kb, batch, c), _halves(vb, batch, c)
+            dkh, dvh = list(_halves(dkb, batch, c)), list(_halves(dvb, batch, c))
+            for a, b, tri in _zigzag_pairs(j, me):
+                dq_t, dk_t, dv_t = _pair_backward(dh[a], qh[a], kh[b], vh[b], oh[a], lse[a], batch, c, tri, scale)
+                dq[a] += dq_t.float()
+                dkh[b] = dkh[b] + dk_t.float()
+                dvh[b] = dvh[b] + dv_t.float()
+            dkb, dvb = _join(dkh[0], dkh[1], batch, c), _join(dvh[0], dvh[1], batch, c)
+            bundle = torch.stack([kb.float(), vb.float(), dkb, dvb])
+            got = transport.exchange([(nxt, bundle)], [(prv, tuple(bundle.shape), bundle.dtype)],
+                                     team=list(ranks))[0].to(q.device)
+            kb, vb, dkb, dvb = got[0].to(k.dtype), got[1].to(v.dtype), got[2], got[3]
+        dq_all = _join(dq[0], dq[1], batch, c)
+        return dq_all.to(q.dtype), dkb.to(k.dtype), dvb.to(v.dtype), None, None, None, None, None, None

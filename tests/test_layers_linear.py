@@ -306,18 +306,22 @@ def test_context_parallel_attention_matches_serial():
     run_ranks("test_layers_linear", "body_context_parallel_attention", 4, args=(False,), timeout=120)
 
 
-def body_ring_attention(rank, world, causal, hq, hkv):
+def body_ring_attention(rank, world, causal, hq, hkv, zigzag=False):
     """K / V blocks travel around the ring; result and all three gradients equal serial attention
     (head counts need not divide by the ring size)."""
     import distdl_b200
     from distdl_b200.nn import DistributedRingAttention
     P = distdl_b200.backends.backend.Partition().create_cartesian_topology_partition([1, world, 1, 1])
-    att = DistributedRingAttention(P, causal=causal)
+    att = DistributedRingAttention(P, causal=causal, zigzag=zigzag)
     b, s, d = 2, 6 * world, 16
     torch.manual_seed(9)
     Q, K, V = torch.randn(b, s, hq, d), torch.randn(b, s, hkv, d), torch.randn(b, s, hkv, d)
     dO = torch.randn(b, s, hq, d)
     sl = slice(rank * (s // world), (rank + 1) * (s // world))
+    if zigzag:                                  # chunks rank and 2 * world - 1 - rank of the 2 * world chunks
+        c = s // (2 * world)
+        hi = 2 * world - 1 - rank
+        sl = list(range(rank * c, (rank + 1) * c)) + list(range(hi * c, (hi + 1) * c))
     q, k, v = (t[:, sl].clone().requires_grad_() for t in (Q, K, V))
     out = att(q, k, v)
     out.backward(dO[:, sl])
@@ -336,6 +340,10 @@ def body_ring_attention(rank, world, causal, hq, hkv):
 def test_ring_attention_matches_serial():
     run_ranks("test_layers_linear", "body_ring_attention", 3, args=(True, 4, 2), timeout=180)
     run_ranks("test_layers_linear", "body_ring_attention", 4, args=(False, 3, 3), timeout=180)
+    # the load-balanced layout: two chunks per worker, same result
+    run_ranks("test_layers_linear", "body_ring_attention", 3, args=(True, 4, 2, True), timeout=180)
+    run_ranks("test_layers_linear", "body_ring_attention", 4, args=(True, 3, 3, True), timeout=180)
+    run_ranks("test_layers_linear", "body_ring_attention", 2, args=(False, 2, 2, True), timeout=180)
 
 
 def body_init(rank, world):
