@@ -57,8 +57,10 @@ class DecoderConfig:
     keep_norms_gathered: bool = True  # and for the norm weights of the blocks (a few KB each)
     prefetch: bool = True             # gather the next block's ZeRO weights while the current block computes
     init_std: float = 0.02
-    cp_mode: str = "ring"             # context-parallel attention: "ring" (K / V blocks travel) or "a2a"
-                                      # (head <-> sequence all-to-all; local head counts must divide by cp)
+    cp_mode: str = "ring"             # context-parallel attention: "ring" (K / V blocks travel), "zigzag" (the
+                                      # ring on the load-balanced layout: worker r holds chunks r and 2 cp - 1 - r
+                                      # of every sequence) or "a2a" (head <-> sequence all-to-all; the local
+                                      # head counts must divide by cp)
     collect_state: bool = False       # state_dict() / load_state_dict() in the serial layout on the first worker:
                                       # a checkpoint that loads on any worker grid
 
@@ -165,8 +167,10 @@ class Attention(torch.nn.Module):
         self.out = _row(cfg, layout, cfg.n_heads * hd, cfg.d_model, num_heads=cfg.n_heads)
         self.ring = None
         if layout.cp > 1:
-            cls = {"ring": dnn.DistributedRingAttention, "a2a": dnn.DistributedSelfAttention}[cfg.cp_mode]
-            self.ring = cls(layout.P_ring, causal=True)
+            if cfg.cp_mode == "a2a":
+                self.ring = dnn.DistributedSelfAttention(layout.P_ring, causal=True)
+            else:
+                self.ring = dnn.DistributedRingAttention(layout.P_ring, causal=True, zigzag=cfg.cp_mode == "zigzag")
 
     def forward(self, x):
         cfg = self.cfg
@@ -179,7 +183,10 @@ class Attention(torch.nn.Module):
             o = ops.attention_packed(t, self.hq, self.hkv, b, s, causal=True)
         else:
             # context parallel: s is this worker's block of the sequence; positions are global
-            if cfg.rope:
+            if cfg.rope and cfg.cp_mode == "zigzag":
+                t = ops.rope_(t, s, self.hq + self.hkv, cfg.rope_theta,
+                              ranges=zigzag_ranges(self.layout.cp, self.layout.cp_index, s * self.layout.cp))
+            elif cfg.rope:
                 t = ops.rope_(t, s, self.hq + self.hkv, cfg.rope_theta, offset=self.layout.cp_index * s)
             t = t.reshape(b, s, self.hq + 2 * self.hkv, cfg.head_dim)
             q, k, v = t.split([self.hq, self.hkv, self.hkv], dim=2)
@@ -226,6 +233,15 @@ class Block(torch.nn.Module):
             fn = getattr(m, "prefetch_weights", None)
             if fn is not None:
                 fn()
+
+
+def zigzag_ranges(cp: int, cp_index: int, seq: int):
+    """The two position ranges ``((start, length), (start, length))`` that context-parallel worker
+    ``cp_index`` holds of a sequence of ``seq`` tokens in the load-balanced layout."""
+    if seq % (2 * cp):
+        raise ValueError(f"sequence length {seq} must divide by twice the context-parallel size {cp}")
+    c = seq // (2 * cp)
+    return (cp_index * c, c), ((2 * cp - 1 - cp_index) * c, c)
 
 
 def stage_layers(n_layers: int, stage: int, n_stages: int):
@@ -298,10 +314,18 @@ class Decoder(torch.nn.Module):
     def _local_tokens(self, tokens):
         """This worker's part of the token ids ``[b_local, seq]`` (the same on all context- and
         tensor-parallel workers of a data-parallel replica): its context-parallel block of the
-        sequence, and of that its sequence-parallel shard.  Returns (ids, global start position)."""
+        sequence, and of that its sequence-parallel shard.  Returns (ids, global start position), or
+        (ids, tensor of global positions) in the zigzag layout, where the ids are not contiguous."""
         lay = self.layout
         s = tokens.shape[1]
         base = 0
+        if lay.cp > 1 and self.cfg.cp_mode == "zigzag":
+            (a0, c), (a1, _) = zigzag_ranges(lay.cp, lay.cp_index, s)
+            pos = torch.cat([torch.arange(a0, a0 + c), torch.arange(a1, a1 + c)])
+            lo = int(compute_start_index(lay.tp, lay.tp_index, [2 * c])[0])
+            n = int(compute_subshape(lay.tp, lay.tp_index, [2 * c])[0])
+            pos = pos[lo:lo + n].to(tokens.device)
+            return tokens.index_select(1, pos), pos
         if lay.cp > 1:
             if s % lay.cp:
                 raise ValueError(f"sequence length {s} must divide by the context-parallel size {lay.cp}")
@@ -317,8 +341,8 @@ class Decoder(torch.nn.Module):
             local, lo = self._local_tokens(tokens)
             x = self.embed(local)
             if not cfg.rope:
-                pos = torch.arange(lo, lo + local.shape[1], device=tokens.device).unsqueeze(0).expand_as(local)
-                x = x + self.pos_embed(pos)
+                pos = lo if torch.is_tensor(lo) else torch.arange(lo, lo + local.shape[1], device=tokens.device)
+                x = x + self.pos_embed(pos.unsqueeze(0).expand_as(local))
         else:
             x = tokens                                 # the hidden state handed over by the stage before
         ckpt = cfg.checkpoint_blocks and self.training

@@ -103,15 +103,31 @@ class _RopeFn(torch.autograd.Function):
         return d, None, None, None
 
 
-def rope_(qkv: torch.Tensor, seq: int, nheads: int, theta: float = 500000.0, offset: int = 0) -> torch.Tensor:
+def rope_table_ranges(ranges, head_dim: int, theta: float, device) -> torch.Tensor:
+    """Table for a local sequence made of several position ranges ``((start, length), ...)``."""
+    key = (tuple(ranges), head_dim, theta, str(device))
+    t = _rope_cache.get(key)
+    if t is None:
+        full = rope_table(max(a + n for a, n in ranges), head_dim, theta, device)
+        t = torch.cat([full[a:a + n] for a, n in ranges]).contiguous()
+        _rope_cache[key] = t
+    return t
+
+
+def rope_(qkv: torch.Tensor, seq: int, nheads: int, theta: float = 500000.0, offset: int = 0,
+          ranges=None) -> torch.Tensor:
     """Applies rotary position embedding (rotate-half convention) to the first
     ``nheads`` heads of ``qkv`` [tokens, heads_total, head_dim]; position of a
     token is ``offset`` plus its index modulo ``seq`` (``offset`` > 0 for a worker that holds a
-    later block of a sequence split across workers).  In place on CUDA."""
+    later block of a sequence split across workers), or, with ``ranges = ((start, length), ...)``
+    adding up to ``seq``, the positions of those ranges one after the other.  In place on CUDA."""
     tokens, ht, hd = qkv.shape
-    table = rope_table(offset + seq, hd, theta, qkv.device)
-    if offset:
-        table = table[offset:]                                # rows [offset, offset + seq)
+    if ranges is not None:
+        table = rope_table_ranges(tuple((int(a), int(n)) for a, n in ranges), hd, theta, qkv.device)
+    else:
+        table = rope_table(offset + seq, hd, theta, qkv.device)
+        if offset:
+            table = table[offset:]                            # rows [offset, offset + seq)
     if use_native(qkv) and qkv.dtype == torch.bfloat16 and hd % 16 == 0 and qkv.is_contiguous():
         return _RopeFn.apply(qkv, table, seq, nheads)
     pos = torch.arange(tokens, device=qkv.device) % seq

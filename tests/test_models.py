@@ -137,6 +137,8 @@ def test_context_parallel_decoder_matches_full_sequence_attention():
     run_ranks("test_models", "body_context_parallel", 4, args=("llama", 2), timeout=300)
     run_ranks("test_models", "body_context_parallel", 4, args=("gpt2", 2), timeout=300)
     run_ranks("test_models", "body_context_parallel", 4, args=("llama", 2, "a2a"), timeout=300)
+    run_ranks("test_models", "body_context_parallel", 4, args=("llama", 2, "zigzag"), timeout=300)
+    run_ranks("test_models", "body_context_parallel", 4, args=("gpt2", 2, "zigzag"), timeout=300)
 
 
 def body_pipelined_decoder(rank, world):
