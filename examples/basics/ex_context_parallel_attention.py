@@ -1,6 +1,7 @@
-"""Attention over a sequence that is split across all workers, two ways: head <-> sequence
-all-to-all (DistributedSelfAttention) and K / V blocks around a ring (DistributedRingAttention).
-Both reproduce serial causal attention.
+"""Attention over a sequence that is split across all workers, three ways: head <-> sequence
+all-to-all (DistributedSelfAttention), K / V blocks around a ring (DistributedRingAttention), and the
+ring on the load-balanced "zigzag" layout (worker r holds chunks r and 2 * world - 1 - r, so the causal
+mask leaves every worker the same amount of work).  All reproduce serial causal attention.
 
     torchrun --nproc-per-node 4 --master-addr 127.0.0.1 examples/basics/ex_context_parallel_attention.py
 """
@@ -24,5 +25,9 @@ sl = slice(rank * 8, (rank + 1) * 8)
 q, k, v = Q[:, sl].contiguous(), K[:, sl].contiguous(), V[:, sl].contiguous()
 a2a = DistributedSelfAttention(P_seq, causal=True)(q, k, v)
 ring = DistributedRingAttention(P_seq, causal=True)(q, k, v)
+hi = 2 * world - 1 - rank
+zz = list(range(rank * 4, rank * 4 + 4)) + list(range(hi * 4, hi * 4 + 4))           # two chunks of 4 tokens
+zig = DistributedRingAttention(P_seq, causal=True, zigzag=True)(Q[:, zz].contiguous(), K[:, zz].contiguous(),
+                                                                V[:, zz].contiguous())
 say(P_world, "block", rank, "max error: all-to-all", float((a2a - ref[:, sl]).abs().max()),
-    "ring", float((ring - ref[:, sl]).abs().max()))
+    "ring", float((ring - ref[:, sl]).abs().max()), "zigzag ring", float((zig - ref[:, zz]).abs().max()))
