@@ -25,6 +25,10 @@ class Trainer:
     def __init__(self, model, global_tokens_per_step: int, micro_batch: int = 1, lr: float = 3e-4,
                  weight_decay: float = 0.1, max_grad_norm: float = 1.0, warmup_steps: int = 10,
                  total_steps: int = 1000, device=None, metrics=None, health_check_every: int = 50, heartbeat=None):
+        # a models.PipelinedDecoder: this process trains its stage, micro-batches run through the 1F1B schedule
+        self.pipeline = model if hasattr(model, "forward_backward") else None
+        if self.pipeline is not None:
+            model = self.pipeline.model
         self.model = model
         self.heartbeat = heartbeat      # a parallel.health.Heartbeat: checked before every step, so that a
                                         # missing rank raises RankFailure here instead of hanging a collective
@@ -54,11 +58,14 @@ class Trainer:
         total = torch.zeros((), dtype=torch.float32, device=tokens.device)
         scale = 1.0 / float(self.global_tokens)
         B = tokens.shape[0]
-        for lo in range(0, B, self.micro_batch):
-            mb = tokens[lo:lo + self.micro_batch]
-            loss = self.model.loss(mb[:, :-1], mb[:, 1:], scale=scale)
-            loss.backward()
-            total += loss.detach().float()
+        if self.pipeline is not None:
+            total += self.pipeline.forward_backward(tokens, self.micro_batch, scale).to(total.device)
+        else:
+            for lo in range(0, B, self.micro_batch):
+                mb = tokens[lo:lo + self.micro_batch]
+                loss = self.model.loss(mb[:, :-1], mb[:, 1:], scale=scale)
+                loss.backward()
+                total += loss.detach().float()
         self.opt.step()
         self.steps_done += 1
         if dist.is_initialized() and dist.get_world_size() > 1:

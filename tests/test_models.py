@@ -208,6 +208,37 @@ def body_pipelined_tp_trains(rank, world):
     return losses
 
 
+def body_pipelined_trainer(rank, world, tmp):
+    """The trainer drives a pipelined decoder like any model: schedule, optimizer per stage, all-reduced
+    loss, sharded checkpoint and resume."""
+    from distdl_b200 import models
+    from distdl_b200.parallel import Trainer
+    cfg = models.llama_tiny(dtype=torch.float32, max_seq=16, vocab_size=96, d_model=32, ffn_dim=64)
+    cfg.n_layers, cfg.n_heads, cfg.n_kv_heads = 2, 4, 2
+
+    def make():
+        torch.manual_seed(0)
+        piped = models.PipelinedDecoder(cfg, pp=2, dp=1, tp=2)
+        return Trainer(piped, global_tokens_per_step=4 * 16, micro_batch=2, lr=1e-2, warmup_steps=0)
+    trainer = make()
+    gen = torch.Generator().manual_seed(3)
+    tokens = torch.randint(0, cfg.vocab_size, (4, 17), generator=gen)
+    losses = [trainer.step(tokens).item() for _ in range(3)]
+    trainer.save_checkpoint(tmp)
+    losses += [trainer.step(tokens).item() for _ in range(2)]
+    again = make()
+    again.load_checkpoint(tmp)
+    resumed = [again.step(tokens).item() for _ in range(2)]
+    assert losses[-1] < losses[0] - 0.1, losses
+    assert all(abs(a - b) < 1e-5 * abs(a) for a, b in zip(losses[3:], resumed)), (losses, resumed)
+    return losses
+
+
+def test_trainer_drives_a_pipelined_decoder(tmp_path):
+    out = run_ranks("test_models", "body_pipelined_trainer", 4, args=(str(tmp_path),), timeout=300)
+    assert out[0] == out[3]
+
+
 def test_pipelined_tensor_parallel_decoder_trains():
     out = run_ranks("test_models", "body_pipelined_tp_trains", 4, timeout=300)
     assert out[0] == out[3]
