@@ -69,3 +69,4 @@ __all__ = [
 # ``__all__`` so that the list above stays the reference's)
 from .attention import DistributedSelfAttention  # noqa: E402,F401
 from .ring_attention import DistributedRingAttention  # noqa: E402,F401
+from .window_attention import DistributedSlidingWindowAttention  # noqa: E402,F401

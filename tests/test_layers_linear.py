@@ -375,3 +375,38 @@ def body_init(rank, world):
 
 def test_initialisers_use_global_fans():
     run_ranks("test_layers_linear", "body_init", 4, timeout=120)
+
+
+def body_window_attention(rank, world, window, hq, hkv):
+    """Sliding-window causal attention with the previous block's last keys fetched by halo exchange:
+    output and all three gradients equal serial banded attention."""
+    import distdl_b200
+    from distdl_b200.nn import DistributedSlidingWindowAttention
+    P = distdl_b200.backends.backend.Partition().create_cartesian_topology_partition([1, world, 1, 1])
+    att = DistributedSlidingWindowAttention(P, window)
+    b, s, d = 2, 6 * world, 8
+    torch.manual_seed(4)
+    Q, K, V = torch.randn(b, s, hq, d), torch.randn(b, s, hkv, d), torch.randn(b, s, hkv, d)
+    dO = torch.randn(b, s, hq, d)
+    sl = slice(rank * 6, (rank + 1) * 6)
+    q, k, v = (t[:, sl].clone().requires_grad_() for t in (Q, K, V))
+    out = att(q, k, v)
+    out.backward(dO[:, sl])
+    Qr, Kr, Vr = (t.clone().requires_grad_() for t in (Q, K, V))
+    i, j = torch.arange(s).unsqueeze(1), torch.arange(s).unsqueeze(0)
+    band = (j <= i) & (j > i - window)
+    rep = hq // hkv
+    ref = torch.nn.functional.scaled_dot_product_attention(
+        Qr.transpose(1, 2), Kr.transpose(1, 2).repeat_interleave(rep, 1), Vr.transpose(1, 2).repeat_interleave(rep, 1),
+        attn_mask=band).transpose(1, 2)
+    ref.backward(dO)
+    assert torch.allclose(out, ref[:, sl], atol=2e-5), (out - ref[:, sl]).abs().max()
+    for got, want, what in ((q.grad, Qr.grad, "dq"), (k.grad, Kr.grad, "dk"), (v.grad, Vr.grad, "dv")):
+        assert torch.allclose(got, want[:, sl], atol=2e-5), (what, (got - want[:, sl]).abs().max())
+    return True
+
+
+def test_sliding_window_attention_by_halo_exchange():
+    run_ranks("test_layers_linear", "body_window_attention", 4, args=(4, 4, 2), timeout=180)
+    run_ranks("test_layers_linear", "body_window_attention", 3, args=(7, 2, 2), timeout=180)
+    run_ranks("test_layers_linear", "body_window_attention", 2, args=(1, 2, 1), timeout=180)
