@@ -244,7 +244,8 @@ class _ZigzagRingAttnFn(torch.autograd.Function):
         batch, seq, scale, ranks, me, transport = ctx.cfg
         S, c = len(ranks), seq // 2
         nxt, prv = ranks[(me + 1) % S], ranks[(me - 1) % S]
-        qh, oh, dh, lse = _halves(q, batch, c), _halves(out, batch, c), _halves(dout.contiguous(), batch, c), (lse0, lse1)
+        qh, oh, lse = _halves(q, batch, c), _halves(out, batch, c), (lse0, lse1)
+        dh = _halves(dout.contiguous(), batch, c)
         dq = [torch.zeros_like(qh[0], dtype=torch.float32) for _ in range(2)]
         kb, vb = k.contiguous(), v.contiguous()
         dkb = torch.zeros_like(kb, dtype=torch.float32)
