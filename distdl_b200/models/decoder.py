@@ -22,6 +22,7 @@ from __future__ import annotations
 import math
 from dataclasses import dataclass
 
+import numpy as np
 import torch
 import torch.utils.checkpoint
 
@@ -372,6 +373,42 @@ class Decoder(torch.nn.Module):
         """Sum of this worker's token losses times ``scale`` (default: 1 / local
         tokens); ``targets`` has the same [b_local, seq] shape as ``tokens``."""
         return self.loss_from_hidden(self.forward(tokens), targets, scale)
+
+    @torch.no_grad()
+    def generate(self, tokens, n_new: int):
+        """Greedy continuation of ``tokens [b_local, seq]`` (the same on all workers of a data-parallel
+        replica) by ``n_new`` tokens; returns ``[b_local, seq + n_new]`` on every worker.  A reference
+        implementation for checking a trained model: every step recomputes the whole prefix (there is no
+        key / value cache), the worker that holds the last position picks the token and the replica's
+        workers agree on it through the control plane.  Contiguous layouts only (not ``cp_mode="zigzag"``)."""
+        if self.n_stages != 1:
+            raise ValueError("generate() runs on an unpipelined decoder")
+        if self.layout.cp > 1 and self.cfg.cp_mode == "zigzag":
+            raise ValueError("generate() needs a contiguous sequence layout")
+        lay = self.layout
+        was_training = self.training
+        self.eval()
+        # the workers that see the same sequences: one row of the [dp, cp * tp] grid
+        base = lay.P_grid.create_partition_inclusive(range(lay.P_grid.size))
+        replica = base.create_cartesian_topology_partition([lay.dp, lay.cp * lay.tp]).create_allreduction_partition((1,))
+        for _ in range(n_new):
+            s = tokens.shape[1]
+            pad = (-s) % lay.cp                          # context parallelism wants equal blocks
+            inp = torch.nn.functional.pad(tokens, (0, pad)) if pad else tokens
+            dnn.reset_setup(self)                        # the length grows: not every worker's shard does
+            h = self.forward(inp)
+            local, lo = self._local_tokens(inp)
+            pick = np.zeros(tokens.shape[0], dtype=np.int64)
+            if lo <= s - 1 < lo + local.shape[1]:        # this worker holds the last real position
+                logits = self.head(h[:, s - 1 - lo:s - lo])
+                pick = logits[:, 0, :cfg_vocab(self.cfg)].float().argmax(-1).cpu().numpy().astype(np.int64)
+            else:
+                self.head(h[:, :1])                      # the head's gathers are collective: take part
+            pick = replica.allreduce_data(pick)          # zeros from everybody but the owner
+            tokens = torch.cat([tokens, torch.as_tensor(pick, device=tokens.device).unsqueeze(1)], dim=1)
+        self.release_gathered()
+        self.train(was_training)
+        return tokens
 
     def loss_from_hidden(self, h, targets, scale=None):
         """The head and the cross-entropy on the output ``h`` of :meth:`forward` (last stage)."""

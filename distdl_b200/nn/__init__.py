@@ -3,7 +3,7 @@ from .all_gather import AllGather  # noqa: F401
 from .all_sum_reduce import AllSumReduce  # noqa: F401
 from .broadcast import Broadcast  # noqa: F401
 from .halo_exchange import HaloExchange  # noqa: F401
-from .module import Module  # noqa: F401
+from .module import Module, reset_setup  # noqa: F401
 from .reduce_scatter import ReduceScatter  # noqa: F401
 from .repartition import Repartition  # noqa: F401
 from .sum_reduce import SumReduce  # noqa: F401

