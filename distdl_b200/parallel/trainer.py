@@ -41,6 +41,7 @@ class Trainer:
         self.device = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available()
                                  else torch.device("cpu"))
         self._dev_tokens = None
+        self._last_shape = None
         self.steps_done = 0
 
     def stage(self, tokens_host: torch.Tensor) -> torch.Tensor:
@@ -53,6 +54,12 @@ class Trainer:
     def step_device(self, tokens: torch.Tensor) -> torch.Tensor:
         if self.heartbeat is not None:
             self.heartbeat.check()
+        if self._last_shape is not None and tuple(tokens.shape) != self._last_shape:
+            # a new block shape is seen by every process, but not every process's shard changes with it:
+            # make all layers set up again together
+            from ..nn import reset_setup
+            reset_setup(self.model)
+        self._last_shape = tuple(tokens.shape)
         self.model.train()
         self.opt.set_lr(cosine_lr(self.steps_done, self.base_lr, self.warmup_steps, self.total_steps))
         total = torch.zeros((), dtype=torch.float32, device=tokens.device)

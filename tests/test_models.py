@@ -397,3 +397,27 @@ def test_greedy_generation_agrees_across_worker_grids():
         per = 2 // dp
         for out, _, d in outs:
             assert torch.equal(out, ref[d * per:(d + 1) * per]), (world, dp, tp, cp, out, ref)
+
+
+def body_varying_length(rank, world):
+    """Sequence lengths that change between steps: 16 tokens give shards 8 + 8 over two sequence-parallel
+    workers, 15 give 8 + 7, so only one worker sees its shard change; the trainer re-runs the layers'
+    collective set-up on both."""
+    from distdl_b200 import models
+    from distdl_b200.parallel import Trainer
+    torch.manual_seed(0)
+    cfg = models.llama_tiny(dtype=torch.float32, max_seq=32, vocab_size=64, d_model=32, ffn_dim=64)
+    cfg.n_layers, cfg.n_heads, cfg.n_kv_heads = 1, 2, 2
+    trainer = Trainer(models.Decoder(cfg, models.ParallelLayout(1, 2)), global_tokens_per_step=2 * 16, micro_batch=1,
+                      warmup_steps=0)
+    gen = torch.Generator().manual_seed(1)
+    out = []
+    for seq in (16, 15, 15, 12, 16):
+        out.append(trainer.step(torch.randint(0, 64, (2, seq + 1), generator=gen)).item())
+    assert all(math.isfinite(v) for v in out)
+    return out
+
+
+def test_trainer_handles_changing_sequence_lengths():
+    out = run_ranks("test_models", "body_varying_length", 2, timeout=240)
+    assert out[0] == out[1]
