@@ -339,6 +339,12 @@ class Decoder(torch.nn.Module):
     def forward(self, tokens):
         cfg = self.cfg
         if self.first_stage:
+            # every worker sees the shape of the token block change, but not every worker's shard changes
+            # with it: the layers' collective set-up has to run again on all of them
+            shape = tuple(tokens.shape)
+            if getattr(self, "_seen_shape", shape) != shape:
+                dnn.reset_setup(self)
+            self._seen_shape = shape
             local, lo = self._local_tokens(tokens)
             x = self.embed(local)
             if not cfg.rope:

@@ -55,8 +55,11 @@ class PipelinedDecoder:
     def _stage(self, micro, seq):
         lay, cfg = self.layout, self.cfg
         s_local = int(compute_subshape(lay.tp, lay.tp_index, [seq // lay.cp])[0])
-        key = (micro, s_local)
+        key = (micro, seq)                               # what every worker sees, not this worker's shard
         if self._pipe_key != key:
+            if self._pipe_key is not None:
+                from ..nn import reset_setup
+                reset_setup(self.model)                  # a new block shape: all layers set up again together
             p = next(self.model.parameters())
             self._pipe = PipelineStage(self.model, self.chain, act_shape=(micro, s_local, cfg.d_model),
                                        act_dtype=cfg.dtype, device=p.device)
