@@ -149,3 +149,22 @@ def body_loss_on_root(rank, world):
 
 def test_loss_value_lives_on_the_first_worker_gradients_everywhere():
     run_ranks("test_behaviour", "body_loss_on_root", 4, timeout=180)
+
+
+def body_reset_setup(rank, world):
+    """A shape change that only one worker can see: 4 + 3 entries, then 4 + 4.  Worker 0's input looks the
+    same both times, so the layer's collective set-up has to be requested explicitly on all workers."""
+    from distdl_b200.nn import AllGather, reset_setup
+    P = _P([0, 1], [2])
+    layer = AllGather(P, axes_all_gather=(0,))
+    y = layer(torch.full((4 if rank == 0 else 3,), float(rank)))
+    assert y.tolist() == [0.0] * 4 + [1.0] * 3
+    reset_setup(layer)
+    assert not layer._distdl_is_setup
+    y = layer(torch.full((4,), float(rank)))
+    assert y.tolist() == [0.0] * 4 + [1.0] * 4 and layer._distdl_is_setup
+    return True
+
+
+def test_reset_setup_for_changes_one_worker_cannot_see():
+    run_ranks("test_behaviour", "body_reset_setup", 2, timeout=120)
