@@ -312,8 +312,9 @@ def check_moe_peer():
 def check_context_parallel_decoder():
     """The decoder with a context-parallel size of 2 against the data-parallel decoder with the
     same shards fed whole sequences on both replicas (its loss and gradients are exactly twice
-    those of the context-parallel model).  bf16, head dim 128, block length 256: the ring runs
-    the tcgen05 attention kernels per block and the rotary kernel with a position offset.
+    those of the context-parallel model), in the three modes ring / zigzag ring / all-to-all.  bf16,
+    head dim 128, blocks of 256 tokens (chunks of 128 in the zigzag layout): the rings run the tcgen05
+    attention kernels per block and the rotary kernel with position offsets or ranges.
     Run by name only (``multi_gpu_worker.py context_decoder`` on an even number of GPUs)."""
     from distdl_b200 import models
     world = dist.get_world_size()
@@ -321,27 +322,29 @@ def check_context_parallel_decoder():
     cfg = models.llama_tiny(d_model=512, n_heads=4, n_kv_heads=2, ffn_dim=1024, max_seq=512, vocab_size=1024)
     cfg.n_layers = 2
     tp = world // 2
-    torch.manual_seed(0)
-    cp_model = models.Decoder(cfg, models.ParallelLayout(1, tp, cp=2))
-    torch.manual_seed(0)
-    dp_model = models.Decoder(cfg, models.ParallelLayout(2, tp))
     gen = torch.Generator().manual_seed(5)
     tokens = torch.randint(0, cfg.vocab_size, (2, 513), generator=gen).to(dev)
-    out = {}
-    for name, model in (("cp", cp_model), ("dp", dp_model)):
-        model.train()
-        loss = model.loss(tokens[:, :-1], tokens[:, 1:], scale=1.0 / 1024)
-        loss.backward()
-        model.release_gathered()
-        total = loss.detach().float().clone()
-        dist.all_reduce(total)
-        out[name] = (total, [None if p.grad is None else p.grad.float().clone() for p in model.parameters()])
-    assert abs(float(out["cp"][0]) * 2 - float(out["dp"][0])) < 2e-2 * abs(float(out["dp"][0])), \
-        (float(out["cp"][0]), float(out["dp"][0]))
-    for ga, gb in zip(out["cp"][1], out["dp"][1]):
-        if ga is not None and ga.numel():
-            err = (ga * 2 - gb).abs().max() / gb.abs().max().clamp_min(1e-6)
-            assert err < 5e-2, float(err)
+    for mode in ("ring", "zigzag", "a2a"):
+        cfg.cp_mode = mode
+        torch.manual_seed(0)
+        cp_model = models.Decoder(cfg, models.ParallelLayout(1, tp, cp=2))
+        torch.manual_seed(0)
+        dp_model = models.Decoder(cfg, models.ParallelLayout(2, tp))
+        out = {}
+        for name, model in (("cp", cp_model), ("dp", dp_model)):
+            model.train()
+            loss = model.loss(tokens[:, :-1], tokens[:, 1:], scale=1.0 / 1024)
+            loss.backward()
+            model.release_gathered()
+            total = loss.detach().float().clone()
+            dist.all_reduce(total)
+            out[name] = (total, [None if p.grad is None else p.grad.float().clone() for p in model.parameters()])
+        assert abs(float(out["cp"][0]) * 2 - float(out["dp"][0])) < 2e-2 * abs(float(out["dp"][0])), \
+            (mode, float(out["cp"][0]), float(out["dp"][0]))
+        for ga, gb in zip(out["cp"][1], out["dp"][1]):
+            if ga is not None and ga.numel():
+                err = (ga * 2 - gb).abs().max() / gb.abs().max().clamp_min(1e-6)
+                assert err < 5e-2, (mode, float(err))
 
 
 def main():
