@@ -38,7 +38,7 @@ def _worker(rank, world_size, port, jobs, results, env):
         import torch.distributed as dist
         torch.set_num_threads(1)
         dist.init_process_group("gloo", rank=rank, world_size=world_size,
-                                timeout=datetime.timedelta(seconds=60))
+                                timeout=datetime.timedelta(seconds=float(os.environ.get("DIST_HARNESS_TIMEOUT_S", 60))))
         import distdl_b200
         distdl_b200.config.set_backend("mpi", "numpy")
         results.put((rank, "ready", None))

@@ -41,9 +41,10 @@ def body_rank_never_joins(rank, world):
 
 
 def test_rank_that_never_joins_times_out():
-    # the gloo process group of the harness has a 60 s limit; the pool is rebuilt afterwards
+    # a pool of its own whose gloo process group has a 10 s limit; it is torn down afterwards
     try:
-        out = run_ranks("test_failure_detection", "body_rank_never_joins", 2, timeout=150)
+        out = run_ranks("test_failure_detection", "body_rank_never_joins", 2, timeout=150,
+                        env={"DIST_HARNESS_TIMEOUT_S": "10"})
     except AssertionError as e:
         # the harness's own closing barrier can be what notices the broken world first
         assert any(k in str(e) for k in ("Timed out", "timeout", "detected", "Connection closed")), str(e)[-400:]
