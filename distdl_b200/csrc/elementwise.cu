@@ -697,19 +697,35 @@ DD_API int dd_norm_bwd_noalloc(int rms, const void* dy, const void* x, const voi
     fprintf(stderr, "dd_norm_bwd_noalloc: d=%d exceeds the built-in scratch (at most %d columns)\n", d, kNoAllocMaxD);
     return DD_ERR_TOO_LARGE;
   }
+  // Argument checks before anything is launched, as in the other entry points:
+  // a null or misaligned pointer would otherwise fault inside the kernel.
+  if (dy == nullptr || x == nullptr || stats == nullptr || dx == nullptr) {
+    fprintf(stderr, "dd_norm_bwd_noalloc: dy, x, stats and dx must not be null\n");
+    return DD_ERR_BAD_ARG;
+  }
+  if (((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dx) |
+        reinterpret_cast<uintptr_t>(w)) & 15) != 0 ||
+      (reinterpret_cast<uintptr_t>(stats) & 7) != 0 ||
+      ((reinterpret_cast<uintptr_t>(dw) | reinterpret_cast<uintptr_t>(db)) & 3) != 0) {
+    fprintf(stderr, "dd_norm_bwd_noalloc: dy, x, w and dx need 16-byte alignment, stats 8, dw and db 4\n");
+    return DD_ERR_ALIGN;
+  }
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= 64) return DD_ERR_BAD_ARG;
   // One-time set-up per device, with that device current: in host code the
   // array's name is only a handle, the device address has to be looked up.
+  // The cache is written without a lock: two threads that race here both look
+  // up and store the same address, which is harmless.
   if (g_norm_bwd_scratch_addr[dev] == nullptr) {
     float* p = nullptr;
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_norm_bwd_scratch);
     if (e != cudaSuccess) return (int)e;
     g_norm_bwd_scratch_addr[dev] = p;
   }
-  float* partial = g_norm_bwd_scratch_addr[dev];
+  // Without dw and db the partial sums are not wanted: the kernel then skips them.
+  float* partial = (dw != nullptr || db != nullptr) ? g_norm_bwd_scratch_addr[dev] : nullptr;
   const int grid = rows < kNoAllocParts ? rows : kNoAllocParts;
   // Every CTA overwrites its whole [2][d] slice of the scratch, so nothing left
   // by an earlier call is ever read: no clearing is needed.
