@@ -72,9 +72,20 @@ class NativeTransport(GroupTransport):
         return self._collectives().reduce_scatter_accumulate_(stacked, acc, ranks, scale)
 
     def exchange(self, sends, recvs, team=None):
-        dev_ok = all(t.is_cuda for _, t in sends) and torch.cuda.is_available()
-        if team is not None and dev_ok and 1 < len(team) <= 8 and self._collectives().available(team):
-            got = self._collectives().exchange(team, sends, recvs)
-            if got is not None:
-                return got
-        return super().exchange(sends, recvs, team)
+        """All messages of a team in one kernel.  Every member launches that kernel on every
+        exchange, whatever its own messages are, because the kernel opens with a barrier over
+        the team.  A message that does not fit a staging slot, or shares its ordered pair with
+        another message, goes through the library's point-to-point path beside the kernel;
+        that is decided per message from what both of its ends know
+        (:func:`distdl_b200.parallel.collectives.exchange_split`)."""
+        coll = self._collectives()
+        if team is None or not torch.cuda.is_available() or not 1 < len(team) <= 8 or not coll.available(team):
+            return super().exchange(sends, recvs, team)
+        ok_s, ok_r = coll.exchange_split(len(team), coll.symm.heap().staging_bytes, sends, recvs)
+        got = coll.exchange(team, [m for m, ok in zip(sends, ok_s) if ok], [m for m, ok in zip(recvs, ok_r) if ok])
+        if all(ok_s) and all(ok_r):
+            return got
+        rest = super().exchange([m for m, ok in zip(sends, ok_s) if not ok],
+                                [m for m, ok in zip(recvs, ok_r) if not ok], team)
+        got, rest = iter(got), iter(rest)
+        return [next(got) if ok else next(rest) for ok in ok_r]

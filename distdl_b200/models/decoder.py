@@ -375,10 +375,16 @@ class Decoder(torch.nn.Module):
         self._backward_phase = True
         return self.final_norm(x) if self.last_stage else x
 
-    def loss(self, tokens, targets, scale=None):
+    def loss(self, tokens, targets, scale=None, unit_grad=False):
         """Sum of this worker's token losses times ``scale`` (default: 1 / local
-        tokens); ``targets`` has the same [b_local, seq] shape as ``tokens``."""
-        return self.loss_from_hidden(self.forward(tokens), targets, scale)
+        tokens); ``targets`` has the same [b_local, seq] shape as ``tokens``.
+
+        ``unit_grad=True`` is a promise that the returned loss is back-propagated as it is
+        (``loss.backward()`` with gradient 1; fold any weighting into ``scale``): the fused
+        cross-entropy has already written ``scale * d loss / d logits`` over the logits, and the
+        backward pass then hands that buffer on without a multiplication.  With the default the
+        incoming gradient is applied, so ``(loss * k).backward()`` is correct as well."""
+        return self.loss_from_hidden(self.forward(tokens), targets, scale, unit_grad)
 
     @torch.no_grad()
     def generate(self, tokens, n_new: int):
@@ -416,13 +422,15 @@ class Decoder(torch.nn.Module):
         self.train(was_training)
         return tokens
 
-    def loss_from_hidden(self, h, targets, scale=None):
-        """The head and the cross-entropy on the output ``h`` of :meth:`forward` (last stage)."""
+    def loss_from_hidden(self, h, targets, scale=None, unit_grad=False):
+        """The head and the cross-entropy on the output ``h`` of :meth:`forward` (last stage);
+        ``unit_grad`` as in :meth:`loss`."""
         tl, _ = self._local_tokens(targets)
         logits = self.head(h)
         rows = logits.shape[0] * logits.shape[1]
         logits2 = logits.reshape(rows, logits.shape[-1])
-        return ops.cross_entropy_(logits2, tl.reshape(-1), vocab=cfg_vocab(self.cfg), scale=scale, unit_grad=True)
+        return ops.cross_entropy_(logits2, tl.reshape(-1), vocab=cfg_vocab(self.cfg), scale=scale,
+                                  unit_grad=unit_grad)
 
 
 def cfg_vocab(cfg):

@@ -81,7 +81,7 @@ class PipelinedDecoder:
         total = run_1f1b(stage,
                          [c[:, :-1] for c in chunks] if self.first else None,
                          [c[:, 1:] for c in chunks] if self.last else None,
-                         (lambda h, t: self.model.loss_from_hidden(h, t, scale)) if self.last else None,
+                         (lambda h, t: self.model.loss_from_hidden(h, t, scale, unit_grad=True)) if self.last else None,
                          n_micro=n)
         if total is None:
             p = next(self.model.parameters())

@@ -61,6 +61,15 @@ class DistributedLinearAllGatherZero(Module):
             shape[-1], shape[-2] = 1, M
             P_weight = P_y.create_partition_inclusive(range(P_y.size)).create_cartesian_topology_partition(shape)
         self.P_weight = P_weight
+        if P_store_bias is not None:
+            # the partition [1, ..., M, 1] through which the bias travels between its shards and the
+            # serial state dict (``src/distdl/nn/linear_ag_zero.py:202-207``): member j must be a worker
+            # of tensor-parallel column j, since it contributes that column's bias slice
+            assert P_store_bias.dim == P_y.dim and int(P_store_bias.shape[-1]) == 1
+            assert int(P_store_bias.shape[-2]) == M
+            assert int(np.prod(P_store_bias.shape[:dim - 2])) == 1
+            if P_store_bias.active and int(P_store_bias.index[-2]) != int(P_weight.index[-2]):
+                raise ValueError("P_store_bias: member j must belong to tensor-parallel column j of P_weight")
         self.P_store_bias = P_store_bias
         D = int(P_weight.shape[0])
         self.allgather_weight = AllGather(P_weight, axes_all_gather=(0,), scale_backward=scale_backward)
@@ -155,7 +164,7 @@ class DistributedLinearAllGatherZero(Module):
             shape = [1] * dim
             shape[-2] = int(self.P_weight.shape[-2])
             from ._linear_common import derived_partition
-            P_col = derived_partition(self.P_weight, idx, shape)
+            P_col = self.P_store_bias if self.P_store_bias is not None else derived_partition(self.P_weight, idx, shape)
             object.__setattr__(self, "_P_bias_col", P_col)
             object.__setattr__(self, "_bias_gather", Repartition(P_col, self.P_root, preserve_batch=False))
             object.__setattr__(self, "_bias_scatter", Repartition(self.P_root, P_col, preserve_batch=False))

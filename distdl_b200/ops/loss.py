@@ -14,9 +14,14 @@ class _XentFn(torch.autograd.Function):
     def forward(ctx, logits, targets, vocab, scale, unit_grad):
         # logits [rows, ld] bf16, contiguous; destroyed (replaced by d loss / d logits * scale)
         rows, ld = logits.shape
+        if targets.dtype != torch.int64:
+            raise TypeError(f"cross_entropy_: targets must be int64 (the kernel reads 8-byte ids), got {targets.dtype}")
         loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
         _native.call("dd_xent", logits.data_ptr(), targets.data_ptr(), loss.data_ptr(), rows, vocab, ld,
                      float(scale), stream_ptr())
+        # the kernel wrote through a raw pointer: tell autograd that the storage changed, so that any
+        # other function that saved these logits for its backward fails loudly instead of reading gradients
+        torch.autograd.graph.increment_version(logits)
         ctx.save_for_backward(logits)
         ctx.unit_grad = unit_grad
         return loss.sum() * scale

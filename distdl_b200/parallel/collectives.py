@@ -40,8 +40,7 @@ def team(ranks):
 
 
 def _launch(name, h, ranks, *args):
-    if h.poisoned:
-        raise RuntimeError("symmetric heap is poisoned by an earlier time-out; restart the job")
+    symm.require_healthy()
     steps = ctypes.c_int(0)
     targs = h.team_args(ranks)
     _native.launch_count += 1
@@ -205,6 +204,7 @@ def reduce_scatter_accumulate_(x: torch.Tensor, acc: torch.Tensor, ranks, scale:
     n = x[0].numel()
     if n % 8 or acc.numel() != n or P * n * 2 > h.staging_bytes // 16 * 16:
         return False
+    symm.require_healthy()
     stage = h.staging_tensor(P * n * 2, torch.bfloat16)
     stage.copy_(x.reshape(-1))
     steps = ctypes.c_int(0)
@@ -242,32 +242,52 @@ def all_to_all(x: torch.Tensor, ranks) -> torch.Tensor:
     return out.view(x.dtype).view(x.shape)
 
 
+def _nbytes(shape, dtype) -> int:
+    n = 1
+    for s_ in shape:
+        n *= int(s_)
+    return n * torch.empty((), dtype=dtype).element_size()
+
+
+def exchange_split(team_size: int, staging_bytes: int, sends, recvs):
+    """Which messages of this member travel inside the one-kernel exchange.
+
+    The kernel is launched by EVERY member of the team on every exchange (it opens with a
+    barrier over the team), so nothing about that launch depends on the messages.  What is
+    decided here, per message, is whether it rides in the kernel or goes through the
+    library's point-to-point path beside it.  A message rides in the kernel when it fits a
+    staging slot and is the only message of its ordered pair; both ends of a pair know the
+    message's size and how many messages the pair has, so the two ends always decide alike
+    and no agreement round is needed.  ``sends`` = [(rank, tensor)], ``recvs`` =
+    [(rank, shape, dtype)].  Returns ``(send_native, recv_native)``: one bool per entry."""
+    slot = (staging_bytes // team_size) // 256 * 256
+    n_to, n_from = {}, {}
+    for dst, _ in sends:
+        n_to[dst] = n_to.get(dst, 0) + 1
+    for src, _, _ in recvs:
+        n_from[src] = n_from.get(src, 0) + 1
+    send_native = [n_to[dst] == 1 and t.numel() * t.element_size() <= slot for dst, t in sends]
+    recv_native = [n_from[src] == 1 and _nbytes(shape, dtype) <= slot for src, shape, dtype in recvs]
+    return send_native, recv_native
+
+
 def exchange(team, sends, recvs):
     """Point-to-point messages inside ``team`` in one kernel.  ``sends`` =
     [(world_rank, tensor)], ``recvs`` = [(world_rank, shape, dtype)]; at most one
-    message per ordered pair.  Returns the received tensors in the order of
-    ``recvs``, or ``None`` when a message does not fit its staging slot (the
-    caller then uses the library path)."""
+    message per ordered pair, each within its staging slot (the messages that
+    :func:`exchange_split` marks; both lists may be empty, the member then only takes part
+    in the kernel's barriers).  Returns the received tensors in the order of ``recvs``."""
     h = symm.heap()
     team = list(team)
     P = len(team)
     slot = (h.staging_bytes // P) // 256 * 256
-    sizes = {}
-    for dst, t in sends:
-        nb = t.numel() * t.element_size()
-        if nb > slot or dst in sizes:
-            return None
-        sizes[dst] = nb
+    ok_s, ok_r = exchange_split(P, h.staging_bytes, sends, recvs)
+    if not (all(ok_s) and all(ok_r)):
+        raise ValueError("exchange: a message does not fit its staging slot, or two messages share a pair")
+    symm.require_healthy()
     outs, dsts, nbytes = [], [0] * P, [0] * P
-    seen = set()
     for src, shape, dtype in recvs:
-        n = 1
-        for s_ in shape:
-            n *= int(s_)
-        nb = n * torch.empty((), dtype=dtype).element_size()
-        if nb > slot or src in seen:
-            return None
-        seen.add(src)
+        nb = _nbytes(shape, dtype)
         padded = (nb + 15) // 16 * 16
         raw = torch.empty(padded, dtype=torch.uint8, device=h.device)
         outs.append(raw[:nb].view(dtype).view(tuple(int(s_) for s_ in shape)))

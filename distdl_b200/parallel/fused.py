@@ -117,6 +117,7 @@ def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, bias, ranks):
     ``x_local`` [batch, s_local, K] bf16 (this member's sequence shard), ``w``
     an [N, K] view (row- or column-contiguous).  Returns ``(y [batch, P*s_local, N],
     G [batch, P*s_local, K])`` where ``G`` is the gathered activation."""
+    symm.require_healthy()
     st = state()
     h = st.h
     ranks = list(ranks)
@@ -171,6 +172,7 @@ def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, bias, ranks):
 def gemm_rs(x: torch.Tensor, w: torch.Tensor, bias, ranks, batch: int, s_local: int):
     """``reduce_scatter_seq(x @ w.T (+ bias))``: ``x`` [batch * P * s_local, K] bf16
     (rows ordered [batch, seq]), returns this member's [batch, s_local, N]."""
+    symm.require_healthy()
     st = state()
     h = st.h
     ranks = list(ranks)

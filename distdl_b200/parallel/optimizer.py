@@ -40,12 +40,17 @@ class FlatAdamW:
         # native transport then gathers ZeRO shards by reading the peers' buffers in place).
         sizes = [p.numel() for _, p in ordered]
         self.uniform_layout = False
-        if multi and ordered:
+        if multi:
+            # every process takes part, also one that holds no trainable parameter (an inactive worker)
             table = [None] * dist.get_world_size()
             dist.all_gather_object(table, [(n, p.numel()) for n, p in ordered])
             if all([n for n, _ in t] == [n for n, _ in table[0]] for t in table):
                 sizes = [max(t[i][1] for t in table) for i in range(len(ordered))]
                 self.uniform_layout = True
+                if not ordered:
+                    self.total = 0          # no process has a parameter: all of them leave here together
+                    self._symmetric, self._full, self._full_any = False, [], False
+                    return
             else:
                 sizes = self._grouped_sizes(ordered, table, sizes)
         if not self.uniform_layout:
@@ -54,11 +59,18 @@ class FlatAdamW:
             ordered = [ordered[i] for i in keep]
             sizes = [sizes[i] for i in keep]
             decay = ordered[:n_dec]
-        if not ordered or sum(sizes) == 0:
+        if not multi and (not ordered or sum(sizes) == 0):
             self.total = 0
+            self._symmetric, self._full, self._full_any = False, [], False
             return
-        ref = next(p for _, p in ordered if p.numel() > 0) if any(p.numel() for _, p in ordered) else ordered[0][1]
-        device, dtype = ref.device, ref.dtype
+        have = [p for _, p in ordered if p.numel() > 0]
+        ref = have[0] if have else (ordered[0][1] if ordered else None)
+        if ref is not None:
+            device, dtype = ref.device, ref.dtype
+        else:                                  # a process without parameters still joins the collective steps below
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() \
+                else torch.device("cpu")
+            dtype = None
         offsets, off = [], 0
         for sz in sizes:
             offsets.append(off)
@@ -116,18 +128,27 @@ class FlatAdamW:
         return [max(table[r][i][1] for r in group) for i in range(len(ordered))]
 
     def _alloc_params(self, numel, dtype, device, multi):
-        """The flat bf16 parameter buffer; in peer-mapped memory on the native backend."""
+        """The flat bf16 parameter buffer; in peer-mapped memory on the native backend.  Allocating
+        peer-mapped memory is collective, so the processes first agree on it: each reports whether
+        its own parameters qualify (a process without parameters always does) and the peer-mapped
+        buffer is used only if all do."""
         self._symmetric = False
-        if (multi and self.uniform_layout and device.type == "cuda" and dtype == torch.bfloat16
-                and dist.get_world_size() <= 8 and os.environ.get("DISTDL_SYMM_PARAMS", "1") != "0"):
-            from . import symm
-            if symm.heap_ready():
+        if multi:
+            local_ok = bool(self.uniform_layout and device.type == "cuda" and dtype in (torch.bfloat16, None)
+                            and dist.get_world_size() <= 8 and os.environ.get("DISTDL_SYMM_PARAMS", "1") != "0")
+            if local_ok:
+                from . import symm
+                local_ok = symm.heap_ready()
+            votes = [None] * dist.get_world_size()
+            dist.all_gather_object(votes, local_ok)
+            if all(votes):
+                from . import symm
                 region = symm.SymmetricRegion(symm.heap(), numel * 2)
                 symm.register_param_region(region)
                 self._region = region
                 self._symmetric = True
-                return region.tensor(numel, dtype)
-        return torch.zeros(numel, dtype=dtype, device=device)
+                return region.tensor(numel, torch.bfloat16)
+        return torch.zeros(numel, dtype=dtype or torch.float32, device=device)
 
     def _setup_full_grads(self, ordered):
         """Unsharded fp32 gradient accumulators for the ZeRO weight matrices (peer-mapped):
@@ -135,6 +156,7 @@ class FlatAdamW:
         reduce-scatters them once, each worker reading its slice of every peer's
         accumulator in place, instead of one reduce-scatter per layer and micro-batch."""
         self._full = []
+        self._full_any = False              # some process has such accumulators: all join the step's barriers
         self._full_region = None
         if not self._symmetric or os.environ.get("DISTDL_FULL_GRADS", "1") == "0":
             return
@@ -157,9 +179,11 @@ class FlatAdamW:
         dist.all_gather_object(needs, [(n, len(t)) for _, _, n, t, _ in plan])
         if not any(needs):
             return
-        if any(x != needs[0] for x in needs):
+        filled = [x for x in needs if x]
+        if any(x != filled[0] for x in filled):
             return                      # differing layouts: keep the per-micro-batch reduce-scatter
         from . import symm
+        self._full_any = True
         region = symm.SymmetricRegion(symm.heap(), max(off, 4) * 4)
         self._full_region = region
         self._full_flat = region.tensor(off, torch.float32)
@@ -169,7 +193,7 @@ class FlatAdamW:
             self._full.append((p, o, n, team, me))
 
     def _reduce_full_grads(self):
-        if not self._full:
+        if not self._full_any:
             return
         import ctypes
         from . import collectives
@@ -185,7 +209,8 @@ class FlatAdamW:
             _native.check(lib.dd_rs_pull_f32(len(team), srcs, p.main_grad_view.data_ptr(), n, 1.0, stream),
                           "dd_rs_pull_f32")
         collectives.barrier(everyone)                  # nobody reads my accumulators any more
-        self._full_flat.zero_()
+        if self._full:
+            self._full_flat.zero_()
 
     def reduce_gradients(self):
         """Brings every gradient of this step into the sharded fp32 accumulator: flushes the
@@ -193,8 +218,7 @@ class FlatAdamW:
         accumulators.  ``step()`` calls it; collective over all processes."""
         if self._release is not None:
             self._release()
-        if self.total:
-            self._reduce_full_grads()
+        self._reduce_full_grads()
 
     def _publish(self):
         """After the parameters changed: no process may read a peer's shard in place
@@ -230,8 +254,14 @@ class FlatAdamW:
         (``release_gathered``) is asked to flush their gradients first."""
         self.reduce_gradients()
         if self.total == 0:
-            if self.max_grad_norm and dist.is_initialized() and dist.get_world_size() > 1:
+            # nothing to update here, but the other processes' collective steps still need this one
+            multi = dist.is_initialized() and dist.get_world_size() > 1
+            if self.max_grad_norm and multi:
                 dist.all_reduce(torch.zeros(1, device="cuda" if torch.cuda.is_available() else "cpu"))
+            elif multi:
+                self._quiesce()
+            if multi:
+                self._publish()
             return
         self.step_count += 1
         clip_ptr = None

@@ -220,6 +220,17 @@ class DeviceTimeout(RuntimeError):
     """A kernel gave up a bounded wait for another GPU."""
 
 
+def require_healthy():
+    """Called by every host wrapper that launches a kernel using the flag counters (the staged
+    collectives, the exchange, the barriers, the fused GEMM + collective kernels, the MoE
+    routing kernels): refuses the launch once a bounded wait has run out.  After a time-out the
+    counters of this process are out of step with its peers, so every further such kernel would
+    only spin for the full wait limit."""
+    if _heap is not None and _heap.poisoned:
+        raise DeviceTimeout("the symmetric heap is poisoned by an earlier device time-out; restart the job "
+                            "from its last checkpoint")
+
+
 def check_health():
     """Reads the device status record (synchronises the device).  If a kernel gave up a
     bounded wait since the last check, the symmetric heap is marked poisoned (its flag

@@ -70,7 +70,8 @@ class Trainer:
         else:
             for lo in range(0, B, self.micro_batch):
                 mb = tokens[lo:lo + self.micro_batch]
-                loss = self.model.loss(mb[:, :-1], mb[:, 1:], scale=scale)
+                # the loss is back-propagated as it is (gradient 1), which the fused cross-entropy may rely on
+                loss = self.model.loss(mb[:, :-1], mb[:, 1:], scale=scale, unit_grad=True)
                 loss.backward()
                 total += loss.detach().float()
         self.opt.step()

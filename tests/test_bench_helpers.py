@@ -51,3 +51,28 @@ def test_model_flops_report():
     assert 700 < r["tflops_per_gpu"] < 850
     if "fraction_of_measured_sustained_bf16" in r:
         assert 0.3 < r["fraction_of_measured_sustained_bf16"] < 1.0
+
+
+def test_exchange_split_is_decided_alike_at_both_ends_of_a_pair():
+    """Three members, one oversize message (0 -> 1) and one pair with two messages (2 -> 0):
+    each member marks exactly those for the library path, whichever end it is, and keeps
+    every other message in the kernel, so no member ever waits for a kernel message that
+    its partner sent another way."""
+    import torch
+    from distdl_b200.parallel.collectives import exchange_split
+    staging = 3 * 1024                      # slot = 1024 bytes per member
+    big, small = torch.zeros(2000, dtype=torch.uint8), torch.zeros(100, dtype=torch.uint8)
+    msgs = {(0, 1): [big], (1, 0): [small], (1, 2): [small], (2, 1): [small], (2, 0): [small, small], (0, 2): [small]}
+    marks = {}
+    for me in range(3):
+        sends = [(dst, t) for (src, dst), ts in msgs.items() if src == me for t in ts]
+        recvs = [(src, tuple(t.shape), t.dtype) for (src, dst), ts in msgs.items() if dst == me for t in ts]
+        ok_s, ok_r = exchange_split(3, staging, sends, recvs)
+        for (dst, _), ok in zip(sends, ok_s):
+            marks.setdefault((me, dst), []).append(("s", ok))
+        for (src, _, _), ok in zip(recvs, ok_r):
+            marks.setdefault((src, me), []).append(("r", ok))
+    for pair, seen in marks.items():
+        native = {ok for _, ok in seen}
+        assert len(native) == 1, (pair, seen)                       # both ends agree
+        assert native.pop() == (pair not in ((0, 1), (2, 0))), pair

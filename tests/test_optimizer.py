@@ -51,9 +51,44 @@ def body_clip(rank, world):
     return True
 
 
+def body_rank_without_parameters(rank, world):
+    """An inactive worker (no trainable parameter at all) must still pass through every collective
+    step of the optimizer's constructor and of step(), or the other workers block."""
+    from distdl_b200.parallel import FlatAdamW
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            torch.manual_seed(5)
+            if rank != world - 1:                       # the last worker holds nothing
+                self.w = torch.nn.Parameter(torch.randn(6) + rank)
+
+    for clip in (None, 1.0):
+        m, ref = M(), M()
+        opt = FlatAdamW(m, lr=1e-2, weight_decay=0.0, max_grad_norm=clip, no_decay=())
+        assert (opt.total == 0) == (rank == world - 1)
+        tref = torch.optim.AdamW(ref.parameters(), lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0) \
+            if rank != world - 1 else None
+        for _ in range(2):
+            if rank != world - 1:
+                (m.w ** 2).sum().mul(1e-3).backward()
+                (ref.w ** 2).sum().mul(1e-3).backward()
+            opt.step()
+            if tref is not None:
+                tref.step()
+                tref.zero_grad()
+                assert torch.allclose(m.w, ref.w, atol=1e-5)        # (the small gradient is never clipped)
+        opt.zero_grad()
+    return True
+
+
 def test_flat_adamw_matches_torch_and_layout_is_uniform():
     run_ranks("test_optimizer", "body_flat_adamw", 2, timeout=120)
 
 
 def test_global_gradient_norm():
     run_ranks("test_optimizer", "body_clip", 2, timeout=120)
+
+
+def test_worker_without_parameters_joins_every_collective_step():
+    run_ranks("test_optimizer", "body_rank_without_parameters", 3, timeout=120)
