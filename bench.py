@@ -114,6 +114,17 @@ def model_flops_report(cfg, seq, tokens_per_s, gpus):
     return out
 
 
+def activation_report(model):
+    plan = model.activation_plan or {}
+    keep, n = plan.get("keep", 0), plan.get("blocks", 0)
+    per = plan.get("bytes_per_kept_block", 0)
+    return (f"policy {plan.get('policy')}: {keep} of {n} blocks keep the outputs of their GEMMs and of attention "
+            f"(with its log-sum-exp) for the backward pass, {per / 1e9:.2f} GB per block and micro-batch, "
+            f"{keep * per / 1e9:.1f} GB per GPU; in those blocks only norm outputs and the activation function's "
+            f"output are recomputed and the ZeRO weight shards are gathered again; the other {n - keep} blocks "
+            f"recompute their forward pass")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -134,6 +145,10 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="diagnosis only: after the timed runs, trace ONE step with torch.profiler on rank 0 and "
                          "print the kernels by total device time (numbers under a profiler are never bench values)")
+    ap.add_argument("--activation-policy", default="auto",
+                    help="auto: as many blocks as the free device memory holds keep their activations for the "
+                         "backward pass, the others recompute; full: every block recomputes; none: every block keeps; "
+                         "an integer: that many blocks keep")
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (invalid as a result)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -175,6 +190,7 @@ def main():
     if args.layers:
         cfg.n_layers = args.layers
     cfg.keep_gathered = bool(args.keep_gathered)
+    cfg.activation_policy = args.activation_policy
     dp, tp = layout_for(args.gpus)
     if args.tp:
         tp, dp = args.tp, args.gpus // args.tp
@@ -195,7 +211,9 @@ def main():
     elif cfg.num_parameters() < 3e9:
         micro = min(local_batch, 16)
     else:
-        micro = {2: 2}.get(args.gpus, 4)      # 1 GPU: 15.8k / 16.5k / 14.6k tokens/s at 2 / 4 / 8 sequences
+        # 1 GPU holds 144 GB of parameters, gradients and optimizer state: with 2 sequences per pass all 32
+        # blocks keep their activations for the backward pass, with 4 only some do
+        micro = {1: 2, 2: 2}.get(args.gpus, 4)
     torch.manual_seed(1234 + rank)
     layout = models.ParallelLayout(dp, tp, cp=cp)
     model = models.Decoder(cfg, layout)
@@ -275,10 +293,13 @@ def main():
                        "zero": ("not used (parameters live on their tensor-parallel owners)" if not cfg.zero else
                                 "gathered once per step (--keep-gathered)" if args.keep_gathered else
                                 "ZeRO-3 parameters and optimizer state: block weight matrices re-gathered at every "
-                                "use; their gradients accumulate unsharded in fp32 and are reduce-scattered once per "
-                                "step; norm weights, embedding and head gathered once per step"),
+                                "use (forward and backward); their gradients " +
+                                ("accumulate unsharded in fp32 and are reduce-scattered once per step"
+                                 if os.environ.get("DISTDL_FULL_GRADS", "1") != "0" else
+                                 "are reduce-scattered after every layer and micro-batch (DISTDL_FULL_GRADS=0)") +
+                                "; norm weights, embedding and head gathered once per step"),
                        "optimizer": "AdamW fp32 master + moments, grad clip 1.0",
-                       "activation_checkpointing": "per block",
+                       "activation_checkpointing": activation_report(model),
                        "l2": "inputs larger than L2: every step streams the model's weights, gradients and optimizer state "
                              f"({cfg.num_parameters() * 16 / max(1, args.gpus) / 1e9:.0f} GB per GPU) through the 126 MB L2; no explicit flush"},
             "clocks": clocks.summary(),

@@ -28,6 +28,7 @@ import torch.utils.checkpoint
 
 from .. import nn as dnn
 from .. import ops
+from ..utilities import recompute
 from ..utilities.slicing import compute_start_index, compute_subshape
 
 
@@ -50,7 +51,14 @@ class DecoderConfig:
     top_k: int = 2
     capacity_factor: float = 1.25
     dtype: torch.dtype = torch.bfloat16
-    checkpoint_blocks: bool = True
+    checkpoint_blocks: bool = True    # False: never recompute a block (the same as activation_policy="none")
+    activation_policy: str = "auto"   # which blocks keep their activations for the backward pass:
+                                      # "auto"  as many (counted from the last block) as the free device memory
+                                      #         holds, the others recompute their forward pass in backward;
+                                      # "full"  every block recomputes; "none" every block keeps;
+                                      # an integer (or a string of digits): that many blocks keep.
+                                      # A block that keeps stores the outputs of its GEMMs and of attention;
+                                      # norm outputs and the activation function's output are rebuilt
     zero: bool = True
     keep_gathered: bool = False  # gather ZeRO shards once per optimizer step, reduce-scatter gradients once
     keep_root_gathered: bool = True   # the same for the embedding, final norm and head only (each is used
@@ -173,9 +181,13 @@ class Attention(torch.nn.Module):
             else:
                 self.ring = dnn.DistributedRingAttention(layout.P_ring, causal=True, zigzag=cfg.cp_mode == "zigzag")
 
-    def forward(self, x):
+    def forward(self, x, remake=None):
+        """``remake``: a function that rebuilds ``x`` (the norm's output), so that the projection
+        need not store it for its backward pass."""
         cfg = self.cfg
-        qkv = self.qkv(x)                                     # [b, s, (hq + 2 hkv) * hd]
+        with recompute.saved_as_recipe(x, remake):
+            qkv = self.qkv(x)                                 # [b, s, (hq + 2 hkv) * hd]
+        del x
         b, s = qkv.shape[0], qkv.shape[1]
         t = qkv.reshape(b * s, self.hq + 2 * self.hkv, cfg.head_dim)
         if self.ring is None:
@@ -205,10 +217,15 @@ class MLP(torch.nn.Module):
             self.up = _col(cfg, layout, cfg.d_model, cfg.ffn_dim)
         self.down = _row(cfg, layout, cfg.ffn_dim, cfg.d_model)
 
-    def forward(self, x):
-        h = self.up(x)
-        h = ops.swiglu(h) if self.cfg.activation == "swiglu" else ops.gelu(h)
-        return self.down(h)
+    def forward(self, x, remake=None):
+        act = ops.swiglu if self.cfg.activation == "swiglu" else ops.gelu
+        with recompute.saved_as_recipe(x, remake):
+            h = self.up(x)
+        del x
+        a = act(h)
+        # the second GEMM saves its input: rebuilt from h, which the activation's backward keeps anyway
+        with recompute.saved_as_recipe(a, lambda: act(h)):
+            return self.down(a)
 
 
 class Block(torch.nn.Module):
@@ -224,8 +241,35 @@ class Block(torch.nn.Module):
             self.mlp = MLP(cfg, layout)
 
     def forward(self, x):
-        x = x + self.attn(self.norm1(x))
+        if not recompute.active():
+            x = x + self.attn(self.norm1(x))
+            return x + self.mlp(self.norm2(x))
+        # this block keeps its activations: the norm outputs are rebuilt in the backward pass
+        x = x + self.attn(self.norm1(x), remake=lambda x=x: self.norm1(x))
+        if isinstance(self.mlp, MLP):
+            return x + self.mlp(self.norm2(x), remake=lambda x=x: self.norm2(x))
         return x + self.mlp(self.norm2(x))
+
+    def kept_bytes(self, cfg, layout, b, s):
+        """(bytes this block stores from forward to backward for a micro-batch of ``b`` sequences of
+        ``s`` tokens when it keeps its activations, bytes it needs for a moment while its backward or
+        its recomputation runs)."""
+        e = torch.empty((), dtype=cfg.dtype).element_size()
+        tp = layout.tp
+        d, hd = cfg.d_model, cfg.head_dim
+        tok, tok_loc = b * s, b * s // tp
+        hq, hkv = -(-cfg.n_heads // tp), -(-cfg.n_kv_heads // tp)
+        x = tok_loc * d * e
+        gathered = tok * d * e if tp > 1 else 0              # the fused all-gather GEMM keeps the gathered input
+        qkv = tok * (hq + 2 * hkv) * hd * e
+        o = tok * hq * hd * e + tok * hq * 4
+        ffn = cfg.ffn_dim * (2 if cfg.activation == "swiglu" else 1)
+        h = tok * (-(-ffn // tp)) * e
+        if cfg.n_experts:
+            h = int(h * cfg.top_k * cfg.capacity_factor * 1.5) + 4 * tok * d * e
+        kept = 2 * x + 2 * gathered + qkv + o + h
+        moment = 2 * h + 2 * qkv + 6 * tok * d * e
+        return kept, moment
 
     def prefetch(self):
         """Starts gathering the ZeRO weight shards of this block's linear layers (a no-op for
@@ -303,6 +347,69 @@ class Decoder(torch.nn.Module):
                     s = std / math.sqrt(2 * cfg.n_layers) if (".out." in name or ".down." in name) else std
                     p.normal_(0.0, s)
 
+    def _backward_prefetch(self, i):
+        block = self.blocks[i]
+
+        def hook(_grad):
+            # (with gradient tracking on: where weight gradients travel through autograd, a recomputed
+            # block must see the gather as part of its graph)
+            with torch.enable_grad():
+                block.prefetch()
+        return hook
+
+    def _blocks_that_keep(self, tokens):
+        """How many blocks (counted from the last) keep their activations for the backward pass; the
+        others recompute their forward pass.  Decided once per input shape from
+        ``cfg.activation_policy``; with "auto", from the device memory that is free at this moment (the
+        optimizer's state is allocated by then) and agreed over all workers (the smallest answer
+        wins), because a recomputed block repeats its collective kernels and its tensor-parallel
+        peers must do the same."""
+        cfg = self.cfg
+        n = len(self.blocks)
+        key = tuple(tokens.shape)
+        plan = getattr(self, "_keep_plan", None)
+        if plan is not None and plan["shape"] == key:
+            return plan["keep"]
+        policy = str(cfg.activation_policy) if cfg.checkpoint_blocks else "none"
+        b = int(tokens.shape[0])
+        s = int(tokens.shape[1]) // (self.layout.cp if self.first_stage else 1)
+        if not self.first_stage:
+            s *= self.layout.tp                       # a later stage is handed the sequence-parallel shard
+        kept, moment = self.blocks[0].kept_bytes(cfg, self.layout, b, s) if n else (0, 0)
+        plan = {"shape": key, "policy": policy, "bytes_per_kept_block": kept, "blocks": n}
+        if policy == "full":
+            keep = 0
+        elif policy == "none" or n == 0:
+            keep = n
+        elif policy.isdigit():
+            keep = min(n, int(policy))
+        elif not tokens.is_cuda:
+            keep = n
+        else:
+            free, _total = torch.cuda.mem_get_info()
+            free += torch.cuda.memory_reserved() - torch.cuda.memory_allocated()
+            rows = b * s // self.layout.tp
+            head = int(2.5 * rows * self.padded_vocab * 2) if self.last_stage else 0
+            slack = 4 << 30
+            budget = free - head - moment - kept - slack
+            keep = max(0, min(n, int(budget // max(kept, 1))))
+            plan["free_bytes"] = int(free)
+            import torch.distributed as dist
+            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+                t = torch.tensor([keep], dtype=torch.int64, device=tokens.device)
+                dist.all_reduce(t, op=dist.ReduceOp.MIN)
+                keep = int(t.item())
+        plan["keep"] = keep
+        self._keep_plan = plan
+        return keep
+
+    @property
+    def activation_plan(self):
+        """The last decision of the activation planner: ``{"keep": blocks that keep their
+        activations, "blocks": all blocks, "bytes_per_kept_block": ..., "policy": ...}`` (None before
+        the first training forward pass)."""
+        return getattr(self, "_keep_plan", None)
+
     def release_gathered(self):
         """With ``keep_gathered``: reduce-scatters the gradients accumulated on the
         gathered parameters into the shards and drops the gathered copies.  Call
@@ -352,27 +459,26 @@ class Decoder(torch.nn.Module):
                 x = x + self.pos_embed(pos.unsqueeze(0).expand_as(local))
         else:
             x = tokens                                 # the hidden state handed over by the stage before
-        ckpt = cfg.checkpoint_blocks and self.training
-        pre = cfg.prefetch and cfg.zero and not cfg.keep_gathered
         n = len(self.blocks)
-        self._backward_phase = False
+        n_keep = self._blocks_that_keep(tokens) if (self.training and torch.is_grad_enabled()) else n
+        pre = cfg.prefetch and cfg.zero and not cfg.keep_gathered
 
         def run(x, i):
-            # inside the recomputation of the backward pass the blocks come in reverse order
-            if pre and self._backward_phase and i > 0:
-                self.blocks[i - 1].prefetch()
             return self.blocks[i](x)
 
         for i in range(n):
             if pre and i + 1 < n:
                 self.blocks[i + 1].prefetch()
-            if ckpt:
+            if i < n - n_keep:
                 x = torch.utils.checkpoint.checkpoint(run, x, i, use_reentrant=False)
             else:
-                x = self.blocks[i](x)
-        if pre and ckpt and n and torch.is_grad_enabled():
-            self.blocks[n - 1].prefetch()          # the first block that the backward pass recomputes
-        self._backward_phase = True
+                with recompute.enabled():
+                    x = self.blocks[i](x)
+            if pre and i > 0 and x.requires_grad:
+                # the backward pass reaches block i: start gathering the weights of block i - 1
+                x.register_hook(self._backward_prefetch(i - 1))
+        if pre and n and self.training and torch.is_grad_enabled():
+            self.blocks[n - 1].prefetch()          # the first block of the backward pass
         return self.final_norm(x) if self.last_stage else x
 
     def loss(self, tokens, targets, scale=None, unit_grad=False):

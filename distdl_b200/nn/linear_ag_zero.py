@@ -6,6 +6,7 @@ import numpy as np
 import torch
 
 from .. import ops
+from ..utilities import recompute
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
 from ._linear_common import (KeptBufferGuard, PrefetchStream, deliver_grad, direct_main_grad, local_out_features,
@@ -263,15 +264,31 @@ class DistributedLinearAllGatherZero(Module):
         if mg is not None:
             wt.main_grad = mg.t()
         y = None
-        if input.is_cuda and getattr(self._distdl_backend, "name", "") == "native_cupy":
-            from ..parallel import fused
-            y = fused.maybe_ag_linear(self, input, wt, b)
-        if y is None:
-            x = self.all_gather(input)
-            y = ops.linear(x, wt, b)
+        # where recipes are on, the backward pass gathers the weight shards again instead of
+        # holding the gathered weight since the forward pass
+        with recompute.saved_as_recipe(w, self._regather if self._resharded_between_passes() else None):
+            if input.is_cuda and getattr(self._distdl_backend, "name", "") == "native_cupy":
+                from ..parallel import fused
+                y = fused.maybe_ag_linear(self, input, wt, b)
+            if y is None:
+                x = self.all_gather(input)
+                y = ops.linear(x, wt, b)
         if self.auto_clear_buffer:
             self.clear_weight_buffer()
         return y
+
+    def _resharded_between_passes(self):
+        return self.auto_clear_buffer and int(self.P_weight.shape[0]) > 1
+
+    def _regather(self):
+        """The gathered weight ``[in, out/M]`` once more, for the backward pass (taken from a
+        prefetch if one is pending)."""
+        self.collect_weights()
+        self.wait_for_streams()
+        w = self.weight_buffer
+        if self.auto_clear_buffer:
+            self.weight_buffer = self.bias_buffer = None
+        return w
 
 
 class _CheckpointedAGZero(torch.autograd.Function):

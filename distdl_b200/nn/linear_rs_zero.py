@@ -6,6 +6,7 @@ import numpy as np
 import torch
 
 from .. import ops
+from ..utilities import recompute
 from ..utilities.slicing import compute_subshape
 from ..utilities.torch import zero_volume_tensor
 from ._linear_common import (KeptBufferGuard, PrefetchStream, deliver_grad, derived_partition, direct_main_grad,
@@ -207,14 +208,29 @@ class DistributedLinearReduceScatterZero(Module):
         self.collect_weights()
         self.wait_for_streams()
         w = self.weight_buffer
+        base = w
         mg = direct_main_grad(self.weight, self.allgather_weight, w.shape)
         if mg is not None:
             w = w.view(w.shape)              # a fresh tensor object to carry the attribute
             w.main_grad = mg
-        y = self._apply(input, w, self.bias_buffer)
+        # where recipes are on, the backward pass gathers the weight shards again instead of
+        # holding the gathered weight since the forward pass
+        resharded = self.auto_clear_buffer and int(self.allgather_weight.P_x.shape[self.allgather_weight.axes_all_gather[0]]) > 1
+        with recompute.saved_as_recipe(base, self._regather if resharded else None):
+            y = self._apply(input, w, self.bias_buffer)
         if self.auto_clear_buffer:
             self.clear_weight_buffer()
         return y
+
+    def _regather(self):
+        """The gathered weight ``[out, in/M]`` once more, for the backward pass (taken from a
+        prefetch if one is pending)."""
+        self.collect_weights()
+        self.wait_for_streams()
+        w = self.weight_buffer
+        if self.auto_clear_buffer:
+            self.weight_buffer = self.bias_buffer = None
+        return w
 
 
 class _CheckpointedRSZero(torch.autograd.Function):

@@ -98,10 +98,12 @@ def _reference(q, k, v, batch, seq, causal, scale):
     qh = q.reshape(batch, seq, Hq, D).transpose(1, 2)
     kh = k.reshape(batch, seq, Hkv, D).transpose(1, 2)
     vh = v.reshape(batch, seq, Hkv, D).transpose(1, 2)
-    if Hkv != Hq:
+    # grouped-query heads are handled by the library kernel itself on CUDA (no expanded copy of K / V)
+    if Hkv != Hq and not q.is_cuda:
         kh = kh.repeat_interleave(Hq // Hkv, dim=1)
         vh = vh.repeat_interleave(Hq // Hkv, dim=1)
-    o = torch.nn.functional.scaled_dot_product_attention(qh, kh, vh, is_causal=causal, scale=scale)
+    o = torch.nn.functional.scaled_dot_product_attention(qh, kh, vh, is_causal=causal, scale=scale,
+                                                         enable_gqa=Hkv != Hq and q.is_cuda)
     return o.transpose(1, 2).reshape(tokens, Hq, D)
 
 

@@ -78,9 +78,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor = None, *, bias: to
     return out
 
 
-def weight_grad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor):
+def grad_target(w: torch.Tensor):
+    """What a weight-gradient GEMM needs to know about the weight ``w`` ([out, in], possibly a
+    transposed view), as a small tuple that a backward pass can keep without keeping ``w``
+    itself alive: ``(main_grad, transposed_storage)``."""
+    return getattr(w, "main_grad", None), (not w.is_contiguous() and w.t().is_contiguous())
+
+
+def weight_grad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor = None, target=None):
     """Gradient of ``y = x @ w.T`` with respect to ``w`` ([out, in]) from
-    ``dy2 [tokens, out]`` and ``x2 [tokens, in]``.
+    ``dy2 [tokens, out]`` and ``x2 [tokens, in]``; give either ``w`` or ``target =
+    grad_target(w)``.
 
     * ``w.main_grad`` (an fp32 tensor in the layout of ``w``, possibly a
       transposed view): the GEMM epilogue accumulates into it and ``None`` is
@@ -89,14 +97,14 @@ def weight_grad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor):
       is produced in that storage order (``x^T dy``) and returned as the matching
       view, so autograd's transpose back is free instead of a strided copy.
     """
-    mg = getattr(w, "main_grad", None)
+    mg, transposed = target if target is not None else grad_target(w)
     if mg is not None:
         if mg.is_contiguous():
             gemm(dy2.t(), x2.t(), out=mg, accumulate=True)
         else:
             gemm(x2.t(), dy2.t(), out=mg.t(), accumulate=True)
         return None
-    if not w.is_contiguous() and w.t().is_contiguous():
+    if transposed:
         return gemm(x2.t(), dy2.t()).t()
     return gemm(dy2.t(), x2.t())
 
@@ -118,8 +126,9 @@ class _LinearFn(torch.autograd.Function):
         gemm(x2, w, out=y.view(-1, w.shape[0]), bias=b)
         ctx.save_for_backward(x2, w)
         ctx.has_bias = b is not None
-        ctx.wref = w
-        ctx.bref = b
+        # (not the weight itself: a gathered ZeRO weight must not be held from forward to backward)
+        ctx.wgrad = grad_target(w)
+        ctx.b_main_grad = getattr(b, "main_grad", None) if b is not None else None
         ctx.xshape = x.shape
         return y
 
@@ -133,9 +142,9 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w.t()).view(ctx.xshape)
         if ctx.needs_input_grad[1]:
-            dw = weight_grad(dy2, x2, ctx.wref)
+            dw = weight_grad(dy2, x2, target=ctx.wgrad)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            mg = getattr(ctx.bref, "main_grad", None)
+            mg = ctx.b_main_grad
             s = dy2.sum(0, dtype=torch.float32)
             if mg is not None:
                 mg.add_(s)

@@ -20,7 +20,7 @@ import torch
 
 from .. import _native
 from ..ops._util import ptr, stream_ptr
-from ..ops.gemm import _major, weight_grad
+from ..ops.gemm import _major, grad_target, weight_grad
 from . import symm
 
 c_void_p, c_int, c_ll, c_uint = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_uint
@@ -214,7 +214,7 @@ class AgLinearFn(torch.autograd.Function):
     def forward(ctx, x, w, bias, ranks):
         y, G = ag_gemm(x, w, bias, ranks)
         ctx.save_for_backward(G, w)
-        ctx.wref = w
+        ctx.wgrad = grad_target(w)
         ctx.ranks, ctx.has_bias = ranks, bias is not None
         ctx.shape = x.shape
         return y
@@ -229,7 +229,7 @@ class AgLinearFn(torch.autograd.Function):
             dy2 = dy2.contiguous()
         dx = dw = db = None
         if ctx.needs_input_grad[1]:
-            dw = weight_grad(dy2, G.reshape(-1, K), ctx.wref)
+            dw = weight_grad(dy2, G.reshape(-1, K), target=ctx.wgrad)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.sum(0, dtype=torch.float32).to(dy.dtype)
         if ctx.needs_input_grad[0]:
@@ -247,7 +247,7 @@ class LinearRsFn(torch.autograd.Function):
             x2 = x2.contiguous()
         out = gemm_rs(x2, w, bias, ranks, b, s // P)
         ctx.save_for_backward(x2, w)
-        ctx.wref = w
+        ctx.wgrad = grad_target(w)
         ctx.ranks, ctx.has_bias = ranks, bias is not None
         ctx.shape = x.shape
         return out
@@ -262,7 +262,7 @@ class LinearRsFn(torch.autograd.Function):
         dx, Gdy = ag_gemm(dyc, w.t(), None, ctx.ranks)
         dw = db = None
         if ctx.needs_input_grad[1]:
-            dw = weight_grad(Gdy.reshape(-1, N), x2, ctx.wref)
+            dw = weight_grad(Gdy.reshape(-1, N), x2, target=ctx.wgrad)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = Gdy.reshape(-1, N).sum(0, dtype=torch.float32).to(dy.dtype)
         return dx.reshape(b, s, K), dw, db, None

@@ -421,3 +421,65 @@ def body_varying_length(rank, world):
 def test_trainer_handles_changing_sequence_lengths():
     out = run_ranks("test_models", "body_varying_length", 2, timeout=240)
     assert out[0] == out[1]
+
+
+def body_activation_policies(rank, world, family, tp):
+    """The same model trained for three steps with every block recomputing, every block keeping its
+    activations and a mix: losses and parameters agree, and in the keeping blocks the norm and
+    activation outputs and the gathered ZeRO weights really are rebuilt in the backward pass."""
+    from distdl_b200 import models
+    from distdl_b200.parallel import FlatAdamW
+    from distdl_b200.utilities import recompute
+    results = {}
+    rebuilds = {}
+    for policy in ("full", "none", "2"):
+        cfg = {"llama": models.llama_tiny, "gpt2": models.gpt2_tiny}[family](dtype=torch.float32, max_seq=16,
+                                                                           vocab_size=96, d_model=32, ffn_dim=64)
+        cfg.n_layers, cfg.n_heads, cfg.activation_policy = 3, 4, policy
+        if family == "llama":
+            cfg.n_kv_heads = 2
+        torch.manual_seed(0)
+        model = models.Decoder(cfg, models.ParallelLayout(world // tp, tp))
+        opt = FlatAdamW(model, lr=1e-2, max_grad_norm=1.0)
+        gen = torch.Generator().manual_seed(11 + rank // tp)
+        losses = []
+        count = {"n": 0}
+        orig = recompute.Recipe.get
+
+        def counting(self, _orig=orig, _count=count):
+            before = self.rebuilds
+            out = _orig(self)
+            _count["n"] += self.rebuilds - before
+            return out
+        recompute.Recipe.get = counting
+        try:
+            for _ in range(3):
+                tokens = torch.randint(0, cfg.vocab_size, (2, 17), generator=gen)
+                model.train()
+                loss = model.loss(tokens[:, :-1], tokens[:, 1:], scale=1.0 / 64)
+                loss.backward()
+                opt.step()
+                losses.append(float(loss.detach()))
+        finally:
+            recompute.Recipe.get = orig
+        assert model.activation_plan["keep"] == {"full": 0, "none": 3, "2": 2}[policy]
+        results[policy] = (losses, [p.detach().clone() for p in model.parameters()])
+        rebuilds[policy] = count["n"]
+    assert rebuilds["full"] == 0
+    # per keeping block and step: the activation output and four gathered weights; without tensor
+    # parallelism also the two norm outputs (with it, the projections save the GATHERED norm output)
+    # (with biases, the CPU library's linear works on a contiguous copy of the weight and saves that)
+    per_block = 1 if family == "gpt2" else (7 if tp == 1 else 5)
+    assert rebuilds["none"] == 3 * 3 * per_block and rebuilds["2"] == 3 * 2 * per_block, rebuilds
+    for policy in ("none", "2"):
+        for a, b in zip(results["full"][0], results[policy][0]):
+            assert abs(a - b) < 1e-6 * max(1.0, abs(a)), (policy, results["full"][0], results[policy][0])
+        for pa, pb in zip(results["full"][1], results[policy][1]):
+            assert torch.allclose(pa, pb, rtol=1e-5, atol=1e-7), (policy, (pa - pb).abs().max())
+    return True
+
+
+def test_blocks_that_keep_their_activations_train_like_blocks_that_recompute():
+    run_ranks("test_models", "body_activation_policies", 4, args=("llama", 2), timeout=300)
+    run_ranks("test_models", "body_activation_policies", 4, args=("gpt2", 2), timeout=300)
+    run_ranks("test_models", "body_activation_policies", 2, args=("llama", 1), timeout=300)
