@@ -25,9 +25,53 @@ def _shape(sl):
     return tuple(max(0, s.stop - s.start) for s in sl)
 
 
+_plans = {}
+
+
+def _box_plan(t, kind, x, P_x, slices, neighbor_ranks):
+    """The one-kernel form of the exchange on transports that have it (device tensors on the
+    native backend): all dimensions in one launch, one phase per dimension, faces packed into
+    the neighbours' inboxes and unpacked (or added and cleared, for the adjoint) by the kernel."""
+    maker = getattr(t, "box_plan", None)
+    if maker is None or not (x.is_cuda or getattr(t, "box_plans_on_host", False)):
+        return None
+    key = (kind, id(t), tuple(int(r) for pair in neighbor_ranks for r in pair),
+           tuple((s.start, s.stop) for per_dim in slices for box in per_dim for s in box))
+    plan = _plans.get(key, False)
+    if plan is not False:
+        return plan
+    phases = []
+    dims = range(P_x.dim) if kind == "fill" else reversed(range(P_x.dim))
+    for d in dims:
+        lb, lg, rb, rg = slices[d]
+        left, right = neighbor_ranks[d]
+        ops = []
+        for nbr, bulk, ghost in ((left, lb, lg), (right, rb, rg)):
+            if nbr == PROC_NULL:
+                continue
+            if kind == "fill":
+                if _volume(bulk):
+                    ops.append(("send", nbr, "x", bulk, False))
+                if _volume(ghost):
+                    ops.append(("recv", nbr, "x", ghost, False))
+            else:
+                if _volume(ghost):
+                    ops.append(("send", nbr, "x", ghost, True))      # ghosts leave and are cleared
+                if _volume(bulk):
+                    ops.append(("recv", nbr, "x", bulk, True))       # and are added to the owner's bulk
+        phases.append(ops)
+    plan = maker(phases, list(P_x.ranks))
+    _plans[key] = plan
+    return plan
+
+
 def fill_ghosts(t, x, P_x, slices, neighbor_ranks):
     """The exchange itself: a copy of ``x`` whose ghost regions hold the neighbours' bulk regions."""
     out = x.detach().clone()
+    plan = _box_plan(t, "fill", out, P_x, slices, neighbor_ranks)
+    if plan is not None:
+        plan.run(x=out)
+        return out
     for d in range(P_x.dim):
         lb, lg, rb, rg = slices[d]
         left, right = neighbor_ranks[d]
@@ -54,6 +98,10 @@ def fold_ghosts(t, x, P_x, slices, neighbor_ranks):
     """The adjoint of :func:`fill_ghosts`: ghost regions travel to the neighbours they came from,
     are ADDED to the bulk regions there, and are cleared here."""
     g = x.detach().clone()
+    plan = _box_plan(t, "fold", g, P_x, slices, neighbor_ranks)
+    if plan is not None:
+        plan.run(x=g)
+        return g
     for d in reversed(range(P_x.dim)):
         lb, lg, rb, rg = slices[d]
         left, right = neighbor_ranks[d]

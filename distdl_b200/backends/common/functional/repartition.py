@@ -9,12 +9,65 @@ once at set-up (the reference broadcasts that flag from the host on every
 call)."""
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ._base import TransportBound, empty_output
 
 
+_plans = {}
+
+
+def _box_plan(transport, send_overlaps, recv_overlaps, team):
+    """The one-kernel form on transports that have it: every overlap rectangle goes straight from
+    the source tensor into the partner's inbox and from there into its place in the output."""
+    maker = getattr(transport, "box_plan", None)
+    if maker is None or team is None:
+        return None
+
+    def sig(overlaps):
+        return tuple((None if sl is None else tuple((s.start, s.stop) for s in sl), str(p)) for sl, _, p in overlaps)
+    key = (id(transport), sig(send_overlaps), sig(recv_overlaps), tuple(team))
+    plan = _plans.get(key, False)
+    if plan is not False:
+        return plan
+    ops = []
+    self_src = next((sl for sl, _, p in send_overlaps if p == "self"), None)
+    for sl, sh, partner in send_overlaps:
+        if sl is not None and partner != "self":
+            ops.append(("send", partner, "src", sl, False))
+    for sl, sh, partner in recv_overlaps:
+        if sl is None:
+            continue
+        if partner == "self":
+            ops.append(("copy", "src", self_src, "out", sl))
+        else:
+            ops.append(("recv", partner, "out", sl, False))
+    plan = maker([ops], list(team))
+    _plans[key] = plan
+    return plan
+
+
 def _move(transport, src_tensor, out_shape, out_dtype, send_overlaps, recv_overlaps, device, team=None):
+    if (src_tensor.is_cuda or (out_shape is not None and torch.device(device).type == "cuda")
+            or getattr(transport, "box_plans_on_host", False)):
+        plan = _box_plan(transport, send_overlaps, recv_overlaps, team)
+        if plan is not None:
+            if send_overlaps and src_tensor.dtype != out_dtype:
+                src_tensor = src_tensor.to(out_dtype)
+            out = None
+            if out_shape is not None:
+                shape = tuple(int(s) for s in out_shape)
+                covered = sum(int(np.prod([int(v) for v in sh])) for sl, sh, _ in recv_overlaps if sl is not None)
+                alloc = torch.empty if covered == int(np.prod(shape)) else torch.zeros
+                out = alloc(shape, dtype=out_dtype, device=device)
+            tensors = {}
+            if send_overlaps:
+                tensors["src"] = src_tensor
+            if out is not None:
+                tensors["out"] = out
+            plan.run(**tensors)
+            return out
     sends = [(partner, src_tensor[sl]) for sl, sh, partner in send_overlaps
              if sl is not None and partner != "self"]
     recvs = [(partner, sh, out_dtype) for sl, sh, partner in recv_overlaps

@@ -71,6 +71,15 @@ class NativeTransport(GroupTransport):
             return False
         return self._collectives().reduce_scatter_accumulate_(stacked, acc, ranks, scale)
 
+    def box_plan(self, phases, team):
+        """A :class:`distdl_b200.parallel.box_exchange.BoxPlan` for the strided boxes of a halo
+        exchange or a repartition (packed, moved and unpacked by one kernel), or None when the
+        team cannot use the peer-mapped memory (more than one node, no device)."""
+        if not torch.cuda.is_available() or not 1 < len(team) <= 8 or not self._collectives().available(team):
+            return None
+        from ...parallel import box_exchange
+        return box_exchange.BoxPlan(phases)
+
     def exchange(self, sends, recvs, team=None):
         """All messages of a team in one kernel.  Every member launches that kernel on every
         exchange, whatever its own messages are, because the kernel opens with a barrier over

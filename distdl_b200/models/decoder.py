@@ -361,7 +361,7 @@ class Decoder(torch.nn.Module):
         """How many blocks (counted from the last) keep their activations for the backward pass; the
         others recompute their forward pass.  Decided once per input shape from
         ``cfg.activation_policy``; with "auto", from the device memory that is free at this moment (the
-        optimizer's state is allocated by then) and agreed over all workers (the smallest answer
+        optimizer's state is allocated by then) and agreed over the decoder's workers (the smallest answer
         wins), because a recomputed block repeats its collective kernels and its tensor-parallel
         peers must do the same."""
         cfg = self.cfg
@@ -394,11 +394,8 @@ class Decoder(torch.nn.Module):
             budget = free - head - moment - kept - slack
             keep = max(0, min(n, int(budget // max(kept, 1))))
             plan["free_bytes"] = int(free)
-            import torch.distributed as dist
-            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
-                t = torch.tensor([keep], dtype=torch.int64, device=tokens.device)
-                dist.all_reduce(t, op=dist.ReduceOp.MIN)
-                keep = int(t.item())
+            # agreed among the workers of this decoder (of this pipeline stage) through the control plane
+            keep = int(self.layout.P_grid.allreduce_data(np.asarray([keep], dtype=np.int64), op="min")[0])
         plan["keep"] = keep
         self._keep_plan = plan
         return keep

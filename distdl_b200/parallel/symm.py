@@ -45,7 +45,8 @@ _native.declare("dd_team_barrier", _TEAM + [_IP, c_void_p])
 SIGNAL_PAD_BYTES = 64 * 1024
 MB = 1 << 20
 # Regions of the staging buffer (same layout on every process).
-REGION_SIZES = (("coll", None), ("ag_shard", 128 * MB), ("rs0", 224 * MB), ("rs1", 224 * MB), ("misc", 4 * MB))
+REGION_SIZES = (("coll", None), ("ag_shard", 128 * MB), ("rs0", 224 * MB), ("rs1", 224 * MB), ("misc", 4 * MB),
+                ("inbox", 64 * MB))      # inbox: chunk buffers of the box exchange, one slot per source GPU
 
 
 class SymmetricHeap:

@@ -97,6 +97,71 @@ def check_primitives_native():
     assert torch.equal(t.grad, want)
 
 
+def check_box_exchange():
+    """The one-kernel halo exchange and repartition against the same primitives on the library path
+    (NCCL point-to-point + PyTorch slicing): messages of several chunks, faces with and without a
+    contiguous run, corners over two phases, the adjoint's add-and-clear in bf16, many calls in a row
+    (buffers and counters are reused)."""
+    import numpy as np
+
+    import distdl_b200
+    from distdl_b200.backends.common.functional import halo_exchange as hx
+    from distdl_b200.backends.common.functional import repartition as rp
+    from distdl_b200.backends.common.transport import GroupTransport
+    from distdl_b200.nn import HaloExchange, Repartition
+    world, rank = dist.get_world_size(), dist.get_rank()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    be = distdl_b200.backends.backend
+    native, plain = be.transport(), GroupTransport()
+    assert getattr(native, "box_plan", None) is not None
+    P_world = be.Partition()
+    # ---- halo exchange on a [1, 1, a, b] grid (a * b = world), widths 1 and 2
+    a = 2 if world % 2 == 0 else 1
+    grid = [1, 1, a, world // a]
+    P = P_world.create_cartesian_topology_partition(grid)
+    halo = np.array([[0, 0], [0, 0], [1, 1], [2, 2]])
+    idx = P.index
+    for d in (2, 3):
+        if idx[d] == 0:
+            halo[d][0] = 0
+        if idx[d] == grid[d] - 1:
+            halo[d][1] = 0
+    layer = HaloExchange(P, halo, halo, halo)
+    for dtype, bulk in ((torch.float32, (64, 52)), (torch.bfloat16, (33, 40)), (torch.float32, (256, 260))):
+        shape = [4, 16] + [bulk[d - 2] + int(halo[d][0]) + int(halo[d][1]) for d in (2, 3)]
+        torch.manual_seed(7 + rank)
+        x = torch.randn(*shape, device=dev).to(dtype)
+        layer._distdl_module_setup((x,))
+        for rep in range(3):
+            for fn in (hx.fill_ghosts, hx.fold_ghosts):
+                want = fn(plain, x, P, layer.slices, layer.neighbor_ranks)
+                got = fn(native, x, P, layer.slices, layer.neighbor_ranks)
+                if dtype == torch.float32:
+                    assert torch.equal(want, got), ("halo", fn.__name__, dtype, bulk, rep)
+                else:
+                    assert torch.allclose(want.float(), got.float(), atol=3e-2, rtol=2e-2), ("halo", fn.__name__, rep)
+            x = x + 1
+    # ---- repartition: row blocks -> column blocks of an [N, N] tensor, small and multi-chunk
+    P_rows = P_world.create_cartesian_topology_partition([world, 1])
+    P_cols = P_world.create_cartesian_topology_partition([1, world])
+    for N, dtype in ((8 * world, torch.float32), (40 * world + 3, torch.float32), (1024 * world, torch.bfloat16),
+                     (2048 * world, torch.float32)):
+        layer = Repartition(P_rows, P_cols, preserve_batch=False)
+        from distdl_b200.utilities.slicing import compute_start_index, compute_subshape
+        lo = int(compute_start_index([world, 1], [rank, 0], [N, N])[0])
+        n = int(compute_subshape([world, 1], [rank, 0], [N, N])[0])
+        gen = torch.Generator(device=dev).manual_seed(3)
+        full = torch.randn(N, N, device=dev, generator=gen).to(dtype)
+        x = full[lo:lo + n].clone()
+        for rep in range(3):
+            y = layer(x)
+            clo = int(compute_start_index([1, world], [0, rank], [N, N])[1])
+            cn = int(compute_subshape([1, world], [0, rank], [N, N])[1])
+            assert torch.equal(y, full[:, clo:clo + cn]), ("repartition", N, dtype, rep)
+    from distdl_b200 import _native
+    assert _native.read_status()[0] == 0
+
+
 def check_zero_grad_accumulate():
     """ZeRO weight gradients on the fast paths must equal the plain path (bf16 reduce-scatter
     by autograd): (1) unsharded fp32 accumulators filled by the weight-gradient GEMMs and
@@ -347,6 +412,54 @@ def check_context_parallel_decoder():
                 assert err < 5e-2, (mode, float(err))
 
 
+def check_activation_policies():
+    """Tensor-parallel (x ZeRO on more than 2 GPUs) training with every block recomputing against every
+    block keeping its activations (the fused kernels' gathered inputs stored, norm and activation
+    outputs rebuilt, weights gathered again in backward): the same loss trajectory."""
+    from distdl_b200 import models
+    from distdl_b200.parallel import SyntheticTokens, Trainer
+    world = dist.get_world_size()
+    tp = 2 if world % 2 == 0 else 1
+    losses = {}
+    for policy in ("full", "none", "1"):
+        torch.manual_seed(0)
+        cfg = models.llama_tiny(d_model=512, n_heads=4, n_kv_heads=2, ffn_dim=1024, max_seq=256, vocab_size=1024)
+        cfg.n_layers, cfg.activation_policy = 3, policy
+        layout = models.ParallelLayout(world // tp, tp)
+        model = models.Decoder(cfg, layout)
+        trainer = Trainer(model, global_tokens_per_step=2 * (world // tp) * 256, micro_batch=1, lr=2e-3,
+                          warmup_steps=0)
+        data = SyntheticTokens(2, 256, cfg.vocab_size, dp_index=layout.dp_index, seed=3)
+        block = data.next()
+        losses[policy] = [trainer.step(block).item() for _ in range(4)]
+        assert model.activation_plan["keep"] == {"full": 0, "none": 3, "1": 1}[policy]
+    for policy in ("none", "1"):
+        for a, b in zip(losses["full"], losses[policy]):
+            assert abs(a - b) < 2e-3 * max(1.0, abs(a)), losses
+    assert losses["none"][-1] < losses["none"][0], losses
+
+
+def check_pipelined_decoder():
+    """Two pipeline stages (of ``world / 2`` tensor-parallel workers each) train: the loss falls and
+    no device wait runs out.  The schedule and the per-stage optimizer layout on GPUs."""
+    from distdl_b200 import models
+    from distdl_b200.parallel import SyntheticTokens, Trainer
+    world = dist.get_world_size()
+    if world % 2:
+        return
+    torch.manual_seed(0)
+    cfg = models.llama_tiny(d_model=512, n_heads=4, n_kv_heads=2, ffn_dim=1024, max_seq=256, vocab_size=1024)
+    cfg.n_layers = 4
+    piped = models.PipelinedDecoder(cfg, pp=2, dp=1, tp=world // 2)
+    trainer = Trainer(piped, global_tokens_per_step=4 * 256, micro_batch=1, lr=2e-3, warmup_steps=0)
+    data = SyntheticTokens(4, 256, cfg.vocab_size, dp_index=0, seed=3)
+    block = data.next()
+    losses = [trainer.step(block).item() for _ in range(5)]
+    assert losses[-1] < losses[0], losses
+    from distdl_b200 import _native
+    assert _native.read_status()[0] == 0
+
+
 def main():
     import distdl_b200
     from distdl_b200.backends.common import world as dworld
@@ -366,6 +479,12 @@ def main():
         check_moe_peer()
     if what == "context_decoder":
         check_context_parallel_decoder()
+    if what in ("box", "all"):
+        check_box_exchange()
+    if what == "activation_policies":
+        check_activation_policies()
+    if what == "pipeline":
+        check_pipelined_decoder()
     if what in ("fused", "all"):
         from multi_gpu_fused import check_fused
         check_fused()

@@ -38,3 +38,23 @@ def test_primitives_on_native_backend():
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_fused_ag_gemm_and_gemm_rs():
     _run("fused", min(_ngpu(), 8))
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_blocks_that_keep_activations_train_like_blocks_that_recompute():
+    _run("activation_policies", min(_ngpu(), 8))
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_context_parallel_decoder_on_gpus():
+    _run("context_decoder", 2 if _ngpu() < 4 else 4)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_pipelined_decoder_on_gpus():
+    _run("pipeline", 2 if _ngpu() < 4 else 4)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_halo_exchange_and_repartition_in_one_kernel():
+    _run("box", min(_ngpu(), 8))
