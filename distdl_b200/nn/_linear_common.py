@@ -85,6 +85,7 @@ def deliver_grad(param, g):
         from ..ops.optim import accumulate_f32_
         accumulate_f32_(acc, g)
     else:
+        g = g.to(param.dtype)          # (an fp32 accumulation of a bf16 parameter's gradient)
         param.grad = g if param.grad is None else param.grad + g
 
 
