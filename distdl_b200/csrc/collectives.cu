@@ -16,6 +16,7 @@
 //
 // All kernels of this file are launched with exactly kCollectiveCtas CTAs so
 // that every flag slot advances in step on all GPUs.
+#include <cmath>
 #include <cstring>
 
 #include "common.cuh"
@@ -673,6 +674,58 @@ __global__ void __launch_bounds__(256) rs_pull_f32_kernel(const PullDescF32 d, f
   }
 }
 
+// The ZeRO gradient step of one parameter shard in ONE kernel: this GPU's slice of every peer's
+// unsharded fp32 gradient accumulator is read in place (peer loads), summed, scaled and fed
+// straight into the AdamW update of the fp32 master weights and both moments; the bf16 working
+// copy of the shard is refreshed and the shard's own fp32 gradient (contributions that arrived
+// by other routes) is consumed and cleared.  The reduced gradient never goes to memory.
+// Stands where the reference runs the all-gather's adjoint (divide, rearrange, ncclReduceScatter:
+// src/distdl/backends/nccl_cupy/functional/all_gather.py:144-240) and leaves the update to a
+// separate optimizer.
+struct AdamHyper {
+  float lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale;
+};
+__global__ void __launch_bounds__(256)
+grad_rs_adamw_kernel(const PullDescF32 d, float4* __restrict__ grad, float4* __restrict__ master,
+                     float4* __restrict__ m, float4* __restrict__ v, uint2* __restrict__ param_bf16, size_t nvec,
+                     const AdamHyper h, const float* __restrict__ grad_scale_ptr) {
+  const float gs = h.grad_scale * (grad_scale_ptr ? *grad_scale_ptr : 1.f);
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = tid; i < nvec; i += stride) {
+    uint4 u[kMaxPeers];
+#pragma unroll
+    for (int k = 0; k < kMaxPeers; ++k)
+      if (k < d.n) u[k] = ld_peer(d.src[k] + i);
+    const float4 g0 = grad[i];
+    float4 p = master[i], mm = m[i], vv = v[i];
+    float ga[4] = {g0.x, g0.y, g0.z, g0.w};
+#pragma unroll
+    for (int k = 0; k < kMaxPeers; ++k)
+      if (k < d.n) {
+        ga[0] += __uint_as_float(u[k].x); ga[1] += __uint_as_float(u[k].y);
+        ga[2] += __uint_as_float(u[k].z); ga[3] += __uint_as_float(u[k].w);
+      }
+    float pa[4] = {p.x, p.y, p.z, p.w}, ma[4] = {mm.x, mm.y, mm.z, mm.w}, va[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float gj = ga[j] * gs;
+      ma[j] = h.beta1 * ma[j] + (1.f - h.beta1) * gj;
+      va[j] = h.beta2 * va[j] + (1.f - h.beta2) * gj * gj;
+      const float mh = ma[j] / h.bc1, vh = va[j] / h.bc2;
+      pa[j] = pa[j] * (1.f - h.lr * h.wd) - h.lr * mh / (sqrtf(vh) + h.eps);
+    }
+    master[i] = make_float4(pa[0], pa[1], pa[2], pa[3]);
+    m[i] = make_float4(ma[0], ma[1], ma[2], ma[3]);
+    v[i] = make_float4(va[0], va[1], va[2], va[3]);
+    grad[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    uint2 o;
+    o.x = pack_bf16x2(pa[0], pa[1]);
+    o.y = pack_bf16x2(pa[2], pa[3]);
+    param_bf16[i] = o;
+  }
+}
+
 __global__ void __launch_bounds__(kThreads) barrier_only_kernel(const Team t) {
   __shared__ int fail;
   if (threadIdx.x == 0) fail = 0;
@@ -878,6 +931,34 @@ DD_API int dd_rs_pull_f32(int n, void* const* srcs, float* acc, size_t count, fl
   if (ctas > 148 * 4) ctas = 148 * 4;
   rs_pull_f32_kernel<<<(int)ctas, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(d, reinterpret_cast<float4*>(acc),
                                                                                   nvec, scale);
+  return (int)cudaGetLastError();
+}
+// count: elements of the shard (multiple of 4); srcs[k]: this GPU's slice of member k's accumulator.
+DD_API int dd_grad_rs_adamw(int n, void* const* srcs, float* grad, float* master, float* m, float* v,
+                            void* param_bf16, size_t count, float lr, float beta1, float beta2, float eps, float wd,
+                            int step, const float* grad_scale_ptr, float grad_scale, void* stream) {
+  if (n < 1 || n > kMaxPeers || count % 4) return DD_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(grad) | reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) |
+       reinterpret_cast<uintptr_t>(v)) & 15)
+    return DD_ERR_ALIGN;
+  if (reinterpret_cast<uintptr_t>(param_bf16) & 7) return DD_ERR_ALIGN;
+  PullDescF32 d;
+  d.n = n;
+  for (int i = 0; i < n; ++i) {
+    if (srcs[i] == nullptr || (reinterpret_cast<uintptr_t>(srcs[i]) & 15)) return DD_ERR_ALIGN;
+    d.src[i] = reinterpret_cast<const float4*>(srcs[i]);
+  }
+  const size_t nvec = count / 4;
+  if (nvec == 0) return 0;
+  AdamHyper h;
+  h.lr = lr; h.beta1 = beta1; h.beta2 = beta2; h.eps = eps; h.wd = wd; h.grad_scale = grad_scale;
+  h.bc1 = 1.f - powf(beta1, (float)step);
+  h.bc2 = 1.f - powf(beta2, (float)step);
+  size_t ctas = (nvec + 255) / 256;
+  if (ctas > 148 * 8) ctas = 148 * 8;
+  grad_rs_adamw_kernel<<<(int)ctas, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      d, reinterpret_cast<float4*>(grad), reinterpret_cast<float4*>(master), reinterpret_cast<float4*>(m),
+      reinterpret_cast<float4*>(v), reinterpret_cast<uint2*>(param_bf16), nvec, h, grad_scale_ptr);
   return (int)cudaGetLastError();
 }
 // Expert-parallel routing over peer memory (see moe_scatter_peer_kernel).  mode 0: scatter

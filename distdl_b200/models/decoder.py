@@ -324,6 +324,7 @@ class Decoder(torch.nn.Module):
         lo, hi = stage_layers(cfg.n_layers, self.stage_index, self.n_stages)
         self.layer_range = (lo, hi)
         self.blocks = torch.nn.ModuleList(Block(cfg, layout) for _ in range(hi - lo))
+        self._block_backward_hooks = []
         if self.last_stage:
             self.final_norm = _norm(cfg, layout.P_flat, True, keep=keep_root)
             self.head = dnn.DistributedLinearAllGatherZero(layout.P_flat, cfg.d_model, V, bias=False, dtype=cfg.dtype,
@@ -347,15 +348,26 @@ class Decoder(torch.nn.Module):
                     s = std / math.sqrt(2 * cfg.n_layers) if (".out." in name or ".down." in name) else std
                     p.normal_(0.0, s)
 
-    def _backward_prefetch(self, i):
-        block = self.blocks[i]
+    def _backward_prefetch(self, i, done=None):
+        block = self.blocks[i] if i >= 0 else None
 
         def hook(_grad):
-            # (with gradient tracking on: where weight gradients travel through autograd, a recomputed
-            # block must see the gather as part of its graph)
-            with torch.enable_grad():
-                block.prefetch()
+            if done is not None:
+                for fn in self._block_backward_hooks:
+                    fn(done)
+            if block is not None:
+                # (with gradient tracking on: where weight gradients travel through autograd, a
+                # recomputed block must see the gather as part of its graph)
+                with torch.enable_grad():
+                    block.prefetch()
         return hook
+
+    def add_block_backward_hook(self, fn):
+        """``fn(i)`` is called during every backward pass as soon as block ``i`` (index within this
+        stage) has finished its backward pass, i.e. when all its parameter gradients of this
+        micro-batch are complete (in order ``n - 1, ..., 0``).  An optimizer uses it to reduce and
+        apply a block's gradients while the blocks before it are still in their backward pass."""
+        self._block_backward_hooks.append(fn)
 
     def _blocks_that_keep(self, tokens):
         """How many blocks (counted from the last) keep their activations for the backward pass; the
@@ -463,6 +475,9 @@ class Decoder(torch.nn.Module):
         def run(x, i):
             return self.blocks[i](x)
 
+        notify = bool(self._block_backward_hooks) and self.training and torch.is_grad_enabled()
+        if notify and n and x.requires_grad:
+            x.register_hook(self._backward_prefetch(-1, done=0))     # the input of block 0
         for i in range(n):
             if pre and i + 1 < n:
                 self.blocks[i + 1].prefetch()
@@ -471,9 +486,11 @@ class Decoder(torch.nn.Module):
             else:
                 with recompute.enabled():
                     x = self.blocks[i](x)
-            if pre and i > 0 and x.requires_grad:
-                # the backward pass reaches block i: start gathering the weights of block i - 1
-                x.register_hook(self._backward_prefetch(i - 1))
+            if x.requires_grad and ((pre and i > 0) or (notify and i + 1 < n)):
+                # the gradient of block i's output is ready when the backward pass of block i + 1 is
+                # complete and that of block i begins: tell the listeners, and start gathering the
+                # weights of block i - 1
+                x.register_hook(self._backward_prefetch(i - 1 if pre else -1, done=i + 1 if notify and i + 1 < n else None))
         if pre and n and self.training and torch.is_grad_enabled():
             self.blocks[n - 1].prefetch()          # the first block of the backward pass
         return self.final_norm(x) if self.last_stage else x

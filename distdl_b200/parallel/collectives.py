@@ -110,6 +110,10 @@ _native.declare("dd_gather_pull", [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ct
 
 _native.declare("dd_rs_pull_f32", [ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.c_size_t,
                                    ctypes.c_float, ctypes.c_void_p])
+_native.declare("dd_grad_rs_adamw", [ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.c_void_p,
+                                     ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float,
+                                     ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_int,
+                                     ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p])
 _native.declare("dd_gather_pull_ce", [ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.c_size_t,
                                       ctypes.c_void_p])
 # messages of at least this many bytes per member go through the copy engines

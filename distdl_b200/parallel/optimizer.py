@@ -28,6 +28,7 @@ class FlatAdamW:
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.max_grad_norm = max_grad_norm
         self.step_count = 0
+        self._by_block, self._armed, self._block_done, self._updated_ranges, self._all_blocks = {}, False, set(), [], []
         self._release = getattr(model, "release_gathered", None)
         named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
         decay = [(n, p) for n, p in named if not any(k in n for k in no_decay)]
@@ -100,6 +101,7 @@ class FlatAdamW:
         self._clip = torch.ones(1, dtype=torch.float32, device=device)
         self.last_grad_norm = None
         self._setup_full_grads(ordered)
+        self._setup_overlap(model, ordered)
         self._publish()
 
     def _grouped_sizes(self, ordered, table, sizes):
@@ -192,6 +194,70 @@ class FlatAdamW:
             p.full_grad_view = self._full_flat[o:o + len(team) * n]
             self._full.append((p, o, n, team, me))
 
+    # ------------------------------------------------- reduction overlapped with the backward pass
+    def _setup_overlap(self, model, ordered):
+        """Groups the unsharded accumulators by the model's blocks, so that a block's gradients can be
+        reduced (and, without gradient clipping, applied) as soon as that block has finished the
+        backward pass of the step's last micro-batch, while the blocks before it are still busy.
+        Needs a model that reports the end of a block's backward pass (``add_block_backward_hook``,
+        parameter names ``blocks.<i>.``) and the same grouping on every process."""
+        import re
+        hook = getattr(model, "add_block_backward_hook", None)
+        if not self._full_any or os.environ.get("DISTDL_OVERLAP_GRADS", "1") == "0":
+            return
+        names = {id(p): n for n, p in ordered}
+        for entry in self._full:
+            mt = re.search(r"(?:^|\.)blocks\.(\d+)\.", names.get(id(entry[0]), ""))
+            if mt is not None:
+                self._by_block.setdefault(int(mt.group(1)), []).append(entry)
+        # collective agreement: the barriers of the per-block reduction involve every process
+        table = [None] * dist.get_world_size()
+        dist.all_gather_object(table, (hook is not None, sorted((b, len(v)) for b, v in self._by_block.items())))
+        filled = [t for t in table if t[1]]
+        if not all(t[0] for t in table) or any(t[1] != filled[0][1] for t in filled):
+            self._by_block = {}
+            return
+        self._all_blocks = [b for b, _ in filled[0][1]] if filled else []
+        hook(self._on_block_backward_done)
+
+    def begin_last_micro_batch(self):
+        """The next backward pass is the last one before :meth:`step`: from now on a block's
+        accumulated gradients are final as soon as its backward pass ends.  (``Trainer`` calls
+        this; without the call everything is reduced inside :meth:`step`.)"""
+        if self._by_block or getattr(self, "_all_blocks", None):
+            self._armed = True
+            self._block_done = set()
+            self._updated_ranges = []
+
+    def _on_block_backward_done(self, block):
+        if not self._armed or block in self._block_done or block not in getattr(self, "_all_blocks", ()):
+            return
+        import ctypes
+        from . import collectives
+        self._block_done.add(block)
+        # every process of the job has finished this block's backward pass: the peers' accumulators
+        # of the block are complete, and nobody reads the block's parameter shards any more
+        collectives.barrier(list(range(dist.get_world_size())))
+        lib = _native.lib()
+        reg = self._full_region
+        stream = stream_ptr()
+        fused = not self.max_grad_norm
+        b1, b2 = self.betas
+        for p, o, n, team, me in self._by_block.get(block, ()):
+            srcs = (ctypes.c_void_p * len(team))(*[reg.ptrs[r] + 4 * (o + me * n) for r in team])
+            g = p.main_grad_view
+            _native.launch_count += 1
+            if fused:
+                lo = (g.data_ptr() - self.grad.data_ptr()) // 4
+                wd = self.weight_decay if lo < self.groups[0][1] else 0.0
+                _native.check(lib.dd_grad_rs_adamw(
+                    len(team), srcs, g.data_ptr(), self.master[lo:lo + n].data_ptr(), self.exp_avg[lo:lo + n].data_ptr(),
+                    self.exp_avg_sq[lo:lo + n].data_ptr(), self.param_flat[lo:lo + n].data_ptr(), n, self.lr, b1, b2,
+                    self.eps, wd, self.step_count + 1, None, 1.0, stream), "dd_grad_rs_adamw")
+                self._updated_ranges.append((lo, n))
+            else:
+                _native.check(lib.dd_rs_pull_f32(len(team), srcs, g.data_ptr(), n, 1.0, stream), "dd_rs_pull_f32")
+
     def _reduce_full_grads(self):
         if not self._full_any:
             return
@@ -203,7 +269,13 @@ class FlatAdamW:
         lib = _native.lib()
         reg = self._full_region
         stream = stream_ptr()
+        done = set()
+        if self._armed:
+            for b in self._block_done:
+                done.update(id(e[0]) for e in self._by_block.get(b, ()))
         for p, o, n, team, me in self._full:
+            if id(p) in done:
+                continue                               # reduced while the backward pass was still running
             srcs = (ctypes.c_void_p * len(team))(*[reg.ptrs[r] + 4 * (o + me * n) for r in team])
             _native.launch_count += 1
             _native.check(lib.dd_rs_pull_f32(len(team), srcs, p.main_grad_view.data_ptr(), n, 1.0, stream),
@@ -278,13 +350,30 @@ class FlatAdamW:
         if not self.max_grad_norm:
             self._quiesce()           # (the all-reduce of the gradient norm already orders the processes)
         for start, length, wd in self.groups:
-            if length == 0:
-                continue
-            sl = slice(start, start + length)
-            ops.adamw_step_(self.master[sl], self.exp_avg[sl], self.exp_avg_sq[sl], self.grad[sl],
-                            self.param_flat[sl], lr=self.lr, beta1=b1, beta2=b2, eps=self.eps, weight_decay=wd,
-                            step=self.step_count, grad_scale_tensor=clip_ptr, grad_scale=grad_scale, zero_grad=True)
+            for lo, n in self._remaining(start, length):
+                sl = slice(lo, lo + n)
+                ops.adamw_step_(self.master[sl], self.exp_avg[sl], self.exp_avg_sq[sl], self.grad[sl],
+                                self.param_flat[sl], lr=self.lr, beta1=b1, beta2=b2, eps=self.eps, weight_decay=wd,
+                                step=self.step_count, grad_scale_tensor=clip_ptr, grad_scale=grad_scale,
+                                zero_grad=True)
+        self._armed = False
+        self._updated_ranges = []
         self._publish()
+
+    def _remaining(self, start, length):
+        """The parts of ``[start, start + length)`` that the per-block fused updates of this step
+        have not already taken care of, as (offset, length) runs."""
+        if length <= 0:
+            return []
+        taken = sorted((lo, n) for lo, n in getattr(self, "_updated_ranges", ()) if lo < start + length and lo + n > start)
+        out, at = [], start
+        for lo, n in taken:
+            if lo > at:
+                out.append((at, lo - at))
+            at = max(at, lo + n)
+        if at < start + length:
+            out.append((at, start + length - at))
+        return out
 
     def zero_grad(self):
         if self.total:

@@ -70,6 +70,8 @@ class Trainer:
         else:
             for lo in range(0, B, self.micro_batch):
                 mb = tokens[lo:lo + self.micro_batch]
+                if lo + self.micro_batch >= B:
+                    self.opt.begin_last_micro_batch()     # gradients are final block by block from here on
                 # the loss is back-propagated as it is (gradient 1), which the fused cross-entropy may rely on
                 loss = self.model.loss(mb[:, :-1], mb[:, 1:], scale=scale, unit_grad=True)
                 loss.backward()

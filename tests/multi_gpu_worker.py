@@ -347,6 +347,39 @@ def check_symmetric_params():
     assert losses["1"][-1] < losses["1"][0], losses
 
 
+def check_overlapped_gradient_step():
+    """ZeRO gradients reduced block by block while the backward pass of the last micro-batch is still
+    running (and, without clipping, applied by the fused reduce + AdamW kernel) against the same
+    training with everything reduced inside the optimizer step."""
+    import os
+    from distdl_b200 import _native, models
+    from distdl_b200.parallel import SyntheticTokens, Trainer
+    world = dist.get_world_size()
+    for clip in (1.0, 0.0):
+        losses = {}
+        for mode in ("0", "1"):
+            os.environ["DISTDL_OVERLAP_GRADS"] = mode
+            torch.manual_seed(0)
+            cfg = models.llama_tiny(d_model=256, n_heads=4, n_kv_heads=2, ffn_dim=512, max_seq=128, vocab_size=1024)
+            cfg.n_layers = 3
+            layout = models.ParallelLayout(world, 1)
+            model = models.Decoder(cfg, layout)
+            trainer = Trainer(model, global_tokens_per_step=4 * world * 128, micro_batch=2, lr=2e-3, warmup_steps=0,
+                              max_grad_norm=clip)
+            assert bool(trainer.opt._by_block) == (mode == "1"), "unexpected grouping of the accumulators"
+            data = SyntheticTokens(4, 128, cfg.vocab_size, dp_index=layout.dp_index, seed=3)
+            block = data.next()
+            launches = _native.launch_count
+            losses[mode] = [trainer.step(block).item() for _ in range(4)]
+            if mode == "1":
+                assert len(trainer.opt._block_done) == 3      # every block was reduced from its backward hook
+        os.environ.pop("DISTDL_OVERLAP_GRADS", None)
+        for a, b in zip(losses["0"], losses["1"]):
+            assert abs(a - b) < 1e-3 * max(1.0, abs(a)), (clip, losses)
+        assert losses["1"][-1] < losses["1"][0], losses
+    assert _native.read_status()[0] == 0
+
+
 def check_moe_peer():
     """Expert-parallel block: dispatch / combine over peer memory against the unfused path
     (permutation kernels + all-to-all), outputs and all gradients."""
@@ -476,6 +509,7 @@ def main():
         check_context_parallel_attention()
         check_ring_attention()
         check_symmetric_params()
+        check_overlapped_gradient_step()
         check_moe_peer()
     if what == "context_decoder":
         check_context_parallel_decoder()
