@@ -105,6 +105,8 @@ class _ZeroNormBase(Module):
         self.buffers_gathered = out
 
     def collect_weights(self):
+        if not hasattr(self, "prefetch"):
+            return          # a worker outside the layer's partition holds nothing
         if not self.elementwise_affine:
             return
         params = [getattr(self, n) for n in self.param_names]
@@ -117,10 +119,14 @@ class _ZeroNormBase(Module):
     prefetch_weights = collect_weights
 
     def wait_for_streams(self):
+        if not hasattr(self, "prefetch"):
+            return          # a worker outside the layer's partition holds nothing
         if self.elementwise_affine:
             self.prefetch.wait()
 
     def clear_weight_buffer(self):
+        if not hasattr(self, "prefetch"):
+            return          # a worker outside the layer's partition holds nothing
         if self.buffers_gathered is not None and not self.auto_clear_buffer:
             for n, full in self.buffers_gathered.items():
                 g = full.grad

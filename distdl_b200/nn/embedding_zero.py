@@ -89,6 +89,8 @@ class DistributedEmbeddingZero(Module):
         self.weight_buffer = w if self.auto_clear_buffer else w.detach().requires_grad_(True)
 
     def collect_weights(self):
+        if not hasattr(self, "prefetch"):
+            return          # a worker outside the layer's partition holds nothing
         if self.weight_buffer is not None and not self.auto_clear_buffer and self._kept.stale(self.weight):
             self.weight_buffer = None
         if self.weight_buffer is None:
@@ -98,9 +100,13 @@ class DistributedEmbeddingZero(Module):
     prefetch_weights = collect_weights
 
     def wait_for_streams(self):
+        if not hasattr(self, "prefetch"):
+            return          # a worker outside the layer's partition holds nothing
         self.prefetch.wait()
 
     def clear_weight_buffer(self):
+        if not hasattr(self, "prefetch"):
+            return          # a worker outside the layer's partition holds nothing
         if not self.auto_clear_buffer and self.weight_buffer is not None and self.weight_buffer.grad is not None:
             reduce_scatter_grad(self.reduce_scatter, self.weight_buffer.grad, self.weight, self.scale_backward)
         self.weight_buffer = None

@@ -220,6 +220,8 @@ class DistributedLinearAllGatherZero(Module):
 
     def collect_weights(self):
         """Gathers the weight (and bias) shards, on the side stream when there is one."""
+        if not hasattr(self, "prefetch"):
+            return          # a worker outside the layer's partition holds nothing
         if self.weight_buffer is not None and not self.auto_clear_buffer and self._kept.stale(self.weight, self.bias):
             self.weight_buffer = self.bias_buffer = None
         if self.weight_buffer is None:
@@ -229,11 +231,15 @@ class DistributedLinearAllGatherZero(Module):
     prefetch_weights = collect_weights
 
     def wait_for_streams(self):
+        if not hasattr(self, "prefetch"):
+            return          # a worker outside the layer's partition holds nothing
         self.prefetch.wait()
 
     def clear_weight_buffer(self):
         """Drops the gathered weights.  In ZeRO-1 mode first reduce-scatters the
         gradients accumulated on them into ``weight.grad`` / ``bias.grad``."""
+        if not hasattr(self, "prefetch"):
+            return          # a worker outside the layer's partition holds nothing
         if not self.auto_clear_buffer and self.weight_buffer is not None and self.weight_buffer.grad is not None:
             g = self.weight_buffer.grad
             reduce_scatter_grad(self.reduce_scatter_weight, g.reshape([self.in_features] + list(self.weight.shape[1:])),

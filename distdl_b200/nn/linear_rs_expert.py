@@ -138,15 +138,21 @@ class DistributedExpertReduceScatter(Module):
             self.bias_buffer = self.broadcast_bias(self.bias)
 
     def collect_weights(self):
+        if not hasattr(self, "prefetch"):
+            return          # a worker outside the layer's partition holds nothing
         if self.weight_buffer is None:
             self.prefetch.run(self._collect_weights)
 
     prefetch_weights = collect_weights
 
     def wait_for_streams(self):
+        if not hasattr(self, "prefetch"):
+            return          # a worker outside the layer's partition holds nothing
         self.prefetch.wait()
 
     def clear_weight_buffer(self):
+        if not hasattr(self, "prefetch"):
+            return          # a worker outside the layer's partition holds nothing
         if not self.auto_clear_buffer and self.weight_buffer is not None and self.weight_buffer.grad is not None:
             g = self.weight_buffer.grad
             if self.scale_backward is not None:

@@ -164,6 +164,8 @@ class DistributedLinearReduceScatterZero(Module):
                 self.bias_buffer = self.bias_buffer.detach().requires_grad_(True)
 
     def collect_weights(self):
+        if not hasattr(self, "prefetch"):
+            return          # a worker outside the layer's partition holds nothing
         bias = self.bias if (self.use_bias and self.P_bias.active) else None
         if self.weight_buffer is not None and not self.auto_clear_buffer and self._kept.stale(self.weight, bias):
             self.weight_buffer = self.bias_buffer = None
@@ -174,9 +176,13 @@ class DistributedLinearReduceScatterZero(Module):
     prefetch_weights = collect_weights
 
     def wait_for_streams(self):
+        if not hasattr(self, "prefetch"):
+            return          # a worker outside the layer's partition holds nothing
         self.prefetch.wait()
 
     def clear_weight_buffer(self):
+        if not hasattr(self, "prefetch"):
+            return          # a worker outside the layer's partition holds nothing
         if not self.auto_clear_buffer and self.weight_buffer is not None and self.weight_buffer.grad is not None:
             g = self.weight_buffer.grad
             reduce_scatter_grad(self.reduce_scatter_weight, g.reshape([self.out_features] + list(self.weight.shape[1:])),
@@ -190,7 +196,7 @@ class DistributedLinearReduceScatterZero(Module):
         self.weight_buffer = None
         self.bias_buffer = None
 
-    def _apply(self, input, w, b):
+    def _linear_then_scatter(self, input, w, b):
         if input.is_cuda and getattr(self._distdl_backend, "name", "") == "native_cupy":
             from ..parallel import fused
             y = fused.maybe_linear_rs(self, input, w, b)
@@ -217,7 +223,7 @@ class DistributedLinearReduceScatterZero(Module):
         # holding the gathered weight since the forward pass
         resharded = self.auto_clear_buffer and int(self.allgather_weight.P_x.shape[self.allgather_weight.axes_all_gather[0]]) > 1
         with recompute.saved_as_recipe(base, self._regather if resharded else None):
-            y = self._apply(input, w, self.bias_buffer)
+            y = self._linear_then_scatter(input, w, self.bias_buffer)
         if self.auto_clear_buffer:
             self.clear_weight_buffer()
         return y
@@ -244,7 +250,7 @@ class _CheckpointedRSZero(torch.autograd.Function):
         with torch.no_grad():
             w = layer.allgather_weight(weight).reshape(layer.out_features, layer.in_features_local)
             b = layer.allgather_bias(bias).reshape(layer.out_features) if bias is not None else None
-            return layer._apply(input, w, b)
+            return layer._linear_then_scatter(input, w, b)
 
     @staticmethod
     def backward(ctx, grad_output):
@@ -256,7 +262,7 @@ class _CheckpointedRSZero(torch.autograd.Function):
             bi = bias.detach().requires_grad_(True) if bias is not None else None
             w = layer.allgather_weight(wi).reshape(layer.out_features, layer.in_features_local)
             b = layer.allgather_bias(bi).reshape(layer.out_features) if bi is not None else None
-            y = layer._apply(xi, w, b)
+            y = layer._linear_then_scatter(xi, w, b)
         ins = [t for t in (xi, wi, bi) if t is not None and t.requires_grad]
         grads = iter(torch.autograd.grad(y, ins, grad_output))
         gx = next(grads) if xi.requires_grad else None

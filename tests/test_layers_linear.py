@@ -410,3 +410,36 @@ def test_sliding_window_attention_by_halo_exchange():
     run_ranks("test_layers_linear", "body_window_attention", 4, args=(4, 4, 2), timeout=180)
     run_ranks("test_layers_linear", "body_window_attention", 3, args=(7, 2, 2), timeout=180)
     run_ranks("test_layers_linear", "body_window_attention", 2, args=(1, 2, 1), timeout=180)
+
+
+def body_store_bias_partition(rank, world):
+    """A user-supplied ``P_store_bias`` (here the second data-parallel row instead of the first) carries
+    the bias between the shards and the serial state dict."""
+    from distdl_b200.nn import DistributedLinearAllGatherZero
+    from distdl_b200.utilities.torch import zero_volume_tensor
+    torch.manual_seed(0)
+    P_feat = _cart([0, 1, 2, 3], [2, 1, 2])
+    P_store = _cart([2, 3], [1, 2, 1])
+    serial = torch.nn.Linear(10, 12)
+    layer = DistributedLinearAllGatherZero(P_feat, 10, 12, collect_state=True, P_store_bias=P_store)
+    sd = serial.state_dict() if rank == 0 else {k: zero_volume_tensor() for k in serial.state_dict()}
+    layer.load_state_dict(sd, strict=False)
+    out = layer.state_dict()
+    if rank == 0:
+        for k, v in serial.state_dict().items():
+            assert torch.allclose(out[k], v), k
+    xg = torch.randn(4, 3, 10)
+    _run_vs_serial(layer, serial, P_feat, P_feat, xg, rank, load=False)
+    # a member that sits in the wrong tensor-parallel column is refused
+    bad = _cart([3, 2], [1, 2, 1])
+    try:
+        DistributedLinearAllGatherZero(P_feat, 10, 12, P_store_bias=bad)
+        ok = rank not in (2, 3)
+    except ValueError:
+        ok = rank in (2, 3)
+    assert ok
+    return True
+
+
+def test_store_bias_partition_is_honoured():
+    run_ranks("test_layers_linear", "body_store_bias_partition", 4, timeout=120)
