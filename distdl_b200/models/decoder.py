@@ -189,19 +189,20 @@ class Attention(torch.nn.Module):
             qkv = self.qkv(x)                                 # [b, s, (hq + 2 hkv) * hd]
         del x
         b, s = qkv.shape[0], qkv.shape[1]
-        t = qkv.reshape(b * s, self.hq + 2 * self.hkv, cfg.head_dim)
+        lay3 = (b * s, self.hq + 2 * self.hkv, cfg.head_dim)
         if self.ring is None:
             if cfg.rope:
-                t = ops.rope_(t, s, self.hq + self.hkv, cfg.rope_theta)
-            o = ops.attention_packed(t, self.hq, self.hkv, b, s, causal=True)
+                qkv = ops.rope_(qkv, s, self.hq + self.hkv, cfg.rope_theta, layout=lay3)
+            o = ops.attention_packed(qkv.reshape(lay3), self.hq, self.hkv, b, s, causal=True)
         else:
             # context parallel: s is this worker's block of the sequence; positions are global
             if cfg.rope and cfg.cp_mode == "zigzag":
-                t = ops.rope_(t, s, self.hq + self.hkv, cfg.rope_theta,
-                              ranges=zigzag_ranges(self.layout.cp, self.layout.cp_index, s * self.layout.cp))
+                qkv = ops.rope_(qkv, s, self.hq + self.hkv, cfg.rope_theta, layout=lay3,
+                                ranges=zigzag_ranges(self.layout.cp, self.layout.cp_index, s * self.layout.cp))
             elif cfg.rope:
-                t = ops.rope_(t, s, self.hq + self.hkv, cfg.rope_theta, offset=self.layout.cp_index * s)
-            t = t.reshape(b, s, self.hq + 2 * self.hkv, cfg.head_dim)
+                qkv = ops.rope_(qkv, s, self.hq + self.hkv, cfg.rope_theta, offset=self.layout.cp_index * s,
+                                layout=lay3)
+            t = qkv.reshape(b, s, self.hq + 2 * self.hkv, cfg.head_dim)
             q, k, v = t.split([self.hq, self.hkv, self.hkv], dim=2)
             o = self.ring(q.contiguous(), k.contiguous(), v.contiguous())
         return self.out(o.reshape(b, s, self.hq * cfg.head_dim))
@@ -240,15 +241,23 @@ class Block(torch.nn.Module):
         else:
             self.mlp = MLP(cfg, layout)
 
-    def forward(self, x):
-        if not recompute.active():
-            x = x + self.attn(self.norm1(x))
-            return x + self.mlp(self.norm2(x))
-        # this block keeps its activations: the norm outputs are rebuilt in the backward pass
-        x = x + self.attn(self.norm1(x), remake=lambda x=x: self.norm1(x))
+    def forward(self, x, delta=None):
+        """``x``: the residual stream, ``delta``: what the block before this one still has to add to
+        it (its feed-forward output), or None.  Returns the pair in the same form: the stream after
+        the attention branch was added, and this block's feed-forward output.  Every residual add
+        thereby runs inside the norm kernel that follows it."""
+        keep = recompute.active()          # this block keeps its activations: norm outputs are rebuilt in backward
+        if delta is None:
+            n1 = self.norm1(x)
+        else:
+            x, n1 = _add_norm(self.norm1, x, delta)
+        a = self.attn(n1, remake=(lambda x=x: self.norm1(x)) if keep else None)
+        del n1
+        x, n2 = _add_norm(self.norm2, x, a)
+        del a
         if isinstance(self.mlp, MLP):
-            return x + self.mlp(self.norm2(x), remake=lambda x=x: self.norm2(x))
-        return x + self.mlp(self.norm2(x))
+            return x, self.mlp(n2, remake=(lambda x=x: self.norm2(x)) if keep else None)
+        return x, self.mlp(n2)
 
     def kept_bytes(self, cfg, layout, b, s):
         """(bytes this block stores from forward to backward for a micro-batch of ``b`` sequences of
@@ -278,6 +287,14 @@ class Block(torch.nn.Module):
             fn = getattr(m, "prefetch_weights", None)
             if fn is not None:
                 fn()
+
+
+def _add_norm(norm, x, delta):
+    """``(x + delta, norm(x + delta))``, fused where the norm layer can take a residual."""
+    if hasattr(norm, "_gathered"):
+        return norm(x, residual=delta)
+    s = x + delta
+    return s, norm(s)
 
 
 def zigzag_ranges(cp: int, cp_index: int, seq: int):
@@ -472,28 +489,34 @@ class Decoder(torch.nn.Module):
         n_keep = self._blocks_that_keep(tokens) if (self.training and torch.is_grad_enabled()) else n
         pre = cfg.prefetch and cfg.zero and not cfg.keep_gathered
 
-        def run(x, i):
-            return self.blocks[i](x)
+        def run(x, delta, i):
+            return self.blocks[i](x, delta)
 
         notify = bool(self._block_backward_hooks) and self.training and torch.is_grad_enabled()
         if notify and n and x.requires_grad:
             x.register_hook(self._backward_prefetch(-1, done=0))     # the input of block 0
+        delta = None
         for i in range(n):
             if pre and i + 1 < n:
                 self.blocks[i + 1].prefetch()
             if i < n - n_keep:
-                x = torch.utils.checkpoint.checkpoint(run, x, i, use_reentrant=False)
+                x, delta = torch.utils.checkpoint.checkpoint(run, x, delta, i, use_reentrant=False)
             else:
                 with recompute.enabled():
-                    x = self.blocks[i](x)
-            if x.requires_grad and ((pre and i > 0) or (notify and i + 1 < n)):
-                # the gradient of block i's output is ready when the backward pass of block i + 1 is
-                # complete and that of block i begins: tell the listeners, and start gathering the
+                    x, delta = self.blocks[i](x, delta)
+            if delta.requires_grad and ((pre and i > 0) or (notify and i + 1 < n)):
+                # the gradient of block i's feed-forward output is ready when the backward pass of block
+                # i + 1 is complete and that of block i begins: tell the listeners, and start gathering the
                 # weights of block i - 1
-                x.register_hook(self._backward_prefetch(i - 1 if pre else -1, done=i + 1 if notify and i + 1 < n else None))
+                delta.register_hook(self._backward_prefetch(i - 1 if pre else -1,
+                                                            done=i + 1 if notify and i + 1 < n else None))
         if pre and n and self.training and torch.is_grad_enabled():
             self.blocks[n - 1].prefetch()          # the first block of the backward pass
-        return self.final_norm(x) if self.last_stage else x
+        if not self.last_stage:
+            return x if delta is None else x + delta
+        if delta is None:
+            return self.final_norm(x)
+        return _add_norm(self.final_norm, x, delta)[1]
 
     def loss(self, tokens, targets, scale=None, unit_grad=False):
         """Sum of this worker's token losses times ``scale`` (default: 1 / local

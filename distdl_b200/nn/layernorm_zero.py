@@ -23,10 +23,17 @@ class DistributedLayerNormZero(_ZeroNormBase):
         self._setup_zero_params(P_x, normalized_shape, ("weight", "bias"), elementwise_affine, collect_state, device,
                                 dtype, scale_backward, auto_clear_buffer)
 
-    def forward(self, input):
+    def forward(self, input, residual=None):
+        """With ``residual``: returns ``(input + residual, norm(input + residual))``, the add fused
+        into the norm kernel."""
         if not self.P_x.active:
-            return input
+            return input if residual is None else (input, input)
         w, b = self._gathered()
+        if residual is not None and len(self.normalized_shape) == 1:
+            return ops.add_layer_norm(input, residual, w, b, self.eps)
+        if residual is not None:
+            input = input + residual
+            return input, self.forward(input)
         if len(self.normalized_shape) == 1:
             return ops.layer_norm(input, w, b, self.eps)
         shape = self.normalized_shape

@@ -21,10 +21,18 @@ class DistributedRMSNormZero(_ZeroNormBase):
         self._setup_zero_params(P_x, normalized_shape, names, elementwise_affine, collect_state, device, dtype,
                                 scale_backward, auto_clear_buffer)
 
-    def forward(self, input):
+    def forward(self, input, residual=None):
+        """With ``residual``: returns ``(input + residual, norm(input + residual))``, the add fused
+        into the norm kernel."""
         if not self.P_x.active:
-            return input
+            return input if residual is None else (input, input)
         w, b = self._gathered()
+        if residual is not None:
+            if len(self.normalized_shape) != 1:
+                s = input + residual
+                x = s.reshape(*s.shape[: s.dim() - len(self.normalized_shape)], -1)
+                return s, ops.rms_norm(x, w, self.eps, b).reshape(s.shape)
+            return ops.add_rms_norm(input, residual, w, self.eps, b)
         if len(self.normalized_shape) != 1:
             x = input.reshape(*input.shape[: input.dim() - len(self.normalized_shape)], -1)
             return ops.rms_norm(x, w, self.eps, b).reshape(input.shape)

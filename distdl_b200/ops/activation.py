@@ -86,21 +86,23 @@ def rope_table(seq: int, head_dim: int, theta: float, device) -> torch.Tensor:
 
 class _RopeFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, qkv, table, seq, nheads):
-        # qkv: [tokens, heads_total, hd]; rotates heads [0, nheads) in place.
+    def forward(ctx, qkv, table, seq, nheads, layout):
+        # qkv: contiguous, read as [tokens, heads_total, hd] = layout; rotates heads [0, nheads) in place.
         ctx.mark_dirty(qkv)
-        tokens, ht, hd = qkv.shape
+        tokens, ht, hd = layout
         _native.call("dd_rope", qkv.data_ptr(), table.data_ptr(), tokens, seq, ht, nheads, hd, 1.0, stream_ptr())
-        ctx.table, ctx.seq, ctx.nheads = table, seq, nheads
+        ctx.table, ctx.seq, ctx.nheads, ctx.layout = table, seq, nheads, layout
         return qkv
 
     @staticmethod
     def backward(ctx, d):
+        # the incoming gradient belongs to this node alone (the rotated tensor has one producer and
+        # its consumers' gradients were summed into a fresh tensor): rotate it back in place
         d = d.contiguous()
-        tokens, ht, hd = d.shape
+        tokens, ht, hd = ctx.layout
         _native.call("dd_rope", d.data_ptr(), ctx.table.data_ptr(), tokens, ctx.seq, ht, ctx.nheads, hd, -1.0,
                      stream_ptr())
-        return d, None, None, None
+        return d, None, None, None, None
 
 
 def rope_table_ranges(ranges, head_dim: int, theta: float, device) -> torch.Tensor:
@@ -115,12 +117,29 @@ def rope_table_ranges(ranges, head_dim: int, theta: float, device) -> torch.Tens
 
 
 def rope_(qkv: torch.Tensor, seq: int, nheads: int, theta: float = 500000.0, offset: int = 0,
-          ranges=None) -> torch.Tensor:
+          ranges=None, layout=None) -> torch.Tensor:
     """Applies rotary position embedding (rotate-half convention) to the first
     ``nheads`` heads of ``qkv`` [tokens, heads_total, head_dim]; position of a
     token is ``offset`` plus its index modulo ``seq`` (``offset`` > 0 for a worker that holds a
     later block of a sequence split across workers), or, with ``ranges = ((start, length), ...)``
-    adding up to ``seq``, the positions of those ranges one after the other.  In place on CUDA."""
+    adding up to ``seq``, the positions of those ranges one after the other.  In place on CUDA.
+
+    ``layout = (tokens, heads_total, head_dim)``: ``qkv`` is the projection's own output in
+    whatever shape it has (say ``[batch, seq, heads_total * head_dim]``) and is only READ in that
+    layout.  Prefer this form: rotating a reshaped VIEW in place makes autograd copy the whole
+    gradient twice in the backward pass."""
+    if layout is not None:
+        if use_native(qkv) and qkv.dtype == torch.bfloat16 and layout[2] % 16 == 0 and qkv.is_contiguous():
+            tokens, ht, hd = (int(v) for v in layout)
+            if ranges is not None:
+                table = rope_table_ranges(tuple((int(a), int(n)) for a, n in ranges), hd, theta, qkv.device)
+            else:
+                table = rope_table(offset + seq, hd, theta, qkv.device)
+                if offset:
+                    table = table[offset:]
+            return _RopeFn.apply(qkv, table, seq, nheads, (tokens, ht, hd))
+        shape = qkv.shape
+        return rope_(qkv.reshape(layout), seq, nheads, theta, offset, ranges).reshape(shape)
     tokens, ht, hd = qkv.shape
     if ranges is not None:
         table = rope_table_ranges(tuple((int(a), int(n)) for a, n in ranges), hd, theta, qkv.device)
@@ -129,7 +148,7 @@ def rope_(qkv: torch.Tensor, seq: int, nheads: int, theta: float = 500000.0, off
         if offset:
             table = table[offset:]                            # rows [offset, offset + seq)
     if use_native(qkv) and qkv.dtype == torch.bfloat16 and hd % 16 == 0 and qkv.is_contiguous():
-        return _RopeFn.apply(qkv, table, seq, nheads)
+        return _RopeFn.apply(qkv, table, seq, nheads, (tokens, ht, hd))
     pos = torch.arange(tokens, device=qkv.device) % seq
     cos = table[pos, :, 0].unsqueeze(1)
     sin = table[pos, :, 1].unsqueeze(1)

@@ -38,6 +38,56 @@ def test_norm_fwd_bwd(d, rms):
         _close(b.grad, br.grad)
 
 
+@pytest.mark.parametrize("rms", [True, False])
+def test_add_norm_returns_sum_and_norm_with_the_gradient_of_both(rms):
+    """The residual add fused into the norm: both outputs and, in backward, gradients arriving on both."""
+    from distdl_b200.ops import add_layer_norm, add_rms_norm
+    torch.manual_seed(1)
+    rows, d = 515, 4096
+    x = torch.randn(rows, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(rows, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(d, device="cuda")).to(torch.bfloat16).requires_grad_()
+    b = None if rms else (0.1 * torch.randn(d, device="cuda")).to(torch.bfloat16).requires_grad_()
+    s, y = add_rms_norm(x, r, w, 1e-5) if rms else add_layer_norm(x, r, w, b, 1e-5)
+    ds, dy = torch.randn_like(s), torch.randn_like(y)
+    torch.autograd.backward([s, y], [ds, dy])
+    xr, rr = x.detach().float().requires_grad_(), r.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    sr = (xr + rr).to(torch.bfloat16).float() + (xr + rr - (xr + rr).detach())      # the stored sum is bf16
+    if rms:
+        yr = sr * torch.rsqrt(sr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+    else:
+        br = b.detach().float().requires_grad_()
+        yr = torch.nn.functional.layer_norm(sr, (d,), wr, br, 1e-5)
+    torch.autograd.backward([sr, yr], [ds.float(), dy.float()])
+    _close(s, sr)
+    _close(y, yr)
+    _close(x.grad, xr.grad)
+    _close(r.grad, rr.grad)
+    _close(w.grad, wr.grad)
+    # only the sum is used downstream: the gradient passes through untouched
+    x2 = x.detach().requires_grad_()
+    s2, _ = add_rms_norm(x2, r.detach(), w.detach(), 1e-5)
+    s2.backward(ds)
+    assert torch.equal(x2.grad, ds)
+
+
+def test_rope_on_the_projection_output_rotates_in_place_without_copying_gradients():
+    from distdl_b200.ops import rope_
+    torch.manual_seed(0)
+    b, seq, hq, hk, hd = 2, 64, 4, 2, 128
+    lin = torch.randn(b, seq, (hq + 2 * hk) * hd, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = lin * 1.0                                                     # a non-leaf, like a projection's output
+    ref = rope_(y.detach().clone().reshape(b * seq, hq + 2 * hk, hd), seq, hq + hk, theta=10000.0)
+    out = rope_(y, seq, hq + hk, theta=10000.0, layout=(b * seq, hq + 2 * hk, hd))
+    assert out.shape == lin.shape and torch.equal(out.reshape(ref.shape), ref)
+    g = torch.randn_like(out)
+    out.backward(g)
+    # the adjoint of a rotation is the inverse rotation: rotating the gradient forward again gives g
+    back = rope_(lin.grad.clone().reshape(b * seq, hq + 2 * hk, hd), seq, hq + hk, theta=10000.0)
+    _close(back, g.reshape(back.shape), 1e-2)
+
+
 def test_swiglu_gelu():
     from distdl_b200.ops import gelu, swiglu
     torch.manual_seed(0)
