@@ -49,154 +49,269 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
 }
 
 // ---------------------------------------------------------------------------
-// Norm forward.  RMS: y = x * rstd * w (+b).  LayerNorm: y = (x-mean)*rstd*w + b.
-// One CTA per row iteration; stats[row] = {mean, rstd} (mean = 0 for RMS).
-// Optional residual: x <- x + res is written to xsum before normalising.
+// Norm kernels.  A CTA of 256 threads works on R rows at a time; thread t owns the
+// 8-element vectors t, t + 256, ... (VEC of them, so rows of up to VEC * 2048
+// elements) of every row.  All loads of the R rows are issued before the first
+// use, and one block reduction serves the R rows, so the bytes in flight per SM
+// (what a memory-bound kernel lives on) do not depend on a single row's round trip.
+// Rows are kept as packed bf16 in registers and unpacked where needed: VEC and R
+// are template parameters so that the register count follows the row length.
 // ---------------------------------------------------------------------------
-template <bool RMS>
+constexpr int kNormWarps = kNormThreads / 32;
+
+// Sums of R values over the CTA at once; red: kNormWarps * R floats of shared memory.
+template <int R>
+__device__ __forceinline__ void block_sum_n(float (&v)[R], float* red) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int r = 0; r < R; ++r) v[r] = warp_sum(v[r]);
+  __syncthreads();
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) red[warp * R + r] = v[r];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < kNormWarps; ++w) t += red[w * R + r];
+    v[r] = t;
+  }
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+  return u;
+}
+
+// Norm forward.  RMS: y = x * rstd * w (+b).  LayerNorm: y = (x-mean)*rstd*w + b.
+// stats[row] = {mean, rstd} (mean = 0 for RMS).  Optional residual: x + res is written
+// to xsum first and the (rounded) sum is what gets normalised.
+template <bool RMS, int VEC, int R>
 __global__ void __launch_bounds__(kNormThreads)
 norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                 __nv_bfloat16* __restrict__ xsum, const __nv_bfloat16* __restrict__ w,
                 const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y, float2* __restrict__ stats,
                 int rows, int d, float eps) {
-  __shared__ float red[32];
+  __shared__ float red[kNormWarps * R];
   const int nvec = d >> 3;
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const __nv_bfloat16* xr = x + (size_t)row * d;
-    float v[kMaxVec][8];
-    float s = 0.f, ss = 0.f;
+  const float inv_d = 1.f / (float)d;
+  for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R) {
+    uint4 v[R][VEC];
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
-      const int vi = threadIdx.x + i * kNormThreads;
-      if (vi < nvec) {
-        load8(xr + vi * 8, v[i]);
-        if (res != nullptr) {
-          float r[8];
-          load8(res + (size_t)row * d + vi * 8, r);
+    for (int r = 0; r < R; ++r)
 #pragma unroll
-          for (int j = 0; j < 8; ++j) v[i][j] += r[j];
-          if (xsum != nullptr) {
-            store8(xsum + (size_t)row * d + vi * 8, v[i]);
-            // normalise exactly what was stored
-            float t[8];
-            load8(xsum + (size_t)row * d + vi * 8, t);
+      for (int i = 0; i < VEC; ++i) {
+        const int vi = threadIdx.x + i * kNormThreads;
+        v[r][i] = make_uint4(0, 0, 0, 0);
+        if (vi < nvec && row0 + r < rows)
+          v[r][i] = *reinterpret_cast<const uint4*>(x + (size_t)(row0 + r) * d + vi * 8);
+      }
+    if (res != nullptr) {
+      uint4 q[R][VEC];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[i][j] = t[j];
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          const int vi = threadIdx.x + i * kNormThreads;
+          q[r][i] = make_uint4(0, 0, 0, 0);
+          if (vi < nvec && row0 + r < rows)
+            q[r][i] = *reinterpret_cast<const uint4*>(res + (size_t)(row0 + r) * d + vi * 8);
+        }
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          const int vi = threadIdx.x + i * kNormThreads;
+          float a[8], c[8];
+          unpack8(v[r][i], a);
+          unpack8(q[r][i], c);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a[j] += c[j];
+          v[r][i] = pack8(a);                   // normalise exactly what is stored
+          if (xsum != nullptr && vi < nvec && row0 + r < rows)
+            *reinterpret_cast<uint4*>(xsum + (size_t)(row0 + r) * d + vi * 8) = v[r][i];
+        }
+    }
+    float s[R], ss[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      s[r] = 0.f; ss[r] = 0.f;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        float a[8];
+        unpack8(v[r][i], a);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { s[r] += a[j]; ss[r] += a[j] * a[j]; }
+      }
+    }
+    float mean[R], rstd[R];
+    if (RMS) {
+      block_sum_n<R>(ss, red);
+#pragma unroll
+      for (int r = 0; r < R; ++r) { mean[r] = 0.f; rstd[r] = rsqrtf(ss[r] * inv_d + eps); }
+    } else {
+      block_sum_n<R>(s, red);
+      float sq[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        mean[r] = s[r] * inv_d;
+        sq[r] = 0.f;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          const int vi = threadIdx.x + i * kNormThreads;
+          if (vi < nvec) {
+            float a[8];
+            unpack8(v[r][i], a);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { const float t = a[j] - mean[r]; sq[r] += t * t; }
           }
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { s += v[i][j]; ss += v[i][j] * v[i][j]; }
       }
+      block_sum_n<R>(sq, red);
+#pragma unroll
+      for (int r = 0; r < R; ++r) rstd[r] = rsqrtf(sq[r] * inv_d + eps);
     }
-    float mean = 0.f, rstd;
-    if (RMS) {
-      ss = block_sum(ss, red);
-      rstd = rsqrtf(ss / d + eps);
-    } else {
-      s = block_sum(s, red);
-      mean = s / d;
-      float sq = 0.f;
+    if (threadIdx.x < R && stats != nullptr && row0 + threadIdx.x < rows) {
 #pragma unroll
-      for (int i = 0; i < kMaxVec; ++i) {
-        const int vi = threadIdx.x + i * kNormThreads;
-        if (vi < nvec) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) { float t = v[i][j] - mean; sq += t * t; }
-        }
-      }
-      sq = block_sum(sq, red);
-      rstd = rsqrtf(sq / d + eps);
+      for (int r = 0; r < R; ++r)
+        if (r == (int)threadIdx.x) stats[row0 + r] = make_float2(mean[r], rstd[r]);
     }
-    if (threadIdx.x == 0 && stats != nullptr) stats[row] = make_float2(mean, rstd);
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
+    for (int i = 0; i < VEC; ++i) {
       const int vi = threadIdx.x + i * kNormThreads;
       if (vi < nvec) {
-        float wv[8], o[8];
+        float wv[8], bv[8];
         if (w != nullptr) load8(w + vi * 8, wv);
         else {
 #pragma unroll
           for (int j = 0; j < 8; ++j) wv[j] = 1.f;
         }
+        if (b != nullptr) load8(b + vi * 8, bv);
+        else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * wv[j];
-        if (b != nullptr) {
-          float bv[8];
-          load8(b + vi * 8, bv);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += bv[j];
+          for (int j = 0; j < 8; ++j) bv[j] = 0.f;
         }
-        store8(y + (size_t)row * d + vi * 8, o);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          if (row0 + r < rows) {
+            float a[8], o[8];
+            unpack8(v[r][i], a);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = (a[j] - mean[r]) * rstd[r] * wv[j] + bv[j];
+            store8(y + (size_t)(row0 + r) * d + vi * 8, o);
+          }
+        }
       }
     }
   }
 }
 
-// ---------------------------------------------------------------------------
 // Norm backward.  g = dy*w, xh = (x-mean)*rstd:
 //   RMS: dx = rstd*(g - xh*mean(g*xh));  LN: dx = rstd*(g - mean(g) - xh*mean(g*xh))
 // dw/db partial sums per CTA go to `partial` ([gridDim.x][2][d] fp32, a scratch
-// buffer); norm_bwd_reduce_kernel folds them.  dx may alias dy.
+// buffer); norm_bwd_reduce_kernel folds them.  dx may alias dy.  WANT_DB: the
+// second half of a CTA's slice (db) is only accumulated and written when asked for.
 // If dres_in is given, it is added to dx (gradient of the residual stream).
-// ---------------------------------------------------------------------------
-template <bool RMS>
+template <bool RMS, int VEC, int R, bool WANT_DB>
 __global__ void __launch_bounds__(kNormThreads)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                 const __nv_bfloat16* __restrict__ w, const float2* __restrict__ stats,
                 const __nv_bfloat16* __restrict__ dres_in, __nv_bfloat16* __restrict__ dx,
                 float* __restrict__ partial, int rows, int d) {
-  __shared__ float red[32];
+  __shared__ float red[kNormWarps * R];
   const int nvec = d >> 3;
-  float dw[kMaxVec][8], db[kMaxVec][8];
+  const float inv_d = 1.f / (float)d;
+  float dw[VEC][8], db[WANT_DB ? VEC : 1][8];
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i)
+  for (int i = 0; i < VEC; ++i)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { dw[i][j] = 0.f; db[i][j] = 0.f; }
-
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const float2 st = stats[row];
-    const float mean = st.x, rstd = st.y;
-    float g[kMaxVec][8], xh[kMaxVec][8];
-    float sg = 0.f, sgx = 0.f;
+    for (int j = 0; j < 8; ++j) { dw[i][j] = 0.f; if (WANT_DB) db[i][j] = 0.f; }
+  float wv[VEC][8];
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
-      const int vi = threadIdx.x + i * kNormThreads;
-      if (vi < nvec) {
-        float dyv[8], xv[8], wv[8];
-        load8(dy + (size_t)row * d + vi * 8, dyv);
-        load8(x + (size_t)row * d + vi * 8, xv);
-        if (w != nullptr) load8(w + vi * 8, wv);
-        else {
+  for (int i = 0; i < VEC; ++i) {
+    const int vi = threadIdx.x + i * kNormThreads;
+    if (w != nullptr && vi < nvec) load8(w + vi * 8, wv[i]);
+    else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) wv[j] = 1.f;
-        }
+      for (int j = 0; j < 8; ++j) wv[i][j] = 1.f;
+    }
+  }
+  for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R) {
+    uint4 pdy[R][VEC], px[R][VEC];
+    float mean[R], rstd[R];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          xh[i][j] = (xv[j] - mean) * rstd;
-          g[i][j] = dyv[j] * wv[j];
-          dw[i][j] += dyv[j] * xh[i][j];
-          db[i][j] += dyv[j];
-          sg += g[i][j];
-          sgx += g[i][j] * xh[i][j];
+    for (int r = 0; r < R; ++r) {
+      const bool live = row0 + r < rows;
+      const float2 st = live ? stats[row0 + r] : make_float2(0.f, 0.f);
+      mean[r] = st.x; rstd[r] = st.y;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const int vi = threadIdx.x + i * kNormThreads;
+        pdy[r][i] = make_uint4(0, 0, 0, 0);
+        px[r][i] = make_uint4(0, 0, 0, 0);
+        if (live && vi < nvec) {
+          pdy[r][i] = *reinterpret_cast<const uint4*>(dy + (size_t)(row0 + r) * d + vi * 8);
+          px[r][i] = *reinterpret_cast<const uint4*>(x + (size_t)(row0 + r) * d + vi * 8);
         }
       }
     }
-    sgx = block_sum(sgx, red) / d;
-    if (!RMS) sg = block_sum(sg, red) / d; else sg = 0.f;
+    float sg[R], sgx[R];
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
-      const int vi = threadIdx.x + i * kNormThreads;
-      if (vi < nvec) {
-        float o[8];
+    for (int r = 0; r < R; ++r) {
+      sg[r] = 0.f; sgx[r] = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - sg - xh[i][j] * sgx);
-        if (dres_in != nullptr) {
-          float r[8];
-          load8(dres_in + (size_t)row * d + vi * 8, r);
+      for (int i = 0; i < VEC; ++i) {
+        const int vi = threadIdx.x + i * kNormThreads;
+        if (vi < nvec) {
+          float dyv[8], xv[8];
+          unpack8(pdy[r][i], dyv);
+          unpack8(px[r][i], xv);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += r[j];
+          for (int j = 0; j < 8; ++j) {
+            const float xh = (xv[j] - mean[r]) * rstd[r];
+            const float g = dyv[j] * wv[i][j];
+            dw[i][j] += dyv[j] * xh;
+            if (WANT_DB) db[i][j] += dyv[j];
+            sg[r] += g;
+            sgx[r] += g * xh;
+          }
         }
-        store8(dx + (size_t)row * d + vi * 8, o);
+      }
+    }
+    block_sum_n<R>(sgx, red);
+    if (!RMS) block_sum_n<R>(sg, red);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (row0 + r >= rows) continue;
+      const float mgx = sgx[r] * inv_d, mg = RMS ? 0.f : sg[r] * inv_d;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const int vi = threadIdx.x + i * kNormThreads;
+        if (vi < nvec) {
+          float dyv[8], xv[8], o[8];
+          unpack8(pdy[r][i], dyv);
+          unpack8(px[r][i], xv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float xh = (xv[j] - mean[r]) * rstd[r];
+            o[j] = rstd[r] * (dyv[j] * wv[i][j] - mg - xh * mgx);
+          }
+          if (dres_in != nullptr) {
+            float q[8];
+            load8(dres_in + (size_t)(row0 + r) * d + vi * 8, q);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] += q[j];
+          }
+          store8(dx + (size_t)(row0 + r) * d + vi * 8, o);
+        }
       }
     }
   }
@@ -204,11 +319,14 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     float* pw = partial + (size_t)blockIdx.x * 2 * d;
     float* pb = pw + d;
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
+    for (int i = 0; i < VEC; ++i) {
       const int vi = threadIdx.x + i * kNormThreads;
       if (vi < nvec) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { pw[vi * 8 + j] = dw[i][j]; pb[vi * 8 + j] = db[i][j]; }
+        for (int j = 0; j < 8; ++j) {
+          pw[vi * 8 + j] = dw[i][j];
+          if (WANT_DB) pb[vi * 8 + j] = db[i][j];
+        }
       }
     }
   }
@@ -547,18 +665,61 @@ inline int grid_for(long long work, int threads, int cap_mult = 16) {
 #define CBF(p) reinterpret_cast<const __nv_bfloat16*>(p)
 
 // Number of CTAs the norm backward uses == rows of the partial scratch buffer.
-DD_API int dd_norm_bwd_parts(int rows) { return rows < 148 * 4 ? rows : 148 * 4; }
+// Rows that a CTA takes per iteration for rows of nvec 8-element vectors (see the kernels).
+static inline int norm_rows_per_iter(int d) { return d <= 4096 ? 4 : 2; }
+
+template <bool RMS>
+static void launch_norm_fwd(int grid, cudaStream_t s, const void* x, const void* res, void* xsum, const void* w,
+                            const void* b, void* y, void* stats, int rows, int d, float eps) {
+  if (d <= 2048)
+    norm_fwd_kernel<RMS, 1, 4><<<grid, kNormThreads, 0, s>>>(CBF(x), CBF(res), BF(xsum), CBF(w), CBF(b), BF(y),
+                                                             (float2*)stats, rows, d, eps);
+  else if (d <= 4096)
+    norm_fwd_kernel<RMS, 2, 4><<<grid, kNormThreads, 0, s>>>(CBF(x), CBF(res), BF(xsum), CBF(w), CBF(b), BF(y),
+                                                             (float2*)stats, rows, d, eps);
+  else
+    norm_fwd_kernel<RMS, 4, 2><<<grid, kNormThreads, 0, s>>>(CBF(x), CBF(res), BF(xsum), CBF(w), CBF(b), BF(y),
+                                                             (float2*)stats, rows, d, eps);
+}
+
+template <bool RMS, bool WANT_DB>
+static void launch_norm_bwd(int grid, cudaStream_t s, const void* dy, const void* x, const void* w, const void* stats,
+                            const void* dres, void* dx, float* partial, int rows, int d) {
+  if (d <= 2048)
+    norm_bwd_kernel<RMS, 1, 4, WANT_DB><<<grid, kNormThreads, 0, s>>>(CBF(dy), CBF(x), CBF(w), (const float2*)stats,
+                                                                      CBF(dres), BF(dx), partial, rows, d);
+  else if (d <= 4096)
+    norm_bwd_kernel<RMS, 2, 2, WANT_DB><<<grid, kNormThreads, 0, s>>>(CBF(dy), CBF(x), CBF(w), (const float2*)stats,
+                                                                      CBF(dres), BF(dx), partial, rows, d);
+  else
+    norm_bwd_kernel<RMS, 4, 1, WANT_DB><<<grid, kNormThreads, 0, s>>>(CBF(dy), CBF(x), CBF(w), (const float2*)stats,
+                                                                      CBF(dres), BF(dx), partial, rows, d);
+}
+static void launch_norm_bwd_any(int rms, bool want_db, int grid, cudaStream_t s, const void* dy, const void* x,
+                                const void* w, const void* stats, const void* dres, void* dx, float* partial,
+                                int rows, int d) {
+  if (rms) {
+    if (want_db) launch_norm_bwd<true, true>(grid, s, dy, x, w, stats, dres, dx, partial, rows, d);
+    else launch_norm_bwd<true, false>(grid, s, dy, x, w, stats, dres, dx, partial, rows, d);
+  } else {
+    if (want_db) launch_norm_bwd<false, true>(grid, s, dy, x, w, stats, dres, dx, partial, rows, d);
+    else launch_norm_bwd<false, false>(grid, s, dy, x, w, stats, dres, dx, partial, rows, d);
+  }
+}
+
+// CTAs of the backward kernel = slices of its partial-sum scratch.
+DD_API int dd_norm_bwd_parts(int rows) {
+  const int groups = (rows + 1) / 2;
+  return groups < 148 * 4 ? (groups > 0 ? groups : 1) : 148 * 4;
+}
 
 DD_API int dd_norm_fwd(int rms, const void* x, const void* res, void* xsum, const void* w, const void* b, void* y,
                        void* stats, int rows, int d, float eps, void* stream) {
   if (d % 8 != 0 || d > kNormThreads * kMaxVec * 8 || rows <= 0) return DD_ERR_BAD_ARG;
-  const int grid = rows < 148 * 16 ? rows : 148 * 16;
-  if (rms)
-    norm_fwd_kernel<true><<<grid, kNormThreads, 0, STREAM(stream)>>>(CBF(x), CBF(res), BF(xsum), CBF(w), CBF(b),
-                                                                     BF(y), (float2*)stats, rows, d, eps);
-  else
-    norm_fwd_kernel<false><<<grid, kNormThreads, 0, STREAM(stream)>>>(CBF(x), CBF(res), BF(xsum), CBF(w), CBF(b),
-                                                                      BF(y), (float2*)stats, rows, d, eps);
+  const int groups = (rows + norm_rows_per_iter(d) - 1) / norm_rows_per_iter(d);
+  const int grid = groups < 148 * 8 ? groups : 148 * 8;
+  if (rms) launch_norm_fwd<true>(grid, STREAM(stream), x, res, xsum, w, b, y, stats, rows, d, eps);
+  else launch_norm_fwd<false>(grid, STREAM(stream), x, res, xsum, w, b, y, stats, rows, d, eps);
   return (int)cudaGetLastError();
 }
 
@@ -569,13 +730,8 @@ DD_API int dd_norm_bwd(int rms, const void* dy, const void* x, const void* w, co
                        void* stream) {
   if (d % 8 != 0 || d > kNormThreads * kMaxVec * 8 || rows <= 0) return DD_ERR_BAD_ARG;
   const int grid = dd_norm_bwd_parts(rows);
-  if (rms)
-    norm_bwd_kernel<true><<<grid, kNormThreads, 0, STREAM(stream)>>>(CBF(dy), CBF(x), CBF(w), (const float2*)stats,
-                                                                     CBF(dres), BF(dx), partial, rows, d);
-  else
-    norm_bwd_kernel<false><<<grid, kNormThreads, 0, STREAM(stream)>>>(CBF(dy), CBF(x), CBF(w),
-                                                                      (const float2*)stats, CBF(dres), BF(dx),
-                                                                      partial, rows, d);
+  launch_norm_bwd_any(rms, db != nullptr && partial != nullptr, grid, STREAM(stream), dy, x, w, stats, dres, dx,
+                      partial, rows, d);
   if (partial != nullptr && (dw != nullptr || db != nullptr))
     norm_bwd_reduce_kernel<<<(d + kRedCols - 1) / kRedCols, dim3(kRedCols, kRedLanes), 0, STREAM(stream)>>>(partial, grid, d, dw, db, accumulate);
   return (int)cudaGetLastError();
@@ -729,13 +885,7 @@ DD_API int dd_norm_bwd_noalloc(int rms, const void* dy, const void* x, const voi
   const int grid = rows < kNoAllocParts ? rows : kNoAllocParts;
   // Every CTA overwrites its whole [2][d] slice of the scratch, so nothing left
   // by an earlier call is ever read: no clearing is needed.
-  if (rms)
-    norm_bwd_kernel<true><<<grid, kNormThreads, 0, STREAM(stream)>>>(CBF(dy), CBF(x), CBF(w), (const float2*)stats,
-                                                                     nullptr, BF(dx), partial, rows, d);
-  else
-    norm_bwd_kernel<false><<<grid, kNormThreads, 0, STREAM(stream)>>>(CBF(dy), CBF(x), CBF(w),
-                                                                      (const float2*)stats, nullptr, BF(dx), partial,
-                                                                      rows, d);
+  launch_norm_bwd_any(rms, db != nullptr, grid, STREAM(stream), dy, x, w, stats, nullptr, dx, partial, rows, d);
   if (dw != nullptr || db != nullptr)
     norm_bwd_reduce_kernel<<<(d + kRedCols - 1) / kRedCols, dim3(kRedCols, kRedLanes), 0, STREAM(stream)>>>(partial, grid, d, dw, db, accumulate);
   return (int)cudaGetLastError();

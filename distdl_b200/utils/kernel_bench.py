@@ -86,6 +86,18 @@ def bench_elementwise(rows):
     ms = time_op(lambda: ops.rms_norm(x, w))
     gbs = 2 * x.numel() * 2 / ms / 1e6
     rows.append(f"rms_norm fwd {T}x{d}: {ms:.3f} ms {gbs:.0f} GB/s ({gbs / hbm:.2f} of {kind} {hbm:.0f})")
+    xg = x.clone().requires_grad_()
+    wg = w.clone().requires_grad_()
+    y = ops.rms_norm(xg, wg)
+    dy = torch.randn_like(y)
+    ms = time_op(lambda: torch.autograd.grad(y, (xg, wg), dy, retain_graph=True))
+    gbs = 3 * x.numel() * 2 / ms / 1e6
+    rows.append(f"rms_norm bwd {T}x{d}: {ms:.3f} ms {gbs:.0f} GB/s ({gbs / hbm:.2f} of {kind} {hbm:.0f})")
+    r = torch.randn_like(x)
+    ms = time_op(lambda: ops.add_rms_norm(x, r, w))
+    gbs = 4 * x.numel() * 2 / ms / 1e6
+    rows.append(f"add + rms_norm fwd {T}x{d}: {ms:.3f} ms {gbs:.0f} GB/s ({gbs / hbm:.2f} of {kind} {hbm:.0f})")
+    del xg, wg, y, dy, r
     gu = torch.randn(T, 2 * 7168, device="cuda", dtype=torch.bfloat16)
     ms = time_op(lambda: ops.swiglu(gu))
     gbs = (gu.numel() * 2 * 1.5) / ms / 1e6
