@@ -120,9 +120,11 @@ def activation_report(model):
     per = plan.get("bytes_per_kept_block", 0)
     return (f"policy {plan.get('policy')}: {keep} of {n} blocks keep the outputs of their GEMMs and of attention "
             f"(with its log-sum-exp) for the backward pass, {per / 1e9:.2f} GB per block and micro-batch, "
-            f"{keep * per / 1e9:.1f} GB per GPU; in those blocks only norm outputs and the activation function's "
-            f"output are recomputed and the ZeRO weight shards are gathered again; the other {n - keep} blocks "
-            f"recompute their forward pass")
+            f"{keep * per / 1e9:.1f} GB per GPU; in those blocks " +
+            ("nothing is recomputed (memory to spare: norm and activation outputs are stored as well)"
+             if plan.get("stores_cheap_outputs") else
+             "only norm outputs and the activation function's output are recomputed") +
+            f" and the ZeRO weight shards are gathered again; the other {n - keep} blocks recompute their forward pass")
 
 
 def main():

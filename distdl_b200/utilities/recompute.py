@@ -27,6 +27,7 @@ import weakref
 import torch
 
 _enabled = 0
+_outputs_too = True    # recipes also stand in for cheap operator outputs (not only for gathered weights)
 _targets = []          # open recipes, innermost last
 
 
@@ -34,16 +35,24 @@ def active() -> bool:
     return _enabled > 0
 
 
+def rebuilds_outputs() -> bool:
+    """Inside ``enabled()``: whether outputs of cheap operators (norms, activation functions) are
+    rebuilt in the backward pass too.  A caller with memory to spare turns that off
+    (``enabled(outputs=False)``) and keeps only the re-gathering of ZeRO weights."""
+    return _enabled > 0 and _outputs_too
+
+
 @contextlib.contextmanager
-def enabled(flag: bool = True):
+def enabled(flag: bool = True, outputs: bool = True):
     """Turns recipes on (or, with ``flag=False``, off) for the duration of the block."""
-    global _enabled
-    before = _enabled
-    _enabled = (before + 1) if flag else 0
+    global _enabled, _outputs_too
+    before = (_enabled, _outputs_too)
+    _enabled = (before[0] + 1) if flag else 0
+    _outputs_too = outputs
     try:
         yield
     finally:
-        _enabled = before
+        _enabled, _outputs_too = before
 
 
 class Recipe:
