@@ -48,6 +48,41 @@ def _launch(name, h, ranks, *args):
     h.advance(ranks, steps.value)
 
 
+MC_ONE_SHOT_BYTES = 512 * 1024
+
+
+def _all_reduce_multicast(mc, h, flat, out):
+    """The job-wide all-reduce through the NVLink multicast region: the input is copied into this
+    GPU's copy of the region, one kernel reads the sums with ``multimem.ld_reduce`` (and, for large
+    messages, spreads them with ``multimem.st``)."""
+    symm.require_healthy()
+    es = flat.element_size()
+    half = (mc.nbytes // 2) // 256 * 256
+    n, done = flat.numel(), 0
+    pads = (ctypes.c_void_p * h.world)(*h.pad_ptrs)
+    lib = _native.lib()
+    while done < n:
+        cnt = min(n - done, half // es)
+        nbytes = (cnt * es + 15) // 16 * 16
+        stage = mc.local_tensor(nbytes, flat.dtype)
+        if cnt * es != nbytes:
+            stage[cnt:].zero_()
+        stage[:cnt].copy_(flat[done:done + cnt])
+        one_shot = int(nbytes <= MC_ONE_SHOT_BYTES)
+        direct = cnt * es == nbytes
+        dst = out[done:done + cnt] if direct else torch.empty(nbytes // es, dtype=flat.dtype, device=flat.device)
+        ctas = max(1, min(mc.max_ctas, nbytes // (16 * 512 * 4)))
+        steps = ctypes.c_int(0)
+        _native.launch_count += 1
+        _native.check(lib.dd_mc_allreduce(h.world, h.rank, pads, (mc.steps_done + 1) & 0xFFFFFFFF, 0, half,
+                                          dst.data_ptr(), nbytes, _DT[flat.dtype], one_shot, ctas, ctypes.byref(steps),
+                                          stream_ptr()), "dd_mc_allreduce")
+        mc.steps_done += steps.value
+        if not direct:
+            out[done:done + cnt].copy_(dst[:cnt])
+        done += cnt
+
+
 def all_reduce(x: torch.Tensor, ranks) -> torch.Tensor:
     """Team-wide sum of ``x`` (bf16 or fp32; fp32 accumulation); returns a new tensor."""
     h = symm.heap()
@@ -56,6 +91,10 @@ def all_reduce(x: torch.Tensor, ranks) -> torch.Tensor:
     if flat.dtype not in _DT:
         flat = flat.float()
     out = torch.empty_like(flat)
+    mc = symm.multicast_region() if len(ranks) == h.world else None
+    if mc is not None:
+        _all_reduce_multicast(mc, h, flat, out)
+        return out.view(x.shape).to(x.dtype)
     es = flat.element_size()
     per = 16 // es
     cap = h.staging_bytes // 16 * 16

@@ -217,6 +217,130 @@ def heap_ready() -> bool:
     return _heap is not None
 
 
+# ----------------------------------------------------------------- NVLink multicast region
+_native.declare("dd_mc_supported", [])
+_native.declare("dd_mc_round_size", [c_int, c_size_t, ctypes.POINTER(c_size_t)])
+_native.declare("dd_mc_create", [c_int, c_size_t, _IP])
+_native.declare("dd_mc_import", [c_int, c_size_t, c_int])
+_native.declare("dd_mc_add_device", [])
+_native.declare("dd_mc_bind_and_map", [_PP, _PP])
+_native.declare("dd_mc_teardown", [])
+_native.declare("dd_close_fd", [c_int])
+_native.declare("dd_mc_max_ctas", [])
+_native.declare("dd_mc_allreduce", [c_int, c_int, _PP, ctypes.c_uint, c_size_t, c_size_t, c_void_p, c_size_t, c_int,
+                                    c_int, c_int, _IP, c_void_p])
+
+
+class MulticastRegion:
+    """One buffer per GPU of the job, all bound to one NVLink multicast object: a kernel reads the
+    sum over all GPUs of a word with one ``multimem.ld_reduce`` and writes a word into all copies
+    with one ``multimem.st`` (the reduction runs inside NVSwitch).  Used by the all-reduce of the
+    job-wide team (:func:`distdl_b200.parallel.collectives.all_reduce`).
+
+    Creating it is collective over all processes.  The multicast object is created by rank 0 and
+    reaches the other processes as a file descriptor over a unix socket.  OFF unless asked for
+    (``DISTDL_MULTIMEM=1`` or :func:`enable_multicast`): a process that ends while its memory is
+    still bound disturbs the GPUs of the others, so only jobs whose processes leave together
+    (after :func:`disable_multicast`) should turn it on; tests that end a rank on purpose must not."""
+
+    def __init__(self, heap: "SymmetricHeap", nbytes: int):
+        import socket
+        import tempfile
+        lib = _native.lib()
+        self.heap = heap
+        W, rank = heap.world, heap.rank
+        size = ctypes.c_size_t(0)
+        _native.check(lib.dd_mc_round_size(W, int(nbytes), ctypes.byref(size)), "dd_mc_round_size")
+        self.nbytes = int(size.value)
+        # rank 0 creates the object and hands its descriptor to every other process
+        path = [None]
+        if rank == 0:
+            fd = c_int(-1)
+            _native.check(lib.dd_mc_create(W, self.nbytes, ctypes.byref(fd)), "dd_mc_create")
+            srv = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+            path[0] = os.path.join(tempfile.gettempdir(), f"distdl_b200_mc_{os.getpid()}.sock")
+            if os.path.exists(path[0]):
+                os.unlink(path[0])
+            srv.bind(path[0])
+            srv.listen(W)
+        dist.broadcast_object_list(path, src=0)
+        if rank == 0:
+            srv.settimeout(60.0)
+            for _ in range(W - 1):
+                conn, _addr = srv.accept()
+                socket.send_fds(conn, [b"mc"], [fd.value])
+                conn.recv(1)                       # the peer has imported the object
+                conn.close()
+            srv.close()
+            os.unlink(path[0])
+            lib.dd_close_fd(fd.value)
+        else:
+            cli = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+            cli.settimeout(60.0)
+            cli.connect(path[0])
+            _msg, fds, _flags, _addr = socket.recv_fds(cli, 16, 1)
+            _native.check(lib.dd_mc_import(W, self.nbytes, fds[0]), "dd_mc_import")
+            cli.send(b"k")
+            cli.close()
+            lib.dd_close_fd(fds[0])
+        dist.barrier()
+        _native.check(lib.dd_mc_add_device(), "dd_mc_add_device")
+        dist.barrier()                                 # every device is part of the object
+        local, mc = c_void_p(), c_void_p()
+        _native.check(lib.dd_mc_bind_and_map(ctypes.byref(local), ctypes.byref(mc)), "dd_mc_bind_and_map")
+        self.local_ptr, self.mc_ptr = local.value, mc.value
+        self.steps_done = 0                            # barrier steps consumed by the multicast kernels
+        self.max_ctas = lib.dd_mc_max_ctas()
+        dist.barrier()
+
+    def local_tensor(self, nbytes, dtype=torch.uint8, offset=0):
+        n = nbytes // torch.empty((), dtype=dtype).element_size()
+        return _wrap_device_pointer(self.local_ptr + offset, n, dtype, self.heap.device)
+
+    def close(self):
+        """Collective: every process calls it when no kernel using the region is in flight."""
+        torch.cuda.synchronize()
+        dist.barrier()
+        _native.lib().dd_mc_teardown()
+        dist.barrier()
+
+
+_multicast = None
+
+
+def multicast_supported() -> bool:
+    return bool(_native.lib().dd_mc_supported())
+
+
+def enable_multicast(nbytes: int = 128 * MB):
+    """Creates the job-wide multicast region (collective over all processes; a no-op where the
+    GPUs do not support multicast objects or the job spans more than 8 GPUs).  Returns the region
+    or None."""
+    global _multicast
+    if _multicast is None:
+        h = heap()
+        ok = [None] * h.world
+        dist.all_gather_object(ok, bool(h.world > 1 and h.world <= 8 and multicast_supported()))
+        if all(ok):
+            _multicast = MulticastRegion(h, nbytes)
+    return _multicast
+
+
+def multicast_region():
+    """The region if it exists; created on first use when ``DISTDL_MULTIMEM=1``."""
+    if _multicast is None and os.environ.get("DISTDL_MULTIMEM", "0") == "1" and heap_ready():
+        return enable_multicast()
+    return _multicast
+
+
+def disable_multicast():
+    """Collective tear-down of the multicast region (call before the processes exit)."""
+    global _multicast
+    if _multicast is not None:
+        _multicast.close()
+        _multicast = None
+
+
 class DeviceTimeout(RuntimeError):
     """A kernel gave up a bounded wait for another GPU."""
 

@@ -162,6 +162,44 @@ def check_box_exchange():
     assert _native.read_status()[0] == 0
 
 
+def check_multimem_allreduce():
+    """The job-wide all-reduce through the NVLink multicast region (multimem.ld_reduce / multimem.st)
+    against NCCL.  All comparisons are collected first and the region is torn down on every rank
+    before anything is asserted, so that no rank leaves while its memory is still bound."""
+    from distdl_b200 import _native
+    from distdl_b200.parallel import collectives, symm
+    world, rank = dist.get_world_size(), dist.get_rank()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    symm.heap()
+    region = symm.enable_multicast(32 << 20)
+    if region is None:
+        if rank == 0:
+            print("multicast objects are not supported here: skipped")
+        return
+    problems = []
+    try:
+        for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+            for n in (1024, 16 * 1024 + 8, 300_000, 3_000_000, 9_000_001):
+                torch.manual_seed(100 + rank)
+                x = (torch.rand(n, device=dev) * 2 - 1).to(dtype)
+                want = x.float().clone()
+                dist.all_reduce(want)
+                for rep in range(2):
+                    got = collectives.all_reduce(x, list(range(world))).float()
+                    err = (got - want).abs().max().item() / (want.abs().max().item() + 1e-6)
+                    if not err < tol:
+                        problems.append((str(dtype), n, rep, err))
+        status = _native.read_status()
+        if status[0]:
+            problems.append(("device status", status))
+    except Exception as e:      # noqa: BLE001  (reported after the tear-down)
+        problems.append(("exception", repr(e)))
+    flags = [None] * world
+    dist.all_gather_object(flags, problems)
+    symm.disable_multicast()
+    assert not any(flags), flags
+
+
 def check_zero_grad_accumulate():
     """ZeRO weight gradients on the fast paths must equal the plain path (bf16 reduce-scatter
     by autograd): (1) unsharded fp32 accumulators filled by the weight-gradient GEMMs and
@@ -515,6 +553,8 @@ def main():
         check_context_parallel_decoder()
     if what in ("box", "all"):
         check_box_exchange()
+    if what == "multimem":
+        check_multimem_allreduce()
     if what == "activation_policies":
         check_activation_policies()
     if what == "pipeline":

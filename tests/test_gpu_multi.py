@@ -58,3 +58,8 @@ def test_pipelined_decoder_on_gpus():
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 def test_halo_exchange_and_repartition_in_one_kernel():
     _run("box", min(_ngpu(), 8))
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_all_reduce_through_the_multicast_region():
+    _run("multimem", min(_ngpu(), 8))
