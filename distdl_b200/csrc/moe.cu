@@ -99,6 +99,117 @@ __global__ void moe_pair_dot_kernel(const __nv_bfloat16* __restrict__ a, const _
   if (lane == 0) out[p] = acc;
 }
 
+// ---------------------------------------------------------------------------
+// Router: softmax over the experts, top-k, renormalised weights, slot assignment
+// and the column sums of the probabilities (for the load-balancing loss) in ONE
+// kernel; one thread per token, the E (<= EMAX) logits of a token in registers.
+//   p = softmax(l);  S = top-k of p;  w_i = p_i / sum_{j in S} p_j  (i in S)
+// Outputs per pair (t, c): ids, w, slot (slot = arrival order at the expert, -1
+// beyond the capacity).  counters[e] ends as the number of pairs routed to e,
+// prob_sum[e] as sum_t p[t, e].  counters and prob_sum must be zero on entry.
+// ---------------------------------------------------------------------------
+template <int EMAX>
+__global__ void __launch_bounds__(256)
+moe_router_fwd_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int tokens, int E, int k, int capacity,
+                      int* __restrict__ ids, float* __restrict__ w, int* __restrict__ slot,
+                      int* __restrict__ counters, float* __restrict__ prob_sum) {
+  __shared__ float s_sum[EMAX];
+  for (int e = threadIdx.x; e < EMAX; e += blockDim.x) s_sum[e] = 0.f;
+  __syncthreads();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < tokens) {
+    float p[EMAX];
+    float m = -INFINITY;
+#pragma unroll
+    for (int e = 0; e < EMAX; ++e) {
+      p[e] = e < E ? __bfloat162float(logits[(size_t)t * ld + e]) : -INFINITY;
+      m = fmaxf(m, p[e]);
+    }
+    float z = 0.f;
+#pragma unroll
+    for (int e = 0; e < EMAX; ++e) { p[e] = e < E ? __expf(p[e] - m) : 0.f; z += p[e]; }
+    const float inv = 1.f / z;
+#pragma unroll
+    for (int e = 0; e < EMAX; ++e) {
+      p[e] *= inv;
+      if (e < E) atomicAdd(&s_sum[e], p[e]);
+    }
+    unsigned long long taken = 0ull;
+    float wsel[8];
+    int isel[8];
+    float zs = 0.f;
+    for (int c = 0; c < k; ++c) {
+      float best = -1.f;
+      int bi = 0;
+#pragma unroll
+      for (int e = 0; e < EMAX; ++e)
+        if (e < E && !((taken >> e) & 1ull) && p[e] > best) { best = p[e]; bi = e; }
+      taken |= 1ull << bi;
+      wsel[c] = best; isel[c] = bi; zs += best;
+    }
+    const float invs = 1.f / zs;
+    for (int c = 0; c < k; ++c) {
+      const int pr = t * k + c;
+      ids[pr] = isel[c];
+      w[pr] = wsel[c] * invs;
+      const int sidx = atomicAdd(counters + isel[c], 1);
+      slot[pr] = sidx < capacity ? sidx : -1;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x)
+    if (s_sum[e] != 0.f) atomicAdd(prob_sum + e, s_sum[e]);
+}
+
+// dl_i = p_i (c_i - sum_e c_e p_e)  +  [i in S] w_i (dw_i - sum_{j in S} w_j dw_j)
+// with c = gradient arriving on prob_sum and dw on the pair weights; columns >= E get 0.
+template <int EMAX>
+__global__ void __launch_bounds__(256)
+moe_router_bwd_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int tokens, int E, int k,
+                      const int* __restrict__ ids, const float* __restrict__ w, const float* __restrict__ dw,
+                      const float* __restrict__ coef, __nv_bfloat16* __restrict__ dlogits) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= tokens) return;
+  float p[EMAX];
+  float m = -INFINITY;
+#pragma unroll
+  for (int e = 0; e < EMAX; ++e) {
+    p[e] = e < E ? __bfloat162float(logits[(size_t)t * ld + e]) : -INFINITY;
+    m = fmaxf(m, p[e]);
+  }
+  float z = 0.f;
+#pragma unroll
+  for (int e = 0; e < EMAX; ++e) { p[e] = e < E ? __expf(p[e] - m) : 0.f; z += p[e]; }
+  const float inv = 1.f / z;
+  float cp = 0.f;
+#pragma unroll
+  for (int e = 0; e < EMAX; ++e) {
+    p[e] *= inv;
+    if (e < E && coef != nullptr) cp += coef[e] * p[e];
+  }
+  float g[EMAX];
+#pragma unroll
+  for (int e = 0; e < EMAX; ++e) g[e] = (e < E && coef != nullptr) ? p[e] * (coef[e] - cp) : 0.f;
+  if (dw != nullptr) {
+    float wd = 0.f;
+    for (int c = 0; c < k; ++c) wd += w[t * k + c] * dw[t * k + c];
+    for (int c = 0; c < k; ++c) {
+      const int i = ids[t * k + c];
+      const float add = w[t * k + c] * (dw[t * k + c] - wd);
+#pragma unroll
+      for (int e = 0; e < EMAX; ++e)
+        if (e == i) g[e] += add;
+    }
+  }
+  for (int e = 0; e < ld; ++e) {
+    float v = 0.f;
+#pragma unroll
+    for (int q = 0; q < EMAX; ++q)
+      if (q == e) v = g[q];
+    dlogits[(size_t)t * ld + e] = __float2bfloat16(v);
+  }
+}
+
 inline int grid_for(long long work, int threads) {
   long long b = (work + threads - 1) / threads;
   if (b > 148 * 16) b = 148 * 16;
@@ -137,5 +248,42 @@ DD_API int dd_moe_pair_dot(const void* a, const void* b, const int* ids, const i
   if (d % 8) return DD_ERR_BAD_ARG;
   if (npairs <= 0) return DD_OK;
   moe_pair_dot_kernel<<<(npairs + 7) / 8, 256, 0, S(stream)>>>(CBF(a), CBF(b), ids, slot, out, npairs, k, capacity, d);
+  return (int)cudaGetLastError();
+}
+
+// logits [tokens, ld] bf16 (columns >= E are padding); E <= 64, k <= 8, k <= E.
+DD_API int dd_moe_router_fwd(const void* logits, int ld, int tokens, int E, int k, int capacity, int* ids, float* w,
+                             int* slot, int* counters, float* prob_sum, void* stream) {
+  if (E < 1 || E > 64 || k < 1 || k > 8 || k > E || ld < E) return DD_ERR_BAD_ARG;
+  if (tokens <= 0) return DD_OK;
+  const int grid = (tokens + 255) / 256;
+  if (E <= 8)
+    moe_router_fwd_kernel<8><<<grid, 256, 0, S(stream)>>>(CBF(logits), ld, tokens, E, k, capacity, ids, w, slot,
+                                                          counters, prob_sum);
+  else if (E <= 16)
+    moe_router_fwd_kernel<16><<<grid, 256, 0, S(stream)>>>(CBF(logits), ld, tokens, E, k, capacity, ids, w, slot,
+                                                           counters, prob_sum);
+  else if (E <= 32)
+    moe_router_fwd_kernel<32><<<grid, 256, 0, S(stream)>>>(CBF(logits), ld, tokens, E, k, capacity, ids, w, slot,
+                                                           counters, prob_sum);
+  else
+    moe_router_fwd_kernel<64><<<grid, 256, 0, S(stream)>>>(CBF(logits), ld, tokens, E, k, capacity, ids, w, slot,
+                                                           counters, prob_sum);
+  return (int)cudaGetLastError();
+}
+// dw [tokens * k] and coef [E] may each be null (no gradient from that output).
+DD_API int dd_moe_router_bwd(const void* logits, int ld, int tokens, int E, int k, const int* ids, const float* w,
+                             const float* dw, const float* coef, void* dlogits, void* stream) {
+  if (E < 1 || E > 64 || k < 1 || k > 8 || ld < E) return DD_ERR_BAD_ARG;
+  if (tokens <= 0) return DD_OK;
+  const int grid = (tokens + 255) / 256;
+  if (E <= 8)
+    moe_router_bwd_kernel<8><<<grid, 256, 0, S(stream)>>>(CBF(logits), ld, tokens, E, k, ids, w, dw, coef, BF(dlogits));
+  else if (E <= 16)
+    moe_router_bwd_kernel<16><<<grid, 256, 0, S(stream)>>>(CBF(logits), ld, tokens, E, k, ids, w, dw, coef, BF(dlogits));
+  else if (E <= 32)
+    moe_router_bwd_kernel<32><<<grid, 256, 0, S(stream)>>>(CBF(logits), ld, tokens, E, k, ids, w, dw, coef, BF(dlogits));
+  else
+    moe_router_bwd_kernel<64><<<grid, 256, 0, S(stream)>>>(CBF(logits), ld, tokens, E, k, ids, w, dw, coef, BF(dlogits));
   return (int)cudaGetLastError();
 }

@@ -144,16 +144,13 @@ class MoEFeedForward(torch.nn.Module):
         b, s, d = x.shape
         T = b * s
         xt = x.reshape(T, d)
-        logits = self.router(x).reshape(T, -1)[:, :E].float()
-        probs = torch.softmax(logits, dim=-1)
-        topw, topi = probs.topk(k, dim=-1)
-        topw = topw / topw.sum(-1, keepdim=True)
-        ids = topi.to(torch.int32).reshape(-1).contiguous()
+        logits = self.router(x).reshape(T, -1)
         C = int(math.ceil(cfg.capacity_factor * T * k / E / 8.0) * 8)
-        slot, counts = moe_ops.assign_slots(ids, E, C)
+        # softmax, top-k, renormalisation, slot assignment and the probability sums: one kernel
+        topw, prob_sum, ids, slot, counts = moe_ops.route(logits, E, k, C)
         # load-balancing auxiliary loss (fraction routed x mean router probability)
         frac = counts.float() / float(T * k)
-        self.aux_loss = E * (frac.detach() * probs.mean(0)).sum()
+        self.aux_loss = E * (frac.detach() * (prob_sum / float(T))).sum()
         self.last_dropped = (slot < 0).sum()
         P, El = self.ep, self.e_local
         peer = None

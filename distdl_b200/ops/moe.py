@@ -18,6 +18,64 @@ _native.declare("dd_moe_gather_rows", [_v, _v, _v, _v, _v, _i, _i, _i, _i, _v])
 _native.declare("dd_moe_pair_dot", [_v, _v, _v, _v, _v, _i, _i, _i, _i, _v])
 
 
+_native.declare("dd_moe_router_fwd", [_v, _i, _i, _i, _i, _i, _v, _v, _v, _v, _v, _v])
+_native.declare("dd_moe_router_bwd", [_v, _i, _i, _i, _i, _v, _v, _v, _v, _v, _v])
+
+
+class _RouterFn(torch.autograd.Function):
+    """Softmax over the experts, top-k, renormalised weights, slot assignment and the column sums
+    of the probabilities in one kernel; one more kernel for the backward pass."""
+
+    @staticmethod
+    def forward(ctx, logits, E, k, capacity):
+        T, ld = logits.shape
+        dev = logits.device
+        ids = torch.empty(T * k, dtype=torch.int32, device=dev)
+        w = torch.empty(T, k, dtype=torch.float32, device=dev)
+        slot = torch.empty(T * k, dtype=torch.int32, device=dev)
+        counts = torch.zeros(E, dtype=torch.int32, device=dev)
+        prob_sum = torch.zeros(E, dtype=torch.float32, device=dev)
+        _native.call("dd_moe_router_fwd", logits.data_ptr(), ld, T, E, k, capacity, ids.data_ptr(), w.data_ptr(),
+                     slot.data_ptr(), counts.data_ptr(), prob_sum.data_ptr(), stream_ptr())
+        ctx.save_for_backward(logits, ids, w)
+        ctx.cfg = (E, k)
+        ctx.mark_non_differentiable(ids, slot, counts)
+        ctx.set_materialize_grads(False)
+        return w, prob_sum, ids, slot, counts
+
+    @staticmethod
+    def backward(ctx, dw, dprob, _dids, _dslot, _dcounts):
+        logits, ids, w = ctx.saved_tensors
+        E, k = ctx.cfg
+        T, ld = logits.shape
+        dlogits = torch.empty_like(logits)
+        dwc = None if dw is None else dw.float().contiguous()
+        dpc = None if dprob is None else dprob.float().contiguous()
+        _native.call("dd_moe_router_bwd", logits.data_ptr(), ld, T, E, k, ids.data_ptr(), w.data_ptr(), ptr(dwc),
+                     ptr(dpc), dlogits.data_ptr(), stream_ptr())
+        return dlogits, None, None, None
+
+
+def route(logits: torch.Tensor, num_experts: int, k: int, capacity: int):
+    """Top-k routing of ``logits [tokens, >= num_experts]`` (extra columns are padding).
+
+    Returns ``(weights [tokens, k] fp32, prob_sum [E] fp32, ids [tokens * k] int32, slot
+    [tokens * k] int32, counts [E] int32)``: the renormalised softmax weights of the chosen
+    experts, the sum over tokens of the softmax probabilities (for the load-balancing loss), the
+    chosen experts, each pair's slot in its expert's capacity buffer (-1 = dropped) and the number
+    of pairs routed to every expert.  ``weights`` and ``prob_sum`` carry gradients back to
+    ``logits``."""
+    E = num_experts
+    if use_native(logits) and logits.dtype == torch.bfloat16 and E <= 64 and k <= 8 and logits.is_contiguous():
+        return _RouterFn.apply(logits, E, k, capacity)
+    probs = torch.softmax(logits[:, :E].float(), dim=-1)
+    topw, topi = probs.topk(k, dim=-1)
+    topw = topw / topw.sum(-1, keepdim=True)
+    ids = topi.to(torch.int32).reshape(-1).contiguous()
+    slot, counts = assign_slots(ids, E, capacity)
+    return topw, probs.sum(0), ids, slot, counts
+
+
 def assign_slots(ids: torch.Tensor, num_experts: int, capacity: int):
     """ids [pairs] int32 -> (slot [pairs] int32 with -1 for dropped pairs, counts [E] int32)."""
     flat = ids.reshape(-1).to(torch.int32).contiguous()

@@ -53,3 +53,41 @@ def test_moe_routing_kernels_match_torch():
     assert (x.grad.float() - gx_ref).abs().max().item() < 3e-2 * gx_ref.abs().max().item()
     gw_ref = (2 * x.detach().float() * g.float()).sum(1, keepdim=True) * keep
     assert (w.grad - gw_ref).abs().max().item() < 3e-2 * gw_ref.abs().max().item() + 1e-3
+
+
+@pytest.mark.parametrize("E,k,ld", [(8, 2, 8), (6, 1, 8), (16, 4, 16), (40, 8, 40), (64, 2, 64)])
+def test_router_kernel_matches_softmax_topk_renormalisation(E, k, ld):
+    """The one-kernel router (softmax, top-k, renormalised weights, slots, probability sums) and its
+    backward kernel against the same computation written with PyTorch ops in fp32."""
+    from distdl_b200.ops import moe
+    torch.manual_seed(E * 10 + k)
+    T, C = 777, 10_000
+    logits = (torch.randn(T, ld, device="cuda") * 2).to(torch.bfloat16).requires_grad_()
+    w, prob_sum, ids, slot, counts = moe.route(logits, E, k, C)
+    lr = logits.detach().float()[:, :E].requires_grad_()
+    probs = torch.softmax(lr, dim=-1)
+    topw, topi = probs.topk(k, dim=-1)
+    topw = topw / topw.sum(-1, keepdim=True)
+    assert torch.equal(ids.reshape(T, k).long().sort(-1).values, topi.sort(-1).values)
+    order = ids.reshape(T, k).long().argsort(-1), topi.argsort(-1)
+    assert torch.allclose(w.gather(1, order[0]), topw.gather(1, order[1]), atol=1e-5)
+    assert torch.allclose(prob_sum, probs.sum(0), rtol=1e-4, atol=1e-3)
+    assert torch.equal(counts.long(), torch.bincount(ids.long(), minlength=E))
+    # every pair has its own slot within its expert (nothing dropped at this capacity)
+    assert (slot >= 0).all()
+    key = ids.long() * C + slot.long()
+    assert key.unique().numel() == key.numel()
+    # gradients through the weights and through the probability sums (the auxiliary loss)
+    gw = torch.randn(T, k, device="cuda")
+    gp = torch.randn(E, device="cuda")
+    (w * gw).sum().add((prob_sum * gp).sum()).backward()
+    gw_ref = torch.zeros_like(gw).scatter(1, order[1], gw.gather(1, order[0]))     # same pairing as the kernel's order
+    ((topw * gw_ref).sum() + (probs.sum(0) * gp).sum()).backward()
+    got = logits.grad.float()
+    assert torch.allclose(got[:, :E], lr.grad, atol=2e-2, rtol=2e-2), (got[:, :E] - lr.grad).abs().max()
+    assert (got[:, E:] == 0).all()
+    # a small capacity drops the late arrivals only
+    _, _, ids2, slot2, _ = moe.route(logits.detach(), E, k, 8)
+    for e in range(min(E, 4)):
+        kept = (slot2[ids2 == e] >= 0).sum().item()
+        assert kept == min(8, int((ids2 == e).sum()))
