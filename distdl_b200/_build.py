@@ -52,8 +52,8 @@ def _headers_digest() -> str:
     return h.hexdigest()
 
 
-def _compile_one(src: str, verbose: bool, hdr: str, force: bool) -> str:
-    obj = os.path.join(OBJ_DIR, src.rsplit(".", 1)[0] + ".o")
+def _compile_one(src: str, verbose: bool, hdr: str, force: bool, debug: bool = False) -> str:
+    obj = os.path.join(OBJ_DIR + ("_debug" if debug else ""), src.rsplit(".", 1)[0] + ".o")
     stamp = obj + ".stamp"
     with open(os.path.join(CSRC, src), "rb") as fh:
         digest = hashlib.sha256(fh.read() + hdr.encode()).hexdigest()
@@ -61,7 +61,8 @@ def _compile_one(src: str, verbose: bool, hdr: str, force: bool) -> str:
         with open(stamp) as fh:
             if fh.read().strip() == digest:
                 return obj
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
+    cmd = [_nvcc(), *NVCC_FLAGS, *(["-DDD_BOUNDS_CHECK"] if debug else []), "-I", CSRC, "-c", os.path.join(CSRC, src),
+           "-o", obj]
     if src.endswith(".cpp"):
         cmd.insert(1, "-x")
         cmd.insert(2, "cu")
@@ -77,24 +78,28 @@ def _compile_one(src: str, verbose: bool, hdr: str, force: bool) -> str:
     return obj
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compiles what changed and links the shared library; returns its path."""
-    os.makedirs(OBJ_DIR, exist_ok=True)
+def build(force: bool = False, verbose: bool = False, debug: bool = False) -> str:
+    """Compiles what changed and links the shared library; returns its path.  ``debug`` builds the
+    bounds-checking variant (``-DDD_BOUNDS_CHECK``: kernels that address tensors through computed
+    offsets check every address against the tensor's storage, record a violation in the status
+    record and skip the access) as ``libdistdl_b200_debug.so``; ``DISTDL_DEBUG_LIB=1`` loads it."""
+    os.makedirs(OBJ_DIR + ("_debug" if debug else ""), exist_ok=True)
     os.makedirs(OUT_DIR, exist_ok=True)
     hdr = _headers_digest()
     srcs = _sources()
+    lib_path = LIB_PATH.replace(".so", "_debug.so") if debug else LIB_PATH
     with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
-        objs = list(ex.map(lambda s: _compile_one(s, verbose, hdr, force), srcs))
+        objs = list(ex.map(lambda s: _compile_one(s, verbose, hdr, force, debug), srcs))
     newest = max(os.path.getmtime(o) for o in objs)
-    if force or not os.path.exists(LIB_PATH) or os.path.getmtime(LIB_PATH) < newest:
-        cmd = [_nvcc(), "-shared", "-o", LIB_PATH, *objs, "-Xcompiler", "-fopenmp", "-lgomp",
+    if force or not os.path.exists(lib_path) or os.path.getmtime(lib_path) < newest:
+        cmd = [_nvcc(), "-shared", "-o", lib_path, *objs, "-Xcompiler", "-fopenmp", "-lgomp",
                "-gencode", "arch=compute_100a,code=sm_100a"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv, debug="--debug" in sys.argv)
     print(path)

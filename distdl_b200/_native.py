@@ -14,6 +14,9 @@ import threading
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "_C", "libdistdl_b200.so")
+# DISTDL_DEBUG_LIB=1 loads the bounds-checking build instead (python -m distdl_b200._build --debug)
+if os.environ.get("DISTDL_DEBUG_LIB", "0") == "1":
+    LIB_PATH = os.path.join(_HERE, "_C", "libdistdl_b200_debug.so")
 
 _lock = threading.Lock()
 _lib = None
@@ -64,6 +67,7 @@ _STATUS_NAMES = {
     1003: "size beyond the supported maximum",
     1004: "CUDA driver call failed",
     1005: "bounded device-side wait timed out",
+    1006: "address outside the tensor's storage (bounds-checking build)",
 }
 
 # Counts launches of this library's kernels (every entry point launches at

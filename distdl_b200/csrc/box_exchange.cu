@@ -58,6 +58,8 @@ struct Box {
   char* base;
   long long s[3];
   int n[4];
+  char* lo;                    // the tensor's storage [lo, hi): checked by the bounds-checking build
+  char* hi;
 };
 
 struct BoxItem {
@@ -170,6 +172,25 @@ __host__ __device__ __forceinline__ void move_unit(char* dst, char* src, int uni
   }
 }
 
+// Bounds-checking build (-DDD_BOUNDS_CHECK, `python -m distdl_b200._build --debug`): an address
+// outside the tensor's storage is recorded in the status record (code 1006, the offending unit
+// index) and the access is skipped, instead of faulting the GPU.
+__device__ __forceinline__ bool in_bounds(const Box& x, const char* p, int unit, StatusRecord* st,
+                                          unsigned long long g) {
+#ifdef DD_BOUNDS_CHECK
+  if (x.lo != nullptr && (p < x.lo || p + unit > x.hi)) {
+    if (st != nullptr && atomicCAS(&st->code, 0, DD_ERR_BOUNDS) == 0) {
+      st->where = 320;
+      st->expected = (int)(g & 0x7fffffff);
+      st->seen = (int)(g >> 31);
+      __threadfence_system();
+    }
+    return false;
+  }
+#endif
+  return true;
+}
+
 __device__ __forceinline__ void red_release_sys_u32(uint32_t* p) {
   asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p) : "memory");
 }
@@ -260,19 +281,24 @@ __global__ void __launch_bounds__(kBoxThreads) box_exchange_kernel(const __grid_
           if (!cta_wait<true>(A.pad[A.me] + PAD_BOX_CONSUMED + buf * 8 + m.peer, use, A.status, 310, &fail)) return;
           char* dst = A.inbox[m.peer] + (unsigned long long)A.me * A.slot_bytes + (unsigned long long)buf * A.chunk_bytes - c_lo;
           const int unit = m.unit;
-          for (unsigned long long g = lo / unit + threadIdx.x; g < hi / unit; g += kBoxThreads)
-            move_unit(dst + g * unit, unit_addr(m.a, unit, g), unit, kAddNone, m.clear_source != 0);
+          for (unsigned long long g = lo / unit + threadIdx.x; g < hi / unit; g += kBoxThreads) {
+            char* src = unit_addr(m.a, unit, g);
+            if (in_bounds(m.a, src, unit, A.status, g)) move_unit(dst + g * unit, src, unit, kAddNone, m.clear_source != 0);
+          }
         } else if (m.kind == kRecv) {
           if (!cta_wait<true>(A.pad[A.me] + PAD_BOX_DELIVERED + buf * 8 + m.peer, use + 1, A.status, 311, &fail)) return;
           char* src = A.inbox[A.me] + (unsigned long long)m.peer * A.slot_bytes + (unsigned long long)buf * A.chunk_bytes - c_lo;
           const int unit = m.unit;
           if (unit == 16 && m.add == kAddNone) {
-            for (unsigned long long g = lo / 16 + threadIdx.x; g < hi / 16; g += kBoxThreads)
-              *reinterpret_cast<uint4*>(unit_addr(m.a, 16, g)) = ld_cg16(src + g * 16);
+            for (unsigned long long g = lo / 16 + threadIdx.x; g < hi / 16; g += kBoxThreads) {
+              char* to = unit_addr(m.a, 16, g);
+              if (in_bounds(m.a, to, 16, A.status, g)) *reinterpret_cast<uint4*>(to) = ld_cg16(src + g * 16);
+            }
           } else if (unit == 16) {
             for (unsigned long long g = lo / 16 + threadIdx.x; g < hi / 16; g += kBoxThreads) {
               uint4 v = ld_cg16(src + g * 16);
-              move_unit(unit_addr(m.a, 16, g), reinterpret_cast<char*>(&v), 16, m.add, false);
+              char* to = unit_addr(m.a, 16, g);
+              if (in_bounds(m.a, to, 16, A.status, g)) move_unit(to, reinterpret_cast<char*>(&v), 16, m.add, false);
             }
           } else {
             for (unsigned long long g = lo / unit + threadIdx.x; g < hi / unit; g += kBoxThreads) {
@@ -285,16 +311,20 @@ __global__ void __launch_bounds__(kBoxThreads) box_exchange_kernel(const __grid_
                 case 4: v = *reinterpret_cast<const volatile uint32_t*>(sp); break;
                 default: v = *reinterpret_cast<const volatile uint64_t*>(sp); break;
               }
-              move_unit(unit_addr(m.a, unit, g), reinterpret_cast<char*>(&v), unit, m.add, false);
+              char* to = unit_addr(m.a, unit, g);
+              if (in_bounds(m.a, to, unit, A.status, g)) move_unit(to, reinterpret_cast<char*>(&v), unit, m.add, false);
             }
           }
         } else {
           // local copy: the two sides may have different units; walk in the smaller one
           const int unit = m.unit < m.unit_b ? m.unit : m.unit_b;
           const int ra = m.unit / unit, rb = m.unit_b / unit;
-          for (unsigned long long g = lo / unit + threadIdx.x; g < hi / unit; g += kBoxThreads)
-            move_unit(unit_addr(m.b, m.unit_b, g / rb) + (g % rb) * unit, unit_addr(m.a, m.unit, g / ra) + (g % ra) * unit,
-                      unit, kAddNone, false);
+          for (unsigned long long g = lo / unit + threadIdx.x; g < hi / unit; g += kBoxThreads) {
+            char* to = unit_addr(m.b, m.unit_b, g / rb) + (g % rb) * unit;
+            char* from = unit_addr(m.a, m.unit, g / ra) + (g % ra) * unit;
+            if (in_bounds(m.b, to, unit, A.status, g) && in_bounds(m.a, from, unit, A.status, g))
+              move_unit(to, from, unit, kAddNone, false);
+          }
         }
         // the piece is done; whoever completes the chunk signals the other GPU
         __syncthreads();
@@ -324,6 +354,11 @@ unsigned* g_box_scratch[64] = {nullptr};   // per device: [0] progress, [16..] p
 
 }  // namespace
 
+#ifdef DD_BOUNDS_CHECK
+DD_API int dd_bounds_checked() { return 1; }
+#else
+DD_API int dd_bounds_checked() { return 0; }
+#endif
 DD_API int dd_box_max_items() { return kBoxMaxItems; }
 DD_API int dd_box_bufs() { return kBoxBufs; }
 DD_API int dd_box_piece_bytes() { return (int)kPieceBytes; }

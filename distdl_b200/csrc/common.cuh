@@ -22,6 +22,7 @@ enum dd_status : int {
   DD_ERR_TOO_LARGE = 1003,
   DD_ERR_DRIVER = 1004,
   DD_ERR_TIMEOUT = 1005,
+  DD_ERR_BOUNDS = 1006,
 };
 
 namespace dd {

@@ -44,7 +44,14 @@ MAX_PEERS = 8
 
 
 class _Box(ctypes.Structure):
-    _fields_ = [("base", _v), ("s", ctypes.c_longlong * 3), ("n", _i * 4)]
+    _fields_ = [("base", _v), ("s", ctypes.c_longlong * 3), ("n", _i * 4), ("lo", _v), ("hi", _v)]
+
+
+def _storage_bounds(t):
+    """[lo, hi) of the tensor's storage: what the bounds-checking build of the library verifies
+    every address against."""
+    st = t.untyped_storage()
+    return st.data_ptr(), st.data_ptr() + st.nbytes()
 
 
 class BoxItem(ctypes.Structure):
@@ -278,6 +285,7 @@ class BoxPlan:
                     it.a.base = bound[slot].data_ptr() + off
                     it.a.n[:] = n
                     it.a.s[:] = s
+                    it.a.lo, it.a.hi = _storage_bounds(bound[slot])
                     it.unit = unit
                     it.bytes, it.kind, it.peer, it.phase, it.clear_source, it.add = nbytes, kind, peer, phase, clear, add
                     if kind == LOCAL:
@@ -285,6 +293,7 @@ class BoxPlan:
                         it.b.base = bound[d_slot].data_ptr() + d_off
                         it.b.n[:] = n2
                         it.b.s[:] = s2
+                        it.b.lo, it.b.hi = _storage_bounds(bound[d_slot])
                         it.unit_b = unit2
                     elif kind == SEND:
                         it.first_seq = st.sent[peer] & 0xFFFFFFFF

@@ -43,6 +43,8 @@ _native.declare("dd_alltoall", _TEAM + [c_void_p, c_size_t, _IP, c_void_p])
 _native.declare("dd_team_barrier", _TEAM + [_IP, c_void_p])
 
 SIGNAL_PAD_BYTES = 64 * 1024
+GUARD_BYTES = 4096            # guard zone after every region of the staging buffer
+GUARD_PATTERN = 0xA5
 MB = 1 << 20
 # Regions of the staging buffer (same layout on every process).
 REGION_SIZES = (("coll", None), ("ag_shard", 128 * MB), ("rs0", 224 * MB), ("rs1", 224 * MB), ("misc", 4 * MB),
@@ -63,11 +65,14 @@ class SymmetricHeap:
             raise RuntimeError(f"the native transport handles up to {self.max_peers} GPUs of one node")
         self.staging_bytes = int(staging_bytes)
         self.regions = {}
+        # every region is followed by a guard zone that holds a fixed pattern: a kernel that runs past
+        # the end of its region (on this GPU or, through the peer mapping, on another one) leaves a
+        # trace that check_canaries() finds
         off = 0
         for name, size in REGION_SIZES:
             size = self.staging_bytes if size is None else size
             self.regions[name] = (off, size)
-            off += size
+            off += size + GUARD_BYTES
         self.total_bytes = off
         self.device = torch.device("cuda", torch.cuda.current_device())
         self._local_buf, self._local_pad = c_void_p(), c_void_p()
@@ -93,7 +98,21 @@ class SymmetricHeap:
         # barrier steps consumed so far with every peer (flags are counters)
         self.steps_done = [0] * self.world
         self.poisoned = False
+        for name, (roff, size) in self.regions.items():
+            _wrap_device_pointer(self._local_buf.value + roff + size, GUARD_BYTES, torch.uint8,
+                                 self.device).fill_(GUARD_PATTERN)
+        torch.cuda.synchronize()
         dist.barrier()
+
+    def check_canaries(self):
+        """Names of the regions whose guard zone no longer holds its pattern (empty list = intact).
+        Synchronises the device."""
+        bad = []
+        for name, (roff, size) in self.regions.items():
+            guard = _wrap_device_pointer(self._local_buf.value + roff + size, GUARD_BYTES, torch.uint8, self.device)
+            if not bool((guard == GUARD_PATTERN).all().item()):
+                bad.append(name)
+        return bad
 
     def staging_tensor(self, nbytes: int, dtype=torch.uint8) -> torch.Tensor:
         """A tensor view of the head of the local staging buffer (no copy, no ownership)."""
@@ -363,6 +382,12 @@ def check_health():
     well) and :class:`DeviceTimeout` is raised with the recorded place and counter values.
     Recovery: restart the job from the last checkpoint."""
     code, where, expected, seen = _native.read_status()
+    if _heap is not None and os.environ.get("DISTDL_CHECK_CANARIES", "1") != "0":
+        bad = _heap.check_canaries()
+        if bad:
+            _heap.poisoned = True
+            raise DeviceTimeout(f"the guard zones after the staging regions {bad} were overwritten: a kernel wrote "
+                                f"past the end of its region")
     if code == 0:
         return
     if _heap is not None:

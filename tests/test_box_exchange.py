@@ -166,3 +166,16 @@ def body_halo_and_repartition(rank, world):
 
 def test_halo_exchange_and_repartition_through_box_plans_on_cpu_ranks():
     run_ranks("test_box_exchange", "body_halo_and_repartition", 4, timeout=180)
+
+
+def test_bounds_checking_build_compiles_and_reports_itself():
+    """`python -m distdl_b200._build --debug` gives a second library in which the box-exchange kernel
+    checks every computed address against the tensor's storage (violations are recorded in the
+    status record and the access is skipped); the regular library does not carry the checks."""
+    import ctypes
+
+    from distdl_b200 import _build
+    path = _build.build(debug=True)
+    assert path.endswith("libdistdl_b200_debug.so")
+    assert ctypes.CDLL(path).dd_bounds_checked() == 1
+    assert ctypes.CDLL(_build.build()).dd_bounds_checked() == 0
