@@ -268,6 +268,93 @@ class LinearRsFn(torch.autograd.Function):
         return dx.reshape(b, s, K), dw, db, None
 
 
+# ------------------------------------------------------------------ uneven shards
+# The kernels work on shards of equal length, a multiple of 128 rows.  Members whose shards
+# differ (the balanced split of a sequence that does not divide by the team size) or are not
+# a multiple of 128 run the same kernels on PADDED shards: every member's rows sit at the head
+# of a slot of ``s_pad`` rows (zero filled), the padded rows take part in the GEMM and are
+# dropped afterwards.  The reference pads unequal shards by one slice for its all-gather in
+# the same spirit (``src/distdl/backends/nccl_cupy/functional/all_gather.py:86-99``).
+
+def _pad_segments(t, extents, s_pad):
+    """[b, sum(extents), F] -> [b, P * s_pad, F]: member i's rows at [i * s_pad, i * s_pad + extents[i])."""
+    b, _, F = t.shape
+    out = torch.zeros(b, len(extents) * s_pad, F, dtype=t.dtype, device=t.device)
+    at = 0
+    for i, e in enumerate(extents):
+        out[:, i * s_pad:i * s_pad + e].copy_(t[:, at:at + e])
+        at += e
+    return out
+
+
+def _unpad_segments(t, extents, s_pad):
+    """The inverse of :func:`_pad_segments`."""
+    return torch.cat([t[:, i * s_pad:i * s_pad + e] for i, e in enumerate(extents)], dim=1)
+
+
+class AgLinearPaddedFn(torch.autograd.Function):
+    """:class:`AgLinearFn` for members with different (or not tile-aligned) shard lengths."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, ranks, extents, s_pad):
+        b, s_local, K = x.shape
+        xp = torch.zeros(b, s_pad, K, dtype=x.dtype, device=x.device)
+        xp[:, :s_local].copy_(x)
+        y_pad, G = ag_gemm(xp, w, bias, ranks)
+        ctx.save_for_backward(G, w)
+        ctx.wgrad = grad_target(w)
+        ctx.cfg = (ranks, bias is not None, tuple(extents), s_pad, s_local, b, K)
+        return _unpad_segments(y_pad, extents, s_pad)
+
+    @staticmethod
+    def backward(ctx, dy):
+        G, w = ctx.saved_tensors
+        ranks, has_bias, extents, s_pad, s_local, b, K = ctx.cfg
+        N = w.shape[0]
+        dy2 = _pad_segments(dy, extents, s_pad).reshape(-1, N)       # zero rows where G has zero rows
+        dx = dw = db = None
+        if ctx.needs_input_grad[1]:
+            dw = weight_grad(dy2, G.reshape(-1, K), target=ctx.wgrad)
+        if has_bias and ctx.needs_input_grad[2]:
+            db = dy.reshape(-1, N).sum(0, dtype=torch.float32).to(dy.dtype)
+        if ctx.needs_input_grad[0]:
+            dx = gemm_rs(dy2, w.t(), None, ranks, b, s_pad)[:, :s_local].contiguous()
+        return dx, dw, db, None, None, None
+
+
+class LinearRsPaddedFn(torch.autograd.Function):
+    """:class:`LinearRsFn` for members with different (or not tile-aligned) shard lengths."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, ranks, extents, s_pad, me):
+        b, S, K = x.shape
+        x2 = _pad_segments(x, extents, s_pad).reshape(-1, K)
+        out = gemm_rs(x2, w, bias, ranks, b, s_pad)[:, :extents[me]].contiguous()
+        ctx.save_for_backward(x2, w)
+        ctx.wgrad = grad_target(w)
+        ctx.cfg = (ranks, bias is not None, tuple(extents), s_pad, me, b, K)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        ranks, has_bias, extents, s_pad, me, b, K = ctx.cfg
+        N = w.shape[0]
+        dyp = torch.zeros(b, s_pad, N, dtype=dy.dtype, device=dy.device)
+        dyp[:, :extents[me]].copy_(dy)
+        dx_pad, Gdy = ag_gemm(dyp, w.t(), None, ranks)
+        dw = db = None
+        if ctx.needs_input_grad[1]:
+            dw = weight_grad(Gdy.reshape(-1, N), x2, target=ctx.wgrad)
+        if has_bias and ctx.needs_input_grad[2]:
+            db = Gdy.reshape(-1, N).sum(0, dtype=torch.float32).to(dy.dtype)
+        return _unpad_segments(dx_pad, extents, s_pad), dw, db, None, None, None, None
+
+
+def _balanced(n, P):
+    return [n // P + (1 if i < n % P else 0) for i in range(P)]
+
+
 def _team_of(layer, P_part, dim):
     key = "_fused_team"
     team = getattr(layer, key, None)
@@ -277,10 +364,18 @@ def _team_of(layer, P_part, dim):
     return team
 
 
-def _usable(t, w, s_local, P):
+def _usable(t, w, P):
     return (ENABLED and t.is_cuda and t.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and t.dim() == 3
-            and s_local % 128 == 0 and w.dim() == 2 and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0
+            and w.dim() == 2 and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0
             and 1 < P <= 8 and symm.heap_ready())
+
+
+def _fits(batch, s_pad, P, K, N):
+    """Shard staging and row-block bookkeeping of the kernels hold this geometry."""
+    h = symm.heap()
+    return (batch * s_pad * max(K, N) * 2 <= h.regions["ag_shard"][1] and
+            P * batch * s_pad * max(K, N) * 2 <= h.regions["rs0"][1] and
+            batch * P * s_pad // 128 <= state().ready_words)
 
 
 def maybe_ag_linear(layer, input, weight, bias):
@@ -291,13 +386,26 @@ def maybe_ag_linear(layer, input, weight, bias):
     if layer.gather_dim != dim - 2 or dim != 3:
         return None
     P = int(P_x.shape[-2])
-    if not _usable(input, weight, input.shape[1], P):
+    if not _usable(input, weight, P):
         return None
     if bias is not None and bias.dtype != torch.bfloat16:
         return None
     ranks = _team_of(layer, P_x, layer.gather_dim)
     x = input if input.is_contiguous() else input.contiguous()
-    return AgLinearFn.apply(x, weight, bias, ranks)
+    # the members' shard lengths: the balanced split of the gathered length, which the layer's
+    # all-gather module learns in its (collective, once per input structure) set-up
+    ag = layer.all_gather
+    ag._distdl_forward_pre_hook(ag, (input,))
+    total = int(ag.output_tensor_structure.shape[layer.gather_dim])
+    extents = _balanced(total, P)
+    if extents[list(ranks).index(symm.heap().rank)] != input.shape[1]:
+        return None
+    if len(set(extents)) == 1 and extents[0] % 128 == 0:
+        return AgLinearFn.apply(x, weight, bias, ranks)
+    s_pad = -(-max(extents) // 128) * 128
+    if not _fits(input.shape[0], s_pad, P, weight.shape[1], weight.shape[0]):
+        return None
+    return AgLinearPaddedFn.apply(x, weight, bias, ranks, tuple(extents), s_pad)
 
 
 def maybe_linear_rs(layer, input, weight, bias):
@@ -307,11 +415,18 @@ def maybe_linear_rs(layer, input, weight, bias):
     if layer.scatter_dim != dim - 2 or dim != 3:
         return None
     P = int(P_y.shape[-2])
-    if input.dim() != 3 or input.shape[1] % P:
+    if input.dim() != 3:
         return None
-    if not _usable(input, weight, input.shape[1] // P, P):
+    if not _usable(input, weight, P):
         return None
     if bias is not None and bias.dtype != torch.bfloat16:
         return None
     ranks = _team_of(layer, P_y, layer.scatter_dim)
-    return LinearRsFn.apply(input, weight, bias, ranks)
+    extents = _balanced(int(input.shape[1]), P)
+    if len(set(extents)) == 1 and extents[0] % 128 == 0:
+        return LinearRsFn.apply(input, weight, bias, ranks)
+    s_pad = -(-max(extents) // 128) * 128
+    if not _fits(input.shape[0], s_pad, P, weight.shape[1], weight.shape[0]):
+        return None
+    return LinearRsPaddedFn.apply(input, weight, bias, ranks, tuple(extents), s_pad,
+                                  list(ranks).index(symm.heap().rank))

@@ -57,6 +57,53 @@ def check_fused():
             dw_ref = dyg.reshape(-1, N).t() @ xin.detach().reshape(-1, K).float()
             err = (w2.grad.float() - dw_ref).abs().max().item() / (dw_ref.abs().max().item() + 1e-6)
             assert err < 3e-2, ("gemm_rs dw", err)
+    # ---- shards of different lengths that are no multiple of 128 rows (3 * 128 + 77 and one less):
+    # the padded forms of both fused operators, forward and backward
+    b, K, N = 2, 512, 768
+    S = 461 * world - 1
+    extents = fused._balanced(S, world)
+    s_pad = -(-max(extents) // 128) * 128
+    s_me, lo = extents[rank], sum(extents[:rank])
+    torch.manual_seed(77)
+    w = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16).requires_grad_()
+    bias = (torch.randn(N, device=dev) * 0.1).to(torch.bfloat16).requires_grad_()
+    xfull = torch.randn(b, S, K, device=dev).to(torch.bfloat16)            # the same on every member
+    x = xfull[:, lo:lo + s_me].clone().requires_grad_()
+    y = fused.AgLinearPaddedFn.apply(x, w, bias, ranks, tuple(extents), s_pad)
+    ref = xfull.float() @ w.detach().float().t() + bias.detach().float()
+    assert y.shape == ref.shape
+    err = (y.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+    assert err < 2e-2, ("padded ag_gemm fwd", err)
+    torch.manual_seed(500 + rank)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    dxg = dy.float() @ w.detach().float()
+    dist.all_reduce(dxg)
+    err = (x.grad.float() - dxg[:, lo:lo + s_me]).abs().max().item() / (dxg.abs().max().item() + 1e-6)
+    assert err < 3e-2, ("padded ag_gemm dx", err)
+    dw_ref = dy.reshape(-1, N).float().t() @ xfull.reshape(-1, K).float()
+    err = (w.grad.float() - dw_ref).abs().max().item() / (dw_ref.abs().max().item() + 1e-6)
+    assert err < 3e-2, ("padded ag_gemm dw", err)
+    w2 = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16).requires_grad_()
+    torch.manual_seed(900 + rank)
+    xin = torch.randn(b, S, K, device=dev).to(torch.bfloat16).requires_grad_()
+    out = fused.LinearRsPaddedFn.apply(xin, w2, None, ranks, tuple(extents), s_pad, rank)
+    full = xin.detach().float() @ w2.detach().float().t()
+    dist.all_reduce(full)
+    err = (out.float() - full[:, lo:lo + s_me]).abs().max().item() / (full.abs().max().item() + 1e-6)
+    assert out.shape == (b, s_me, N) and err < 3e-2, ("padded gemm_rs fwd", err)
+    dyl = torch.randn_like(out)
+    out.backward(dyl)
+    dys = [torch.empty(b, e, N, dtype=dyl.dtype, device=dev) for e in extents]
+    dist.all_gather(dys, dyl) if len(set(extents)) == 1 else [
+        dist.broadcast(t if r != rank else t.copy_(dyl), src=r) for r, t in enumerate(dys)]
+    dyg = torch.cat(dys, dim=1).float()
+    dx_ref = dyg @ w2.detach().float()
+    err = (xin.grad.float() - dx_ref).abs().max().item() / (dx_ref.abs().max().item() + 1e-6)
+    assert err < 3e-2, ("padded gemm_rs dx", err)
+    dw_ref = dyg.reshape(-1, N).t() @ xin.detach().reshape(-1, K).float()
+    err = (w2.grad.float() - dw_ref).abs().max().item() / (dw_ref.abs().max().item() + 1e-6)
+    assert err < 3e-2, ("padded gemm_rs dw", err)
     # back-to-back calls without synchronisation in between: the shard staging is double
     # buffered, so a call must never overwrite a shard that a slower peer still reads
     b, s_local, K, N = 2, 512, 2048, 1024
