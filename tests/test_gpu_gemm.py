@@ -90,3 +90,31 @@ def test_linear_autograd_matches_torch():
     _check(x.grad, xr.grad)
     _check(w.grad, wr.grad)
     _check(b.grad, br.grad)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 4096), (384, 256, 8192), (1024, 768, 1600), (512, 512, 14336)])
+def test_gemm_error_bound_scales_with_the_contraction_length(M, N, K):
+    """Element-wise bounds that a lost k-block cannot hide behind.  With fp32 output the only error is
+    the accumulation's: a few fp32 roundings of sums of size sqrt(K), orders of magnitude below the
+    sqrt(64) / sqrt(K) share of one 64-deep k-block.  With bf16 output every element is within one
+    bf16 rounding of the exact value (plus the same accumulation term)."""
+    from distdl_b200.ops import gemm
+    torch.manual_seed(K)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    ref = a.double() @ b.double().t()
+    acc_term = 2e-5 * (K ** 0.5)                  # ~ 2^-16 sqrt(K): generous for fp32 accumulation in any order
+    out32 = gemm(a, b, out_dtype=torch.float32)
+    err = (out32.double() - ref).abs().max().item()
+    assert err < acc_term, (err, acc_term)
+    out16 = gemm(a, b)
+    bound = ref.abs() * 2.0 ** -8 + acc_term
+    assert bool(((out16.double() - ref).abs() <= bound).all()), ((out16.double() - ref).abs() - bound).max().item()
+    # the gradient layouts (dy @ w and dy^T @ x) under the same bound
+    wg = gemm(a.t().contiguous().t(), b, out_dtype=torch.float32)          # A as a transposed (MN-major) view
+    assert (wg.double() - ref).abs().max().item() < acc_term
+    at = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)      # MN-major operands, as in a weight gradient
+    bt = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
+    reft = at.double().t() @ bt.double()
+    outt = gemm(at.t(), bt.t(), out_dtype=torch.float32)
+    assert (outt.double() - reft).abs().max().item() < acc_term
