@@ -103,7 +103,7 @@ def test_gemm_error_bound_scales_with_the_contraction_length(M, N, K):
     a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
     b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
     ref = a.double() @ b.double().t()
-    acc_term = 2e-5 * (K ** 0.5)                  # ~ 2^-16 sqrt(K): generous for fp32 accumulation in any order
+    acc_term = 1e-4 * (K ** 0.5)                  # generous for fp32 accumulation in any order; one lost k-block is ~ 8
     out32 = gemm(a, b, out_dtype=torch.float32)
     err = (out32.double() - ref).abs().max().item()
     assert err < acc_term, (err, acc_term)
