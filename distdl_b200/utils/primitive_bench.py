@@ -2,14 +2,16 @@
 
     torchrun --nnodes=1 --nproc-per-node N -m distdl_b200.utils.primitive_bench [--max-bytes B]
 
-AllSumReduce, AllGather, ReduceScatter and Repartition (an [n, n] tensor from a
-row partition to a column partition) in bf16 for message sizes 4 KB ... 1 GB in
-powers of 4, values ~ U(-1, 1), seed 1; plus HaloExchange of an fp32
+AllSumReduce, AllGather, ReduceScatter, Broadcast, SumReduce and Repartition (an
+[n, n] tensor from a row partition to a column partition) in bf16 for message sizes
+4 KB ... 1 GB in powers of 4, values ~ U(-1, 1), seed 1; plus HaloExchange of an fp32
 [8, 64, 512, 512] tensor with width-1 halos on a 2 x (N/2) spatial partition.
 Each op is timed on the device (CUDA events, warm-up, max over ranks) for the
 native backend (this library's kernels over peer memory) and for the NCCL
 backend (library collectives); bus bandwidth uses the usual factors
-(all-reduce 2(P-1)/P, others (P-1)/P of the full message).
+(all-reduce 2(P-1)/P, others (P-1)/P of the full message).  ``--multimem`` runs the
+native all-reduce through the NVLink multicast region (``multimem.ld_reduce`` /
+``multimem.st``); ``--md FILE`` writes the table as a markdown summary.
 """
 from __future__ import annotations
 
@@ -41,6 +43,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--max-bytes", type=int, default=1 << 30)
     ap.add_argument("--json", default=None)
+    ap.add_argument("--md", default=None, help="write a markdown summary (native vs NCCL per op and size)")
+    ap.add_argument("--multimem", action="store_true", help="native all-reduce through the NVLink multicast region")
     args = ap.parse_args()
     import distdl_b200
     from distdl_b200.backends.common import world as dworld
@@ -55,7 +59,12 @@ def main():
         b *= 4
     for backend in ("native", "nccl"):
         distdl_b200.config.set_backend(backend, "cupy")
-        from distdl_b200.nn import AllGather, AllSumReduce, HaloExchange, ReduceScatter, Repartition
+        from distdl_b200.nn import (AllGather, AllSumReduce, Broadcast, HaloExchange, ReduceScatter, Repartition,
+                                    SumReduce)
+        if backend == "native" and args.multimem:
+            from distdl_b200.parallel import symm
+            symm.heap()
+            symm.enable_multicast(min(2 * args.max_bytes, 1 << 30) + (4 << 20))
         P_world = distdl_b200.backends.backend.Partition()
         P_flat = P_world.create_cartesian_topology_partition([P])
         P_rows = P_world.create_cartesian_topology_partition([P, 1])
@@ -75,6 +84,12 @@ def main():
                 ms = _time(fn)
                 rows.append({"op": name, "backend": backend, "bytes": msg, "ms": ms,
                              "busbw_GBs": msg * factor / ms / 1e6})
+            P_one = P_world.create_partition_inclusive([0]).create_cartesian_topology_partition([1])
+            bc, sr = Broadcast(P_one, P_flat, preserve_batch=False), SumReduce(P_flat, P_one, preserve_batch=False)
+            src = x if rank == 0 else x[:0]
+            for name, fn, msg in (("broadcast", lambda: bc(src), nbytes), ("sum_reduce", lambda: sr(x), nbytes)):
+                ms = _time(fn)
+                rows.append({"op": name, "backend": backend, "bytes": msg, "ms": ms, "busbw_GBs": msg / ms / 1e6})
             side = int(math.sqrt(n)) // (8 * P) * (8 * P)
             if side >= 8 * P:
                 m = torch.rand(side // P, side, device=dev).to(torch.bfloat16)
@@ -95,6 +110,26 @@ def main():
             ms = _time(lambda: he(xt))
             rows.append({"op": f"halo_exchange_8x64x512x512_on_{py}x{px}", "backend": backend,
                          "bytes": xt.numel() * 4, "ms": ms, "busbw_GBs": None})
+        if backend == "native" and args.multimem:
+            symm.disable_multicast()
+    if rank == 0 and args.md:
+        ops = []
+        for r in rows:
+            if r["op"] not in ops:
+                ops.append(r["op"])
+        with open(args.md, "w") as fh:
+            fh.write(f"# Primitive sweep on {P} GPUs (bf16; device-timed, max over ranks)\n\n")
+            fh.write("Command: `torchrun --nnodes=1 --nproc-per-node " + str(P) + " -m distdl_b200.utils.primitive_bench"
+                     + (" --multimem" if args.multimem else "") + f" --max-bytes {args.max_bytes} --md FILE`\n\n")
+            fh.write("| op | bytes | native ms | NCCL ms | native GB/s | NCCL GB/s |\n|---|---|---|---|---|---|\n")
+            for op in ops:
+                sizes_seen = sorted({r["bytes"] for r in rows if r["op"] == op})
+                for nb in sizes_seen:
+                    nat = next((r for r in rows if r["op"] == op and r["bytes"] == nb and r["backend"] == "native"), None)
+                    lib = next((r for r in rows if r["op"] == op and r["bytes"] == nb and r["backend"] == "nccl"), None)
+                    f = lambda r, k: "-" if r is None or r[k] is None else (f"{r[k]:.4f}" if k == "ms" else f"{r[k]:.0f}")
+                    fh.write(f"| {op} | {nb} | {f(nat, 'ms')} | {f(lib, 'ms')} | {f(nat, 'busbw_GBs')} | "
+                             f"{f(lib, 'busbw_GBs')} |\n")
     if rank == 0:
         for r in rows:
             bw = "" if r["busbw_GBs"] is None else f"{r['busbw_GBs']:.1f} GB/s"
