@@ -277,6 +277,11 @@ class Block(torch.nn.Module):
         if cfg.n_experts:
             h = int(h * cfg.top_k * cfg.capacity_factor * 1.5) + 4 * tok * d * e
         kept = 2 * x + 2 * gathered + qkv + o + h
+        import os
+        if os.environ.get("DISTDL_FORCE_TORCH", "0") == "1":
+            # the library operators keep more: the rotary embedding is not in place (a second copy of the
+            # projection), silu(gate) and its product are separate tensors, attention keeps fp32 statistics
+            kept += 2 * qkv + h + 2 * x
         moment = 2 * h + 2 * qkv + 6 * tok * d * e
         # what storing the cheap outputs as well would add: the activation function's output, and
         # (where the projections save their input itself, i.e. without tensor parallelism) both norm outputs
