@@ -104,6 +104,26 @@ def check_fused():
     dw_ref = dyg.reshape(-1, N).t() @ xin.detach().reshape(-1, K).float()
     err = (w2.grad.float() - dw_ref).abs().max().item() / (dw_ref.abs().max().item() + 1e-6)
     assert err < 3e-2, ("padded gemm_rs dw", err)
+    # ---- GEMM -> reduce-scatter: run-to-run determinism, and an error bound that follows the team size.
+    # The partial products travel as bf16 and are folded in fp32 in member order, so every output
+    # element is the fp32 sum of P values each within one bf16 rounding of its exact partial: the error
+    # is bounded by sum_i |partial_i| * 2^-8 (plus the final rounding of the result), whatever P is.
+    b, s_local, K, N = 2, 256, 2048, 1024
+    torch.manual_seed(31)
+    w3 = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16)
+    torch.manual_seed(300 + rank)
+    x3 = torch.randn(b, world * s_local, K, device=dev).to(torch.bfloat16)
+    first = fused.gemm_rs(x3.reshape(-1, K), w3, None, ranks, b, s_local)
+    again = fused.gemm_rs(x3.reshape(-1, K), w3, None, ranks, b, s_local)
+    assert torch.equal(first, again), "gemm_rs is not deterministic from run to run"
+    part = x3.double() @ w3.double().t()                                   # this member's exact partial
+    total, mag = part.clone(), part.abs()
+    dist.all_reduce(total)
+    dist.all_reduce(mag)
+    sl = slice(rank * s_local, (rank + 1) * s_local)
+    bound = mag[:, sl] * 2.0 ** -8 + total[:, sl].abs() * 2.0 ** -8 + 1e-3
+    excess = ((first.double() - total[:, sl]).abs() - bound).max().item()
+    assert excess <= 0, ("gemm_rs error beyond the bf16-partial bound", world, excess)
     # back-to-back calls without synchronisation in between: the shard staging is double
     # buffered, so a call must never overwrite a shard that a slower peer still reads
     b, s_local, K, N = 2, 512, 2048, 1024
