@@ -373,6 +373,32 @@ def require_healthy():
     if _heap is not None and _heap.poisoned:
         raise DeviceTimeout("the symmetric heap is poisoned by an earlier device time-out; restart the job "
                             "from its last checkpoint")
+    _one_waiting_stream()
+
+
+_last_waiting = [None, None]       # (stream handle, event recorded after the last peer-waiting launch)
+
+
+def _one_waiting_stream():
+    """Kernels that wait for other GPUs must not be resident on one GPU from two streams at once: each
+    could hold the SMs that the other needs while their peers wait for both.  Every such launch passes
+    through here; a launch on another stream than the previous one is refused unless the previous
+    kernel has already finished."""
+    if not torch.cuda.is_available() or os.environ.get("DISTDL_STREAM_GUARD", "1") == "0":
+        return
+    cur = torch.cuda.current_stream()
+    last_stream, last_event = _last_waiting
+    if last_stream is not None and last_stream != cur.cuda_stream and last_event is not None \
+            and not last_event.query():
+        raise RuntimeError("a kernel that waits for other GPUs is still running on another stream of this GPU: "
+                           "launch the collectives, exchanges and fused GEMMs of one GPU on one stream "
+                           "(or synchronise the streams first)")
+    if last_stream != cur.cuda_stream:
+        _last_waiting[0] = cur.cuda_stream
+    ev = _last_waiting[1]
+    if ev is None:
+        ev = _last_waiting[1] = torch.cuda.Event()
+    ev.record(cur)
 
 
 def check_health():
