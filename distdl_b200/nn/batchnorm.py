@@ -125,12 +125,13 @@ class DistributedBatchNorm(Module):
     def forward(self, input):
         if not self.P_x.active:
             return input
-        dims = [d for d in range(input.dim()) if d != 1]
+        from ..ops import batchnorm as bn_ops
         if self.training or not self.track_running_stats:
-            s = self.sr(input.sum(dims, keepdim=True))
+            # local per-feature sums: one reduction kernel each (fp32 accumulation)
+            s = self.sr(bn_ops.channel_sum(input))
             mean_root = s / self.global_count if self.P_sum.active else s
             mean = self.bc(mean_root)
-            v = self.sr2(((input - mean) ** 2).sum(dims, keepdim=True))
+            v = self.sr2(bn_ops.channel_sqdev(input, mean))
             var_root = v / self.global_count if self.P_sum.active else v
             var = self.bc2(var_root)
             if self.track_running_stats and self.P_sum.active and self.training:
@@ -142,10 +143,12 @@ class DistributedBatchNorm(Module):
         else:
             mean = self.bc_rm(self.running_mean)
             var = self.bc_rv(self.running_var)
-        y = (input - mean) / torch.sqrt(var + self.eps)
+        gamma = beta = None
         if self.affine:
             if self.gamma_buffer is None:
                 self.prefetch_weights()
-            y = self.gamma_buffer * y + self.beta_buffer
+            gamma, beta = self.gamma_buffer, self.beta_buffer
             self.gamma_buffer = self.beta_buffer = None
-        return y
+        # normalisation and affine map in one element-wise kernel (and one reduction + one element-wise
+        # kernel in its backward pass)
+        return bn_ops.normalize(input, mean, var, gamma, beta, self.eps)

@@ -91,3 +91,39 @@ def test_router_kernel_matches_softmax_topk_renormalisation(E, k, ld):
     for e in range(min(E, 4)):
         kept = (slot2[ids2 == e] >= 0).sum().item()
         assert kept == min(8, int((ids2 == e).sum()))
+
+
+@pytest.mark.parametrize("dtype,shape", [(torch.float32, (6, 5, 7, 9)), (torch.bfloat16, (8, 16, 33)),
+                                         (torch.float32, (3, 64, 4, 4, 5))])
+def test_batch_norm_kernels_match_the_pytorch_formulation(dtype, shape):
+    """Per-feature sum, sum of squared deviations and the normalise + affine map (forward and backward)
+    against the same expressions written with PyTorch operations in fp32."""
+    from distdl_b200.ops import batchnorm as bn
+    torch.manual_seed(3)
+    F = shape[1]
+    stat = (1, F) + (1,) * (len(shape) - 2)
+    x = torch.randn(*shape, device="cuda").to(dtype).requires_grad_()
+    mean = torch.randn(stat, device="cuda").mul(0.1).to(dtype).requires_grad_()
+    var = (torch.rand(stat, device="cuda") + 0.5).to(dtype).requires_grad_()
+    gamma = (1 + 0.1 * torch.randn(stat, device="cuda")).to(dtype).requires_grad_()
+    beta = (0.1 * torch.randn(stat, device="cuda")).to(dtype).requires_grad_()
+    dims = [d for d in range(len(shape)) if d != 1]
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+
+    def close(a, b):
+        err = (a.float() - b.float()).abs().max().item() / (b.float().abs().max().item() + 1e-6)
+        assert err < tol, err
+
+    ref = [t.detach().float().requires_grad_() for t in (x, mean, var, gamma, beta)]
+    s, sr = bn.channel_sum(x), ref[0].sum(dims, keepdim=True)
+    q, qr = bn.channel_sqdev(x, mean), ((ref[0] - ref[1]) ** 2).sum(dims, keepdim=True)
+    y = bn.normalize(x, mean, var, gamma, beta, 1e-5)
+    yr = ref[3] * (ref[0] - ref[1]) / torch.sqrt(ref[2] + 1e-5) + ref[4]
+    close(s, sr)
+    close(q, qr)
+    close(y, yr)
+    gs, gq, gy = torch.randn_like(sr), torch.randn_like(qr), torch.randn_like(yr)
+    torch.autograd.backward([s, q, y], [gs.to(dtype), gq.to(dtype), gy.to(dtype)])
+    torch.autograd.backward([sr, qr, yr], [gs.to(dtype).float(), gq.to(dtype).float(), gy.to(dtype).float()])
+    for got, want in zip((x, mean, var, gamma, beta), ref):
+        close(got.grad, want.grad)
