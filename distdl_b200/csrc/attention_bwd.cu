@@ -47,23 +47,28 @@ struct BwdParams {
 // warpgroups split every row between them.
 __device__ __forceinline__ void form_p_ds(uint32_t tS, uint32_t tdP, uint8_t* sP, uint8_t* sdS, int row,
                                           float lse_l2, float delta, float c, float scale, bool diag, int half) {
-#pragma unroll 1
-  for (int ch = 2 * half; ch < 2 * half + 2; ++ch) {
-    uint32_t s[32], dp[32];
-    tmem_ld_32x32(tS + ch * 32, s);
-    tmem_ld_32x32(tdP + ch * 32, dp);
-    tmem_ld_wait();
+  // all four tensor-memory loads of this thread's 64 columns are in flight before the first use
+  uint32_t s[2][32], dp[2][32];
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    tmem_ld_32x32(tS + (2 * half + q) * 32, s[q]);
+    tmem_ld_32x32(tdP + (2 * half + q) * 32, dp[q]);
+  }
+  tmem_ld_wait();
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const int ch = 2 * half + q;
     uint32_t pp[16], pds[16];
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
-      float p0 = exp2f(__uint_as_float(s[i]) * c - lse_l2);
-      float p1 = exp2f(__uint_as_float(s[i + 1]) * c - lse_l2);
+      float p0 = exp2f(__uint_as_float(s[q][i]) * c - lse_l2);
+      float p1 = exp2f(__uint_as_float(s[q][i + 1]) * c - lse_l2);
       if (diag) {
         if (ch * 32 + i > row) p0 = 0.f;
         if (ch * 32 + i + 1 > row) p1 = 0.f;
       }
-      const float d0 = p0 * (__uint_as_float(dp[i]) - delta) * scale;
-      const float d1 = p1 * (__uint_as_float(dp[i + 1]) - delta) * scale;
+      const float d0 = p0 * (__uint_as_float(dp[q][i]) - delta) * scale;
+      const float d1 = p1 * (__uint_as_float(dp[q][i + 1]) - delta) * scale;
       pp[i >> 1] = pack_bf16x2(p0, p1);
       pds[i >> 1] = pack_bf16x2(d0, d1);
     }

@@ -53,7 +53,7 @@ def test_add_norm_returns_sum_and_norm_with_the_gradient_of_both(rms):
     torch.autograd.backward([s, y], [ds, dy])
     xr, rr = x.detach().float().requires_grad_(), r.detach().float().requires_grad_()
     wr = w.detach().float().requires_grad_()
-    sr = (xr + rr).to(torch.bfloat16).float() + (xr + rr - (xr + rr).detach())      # the stored sum is bf16
+    sr = (xr + rr).detach().to(torch.bfloat16).float() + (xr + rr - (xr + rr).detach())     # the stored sum is bf16
     if rms:
         yr = sr * torch.rsqrt(sr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
     else:
