@@ -122,7 +122,9 @@ def activation_report(model):
             f"(with its log-sum-exp) for the backward pass, {per / 1e9:.2f} GB per block and micro-batch, "
             f"{keep * per / 1e9:.1f} GB per GPU; in those blocks " +
             ("nothing is recomputed (memory to spare: norm and activation outputs are stored as well)"
-             if plan.get("stores_cheap_outputs") else
+             if plan.get("stores_activation_output") and plan.get("stores_norm_outputs") else
+             "only norm outputs are recomputed (the activation function's output is stored as well)"
+             if plan.get("stores_activation_output") else
              "only norm outputs and the activation function's output are recomputed") +
             f" and the ZeRO weight shards are gathered again; the other {n - keep} blocks recompute their forward pass")
 

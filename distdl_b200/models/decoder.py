@@ -225,7 +225,7 @@ class MLP(torch.nn.Module):
         del x
         a = act(h)
         # the second GEMM saves its input: rebuilt from h, which the activation's backward keeps anyway
-        with recompute.saved_as_recipe(a, (lambda: act(h)) if recompute.rebuilds_outputs() else None):
+        with recompute.saved_as_recipe(a, (lambda: act(h)) if recompute.rebuilds_activation_output() else None):
             return self.down(a)
 
 
@@ -246,7 +246,7 @@ class Block(torch.nn.Module):
         it (its feed-forward output), or None.  Returns the pair in the same form: the stream after
         the attention branch was added, and this block's feed-forward output.  Every residual add
         thereby runs inside the norm kernel that follows it."""
-        keep = recompute.rebuilds_outputs()   # this block keeps its activations: norm outputs are rebuilt in backward
+        keep = recompute.rebuilds_norm_outputs()   # this block keeps its activations: norm outputs are rebuilt in backward
         if delta is None:
             n1 = self.norm1(x)
         else:
@@ -285,7 +285,8 @@ class Block(torch.nn.Module):
         moment = 2 * h + 2 * qkv + 6 * tok * d * e
         # what storing the cheap outputs as well would add: the activation function's output, and
         # (where the projections save their input itself, i.e. without tensor parallelism) both norm outputs
-        self.cheap_bytes = (h // 2 if cfg.activation == "swiglu" else h) + (2 * x if tp == 1 else 0)
+        self.activation_out_bytes = h // 2 if cfg.activation == "swiglu" else h
+        self.norm_out_bytes = 2 * x if tp == 1 else 0
         return kept, moment
 
     def prefetch(self):
@@ -431,13 +432,20 @@ class Decoder(torch.nn.Module):
             budget = free - head - moment - kept - slack
             keep = max(0, min(n, int(budget // max(kept, 1))))
             plan["free_bytes"] = int(free)
-            # memory to spare after every block keeps: store the cheap outputs too instead of rebuilding them
-            cheap = int(getattr(self.blocks[0], "cheap_bytes", 0))
-            spare = int(keep == n and budget - n * kept >= n * cheap + (8 << 30))
+            # memory to spare after every block keeps: store cheap outputs too instead of rebuilding them,
+            # the activation function's output first (rebuilding it moves three times its size, a norm
+            # output twice its size)
+            left = budget - n * kept - (6 << 30) if keep == n else -1
+            act_b, norm_b = (int(getattr(self.blocks[0], a, 0)) for a in ("activation_out_bytes", "norm_out_bytes"))
+            spare_act = int(left >= n * act_b)
+            left -= n * act_b if spare_act else 0
+            spare_norm = int(left >= n * norm_b)
             # agreed among the workers of this decoder (of this pipeline stage) through the control plane
-            agreed = self.layout.P_grid.allreduce_data(np.asarray([keep, spare], dtype=np.int64), op="min")
+            agreed = self.layout.P_grid.allreduce_data(np.asarray([keep, spare_act, spare_norm], dtype=np.int64),
+                                                       op="min")
             keep = int(agreed[0])
-            plan["stores_cheap_outputs"] = bool(agreed[1]) and keep == n
+            plan["stores_activation_output"] = bool(agreed[1]) and keep == n
+            plan["stores_norm_outputs"] = bool(agreed[2]) and keep == n
         plan["keep"] = keep
         self._keep_plan = plan
         return keep
@@ -515,8 +523,9 @@ class Decoder(torch.nn.Module):
             if i < n - n_keep:
                 x, delta = torch.utils.checkpoint.checkpoint(run, x, delta, i, use_reentrant=False)
             else:
-                with recompute.enabled(outputs=not self._keep_plan.get("stores_cheap_outputs", False)
-                                       if getattr(self, "_keep_plan", None) else True):
+                plan = getattr(self, "_keep_plan", None) or {}
+                with recompute.enabled(norms=not plan.get("stores_norm_outputs", False),
+                                       activation=not plan.get("stores_activation_output", False)):
                     x, delta = self.blocks[i](x, delta)
             if delta.requires_grad and ((pre and i > 0) or (notify and i + 1 < n)):
                 # the gradient of block i's feed-forward output is ready when the backward pass of block

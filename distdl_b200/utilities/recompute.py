@@ -27,7 +27,7 @@ import weakref
 import torch
 
 _enabled = 0
-_outputs_too = True    # recipes also stand in for cheap operator outputs (not only for gathered weights)
+_norms, _activation = True, True    # which cheap operator outputs recipes stand in for (besides gathered weights)
 _targets = []          # open recipes, innermost last
 
 
@@ -35,24 +35,33 @@ def active() -> bool:
     return _enabled > 0
 
 
+def rebuilds_norm_outputs() -> bool:
+    """Inside ``enabled()``: whether norm outputs are rebuilt in the backward pass."""
+    return _enabled > 0 and _norms
+
+
+def rebuilds_activation_output() -> bool:
+    """Inside ``enabled()``: whether the activation function's output is rebuilt in the backward pass."""
+    return _enabled > 0 and _activation
+
+
 def rebuilds_outputs() -> bool:
-    """Inside ``enabled()``: whether outputs of cheap operators (norms, activation functions) are
-    rebuilt in the backward pass too.  A caller with memory to spare turns that off
-    (``enabled(outputs=False)``) and keeps only the re-gathering of ZeRO weights."""
-    return _enabled > 0 and _outputs_too
+    return rebuilds_norm_outputs() or rebuilds_activation_output()
 
 
 @contextlib.contextmanager
-def enabled(flag: bool = True, outputs: bool = True):
-    """Turns recipes on (or, with ``flag=False``, off) for the duration of the block."""
-    global _enabled, _outputs_too
-    before = (_enabled, _outputs_too)
+def enabled(flag: bool = True, norms: bool = True, activation: bool = True):
+    """Turns recipes on (or, with ``flag=False``, off) for the duration of the block.  A caller with
+    memory to spare keeps the re-gathering of ZeRO weights but stores the outputs of cheap operators
+    after all: ``norms=False`` / ``activation=False``."""
+    global _enabled, _norms, _activation
+    before = (_enabled, _norms, _activation)
     _enabled = (before[0] + 1) if flag else 0
-    _outputs_too = outputs
+    _norms, _activation = norms, activation
     try:
         yield
     finally:
-        _enabled, _outputs_too = before
+        _enabled, _norms, _activation = before
 
 
 class Recipe:
