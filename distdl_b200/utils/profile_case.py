@@ -1,7 +1,8 @@
 """Runs a few launches of ONE hand-written kernel on a small case, for use
 under a profiler:
 
-    python -m distdl_b200.utils.profile_case gemm|gemm_wgrad|ag_gemm|gemm_rs|attn_fwd|attn_bwd|rmsnorm|adamw|xent [launches]
+    python -m distdl_b200.utils.profile_case gemm|gemm_wgrad|ag_gemm|gemm_rs|attn_fwd|attn_bwd|rmsnorm|rmsnorm_bwd|
+        add_rmsnorm|router|adamw|xent [launches]
 
 Inputs are larger than the 126 MB L2 where that matters for the DRAM figures
 but stay well under a few GB.
@@ -63,6 +64,21 @@ def main():
         x = torch.randn(32768, 4096, device=dev, dtype=torch.bfloat16)
         w = torch.ones(4096, device=dev, dtype=torch.bfloat16)
         fn = lambda: ops.rms_norm(x, w)  # noqa: E731
+    elif what == "rmsnorm_bwd":
+        x = torch.randn(32768, 4096, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        w = torch.ones(4096, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        y = ops.rms_norm(x, w)
+        dy = torch.randn_like(y)
+        fn = lambda: torch.autograd.grad(y, (x, w), dy, retain_graph=True)  # noqa: E731
+    elif what == "add_rmsnorm":
+        x = torch.randn(32768, 4096, device=dev, dtype=torch.bfloat16)
+        r = torch.randn_like(x)
+        w = torch.ones(4096, device=dev, dtype=torch.bfloat16)
+        fn = lambda: ops.add_rms_norm(x, r, w)  # noqa: E731
+    elif what == "router":
+        from distdl_b200.ops import moe
+        logits = torch.randn(1 << 20, 8, device=dev, dtype=torch.bfloat16)
+        fn = lambda: moe.route(logits, 8, 2, 1 << 19)  # noqa: E731
     elif what == "adamw":
         m = 64 * 1024 * 1024
         p, a, b, g = (torch.zeros(m, device=dev) for _ in range(4))

@@ -106,7 +106,6 @@ def check_box_exchange():
 
     import distdl_b200
     from distdl_b200.backends.common.functional import halo_exchange as hx
-    from distdl_b200.backends.common.functional import repartition as rp
     from distdl_b200.backends.common.transport import GroupTransport
     from distdl_b200.nn import HaloExchange, Repartition
     world, rank = dist.get_world_size(), dist.get_rank()

@@ -2,7 +2,6 @@
 units), the kernel's index arithmetic (compiled for the host as well) against PyTorch slicing,
 the way plans are cut into launches, and whole halo exchanges / repartitions on CPU ranks with
 the plan executed by ``BoxPlan.run_on_host`` against the slicing formulation."""
-import itertools
 
 import pytest
 import torch
