@@ -225,7 +225,7 @@ namespace {
 
 constexpr int kMaxPeers = 8;
 constexpr int kMcThreads = 512;
-constexpr int kMcMaxCtas = 64;
+constexpr int kMcMaxCtas = 48;
 // signal-pad words [1200, 1200 + 64 * 8): one counter per (CTA, writer) for these kernels
 constexpr int PAD_MC = 1200;
 
@@ -339,8 +339,10 @@ DD_API int dd_mc_allreduce(int n, int me, void* const* pads, unsigned expect, si
   int err = 0;
   t.status = device_status(&err);
   if (err) return err;
-  if (ctas < 1) ctas = 1;
-  if (ctas > kMcMaxCtas) ctas = kMcMaxCtas;
+  // Always the same grid: every CTA owns one counter per peer, and the host counts barrier steps
+  // once for all of them, so all slots have to advance in step from launch to launch.
+  (void)ctas;
+  ctas = kMcMaxCtas;
   *steps = 2;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   char* mc = reinterpret_cast<char*>(g_mc.mc_va);
