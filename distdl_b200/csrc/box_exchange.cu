@@ -42,7 +42,7 @@ namespace {
 constexpr int kMaxPeers = 8;
 constexpr int kBoxBufs = 4;
 constexpr int kBoxMaxItems = 48;
-constexpr int kBoxCtas = 96;            // half send, half receive
+constexpr int kBoxCtas = 128;           // half send, half receive
 constexpr int kBoxThreads = 256;
 constexpr unsigned long long kPieceBytes = 32 * 1024;
 // word offsets inside a signal pad (uint32 units); [0, 1104) belong to the collectives and the fused GEMMs
@@ -211,6 +211,82 @@ __device__ __forceinline__ uint4 ld_cg16(const void* p) {
   return v;
 }
 
+// Address of row r (all outer indices folded into one number) of a box.
+__device__ __forceinline__ char* row_addr(const Box& x, unsigned long long r) {
+  const unsigned long long i2 = r % (unsigned long long)x.n[2];
+  const unsigned long long t = r / (unsigned long long)x.n[2];
+  const unsigned long long i1 = t % (unsigned long long)x.n[1];
+  const unsigned long long i0 = t / (unsigned long long)x.n[1];
+  return x.base + (long long)i0 * x.s[0] + (long long)i1 * x.s[1] + (long long)i2 * x.s[2];
+}
+
+// body(box address, unit index g) for every unit g in [lo_u, hi_u) of the box, the threads of the CTA
+// sharing the work.  Rows of 8 units or more: one warp per row and the lanes along it, so that
+// the index arithmetic (divisions) is paid once per row and the accesses of a warp are contiguous.
+// Shorter rows: one unit per thread, with 32-bit arithmetic where the message allows it.
+template <typename Body>
+__device__ __forceinline__ void walk_units(const Box& x, int unit, unsigned long long lo_u, unsigned long long hi_u,
+                                           Body body) {
+  if (hi_u <= lo_u) return;
+  const unsigned n3 = (unsigned)x.n[3];
+  if (n3 >= 8) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned long long r0 = lo_u / n3, r1 = (hi_u - 1) / n3;
+    for (unsigned long long r = r0 + warp; r <= r1; r += kBoxThreads / 32) {
+      char* rowp = row_addr(x, r);
+      const unsigned ub = r == r0 ? (unsigned)(lo_u - r * n3) : 0u;
+      const unsigned ue = r == r1 ? (unsigned)(hi_u - r * n3) : n3;
+      for (unsigned u = ub + lane; u < ue; u += 32) body(rowp + (size_t)u * unit, r * n3 + u);
+    }
+  } else if (hi_u <= 0xffffffffull) {
+    const unsigned n2 = (unsigned)x.n[2], n1 = (unsigned)x.n[1];
+    for (unsigned g = (unsigned)lo_u + threadIdx.x; g < (unsigned)hi_u; g += kBoxThreads) {
+      const unsigned i3 = g % n3;
+      unsigned t = g / n3;
+      const unsigned i2 = t % n2;
+      t /= n2;
+      const unsigned i1 = t % n1, i0 = t / n1;
+      body(x.base + (long long)i0 * x.s[0] + (long long)i1 * x.s[1] + (long long)i2 * x.s[2] + (long long)i3 * unit, g);
+    }
+  } else {
+    for (unsigned long long g = lo_u + threadIdx.x; g < hi_u; g += kBoxThreads) body(unit_addr(x, unit, g), g);
+  }
+}
+
+// Plain copy in 16-byte units between a box and a contiguous buffer (`lin` = address of unit 0),
+// a warp per row, four vectors per lane in flight.  TO_BOX: the contiguous side is an inbox that
+// another GPU wrote (read at L2).  Rows of at least 8 units.
+template <bool TO_BOX>
+__device__ __forceinline__ void copy16_rows(const Box& x, char* lin, unsigned long long lo_u,
+                                            unsigned long long hi_u) {
+  if (hi_u <= lo_u) return;
+  const unsigned n3 = (unsigned)x.n[3];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned long long r0 = lo_u / n3, r1 = (hi_u - 1) / n3;
+  for (unsigned long long r = r0 + warp; r <= r1; r += kBoxThreads / 32) {
+    char* rowp = row_addr(x, r);
+    char* linp = lin + ((r * n3) << 4);
+    const unsigned ub = r == r0 ? (unsigned)(lo_u - r * n3) : 0u;
+    const unsigned ue = r == r1 ? (unsigned)(hi_u - r * n3) : n3;
+    for (unsigned u = ub + lane; u < ue; u += 128) {
+      uint4 v[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const unsigned uu = u + 32 * q;
+        if (uu < ue) v[q] = TO_BOX ? ld_cg16(linp + ((size_t)uu << 4)) : *reinterpret_cast<const uint4*>(rowp + ((size_t)uu << 4));
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const unsigned uu = u + 32 * q;
+        if (uu < ue) {
+          if (TO_BOX) *reinterpret_cast<uint4*>(rowp + ((size_t)uu << 4)) = v[q];
+          else *reinterpret_cast<uint4*>(linp + ((size_t)uu << 4)) = v[q];
+        }
+      }
+    }
+  }
+}
+
 // Thread 0 waits (bounded) until the counter at p has reached `want`; every thread of the CTA
 // learns the outcome.  SYS: the counter is written by another GPU.
 template <bool SYS>
@@ -281,27 +357,37 @@ __global__ void __launch_bounds__(kBoxThreads) box_exchange_kernel(const __grid_
           if (!cta_wait<true>(A.pad[A.me] + PAD_BOX_CONSUMED + buf * 8 + m.peer, use, A.status, 310, &fail)) return;
           char* dst = A.inbox[m.peer] + (unsigned long long)A.me * A.slot_bytes + (unsigned long long)buf * A.chunk_bytes - c_lo;
           const int unit = m.unit;
-          for (unsigned long long g = lo / unit + threadIdx.x; g < hi / unit; g += kBoxThreads) {
-            char* src = unit_addr(m.a, unit, g);
-            if (in_bounds(m.a, src, unit, A.status, g)) move_unit(dst + g * unit, src, unit, kAddNone, m.clear_source != 0);
+          const bool clear = m.clear_source != 0;
+          StatusRecord* st = A.status;
+#ifndef DD_BOUNDS_CHECK
+          if (unit == 16 && !clear && m.a.n[3] >= 8) {
+            copy16_rows<false>(m.a, dst, lo / 16, hi / 16);
+          } else
+#endif
+          {
+            const Box& bx = m.a;
+            walk_units(bx, unit, lo / unit, hi / unit, [&](char* src, unsigned long long g) {
+              if (in_bounds(bx, src, unit, st, g)) move_unit(dst + g * unit, src, unit, kAddNone, clear);
+            });
           }
         } else if (m.kind == kRecv) {
           if (!cta_wait<true>(A.pad[A.me] + PAD_BOX_DELIVERED + buf * 8 + m.peer, use + 1, A.status, 311, &fail)) return;
           char* src = A.inbox[A.me] + (unsigned long long)m.peer * A.slot_bytes + (unsigned long long)buf * A.chunk_bytes - c_lo;
-          const int unit = m.unit;
-          if (unit == 16 && m.add == kAddNone) {
-            for (unsigned long long g = lo / 16 + threadIdx.x; g < hi / 16; g += kBoxThreads) {
-              char* to = unit_addr(m.a, 16, g);
-              if (in_bounds(m.a, to, 16, A.status, g)) *reinterpret_cast<uint4*>(to) = ld_cg16(src + g * 16);
-            }
-          } else if (unit == 16) {
-            for (unsigned long long g = lo / 16 + threadIdx.x; g < hi / 16; g += kBoxThreads) {
+          const int unit = m.unit, add = m.add;
+          StatusRecord* st = A.status;
+          const Box& bx = m.a;
+#ifndef DD_BOUNDS_CHECK
+          if (unit == 16 && add == kAddNone && bx.n[3] >= 8) {
+            copy16_rows<true>(bx, src, lo / 16, hi / 16);
+          } else
+#endif
+          if (unit == 16) {
+            walk_units(bx, 16, lo / 16, hi / 16, [&](char* to, unsigned long long g) {
               uint4 v = ld_cg16(src + g * 16);
-              char* to = unit_addr(m.a, 16, g);
-              if (in_bounds(m.a, to, 16, A.status, g)) move_unit(to, reinterpret_cast<char*>(&v), 16, m.add, false);
-            }
+              if (in_bounds(bx, to, 16, st, g)) move_unit(to, reinterpret_cast<char*>(&v), 16, add, false);
+            });
           } else {
-            for (unsigned long long g = lo / unit + threadIdx.x; g < hi / unit; g += kBoxThreads) {
+            walk_units(bx, unit, lo / unit, hi / unit, [&](char* to, unsigned long long g) {
               // (volatile read: the buffer was written by another GPU)
               uint64_t v = 0;
               const char* sp = src + g * unit;
@@ -311,19 +397,30 @@ __global__ void __launch_bounds__(kBoxThreads) box_exchange_kernel(const __grid_
                 case 4: v = *reinterpret_cast<const volatile uint32_t*>(sp); break;
                 default: v = *reinterpret_cast<const volatile uint64_t*>(sp); break;
               }
-              char* to = unit_addr(m.a, unit, g);
-              if (in_bounds(m.a, to, unit, A.status, g)) move_unit(to, reinterpret_cast<char*>(&v), unit, m.add, false);
-            }
+              if (in_bounds(bx, to, unit, st, g)) move_unit(to, reinterpret_cast<char*>(&v), unit, add, false);
+            });
           }
         } else {
           // local copy: the two sides may have different units; walk in the smaller one
           const int unit = m.unit < m.unit_b ? m.unit : m.unit_b;
           const int ra = m.unit / unit, rb = m.unit_b / unit;
-          for (unsigned long long g = lo / unit + threadIdx.x; g < hi / unit; g += kBoxThreads) {
-            char* to = unit_addr(m.b, m.unit_b, g / rb) + (g % rb) * unit;
-            char* from = unit_addr(m.a, m.unit, g / ra) + (g % ra) * unit;
-            if (in_bounds(m.b, to, unit, A.status, g) && in_bounds(m.a, from, unit, A.status, g))
-              move_unit(to, from, unit, kAddNone, false);
+          StatusRecord* st = A.status;
+          const Box& ba = m.a;
+          const Box& bb = m.b;
+          if (ra == 1 && rb == 1 && ba.n[3] == bb.n[3]) {
+            // rows of the two boxes correspond: walk the source, address the destination row-wise
+            const unsigned n3 = (unsigned)ba.n[3];
+            walk_units(ba, unit, lo / unit, hi / unit, [&](char* from, unsigned long long g) {
+              char* to = row_addr(bb, g / n3) + (size_t)(g % n3) * unit;
+              if (in_bounds(bb, to, unit, st, g) && in_bounds(ba, from, unit, st, g)) move_unit(to, from, unit, kAddNone, false);
+            });
+          } else {
+            for (unsigned long long g = lo / unit + threadIdx.x; g < hi / unit; g += kBoxThreads) {
+              char* to = unit_addr(bb, m.unit_b, g / rb) + (g % rb) * unit;
+              char* from = unit_addr(ba, m.unit, g / ra) + (g % ra) * unit;
+              if (in_bounds(bb, to, unit, st, g) && in_bounds(ba, from, unit, st, g))
+                move_unit(to, from, unit, kAddNone, false);
+            }
           }
         }
         // the piece is done; whoever completes the chunk signals the other GPU

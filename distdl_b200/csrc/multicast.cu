@@ -302,6 +302,17 @@ mc_allreduce_kernel(const McTeam t, char* mc_base, char* uc_base, size_t in_off,
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   if (!mc_barrier(t, 0, &fail)) return;                 // every GPU's input is in place
+  if (one_shot == 2) {
+    // reduce-scatter: `bytes` is one member's slice; member i's slice is the i-th of every input
+    const size_t base = in_off + (size_t)t.me * bytes;
+    for (size_t v = tid; v < nvec; v += stride) {
+      const uint4 r = BF16 ? multimem_ld_reduce_bf16(mc_base + base + (v << 4))
+                           : multimem_ld_reduce_f32(mc_base + base + (v << 4));
+      *reinterpret_cast<uint4*>(out + (v << 4)) = r;
+    }
+    mc_barrier(t, 1, &fail);
+    return;
+  }
   if (one_shot) {
     for (size_t v = tid; v < nvec; v += stride) {
       const uint4 r = BF16 ? multimem_ld_reduce_bf16(mc_base + in_off + (v << 4))
@@ -327,12 +338,18 @@ mc_allreduce_kernel(const McTeam t, char* mc_base, char* uc_base, size_t in_off,
 
 // dtype 0 = bf16, 1 = fp32; bytes a multiple of 16; the input must already be at in_off of this
 // GPU's copy (written on `stream` before this call).  *steps = barrier steps consumed.
+// one_shot: 1 = all-reduce read in one pass, 0 = all-reduce in two shots, 2 = reduce-scatter (the
+// input holds n slices of `bytes` each, member i receives the sum of everybody's slice i).
 DD_API int dd_mc_allreduce(int n, int me, void* const* pads, unsigned expect, size_t in_off, size_t out_off,
                            void* out, size_t bytes, int dtype, int one_shot, int ctas, int* steps, void* stream) {
   if (g_mc.mc_va == 0) return DD_ERR_BAD_ARG;
   if (n < 2 || n > kMaxPeers || me < 0 || me >= n || n != g_mc.n_devices) return DD_ERR_BAD_ARG;
   if (bytes % 16 || in_off % 16 || out_off % 16) return DD_ERR_ALIGN;
-  if (in_off + bytes > g_mc.size || (!one_shot && out_off + bytes > g_mc.size)) return DD_ERR_TOO_LARGE;
+  if (one_shot == 2) {
+    if (in_off + (size_t)n * bytes > g_mc.size) return DD_ERR_TOO_LARGE;
+  } else if (in_off + bytes > g_mc.size || (!one_shot && out_off + bytes > g_mc.size)) {
+    return DD_ERR_TOO_LARGE;
+  }
   McTeam t;
   t.n = n; t.me = me; t.expect = expect;
   for (int i = 0; i < n; ++i) t.pad[i] = reinterpret_cast<uint32_t*>(pads[i]);

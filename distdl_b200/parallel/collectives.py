@@ -214,6 +214,10 @@ def reduce_scatter(x: torch.Tensor, ranks) -> torch.Tensor:
     chunk = xs[0].numel()
     out = torch.empty(chunk, dtype=xs.dtype, device=x.device)
     flat = xs.view(P, chunk)
+    mc = symm.multicast_region() if P == h.world else None
+    if mc is not None:
+        _reduce_scatter_multicast(mc, h, flat, out)
+        return out.view(x.shape[1:]).to(x.dtype)
     cap_elems = (h.staging_bytes // P) // 16 * 16 // es
     done = 0
     while done < chunk:
@@ -232,6 +236,38 @@ def reduce_scatter(x: torch.Tensor, ranks) -> torch.Tensor:
             out[done:done + cnt].copy_(tmp[:cnt])
         done += cnt
     return out.view(x.shape[1:]).to(x.dtype)
+
+
+def _reduce_scatter_multicast(mc, h, xs, out):
+    """Job-wide reduce-scatter through the multicast region: every GPU stages its whole input in its
+    copy, then reads the sum of its own slice with ``multimem.ld_reduce``."""
+    symm.require_healthy()
+    P = h.world
+    es = xs.element_size()
+    n = xs.shape[1]
+    cap = (mc.nbytes // P) // 256 * 256
+    pads = (ctypes.c_void_p * P)(*h.pad_ptrs)
+    lib = _native.lib()
+    done = 0
+    while done < n:
+        cnt = min(n - done, cap // es)
+        padded = (cnt * es + 15) // 16 * 16
+        pe = padded // es
+        stage = mc.local_tensor(P * padded, xs.dtype).view(P, pe)
+        if pe != cnt:
+            stage[:, cnt:].zero_()
+        stage[:, :cnt].copy_(xs[:, done:done + cnt])
+        direct = pe == cnt
+        dst = out[done:done + cnt] if direct else torch.empty(pe, dtype=xs.dtype, device=xs.device)
+        steps = ctypes.c_int(0)
+        _native.launch_count += 1
+        _native.check(lib.dd_mc_allreduce(P, h.rank, pads, (mc.steps_done + 1) & 0xFFFFFFFF, 0, 0, dst.data_ptr(),
+                                          padded, _DT[xs.dtype], 2, 0, ctypes.byref(steps), stream_ptr()),
+                      "dd_mc_allreduce")
+        mc.steps_done += steps.value
+        if not direct:
+            out[done:done + cnt].copy_(dst[:cnt])
+        done += cnt
 
 
 def reduce_scatter_accumulate_(x: torch.Tensor, acc: torch.Tensor, ranks, scale: float = 1.0) -> bool:

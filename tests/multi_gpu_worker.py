@@ -188,6 +188,16 @@ def check_multimem_allreduce():
                     err = (got - want).abs().max().item() / (want.abs().max().item() + 1e-6)
                     if not err < tol:
                         problems.append((str(dtype), n, rep, err))
+        for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+            for n in (512, 40_000, 2_000_003):
+                torch.manual_seed(200 + rank)
+                x = (torch.rand(world, n, device=dev) * 2 - 1).to(dtype)
+                want = x.float().clone()
+                dist.all_reduce(want)
+                got = collectives.reduce_scatter(x, list(range(world))).float()
+                err = (got - want[rank]).abs().max().item() / (want.abs().max().item() + 1e-6)
+                if not err < tol:
+                    problems.append(("reduce_scatter", str(dtype), n, err))
         status = _native.read_status()
         if status[0]:
             problems.append(("device status", status))
