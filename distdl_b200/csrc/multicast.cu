@@ -330,8 +330,13 @@ mc_allreduce_kernel(const McTeam t, char* mc_base, char* uc_base, size_t in_off,
     multimem_st(mc_base + out_off + (v << 4), r);
   }
   if (!mc_barrier(t, 1, &fail)) return;                 // all slices have been written everywhere
-  for (size_t v = tid; v < nvec; v += stride)
-    *reinterpret_cast<uint4*>(out + (v << 4)) = ld_cg16(uc_base + out_off + (v << 4));
+  // The barrier pairs CTA b of this GPU with CTA b of every other GPU only: read, of every member's
+  // slice, exactly the vectors that the same-numbered CTA of that member wrote.
+  for (int i = 0; i < t.n; ++i) {
+    const size_t lo_i = per * i, hi_i = lo_i + per < nvec ? lo_i + per : nvec;
+    for (size_t v = lo_i + tid; v < hi_i; v += stride)
+      *reinterpret_cast<uint4*>(out + (v << 4)) = ld_cg16(uc_base + out_off + (v << 4));
+  }
 }
 
 }  // namespace
