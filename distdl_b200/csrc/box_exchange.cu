@@ -44,7 +44,7 @@ constexpr int kBoxBufs = 4;
 constexpr int kBoxMaxItems = 48;
 constexpr int kBoxCtas = 128;           // half send, half receive
 constexpr int kBoxThreads = 256;
-constexpr unsigned long long kPieceBytes = 32 * 1024;
+constexpr unsigned long long kPieceBytes = 128 * 1024;
 // word offsets inside a signal pad (uint32 units); [0, 1104) belong to the collectives and the fused GEMMs
 constexpr int PAD_BOX_DELIVERED = 1104;   // [buf * 8 + writer]
 constexpr int PAD_BOX_CONSUMED = 1136;    // [buf * 8 + writer]
@@ -213,6 +213,12 @@ __device__ __forceinline__ uint4 ld_cg16(const void* p) {
 
 // Address of row r (all outer indices folded into one number) of a box.
 __device__ __forceinline__ char* row_addr(const Box& x, unsigned long long r) {
+  if (r <= 0xffffffffull) {             // 32-bit divisions are several times cheaper
+    const unsigned r32 = (unsigned)r, n2 = (unsigned)x.n[2], n1 = (unsigned)x.n[1];
+    const unsigned i2 = r32 % n2, t = r32 / n2;
+    const unsigned i1 = t % n1, i0 = t / n1;
+    return x.base + (long long)i0 * x.s[0] + (long long)i1 * x.s[1] + (long long)i2 * x.s[2];
+  }
   const unsigned long long i2 = r % (unsigned long long)x.n[2];
   const unsigned long long t = r / (unsigned long long)x.n[2];
   const unsigned long long i1 = t % (unsigned long long)x.n[1];
@@ -220,68 +226,74 @@ __device__ __forceinline__ char* row_addr(const Box& x, unsigned long long r) {
   return x.base + (long long)i0 * x.s[0] + (long long)i1 * x.s[1] + (long long)i2 * x.s[2];
 }
 
+// A thread's walk through the units g, g + T, g + 2T, ... of a box (T = threads of the CTA): the row
+// and the position inside the row are carried along, so that the divisions of the index arithmetic
+// are paid once per thread (and once more only where a step crosses rows of fewer than T units).
+struct Cursor {
+  unsigned long long row;
+  unsigned col;
+  char* rowp;
+};
+__device__ __forceinline__ Cursor cursor_at(const Box& x, unsigned long long g) {
+  Cursor c;
+  const unsigned n3 = (unsigned)x.n[3];
+  c.row = g / n3;
+  c.col = (unsigned)(g - c.row * n3);
+  c.rowp = row_addr(x, c.row);
+  return c;
+}
+__device__ __forceinline__ void cursor_step(const Box& x, Cursor& c, unsigned step) {
+  const unsigned n3 = (unsigned)x.n[3];
+  c.col += step;
+  if (c.col >= n3) {
+    const unsigned adv = c.col / n3;
+    c.row += adv;
+    c.col -= adv * n3;
+    c.rowp = row_addr(x, c.row);
+  }
+}
+
 // body(box address, unit index g) for every unit g in [lo_u, hi_u) of the box, the threads of the CTA
-// sharing the work.  Rows of 8 units or more: one warp per row and the lanes along it, so that
-// the index arithmetic (divisions) is paid once per row and the accesses of a warp are contiguous.
-// Shorter rows: one unit per thread, with 32-bit arithmetic where the message allows it.
+// sharing the work: consecutive threads take consecutive units (contiguous inside a row).
 template <typename Body>
 __device__ __forceinline__ void walk_units(const Box& x, int unit, unsigned long long lo_u, unsigned long long hi_u,
                                            Body body) {
-  if (hi_u <= lo_u) return;
-  const unsigned n3 = (unsigned)x.n[3];
-  if (n3 >= 8) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const unsigned long long r0 = lo_u / n3, r1 = (hi_u - 1) / n3;
-    for (unsigned long long r = r0 + warp; r <= r1; r += kBoxThreads / 32) {
-      char* rowp = row_addr(x, r);
-      const unsigned ub = r == r0 ? (unsigned)(lo_u - r * n3) : 0u;
-      const unsigned ue = r == r1 ? (unsigned)(hi_u - r * n3) : n3;
-      for (unsigned u = ub + lane; u < ue; u += 32) body(rowp + (size_t)u * unit, r * n3 + u);
-    }
-  } else if (hi_u <= 0xffffffffull) {
-    const unsigned n2 = (unsigned)x.n[2], n1 = (unsigned)x.n[1];
-    for (unsigned g = (unsigned)lo_u + threadIdx.x; g < (unsigned)hi_u; g += kBoxThreads) {
-      const unsigned i3 = g % n3;
-      unsigned t = g / n3;
-      const unsigned i2 = t % n2;
-      t /= n2;
-      const unsigned i1 = t % n1, i0 = t / n1;
-      body(x.base + (long long)i0 * x.s[0] + (long long)i1 * x.s[1] + (long long)i2 * x.s[2] + (long long)i3 * unit, g);
-    }
-  } else {
-    for (unsigned long long g = lo_u + threadIdx.x; g < hi_u; g += kBoxThreads) body(unit_addr(x, unit, g), g);
+  unsigned long long g = lo_u + threadIdx.x;
+  if (g >= hi_u) return;
+  Cursor c = cursor_at(x, g);
+  for (; g < hi_u; g += kBoxThreads) {
+    body(c.rowp + (size_t)c.col * unit, g);
+    cursor_step(x, c, kBoxThreads);
   }
 }
 
 // Plain copy in 16-byte units between a box and a contiguous buffer (`lin` = address of unit 0),
-// a warp per row, four vectors per lane in flight.  TO_BOX: the contiguous side is an inbox that
-// another GPU wrote (read at L2).  Rows of at least 8 units.
+// four vectors per thread in flight.  TO_BOX: the contiguous side is an inbox that another GPU
+// wrote (read at L2).
 template <bool TO_BOX>
 __device__ __forceinline__ void copy16_rows(const Box& x, char* lin, unsigned long long lo_u,
                                             unsigned long long hi_u) {
-  if (hi_u <= lo_u) return;
-  const unsigned n3 = (unsigned)x.n[3];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const unsigned long long r0 = lo_u / n3, r1 = (hi_u - 1) / n3;
-  for (unsigned long long r = r0 + warp; r <= r1; r += kBoxThreads / 32) {
-    char* rowp = row_addr(x, r);
-    char* linp = lin + ((r * n3) << 4);
-    const unsigned ub = r == r0 ? (unsigned)(lo_u - r * n3) : 0u;
-    const unsigned ue = r == r1 ? (unsigned)(hi_u - r * n3) : n3;
-    for (unsigned u = ub + lane; u < ue; u += 128) {
-      uint4 v[4];
+  unsigned long long g = lo_u + threadIdx.x;
+  if (g >= hi_u) return;
+  Cursor c = cursor_at(x, g);
+  for (; g < hi_u; g += 4ull * kBoxThreads) {
+    uint4 v[4];
+    char* addr[4];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const unsigned uu = u + 32 * q;
-        if (uu < ue) v[q] = TO_BOX ? ld_cg16(linp + ((size_t)uu << 4)) : *reinterpret_cast<const uint4*>(rowp + ((size_t)uu << 4));
+    for (int q = 0; q < 4; ++q) {
+      const unsigned long long gq = g + (unsigned long long)q * kBoxThreads;
+      addr[q] = c.rowp + ((size_t)c.col << 4);
+      if (gq < hi_u) {
+        v[q] = TO_BOX ? ld_cg16(lin + (gq << 4)) : *reinterpret_cast<const uint4*>(addr[q]);
+        cursor_step(x, c, kBoxThreads);
       }
+    }
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const unsigned uu = u + 32 * q;
-        if (uu < ue) {
-          if (TO_BOX) *reinterpret_cast<uint4*>(rowp + ((size_t)uu << 4)) = v[q];
-          else *reinterpret_cast<uint4*>(linp + ((size_t)uu << 4)) = v[q];
-        }
+    for (int q = 0; q < 4; ++q) {
+      const unsigned long long gq = g + (unsigned long long)q * kBoxThreads;
+      if (gq < hi_u) {
+        if (TO_BOX) *reinterpret_cast<uint4*>(addr[q]) = v[q];
+        else *reinterpret_cast<uint4*>(lin + (gq << 4)) = v[q];
       }
     }
   }
@@ -360,7 +372,7 @@ __global__ void __launch_bounds__(kBoxThreads) box_exchange_kernel(const __grid_
           const bool clear = m.clear_source != 0;
           StatusRecord* st = A.status;
 #ifndef DD_BOUNDS_CHECK
-          if (unit == 16 && !clear && m.a.n[3] >= 8) {
+          if (unit == 16 && !clear) {
             copy16_rows<false>(m.a, dst, lo / 16, hi / 16);
           } else
 #endif
@@ -377,7 +389,7 @@ __global__ void __launch_bounds__(kBoxThreads) box_exchange_kernel(const __grid_
           StatusRecord* st = A.status;
           const Box& bx = m.a;
 #ifndef DD_BOUNDS_CHECK
-          if (unit == 16 && add == kAddNone && bx.n[3] >= 8) {
+          if (unit == 16 && add == kAddNone) {
             copy16_rows<true>(bx, src, lo / 16, hi / 16);
           } else
 #endif
@@ -407,13 +419,21 @@ __global__ void __launch_bounds__(kBoxThreads) box_exchange_kernel(const __grid_
           StatusRecord* st = A.status;
           const Box& ba = m.a;
           const Box& bb = m.b;
-          if (ra == 1 && rb == 1 && ba.n[3] == bb.n[3]) {
-            // rows of the two boxes correspond: walk the source, address the destination row-wise
-            const unsigned n3 = (unsigned)ba.n[3];
-            walk_units(ba, unit, lo / unit, hi / unit, [&](char* from, unsigned long long g) {
-              char* to = row_addr(bb, g / n3) + (size_t)(g % n3) * unit;
-              if (in_bounds(bb, to, unit, st, g) && in_bounds(ba, from, unit, st, g)) move_unit(to, from, unit, kAddNone, false);
-            });
+          if (ra == 1 && rb == 1) {
+            // the same unit on both sides: one cursor per box, stepped together
+            unsigned long long g = lo / unit + threadIdx.x;
+            const unsigned long long g_end = hi / unit;
+            if (g < g_end) {
+              Cursor ca = cursor_at(ba, g), cb = cursor_at(bb, g);
+              for (; g < g_end; g += kBoxThreads) {
+                char* from = ca.rowp + (size_t)ca.col * unit;
+                char* to = cb.rowp + (size_t)cb.col * unit;
+                if (in_bounds(bb, to, unit, st, g) && in_bounds(ba, from, unit, st, g))
+                  move_unit(to, from, unit, kAddNone, false);
+                cursor_step(ba, ca, kBoxThreads);
+                cursor_step(bb, cb, kBoxThreads);
+              }
+            }
           } else {
             for (unsigned long long g = lo / unit + threadIdx.x; g < hi / unit; g += kBoxThreads) {
               char* to = unit_addr(bb, m.unit_b, g / rb) + (g % rb) * unit;

@@ -259,6 +259,28 @@ __device__ __forceinline__ void multimem_st(void* mc, const uint4& v) {
                ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// store(v, sum) for the vectors v = lo + tid, + stride, ... < hi, where sum is the job-wide sum of the
+// 16-byte vector at byte offset `base + 16 v` of the multicast region; kMcDepth reductions per thread
+// are in flight before the first store (the switch's round trip is a few microseconds).
+constexpr int kMcDepth = 8;
+template <bool BF16, typename Store>
+__device__ __forceinline__ void mc_reduce_loop(const char* mc, size_t lo, size_t hi, size_t tid, size_t stride,
+                                               Store store) {
+  for (size_t v = lo + tid; v < hi; v += kMcDepth * stride) {
+    uint4 r[kMcDepth];
+#pragma unroll
+    for (int q = 0; q < kMcDepth; ++q) {
+      const size_t vq = v + q * stride;
+      if (vq < hi) r[q] = BF16 ? multimem_ld_reduce_bf16(mc + (vq << 4)) : multimem_ld_reduce_f32(mc + (vq << 4));
+    }
+#pragma unroll
+    for (int q = 0; q < kMcDepth; ++q) {
+      const size_t vq = v + q * stride;
+      if (vq < hi) store(vq, r[q]);
+    }
+  }
+}
+
 // Barrier number `step` of this launch between CTA blockIdx.x of all GPUs (counters only
 // grow; bounded wait).  Returns false after a time-out.
 __device__ bool mc_barrier(const McTeam& t, uint32_t step, int* sh_fail) {
@@ -305,37 +327,36 @@ mc_allreduce_kernel(const McTeam t, char* mc_base, char* uc_base, size_t in_off,
   if (one_shot == 2) {
     // reduce-scatter: `bytes` is one member's slice; member i's slice is the i-th of every input
     const size_t base = in_off + (size_t)t.me * bytes;
-    for (size_t v = tid; v < nvec; v += stride) {
-      const uint4 r = BF16 ? multimem_ld_reduce_bf16(mc_base + base + (v << 4))
-                           : multimem_ld_reduce_f32(mc_base + base + (v << 4));
-      *reinterpret_cast<uint4*>(out + (v << 4)) = r;
-    }
+    mc_reduce_loop<BF16>(mc_base + base, 0, nvec, tid, stride,
+                         [&](size_t v, const uint4& r) { *reinterpret_cast<uint4*>(out + (v << 4)) = r; });
     mc_barrier(t, 1, &fail);
     return;
   }
   if (one_shot) {
-    for (size_t v = tid; v < nvec; v += stride) {
-      const uint4 r = BF16 ? multimem_ld_reduce_bf16(mc_base + in_off + (v << 4))
-                           : multimem_ld_reduce_f32(mc_base + in_off + (v << 4));
-      *reinterpret_cast<uint4*>(out + (v << 4)) = r;
-    }
+    mc_reduce_loop<BF16>(mc_base + in_off, 0, nvec, tid, stride,
+                         [&](size_t v, const uint4& r) { *reinterpret_cast<uint4*>(out + (v << 4)) = r; });
     mc_barrier(t, 1, &fail);                            // nobody overwrites its input before all have read
     return;
   }
   const size_t per = (nvec + t.n - 1) / t.n;
   const size_t lo = per * t.me, hi = lo + per < nvec ? lo + per : nvec;
-  for (size_t v = lo + tid; v < hi; v += stride) {
-    const uint4 r = BF16 ? multimem_ld_reduce_bf16(mc_base + in_off + (v << 4))
-                         : multimem_ld_reduce_f32(mc_base + in_off + (v << 4));
-    multimem_st(mc_base + out_off + (v << 4), r);
-  }
+  char* mc_out = mc_base + out_off;
+  mc_reduce_loop<BF16>(mc_base + in_off, lo, hi, tid, stride,
+                       [&](size_t v, const uint4& r) { multimem_st(mc_out + (v << 4), r); });
   if (!mc_barrier(t, 1, &fail)) return;                 // all slices have been written everywhere
   // The barrier pairs CTA b of this GPU with CTA b of every other GPU only: read, of every member's
   // slice, exactly the vectors that the same-numbered CTA of that member wrote.
   for (int i = 0; i < t.n; ++i) {
     const size_t lo_i = per * i, hi_i = lo_i + per < nvec ? lo_i + per : nvec;
-    for (size_t v = lo_i + tid; v < hi_i; v += stride)
-      *reinterpret_cast<uint4*>(out + (v << 4)) = ld_cg16(uc_base + out_off + (v << 4));
+    for (size_t v = lo_i + tid; v < hi_i; v += 4 * stride) {
+      uint4 r[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        if (v + q * stride < hi_i) r[q] = ld_cg16(uc_base + out_off + ((v + q * stride) << 4));
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        if (v + q * stride < hi_i) *reinterpret_cast<uint4*>(out + ((v + q * stride) << 4)) = r[q];
+    }
   }
 }
 
