@@ -44,7 +44,9 @@ constexpr int kBoxBufs = 4;
 constexpr int kBoxMaxItems = 48;
 constexpr int kBoxCtas = 128;           // half send, half receive
 constexpr int kBoxThreads = 256;
-constexpr unsigned long long kPieceBytes = 128 * 1024;
+// bytes that one CTA moves between two looks at the flags: larger where 16-byte units stream,
+// smaller where single elements are gathered (more CTAs share a face)
+__host__ __device__ constexpr unsigned long long piece_bytes_for(int unit) { return unit == 16 ? 128 * 1024 : 16 * 1024; }
 // word offsets inside a signal pad (uint32 units); [0, 1104) belong to the collectives and the fused GEMMs
 constexpr int PAD_BOX_DELIVERED = 1104;   // [buf * 8 + writer]
 constexpr int PAD_BOX_CONSUMED = 1136;    // [buf * 8 + writer]
@@ -299,6 +301,46 @@ __device__ __forceinline__ void copy16_rows(const Box& x, char* lin, unsigned lo
   }
 }
 
+// The same for units of 1, 2, 4 or 8 bytes (U = an unsigned integer type of that size): eight units per
+// thread in flight, which is what a gather of single elements along a strided direction needs.
+template <typename U, bool TO_BOX>
+__device__ __forceinline__ void copy_small(const Box& x, char* lin, unsigned long long lo_u, unsigned long long hi_u) {
+  unsigned long long g = lo_u + threadIdx.x;
+  if (g >= hi_u) return;
+  Cursor c = cursor_at(x, g);
+  for (; g < hi_u; g += 8ull * kBoxThreads) {
+    U v[8];
+    char* addr[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const unsigned long long gq = g + (unsigned long long)q * kBoxThreads;
+      addr[q] = c.rowp + (size_t)c.col * sizeof(U);
+      if (gq < hi_u) {
+        v[q] = TO_BOX ? *reinterpret_cast<const volatile U*>(lin + gq * sizeof(U)) : *reinterpret_cast<const U*>(addr[q]);
+        cursor_step(x, c, kBoxThreads);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const unsigned long long gq = g + (unsigned long long)q * kBoxThreads;
+      if (gq < hi_u) {
+        if (TO_BOX) *reinterpret_cast<U*>(addr[q]) = v[q];
+        else *reinterpret_cast<U*>(lin + gq * sizeof(U)) = v[q];
+      }
+    }
+  }
+}
+template <bool TO_BOX>
+__device__ __forceinline__ void copy_small_any(const Box& x, int unit, char* lin, unsigned long long lo_u,
+                                               unsigned long long hi_u) {
+  switch (unit) {
+    case 1: copy_small<uint8_t, TO_BOX>(x, lin, lo_u, hi_u); break;
+    case 2: copy_small<uint16_t, TO_BOX>(x, lin, lo_u, hi_u); break;
+    case 4: copy_small<uint32_t, TO_BOX>(x, lin, lo_u, hi_u); break;
+    default: copy_small<uint64_t, TO_BOX>(x, lin, lo_u, hi_u); break;
+  }
+}
+
 // Thread 0 waits (bounded) until the counter at p has reached `want`; every thread of the CTA
 // learns the outcome.  SYS: the counter is written by another GPU.
 template <bool SYS>
@@ -354,6 +396,7 @@ __global__ void __launch_bounds__(kBoxThreads) box_exchange_kernel(const __grid_
     for (unsigned long long c = 0; c < nchunks; ++c) {
       const unsigned long long c_lo = m.kind == kLocal ? 0 : c * A.chunk_bytes;
       const unsigned long long c_hi = m.kind == kLocal ? m.bytes : (c_lo + A.chunk_bytes < m.bytes ? c_lo + A.chunk_bytes : m.bytes);
+      const unsigned long long kPieceBytes = piece_bytes_for(m.kind == kLocal ? (m.unit < m.unit_b ? m.unit : m.unit_b) : m.unit);
       const unsigned pieces = (unsigned)((c_hi - c_lo + kPieceBytes - 1) / kPieceBytes);
       const unsigned seq = m.first_seq + (unsigned)c;
       const int buf = seq % kBoxBufs;
@@ -374,6 +417,8 @@ __global__ void __launch_bounds__(kBoxThreads) box_exchange_kernel(const __grid_
 #ifndef DD_BOUNDS_CHECK
           if (unit == 16 && !clear) {
             copy16_rows<false>(m.a, dst, lo / 16, hi / 16);
+          } else if (unit != 16 && !clear) {
+            copy_small_any<false>(m.a, unit, dst, lo / unit, hi / unit);
           } else
 #endif
           {
@@ -391,6 +436,8 @@ __global__ void __launch_bounds__(kBoxThreads) box_exchange_kernel(const __grid_
 #ifndef DD_BOUNDS_CHECK
           if (unit == 16 && add == kAddNone) {
             copy16_rows<true>(bx, src, lo / 16, hi / 16);
+          } else if (unit != 16 && add == kAddNone) {
+            copy_small_any<true>(bx, unit, src, lo / unit, hi / unit);
           } else
 #endif
           if (unit == 16) {
@@ -478,7 +525,7 @@ DD_API int dd_bounds_checked() { return 0; }
 #endif
 DD_API int dd_box_max_items() { return kBoxMaxItems; }
 DD_API int dd_box_bufs() { return kBoxBufs; }
-DD_API int dd_box_piece_bytes() { return (int)kPieceBytes; }
+DD_API int dd_box_piece_bytes(int unit) { return (int)piece_bytes_for(unit); }
 DD_API int dd_box_item_bytes() { return (int)sizeof(BoxItem); }
 
 // items: n_items BoxItem records in the layout of this file (see parallel/box_exchange.py);

@@ -534,25 +534,38 @@ moe_scatter_peer_kernel(const Team t, const MoeGeom g, const __nv_bfloat16* __re
   __shared__ int fail;
   if (threadIdx.x == 0) fail = 0;
   if (!team_barrier(t, 0, &fail)) return;
+  // one warp per (token, choice) pair: the row's 16-byte vectors are spread over the lanes and eight
+  // of them per lane are in flight before the first store
   const int dv = g.d >> 3;
-  const long long total = (long long)npairs * dv;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int p = (int)(i / dv);
-    const int c = (int)(i - (long long)p * dv) * 8;
+  const int lane = threadIdx.x & 31;
+  const int wpb = kThreads / 32;
+  for (int p = blockIdx.x * wpb + (threadIdx.x >> 5); p < npairs; p += gridDim.x * wpb) {
     const int s = slot[p];
     if (s < 0) continue;
     const int e = ids[p];
-    const uint4 u = *reinterpret_cast<const uint4*>(src + (size_t)(p / g.k) * g.d + c);
-    uint4 o = u;
-    if (w != nullptr) {
-      const float sc = w[p];
-      float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), cc = unpack_bf16x2(u.z), ee = unpack_bf16x2(u.w);
-      o.x = pack_bf16x2(a.x * sc, a.y * sc); o.y = pack_bf16x2(b.x * sc, b.y * sc);
-      o.z = pack_bf16x2(cc.x * sc, cc.y * sc); o.w = pack_bf16x2(ee.x * sc, ee.y * sc);
+    const float sc = w != nullptr ? w[p] : 1.f;
+    const __nv_bfloat16* from = src + (size_t)(p / g.k) * g.d;
+    __nv_bfloat16* to = reinterpret_cast<__nv_bfloat16*>(t.buf[e / g.El]) + moe_row_offset(g, e, g.me, s);
+    for (int v0 = lane; v0 < dv; v0 += 32 * 8) {
+      uint4 u[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const int v = v0 + 32 * q;
+        if (v < dv) u[q] = *reinterpret_cast<const uint4*>(from + v * 8);
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const int v = v0 + 32 * q;
+        if (v >= dv) continue;
+        uint4 o = u[q];
+        if (w != nullptr) {
+          float2 a = unpack_bf16x2(o.x), b = unpack_bf16x2(o.y), cc = unpack_bf16x2(o.z), ee = unpack_bf16x2(o.w);
+          o.x = pack_bf16x2(a.x * sc, a.y * sc); o.y = pack_bf16x2(b.x * sc, b.y * sc);
+          o.z = pack_bf16x2(cc.x * sc, cc.y * sc); o.w = pack_bf16x2(ee.x * sc, ee.y * sc);
+        }
+        *reinterpret_cast<uint4*>(to + v * 8) = o;
+      }
     }
-    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(t.buf[e / g.El]) + moe_row_offset(g, e, g.me, s) + c;
-    *reinterpret_cast<uint4*>(dst) = o;
   }
   __threadfence_system();
   team_barrier(t, 1, &fail);
@@ -564,27 +577,51 @@ moe_gather_peer_kernel(const Team t, const MoeGeom g, const int* __restrict__ id
   __shared__ int fail;
   if (threadIdx.x == 0) fail = 0;
   if (!team_barrier(t, 0, &fail)) return;
+  // one warp per token: for every choice the owner's row is read from peer memory, four vectors per
+  // lane and choice in flight, and folded into the token's output row
   const int dv = g.d >> 3;
-  const long long total = (long long)tokens * dv;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int tok = (int)(i / dv);
-    const int c = (int)(i - (long long)tok * dv) * 8;
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int j = 0; j < g.k; ++j) {
-      const int p = tok * g.k + j;
-      const int s = slot[p];
-      if (s < 0) continue;
-      const int e = ids[p];
-      const float sc = w ? w[p] : 1.f;
-      const uint4 u = ld_peer(reinterpret_cast<const __nv_bfloat16*>(t.buf[e / g.El]) + moe_row_offset(g, e, g.me, s) + c);
-      float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), cc = unpack_bf16x2(u.z), ee = unpack_bf16x2(u.w);
-      acc[0] += sc * a.x; acc[1] += sc * a.y; acc[2] += sc * b.x; acc[3] += sc * b.y;
-      acc[4] += sc * cc.x; acc[5] += sc * cc.y; acc[6] += sc * ee.x; acc[7] += sc * ee.y;
+  const int lane = threadIdx.x & 31;
+  const int wpb = kThreads / 32;
+  for (int tok = blockIdx.x * wpb + (threadIdx.x >> 5); tok < tokens; tok += gridDim.x * wpb) {
+    for (int v0 = lane; v0 < dv; v0 += 32 * 4) {
+      float acc[4][8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[q][j] = 0.f;
+      for (int j = 0; j < g.k; ++j) {
+        const int p = tok * g.k + j;
+        const int s = slot[p];
+        if (s < 0) continue;
+        const int e = ids[p];
+        const float sc = w ? w[p] : 1.f;
+        const __nv_bfloat16* row =
+            reinterpret_cast<const __nv_bfloat16*>(t.buf[e / g.El]) + moe_row_offset(g, e, g.me, s);
+        uint4 u[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int v = v0 + 32 * q;
+          if (v < dv) u[q] = ld_peer(row + v * 8);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int v = v0 + 32 * q;
+          if (v >= dv) continue;
+          float2 a = unpack_bf16x2(u[q].x), b = unpack_bf16x2(u[q].y), cc = unpack_bf16x2(u[q].z),
+                 ee = unpack_bf16x2(u[q].w);
+          acc[q][0] += sc * a.x; acc[q][1] += sc * a.y; acc[q][2] += sc * b.x; acc[q][3] += sc * b.y;
+          acc[q][4] += sc * cc.x; acc[q][5] += sc * cc.y; acc[q][6] += sc * ee.x; acc[q][7] += sc * ee.y;
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int v = v0 + 32 * q;
+        if (v < dv)
+          *reinterpret_cast<uint4*>(dst + (size_t)tok * g.d + v * 8) =
+              make_uint4(pack_bf16x2(acc[q][0], acc[q][1]), pack_bf16x2(acc[q][2], acc[q][3]),
+                         pack_bf16x2(acc[q][4], acc[q][5]), pack_bf16x2(acc[q][6], acc[q][7]));
+      }
     }
-    *reinterpret_cast<uint4*>(dst + (size_t)tok * g.d + c) =
-        make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
-                   pack_bf16x2(acc[6], acc[7]));
   }
   team_barrier(t, 1, &fail);
 }

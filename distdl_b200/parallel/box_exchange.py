@@ -36,7 +36,7 @@ _native.declare("dd_box_bufs", [])
 _native.declare("dd_box_item_bytes", [])
 _native.declare("dd_box_copy_host", [_v, _v])
 _native.declare("dd_box_progress", [ctypes.POINTER(_u)])
-_native.declare("dd_box_piece_bytes", [])
+_native.declare("dd_box_piece_bytes", [_i])
 
 SEND, RECV, LOCAL = 0, 1, 2
 _ADD = {torch.float32: 1, torch.bfloat16: 2, torch.float16: 3, torch.float64: 4}
@@ -106,7 +106,7 @@ class _State:
         lib = _native.lib()
         self.max_items = lib.dd_box_max_items()
         self.bufs = lib.dd_box_bufs()
-        self.piece = int(lib.dd_box_piece_bytes())
+        self.piece = {u: int(lib.dd_box_piece_bytes(u)) for u in (1, 2, 4, 8, 16)}
         assert lib.dd_box_item_bytes() == ctypes.sizeof(BoxItem), "BoxItem layout differs from the library's"
         off, size = self.h.regions["inbox"]
         self.slot = (size // MAX_PEERS) // 256 * 256
@@ -134,7 +134,8 @@ def _limits():
         return st.max_items, st.chunk, st.piece
     lib = _native.lib()
     slot = (dict(symm.REGION_SIZES)["inbox"] // MAX_PEERS) // 256 * 256
-    return lib.dd_box_max_items(), (slot // lib.dd_box_bufs()) // 256 * 256, int(lib.dd_box_piece_bytes())
+    return (lib.dd_box_max_items(), (slot // lib.dd_box_bufs()) // 256 * 256,
+            {u: int(lib.dd_box_piece_bytes(u)) for u in (1, 2, 4, 8, 16)})
 
 
 def pieces_of(nbytes: int, chunk: int, piece: int, local: bool = False) -> int:
@@ -206,7 +207,7 @@ class BoxPlan:
                         needs_tmp = True
                         continue
                     recs.append((LOCAL, -1, s_slot, so, sg, sb, 0, 0, d_slot, do, dg))
-                    pieces += pieces_of(sb, chunk, piece, local=True)
+                    pieces += pieces_of(sb, chunk, piece[min(sg[2], dg[2])], local=True)
                     continue
                 kind, peer, slot, sl, flag = op
                 off, nbytes, geo, bshape = self._geometry(metas[slot], sl)
@@ -220,7 +221,10 @@ class BoxPlan:
                 else:
                     recs.append((SEND if kind == "send" else RECV, int(peer), slot, off, geo, nbytes,
                                  int(bool(flag)) if kind == "send" else 0, add_code, None, 0, None))
-                pieces += pieces_of(nbytes, chunk, piece)
+                # (an op that goes through a contiguous temporary moves it in 16-byte units where the size allows)
+                eff_unit = geo[2] if (geo is not None and add_code >= 0) else \
+                    (16 if nbytes % 16 == 0 else torch.empty((), dtype=dtype).element_size())
+                pieces += pieces_of(nbytes, chunk, piece[eff_unit])
             n_new = sum(1 for r in recs if r[0] != "torch_copy")
             if needs_tmp or len(items) + n_new > max_items or phase_in_launch >= 8:
                 flush()

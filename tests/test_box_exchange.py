@@ -70,14 +70,14 @@ def test_plans_are_cut_into_launches_where_the_kernel_cannot_take_a_box():
     assert len(launches) == 1
     items, phase_pieces, pre, post = launches[0]
     assert [it[-1] for it in items] == [0, 0, 1, 1] and not pre and not post
-    assert phase_pieces == [2 * pieces_of(4 * 6 * 8 * 4, chunk, piece), 2 * pieces_of(x.numel() * 4, chunk, piece)]
+    assert phase_pieces == [2 * pieces_of(4 * 6 * 8 * 4, chunk, piece[4]), 2 * pieces_of(x.numel() * 4, chunk, piece[16])]
     # an integer tensor cannot be added by the kernel: that phase runs through a temporary, alone in its launch
     xi = torch.zeros(4, 6, dtype=torch.int32)
     plan = BoxPlan([[("send", 1, "x", None, False)], [("recv", 1, "x", None, True)], [("send", 1, "x", None, False)]])
     launches = plan._compile({"x": BoxPlan._meta(xi)})
     assert len(launches) == 3 and launches[1][3] and launches[1][3][0][0] == "tmp_recv"
     # a message larger than a chunk advances the progress counter by all its pieces
-    assert pieces_of(chunk + 1, chunk, piece) == chunk // piece + 1
+    assert pieces_of(chunk + 1, chunk, piece[16]) == chunk // piece[16] + 1
 
 
 class _HostBoxPlan:
