@@ -29,14 +29,15 @@ import torch.distributed as dist
 NVLINK_GBS = 770.0           # measured peer-copy bandwidth per direction and GPU on this pool
 
 
-def _peak_tflops():
+def _peaks():
     path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
                         "MEASURED_PEAKS.json")
     try:
         with open(path) as fh:
-            return float(json.load(fh)["bf16_tflops_sustained"]), "measured"
+            d = json.load(fh)
+            return float(d["bf16_tflops_sustained"]), float(d["hbm_gbs"]), "measured"
     except (OSError, ValueError, KeyError):
-        return 1400.0, "fallback"
+        return 1400.0, 6650.0, "fallback"
 
 
 _flush = None
@@ -79,16 +80,17 @@ def main():
     rank, P = dist.get_rank(), dist.get_world_size()
     dev = torch.device("cuda", torch.cuda.current_device())
     ranks = tuple(range(P))
-    peak, kind = _peak_tflops()
+    peak, hbm, kind = _peaks()
     rows = []
 
-    def add(name, what, flops, nvlink_bytes, ms):
+    def add(name, what, flops, nvlink_bytes, ms, hbm_bytes=0.0):
         t_c = flops / (peak * 1e12) * 1e3
         t_n = nvlink_bytes / (NVLINK_GBS * 1e9) * 1e3
-        roof = max(t_c, t_n)
+        t_h = hbm_bytes / (hbm * 1e9) * 1e3
+        roof = max(t_c, t_n, t_h)
+        bound = "compute" if roof == t_c else ("NVLink" if roof == t_n else "HBM")
         rows.append({"path": name, "what": what, "tflop": flops / 1e12, "nvlink_mb": nvlink_bytes / 1e6,
-                     "ms": ms, "roofline_ms": roof, "bound": "compute" if t_c >= t_n else "NVLink",
-                     "fraction": roof / ms})
+                     "ms": ms, "roofline_ms": roof, "bound": bound, "fraction": roof / ms})
 
     b, S, d, F = 4, 4096, 4096, 14336
     s_local = S // P
@@ -131,17 +133,17 @@ def main():
                                                      m2.data_ptr(), pbf.data_ptr(), n, 1e-4, 0.9, 0.95, 1e-8, 0.1, 1,
                                                      None, 1.0, stream_ptr()), "dd_grad_rs_adamw")
     ms = _time(grad_step)
+    # (local traffic of the update itself: master, both moments and the shard gradient read and written,
+    # the bf16 copy written, this GPU's own accumulator slice read)
     add("K4 gradient reduce + AdamW", f"shard of {n / 1e6:.0f} M elements, {P} accumulators", 0.0,
-        (P - 1) * n * 4, ms)
-    rows[-1]["hbm_ms"] = (n * (4 * 7 + 2) + n * 4) / 6.5e12 * 1e3      # local traffic of the update itself
+        (P - 1) * n * 4, ms, hbm_bytes=n * (4 * 8 + 2 + 4))
     # K5: RMSNorm over features split across the team
     xs = torch.randn(b * S // 4, d // P, device=dev).to(torch.bfloat16)
     wn = torch.ones(d // P, device=dev, dtype=torch.bfloat16)
     if split_norm.usable(xs, wn, None, ranks):
         ms = _time(lambda: split_norm.split_norm(xs, wn, None, 1e-5, ranks, d, rms=True))
         add("K5 split-norm statistics", f"[{xs.shape[0]},{d}] over {P} feature shards", 0.0,
-            (P - 1) * xs.shape[0] * 8, ms)
-        rows[-1]["hbm_ms"] = 2 * xs.numel() * 2 / 6.5e12 * 1e3
+            (P - 1) * xs.shape[0] * 8, ms, hbm_bytes=2 * xs.numel() * 2)
     # K6: expert-parallel dispatch and combine (top-2 of P experts, one expert per GPU)
     T, k, E = b * S, 2, P
     C = int(-(-1.25 * T * k / E // 8) * 8)
@@ -159,7 +161,9 @@ def main():
                  "",
                  f"Command: `torchrun --nnodes=1 --nproc-per-node {P} -m distdl_b200.utils.fused_bench --md FILE`.",
                  f"Roofline = max(FLOPs / {peak:.0f} TFLOP/s ({kind} sustained cuBLAS bf16), NVLink bytes per GPU / "
-                 f"{NVLINK_GBS:.0f} GB/s); device time by CUDA events, L2 flushed between launches, max over ranks.",
+                 f"{NVLINK_GBS:.0f} GB/s, local bytes / {hbm:.0f} GB/s ({kind} copy bandwidth)); device time by CUDA "
+                 "events around ONE call (so a path of a few tens of microseconds shows the launch latency of the "
+                 "host, about 0.1 ms, not the kernel), L2 flushed between launches, max over ranks.",
                  "",
                  "| path | case | TFLOP | NVLink MB / GPU | device ms | roofline ms | bound | fraction |",
                  "|---|---|---|---|---|---|---|---|"]
