@@ -48,7 +48,7 @@ class NativeTransport(GroupTransport):
 
     def reduce_scatter(self, chunks, ranks):
         if self._native_ok(chunks[0], ranks) and len({tuple(c.shape) for c in chunks}) == 1:
-            return self._collectives().reduce_scatter(torch.stack([c.contiguous() for c in chunks]), ranks)
+            return self._collectives().reduce_scatter(chunks, ranks)
         return super().reduce_scatter(chunks, ranks)
 
     def allgather_stacked(self, tensor, ranks):

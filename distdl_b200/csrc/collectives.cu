@@ -27,7 +27,7 @@ using namespace dd;
 namespace {
 
 constexpr int kMaxPeers = 8;
-constexpr int kCollectiveCtas = 32;
+constexpr int kCollectiveCtas = 96;        // at most 128: the first 1024 pad words hold [CTA][writer]
 constexpr int kThreads = 512;
 
 struct Team {

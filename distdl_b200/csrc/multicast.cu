@@ -225,8 +225,8 @@ namespace {
 
 constexpr int kMaxPeers = 8;
 constexpr int kMcThreads = 512;
-constexpr int kMcMaxCtas = 48;
-// signal-pad words [1200, 1200 + 64 * 8): one counter per (CTA, writer) for these kernels
+constexpr int kMcMaxCtas = 144;
+// signal-pad words [1200, 1200 + 144 * 8): one counter per (CTA, writer) for these kernels
 constexpr int PAD_MC = 1200;
 
 struct McTeam {
@@ -382,10 +382,10 @@ DD_API int dd_mc_allreduce(int n, int me, void* const* pads, unsigned expect, si
   int err = 0;
   t.status = device_status(&err);
   if (err) return err;
-  // Always the same grid: every CTA owns one counter per peer, and the host counts barrier steps
-  // once for all of them, so all slots have to advance in step from launch to launch.
-  (void)ctas;
-  ctas = kMcMaxCtas;
+  // The caller passes the same grid at every launch of the process (and on every GPU): every CTA
+  // owns one counter per peer, and the host counts barrier steps once for all of them, so all
+  // slots have to advance in step from launch to launch.
+  if (ctas < 1 || ctas > kMcMaxCtas) return DD_ERR_BAD_ARG;
   *steps = 2;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   char* mc = reinterpret_cast<char*>(g_mc.mc_va);

@@ -71,11 +71,10 @@ def _all_reduce_multicast(mc, h, flat, out):
         one_shot = int(nbytes <= MC_ONE_SHOT_BYTES)
         direct = cnt * es == nbytes
         dst = out[done:done + cnt] if direct else torch.empty(nbytes // es, dtype=flat.dtype, device=flat.device)
-        ctas = max(1, min(mc.max_ctas, nbytes // (16 * 512 * 4)))
         steps = ctypes.c_int(0)
         _native.launch_count += 1
         _native.check(lib.dd_mc_allreduce(h.world, h.rank, pads, (mc.steps_done + 1) & 0xFFFFFFFF, 0, half,
-                                          dst.data_ptr(), nbytes, _DT[flat.dtype], one_shot, ctas, ctypes.byref(steps),
+                                          dst.data_ptr(), nbytes, _DT[flat.dtype], one_shot, mc.ctas, ctypes.byref(steps),
                                           stream_ptr()), "dd_mc_allreduce")
         mc.steps_done += steps.value
         if not direct:
@@ -201,50 +200,54 @@ def gather_in_place(x: torch.Tensor, ranks):
     return out
 
 
-def reduce_scatter(x: torch.Tensor, ranks) -> torch.Tensor:
-    """``x`` is ``[P, ...]``: member ``i`` receives the team-wide sum of ``x[i]``."""
+def reduce_scatter(x, ranks) -> torch.Tensor:
+    """``x`` is ``[P, ...]`` (or a list of ``P`` equally shaped tensors): member ``i`` receives the
+    team-wide sum of ``x[i]``.  The slices are copied once, straight into the staging buffer."""
     h = symm.heap()
     ranks = list(ranks)
     P = len(ranks)
-    assert x.shape[0] == P
-    xs = x.contiguous()
-    if xs.dtype not in _DT:
-        xs = xs.float()
-    es = xs.element_size()
-    chunk = xs[0].numel()
-    out = torch.empty(chunk, dtype=xs.dtype, device=x.device)
-    flat = xs.view(P, chunk)
+    assert len(x) == P
+    dtype_in = x[0].dtype
+    rows = [x[i].contiguous().view(-1) for i in range(P)]
+    if dtype_in not in _DT:
+        rows = [r.float() for r in rows]
+    dt = rows[0].dtype
+    es = rows[0].element_size()
+    chunk = rows[0].numel()
+    out = torch.empty(chunk, dtype=dt, device=rows[0].device)
     mc = symm.multicast_region() if P == h.world else None
     if mc is not None:
-        _reduce_scatter_multicast(mc, h, flat, out)
-        return out.view(x.shape[1:]).to(x.dtype)
+        _reduce_scatter_multicast(mc, h, rows, out)
+        return out.view(x[0].shape).to(dtype_in)
     cap_elems = (h.staging_bytes // P) // 16 * 16 // es
     done = 0
     while done < chunk:
         cnt = min(chunk - done, cap_elems)
         padded = (cnt * es + 15) // 16 * 16
         pe = padded // es
-        stage = h.staging_tensor(P * padded, xs.dtype).view(P, pe)
+        stage = h.staging_tensor(P * padded, dt).view(P, pe)
         if pe != cnt:
             stage[:, cnt:].zero_()
-        stage[:, :cnt].copy_(flat[:, done:done + cnt])
+        for i in range(P):
+            stage[i, :cnt].copy_(rows[i][done:done + cnt])
         if pe == cnt:
-            _launch("dd_reducescatter", h, ranks, out[done:done + cnt].data_ptr(), padded, _DT[xs.dtype])
+            _launch("dd_reducescatter", h, ranks, out[done:done + cnt].data_ptr(), padded, _DT[dt])
         else:
-            tmp = torch.empty(pe, dtype=xs.dtype, device=x.device)
-            _launch("dd_reducescatter", h, ranks, tmp.data_ptr(), padded, _DT[xs.dtype])
+            tmp = torch.empty(pe, dtype=dt, device=out.device)
+            _launch("dd_reducescatter", h, ranks, tmp.data_ptr(), padded, _DT[dt])
             out[done:done + cnt].copy_(tmp[:cnt])
         done += cnt
-    return out.view(x.shape[1:]).to(x.dtype)
+    return out.view(x[0].shape).to(dtype_in)
 
 
 def _reduce_scatter_multicast(mc, h, xs, out):
-    """Job-wide reduce-scatter through the multicast region: every GPU stages its whole input in its
+    """Job-wide reduce-scatter (``xs``: the P flat slices) through the multicast region: every GPU stages its whole input in its
     copy, then reads the sum of its own slice with ``multimem.ld_reduce``."""
     symm.require_healthy()
     P = h.world
-    es = xs.element_size()
-    n = xs.shape[1]
+    dt = xs[0].dtype
+    es = xs[0].element_size()
+    n = xs[0].numel()
     cap = (mc.nbytes // P) // 256 * 256
     pads = (ctypes.c_void_p * P)(*h.pad_ptrs)
     lib = _native.lib()
@@ -253,16 +256,17 @@ def _reduce_scatter_multicast(mc, h, xs, out):
         cnt = min(n - done, cap // es)
         padded = (cnt * es + 15) // 16 * 16
         pe = padded // es
-        stage = mc.local_tensor(P * padded, xs.dtype).view(P, pe)
+        stage = mc.local_tensor(P * padded, dt).view(P, pe)
         if pe != cnt:
             stage[:, cnt:].zero_()
-        stage[:, :cnt].copy_(xs[:, done:done + cnt])
+        for i in range(P):
+            stage[i, :cnt].copy_(xs[i][done:done + cnt])
         direct = pe == cnt
-        dst = out[done:done + cnt] if direct else torch.empty(pe, dtype=xs.dtype, device=xs.device)
+        dst = out[done:done + cnt] if direct else torch.empty(pe, dtype=dt, device=out.device)
         steps = ctypes.c_int(0)
         _native.launch_count += 1
         _native.check(lib.dd_mc_allreduce(P, h.rank, pads, (mc.steps_done + 1) & 0xFFFFFFFF, 0, 0, dst.data_ptr(),
-                                          padded, _DT[xs.dtype], 2, 0, ctypes.byref(steps), stream_ptr()),
+                                          padded, _DT[dt], 2, mc.ctas, ctypes.byref(steps), stream_ptr()),
                       "dd_mc_allreduce")
         mc.steps_done += steps.value
         if not direct:

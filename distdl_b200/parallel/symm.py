@@ -309,7 +309,8 @@ class MulticastRegion:
         _native.check(lib.dd_mc_bind_and_map(ctypes.byref(local), ctypes.byref(mc)), "dd_mc_bind_and_map")
         self.local_ptr, self.mc_ptr = local.value, mc.value
         self.steps_done = 0                            # barrier steps consumed by the multicast kernels
-        self.max_ctas = lib.dd_mc_max_ctas()
+        # the grid of every multicast kernel of this process (the per-CTA counters have to advance in step)
+        self.ctas = max(1, min(lib.dd_mc_max_ctas(), int(os.environ.get("DISTDL_MC_CTAS", "96"))))
         dist.barrier()
 
     def local_tensor(self, nbytes, dtype=torch.uint8, offset=0):

@@ -45,6 +45,8 @@ def main():
     ap.add_argument("--json", default=None)
     ap.add_argument("--md", default=None, help="write a markdown summary (native vs NCCL per op and size)")
     ap.add_argument("--multimem", action="store_true", help="native all-reduce through the NVLink multicast region")
+    ap.add_argument("--ops", default="", help="comma-separated subset of the op names (default: all)")
+    ap.add_argument("--backends", default="native,nccl")
     args = ap.parse_args()
     import distdl_b200
     from distdl_b200.backends.common import world as dworld
@@ -52,12 +54,14 @@ def main():
     rank, P = dist.get_rank(), dist.get_world_size()
     dev = torch.device("cuda", torch.cuda.current_device())
     rows = []
+    only = set(filter(None, args.ops.split(",")))
+    want = lambda name: not only or name in only
     sizes = []
     b = 4096
     while b <= args.max_bytes:
         sizes.append(b)
         b *= 4
-    for backend in ("native", "nccl"):
+    for backend in args.backends.split(","):
         distdl_b200.config.set_backend(backend, "cupy")
         from distdl_b200.nn import (AllGather, AllSumReduce, Broadcast, HaloExchange, ReduceScatter, Repartition,
                                     SumReduce)
@@ -81,6 +85,8 @@ def main():
                     ("all_sum_reduce", lambda: ar(x), 2 * (P - 1) / P, nbytes),
                     ("all_gather", lambda: ag(shard), (P - 1) / P, shard.numel() * 2 * P),
                     ("reduce_scatter", lambda: rs(full), (P - 1) / P, full.numel() * 2)):
+                if not want(name):
+                    continue
                 ms = _time(fn)
                 rows.append({"op": name, "backend": backend, "bytes": msg, "ms": ms,
                              "busbw_GBs": msg * factor / ms / 1e6})
@@ -88,17 +94,19 @@ def main():
             bc, sr = Broadcast(P_one, P_flat, preserve_batch=False), SumReduce(P_flat, P_one, preserve_batch=False)
             src = x if rank == 0 else x[:0]
             for name, fn, msg in (("broadcast", lambda: bc(src), nbytes), ("sum_reduce", lambda: sr(x), nbytes)):
+                if not want(name):
+                    continue
                 ms = _time(fn)
                 rows.append({"op": name, "backend": backend, "bytes": msg, "ms": ms, "busbw_GBs": msg / ms / 1e6})
             side = int(math.sqrt(n)) // (8 * P) * (8 * P)
-            if side >= 8 * P:
+            if side >= 8 * P and want("repartition_row_to_col"):
                 m = torch.rand(side // P, side, device=dev).to(torch.bfloat16)
                 rp = Repartition(P_rows, P_cols)
                 ms = _time(lambda: rp(m))
                 msg = side * side * 2
                 rows.append({"op": "repartition_row_to_col", "backend": backend, "bytes": msg, "ms": ms,
                              "busbw_GBs": msg / P * (P - 1) / P / ms / 1e6})
-        if P >= 2:
+        if P >= 2 and want("halo_exchange"):
             py = 2 if P % 2 == 0 and P > 2 else 1
             px = P // py
             P_sp = P_world.create_cartesian_topology_partition([1, 1, py, px])

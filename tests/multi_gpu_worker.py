@@ -546,9 +546,11 @@ def main():
     dworld.init_process_group_from_env()
     distdl_b200.config.set_backend("native", "cupy")
     what = sys.argv[1] if len(sys.argv) > 1 else "collectives"
-    if what in ("collectives", "all"):
+    todo = set(what.split(","))                 # several groups in one launch: "all,activation_policies,multimem"
+    run_all = "all" in todo
+    if run_all or "collectives" in todo:
         check_collectives()
-    if what in ("primitives", "all"):
+    if run_all or "primitives" in todo:
         check_primitives_native()
         check_zero_grad_accumulate()
         check_split_norm()
@@ -558,19 +560,19 @@ def main():
         check_symmetric_params()
         check_overlapped_gradient_step()
         check_moe_peer()
-    if what == "context_decoder":
+    if "context_decoder" in todo:
         check_context_parallel_decoder()
-    if what in ("box", "all"):
+    if run_all or "box" in todo:
         check_box_exchange()
-    if what == "multimem":
-        check_multimem_allreduce()
-    if what == "activation_policies":
+    if "activation_policies" in todo:
         check_activation_policies()
-    if what == "pipeline":
+    if "pipeline" in todo:
         check_pipelined_decoder()
-    if what in ("fused", "all"):
+    if run_all or "fused" in todo:
         from multi_gpu_fused import check_fused
         check_fused()
+    if "multimem" in todo:                      # last: binds the multicast region for the rest of the process
+        check_multimem_allreduce()
     dist.barrier()
     if dist.get_rank() == 0:
         print(f"multi-gpu {what}: OK on {dist.get_world_size()} GPUs")
