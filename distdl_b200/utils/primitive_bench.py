@@ -69,57 +69,63 @@ def main():
             from distdl_b200.parallel import symm
             symm.heap()
             symm.enable_multicast(min(2 * args.max_bytes, 1 << 30) + (4 << 20))
-        P_world = distdl_b200.backends.backend.Partition()
-        P_flat = P_world.create_cartesian_topology_partition([P])
-        P_rows = P_world.create_cartesian_topology_partition([P, 1])
-        P_cols = P_world.create_cartesian_topology_partition([1, P])
-        for nbytes in sizes:
-            n = nbytes // 2
-            torch.manual_seed(1)
-            x = (torch.rand(n, device=dev) * 2 - 1).to(torch.bfloat16)
-            ar, ag, rs = AllSumReduce(P_flat, axes_reduce=(0,)), AllGather(P_flat, axes_all_gather=(0,)), \
-                ReduceScatter(P_flat, axes_reduce_scatter=(0,))
-            shard = x[: max(8, n // P // 8 * 8)]
-            full = x[: shard.numel() * P]
-            for name, fn, factor, msg in (
-                    ("all_sum_reduce", lambda: ar(x), 2 * (P - 1) / P, nbytes),
-                    ("all_gather", lambda: ag(shard), (P - 1) / P, shard.numel() * 2 * P),
-                    ("reduce_scatter", lambda: rs(full), (P - 1) / P, full.numel() * 2)):
-                if not want(name):
-                    continue
-                ms = _time(fn)
-                rows.append({"op": name, "backend": backend, "bytes": msg, "ms": ms,
-                             "busbw_GBs": msg * factor / ms / 1e6})
-            P_one = P_world.create_partition_inclusive([0]).create_cartesian_topology_partition([1])
-            bc, sr = Broadcast(P_one, P_flat, preserve_batch=False), SumReduce(P_flat, P_one, preserve_batch=False)
-            src = x if rank == 0 else x[:0]
-            for name, fn, msg in (("broadcast", lambda: bc(src), nbytes), ("sum_reduce", lambda: sr(x), nbytes)):
-                if not want(name):
-                    continue
-                ms = _time(fn)
-                rows.append({"op": name, "backend": backend, "bytes": msg, "ms": ms, "busbw_GBs": msg / ms / 1e6})
-            side = int(math.sqrt(n)) // (8 * P) * (8 * P)
-            if side >= 8 * P and want("repartition_row_to_col"):
-                m = torch.rand(side // P, side, device=dev).to(torch.bfloat16)
-                rp = Repartition(P_rows, P_cols)
-                ms = _time(lambda: rp(m))
-                msg = side * side * 2
-                rows.append({"op": "repartition_row_to_col", "backend": backend, "bytes": msg, "ms": ms,
-                             "busbw_GBs": msg / P * (P - 1) / P / ms / 1e6})
-        if P >= 2 and want("halo_exchange"):
-            py = 2 if P % 2 == 0 and P > 2 else 1
-            px = P // py
-            P_sp = P_world.create_cartesian_topology_partition([1, 1, py, px])
-            halo = [[0, 0], [0, 0], [int(P_sp.index[2] > 0), int(P_sp.index[2] < py - 1)],
-                    [int(P_sp.index[3] > 0), int(P_sp.index[3] < px - 1)]]
-            H, Wd = 512 // py, 512 // px
-            xt = torch.rand(8, 64, H + halo[2][0] + halo[2][1], Wd + halo[3][0] + halo[3][1], device=dev)
-            he = HaloExchange(P_sp, halo, halo, halo)
-            ms = _time(lambda: he(xt))
-            rows.append({"op": f"halo_exchange_8x64x512x512_on_{py}x{px}", "backend": backend,
-                         "bytes": xt.numel() * 4, "ms": ms, "busbw_GBs": None})
+        failure = None
+        try:
+            P_world = distdl_b200.backends.backend.Partition()
+            P_flat = P_world.create_cartesian_topology_partition([P])
+            P_rows = P_world.create_cartesian_topology_partition([P, 1])
+            P_cols = P_world.create_cartesian_topology_partition([1, P])
+            for nbytes in sizes:
+                n = nbytes // 2
+                torch.manual_seed(1)
+                x = (torch.rand(n, device=dev) * 2 - 1).to(torch.bfloat16)
+                ar, ag, rs = AllSumReduce(P_flat, axes_reduce=(0,)), AllGather(P_flat, axes_all_gather=(0,)), \
+                    ReduceScatter(P_flat, axes_reduce_scatter=(0,))
+                shard = x[: max(8, n // P // 8 * 8)]
+                full = x[: shard.numel() * P]
+                for name, fn, factor, msg in (
+                        ("all_sum_reduce", lambda: ar(x), 2 * (P - 1) / P, nbytes),
+                        ("all_gather", lambda: ag(shard), (P - 1) / P, shard.numel() * 2 * P),
+                        ("reduce_scatter", lambda: rs(full), (P - 1) / P, full.numel() * 2)):
+                    if not want(name):
+                        continue
+                    ms = _time(fn)
+                    rows.append({"op": name, "backend": backend, "bytes": msg, "ms": ms,
+                                 "busbw_GBs": msg * factor / ms / 1e6})
+                P_one = P_world.create_partition_inclusive([0]).create_cartesian_topology_partition([1])
+                bc, sr = Broadcast(P_one, P_flat, preserve_batch=False), SumReduce(P_flat, P_one, preserve_batch=False)
+                src = x if rank == 0 else x[:0]
+                for name, fn, msg in (("broadcast", lambda: bc(src), nbytes), ("sum_reduce", lambda: sr(x), nbytes)):
+                    if not want(name):
+                        continue
+                    ms = _time(fn)
+                    rows.append({"op": name, "backend": backend, "bytes": msg, "ms": ms, "busbw_GBs": msg / ms / 1e6})
+                side = int(math.sqrt(n)) // (8 * P) * (8 * P)
+                if side >= 8 * P and want("repartition_row_to_col"):
+                    m = torch.rand(side // P, side, device=dev).to(torch.bfloat16)
+                    rp = Repartition(P_rows, P_cols)
+                    ms = _time(lambda: rp(m))
+                    msg = side * side * 2
+                    rows.append({"op": "repartition_row_to_col", "backend": backend, "bytes": msg, "ms": ms,
+                                 "busbw_GBs": msg / P * (P - 1) / P / ms / 1e6})
+            if P >= 2 and want("halo_exchange"):
+                py = 2 if P % 2 == 0 and P > 2 else 1
+                px = P // py
+                P_sp = P_world.create_cartesian_topology_partition([1, 1, py, px])
+                halo = [[0, 0], [0, 0], [int(P_sp.index[2] > 0), int(P_sp.index[2] < py - 1)],
+                        [int(P_sp.index[3] > 0), int(P_sp.index[3] < px - 1)]]
+                H, Wd = 512 // py, 512 // px
+                xt = torch.rand(8, 64, H + halo[2][0] + halo[2][1], Wd + halo[3][0] + halo[3][1], device=dev)
+                he = HaloExchange(P_sp, halo, halo, halo)
+                ms = _time(lambda: he(xt))
+                rows.append({"op": f"halo_exchange_8x64x512x512_on_{py}x{px}", "backend": backend,
+                             "bytes": xt.numel() * 4, "ms": ms, "busbw_GBs": None})
+        except Exception as exc:      # noqa: BLE001  (raised again once no memory is bound to the multicast object)
+            failure = exc
         if backend == "native" and args.multimem:
             symm.disable_multicast()
+        if failure is not None:
+            raise failure
     if rank == 0 and args.md:
         ops = []
         for r in rows:
