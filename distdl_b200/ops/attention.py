@@ -25,6 +25,14 @@ _native.declare("dd_attn_fwd2", [_native.c_void_p, _native.c_ll, _native.c_ll, _
                                  _native.c_ll, _native.c_void_p, _native.c_ll, _native.c_ll, _native.c_void_p,
                                  _native.c_void_p, _native.c_int, _native.c_int, _native.c_int, _native.c_int,
                                  _native.c_int, _native.c_int, _native.c_float, _native.c_void_p])
+_BWD_ARGS = [_native.c_void_p, _native.c_ll, _native.c_ll, _native.c_void_p, _native.c_ll,
+             _native.c_ll, _native.c_void_p, _native.c_ll, _native.c_ll, _native.c_void_p,
+             _native.c_void_p, _native.c_void_p, _native.c_void_p, _native.c_void_p,
+             _native.c_ll, _native.c_ll, _native.c_void_p, _native.c_ll, _native.c_ll,
+             _native.c_void_p, _native.c_ll, _native.c_ll, _native.c_int, _native.c_int,
+             _native.c_int, _native.c_int, _native.c_int, _native.c_int, _native.c_float,
+             _native.c_void_p]
+_native.declare("dd_attn_bwd2", _BWD_ARGS)
 _native.declare("dd_attn_bwd", [_native.c_void_p, _native.c_ll, _native.c_ll, _native.c_void_p, _native.c_ll,
                                 _native.c_ll, _native.c_void_p, _native.c_ll, _native.c_ll, _native.c_void_p,
                                 _native.c_void_p, _native.c_void_p, _native.c_void_p, _native.c_void_p,
@@ -68,10 +76,12 @@ def attention_backward(dout, q, k, v, out, lse, batch, seq, causal=True, scale=N
     if dv is None:
         dv = torch.empty(tokens, Hkv, D, dtype=q.dtype, device=q.device)
     dout = dout.contiguous()
-    delta = torch.empty(batch, Hq, seq, dtype=torch.float32, device=q.device)
-    _native.call("dd_attn_bwd", q.data_ptr(), *_strides(q), k.data_ptr(), *_strides(k), v.data_ptr(), *_strides(v),
-                 out.data_ptr(), dout.data_ptr(), lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), *_strides(dq),
-                 dk.data_ptr(), *_strides(dk), dv.data_ptr(), *_strides(dv), batch, seq, Hq, Hkv, D, int(causal),
+    # head dim 128: the kernels that keep P / dS in tensor memory (scratch: delta and the base-2 lse)
+    in_tmem = D == 128 and os.environ.get("DISTDL_ATTN_BWD2", "1") != "0"
+    delta = torch.empty(2 if in_tmem else 1, batch, Hq, seq, dtype=torch.float32, device=q.device)
+    _native.call("dd_attn_bwd2" if in_tmem else "dd_attn_bwd", q.data_ptr(), *_strides(q), k.data_ptr(), *_strides(k),
+                 v.data_ptr(), *_strides(v), out.data_ptr(), dout.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+                 dq.data_ptr(), *_strides(dq), dk.data_ptr(), *_strides(dk), dv.data_ptr(), *_strides(dv), batch, seq, Hq, Hkv, D, int(causal),
                  float(scale), stream_ptr())
     return dq, dk, dv
 
