@@ -75,6 +75,10 @@ class DistributedPoolBase(Module, HaloMixin, PoolingMixin):
         x = x[self.needed_slices]
         k = tuple(int(v) for v in self.kernel_size)
         s = tuple(int(v) for v in self.stride)
+        if not self.extra and x.is_cuda:
+            from ..ops import pooling as pool_ops
+            if pool_ops.usable(x):          # this library's kernel reads the cropped view in place
+                return pool_ops.pool(x, self.pool_kind, k, s, tuple(int(v) for v in self.dilation))
         if self.pool_kind == "avg":
             fn = {1: F.avg_pool1d, 2: F.avg_pool2d, 3: F.avg_pool3d}[self.num_dimensions]
             return fn(x, k, stride=s, padding=0, **self.extra)

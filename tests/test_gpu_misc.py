@@ -127,3 +127,36 @@ def test_batch_norm_kernels_match_the_pytorch_formulation(dtype, shape):
     torch.autograd.backward([sr, qr, yr], [gs.to(dtype).float(), gq.to(dtype).float(), gy.to(dtype).float()])
     for got, want in zip((x, mean, var, gamma, beta), ref):
         close(got.grad, want.grad)
+
+
+@pytest.mark.parametrize("nd,kind,kernel,stride,dilation", [
+    (1, "avg", (3,), (2,), (1,)), (1, "max", (3,), (1,), (2,)),
+    (2, "avg", (2, 3), (2, 1), (1, 1)), (2, "max", (3, 3), (2, 2), (1, 1)), (2, "max", (2, 2), (1, 1), (2, 3)),
+    (3, "avg", (2, 2, 2), (2, 2, 2), (1, 1, 1)), (3, "max", (3, 2, 3), (1, 2, 1), (1, 1, 2))])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_pooling_kernels_match_torch_on_a_cropped_view(nd, kind, kernel, stride, dilation, dtype):
+    import torch.nn.functional as F
+
+    from distdl_b200.ops import pooling
+    torch.manual_seed(3)
+    space = {1: (37,), 2: (19, 23), 3: (9, 11, 13)}[nd]
+    full = torch.randn(3, 5, *[n + 3 for n in space], device="cuda").to(dtype)
+    crop = (slice(None), slice(None)) + tuple(slice(1, 1 + n) for n in space)
+    x = full.clone().requires_grad_()
+    xr = full.float().clone().requires_grad_()
+    view = x[crop]
+    assert pooling.usable(view) and not view.is_contiguous()
+    y = pooling.pool(view, kind, kernel, stride, dilation)
+    if kind == "avg":
+        fn = {1: F.avg_pool1d, 2: F.avg_pool2d, 3: F.avg_pool3d}[nd]
+        yr = fn(xr[crop], kernel, stride=stride)
+    else:
+        fn = {1: F.max_pool1d, 2: F.max_pool2d, 3: F.max_pool3d}[nd]
+        yr = fn(xr[crop], kernel, stride=stride, dilation=dilation)
+    assert y.shape == yr.shape
+    tol = 1e-6 if dtype == torch.float32 else 1e-2
+    assert (y.float() - yr).abs().max().item() <= tol * (1 + yr.abs().max().item())
+    dy = torch.randn_like(yr)
+    y.backward(dy.to(dtype))
+    yr.backward(dy)
+    assert (x.grad.float() - xr.grad).abs().max().item() <= tol * (1 + xr.grad.abs().max().item()) * 4
