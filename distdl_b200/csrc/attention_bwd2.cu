@@ -22,6 +22,8 @@
 //
 // Every wait is bounded; a time-out records a status and the CTA falls through to its
 // tensor-memory release.  Sequence length must be a multiple of 128.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "runtime.cuh"
 
@@ -137,6 +139,7 @@ struct KVBarriers {
   volatile int abort_flag;
 };
 
+template <bool POLY>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -295,10 +298,10 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
           const float4 l = L4[g];
-          pr[4 * g] = exp2f(fmaf(__uint_as_float(s[4 * g]), c, -l.x));
-          pr[4 * g + 1] = exp2f(fmaf(__uint_as_float(s[4 * g + 1]), c, -l.y));
-          pr[4 * g + 2] = exp2f(fmaf(__uint_as_float(s[4 * g + 2]), c, -l.z));
-          pr[4 * g + 3] = exp2f(fmaf(__uint_as_float(s[4 * g + 3]), c, -l.w));
+          pr[4 * g] = exp2_mixed<POLY>(fmaf(__uint_as_float(s[4 * g]), c, -l.x), 4 * g);
+          pr[4 * g + 1] = exp2_mixed<POLY>(fmaf(__uint_as_float(s[4 * g + 1]), c, -l.y), 4 * g + 1);
+          pr[4 * g + 2] = exp2_mixed<POLY>(fmaf(__uint_as_float(s[4 * g + 2]), c, -l.z), 4 * g + 2);
+          pr[4 * g + 3] = exp2_mixed<POLY>(fmaf(__uint_as_float(s[4 * g + 3]), c, -l.w), 4 * g + 3);
         }
       }
       if (diag) {
@@ -370,6 +373,7 @@ struct QBarriers {
   volatile int abort_flag;
 };
 
+template <bool POLY>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -501,7 +505,7 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar->p_done);
 #pragma unroll
-        for (int k = 0; k < 32; ++k) pr[k] = exp2f(fmaf(__uint_as_float(s[k]), c, -lse2));
+        for (int k = 0; k < 32; ++k) pr[k] = exp2_mixed<POLY>(fmaf(__uint_as_float(s[k]), c, -lse2), k);
       }
       if (diag) {
 #pragma unroll
@@ -581,19 +585,30 @@ DD_API int dd_attn_bwd2(const void* q, long long q_row, long long q_head, const 
   p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.batch = batch; p.causal = causal; p.scale = scale;
   p.status = device_status(&err);
   if (err) return err;
+  // DISTDL_ATTN_EXP_POLY=1: a third of the exponentials on the FMA pipe (see exp2_fma)
+  static const bool poly = [] { const char* e = getenv("DISTDL_ATTN_EXP_POLY"); return e != nullptr && e[0] == '1'; }();
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!configured[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd2_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd2_dkdv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          KVSmem::TOTAL);
-    if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(attn_bwd2_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, QSmem::TOTAL);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_bwd2_dkdv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, KVSmem::TOTAL);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_bwd2_dq_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, QSmem::TOTAL);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_bwd2_dq_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, QSmem::TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured[dev & 63] = true;
   }
   const int nT = S / BT;
-  attn_bwd2_dkdv_kernel<<<nT * Hkv * batch, NUM_THREADS, KVSmem::TOTAL, s>>>(tq, tk, tv, tdo, p);
-  attn_bwd2_dq_kernel<<<nT * Hq * batch, NUM_THREADS, QSmem::TOTAL, s>>>(tq, tk, tv, tdo, p);
+  if (poly) {
+    attn_bwd2_dkdv_kernel<true><<<nT * Hkv * batch, NUM_THREADS, KVSmem::TOTAL, s>>>(tq, tk, tv, tdo, p);
+    attn_bwd2_dq_kernel<true><<<nT * Hq * batch, NUM_THREADS, QSmem::TOTAL, s>>>(tq, tk, tv, tdo, p);
+  } else {
+    attn_bwd2_dkdv_kernel<false><<<nT * Hkv * batch, NUM_THREADS, KVSmem::TOTAL, s>>>(tq, tk, tv, tdo, p);
+    attn_bwd2_dq_kernel<false><<<nT * Hq * batch, NUM_THREADS, QSmem::TOTAL, s>>>(tq, tk, tv, tdo, p);
+  }
   return (int)cudaGetLastError();
 }

@@ -19,6 +19,8 @@
 // one thread execute in order, so S_t(j+1) may overwrite P_t(j) right after PV_t(j)
 // was issued.  Causal: tile t of query pair qp sees blocks 0 .. 2 qp + t.
 // All waits are bounded; a timeout drains and frees tensor memory.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "runtime.cuh"
 
@@ -56,6 +58,7 @@ struct Params2 {
   StatusRecord* status;
 };
 
+template <bool POLY>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const Params2 p) {
@@ -261,8 +264,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = exp2f(__uint_as_float(s[ch * 32 + i]) * c - mc);
-          const float p1 = exp2f(__uint_as_float(s[ch * 32 + i + 1]) * c - mc);
+          const float p0 = exp2_mixed<POLY>(__uint_as_float(s[ch * 32 + i]) * c - mc, i);
+          const float p1 = exp2_mixed<POLY>(__uint_as_float(s[ch * 32 + i + 1]) * c - mc, i + 1);
           lsum += p0 + p1;
           packed[i >> 1] = pack_bf16x2(p0, p1);
         }
@@ -334,12 +337,18 @@ DD_API int dd_attn_fwd2(const void* q, long long q_row_stride, long long q_head_
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
+  // DISTDL_ATTN_EXP_POLY=1: a third of the exponentials on the FMA pipe (exp2_fma in common.cuh)
+  static const bool poly = [] { const char* e = getenv("DISTDL_ATTN_EXP_POLY"); return e != nullptr && e[0] == '1'; }();
   if (!configured[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_fwd2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured[dev & 63] = true;
   }
   const int grid = (S / (2 * BQ)) * Hq * batch;
-  attn_fwd2_kernel<<<grid, NUM_THREADS, SMEM_TOTAL, reinterpret_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (poly) attn_fwd2_kernel<true><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tq, tk, tv, p);
+  else attn_fwd2_kernel<false><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tq, tk, tv, p);
   return (int)cudaGetLastError();
 }

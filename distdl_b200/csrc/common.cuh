@@ -306,4 +306,22 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// 2^x on the FMA pipe: round x to the nearest integer n with the magic-number add, evaluate a cubic
+// for 2^(x - n) on [-0.5, 0.5] (relative error 7.5e-5, far inside bf16 rounding) and add n to the
+// exponent field.  The exp2 unit delivers 16 results per clock and SM, which is as long per
+// 128 x 128 tile as two of the tile's tensor-core products; every POLY_EVERY-th exponential goes
+// through here instead so that both pipes share the work.
+__device__ __forceinline__ float exp2_fma(float x) {
+  x = fmaxf(x, -126.f);
+  const float t = __fadd_rn(x, 12582912.f);
+  const float f = __fsub_rn(x, __fsub_rn(t, 12582912.f));
+  const float p = fmaf(fmaf(fmaf(0.0551716648f, f, 0.2426111251f), f, 0.6932609677f), f, 0.9999280572f);
+  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
+}
+constexpr int POLY_EVERY = 3;
+template <bool POLY>
+__device__ __forceinline__ float exp2_mixed(float x, int k) {
+  return (POLY && (k % POLY_EVERY) == POLY_EVERY - 1) ? exp2_fma(x) : exp2f(x);
+}
+
 }  // namespace dd

@@ -12,14 +12,65 @@ using namespace dd;
 
 namespace {
 
-__global__ void moe_assign_kernel(const int* __restrict__ ids, int npairs, int E, int capacity,
-                                  int* __restrict__ counters, int* __restrict__ slot) {
-  const int p = blockIdx.x * blockDim.x + threadIdx.x;
-  if (p >= npairs) return;
-  const int e = ids[p];
-  if (e < 0 || e >= E) { slot[p] = -1; return; }
-  const int s = atomicAdd(counters + e, 1);
-  slot[p] = s < capacity ? s : -1;
+// Slots are positions in the arrival order of the pairs at their expert, and the arrival order is
+// the pair index: the result does not depend on how the threads are scheduled, so the same pairs
+// are dropped at an overflowing expert in every run.  Two steps over chunks of kChunk tokens (one
+// CTA each, one thread per token, k pairs per thread):
+//   histogram: hist[chunk][e] = pairs of the chunk routed to e
+//   slots    : base[e] = sum of the earlier chunks' histograms; inside the chunk a pair's rank is the
+//              number of earlier lanes (and warps) of the CTA with a pair for the same expert.
+constexpr int kChunk = 256;
+constexpr int kMaxExperts = 64;
+
+__global__ void __launch_bounds__(kChunk)
+moe_hist_kernel(const int* __restrict__ ids, int tokens, int k, int E, int* __restrict__ hist) {
+  __shared__ int s_hist[kMaxExperts];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) s_hist[e] = 0;
+  __syncthreads();
+  const int t = blockIdx.x * kChunk + threadIdx.x;
+  if (t < tokens)
+    for (int c = 0; c < k; ++c) {
+      const int e = ids[(size_t)t * k + c];
+      if (e >= 0 && e < E) atomicAdd(&s_hist[e], 1);
+    }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) hist[(size_t)blockIdx.x * E + e] = s_hist[e];
+}
+
+// The k experts of one token must differ (top-k routing) or k must be 1.
+__global__ void __launch_bounds__(kChunk)
+moe_slot_kernel(const int* __restrict__ ids, int tokens, int k, int E, int capacity, const int* __restrict__ hist,
+                int* __restrict__ totals, int* __restrict__ slot) {
+  __shared__ unsigned s_mask[kChunk / 32][kMaxExperts];     // lanes of a warp with a pair for expert e
+  __shared__ int s_base[kChunk / 32][kMaxExperts];          // pairs for e before this warp
+  for (int i = threadIdx.x; i < (kChunk / 32) * kMaxExperts; i += blockDim.x) (&s_mask[0][0])[i] = 0u;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kChunk + threadIdx.x;
+  if (t < tokens)
+    for (int c = 0; c < k; ++c) {
+      const int e = ids[(size_t)t * k + c];
+      if (e >= 0 && e < E) atomicOr(&s_mask[warp][e], 1u << lane);
+    }
+  __syncthreads();
+  if ((int)threadIdx.x < E) {
+    const int e = threadIdx.x;
+    int run = 0;
+    for (int cta = 0; cta < (int)blockIdx.x; ++cta) run += hist[(size_t)cta * E + e];
+    for (int w = 0; w < kChunk / 32; ++w) { s_base[w][e] = run; run += __popc(s_mask[w][e]); }
+    if (blockIdx.x == gridDim.x - 1) totals[e] = run;
+  }
+  __syncthreads();
+  if (t < tokens)
+    for (int c = 0; c < k; ++c) {
+      const int e = ids[(size_t)t * k + c];
+      int sl = -1;
+      if (e >= 0 && e < E) {
+        sl = s_base[warp][e] + __popc(s_mask[warp][e] & ((1u << lane) - 1u));
+        if (sl >= capacity) sl = -1;
+      }
+      slot[(size_t)t * k + c] = sl;
+    }
 }
 
 // dst[e, slot, :] = (w ? w[p] : 1) * src[p / k, :]
@@ -100,21 +151,22 @@ __global__ void moe_pair_dot_kernel(const __nv_bfloat16* __restrict__ a, const _
 }
 
 // ---------------------------------------------------------------------------
-// Router: softmax over the experts, top-k, renormalised weights, slot assignment
-// and the column sums of the probabilities (for the load-balancing loss) in ONE
+// Router: softmax over the experts, top-k, renormalised weights, the chunk's expert
+// histogram and the column sums of the probabilities (for the load-balancing loss) in one
 // kernel; one thread per token, the E (<= EMAX) logits of a token in registers.
 //   p = softmax(l);  S = top-k of p;  w_i = p_i / sum_{j in S} p_j  (i in S)
-// Outputs per pair (t, c): ids, w, slot (slot = arrival order at the expert, -1
-// beyond the capacity).  counters[e] ends as the number of pairs routed to e,
-// prob_sum[e] as sum_t p[t, e].  counters and prob_sum must be zero on entry.
+// Outputs per pair (t, c): ids, w; hist[chunk][e] for moe_slot_kernel, which follows and
+// turns the histograms into slots (arrival order at the expert = pair index order, -1 beyond
+// the capacity).  prob_sum[e] ends as sum_t p[t, e] and must be zero on entry.
 // ---------------------------------------------------------------------------
 template <int EMAX>
 __global__ void __launch_bounds__(256)
 moe_router_fwd_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int tokens, int E, int k, int capacity,
-                      int* __restrict__ ids, float* __restrict__ w, int* __restrict__ slot,
-                      int* __restrict__ counters, float* __restrict__ prob_sum) {
+                      int* __restrict__ ids, float* __restrict__ w, int* __restrict__ hist,
+                      float* __restrict__ prob_sum) {
   __shared__ float s_sum[EMAX];
-  for (int e = threadIdx.x; e < EMAX; e += blockDim.x) s_sum[e] = 0.f;
+  __shared__ int s_hist[EMAX];
+  for (int e = threadIdx.x; e < EMAX; e += blockDim.x) { s_sum[e] = 0.f; s_hist[e] = 0; }
   __syncthreads();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t < tokens) {
@@ -152,13 +204,14 @@ moe_router_fwd_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int toke
       const int pr = t * k + c;
       ids[pr] = isel[c];
       w[pr] = wsel[c] * invs;
-      const int sidx = atomicAdd(counters + isel[c], 1);
-      slot[pr] = sidx < capacity ? sidx : -1;
+      atomicAdd(&s_hist[isel[c]], 1);
     }
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < E; e += blockDim.x)
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
     if (s_sum[e] != 0.f) atomicAdd(prob_sum + e, s_sum[e]);
+    hist[(size_t)blockIdx.x * E + e] = s_hist[e];
+  }
 }
 
 // dl_i = p_i (c_i - sum_e c_e p_e)  +  [i in S] w_i (dw_i - sum_{j in S} w_j dw_j)
@@ -222,9 +275,15 @@ inline int grid_for(long long work, int threads) {
 #define CBF(p) reinterpret_cast<const __nv_bfloat16*>(p)
 
 // counters[E] must be zero on entry.
+// counters: (chunks + 1) * E ints with chunks = dd_moe_chunks(npairs): [0, E) receives the number
+// of pairs per expert, the rest is scratch (nothing has to be zero on entry).  E <= 64.
+DD_API int dd_moe_chunks(int tokens) { return (tokens + kChunk - 1) / kChunk; }
 DD_API int dd_moe_assign(const int* ids, int npairs, int E, int capacity, int* counters, int* slot, void* stream) {
+  if (E < 1 || E > kMaxExperts) return DD_ERR_BAD_ARG;
   if (npairs <= 0) return DD_OK;
-  moe_assign_kernel<<<(npairs + 255) / 256, 256, 0, S(stream)>>>(ids, npairs, E, capacity, counters, slot);
+  const int grid = dd_moe_chunks(npairs);
+  moe_hist_kernel<<<grid, kChunk, 0, S(stream)>>>(ids, npairs, 1, E, counters + E);
+  moe_slot_kernel<<<grid, kChunk, 0, S(stream)>>>(ids, npairs, 1, E, capacity, counters + E, counters, slot);
   return (int)cudaGetLastError();
 }
 DD_API int dd_moe_scatter_rows(const void* src, const int* ids, const int* slot, const float* w, void* dst,
@@ -251,24 +310,24 @@ DD_API int dd_moe_pair_dot(const void* a, const void* b, const int* ids, const i
   return (int)cudaGetLastError();
 }
 
-// logits [tokens, ld] bf16 (columns >= E are padding); E <= 64, k <= 8, k <= E.
+// logits [tokens, ld] bf16 (columns >= E are padding); E <= 64, k <= 8, k <= E.  counters as for
+// dd_moe_assign with chunks = dd_moe_chunks(tokens); prob_sum [E] must be zero on entry.
 DD_API int dd_moe_router_fwd(const void* logits, int ld, int tokens, int E, int k, int capacity, int* ids, float* w,
                              int* slot, int* counters, float* prob_sum, void* stream) {
-  if (E < 1 || E > 64 || k < 1 || k > 8 || k > E || ld < E) return DD_ERR_BAD_ARG;
+  if (E < 1 || E > kMaxExperts || k < 1 || k > 8 || k > E || ld < E) return DD_ERR_BAD_ARG;
   if (tokens <= 0) return DD_OK;
-  const int grid = (tokens + 255) / 256;
+  static_assert(kChunk == 256, "the router kernel handles one chunk of 256 tokens per CTA");
+  const int grid = dd_moe_chunks(tokens);
+  int* hist = counters + E;
   if (E <= 8)
-    moe_router_fwd_kernel<8><<<grid, 256, 0, S(stream)>>>(CBF(logits), ld, tokens, E, k, capacity, ids, w, slot,
-                                                          counters, prob_sum);
+    moe_router_fwd_kernel<8><<<grid, 256, 0, S(stream)>>>(CBF(logits), ld, tokens, E, k, capacity, ids, w, hist, prob_sum);
   else if (E <= 16)
-    moe_router_fwd_kernel<16><<<grid, 256, 0, S(stream)>>>(CBF(logits), ld, tokens, E, k, capacity, ids, w, slot,
-                                                           counters, prob_sum);
+    moe_router_fwd_kernel<16><<<grid, 256, 0, S(stream)>>>(CBF(logits), ld, tokens, E, k, capacity, ids, w, hist, prob_sum);
   else if (E <= 32)
-    moe_router_fwd_kernel<32><<<grid, 256, 0, S(stream)>>>(CBF(logits), ld, tokens, E, k, capacity, ids, w, slot,
-                                                           counters, prob_sum);
+    moe_router_fwd_kernel<32><<<grid, 256, 0, S(stream)>>>(CBF(logits), ld, tokens, E, k, capacity, ids, w, hist, prob_sum);
   else
-    moe_router_fwd_kernel<64><<<grid, 256, 0, S(stream)>>>(CBF(logits), ld, tokens, E, k, capacity, ids, w, slot,
-                                                           counters, prob_sum);
+    moe_router_fwd_kernel<64><<<grid, 256, 0, S(stream)>>>(CBF(logits), ld, tokens, E, k, capacity, ids, w, hist, prob_sum);
+  moe_slot_kernel<<<grid, kChunk, 0, S(stream)>>>(ids, tokens, k, E, capacity, hist, counters, slot);
   return (int)cudaGetLastError();
 }
 // dw [tokens * k] and coef [E] may each be null (no gradient from that output).

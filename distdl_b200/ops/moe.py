@@ -13,6 +13,14 @@ from ._util import ptr, stream_ptr, use_native
 
 _v, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 _native.declare("dd_moe_assign", [_v, _i, _i, _i, _v, _v, _v])
+_native.declare("dd_moe_chunks", [_i])
+
+
+def _counters(items: int, E: int, device):
+    """Scratch of the slot assignment: [0, E) receives the pairs per expert, the rest holds the
+    per-chunk histograms."""
+    chunks = _native.lib().dd_moe_chunks(int(items))
+    return torch.empty((chunks + 1) * E, dtype=torch.int32, device=device)
 _native.declare("dd_moe_scatter_rows", [_v, _v, _v, _v, _v, _i, _i, _i, _i, _v])
 _native.declare("dd_moe_gather_rows", [_v, _v, _v, _v, _v, _i, _i, _i, _i, _v])
 _native.declare("dd_moe_pair_dot", [_v, _v, _v, _v, _v, _i, _i, _i, _i, _v])
@@ -23,8 +31,9 @@ _native.declare("dd_moe_router_bwd", [_v, _i, _i, _i, _i, _v, _v, _v, _v, _v, _v
 
 
 class _RouterFn(torch.autograd.Function):
-    """Softmax over the experts, top-k, renormalised weights, slot assignment and the column sums
-    of the probabilities in one kernel; one more kernel for the backward pass."""
+    """Softmax over the experts, top-k, renormalised weights and the column sums of the probabilities
+    in one kernel, the slots (arrival order = pair index, so overflow drops the same pairs in every
+    run) in a second one; one more kernel for the backward pass."""
 
     @staticmethod
     def forward(ctx, logits, E, k, capacity):
@@ -33,10 +42,11 @@ class _RouterFn(torch.autograd.Function):
         ids = torch.empty(T * k, dtype=torch.int32, device=dev)
         w = torch.empty(T, k, dtype=torch.float32, device=dev)
         slot = torch.empty(T * k, dtype=torch.int32, device=dev)
-        counts = torch.zeros(E, dtype=torch.int32, device=dev)
+        scratch = _counters(T, E, dev)
+        counts = scratch[:E]
         prob_sum = torch.zeros(E, dtype=torch.float32, device=dev)
         _native.call("dd_moe_router_fwd", logits.data_ptr(), ld, T, E, k, capacity, ids.data_ptr(), w.data_ptr(),
-                     slot.data_ptr(), counts.data_ptr(), prob_sum.data_ptr(), stream_ptr())
+                     slot.data_ptr(), scratch.data_ptr(), prob_sum.data_ptr(), stream_ptr())
         ctx.save_for_backward(logits, ids, w)
         ctx.cfg = (E, k)
         ctx.mark_non_differentiable(ids, slot, counts)
@@ -80,11 +90,11 @@ def assign_slots(ids: torch.Tensor, num_experts: int, capacity: int):
     """ids [pairs] int32 -> (slot [pairs] int32 with -1 for dropped pairs, counts [E] int32)."""
     flat = ids.reshape(-1).to(torch.int32).contiguous()
     if use_native(flat):
-        counts = torch.zeros(num_experts, dtype=torch.int32, device=flat.device)
+        scratch = _counters(flat.numel(), num_experts, flat.device)
         slot = torch.empty_like(flat)
-        _native.call("dd_moe_assign", flat.data_ptr(), flat.numel(), num_experts, capacity, counts.data_ptr(),
+        _native.call("dd_moe_assign", flat.data_ptr(), flat.numel(), num_experts, capacity, scratch.data_ptr(),
                      slot.data_ptr(), stream_ptr())
-        return slot, counts
+        return slot, scratch[:num_experts]
     onehot = torch.nn.functional.one_hot(flat.long(), num_experts)
     pos = (onehot.cumsum(0) - 1)[torch.arange(flat.numel()), flat.long()]
     slot = torch.where(pos < capacity, pos, torch.full_like(pos, -1)).to(torch.int32)

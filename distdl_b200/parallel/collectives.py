@@ -200,6 +200,25 @@ def gather_in_place(x: torch.Tensor, ranks):
     return out
 
 
+def _as_one(rows):
+    """The flat slices as one ``[P, n]`` tensor when they sit back to back in memory (the slices of
+    one contiguous tensor, the usual case), else the list unchanged."""
+    n, es = rows[0].numel(), rows[0].element_size()
+    base = rows[0].data_ptr()
+    if n and all(r.numel() == n and r.data_ptr() == base + i * n * es for i, r in enumerate(rows)):
+        return torch.as_strided(rows[0], (len(rows), n), (n, 1))
+    return rows
+
+
+def _stage_rows(stage, rows, done, cnt):
+    """stage[i, :cnt] = rows[i][done:done + cnt]: one copy when the rows are one tensor."""
+    if isinstance(rows, torch.Tensor):
+        stage[:, :cnt].copy_(rows[:, done:done + cnt])
+    else:
+        for i, r in enumerate(rows):
+            stage[i, :cnt].copy_(r[done:done + cnt])
+
+
 def reduce_scatter(x, ranks) -> torch.Tensor:
     """``x`` is ``[P, ...]`` (or a list of ``P`` equally shaped tensors): member ``i`` receives the
     team-wide sum of ``x[i]``.  The slices are copied once, straight into the staging buffer."""
@@ -211,6 +230,7 @@ def reduce_scatter(x, ranks) -> torch.Tensor:
     rows = [x[i].contiguous().view(-1) for i in range(P)]
     if dtype_in not in _DT:
         rows = [r.float() for r in rows]
+    rows = _as_one(rows)
     dt = rows[0].dtype
     es = rows[0].element_size()
     chunk = rows[0].numel()
@@ -228,8 +248,7 @@ def reduce_scatter(x, ranks) -> torch.Tensor:
         stage = h.staging_tensor(P * padded, dt).view(P, pe)
         if pe != cnt:
             stage[:, cnt:].zero_()
-        for i in range(P):
-            stage[i, :cnt].copy_(rows[i][done:done + cnt])
+        _stage_rows(stage, rows, done, cnt)
         if pe == cnt:
             _launch("dd_reducescatter", h, ranks, out[done:done + cnt].data_ptr(), padded, _DT[dt])
         else:
@@ -259,8 +278,7 @@ def _reduce_scatter_multicast(mc, h, xs, out):
         stage = mc.local_tensor(P * padded, dt).view(P, pe)
         if pe != cnt:
             stage[:, cnt:].zero_()
-        for i in range(P):
-            stage[i, :cnt].copy_(xs[i][done:done + cnt])
+        _stage_rows(stage, xs, done, cnt)
         direct = pe == cnt
         dst = out[done:done + cnt] if direct else torch.empty(pe, dtype=dt, device=out.device)
         steps = ctypes.c_int(0)

@@ -38,6 +38,8 @@ def test_moe_routing_kernels_match_torch():
     w = torch.rand(T, k, device="cuda", requires_grad=True)
     slot, counts = moe.assign_slots(ids, E, C)
     assert int(counts.sum()) == T * k
+    ref_slot, ref_counts = moe.assign_slots(ids.cpu(), E, C)
+    assert torch.equal(slot.cpu(), ref_slot) and torch.equal(counts.cpu(), ref_counts)
     for e in range(E):
         s = slot[(ids == e)]
         kept = s[s >= 0]
@@ -57,8 +59,8 @@ def test_moe_routing_kernels_match_torch():
 
 @pytest.mark.parametrize("E,k,ld", [(8, 2, 8), (6, 1, 8), (16, 4, 16), (40, 8, 40), (64, 2, 64)])
 def test_router_kernel_matches_softmax_topk_renormalisation(E, k, ld):
-    """The one-kernel router (softmax, top-k, renormalised weights, slots, probability sums) and its
-    backward kernel against the same computation written with PyTorch ops in fp32."""
+    """The router kernels (softmax, top-k, renormalised weights, probability sums; slots in pair-index
+    order) and the backward kernel against the same computation written with PyTorch ops in fp32."""
     from distdl_b200.ops import moe
     torch.manual_seed(E * 10 + k)
     T, C = 777, 10_000
@@ -91,6 +93,12 @@ def test_router_kernel_matches_softmax_topk_renormalisation(E, k, ld):
     for e in range(min(E, 4)):
         kept = (slot2[ids2 == e] >= 0).sum().item()
         assert kept == min(8, int((ids2 == e).sum()))
+    # the slots are the arrival order by pair index (the same in every run): compare with the
+    # index-ordered assignment written with PyTorch ops on the host
+    ref_slot, ref_counts = moe.assign_slots(ids2.cpu(), E, 8)
+    assert torch.equal(slot2.cpu(), ref_slot)
+    ref_slot, ref_counts = moe.assign_slots(ids.cpu(), E, C)
+    assert torch.equal(slot.cpu(), ref_slot) and torch.equal(counts.cpu(), ref_counts)
 
 
 @pytest.mark.parametrize("dtype,shape", [(torch.float32, (6, 5, 7, 9)), (torch.bfloat16, (8, 16, 33)),
