@@ -77,8 +77,7 @@ def attention_backward(dout, q, k, v, out, lse, batch, seq, causal=True, scale=N
         dv = torch.empty(tokens, Hkv, D, dtype=q.dtype, device=q.device)
     dout = dout.contiguous()
     # the kernels that keep P / dS in tensor memory (scratch: delta and the base-2 lse)
-    in_tmem = (D == 128 or (D == 64 and os.environ.get("DISTDL_ATTN_BWD2_D64", "0") == "1")) \
-        and os.environ.get("DISTDL_ATTN_BWD2", "1") != "0"
+    in_tmem = D in (64, 128) and os.environ.get("DISTDL_ATTN_BWD2", "1") != "0"
     delta = torch.empty(2 if in_tmem else 1, batch, Hq, seq, dtype=torch.float32, device=q.device)
     _native.call("dd_attn_bwd2" if in_tmem else "dd_attn_bwd", q.data_ptr(), *_strides(q), k.data_ptr(), *_strides(k),
                  v.data_ptr(), *_strides(v), out.data_ptr(), dout.data_ptr(), lse.data_ptr(), delta.data_ptr(),

@@ -17,7 +17,11 @@ def _run(what, nproc):
            "--master-addr", "127.0.0.1", "--master-port", str(29400 + os.getpid() % 500),
            os.path.join(HERE, "multi_gpu_worker.py"), what]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    if res.returncode != 0:
+        # the ranks' own tracebacks come before the launcher's summary: show their last frames and errors
+        lines = (res.stdout + "\n" + res.stderr).splitlines()
+        keep = [ln for ln in lines if "multi_gpu_" in ln or "Error" in ln or "assert" in ln or "distdl_b200" in ln]
+        raise AssertionError("\n".join(keep[:60]) + "\n...\n" + res.stderr[-1500:])
     assert "OK" in res.stdout
 
 
