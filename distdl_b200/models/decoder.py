@@ -20,6 +20,7 @@ tensor-parallel communication.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 
 import numpy as np
@@ -428,6 +429,8 @@ class Decoder(torch.nn.Module):
             free += torch.cuda.memory_reserved() - torch.cuda.memory_allocated()
             rows = b * s // self.layout.tp
             head = int(2.5 * rows * self.padded_vocab * 2) if self.last_stage else 0
+            if os.environ.get("DISTDL_FORCE_TORCH", "0") == "1":
+                head = int(3.2 * head)         # the library loss keeps fp32 logits, their log-softmax and its gradient
             slack = 4 << 30
             budget = free - head - moment - kept - slack
             keep = max(0, min(n, int(budget // max(kept, 1))))

@@ -82,7 +82,7 @@ def test_rope_on_the_projection_output_rotates_in_place_without_copying_gradient
     out = rope_(y, seq, hq + hk, theta=10000.0, layout=(b * seq, hq + 2 * hk, hd))
     assert out.shape == lin.shape and torch.equal(out.reshape(ref.shape), ref)
     g = torch.randn_like(out)
-    out.backward(g)
+    out.backward(g.clone())           # the node rotates the gradient it is handed in place
     # the adjoint of a rotation is the inverse rotation: rotating the gradient forward again gives g
     back = rope_(lin.grad.clone().reshape(b * seq, hq + 2 * hk, hd), seq, hq + hk, theta=10000.0)
     _close(back, g.reshape(back.shape), 1e-2)
