@@ -464,9 +464,12 @@ def check_context_parallel_decoder():
     from distdl_b200 import models
     world = dist.get_world_size()
     dev = torch.device("cuda", torch.cuda.current_device())
-    cfg = models.llama_tiny(d_model=512, n_heads=4, n_kv_heads=2, ffn_dim=1024, max_seq=512, vocab_size=1024)
-    cfg.n_layers = 2
     tp = world // 2
+    # the all-to-all mode re-splits the LOCAL heads over the context-parallel workers: 4 query and 2
+    # key heads per tensor-parallel worker, head dim 128
+    cfg = models.llama_tiny(d_model=512 * tp, n_heads=4 * tp, n_kv_heads=2 * tp, ffn_dim=1024 * tp, max_seq=512,
+                            vocab_size=1024)
+    cfg.n_layers = 2
     gen = torch.Generator().manual_seed(5)
     tokens = torch.randint(0, cfg.vocab_size, (2, 513), generator=gen).to(dev)
     for mode in ("ring", "zigzag", "a2a"):
