@@ -14,7 +14,7 @@ def _ref(q, k, v, batch, seq, causal):
 
 @pytest.mark.parametrize("batch,seq,Hq,Hkv,D,causal", [
     (1, 128, 1, 1, 128, True), (2, 256, 4, 2, 128, True), (1, 512, 8, 2, 128, False), (2, 384, 5, 5, 64, True),
-    (1, 1024, 4, 1, 128, True)])
+    (1, 1024, 4, 1, 128, True), (2, 512, 6, 3, 64, True), (1, 256, 2, 2, 64, False)])
 def test_attention_forward(batch, seq, Hq, Hkv, D, causal):
     from distdl_b200 import _native
     from distdl_b200.ops import attention_forward
@@ -38,7 +38,8 @@ def test_attention_forward(batch, seq, Hq, Hkv, D, causal):
 
 
 @pytest.mark.parametrize("batch,seq,Hq,Hkv,D,causal", [
-    (1, 128, 1, 1, 128, True), (2, 256, 4, 2, 128, True), (1, 512, 4, 1, 128, False), (2, 384, 3, 3, 64, True)])
+    (1, 128, 1, 1, 128, True), (2, 256, 4, 2, 128, True), (1, 512, 4, 1, 128, False), (2, 384, 3, 3, 64, True),
+    (2, 512, 4, 2, 64, True)])
 def test_attention_backward(batch, seq, Hq, Hkv, D, causal):
     from distdl_b200 import _native
     from distdl_b200.ops import attention
