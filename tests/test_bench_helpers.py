@@ -76,3 +76,21 @@ def test_exchange_split_is_decided_alike_at_both_ends_of_a_pair():
         native = {ok for _, ok in seen}
         assert len(native) == 1, (pair, seen)                       # both ends agree
         assert native.pop() == (pair not in ((0, 1), (2, 0))), pair
+
+
+def test_reduce_scatter_staging_sees_adjacent_slices_as_one_tensor():
+    """Slices of one contiguous tensor are staged with a single copy; separate tensors one by one."""
+    import torch
+
+    from distdl_b200.parallel import collectives as C
+    x = torch.arange(24.).view(4, 6)
+    rows = [x[i].contiguous().view(-1) for i in range(4)]
+    one = C._as_one(rows)
+    assert isinstance(one, torch.Tensor) and one.shape == (4, 6) and torch.equal(one, x)
+    apart = [torch.randn(6) for _ in range(4)]
+    assert isinstance(C._as_one(apart), list)
+    for src in (one, apart):
+        stage = torch.zeros(4, 8)
+        C._stage_rows(stage, src, 2, 3)
+        want = torch.stack([r[2:5] for r in (rows if src is one else apart)])
+        assert torch.equal(stage[:, :3], want) and not stage[:, 3:].any()
