@@ -55,10 +55,9 @@ def attention_forward(q, k, v, batch, seq, causal=True, scale=None):
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     out = torch.empty(tokens, Hq, D, dtype=q.dtype, device=q.device)
     lse = torch.empty(batch, Hq, seq, dtype=torch.float32, device=q.device)
-    # head dim 128 and sequences of whole 256-row pairs run the two-tile kernel (scores and
+    # head dim 128 / 64 and sequences of whole 256-row pairs run the two-tile kernel (scores and
     # probabilities in tensor memory, two query tiles alternating on the tensor cores)
-    two_tile = (D == 128 or (D == 64 and os.environ.get("DISTDL_ATTN_FWD2_D64", "0") == "1")) and seq % 256 == 0 \
-        and os.environ.get("DISTDL_ATTN_FWD2", "1") != "0"
+    two_tile = D in (64, 128) and seq % 256 == 0 and os.environ.get("DISTDL_ATTN_FWD2", "1") != "0"
     _native.call("dd_attn_fwd2" if two_tile else "dd_attn_fwd", q.data_ptr(), *_strides(q), k.data_ptr(), *_strides(k),
                  v.data_ptr(), *_strides(v), out.data_ptr(), lse.data_ptr(), batch, seq, Hq, Hkv, D, int(causal),
                  float(scale), stream_ptr())
