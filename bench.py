@@ -34,7 +34,11 @@ def reference_arm(args):
     ref = os.path.join(ROOT, "baseline", "_ref")
     if os.path.isdir(os.path.join(ref, "distdl")):
         sys.path.insert(0, ref)
+        import tempfile
+        here = os.getcwd()
         try:
+            # the reference's logger opens ./distdl.log when it is imported: not in this tree
+            os.chdir(tempfile.mkdtemp(prefix="distdl_ref_"))
             import distdl  # noqa: F401
         except Exception as e:  # pragma: no cover
             why = f"import distdl failed: {type(e).__name__}: {e}"
@@ -44,6 +48,8 @@ def reference_arm(args):
     else:
         why = ("offline install failed: its C++ extension does not link here and mpi4py, cupy, pytorch-pfn-extras "
                "and mpirun are absent, so `import distdl` cannot succeed")
+    if os.path.isdir(os.path.join(ref, "distdl")):
+        os.chdir(here)
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 

@@ -246,6 +246,33 @@ reducescatter_kernel(const Team t, char* out, size_t bytes) {
   team_barrier(t, 1, &fail);
 }
 
+// reduce-scatter without a staging copy: every member PUSHES slice j of its input straight from
+// the input tensor into slot [me] of member j's staging buffer (local loads, peer stores), and
+// after the barrier sums the slices it received with its own slice (all local reads).
+struct RowPtrs {
+  const char* row[kMaxPeers];   // this GPU's input slices, one per member (local memory, 16-byte aligned)
+};
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads)
+reducescatter_push_kernel(const Team t, const RowPtrs in, char* out, size_t bytes) {
+  __shared__ int fail;
+  if (threadIdx.x == 0) fail = 0;
+  const size_t nvec = bytes >> 4;
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  if (!team_barrier(t, 0, &fail)) return;               // the members are done with their staging buffers
+  for (int k = 1; k < t.n; ++k) {
+    const int j = (t.me + k) % t.n;                     // start with a different member on every GPU
+    copy_vecs(reinterpret_cast<char*>(t.buf[j]) + (size_t)t.me * bytes, in.row[j], nvec, tid, stride);
+  }
+  if (!team_barrier(t, 1, &fail)) return;               // every slice for this GPU has arrived
+  Team loc = t;                                         // summed in member order, as the pull form does
+  for (int i = 0; i < t.n; ++i)
+    loc.buf[i] = i == t.me ? const_cast<char*>(in.row[i]) : reinterpret_cast<char*>(t.buf[t.me]) + (size_t)i * bytes;
+  reduce_loop<BF16>(loc, 0, 0, nvec, tid, stride,
+                    [&](size_t v, const uint4& r) { *reinterpret_cast<uint4*>(out + (v << 4)) = r; });
+}
+
 template <int U, int NMAX>
 __device__ __forceinline__ void rs_acc_loop(const Team& t, float* acc, size_t base, size_t nvec, size_t tid,
                                             size_t stride, float scale) {
@@ -852,6 +879,27 @@ DD_API int dd_reducescatter(int n, int me, int my_writer, void* const* bufs, voi
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == 0) reducescatter_kernel<true><<<kCollectiveCtas, kThreads, 0, s>>>(t, (char*)out, bytes);
   else reducescatter_kernel<false><<<kCollectiveCtas, kThreads, 0, s>>>(t, (char*)out, bytes);
+  return (int)cudaGetLastError();
+}
+// rows[i]: this GPU's slice for member i (local, 16-byte aligned, `bytes` long); the staging buffer of
+// every member must hold n * bytes.
+DD_API int dd_reducescatter_push(int n, int me, int my_writer, void* const* bufs, void* const* flags,
+                                 const int* writers, const unsigned* expect, void* const* rows, void* out, size_t bytes,
+                                 int dtype, int* steps, void* stream) {
+  if (bytes % 16) return DD_ERR_ALIGN;
+  Team t;
+  int r = fill_team(t, n, me, my_writer, bufs, flags, writers, expect);
+  if (r) return r;
+  RowPtrs in;
+  for (int i = 0; i < kMaxPeers; ++i) {
+    in.row[i] = i < n ? reinterpret_cast<const char*>(rows[i]) : nullptr;
+    if (i < n && (rows[i] == nullptr || (reinterpret_cast<uintptr_t>(rows[i]) & 15))) return DD_ERR_ALIGN;
+  }
+  if (out == nullptr || (reinterpret_cast<uintptr_t>(out) & 15)) return DD_ERR_ALIGN;
+  *steps = 2;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == 0) reducescatter_push_kernel<true><<<kCollectiveCtas, kThreads, 0, s>>>(t, in, (char*)out, bytes);
+  else reducescatter_push_kernel<false><<<kCollectiveCtas, kThreads, 0, s>>>(t, in, (char*)out, bytes);
   return (int)cudaGetLastError();
 }
 DD_API int dd_reducescatter_acc(int n, int me, int my_writer, void* const* bufs, void* const* flags,

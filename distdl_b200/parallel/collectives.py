@@ -221,7 +221,9 @@ def _stage_rows(stage, rows, done, cnt):
 
 def reduce_scatter(x, ranks) -> torch.Tensor:
     """``x`` is ``[P, ...]`` (or a list of ``P`` equally shaped tensors): member ``i`` receives the
-    team-wide sum of ``x[i]``.  The slices are copied once, straight into the staging buffer."""
+    team-wide sum of ``x[i]``.  Slices that are 16-byte aligned are pushed from where they are into
+    the owners' staging buffers by the kernel itself; others are copied into this GPU's staging
+    buffer first and pulled."""
     h = symm.heap()
     ranks = list(ranks)
     P = len(ranks)
@@ -241,6 +243,14 @@ def reduce_scatter(x, ranks) -> torch.Tensor:
         return out.view(x[0].shape).to(dtype_in)
     cap_elems = (h.staging_bytes // P) // 16 * 16 // es
     done = 0
+    if (chunk * es) % 16 == 0 and all(rows[i].data_ptr() % 16 == 0 for i in range(P)):
+        # no staging copy: every member pushes its slices straight into the owners' staging buffers
+        while done < chunk:
+            cnt = min(chunk - done, cap_elems)
+            ptrs = (ctypes.c_void_p * P)(*[rows[i].data_ptr() + done * es for i in range(P)])
+            _launch("dd_reducescatter_push", h, ranks, ptrs, out[done:done + cnt].data_ptr(), cnt * es, _DT[dt])
+            done += cnt
+        return out.view(x[0].shape).to(dtype_in)
     while done < chunk:
         cnt = min(chunk - done, cap_elems)
         padded = (cnt * es + 15) // 16 * 16

@@ -37,6 +37,7 @@ _TEAM = [c_int, c_int, c_int, _PP, _PP, _IP, _UP]
 _native.declare("dd_allreduce", _TEAM + [c_void_p, c_size_t, c_int, c_int, _IP, c_void_p])
 _native.declare("dd_allgather", _TEAM + [c_void_p, c_size_t, _IP, c_void_p])
 _native.declare("dd_reducescatter", _TEAM + [c_void_p, c_size_t, c_int, _IP, c_void_p])
+_native.declare("dd_reducescatter_push", _TEAM + [_PP, c_void_p, c_size_t, c_int, _IP, c_void_p])
 _native.declare("dd_reducescatter_acc", _TEAM + [c_void_p, c_size_t, ctypes.c_float, _IP, c_void_p])
 _native.declare("dd_exchange", _TEAM + [_PP, ctypes.POINTER(ctypes.c_ulonglong), ctypes.c_ulonglong, _IP, c_void_p])
 _native.declare("dd_alltoall", _TEAM + [c_void_p, c_size_t, _IP, c_void_p])

@@ -16,7 +16,7 @@ def check_collectives():
     ranks = list(range(world))
     dev = torch.device("cuda", torch.cuda.current_device())
     for dtype in (torch.bfloat16, torch.float32):
-        for n in (8, 1000, 4096, 65536 + 24, 3 * 1024 * 1024 + 8):
+        for n in (8, 1000, 1001, 4096, 65536 + 24, 3 * 1024 * 1024 + 8):
             torch.manual_seed(n + rank)
             x = (torch.rand(n, device=dev) * 2 - 1).to(dtype)
             ref = x.clone().float()
