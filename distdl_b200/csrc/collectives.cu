@@ -171,8 +171,11 @@ __device__ __forceinline__ void reduce_loop(const Team& t, size_t byte_base, siz
 // ---------------------------------------------------------------------------
 // all-reduce.  Input staged at buf[me][0, bytes); result written to `out`
 // (local).  one_shot: every GPU reads everything; else every GPU sums one slice
-// and pushes it to all members, and the rest is a local copy.
+// and either pushes it to the other member (teams of two) or the members pull it.
 // ---------------------------------------------------------------------------
+// the two-shot all-reduce pushes its sums (two barriers) in teams of two, pulls (three barriers) above
+__host__ __device__ constexpr bool allreduce_pushes(int n) { return n <= 2; }
+
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads)
 allreduce_kernel(const Team t, char* out, size_t bytes, int one_shot) {
@@ -188,28 +191,47 @@ allreduce_kernel(const Team t, char* out, size_t bytes, int one_shot) {
     team_barrier(t, 1, &fail);
     return;
   }
-  // Two shots, the second one local: this GPU sums its slice of the vectors (peer loads) and PUSHES
-  // the sums into every member's staging buffer (peer stores, so both directions of the links carry
-  // data at the same time) and into its own output.  A member's staging holds that slice of its
-  // input until the one thread that reads it for the sum overwrites it, so the sums can land in
-  // place.  After the barrier every staging buffer holds the complete result and the other slices
-  // are copied from local memory; nobody touches another GPU's staging any more, so no third
-  // barrier is needed.
   const size_t per = (nvec + t.n - 1) / t.n;
   const size_t lo = min(nvec, per * t.me), hi = min(nvec, lo + per);
-  reduce_loop<BF16>(t, 0, lo, hi, tid, stride, [&](size_t v, const uint4& r) {
+  if (allreduce_pushes(t.n)) {
+    // Two shots, the second one local: this GPU sums its slice of the vectors (peer loads) and PUSHES
+    // the sums into the other member's staging buffer (peer stores, so both directions of the links
+    // carry data at the same time) and into its own output.  A member's staging holds that slice of
+    // its input until the one thread that reads it for the sum overwrites it, so the sums can land in
+    // place.  After the barrier every staging buffer holds the complete result and the other slices
+    // are copied from local memory; nobody touches another GPU's staging any more, so no third
+    // barrier is needed.  (Measured: 426 against 381 GB/s at 256 MB on 2 GPUs; on 4 GPUs the
+    // scattered stores to three peers cost more than they save, 491 against 523, hence the limit.)
+    reduce_loop<BF16>(t, 0, lo, hi, tid, stride, [&](size_t v, const uint4& r) {
 #pragma unroll
-    for (int i = 0; i < kMaxPeers; ++i)
-      if (i < t.n && i != t.me) *reinterpret_cast<uint4*>(reinterpret_cast<char*>(t.buf[i]) + (v << 4)) = r;
+      for (int i = 0; i < kMaxPeers; ++i)
+        if (i < t.n && i != t.me) *reinterpret_cast<uint4*>(reinterpret_cast<char*>(t.buf[i]) + (v << 4)) = r;
+      *reinterpret_cast<uint4*>(out + (v << 4)) = r;
+    });
+    if (!team_barrier(t, 1, &fail)) return;
+    const char* mine = reinterpret_cast<const char*>(t.buf[t.me]);
+    for (int k = 1; k < t.n; ++k) {
+      const int i = (t.me + k) % t.n;
+      const size_t plo = min(nvec, per * i), phi = min(nvec, plo + per);
+      if (phi > plo) copy_vecs(out + (plo << 4), mine + (plo << 4), phi - plo, tid, stride);
+    }
+    return;
+  }
+  // Two shots, both over the links: the sums of this GPU's slice go to its own staging buffer and
+  // output; after the barrier every GPU pulls the other slices from their owners.
+  char* mine = reinterpret_cast<char*>(t.buf[t.me]);
+  reduce_loop<BF16>(t, 0, lo, hi, tid, stride, [&](size_t v, const uint4& r) {
+    *reinterpret_cast<uint4*>(mine + (v << 4)) = r;
     *reinterpret_cast<uint4*>(out + (v << 4)) = r;
   });
   if (!team_barrier(t, 1, &fail)) return;
-  const char* mine = reinterpret_cast<const char*>(t.buf[t.me]);
   for (int k = 1; k < t.n; ++k) {
-    const int i = (t.me + k) % t.n;
+    const int i = (t.me + k) % t.n;   // start with a different peer on every GPU
     const size_t plo = min(nvec, per * i), phi = min(nvec, plo + per);
-    if (phi > plo) copy_vecs(out + (plo << 4), mine + (plo << 4), phi - plo, tid, stride);
+    const char* src = reinterpret_cast<const char*>(t.buf[i]);
+    if (phi > plo) copy_vecs(out + (plo << 4), src + (plo << 4), phi - plo, tid, stride);
   }
+  team_barrier(t, 2, &fail);
 }
 
 // all-gather: member i's `bytes` staged at buf[i][0, bytes); out[i*bytes ...] = it.
@@ -853,7 +875,7 @@ DD_API int dd_allreduce(int n, int me, int my_writer, void* const* bufs, void* c
   Team t;
   int r = fill_team(t, n, me, my_writer, bufs, flags, writers, expect);
   if (r) return r;
-  *steps = 2;
+  *steps = (one_shot || allreduce_pushes(n)) ? 2 : 3;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == 0) allreduce_kernel<true><<<kCollectiveCtas, kThreads, 0, s>>>(t, (char*)out, bytes, one_shot);
   else allreduce_kernel<false><<<kCollectiveCtas, kThreads, 0, s>>>(t, (char*)out, bytes, one_shot);

@@ -65,6 +65,7 @@ class SymmetricHeap:
         if self.world > self.max_peers:
             raise RuntimeError(f"the native transport handles up to {self.max_peers} GPUs of one node")
         self.staging_bytes = int(staging_bytes)
+        self._team_cache = {}          # rank tuple -> the arguments of a team that never change
         self.regions = {}
         # every region is followed by a guard zone that holds a fixed pattern: a kernel that runs past
         # the end of its region (on this GPU or, through the peer mapping, on another one) leaves a
@@ -137,13 +138,16 @@ class SymmetricHeap:
 
     def team_args(self, ranks):
         """ctypes arguments describing a team (ordered world ranks containing this rank)."""
-        n = len(ranks)
-        me = list(ranks).index(self.rank)
-        bufs = (c_void_p * n)(*[self.buf_ptrs[r] for r in ranks])
-        pads = (c_void_p * n)(*[self.pad_ptrs[r] for r in ranks])
-        writers = (c_int * n)(*[int(r) for r in ranks])
-        expect = (ctypes.c_uint * n)(*[(self.steps_done[r] + 1) & 0xFFFFFFFF for r in ranks])
-        return n, me, self.rank, bufs, pads, writers, expect
+        key = tuple(ranks)
+        fixed = self._team_cache.get(key)
+        if fixed is None:
+            n = len(key)
+            fixed = self._team_cache[key] = (n, key.index(self.rank), self.rank,
+                                             (c_void_p * n)(*[self.buf_ptrs[r] for r in key]),
+                                             (c_void_p * n)(*[self.pad_ptrs[r] for r in key]),
+                                             (c_int * n)(*[int(r) for r in key]))
+        expect = (ctypes.c_uint * fixed[0])(*[(self.steps_done[r] + 1) & 0xFFFFFFFF for r in key])
+        return fixed + (expect,)
 
     def advance(self, ranks, steps: int):
         for r in ranks:
@@ -378,29 +382,23 @@ def require_healthy():
     _one_waiting_stream()
 
 
-_last_waiting = [None, None]       # (stream handle, event recorded after the last peer-waiting launch)
+_last_waiting = [None]             # stream of the last peer-waiting launch
 
 
 def _one_waiting_stream():
     """Kernels that wait for other GPUs must not be resident on one GPU from two streams at once: each
     could hold the SMs that the other needs while their peers wait for both.  Every such launch passes
-    through here; a launch on another stream than the previous one is refused unless the previous
-    kernel has already finished."""
+    through here; a launch on another stream than the previous one is refused unless everything
+    queued on that stream (the previous such kernel included) has finished."""
     if not torch.cuda.is_available() or os.environ.get("DISTDL_STREAM_GUARD", "1") == "0":
         return
     cur = torch.cuda.current_stream()
-    last_stream, last_event = _last_waiting
-    if last_stream is not None and last_stream != cur.cuda_stream and last_event is not None \
-            and not last_event.query():
+    last = _last_waiting[0]
+    if last is not None and last.cuda_stream != cur.cuda_stream and last.device == cur.device and not last.query():
         raise RuntimeError("a kernel that waits for other GPUs is still running on another stream of this GPU: "
                            "launch the collectives, exchanges and fused GEMMs of one GPU on one stream "
                            "(or synchronise the streams first)")
-    if last_stream != cur.cuda_stream:
-        _last_waiting[0] = cur.cuda_stream
-    ev = _last_waiting[1]
-    if ev is None:
-        ev = _last_waiting[1] = torch.cuda.Event()
-    ev.record(cur)
+    _last_waiting[0] = cur
 
 
 def check_health():
