@@ -61,8 +61,11 @@ class BufferManager:
         self.buffers_map = {}
 
     def request_buffers(self, n_buffers, dtype, **kwargs):
-        pool = self.buffers_map.setdefault(dtype, [])
-        device = kwargs.get("device", self.device)
+        device = kwargs.get("device", None)
+        device = self.device if device is None else device
+        on_host = device is None or torch.device(device).type == "cpu"
+        # one pool per dtype, as in the reference; device tensors get pools of their own
+        pool = self.buffers_map.setdefault(dtype if on_host else (dtype, str(torch.device(device))), [])
         while len(pool) < n_buffers:
             pool.append(ExpandableBuffer(dtype, 0, device=device, allocator=self._allocator))
         return pool[:n_buffers]

@@ -5,14 +5,14 @@ from __future__ import annotations
 import numpy as np
 
 
-def allocate_repartition_buffers(buffer_manager, P_x_to_y_overlaps, P_y_to_x_overlaps, dtype):
+def allocate_repartition_buffers(buffer_manager, P_x_to_y_overlaps, P_y_to_x_overlaps, dtype, device=None):
     """One buffer per message that leaves or enters this worker (overlaps with
     ``"self"`` or ``None`` need none).  Returns ``(send_views, recv_views)``
     aligned with the two overlap lists; sends take the first buffers."""
     def need(overlaps):
         return [i for i, (sl, sh, partner) in enumerate(overlaps) if sl is not None and partner != "self"]
     s_idx, r_idx = need(P_x_to_y_overlaps), need(P_y_to_x_overlaps)
-    bufs = buffer_manager.request_buffers(len(s_idx) + len(r_idx), dtype=dtype)
+    bufs = buffer_manager.request_buffers(len(s_idx) + len(r_idx), dtype=dtype, device=device)
     send = [None] * len(P_x_to_y_overlaps)
     recv = [None] * len(P_y_to_x_overlaps)
     k = 0
@@ -25,12 +25,12 @@ def allocate_repartition_buffers(buffer_manager, P_x_to_y_overlaps, P_y_to_x_ove
     return send, recv
 
 
-def allocate_halo_exchange_buffers(buffer_manager, slices, recv_buffer_shape, send_buffer_shape, dtype):
+def allocate_halo_exchange_buffers(buffer_manager, slices, recv_buffer_shape, send_buffer_shape, dtype, device=None):
     """Four buffers (left/right x send/recv) re-viewed per dimension, since the
     dimensions are exchanged one after another.  Returns a list with one
     ``[left_send, left_recv, right_send, right_recv]`` entry per dimension
     (``None`` where nothing moves)."""
-    bufs = buffer_manager.request_buffers(4, dtype=dtype)
+    bufs = buffer_manager.request_buffers(4, dtype=dtype, device=device)
     out = []
     for d, (lb, lg, rb, rg) in enumerate(slices):
         def view(buf, sl, width):

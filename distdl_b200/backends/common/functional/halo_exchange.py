@@ -65,8 +65,26 @@ def _box_plan(t, kind, x, P_x, slices, neighbor_ranks):
     return plan
 
 
-def fill_ghosts(t, x, P_x, slices, neighbor_ranks):
-    """The exchange itself: a copy of ``x`` whose ghost regions hold the neighbours' bulk regions."""
+def _staged(buffers, d, k, like, shape):
+    """View ``k`` (0 / 1: left send / receive, 2 / 3: right send / receive) of the layer's staging
+    buffers for dimension ``d`` if it can carry a message of ``shape`` for tensor ``like``."""
+    if buffers is None or buffers[d] is None:
+        return None
+    b = buffers[d][k]
+    if b is None or b.dtype != like.dtype or b.device != like.device or tuple(b.shape) != tuple(shape):
+        return None
+    return b
+
+
+def _packed(buf, face):
+    """The face as a contiguous message: packed into the staging view when there is one."""
+    return face if buf is None else buf.copy_(face)
+
+
+def fill_ghosts(t, x, P_x, slices, neighbor_ranks, buffers=None):
+    """The exchange itself: a copy of ``x`` whose ghost regions hold the neighbours' bulk regions.
+    On the transports that move whole messages (``recv_into``), the faces are packed into and
+    received into the views that the layer obtained from its buffer manager."""
     out = x.detach().clone()
     plan = _box_plan(t, "fill", out, P_x, slices, neighbor_ranks)
     if plan is not None:
@@ -76,27 +94,32 @@ def fill_ghosts(t, x, P_x, slices, neighbor_ranks):
         lb, lg, rb, rg = slices[d]
         left, right = neighbor_ranks[d]
         sends, recvs, targets = [], [], []
+        staged = buffers if getattr(t, "recv_into", False) else None
         if left != PROC_NULL:
             if _volume(lb):
-                sends.append((left, out[lb]))
+                sends.append((left, _packed(_staged(staged, d, 0, out, _shape(lb)), out[lb])))
             if _volume(lg):
-                recvs.append((left, _shape(lg), out.dtype))
+                recvs.append((left, _shape(lg), out.dtype, _staged(staged, d, 1, out, _shape(lg))))
                 targets.append(lg)
         if right != PROC_NULL:
             if _volume(rb):
-                sends.append((right, out[rb]))
+                sends.append((right, _packed(_staged(staged, d, 2, out, _shape(rb)), out[rb])))
             if _volume(rg):
-                recvs.append((right, _shape(rg), out.dtype))
+                recvs.append((right, _shape(rg), out.dtype, _staged(staged, d, 3, out, _shape(rg))))
                 targets.append(rg)
+        if staged is None:
+            recvs = [r[:3] for r in recvs]
         got = t.exchange(sends, recvs, list(P_x.ranks))
         for sl, g in zip(targets, got):
             out[sl] = g.to(out.device)
     return out
 
 
-def fold_ghosts(t, x, P_x, slices, neighbor_ranks):
+def fold_ghosts(t, x, P_x, slices, neighbor_ranks, buffers=None):
     """The adjoint of :func:`fill_ghosts`: ghost regions travel to the neighbours they came from,
-    are ADDED to the bulk regions there, and are cleared here."""
+    are ADDED to the bulk regions there, and are cleared here.  The staging views swap roles: a
+    ghost leaves through the view that received it, a bulk contribution arrives in the view that
+    sent the bulk."""
     g = x.detach().clone()
     plan = _box_plan(t, "fold", g, P_x, slices, neighbor_ranks)
     if plan is not None:
@@ -106,18 +129,25 @@ def fold_ghosts(t, x, P_x, slices, neighbor_ranks):
         lb, lg, rb, rg = slices[d]
         left, right = neighbor_ranks[d]
         sends, recvs, targets = [], [], []
+        staged = buffers if getattr(t, "recv_into", False) else None
+
+        def leaving(k, sl):
+            buf = _staged(staged, d, k, g, _shape(sl))
+            return g[sl].clone() if buf is None else buf.copy_(g[sl])
         if left != PROC_NULL:
             if _volume(lg):
-                sends.append((left, g[lg].clone()))
+                sends.append((left, leaving(1, lg)))
             if _volume(lb):
-                recvs.append((left, _shape(lb), g.dtype))
+                recvs.append((left, _shape(lb), g.dtype, _staged(staged, d, 0, g, _shape(lb))))
                 targets.append(lb)
         if right != PROC_NULL:
             if _volume(rg):
-                sends.append((right, g[rg].clone()))
+                sends.append((right, leaving(3, rg)))
             if _volume(rb):
-                recvs.append((right, _shape(rb), g.dtype))
+                recvs.append((right, _shape(rb), g.dtype, _staged(staged, d, 2, g, _shape(rb))))
                 targets.append(rb)
+        if staged is None:
+            recvs = [r[:3] for r in recvs]
         got = t.exchange(sends, recvs, list(P_x.ranks))
         if left != PROC_NULL and _volume(lg):
             g[lg] = 0
@@ -137,7 +167,8 @@ class HaloExchangeFunction(TransportBound, torch.autograd.Function):
             ctx.identity = True
             return input
         ctx.identity = False
-        out = fill_ghosts(cls.transport(), input, P_x, slices, neighbor_ranks)
+        ctx.buffers = buffers
+        out = fill_ghosts(cls.transport(), input, P_x, slices, neighbor_ranks, buffers)
         out.requires_grad_(input.requires_grad)
         return out
 
@@ -146,7 +177,7 @@ class HaloExchangeFunction(TransportBound, torch.autograd.Function):
         if ctx.identity:
             return grad_output, None, None, None, None
         cls = ctx._forward_cls
-        g = fold_ghosts(cls.transport(), grad_output, ctx.P_x, ctx.slices, ctx.neighbor_ranks)
+        g = fold_ghosts(cls.transport(), grad_output, ctx.P_x, ctx.slices, ctx.neighbor_ranks, ctx.buffers)
         return g, None, None, None, None
 
 
@@ -164,7 +195,8 @@ class HaloAccumulateFunction(TransportBound, torch.autograd.Function):
             ctx.identity = True
             return input
         ctx.identity = False
-        out = fold_ghosts(cls.transport(), input, P_x, slices, neighbor_ranks)
+        ctx.buffers = buffers
+        out = fold_ghosts(cls.transport(), input, P_x, slices, neighbor_ranks, buffers)
         out.requires_grad_(input.requires_grad)
         return out
 
@@ -173,5 +205,5 @@ class HaloAccumulateFunction(TransportBound, torch.autograd.Function):
         if ctx.identity:
             return grad_output, None, None, None, None
         cls = ctx._forward_cls
-        g = fill_ghosts(cls.transport(), grad_output, ctx.P_x, ctx.slices, ctx.neighbor_ranks)
+        g = fill_ghosts(cls.transport(), grad_output, ctx.P_x, ctx.slices, ctx.neighbor_ranks, ctx.buffers)
         return g, None, None, None, None

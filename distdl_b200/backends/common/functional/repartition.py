@@ -48,7 +48,15 @@ def _box_plan(transport, send_overlaps, recv_overlaps, team):
     return plan
 
 
-def _move(transport, src_tensor, out_shape, out_dtype, send_overlaps, recv_overlaps, device, team=None):
+def _fits(buf, like_dtype, device, shape):
+    return (buf is not None and buf.dtype == like_dtype and buf.device == torch.device(device)
+            and tuple(buf.shape) == tuple(int(v) for v in shape))
+
+
+def _move(transport, src_tensor, out_shape, out_dtype, send_overlaps, recv_overlaps, device, team=None,
+          send_buffers=None, recv_buffers=None):
+    """``send_buffers`` / ``recv_buffers``: the layer's staging views, aligned with the two overlap lists;
+    transports that move whole messages pack into them and receive into them."""
     if (src_tensor.is_cuda or (out_shape is not None and torch.device(device).type == "cuda")
             or getattr(transport, "box_plans_on_host", False)):
         plan = _box_plan(transport, send_overlaps, recv_overlaps, team)
@@ -68,10 +76,19 @@ def _move(transport, src_tensor, out_shape, out_dtype, send_overlaps, recv_overl
                 tensors["out"] = out
             plan.run(**tensors)
             return out
-    sends = [(partner, src_tensor[sl]) for sl, sh, partner in send_overlaps
-             if sl is not None and partner != "self"]
-    recvs = [(partner, sh, out_dtype) for sl, sh, partner in recv_overlaps
-             if sl is not None and partner != "self"]
+    staged = getattr(transport, "recv_into", False)
+    sends, recvs = [], []
+    for i, (sl, sh, partner) in enumerate(send_overlaps):
+        if sl is None or partner == "self":
+            continue
+        buf = send_buffers[i] if staged and send_buffers is not None and i < len(send_buffers) else None
+        piece = src_tensor[sl]
+        sends.append((partner, buf.copy_(piece) if _fits(buf, src_tensor.dtype, src_tensor.device, piece.shape) else piece))
+    for i, (sl, sh, partner) in enumerate(recv_overlaps):
+        if sl is None or partner == "self":
+            continue
+        buf = recv_buffers[i] if staged and recv_buffers is not None and i < len(recv_buffers) else None
+        recvs.append((partner, sh, out_dtype, buf) if _fits(buf, out_dtype, device, sh) else (partner, sh, out_dtype))
     got = transport.exchange(sends, recvs, team)
     out = None
     if out_shape is not None:
@@ -97,6 +114,7 @@ class RepartitionFunction(TransportBound, torch.autograd.Function):
         device = input.device
         ctx.args = (P_union, x_global_structure, x_local_structure, y_local_structure, P_x, P_x_to_y_overlaps,
                     P_y, P_y_to_x_overlaps, preserve_batch)
+        ctx.buffers = (P_x_to_y_buffers, P_y_to_x_buffers)
         ctx.device = device
         if not P_union.active:
             return empty_output(input, preserve_batch, device)
@@ -104,7 +122,8 @@ class RepartitionFunction(TransportBound, torch.autograd.Function):
         recvs = P_y_to_x_overlaps if P_y.active else []
         out_shape = y_local_structure.shape if P_y.active else None
         out = _move(cls.transport(), input.detach(), out_shape, x_global_structure.dtype, sends, recvs, device,
-                    list(P_union.ranks))
+                    list(P_union.ranks), P_x_to_y_buffers if P_x.active else None,
+                    P_y_to_x_buffers if P_y.active else None)
         if out is None:
             b = input.shape[0] if (preserve_batch and input.dim() > 0) else None
             from ....utilities.torch import zero_volume_tensor
@@ -124,8 +143,9 @@ class RepartitionFunction(TransportBound, torch.autograd.Function):
         sends = P_y_to_x_overlaps if P_y.active else []
         recvs = P_x_to_y_overlaps if P_x.active else []
         out_shape = x_local_structure.shape if P_x.active else None
+        # the adjoint sends what the forward pass received and receives what it sent: the views swap roles
         g = _move(cls.transport(), grad_output.detach(), out_shape, x_global_structure.dtype, sends, recvs, device,
-                  list(P_union.ranks))
+                  list(P_union.ranks), ctx.buffers[1] if P_y.active else None, ctx.buffers[0] if P_x.active else None)
         if g is None:
             from ....utilities.torch import zero_volume_tensor
             b = grad_output.shape[0] if (preserve_batch and grad_output.dim() > 0) else None

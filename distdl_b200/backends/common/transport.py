@@ -37,9 +37,20 @@ def _as_bytes(t: torch.Tensor) -> torch.Tensor:
     return t.contiguous().view(-1).view(torch.uint8)
 
 
+def _recv_target(shape, dtype, into, device):
+    """The tensor a message is received into: the caller's staging view if it fits, else a new one."""
+    shape = tuple(int(v) for v in shape)
+    if into and into[0] is not None:
+        t = into[0]
+        if tuple(t.shape) == shape and t.dtype == dtype and t.device.type == device.type and t.is_contiguous():
+            return t
+    return torch.empty(shape, dtype=dtype, device=device)
+
+
 class P2PTransport:
     """Team collectives from isend/irecv on ``group`` (default: control-plane gloo group)."""
 
+    recv_into = True       # exchange() accepts a target tensor as the fourth item of a receive
     name = "p2p"
 
     def __init__(self, group=None):
@@ -174,12 +185,14 @@ class P2PTransport:
         return self.reduce_scatter(list(stacked.unbind(0)), ranks)
 
     def exchange(self, sends, recvs, team=None):
-        """Generic neighbour exchange (``team``: all workers that make this call together).  ``sends`` = [(world_rank, tensor)],
-        ``recvs`` = [(world_rank, shape, dtype)] -> list of received tensors (CPU
-        or the transport's native device) in the order of ``recvs``."""
+        """Generic neighbour exchange (``team``: all workers that make this call together).
+        ``sends`` = [(world_rank, tensor)], ``recvs`` = [(world_rank, shape, dtype)] or
+        [(world_rank, shape, dtype, into)] -> list of received tensors (CPU or the transport's
+        native device) in the order of ``recvs``; a message lands in ``into`` (a staging view of
+        the caller's buffer manager) when that tensor has the message's shape, type and device."""
         outs, reqs = [], []
-        for src, shape, dtype in recvs:
-            t = torch.empty(tuple(int(s) for s in shape), dtype=dtype)
+        for src, shape, dtype, *into in recvs:
+            t = _recv_target(shape, dtype, into, torch.device("cpu"))
             outs.append(t)
             if t.numel():
                 reqs.append(self._irecv_into(t, src, TAG_SENDRECV))
@@ -353,8 +366,8 @@ class GroupTransport(P2PTransport):
             return super().exchange(sends, recvs, team)
         dev = torch.device("cuda", torch.cuda.current_device())
         outs, ops, keep = [], [], []
-        for src, shape, dtype in recvs:
-            t = torch.empty(tuple(int(s) for s in shape), dtype=dtype, device=dev)
+        for src, shape, dtype, *into in recvs:
+            t = _recv_target(shape, dtype, into, dev)
             outs.append(t)
             if t.numel():
                 ops.append(dist.P2POp(dist.irecv, t, src))

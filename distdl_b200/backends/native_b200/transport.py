@@ -16,6 +16,7 @@ from ..common.transport import GroupTransport
 
 class NativeTransport(GroupTransport):
     name = "native"
+    recv_into = False      # its exchange kernel delivers into tensors of its own
 
     def __init__(self):
         super().__init__()

@@ -72,8 +72,13 @@ class HaloExchange(Module):
         if self.P_x.active:
             x_local_shape = input[0].shape
             self.slices = self._assemble_slices(x_local_shape, self.recv_buffer_shape, self.send_buffer_shape)
-            self.buffers = self._distdl_backend.buffer_allocator.allocate_halo_exchange_buffers(
-                self.buffer_manager, self.slices, self.recv_buffer_shape, self.send_buffer_shape, input[0].dtype)
+            # staging views for the transports that move whole messages; the native transport packs
+            # and unpacks inside its exchange kernel and needs none
+            self.buffers = None
+            if getattr(self._distdl_backend.transport(), "recv_into", False):
+                self.buffers = self._distdl_backend.buffer_allocator.allocate_halo_exchange_buffers(
+                    self.buffer_manager, self.slices, self.recv_buffer_shape, self.send_buffer_shape, input[0].dtype,
+                    input[0].device)
             self.P_x.initialize_backend_comm()
         self._distdl_is_setup = True
         self._input_tensor_structure = TensorStructure(input[0])

@@ -90,8 +90,11 @@ class Repartition(Module):
             out.shape = tuple(int(s) for s in y_shapes[me_y])
             out.dtype, out.requires_grad = g.dtype, g.requires_grad
             self.output_tensor_structure = out
-        self.P_x_to_y_buffers, self.P_y_to_x_buffers = be.buffer_allocator.allocate_repartition_buffers(
-            self.buffer_manager, self.P_x_to_y_overlaps, self.P_y_to_x_overlaps, g.dtype)
+        # staging views for the transports that move whole messages (the native transport needs none)
+        self.P_x_to_y_buffers, self.P_y_to_x_buffers = None, None
+        if getattr(be.transport(), "recv_into", False):
+            self.P_x_to_y_buffers, self.P_y_to_x_buffers = be.buffer_allocator.allocate_repartition_buffers(
+                self.buffer_manager, self.P_x_to_y_overlaps, self.P_y_to_x_overlaps, g.dtype, input[0].device)
 
     def _distdl_module_teardown(self, input):
         self.P_x_to_y_overlaps, self.P_y_to_x_overlaps = [], []

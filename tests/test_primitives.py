@@ -382,6 +382,46 @@ def test_halo_exchange():
     run_ranks("test_primitives", "body_halo", 4)
 
 
+def body_staging_buffers_carry_the_messages(rank, world):
+    """The views that HaloExchange and Repartition obtain from their buffer manager are what travels:
+    after a call, a send view holds the packed face / overlap and a receive view what arrived."""
+    import distdl_b200
+    from distdl_b200.nn import HaloExchange, Repartition
+    be = distdl_b200.backends.backend
+    # 1-D chain of 2 workers, halo width 1 towards the neighbour
+    P = _P([0, 1], [1, 1, 2])
+    hl, hr = int(rank > 0), int(rank < 1)
+    halo = np.array([[0, 0], [0, 0], [hl, hr]])
+    manager = be.BufferManager()
+    layer = HaloExchange(P, halo, halo, halo, buffer_manager=manager)
+    x = torch.zeros(2, 3, 4 + hl + hr, dtype=torch.float64)
+    x[:, :, hl:hl + 4] = torch.arange(4, dtype=torch.float64) + 10 * (rank + 1)
+    y = layer(x)
+    views = layer.buffers[2]                      # [left send, left recv, right send, right recv]
+    if rank == 0:
+        assert views[2] is not None and torch.equal(views[2], x[:, :, 3:4])        # my last bulk column went right
+        assert torch.equal(views[3], y[:, :, 4:5]) and (views[3] == 20).all()      # the neighbour's first column arrived
+    else:
+        assert torch.equal(views[0], x[:, :, 1:2]) and (views[1] == 13).all()
+    assert len(manager.buffers_map[torch.float64]) == 4
+    # repartition rows -> columns of a [4, 4] tensor over 2 workers
+    P_rows, P_cols = _P([0, 1], [2, 1]), _P([0, 1], [1, 2])
+    rp = Repartition(P_rows, P_cols, buffer_manager=manager)
+    full = torch.arange(16, dtype=torch.float64).reshape(4, 4)
+    out = rp(full[2 * rank:2 * rank + 2].clone())
+    assert torch.equal(out, full[:, 2 * rank:2 * rank + 2])
+    other = 1 - rank
+    sent = [b for b, (sl, sh, partner) in zip(rp.P_x_to_y_buffers, rp.P_x_to_y_overlaps) if b is not None]
+    got = [b for b, (sl, sh, partner) in zip(rp.P_y_to_x_buffers, rp.P_y_to_x_overlaps) if b is not None]
+    assert len(sent) == 1 and torch.equal(sent[0], full[2 * rank:2 * rank + 2, 2 * other:2 * other + 2])
+    assert len(got) == 1 and torch.equal(got[0], full[2 * other:2 * other + 2, 2 * rank:2 * rank + 2])
+    return True
+
+
+def test_staging_buffers_carry_the_messages():
+    run_ranks("test_primitives", "body_staging_buffers_carry_the_messages", 2)
+
+
 def body_allgather_skips_adjoint_when_gradient_goes_elsewhere(rank, world):
     """A parameter whose gradient is accumulated outside of autograd (``full_grad_view``)
     yields no gradient for its gathered copy; the adjoint reduce-scatter is then skipped on
