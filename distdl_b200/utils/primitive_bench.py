@@ -134,7 +134,8 @@ def main():
         with open(args.md, "w") as fh:
             fh.write(f"# Primitive sweep on {P} GPUs (bf16; device-timed, max over ranks)\n\n")
             fh.write("Command: `torchrun --nnodes=1 --nproc-per-node " + str(P) + " -m distdl_b200.utils.primitive_bench"
-                     + (" --multimem" if args.multimem else "") + f" --max-bytes {args.max_bytes} --md FILE`\n\n")
+                     + (" --multimem" if args.multimem else "") + f" --max-bytes {args.max_bytes}"
+                     + (f" --ops {args.ops}" if args.ops else "") + " --md FILE`\n\n")
             fh.write("| op | bytes | native ms | NCCL ms | native GB/s | NCCL GB/s |\n|---|---|---|---|---|---|\n")
             for op in ops:
                 sizes_seen = sorted({r["bytes"] for r in rows if r["op"] == op})
