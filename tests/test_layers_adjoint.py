@@ -164,9 +164,54 @@ def body_other_adjoints(rank, world):
     return True
 
 
+def body_expert_pool_upsample_adjoints(rank, world):
+    """Expert layers (input / weight / bias), average pooling, up-sampling and the transposed feature
+    convolution (all linear in their input): six workers, four in the layer."""
+    from distdl_b200 import nn as dnn
+    from distdl_b200.utilities.slicing import compute_subshape
+    from distdl_b200.utilities.torch import zero_volume_tensor
+    active = rank < 4
+
+    def local(P, gshape):
+        if not P.active:
+            return zero_volume_tensor()
+        return torch.randn(*[int(v) for v in compute_subshape(P.shape, P.index, gshape)])
+
+    # expert layers on [E = 2, N = 1, 1, M = 2]: experts x capacity x sequence x features
+    P_e = _cart([0, 1, 2, 3], [2, 1, 1, 2])
+    experts, cap, seq, d, f = 4, 3, 2, 8, 12
+    _adjoints(lambda bias: dnn.DistributedExpertAllGather(P_e, experts, d, f, bias=bias),
+              lambda: local(P_e, [experts, cap, seq, d]), active)
+    _adjoints(lambda bias: dnn.DistributedExpertReduceScatter(P_e, experts, f, d, bias=bias),
+              lambda: local(P_e, [experts, cap, seq, f]), active)
+    # layers without parameters: the input adjoint alone
+    P_sp = _cart([0, 1, 2, 3], [1, 1, 2, 2])
+    for make, gshape in ((lambda: dnn.DistributedAvgPool2d(P_sp, kernel_size=2, stride=2), [2, 3, 8, 12]),
+                         (lambda: dnn.DistributedAvgPool2d(P_sp, kernel_size=3, stride=1, padding=1), [2, 3, 7, 9]),
+                         (lambda: dnn.DistributedUpsample(P_sp, scale_factor=2, mode="linear"), [2, 3, 5, 6]),
+                         (lambda: dnn.DistributedUpsample(P_sp, size=[9, 11], mode="nearest"), [2, 3, 5, 6])):
+        torch.manual_seed(3)
+        layer = make()
+        x = local(P_sp, gshape).double().requires_grad_()
+        y = layer(x)
+        dy = torch.randn_like(y)
+        if y.requires_grad:
+            y.backward(dy)
+        dx = x.grad if x.grad is not None else zero_volume_tensor(dtype=torch.float64)
+        check_adjoint_test_tight(x.detach(), dx, y.detach(), dy, rtol=1e-5)
+    # transposed feature convolution (halo accumulate inside)
+    _adjoints(lambda bias: dnn.DistributedFeatureConvTranspose2d(P_sp, 3, 4, 3, stride=2, padding=1, bias=bias),
+              lambda: local(P_sp, [2, 3, 6, 8]), active)
+    return True
+
+
 def test_linear_family_adjoints_with_inactive_workers():
     run_ranks("test_layers_adjoint", "body_linear_adjoints", 6, timeout=300)
 
 
 def test_conv_norm_and_embedding_adjoints_with_inactive_workers():
     run_ranks("test_layers_adjoint", "body_other_adjoints", 6, timeout=300)
+
+
+def test_expert_pooling_upsampling_and_transposed_conv_adjoints():
+    run_ranks("test_layers_adjoint", "body_expert_pool_upsample_adjoints", 6, timeout=300)
