@@ -4,10 +4,14 @@
 An :class:`ExpandableBuffer` owns one flat tensor and hands out shaped views
 of its head; asking for a view larger than the capacity reallocates (contents
 kept, existing views re-pointed).  A :class:`BufferManager` keeps a list of
-buffers per dtype so that many layers reuse the same staging memory.  The
-allocation function is pluggable: the native backend passes one that carves
-the storage out of its symmetric (peer-mapped) heap so that staging buffers
-are directly addressable by the other GPUs.
+buffers per dtype (and per device) so that many layers reuse the same staging
+memory; the allocation function is pluggable.  HaloExchange and Repartition pack
+into and receive into these views on the transports that move whole messages
+(gloo, NCCL).  The native transport needs none of them: its exchange kernel packs
+straight into the receiving GPU's inbox, a region of the peer-mapped symmetric heap
+that every process allocates once (``parallel/symm.py``); growing a peer-mapped
+buffer on demand would be a collective over all processes in the middle of a layer's
+lazy set-up, which inactive workers never enter.
 """
 from __future__ import annotations
 
