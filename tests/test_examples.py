@@ -18,7 +18,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
                                           ("examples/basics/ex_linear_zero.py", 4),
                                           ("examples/basics/train_decoder.py --cp 2", 4),
                                           ("examples/basics/ex_pipelined_decoder.py", 4),
-                                          ("examples/basics/ex_window_attention.py", 4)])
+                                          ("examples/basics/ex_window_attention.py", 4),
+                                          ("examples/basics/ex_moe_decoder.py", 4)])
 def test_example_runs(script, nproc):
     script, *extra = script.split()
     port = 29600 + (os.getpid() + hash(script)) % 300
