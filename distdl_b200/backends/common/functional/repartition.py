@@ -83,7 +83,8 @@ def _move(transport, src_tensor, out_shape, out_dtype, send_overlaps, recv_overl
             continue
         buf = send_buffers[i] if staged and send_buffers is not None and i < len(send_buffers) else None
         piece = src_tensor[sl]
-        sends.append((partner, buf.copy_(piece) if _fits(buf, src_tensor.dtype, src_tensor.device, piece.shape) else piece))
+        fits = _fits(buf, src_tensor.dtype, src_tensor.device, piece.shape)
+        sends.append((partner, buf.copy_(piece) if fits else piece))
     for i, (sl, sh, partner) in enumerate(recv_overlaps):
         if sl is None or partner == "self":
             continue

@@ -81,8 +81,8 @@ def attention_backward(dout, q, k, v, out, lse, batch, seq, causal=True, scale=N
     delta = torch.empty(2 if in_tmem else 1, batch, Hq, seq, dtype=torch.float32, device=q.device)
     _native.call("dd_attn_bwd2" if in_tmem else "dd_attn_bwd", q.data_ptr(), *_strides(q), k.data_ptr(), *_strides(k),
                  v.data_ptr(), *_strides(v), out.data_ptr(), dout.data_ptr(), lse.data_ptr(), delta.data_ptr(),
-                 dq.data_ptr(), *_strides(dq), dk.data_ptr(), *_strides(dk), dv.data_ptr(), *_strides(dv), batch, seq, Hq, Hkv, D, int(causal),
-                 float(scale), stream_ptr())
+                 dq.data_ptr(), *_strides(dq), dk.data_ptr(), *_strides(dk), dv.data_ptr(), *_strides(dv), batch, seq,
+                 Hq, Hkv, D, int(causal), float(scale), stream_ptr())
     return dq, dk, dv
 
 

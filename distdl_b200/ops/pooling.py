@@ -59,8 +59,8 @@ class _PoolFn(torch.autograd.Function):
         arg = ctx.saved_tensors[0] if is_max else None
         dy = dy.contiguous()
         dx = torch.empty(shape, dtype=dy.dtype, device=dy.device)
-        _native.call("dd_pool_bwd", dy.data_ptr(), arg.data_ptr() if is_max else None, dx.data_ptr(), planes, _i3(*n_in),
-                     _i3(*n_out), _i3(*k), _i3(*s), _i3(*d), is_max, _DT[dy.dtype], stream_ptr())
+        _native.call("dd_pool_bwd", dy.data_ptr(), arg.data_ptr() if is_max else None, dx.data_ptr(), planes,
+                     _i3(*n_in), _i3(*n_out), _i3(*k), _i3(*s), _i3(*d), is_max, _DT[dy.dtype], stream_ptr())
         return dx, None, None, None, None
 
 

@@ -74,8 +74,8 @@ def _all_reduce_multicast(mc, h, flat, out):
         steps = ctypes.c_int(0)
         _native.launch_count += 1
         _native.check(lib.dd_mc_allreduce(h.world, h.rank, pads, (mc.steps_done + 1) & 0xFFFFFFFF, 0, half,
-                                          dst.data_ptr(), nbytes, _DT[flat.dtype], one_shot, mc.ctas, ctypes.byref(steps),
-                                          stream_ptr()), "dd_mc_allreduce")
+                                          dst.data_ptr(), nbytes, _DT[flat.dtype], one_shot, mc.ctas,
+                                          ctypes.byref(steps), stream_ptr()), "dd_mc_allreduce")
         mc.steps_done += steps.value
         if not direct:
             out[done:done + cnt].copy_(dst[:cnt])
@@ -270,8 +270,8 @@ def reduce_scatter(x, ranks) -> torch.Tensor:
 
 
 def _reduce_scatter_multicast(mc, h, xs, out):
-    """Job-wide reduce-scatter (``xs``: the P flat slices) through the multicast region: every GPU stages its whole input in its
-    copy, then reads the sum of its own slice with ``multimem.ld_reduce``."""
+    """Job-wide reduce-scatter (``xs``: the P flat slices) through the multicast region: every GPU stages
+    its whole input in its copy, then reads the sum of its own slice with ``multimem.ld_reduce``."""
     symm.require_healthy()
     P = h.world
     dt = xs[0].dtype
