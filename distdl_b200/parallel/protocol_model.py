@@ -118,6 +118,67 @@ class World:
         return out
 
 
+    # ---- the push forms (csrc/collectives.cu: reducescatter_push_kernel, allreduce_kernel in teams of two) ----
+    def reduce_scatter_push(self, me, team, rows, jitter=None):
+        """One launch of the reduce-scatter that needs no staging copy.  ``rows[i]`` is this rank's
+        slice (a list of numbers) for member ``i``.  Barrier 0: the members are done with their staging
+        buffers (a fast rank must not push the next launch's slices into a buffer that its owner is
+        still summing).  Then slice ``j`` goes straight into slot ``[me]`` of member ``j``'s staging
+        buffer; barrier 1: everything for this rank has arrived; the sum is formed from local memory in
+        member order.  Returns this rank's summed slice, or None after a time-out."""
+        idx, n = team.index(me), len(team)
+        expect = self.team_args(me, team)
+        out = None
+        if self.barrier(me, team, expect, 0):
+            for k in range(1, n):
+                j = (idx + k) % n
+                if jitter:
+                    jitter()
+                if not isinstance(self.staging[team[j]], dict):
+                    self.staging[team[j]] = {}
+                self.staging[team[j]][("slot", idx)] = list(rows[j])
+            if self.barrier(me, team, expect, 1):
+                mine = self.staging[me] if isinstance(self.staging[me], dict) else {}
+                parts = [rows[idx] if i == idx else mine[("slot", i)] for i in range(n)]
+                if jitter:
+                    jitter()
+                out = [sum(vals) for vals in zip(*parts)]
+        self.advance(me, team, 2)
+        return out
+
+    def all_reduce_push(self, me, team, value, jitter=None):
+        """One launch of the two-shot all-reduce of a team of two.  The input is staged in this rank's
+        buffer; barrier 0; this rank sums ITS half of the vector from both buffers and writes the sums
+        into its output and, in place, into the other rank's staging buffer (that half of the other
+        rank's input has just been read by the one reader it has); barrier 1; the other half of the
+        result is now in this rank's own staging buffer.  No third barrier: after barrier 1 nobody
+        touches the other rank's buffer any more."""
+        assert len(team) == 2
+        idx = team.index(me)
+        other = team[1 - idx]
+        self.staging[me] = list(value)
+        expect = self.team_args(me, team)
+        n = len(value)
+        half = (n + 1) // 2
+        lo, hi = (0, half) if idx == 0 else (half, n)
+        out = None
+        if self.barrier(me, team, expect, 0):
+            out = [None] * n
+            for v in range(lo, hi):
+                s = self.staging[team[0]][v] + self.staging[team[1]][v]
+                if jitter:
+                    jitter()
+                self.staging[other][v] = s
+                out[v] = s
+            if self.barrier(me, team, expect, 1):
+                for v in list(range(0, lo)) + list(range(hi, n)):
+                    out[v] = self.staging[me][v]
+            else:
+                out = None
+        self.advance(me, team, 2)
+        return out
+
+
 def run_ranks(world: World, fn):
     """Runs ``fn(rank)`` on one thread per rank; returns the results (exceptions re-raised)."""
     results, errors = [None] * world.n, []

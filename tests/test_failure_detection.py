@@ -257,3 +257,55 @@ def test_flag_protocol_withheld_signal_times_out_and_fails_fast():
     # out as well: a failure on one rank surfaces on its peers, which is why the heap is then poisoned
     assert b1 == [0, 1] and b2 is None
     assert world.status[1].code == pm.TIMEOUT_CODE and world.status[1].where in (100, 101)
+
+
+def test_push_collectives_keep_every_launch_apart():
+    """The reduce-scatter that pushes slices into the owners' staging buffers and the two-rank
+    all-reduce that pushes its sums: many launches in a row with ranks running ahead of each other at
+    random; every launch must see its own data only (a missing barrier would let a fast rank's next
+    launch overwrite a slice that its owner has not summed yet: with the first barrier taken out of
+    the model, about half of these launches return wrong sums), mixed with all-gathers on the same
+    counters."""
+    import random
+
+    from distdl_b200.parallel import protocol_model as pm
+    n, launches, length = 4, 60, 6
+    world = pm.World(n, ctas=2, spin_limit_s=30.0)
+    team = list(range(n))
+
+    def rank_program(me):
+        rng = random.Random(me)
+
+        def jitter():
+            if rng.random() < 0.3:
+                time.sleep(rng.random() * 0.002)
+        for it in range(launches):
+            rows = [[1000 * it + 10 * me + j + v for v in range(length)] for j in range(n)]
+            got = world.reduce_scatter_push(me, team, rows, jitter)
+            want = [sum(1000 * it + 10 * r + me + v for r in range(n)) for v in range(length)]
+            assert got == want, (me, it, got, want)
+            if it % 7 == 0:
+                assert world.all_gather(me, team, (me, it)) == [(r, it) for r in team]
+        return True
+    assert all(pm.run_ranks(world, rank_program))
+    assert all(world.status[r].code == 0 for r in range(n))
+    # the two-rank all-reduce, odd length (unequal halves), on a sub-team while the others idle
+    world = pm.World(n, ctas=2, spin_limit_s=30.0)
+    pair = [2, 1]
+
+    def pair_program(me):
+        if me not in pair:
+            return True
+        rng = random.Random(7 + me)
+
+        def jitter():
+            if rng.random() < 0.3:
+                time.sleep(rng.random() * 0.002)
+        for it in range(launches):
+            value = [100 * it + me + 3 * v for v in range(7)]
+            got = world.all_reduce_push(me, pair, value, jitter)
+            want = [200 * it + pair[0] + pair[1] + 6 * v for v in range(7)]
+            assert got == want, (me, it, got, want)
+        return True
+    assert all(pm.run_ranks(world, pair_program))
+    assert world.steps_done[1][2] == 2 * launches and world.steps_done[0][1] == 0
