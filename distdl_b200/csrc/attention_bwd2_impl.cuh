@@ -371,7 +371,11 @@ struct QSmem {
 struct QBarriers {
   uint64_t qdo_full;
   uint64_t k_full[K_STAGES], k_empty[K_STAGES], v_full[V_STAGES], v_empty[V_STAGES];
-  uint64_t s_full, p_done, dp_full[2], ds_full, acc_done;
+  // dp_full / ds_full: one per dP buffer.  A softmax warp may run one iteration ahead of another (S and dP
+  // of the next key tile are issued as soon as S of this one is in registers); with a single "dS written"
+  // barrier its arrival for the next tile would complete the phase that the slower warp has not arrived
+  // for yet (ops/attention_bwd_model.py reproduces that).
+  uint64_t s_full, p_done, dp_full[2], ds_full[2], acc_done;
   uint32_t tmem_base;
   volatile int abort_flag;
 };
@@ -406,7 +410,7 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     for (int s = 0; s < V_STAGES; ++s) { mbar_init(&bar->v_full[s], 1); mbar_init(&bar->v_empty[s], 1); }
     mbar_init(&bar->s_full, 1); mbar_init(&bar->p_done, SOFTMAX_WARPS);
     mbar_init(&bar->dp_full[0], 1); mbar_init(&bar->dp_full[1], 1);
-    mbar_init(&bar->ds_full, SOFTMAX_WARPS);
+    mbar_init(&bar->ds_full[0], SOFTMAX_WARPS); mbar_init(&bar->ds_full[1], SOFTMAX_WARPS);
     mbar_init(&bar->acc_done, 1);
     bar->abort_flag = 0;
     mbar_fence_init();
@@ -475,7 +479,7 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           ok = issue_s_dp(jj + 1);
           if (!ok) break;
         }
-        ok = mbar_wait(&bar->ds_full, jj & 1, &bar->abort_flag, p.status, 157);
+        ok = mbar_wait(&bar->ds_full[jj & 1], (jj >> 1) & 1, &bar->abort_flag, p.status, 157);
         if (!ok) break;
         tc_fence_after();
         issue_from_tmem(tdQ, tdP0 + (jj & 1) * 128, aK + (jj % K_STAGES) * T_BYTES, jj > 0);   // dQ += dS K
@@ -533,7 +537,7 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bar->ds_full);
+      if (lane == 0) mbar_arrive(&bar->ds_full[jj & 1]);
     }
     if (ok) ok = mbar_wait(&bar->acc_done, 0, &bar->abort_flag, p.status, 160);
     if (ok) {
