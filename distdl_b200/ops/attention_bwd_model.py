@@ -1,12 +1,12 @@
-"""A host model of the pipelines inside the attention backward kernels (``csrc/attention_bwd2_impl.cuh``),
-for tests without a GPU.
+"""A host model of the pipelines inside the attention kernels (``csrc/attention_bwd2_impl.cuh`` and the
+two-tile forward kernel ``csrc/attention_fwd2_impl.cuh``), for tests without a GPU.
 
 The kernels are warp-specialised: one thread issues TMA loads, one thread issues tensor-core products
 (which execute in issue order and signal completion through ``tcgen05.commit``), sixteen warps do the
 softmax arithmetic; they hand tiles to each other through mbarriers whose phases are waited for by
 parity.  What can go wrong in such a design is not arithmetic but scheduling: a barrier that is waited
 for with the wrong parity, a tile that is overwritten before its last reader is through, a cycle of
-waits.  This module restates the two kernels' schedules with the same barriers, the same parities and
+waits.  This module restates the kernels' schedules with the same barriers, the same parities and
 the same issue order, one Python thread per role, tiles as small NumPy arrays, and random delays in
 every role, so that
 
@@ -324,3 +324,125 @@ def dq_tile(Q, dO, K, V, lse2, delta, scale, causal_diag_at=None, softmax_warps=
     finally:
         pipe.close()
     return tmem["dQ"] * scale
+
+
+def fwd_pair(Q, K, V, n, scale, diag=(None, None), row_warps=4, seed=0, grow_threshold=8.0, slow_warp=None):
+    """The two-tile forward kernel for ONE pair of query tiles: ``Q`` = two ``[BQ, D]`` tiles, ``K`` /
+    ``V`` = lists of ``[BKV, D]`` blocks, ``n = (n0, n1)`` blocks seen by tile 0 / tile 1 (``n1 >= n0``),
+    ``diag[t]`` = the block on which tile ``t`` applies the causal mask.  Scores, probabilities and the
+    output accumulators live in "tensor memory"; the output is rescaled lazily (only when a row's
+    running maximum has grown by more than ``grow_threshold`` in base-2 exponent units).  Returns
+    ``(O, lse)`` with ``O`` = ``[2, BQ, D]`` and ``lse`` = ``[2, BQ]`` (natural logarithm)."""
+    n0, n1 = n
+    BQ, D = Q[0].shape
+    BKV = K[0].shape[0]
+    rows_per = BQ // row_warps
+    c = scale * 1.4426950408889634
+    ST = 2
+    bar = {"q_full": MBarrier(1, "q_full")}
+    for name in ("k_full", "k_empty", "v_full", "v_empty"):
+        bar[name] = [MBarrier(1, f"{name}[{s}]") for s in range(ST)]
+    bar["s_full"] = [MBarrier(1, f"s_full[{t}]") for t in range(2)]
+    bar["p_full"] = [MBarrier(row_warps, f"p_full[{t}]") for t in range(2)]
+    bar["pv_done"] = [MBarrier(1, f"pv_done[{t}]") for t in range(2)]
+    smem = {"Q": [None, None], "K": [None] * ST, "V": [None] * ST}
+    tmem = {"S": [np.zeros((BQ, BKV)), np.zeros((BQ, BKV))], "O": [np.zeros((BQ, D)), np.zeros((BQ, D))]}
+    out, lse = np.zeros((2, BQ, D)), np.zeros((2, BQ))
+    pipe = TensorPipe(random.Random(seed))
+
+    def tma():
+        rng = random.Random(seed + 1)
+        smem["Q"] = [Q[0].copy(), Q[1].copy()]
+        bar["q_full"].arrive()
+        for j in range(n1):
+            st, ph = j % ST, (j // ST) & 1
+            bar["k_empty"][st].wait(ph ^ 1)
+            _jitter(rng)
+            smem["K"][st] = K[j].copy()
+            bar["k_full"][st].arrive()
+            bar["v_empty"][st].wait(ph ^ 1)
+            _jitter(rng)
+            smem["V"][st] = V[j].copy()
+            bar["v_full"][st].arrive()
+
+    def mma():
+        rng = random.Random(seed + 2)
+
+        def issue_s(t, j):
+            st = j % ST
+            pipe.issue(lambda: tmem["S"][t].__setitem__(slice(None), smem["Q"][t] @ smem["K"][st].T))
+            pipe.commit(bar["s_full"][t])
+
+        def issue_pv(t, j):
+            st = j % ST
+
+            def fn():
+                prod = tmem["S"][t] @ smem["V"][st]             # P from tensor memory
+                tmem["O"][t][:] = prod if j == 0 else tmem["O"][t] + prod
+            pipe.issue(fn)
+            pipe.commit(bar["pv_done"][t])
+        bar["q_full"].wait(0)
+        bar["k_full"][0].wait(0)
+        issue_s(0, 0)
+        issue_s(1, 0)
+        for j in range(n1):
+            st, ph = j % ST, (j // ST) & 1
+            stn, phn = (j + 1) % ST, ((j + 1) // ST) & 1
+            bar["v_full"][st].wait(ph)
+            k_next_ready = False
+            for t in range(2):
+                nt = n0 if t == 0 else n1
+                if j >= nt:
+                    continue
+                bar["p_full"][t].wait(j & 1)
+                _jitter(rng)
+                issue_pv(t, j)
+                if j + 1 < nt:
+                    if not k_next_ready:
+                        bar["k_full"][stn].wait(phn)
+                        k_next_ready = True
+                    issue_s(t, j + 1)
+            pipe.commit(bar["v_empty"][st])
+            pipe.commit(bar["k_empty"][st])
+
+    def softmax(t, w):
+        def run():
+            rng = random.Random(seed + 10 + 4 * t + w)
+            mine = slice(w * rows_per, (w + 1) * rows_per)
+            rows = np.arange(w * rows_per, (w + 1) * rows_per)[:, None]
+            nt = n0 if t == 0 else n1
+            m_ref = np.full(rows_per, -np.inf)
+            l = np.zeros(rows_per)
+            for j in range(nt):
+                bar["s_full"][t].wait(j & 1)
+                _jitter(rng)
+                s = tmem["S"][t][mine].copy()
+                if diag[t] is not None and j == diag[t]:
+                    s = np.where(np.arange(BKV)[None, :] > rows, -np.inf, s)
+                mx = np.maximum(m_ref, s.max(axis=1))
+                grow = (mx - m_ref) * c > grow_threshold if j > 0 else np.zeros(rows_per, dtype=bool)
+                if j == 0:
+                    m_ref = mx
+                if grow.any():
+                    alpha = np.where(grow, np.exp2((m_ref - mx) * c), 1.0)
+                    m_ref = np.where(grow, mx, m_ref)
+                    l = l * alpha
+                    bar["pv_done"][t].wait((j - 1) & 1)          # O_t is complete up to block j - 1
+                    _jitter(rng)
+                    tmem["O"][t][mine] *= alpha[:, None]
+                p = np.exp2(s * c - (m_ref * c)[:, None])
+                l = l + p.sum(axis=1)
+                if (t, w) == slow_warp:
+                    time.sleep(0.01)                             # a warp that lags behind the others
+                tmem["S"][t][mine] = p                           # P over S, this warp's rows
+                bar["p_full"][t].arrive()
+            bar["pv_done"][t].wait((nt - 1) & 1)
+            out[t, mine] = tmem["O"][t][mine] / l[:, None]
+            lse[t, mine] = m_ref * scale + np.log(l)
+        return run
+
+    try:
+        _run_roles([tma, mma] + [softmax(t, w) for t in range(2) for w in range(row_warps)])
+    finally:
+        pipe.close()
+    return out, lse

@@ -105,3 +105,35 @@ def test_a_softmax_warp_that_lags_an_iteration_behind():
     dQ = sum((_p(q, Ks[j], l2[0], None) * (do @ Vs[j].T - dl[0][:, None]) * SCALE) @ Ks[j] for j in range(n))
     assert np.allclose(model.dq_tile(q, do, Ks, Vs, l2[0], dl[0], SCALE, slow_warp=1), dQ)
     assert not np.allclose(model.dq_tile(q, do, Ks, Vs, l2[0], dl[0], SCALE, slow_warp=1, ds_full_buffers=1), dQ)
+
+
+@pytest.mark.parametrize("qp,causal", [(0, True), (1, True), (3, True), (0, False), (2, False)])
+def test_forward_pair_schedule_terminates_and_matches(qp, causal):
+    """The two-tile forward kernel: both tiles alternate on the tensor pipe, the causal tiles see
+    different numbers of blocks (2 qp + 1 and 2 qp + 2), scores that grow from block to block force
+    the lazy rescale of the output accumulator."""
+    rng = np.random.default_rng(50 + qp)
+    nkv = 2 * qp + 2 if causal else 5
+    n = (2 * qp + 1, 2 * qp + 2) if causal else (nkv, nkv)
+    diag = (2 * qp, 2 * qp + 1) if causal else (None, None)
+    Q = _tiles(rng, 2)
+    K = [rng.standard_normal((BT, D)) * (1 + 4 * j) for j in range(nkv)]        # later blocks score higher
+    V = _tiles(rng, nkv)
+    want_o, want_l = np.zeros((2, BT, D)), np.zeros((2, BT))
+    for t in range(2):
+        s = np.concatenate([Q[t] @ K[j].T for j in range(n[t])], axis=1) * SCALE
+        if causal:
+            cols = np.arange(n[t] * BT)[None, :]
+            s = np.where(cols > (diag[t] * BT + np.arange(BT))[:, None], -np.inf, s)
+        m = s.max(axis=1, keepdims=True)
+        e = np.exp(s - m)
+        want_o[t] = (e / e.sum(axis=1, keepdims=True)) @ np.concatenate(V[:n[t]], axis=0)
+        want_l[t] = (m + np.log(e.sum(axis=1, keepdims=True)))[:, 0]
+    for seed in range(3):
+        o, lse = model.fwd_pair(Q, K, V, n, SCALE, diag=diag, seed=seed, grow_threshold=2.0)
+        assert np.allclose(o, want_o, rtol=1e-9, atol=1e-9), (qp, causal, seed)
+        assert np.allclose(lse, want_l, rtol=1e-9, atol=1e-9)
+    # one softmax warp of tile 1 lagging: S of the next block is only issued after all four warps of a tile
+    # have written their probabilities, so nobody can run ahead of it
+    o, lse = model.fwd_pair(Q, K, V, n, SCALE, diag=diag, grow_threshold=2.0, slow_warp=(1, 2))
+    assert np.allclose(o, want_o, rtol=1e-9, atol=1e-9) and np.allclose(lse, want_l, rtol=1e-9, atol=1e-9)
