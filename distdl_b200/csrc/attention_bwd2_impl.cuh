@@ -374,7 +374,7 @@ struct QBarriers {
   // dp_full / ds_full: one per dP buffer.  A softmax warp may run one iteration ahead of another (S and dP
   // of the next key tile are issued as soon as S of this one is in registers); with a single "dS written"
   // barrier its arrival for the next tile would complete the phase that the slower warp has not arrived
-  // for yet (ops/attention_bwd_model.py reproduces that).
+  // for yet (ops/attention_model.py reproduces that).
   uint64_t s_full, p_done, dp_full[2], ds_full[2], acc_done;
   uint32_t tmem_base;
   volatile int abort_flag;

@@ -4,7 +4,7 @@ every sweep length must terminate and give the directly computed gradients."""
 import numpy as np
 import pytest
 
-from distdl_b200.ops import attention_bwd_model as model
+from distdl_b200.ops import attention_model as model
 
 BT, D = 8, 4
 SCALE = 0.5
